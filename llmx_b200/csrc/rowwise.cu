@@ -1,0 +1,192 @@
+// Row-wise kernels: embedding gather, RMSNorm, per-head norm + rotation + cache write, SwiGLU.
+//
+// All arithmetic is 32-bit: sums of squares, the reciprocal root, the rotation
+// and the activation.  Only what is stored for a matrix product or in the cache
+// is rounded to bfloat16 on the bfloat16 path.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// Embedding: x[r, :] = table[ids[r], :] widened to 32-bit.
+// Reference: llmx_gather (src/backends/gpu/kernels/f32.gpu:747-751).  Ids are checked
+// on the host before the step; an id outside the table writes a zero row here.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ x,
+                             int width, int table_rows) {
+    const int r = blockIdx.x;
+    const int id = ids[r];
+    float* dst = x + (size_t)r * width;
+    if (id < 0 || id >= table_rows) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = 0.0f;
+        return;
+    }
+    const T* src = table + (size_t)id * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = to_float(src[i]);
+}
+
+LLMX_EXPORT int llmx_embed(const void* table, int table_dtype, const int* ids, float* x, int rows, int width,
+                           int table_rows, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (table_dtype == LLMX_BF16)
+        embed_kernel<<<rows, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, x, width, table_rows);
+    else
+        embed_kernel<<<rows, 256, 0, stream>>>((const float*)table, ids, x, width, table_rows);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm: s = sum x_i^2; r = 1 / sqrt(s / n + eps); y_i = x_i * (r * w_i)
+// (the grouping x * (r * w) is the reference's, src/backends/cpu/cpu_backend.hpp:1437-1459).
+// `row_index` (optional) picks the source rows: y[i] = norm(x[row_index[i]]), which folds
+// the head's row gather (src/model/arch/blocks.hpp:267-272) into its norm.
+// ---------------------------------------------------------------------------
+template <typename OutT>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, OutT* __restrict__ y,
+                               const int* __restrict__ row_index, int width, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const float* src = x + (size_t)(row_index ? row_index[r] : r) * width;
+    float s = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = src[i];
+        s = fmaf(v, v, s);
+    }
+    s = block_sum(s, scratch);
+    const float rr = 1.0f / sqrtf(s / (float)width + eps);
+    OutT* dst = y + (size_t)r * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_float<OutT>(src[i] * (rr * w[i]));
+}
+
+LLMX_EXPORT int llmx_rmsnorm(const float* x, const float* w, void* y, int out_dtype, const int* row_index, int rows,
+                             int width, float eps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (out_dtype == LLMX_BF16)
+        rmsnorm_kernel<<<rows, threads, 0, stream>>>(x, w, (__nv_bfloat16*)y, row_index, width, eps);
+    else
+        rmsnorm_kernel<<<rows, threads, 0, stream>>>(x, w, (float*)y, row_index, width, eps);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Per-head norm, rotation and cache write, one warp per (row, head).
+//
+// For a query head: RMSNorm over the head's D values with q_weight (skipped when null),
+// rotate the first 2*rot_half values by the row's position, store to q_out.
+// For a key head: the same with k_weight, stored to the key plane of the row's cache
+// slot; the value head is stored raw to the value plane.
+// Rotation pairs (i, i + rot_half), i < rot_half ("rotate half"):
+//   a' = fma(-b, sin_i, a * cos_i);  b' = fma(a, sin_i, b * cos_i)
+// (src/backends/cpu/cpu_backend.hpp:1461-1480, fused form f32.gpu:722-744).
+// Cache layout: [page][plane][kv_head][slot][D]; `slots[row]` = page * page_size + slot,
+// or negative to skip the write (a layer that reads another layer's cache).
+// ---------------------------------------------------------------------------
+template <typename QT, typename KVT>
+__global__ void head_norm_rope_kernel(const float* __restrict__ qkv, int qkv_stride, int k_offset, int v_offset,
+                                      const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+                                      float eps, const float* __restrict__ cos_table, const float* __restrict__ sin_table,
+                                      int rot_half, const int* __restrict__ positions, const int* __restrict__ slots,
+                                      QT* __restrict__ q_out, KVT* __restrict__ cache, int rows, int heads, int kv_heads,
+                                      int head_dim, int page_size) {
+    extern __shared__ float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int per_row = heads + kv_heads;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (item >= (long long)rows * per_row) return;
+    const int row = (int)(item / per_row), j = (int)(item % per_row);
+    const bool is_q = j < heads;
+    const int g = is_q ? 0 : j - heads;
+    float* buf = smem + warp * head_dim;
+    const float* src = qkv + (size_t)row * qkv_stride + (is_q ? j * head_dim : k_offset + g * head_dim);
+    const float* weight = is_q ? q_weight : k_weight;
+
+    int slot = 0;
+    if (!is_q) {
+        slot = slots[row];
+        if (slot < 0) return;
+    }
+    float s = 0.0f;
+    for (int d = lane; d < head_dim; d += 32) {
+        const float v = src[d];
+        buf[d] = v;
+        s = fmaf(v, v, s);
+    }
+    if (weight) {
+        s = warp_sum(s);
+        const float rr = 1.0f / sqrtf(s / (float)head_dim + eps);
+        __syncwarp();
+        for (int d = lane; d < head_dim; d += 32) buf[d] = buf[d] * (rr * weight[d]);
+    }
+    __syncwarp();
+    size_t key_base = 0, value_base = 0;
+    if (!is_q) {
+        const int page = slot / page_size, off = slot % page_size;
+        key_base = ((((size_t)page * 2 + 0) * kv_heads + g) * page_size + off) * head_dim;
+        value_base = ((((size_t)page * 2 + 1) * kv_heads + g) * page_size + off) * head_dim;
+    }
+    const float* cs = cos_table ? cos_table + (size_t)positions[row] * rot_half : nullptr;
+    const float* sn = cos_table ? sin_table + (size_t)positions[row] * rot_half : nullptr;
+    for (int d = lane; d < head_dim; d += 32) {
+        float out;
+        if (cs && d < 2 * rot_half) {
+            const int i = d < rot_half ? d : d - rot_half;
+            const float a = buf[i], b = buf[i + rot_half];
+            out = d < rot_half ? fmaf(-b, sn[i], a * cs[i]) : fmaf(a, sn[i], b * cs[i]);
+        } else {
+            out = buf[d];
+        }
+        if (is_q) q_out[(size_t)row * heads * head_dim + j * head_dim + d] = from_float<QT>(out);
+        else cache[key_base + d] = from_float<KVT>(out);
+    }
+    if (!is_q) {
+        const float* vsrc = qkv + (size_t)row * qkv_stride + v_offset + g * head_dim;
+        for (int d = lane; d < head_dim; d += 32) cache[value_base + d] = from_float<KVT>(vsrc[d]);
+    }
+}
+
+LLMX_EXPORT int llmx_head_norm_rope_kv(const float* qkv, int qkv_stride, int k_offset, int v_offset,
+                                       const float* q_weight, const float* k_weight, float eps,
+                                       const float* cos_table, const float* sin_table, int rot_half,
+                                       const int* positions, const int* slots, void* q_out, int q_dtype, void* cache,
+                                       int cache_dtype, int rows, int heads, int kv_heads, int head_dim,
+                                       int page_size, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (head_dim <= 0 || rot_half < 0 || 2 * rot_half > head_dim || q_dtype != cache_dtype) return LLMX_ERR_BAD_ARGUMENT;
+    const int warps = 4;
+    const long long items = (long long)rows * (heads + kv_heads);
+    const unsigned blocks = (unsigned)((items + warps - 1) / warps);
+    const size_t shmem = (size_t)warps * head_dim * sizeof(float);
+    if (q_dtype == LLMX_BF16)
+        head_norm_rope_kernel<<<blocks, warps * 32, shmem, stream>>>(
+            qkv, qkv_stride, k_offset, v_offset, q_weight, k_weight, eps, cos_table, sin_table, rot_half, positions,
+            slots, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, rows, heads, kv_heads, head_dim, page_size);
+    else
+        head_norm_rope_kernel<<<blocks, warps * 32, shmem, stream>>>(
+            qkv, qkv_stride, k_offset, v_offset, q_weight, k_weight, eps, cos_table, sin_table, rot_half, positions,
+            slots, (float*)q_out, (float*)cache, rows, heads, kv_heads, head_dim, page_size);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// SwiGLU: act = silu(g) * u, silu(g) = g / (1 + exp(-g))
+// (src/backends/cpu/cpu_backend.hpp:1677; f32.gpu:596-631).  `gu` holds a row's gate
+// values then its up values ([rows, 2 * width]).
+// ---------------------------------------------------------------------------
+template <typename OutT>
+__global__ void swiglu_kernel(const float* __restrict__ gu, OutT* __restrict__ act, long long total, int width) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long r = i / width;
+    const int c = (int)(i % width);
+    const float g = gu[r * 2 * width + c], u = gu[r * 2 * width + width + c];
+    act[i] = from_float<OutT>(g / (1.0f + expf(-g)) * u);
+}
+
+LLMX_EXPORT int llmx_swiglu(const float* gu, void* act, int out_dtype, int rows, int width, cudaStream_t stream) {
+    const long long total = (long long)rows * width;
+    if (total <= 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (out_dtype == LLMX_BF16) swiglu_kernel<<<blocks, 256, 0, stream>>>(gu, (__nv_bfloat16*)act, total, width);
+    else swiglu_kernel<<<blocks, 256, 0, stream>>>(gu, (float*)act, total, width);
+    return launch_status();
+}

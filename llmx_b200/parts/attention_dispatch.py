@@ -1,0 +1,27 @@
+"""Which attention kernel runs for which rows of a step.
+
+The float32 path, and any shape the tiled kernels do not take, runs the plain
+kernel (one block per row and head).  On the bfloat16 path requests that bring
+one or a few rows run the split-KV decode kernel and requests that bring a
+portion of a prompt run the tiled prefill kernel; both read the same pages and
+differ only in rounding.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops
+from .base import GroupView, StepBatch
+
+
+def paged_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, step: StepBatch, group: GroupView,
+                    heads: int, kv_heads: int, head_dim: int, window: Optional[int], scale: float) -> None:
+    if q.dtype is torch.bfloat16:
+        from .. import ops_attn
+        if ops_attn.supported(heads, kv_heads, head_dim, cache.shape[3]):
+            ops_attn.paged_attention_bf16(q, cache, out, step, group, heads, kv_heads, head_dim, window, scale)
+            return
+    ops.attention_plain(q, cache, out, step.row_request, step.positions, group.block_tables, heads, kv_heads,
+                        head_dim, window, scale)

@@ -1,0 +1,40 @@
+"""A weight matrix [out, in] and its product with the rows of a step.
+
+`Linear` is the one place that decides which matrix-product kernel runs:
+on the float32 path the plain CUDA-core product; on the bfloat16 path the
+tcgen05 tensor-core product, or the plain one when the input width is not a
+multiple of 8 elements (a TMA descriptor needs row strides that are multiples
+of 16 bytes).  The choice depends on the weight's shape and the path alone,
+never on the batch, so a row's result does not depend on what it was batched
+with.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops
+from .base import Precision
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor, precision: Precision):
+        # A weight stored in 32-bit is rounded once for the bfloat16 path; a bfloat16 weight
+        # is widened exactly for the float32 path.
+        self.weight = weight.to(precision.act).contiguous()
+        self.out_features, self.in_features = self.weight.shape
+        self.precision = precision
+        self.tensor_core = precision.act is torch.bfloat16 and self.in_features % 8 == 0
+        self._tc = None
+
+    def __call__(self, a: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
+        """out (+)= a @ W.T; a [rows, in] of the path's activation type; out float32 [rows, out]."""
+        if out is None:
+            if accumulate:
+                raise ValueError("accumulate needs an output to add to")
+            out = torch.empty((a.shape[0], self.out_features), dtype=torch.float32, device=a.device)
+        if self.tensor_core:
+            from .. import ops_tc
+            return ops_tc.gemm_tc(a, self.weight, out, accumulate)
+        return ops.gemm_plain(a, self.weight, out, accumulate)

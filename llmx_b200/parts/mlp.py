@@ -1,0 +1,41 @@
+"""Feed-forward parts.  GatedMLP: residual += (act(h Wg^T) * (h Wu^T)) Wd^T.
+
+With act = silu this is the SwiGLU block (src/model/arch/blocks.hpp:101-106):
+silu(g) = g / (1 + exp(-g)) in 32-bit.  Gate and up weights are stacked by rows
+so one product gives both.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from .. import ops
+from ..weights.spec import TensorSpec
+from .base import Part, Precision, StepBatch
+from .linear import Linear
+
+
+class GatedMLP(Part):
+    def __init__(self, hidden: int, intermediate: int, activation: str = "silu"):
+        if activation != "silu":
+            raise ValueError(f"activation {activation!r} has no kernel here (silu)")
+        self.hidden, self.intermediate, self.activation = int(hidden), int(intermediate), activation
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {
+            "gate_proj.weight": TensorSpec((self.intermediate, self.hidden)),
+            "up_proj.weight": TensorSpec((self.intermediate, self.hidden)),
+            "down_proj.weight": TensorSpec((self.hidden, self.intermediate)),
+        }
+
+    def load(self, tensors, precision: Precision) -> None:
+        super().load(tensors, precision)
+        self.gate_up = Linear(torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0), precision)
+        self.down = Linear(tensors["down_proj.weight"], precision)
+
+    def forward(self, h: torch.Tensor, step: StepBatch, residual: torch.Tensor) -> None:
+        gu = self.gate_up(h)
+        act = torch.empty((h.shape[0], self.intermediate), dtype=self.precision.act, device=h.device)
+        ops.swiglu(gu, act)
+        self.down(act, out=residual, accumulate=True)
