@@ -36,5 +36,7 @@ class Linear:
             out = torch.empty((a.shape[0], self.out_features), dtype=torch.float32, device=a.device)
         if self.tensor_core:
             from .. import ops_tc
-            return ops_tc.gemm_tc(a, self.weight, out, accumulate)
+            if self._tc is None:
+                self._tc = ops_tc.WeightMap(self.weight)
+            return ops_tc.gemm_tc(a, self.weight, out, accumulate, wmap=self._tc)
         return ops.gemm_plain(a, self.weight, out, accumulate)
