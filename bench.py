@@ -1,0 +1,259 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at Qwen3-8B sizes, random weights, one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--context C]
+
+A "step" is one decode step: every live request brings one token.  The default run has the layer
+sizes of Qwen3-8B (36 layers unless --layers says otherwise), a batch of 8 and a context of 8,192
+tokens per request.  One JSON line is printed:
+
+  value        decoded tokens a second, the K steps timed on the device with CUDA events
+  e2e          the same through the Python entry point: host token ids in, sampled ids out, every step
+  prefill      a 2,048-token prompt from an empty cache: tokens a second and the fraction of the
+               measured bf16 peak its flops reach
+  roofline     the bytes a decode step must read (every weight once, the cache of the live requests)
+               divided by its time, against the measured copy bandwidth
+  points       decode tokens a second at batch 1 and batch 64
+
+The histories of the decoding requests are synthetic cache contents (pages taken and filled with
+random values): what a decode step costs depends on how much it reads, not on what it reads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=36, hidden_size=4096,
+                intermediate_size=12288, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                max_position_embeddings=40960)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.path = os.path.join(tempfile.gettempdir(), f"llmx_clocks_{os.getpid()}.csv")
+
+    def start(self):
+        try:
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.out,
+                                         stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.proc.wait()
+        self.out.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 7:
+                    continue
+                try:
+                    sm.append(float(parts[0]))
+                    mx.append(float(parts[1]))
+                except ValueError:
+                    continue
+                for n, v in zip(names, parts[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+        os.remove(self.path)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_arm():
+    why = ("mxxm-t/llmx is a C++/CMake project with no Python packaging and no sm_100 build target; "
+           "pip install of /root/reference fails (neither setup.py nor pyproject.toml)")
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--layers", type=int, default=36, help="fewer layers than the model has (both numbers are reported)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--no-points", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU; --gpus {args.gpus} is not built in this engine")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    from llmx_b200 import ops, ops_tc
+    from llmx_b200.config import Qwen3Config
+    from llmx_b200.engine import Engine, EngineOptions, StepEntry
+    from llmx_b200.engine.decode_loop import DecodeSession
+    from llmx_b200.sampling import RequestSampling, SamplingParams, sample
+
+    pk = peaks()
+    raw = dict(QWEN3_8B)
+    raw["num_hidden_layers"] = args.layers
+    cfg = Qwen3Config.from_dict(raw)
+    page = 16
+    max_batch = max(args.batch, 1 if args.no_points else 64)
+    per_request = -(-(args.context + args.steps + args.warmup + 64) // page) * page
+    kv_tokens = max(max_batch * per_request, args.prefill_tokens + page)
+    torch.cuda.set_device(0)
+    engine = Engine.from_config(cfg, seed=0, options=EngineOptions(dtype="bfloat16", kv_tokens=kv_tokens,
+                                                                   page_size=page, max_requests=max_batch))
+    model = engine.model
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1)
+    for g in engine.cache.groups:          # synthetic histories: random keys and values
+        for layer in range(g.storage.shape[0]):
+            g.storage[layer].normal_(0.0, 1.0, generator=gen)
+    host_gen = torch.Generator()
+    host_gen.manual_seed(2)
+
+    def ids(n):
+        return torch.randint(0, cfg.vocab_size, (n,), generator=host_gen).tolist()
+
+    # ---- bytes a decode step must read ------------------------------------------------------------
+    E, F, Q, KV, V, L = cfg.hidden_size, cfg.intermediate_size, cfg.q_width, cfg.kv_width, cfg.vocab_size, args.layers
+    weight_bytes = 2 * (L * ((Q + 2 * KV) * E + E * Q + 2 * F * E + E * F) + V * E) + 4 * (L * (2 * E + 2 * cfg.head_dim) + E)
+    kv_bytes_per_token = L * 2 * KV * 2
+
+    def decode_bytes(batch, context):
+        return weight_bytes + batch * E * 2 + batch * context * kv_bytes_per_token
+
+    def run_decode(batch, steps, warmup, e2e):
+        """Tokens a second and ms a step for `batch` requests at `context` tokens each."""
+        rids = [("bench", batch, i) for i in range(batch)]
+        for rid in rids:                                    # take pages for the history without running it
+            rc = engine.cache.new_request(rid)
+            rc.prepare(args.context)
+            rc.commit()
+        session = DecodeSession(engine, rids)
+        tokens = ids(batch)
+        states = [RequestSampling(SamplingParams(temp=0.0, top_k=0, top_p=1.0)) for _ in rids]
+        launches0 = ops.launch_count()
+        try:
+            if e2e:
+                for _ in range(warmup):
+                    tokens = sample(session.step(tokens), states)
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                for _ in range(steps):
+                    tokens = sample(session.step(tokens), states)     # host ids in, host ids out
+                torch.cuda.synchronize()
+                ms = (time.perf_counter() - t0) * 1e3 / steps
+            else:
+                for _ in range(warmup):
+                    session.step(tokens)
+                torch.cuda.synchronize()
+                launches0 = ops.launch_count()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(steps):
+                    session.step(tokens)
+                e1.record()
+                torch.cuda.synchronize()
+                ms = e0.elapsed_time(e1) / steps
+            launches = ops.launch_count() - launches0
+            h2d = session.h2d_bytes_per_step
+        finally:
+            session.close()
+            for rid in rids:
+                engine.end(rid)
+        return batch * 1e3 / ms, ms, launches, h2d
+
+    def run_prefill(tokens_n, reps, warmup):
+        prompt = ids(tokens_n)
+        times = []
+        for i in range(warmup + reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            engine.step([StepEntry("prefill", prompt, [tokens_n - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            engine.end("prefill")
+            if i >= warmup:
+                times.append(e0.elapsed_time(e1))
+        ms = sum(times) / len(times)
+        T = tokens_n
+        flops = L * (2 * T * E * (Q + 2 * KV) + 2 * T * Q * E + 2 * T * E * 2 * F + 2 * T * F * E) \
+            + L * 2 * cfg.num_attention_heads * cfg.head_dim * T * T + 2 * V * E
+        return T * 1e3 / ms, ms, flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops"]
+
+    clocks = ClockSampler()
+    clocks.start()
+    value, ms, launches, _ = run_decode(args.batch, args.steps, args.warmup, e2e=False)
+    clock_record = clocks.stop()
+    e2e_value, e2e_ms, _, h2d = run_decode(args.batch, args.steps, args.warmup, e2e=True)
+    pf_value, pf_ms, pf_frac = run_prefill(args.prefill_tokens, 3, 3)
+    points = {}
+    if not args.no_points:
+        points["decode_b1"] = round(run_decode(1, args.steps, args.warmup, e2e=False)[0], 1)
+        points["decode_b64"] = round(run_decode(64, max(args.steps // 2, 8), args.warmup, e2e=False)[0], 1)
+    ops_tc.check_errors()
+    achieved = decode_bytes(args.batch, args.context) / (ms * 1e-3) / 1e9
+    line = {
+        "metric": "decode tok/s at batch 8, context 8192 (Qwen3-8B sizes, bf16, random weights)",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {"model": "Qwen3-8B sizes, random weights", "layers": args.layers, "model_layers": 36,
+                   "hidden": E, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": F, "vocab": V, "global_batch": args.batch,
+                   "seq_len": args.context, "page_size": page, "prefill_tokens": args.prefill_tokens,
+                   "parallelism": "single GPU", "l2": "inputs larger than L2 (weights and cache read each step)",
+                   "history": "synthetic cache contents", "peaks": pk["source"]},
+        "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch},
+        "gpu_launches": launches,
+        "prefill": {"value": round(pf_value, 1), "tokens": args.prefill_tokens, "ms": round(pf_ms, 3),
+                    "frac": round(pf_frac, 4), "peak_tflops": pk["bf16_tflops"]},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clock_record,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,243 @@
+"""The command line: `llmx generate MODEL PROMPT_IDS [flags]` and `llmx bench`.
+
+Names and meanings of the options are the reference's where it has them
+(src/cli/main.cpp:2018-2040 for generate's flags, :544-574 for the execution flags,
+:2193-2204 for bench; short forms :119-120; strictness :100-284): exact numeric forms, a flag
+given twice is refused, a usage error prints the command's page on stderr and exits with 2.
+The tokenizer is outside this engine, so the prompt is token ids: `1,2,3` (commas or spaces),
+or `--file F` right after the model for ids in a file.  The reply is printed as ids.
+"""
+from __future__ import annotations
+
+import sys
+import time
+from typing import Dict, List, Optional, Tuple
+
+USAGE = """usage:
+  llmx generate MODEL (IDS | --file F) [-n N|--max-tokens N] [--temp T] [--topk K] [--topp P] [--min-p P]
+                [--penalty P] [--presence-penalty P] [--frequency-penalty P] [--seed S] [--ignore-eos]
+                [--dtype auto|bf16|f32] [--ubatch N] [--kv-tokens N] [--cache-type-k T] [--cache-type-v T]
+                [--device D] [--verbose]
+      MODEL   a folder with config.json and model.safetensors
+      IDS     the prompt as token ids, e.g. 1,2,3
+  llmx bench --model MODEL [--p P] [--n G] [--r R] [--seqs S] [--depth D] [--dtype auto|bf16|f32]
+      prompt of P tokens (default 512), G generated tokens (default 128), R repeats (default 3),
+      S sequences decoded together (default 1) after a history of D tokens each (default P)
+"""
+
+SHORT = {"-n": "--max-tokens", "-ctk": "--cache-type-k", "-ctv": "--cache-type-v", "-f": "--file"}
+
+
+class UsageError(Exception):
+    pass
+
+
+def _int(flag: str, text: str, lo: int, hi: Optional[int] = None) -> int:
+    if not text or not (text.isdigit() or (text[0] in "+-" and text[1:].isdigit())) or text[0] == "+":
+        raise UsageError(f"{flag}: expected an integer, got '{text}'")
+    v = int(text)
+    if v < lo or (hi is not None and v > hi):
+        raise UsageError(f"{flag}: {v} is out of range")
+    return v
+
+
+def _float(flag: str, text: str, lo: float, hi: float) -> float:
+    try:
+        v = float(text)
+    except ValueError:
+        raise UsageError(f"{flag}: expected a number, got '{text}'") from None
+    if text.strip() != text or text.lower() in ("nan", "inf", "-inf", "+inf", "infinity") or not (lo <= v <= hi):
+        raise UsageError(f"{flag}: {text} is out of range")
+    return v
+
+
+def _ids(text: str) -> List[int]:
+    parts = [p for p in text.replace(",", " ").split()]
+    if not parts:
+        raise UsageError("generate: empty prompt")
+    out = []
+    for p in parts:
+        if not p.isdigit():
+            raise UsageError(f"the prompt is token ids, not '{p}'")
+        out.append(int(p))
+    return out
+
+
+def _dtype(value: str) -> str:
+    table = {"auto": "bfloat16", "bf16": "bfloat16", "f32": "float32"}
+    if value not in table:
+        raise UsageError("--dtype: expected auto, bf16 or f32 (f16 and int8 are not built in this engine)")
+    return table[value]
+
+
+def _parse(argv: List[str], valued: Dict[str, str], switches: Tuple[str, ...]):
+    """Splits argv into ({flag: text}, [positional]); refuses unknown and repeated flags."""
+    given: Dict[str, str] = {}
+    positional: List[str] = []
+    i = 0
+    while i < len(argv):
+        a = argv[i]
+        f = SHORT.get(a, a)
+        if f in valued or f in switches:
+            if f in given:
+                raise UsageError(f"{a} given twice")
+            if f in switches:
+                given[f] = "1"
+            else:
+                if i + 1 >= len(argv):
+                    raise UsageError(f"{a} needs a value")
+                i += 1
+                given[f] = argv[i]
+        elif a.startswith("-") and len(a) > 1 and not a[1:].replace(",", "").isdigit():
+            raise UsageError(f"unknown flag: {a}")
+        else:
+            positional.append(a)
+        i += 1
+    return given, positional
+
+
+def cmd_generate(argv: List[str]) -> int:
+    from ..sampling import SamplingParams
+    valued = {k: k for k in ("--max-tokens", "--temp", "--topk", "--topp", "--min-p", "--penalty", "--presence-penalty",
+                             "--frequency-penalty", "--seed", "--dtype", "--ubatch", "--kv-tokens", "--cache-type-k",
+                             "--cache-type-v", "--device", "--file")}
+    given, pos = _parse(argv, valued, ("--ignore-eos", "--verbose"))
+    if not pos:
+        raise UsageError("missing the model")
+    model = pos[0]
+    if "--file" in given:
+        if len(pos) > 1:
+            raise UsageError(f"a second prompt, '{pos[1]}'")
+        with open(given["--file"], "r", encoding="utf-8") as fh:
+            prompt = _ids(fh.read())
+    else:
+        if len(pos) < 2:
+            raise UsageError("missing the prompt")
+        if len(pos) > 2:
+            raise UsageError(f"a second prompt, '{pos[2]}'; quote the prompt to keep its spaces")
+        prompt = _ids(pos[1])
+    d = SamplingParams()
+    fmax = 3.4028234e38
+    params = SamplingParams(
+        max_tokens=_int("--max-tokens", given.get("--max-tokens", str(d.max_tokens)), 1),
+        temp=_float("--temp", given.get("--temp", repr(d.temp)), 0.0, fmax),
+        top_k=_int("--topk", given.get("--topk", str(d.top_k)), 0, 2 ** 31 - 1),
+        top_p=_float("--topp", given.get("--topp", repr(d.top_p)), 0.0, 1.0),
+        min_p=_float("--min-p", given.get("--min-p", repr(d.min_p)), 0.0, 1.0),
+        penalty=_float("--penalty", given.get("--penalty", repr(d.penalty)), 1.0, fmax),
+        presence_penalty=_float("--presence-penalty", given.get("--presence-penalty", "0"), -2.0, 2.0),
+        frequency_penalty=_float("--frequency-penalty", given.get("--frequency-penalty", "0"), -2.0, 2.0),
+        seed=_int("--seed", given.get("--seed", "0"), 0, 2 ** 64 - 1),
+        ignore_eos="--ignore-eos" in given)
+    dtype = _dtype(given.get("--dtype", "auto"))
+    for f in ("--cache-type-k", "--cache-type-v"):
+        if f in given and given[f] not in ("bf16", "f32"):
+            raise UsageError(f"{f}: the cache has the path's type here (bf16 with --dtype bf16, f32 with --dtype f32)")
+    ubatch = _int("--ubatch", given.get("--ubatch", "512"), 1)
+    kv_tokens = _int("--kv-tokens", given["--kv-tokens"], 1) if "--kv-tokens" in given else None
+    if kv_tokens is None:
+        kv_tokens = -(-(len(prompt) + params.max_tokens) // 64) * 64
+
+    from ..engine.generate import LLM
+    t0 = time.perf_counter()
+    llm = LLM(model, dtype=dtype, kv_tokens=kv_tokens, ubatch=ubatch, max_seqs=1, device=given.get("--device", "cuda:0"))
+    if "--verbose" in given:
+        print(f"load: {time.perf_counter() - t0:.2f} s", file=sys.stderr)
+        print(f"prompt tokens: {len(prompt)}")
+    out = llm.generate([prompt], params)[0]
+    s = llm.stats
+    print("ids: " + ",".join(str(t) for t in out.tokens))
+    pp_ms, tg_ms = s.prefill_seconds * 1e3, s.decode_seconds * 1e3
+    print(f"pp: {len(prompt)} tok, {pp_ms:.0f} ms, {len(prompt) / max(pp_ms / 1e3, 1e-9):.2f} tok/s")
+    print(f"tg: {len(out.tokens)} tok, {tg_ms:.0f} ms, {len(out.tokens) / max(tg_ms / 1e3, 1e-9):.2f} tok/s")
+    if "--verbose" in given:
+        c = llm.engine.cache
+        print(f"kv: allocated {c.storage_bytes()} bytes, pages {c.total_pages()}, finish {out.finish_reason}")
+    return 0
+
+
+def cmd_bench(argv: List[str]) -> int:
+    import torch
+    from ..engine import Engine, EngineOptions, StepEntry
+    valued = {k: k for k in ("--model", "--p", "--n", "--r", "--seqs", "--depth", "--dtype", "--device")}
+    given, pos = _parse(argv, valued, ())
+    if pos:
+        raise UsageError(f"bench takes flags only, not '{pos[0]}'")
+    if "--model" not in given:
+        raise UsageError("bench needs --model (a model folder)")
+    p = _int("--p", given.get("--p", "512"), 1)
+    g = _int("--n", given.get("--n", "128"), 1)
+    reps = _int("--r", given.get("--r", "3"), 1)
+    seqs = _int("--seqs", given.get("--seqs", "1"), 1)
+    depth = _int("--depth", given.get("--depth", str(p)), 1)
+    dtype = _dtype(given.get("--dtype", "auto"))
+    kv = -(-(max(p, depth) + g + 64) // 64) * 64 * seqs
+    engine = Engine.from_dir(given["--model"], EngineOptions(dtype=dtype, kv_tokens=kv, max_requests=seqs,
+                                                             device=given.get("--device", "cuda:0")))
+    vocab = engine.model.vocab_size
+    # Fixed ids spread over the vocabulary (the reference's bench_ids, src/cli/main.cpp:1185-1189).
+    state = 12345
+
+    def ids(n):
+        nonlocal state
+        out = []
+        for _ in range(n):
+            state = (1664525 * state + 1013904223) & 0xFFFFFFFF
+            out.append((state >> 8) % vocab)
+        return out
+
+    def timed(fn):
+        torch.cuda.synchronize()
+        t = time.perf_counter()
+        fn()
+        torch.cuda.synchronize()
+        return time.perf_counter() - t
+
+    prompt = ids(p)
+    pp, tg = [], []
+    for rep in range(reps + 1):                       # the first repeat is the untimed warm-up
+        dt = timed(lambda: engine.step([StepEntry("p", prompt, [p - 1])]))
+        engine.end("p")
+        if rep:
+            pp.append(p / dt)
+        hist = ids(depth)
+        for s in range(seqs):
+            engine.step([StepEntry(s, hist, [])])
+        toks = ids(seqs)
+
+        def decode():
+            for _ in range(g):
+                engine.step([StepEntry(s, [toks[s]], [0]) for s in range(seqs)])
+        dt = timed(decode)
+        for s in range(seqs):
+            engine.end(s)
+        if rep:
+            tg.append(g * seqs / dt)
+
+    def stat(v):
+        m = sum(v) / len(v)
+        return m, (sum((x - m) ** 2 for x in v) / len(v)) ** 0.5
+    print("pp%d: %.2f +- %.2f tok/s" % ((p,) + stat(pp)))
+    print("tg%d x%d @%d: %.2f +- %.2f tok/s" % ((g, seqs, depth) + stat(tg)))
+    return 0
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    try:
+        if not argv or argv[0] in ("-h", "--help", "help"):
+            print(USAGE)
+            return 0
+        cmd, rest = argv[0], argv[1:]
+        if cmd == "generate":
+            return cmd_generate(rest)
+        if cmd == "bench":
+            return cmd_bench(rest)
+        raise UsageError(f"unknown command: {cmd}")
+    except UsageError as e:
+        print(f"llmx: {e}\n{USAGE}", file=sys.stderr)
+        return 2
+
+
+if __name__ == "__main__":
+    sys.exit(main())

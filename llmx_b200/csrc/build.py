@@ -43,7 +43,6 @@ LIBRARIES: Dict[str, List[str]] = {
     "sampling": ["sampling.cu"],
 }
 
-_HEADERS = ["common.cuh"]
 _lock = threading.Lock()
 _loaded: Dict[str, ctypes.CDLL] = {}
 
@@ -60,7 +59,19 @@ def _nvcc() -> str:
                      "the kernels cannot be built and there is no other path")
 
 
+_build_dir_cache: Optional[str] = None
+_dir_lock = threading.Lock()
+
+
 def _build_dir() -> str:
+    global _build_dir_cache
+    with _dir_lock:
+        if _build_dir_cache is None:
+            _build_dir_cache = _find_build_dir()
+        return _build_dir_cache
+
+
+def _find_build_dir() -> str:
     for cand in (os.environ.get("LLMX_BUILD_DIR"), os.path.join(_HERE, "_build")):
         if not cand:
             continue
@@ -78,13 +89,28 @@ def _build_dir() -> str:
     return d
 
 
+def _includes(path: str, seen: set) -> None:
+    """The local headers `path` includes, recursively."""
+    with open(path, "r", encoding="utf-8") as fh:
+        for line in fh:
+            line = line.strip()
+            if line.startswith("#include \""):
+                inc = os.path.join(_HERE, line.split('"')[1])
+                if inc not in seen and os.path.exists(inc):
+                    seen.add(inc)
+                    _includes(inc, seen)
+
+
 def _digest(name: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS).encode())
-    headers = sorted(f for f in os.listdir(_HERE) if f.endswith((".cuh", ".h")))
-    for f in LIBRARIES[name] + headers:
-        with open(os.path.join(_HERE, f), "rb") as fh:
-            h.update(f.encode())
+    files = [os.path.join(_HERE, f) for f in LIBRARIES[name]]
+    headers: set = set()
+    for f in files:
+        _includes(f, headers)
+    for f in files + sorted(headers):
+        with open(f, "rb") as fh:
+            h.update(os.path.basename(f).encode())
             h.update(fh.read())
     return h.hexdigest()[:16]
 

@@ -68,6 +68,7 @@ class Engine:
                                   options.max_requests, kv_dtype=self.precision.act, device=self.device)
         model.prepare(min(self.max_positions, max(options.kv_tokens, 1)), self.device)
         self.steps_run = 0
+        self.last_h2d_bytes = 0
 
     # -- construction ------------------------------------------------------------
     @classmethod
@@ -181,6 +182,7 @@ class Engine:
                 sl[a:a + counts[r]] = parr[p // ps] * ps + p % ps
             # A released page (-1) is never addressed: the window keeps queries above it.
         dev = host.to(self.device, non_blocking=True)
+        self.last_h2d_bytes = host.numel() * 4
 
         def dsec(i):
             return dev[offsets[i]:offsets[i] + sizes[i]]

@@ -1,0 +1,151 @@
+"""Generation: the Python entry point.  `LLM(model_dir).generate(prompts, params)`.
+
+The loop is the reference's generate loop run for many requests at once
+(src/inference/generate.hpp:19-124 for one request; the server's rounds, docs/SERVER.md:143-227):
+plan a step, run it through `Engine.step`, draw a token for every entry that asked for logits,
+record it, finish and free what ended.  Token ids in, token ids out: the tokenizer is not part of
+this engine.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, Iterable, List, Optional, Sequence, Union
+
+import torch
+
+from ..sampling import RequestSampling, SamplingParams, sample
+from .engine import Engine, EngineOptions, StepEntry
+from .scheduler import PlannedEntry, Request, Scheduler
+
+
+@dataclass
+class GenerationOutput:
+    request_id: Hashable
+    prompt: List[int]
+    tokens: List[int]
+    finish_reason: str
+
+
+@dataclass
+class GenerationStats:
+    prompt_tokens: int = 0
+    generated_tokens: int = 0
+    steps: int = 0
+    prefill_seconds: float = 0.0     # wall time of steps that held prompt portions only
+    decode_seconds: float = 0.0      # wall time of all other steps
+    preemptions: int = 0
+
+
+class LLM:
+    """A loaded model ready to generate.
+
+    model:            a folder with config.json and safetensors files (or an `Engine`)
+    dtype:            "bfloat16" (the serving path) or "float32" (everything in true 32-bit)
+    kv_tokens:        tokens the cache pool is made for (default: the model's context, at most 1/3 of free memory)
+    ubatch:           the most tokens one step holds (the reference's --ubatch)
+    max_seqs:         the most requests that run at once
+    reserve:          "full" or "prompt" (see llmx_b200.engine.scheduler)
+    """
+
+    def __init__(self, model: Union[str, Engine], *, dtype: str = "bfloat16", kv_tokens: Optional[int] = None,
+                 page_size: int = 16, ubatch: int = 512, max_seqs: int = 16, reserve: str = "full",
+                 device: str = "cuda:0"):
+        if isinstance(model, Engine):
+            self.engine = model
+        else:
+            if kv_tokens is None:
+                kv_tokens = self._default_kv_tokens(model, dtype, page_size, device)
+            self.engine = Engine.from_dir(model, EngineOptions(dtype=dtype, kv_tokens=kv_tokens, page_size=page_size,
+                                                               max_requests=max_seqs, device=device))
+        self.ubatch, self.max_seqs, self.reserve = int(ubatch), int(max_seqs), reserve
+        self.stats = GenerationStats()
+        self._next_id = 0
+
+    @staticmethod
+    def _default_kv_tokens(model_dir: str, dtype: str, page_size: int, device: str) -> int:
+        from ..registry import config_from_dir
+        entry, config = config_from_dir(model_dir)
+        model = entry.build(config)
+        per_token = 0
+        width = 2 if dtype in ("bfloat16", "bf16") else 4
+        for spec in model.cache_entry_specs():
+            if hasattr(spec, "kv_heads"):
+                per_token += 2 * spec.kv_heads * spec.head_dim * width
+        free, _ = torch.cuda.mem_get_info(torch.device(device))
+        by_memory = (free // 3) // max(per_token, 1)
+        tokens = int(min(model.max_positions, by_memory))
+        return max(page_size, tokens // page_size * page_size)
+
+    def _scheduler(self) -> Scheduler:
+        cache = self.engine.cache
+        return Scheduler(pages_needed=cache.pages_needed, total_pages=cache.total_pages(),
+                         max_positions=self.engine.max_positions, max_batch_tokens=self.ubatch,
+                         max_requests=min(self.max_seqs, self.engine.options.max_requests), max_queue=1 << 30,
+                         reserve=self.reserve, page_size=cache.page_size, eos_ids=self.engine.model.eos_ids)
+
+    def generate(self, prompts: Sequence[Sequence[int]],
+                 params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
+                 on_token=None) -> List[GenerationOutput]:
+        """Generate a reply for every prompt (lists of token ids); returns them in the prompts' order.
+
+        `on_token(request_index, token)` (optional) is called as tokens are drawn.
+        """
+        if params is None:
+            params = SamplingParams()
+        plist = list(params) if not isinstance(params, SamplingParams) else [params] * len(prompts)
+        if len(plist) != len(prompts):
+            raise ValueError("one SamplingParams for all prompts, or one for each")
+        sched = self._scheduler()
+        eos = self.engine.model.eos_ids
+        requests: List[Request] = []
+        for prompt, p in zip(prompts, plist):
+            r = Request(("gen", self._next_id), [int(t) for t in prompt], p)
+            self._next_id += 1
+            r.sampling = RequestSampling(p, eos_id=eos[0] if eos else -1)
+            sched.add(r)
+            requests.append(r)
+        index = {r.request_id: i for i, r in enumerate(requests)}
+        stats = self.stats
+        stats.prompt_tokens += sum(len(r.prompt) for r in requests)
+        while not sched.idle:
+            entries = sched.plan()
+            for rid in sched.take_releases():
+                self.engine.end(rid)
+            if not entries:
+                if sched.idle:
+                    break
+                raise RuntimeError("the scheduler planned an empty step while requests are waiting")
+            t0 = time.perf_counter()
+            step = [StepEntry(e.request.request_id, e.tokens, [len(e.tokens) - 1] if e.want_last else [])
+                    for e in entries]
+            logits = self.engine.step(step)
+            sampled: Dict[Hashable, int] = {}
+            wanting = [e for e in entries if e.want_last]
+            if wanting:
+                ids = sample(logits, [e.request.sampling for e in wanting])
+                for e, t in zip(wanting, ids):
+                    sampled[e.request.request_id] = t
+            else:
+                torch.cuda.current_stream().synchronize()
+            dt = time.perf_counter() - t0
+            if all(not e.request.decoding and len(e.tokens) > 1 for e in entries):
+                stats.prefill_seconds += dt
+            else:
+                stats.decode_seconds += dt
+            stats.steps += 1
+            before = {e.request.request_id: len(e.request.output) for e in wanting}
+            sched.complete(entries, sampled)
+            for e in wanting:
+                r = e.request
+                if len(r.output) > before[r.request_id]:
+                    r.sampling.saw(r.output[-1])
+                    stats.generated_tokens += 1
+                    if on_token:
+                        on_token(index[r.request_id], r.output[-1])
+            for rid in sched.take_releases():
+                self.engine.end(rid)
+        stats.preemptions += sched.preemptions
+        from .. import ops_tc
+        ops_tc.check_errors()
+        return [GenerationOutput(r.request_id, r.prompt, list(r.output), r.finish_reason or "unknown") for r in requests]

@@ -55,7 +55,17 @@ _ERRORS = {10001: "bad argument", 10002: "shape or type not supported by this ke
            10003: "TMA descriptor could not be encoded", 10004: "size beyond the stated maximum"}
 
 
-def _check(status: int, what: str) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this package launched so far (each call of an exported function counts its launches)."""
+    return _launches
+
+
+def _check(status: int, what: str, launches: int = 1) -> None:
+    global _launches
+    _launches += launches
     if status != 0:
         why = _ERRORS.get(status, f"CUDA error {status}")
         raise KernelError(f"{what}: {why}")

@@ -1,0 +1,28 @@
+"""Tiny configurations of the architecture for the tests.
+
+A and B differ in every size and option: layers, widths, head counts and group
+ratio, head width, vocabulary, rope base, eps, tying, context, page size, and B
+has YaRN rope scaling (a frequency blend and an attention factor).  C has widths
+the tensor-core path cannot take (an input width that is no multiple of 8), a
+head width of 48 and an odd vocabulary.
+"""
+TINY_A = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=64, intermediate_size=128, num_attention_heads=4, num_key_value_heads=2,
+    head_dim=16, vocab_size=256, rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=True,
+    max_position_embeddings=512, eos_token_id=255)
+
+TINY_B = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=3, hidden_size=96, intermediate_size=160, num_attention_heads=6, num_key_value_heads=3,
+    head_dim=32, vocab_size=384, rope_theta=1000000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
+    max_position_embeddings=1024,
+    rope_scaling=dict(rope_type="yarn", factor=2.0, original_max_position_embeddings=512, beta_fast=32.0, beta_slow=1.0))
+
+TINY_C = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=100, intermediate_size=172, num_attention_heads=3, num_key_value_heads=1,
+    head_dim=48, vocab_size=257, rope_theta=50000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+    max_position_embeddings=512)
+
+CONFIGS = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16)}   # config, seed, page size

@@ -1,0 +1,102 @@
+"""Configuration: every key read, defaults, and each refusal by message; the registry."""
+import json
+
+import pytest
+
+from configs import TINY_A, TINY_B
+from llmx_b200.config import ConfigError, Qwen3Config
+from llmx_b200.registry import architecture_of, config_from_dir, register_architecture, unregister_architecture
+
+
+def test_reads_every_size_from_config():
+    c = Qwen3Config.from_dict(TINY_B)
+    assert (c.num_hidden_layers, c.hidden_size, c.intermediate_size) == (3, 96, 160)
+    assert (c.num_attention_heads, c.num_key_value_heads, c.head_dim) == (6, 3, 32)
+    assert c.q_width == 192 and c.kv_width == 96 and c.vocab_size == 384
+    assert c.rope_theta == 1e6 and c.rms_norm_eps == 1e-5 and c.tie_word_embeddings is False
+    assert c.rope_scaling.factor == 2.0 and c.rope_scaling.original_max_position_embeddings == 512
+    assert abs(c.rope_scaling.attention_factor - 1.0693147) < 1e-6
+
+
+def test_defaults():
+    raw = dict(num_hidden_layers=1, hidden_size=64, intermediate_size=8, num_attention_heads=4, vocab_size=10)
+    c = Qwen3Config.from_dict(raw)
+    assert c.num_key_value_heads == 4 and c.head_dim == 16
+    assert c.max_position_embeddings == 4096 and c.rope_theta == 10000.0 and c.rms_norm_eps == 1e-6
+    assert c.rope_scaling is None and c.eos_ids == ()
+    assert Qwen3Config.from_dict(dict(raw, eos_token_id=[3, 4])).eos_ids == (3, 4)
+
+
+def test_round_trip_through_to_dict():
+    for raw in (TINY_A, TINY_B):
+        c = Qwen3Config.from_dict(raw)
+        assert Qwen3Config.from_dict(json.loads(json.dumps(c.to_dict()))) == c
+
+
+@pytest.mark.parametrize("change,message", [
+    (dict(bogus_key=1), "unknown config.json key"),
+    (dict(num_hidden_layers=0), "num_hidden_layers must be an integer >= 1"),
+    (dict(hidden_size=64.0), "hidden_size must be an integer"),
+    (dict(num_attention_heads=True), "num_attention_heads must be an integer"),
+    (dict(num_key_value_heads=3), "divisible by KV head count"),
+    (dict(head_dim=15), "head_dim must be even"),
+    (dict(attention_bias=True), "attention_bias must be one of"),
+    (dict(hidden_act="gelu"), "hidden_act must be one of"),
+    (dict(use_sliding_window=True), "use_sliding_window must be one of"),
+    (dict(layer_types=["full_attention", "sliding_attention"]), "every entry of layer_types"),
+    (dict(torch_dtype="int8"), "torch_dtype must be one of"),
+    (dict(rope_theta="big"), "rope_theta must be a finite number"),
+    (dict(rope_scaling={"factor": 2.0}), "gives no rope_type"),
+    (dict(rope_scaling={"rope_type": "linear", "factor": 2.0}), "is not supported"),
+    (dict(rope_scaling={"rope_type": "yarn"}), "gives no factor"),
+    (dict(rope_scaling={"rope_type": "yarn", "factor": 1.0}), "factor must be above 1"),
+    (dict(rope_scaling={"rope_type": "yarn", "factor": 2.0, "mscale": 1.0}), "mscale is not supported"),
+    (dict(rope_scaling={"rope_type": "yarn", "factor": 2.0, "beta_fast": 1.0, "beta_slow": 2.0}), "beta_fast must be above"),
+    (dict(architectures=["LlamaForCausalLM"]), "architectures"),
+    (dict(tie_word_embeddings="yes"), "tie_word_embeddings must be true or false"),
+])
+def test_refusals(change, message):
+    raw = dict(TINY_A)
+    raw.update(change)
+    with pytest.raises(ConfigError) as e:
+        Qwen3Config.from_dict(raw)
+    assert message in str(e.value)
+
+
+def test_missing_keys_are_listed():
+    with pytest.raises(ConfigError) as e:
+        Qwen3Config.from_dict(dict(hidden_size=64))
+    assert "num_hidden_layers" in str(e.value) and "vocab_size" in str(e.value)
+
+
+def test_head_dim_must_divide_when_absent():
+    raw = {k: v for k, v in TINY_A.items() if k != "head_dim"}
+    raw["hidden_size"] = 66
+    with pytest.raises(ConfigError):
+        Qwen3Config.from_dict(raw)
+
+
+def test_registry_by_class_name_and_model_type(tmp_path):
+    assert architecture_of({"architectures": ["Qwen3ForCausalLM"]}).config_cls is Qwen3Config
+    assert architecture_of({"model_type": "qwen3"}).config_cls is Qwen3Config
+    with pytest.raises(ConfigError) as e:
+        architecture_of({"architectures": ["GPT2LMHeadModel"], "model_type": "gpt2"})
+    assert "GPT2LMHeadModel" in str(e.value) and "qwen3" in str(e.value)
+    (tmp_path / "config.json").write_text(json.dumps(TINY_A))
+    entry, cfg = config_from_dir(str(tmp_path))
+    assert entry.name == "Qwen3ForCausalLM" and cfg.hidden_size == 64
+    model = entry.build(cfg)
+    assert len(model.blocks) == 2 and model.vocab_size == 256
+    with pytest.raises(ConfigError):
+        config_from_dir(str(tmp_path / "nothing"))
+
+
+def test_registering_another_architecture():
+    calls = []
+    register_architecture(["ToyForCausalLM", "toy"], Qwen3Config, lambda c: calls.append(c) or "model")
+    try:
+        assert architecture_of({"model_type": "toy"}).build("cfg") == "model" and calls == ["cfg"]
+        with pytest.raises(ValueError):
+            register_architecture(["toy"], Qwen3Config, lambda c: None)
+    finally:
+        unregister_architecture(["ToyForCausalLM", "toy"])

@@ -1,0 +1,177 @@
+"""The engine against the plain implementation, under every way of cutting and batching.
+
+Each test replays the same requests through `Engine.step` in a different way and compares every
+position's logits with `tests/plain_qwen3.py` (whole sequences, no cache).  float32 is held to
+1e-4 of the logit scale; bfloat16 is compared with the plain implementation rounding what the
+bfloat16 path rounds (inputs of products, cache) and held to BF16_TOL of the logit scale.
+"""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import helpers
+from configs import CONFIGS
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"float32": 1e-4, "bfloat16": 2e-2}
+LENGTHS = [70, 1, 9, 40, 133, 33, 5, 96]
+
+
+def _requests(name):
+    vocab = CONFIGS[name][0]["vocab_size"]
+    return {f"r{i}": helpers.random_ids(vocab, n, seed=100 * i + n) for i, n in enumerate(LENGTHS)}
+
+
+def _engine(model_dirs, name, dtype, kv_tokens):
+    from llmx_b200.engine import Engine, EngineOptions
+    d16, d32, page = model_dirs[name]
+    folder = d32 if dtype == "float32" else d16
+    return folder, Engine.from_dir(folder, EngineOptions(dtype=dtype, kv_tokens=kv_tokens, page_size=page,
+                                                         max_requests=8))
+
+
+def _check(engine, folder, steps, requests, dtype):
+    from llmx_b200 import ops_tc
+    got = helpers.run_trace(engine, steps)
+    ops_tc.check_errors()
+    engine.cache.check()
+    assert engine.cache.used_pages() == [0] * len(engine.cache.groups)
+    wanted = sum(len(e["want"]) for s in steps for e in s["entries"])
+    assert len(got) == wanted == sum(len(v) for v in requests.values())
+    worst, scale, where = helpers.compare(got, requests, folder, dtype == "bfloat16")
+    assert worst <= TOL[dtype] * scale, f"largest difference {worst:.3e} at {where} (logit scale {scale:.3f})"
+    return worst, scale
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+class TestCuttings:
+    def test_whole(self, model_dirs, name, dtype):
+        requests = _requests(name)
+        steps = helpers.trace_whole(requests)
+        folder, engine = _engine(model_dirs, name, dtype, helpers.tokens_needed(steps))
+        _check(engine, folder, steps, requests, dtype)
+
+    def test_last_32_one_by_one(self, model_dirs, name, dtype):
+        requests = _requests(name)
+        steps = helpers.trace_tail_decoded(requests, 32)
+        folder, engine = _engine(model_dirs, name, dtype, helpers.tokens_needed(steps))
+        _check(engine, folder, steps, requests, dtype)
+
+    def test_portions_of_changing_size(self, model_dirs, name, dtype):
+        requests = _requests(name)
+        steps = helpers.trace_portions(requests)
+        assert min(len(e["tokens"]) for s in steps for e in s["entries"] if len(e["tokens"]) > 1) == 2
+        folder, engine = _engine(model_dirs, name, dtype, helpers.tokens_needed(steps))
+        _check(engine, folder, steps, requests, dtype)
+
+    def test_mixed_with_pages_used_again(self, model_dirs, name, dtype):
+        requests = _requests(name)
+        steps = helpers.trace_mixed(requests)
+        assert max(len(s["entries"]) for s in steps) == 4
+        need = helpers.tokens_needed(steps)
+        assert need < sum(-(-len(v) // 64) * 64 for v in requests.values())   # the pool cannot hold them all at once
+        folder, engine = _engine(model_dirs, name, dtype, need)
+        seen = set()
+        reused = False
+        from llmx_b200.engine import StepEntry
+        # Watch the block tables as the trace runs: a page id must come back after it was given up.
+        got = {}
+        at = {}
+        for s in steps:
+            logits = engine.step([StepEntry(e["id"], e["tokens"], e["want"]) for e in s["entries"]])
+            rows = logits.float().cpu().numpy()
+            k = 0
+            for e in s["entries"]:
+                base = at.get(e["id"], 0)
+                for w in e["want"]:
+                    got[(e["id"], base + w)] = rows[k]
+                    k += 1
+                at[e["id"]] = base + len(e["tokens"])
+            held = {p for rc in engine.cache.live.values() for p in rc.tables[0].pages}
+            for rid in s["end"]:
+                gone = set(engine.cache.live[rid].tables[0].pages)
+                engine.end(rid)
+                seen |= gone
+                held -= gone
+            reused = reused or bool(seen & held)
+            engine.cache.check()
+        assert reused, "no page was used again; the pool was not tight enough to test reuse"
+        worst, scale, where = helpers.compare(got, requests, folder, dtype == "bfloat16")
+        assert worst <= TOL[dtype] * scale, f"largest difference {worst:.3e} at {where} (logit scale {scale:.3f})"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(model_dirs, dtype):
+    """A short prompt, then 300 tokens one by one across many pages."""
+    name = "B"
+    vocab = CONFIGS[name][0]["vocab_size"]
+    requests = {"long": helpers.random_ids(vocab, 320, seed=7)}
+    steps = helpers.trace_tail_decoded(requests, tail=300)
+    folder, engine = _engine(model_dirs, name, dtype, 320)
+    _check(engine, folder, steps, requests, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_first_tokens_of_a_sequence(model_dirs, name, dtype):
+    """Positions 0, 1, 2: a single key, the first page's first slots, decoded one by one from nothing."""
+    vocab = CONFIGS[name][0]["vocab_size"]
+    requests = {"s": helpers.random_ids(vocab, 3, seed=3), "t": helpers.random_ids(vocab, 1, seed=4)}
+    steps = helpers.trace_tail_decoded(requests, tail=3)
+    folder, engine = _engine(model_dirs, name, dtype, 128)
+    _check(engine, folder, steps, requests, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(model_dirs, tmp_path, dtype):
+    """bin/trace_run as a user runs it: JSON steps on standard input, .f32 files out, `done` lines."""
+    name = "B"
+    d16, d32, page = model_dirs[name]
+    folder = d32 if dtype == "float32" else d16
+    vocab = CONFIGS[name][0]["vocab_size"]
+    requests = {f"q{i}": helpers.random_ids(vocab, n, seed=50 + i) for i, n in enumerate([45, 3, 80, 20, 64])}
+    steps = helpers.trace_mixed(requests, tail=5)
+    need = helpers.tokens_needed(steps)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "out"
+    text = "".join(json.dumps(s) + "\n" for s in steps)
+    proc = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
+                           "--out", str(out), "--max-tokens", str(need)], input=text, capture_output=True, text=True,
+                          timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    got = helpers.read_trace_output(steps, str(out), vocab)
+    worst, scale, where = helpers.compare(got, requests, folder, dtype == "bfloat16")
+    assert worst <= TOL[dtype] * scale, f"largest difference {worst:.3e} at {where} (logit scale {scale:.3f})"
+
+
+def test_step_refusals(model_dirs):
+    from llmx_b200.cache import CacheExhausted
+    from llmx_b200.engine import StepEntry, StepError
+    folder, engine = _engine(model_dirs, "A", "float32", 64)
+    with pytest.raises(StepError):
+        engine.step([])
+    with pytest.raises(StepError):
+        engine.step([StepEntry("a", [], [])])
+    with pytest.raises(StepError):
+        engine.step([StepEntry("a", [1], [0]), StepEntry("a", [2], [0])])
+    with pytest.raises(StepError):
+        engine.step([StepEntry("a", [256], [0])])
+    with pytest.raises(StepError):
+        engine.step([StepEntry("a", [1, 2], [2])])
+    # Pages run out: nothing is kept, and the same request fits once room is made.
+    engine.step([StepEntry("a", list(range(48)), [47])])
+    with pytest.raises(CacheExhausted):
+        engine.step([StepEntry("b", list(range(40)), [0])])
+    engine.cache.check()
+    assert "b" not in engine.cache.live and engine.length("a") == 48
+    engine.end("a")
+    assert engine.step([StepEntry("b", list(range(40)), [0])]).shape == (1, 256)
+    engine.end("b")
+    assert engine.cache.used_pages() == [0]
