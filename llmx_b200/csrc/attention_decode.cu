@@ -1,0 +1,368 @@
+// Split-KV attention over block tables for requests that bring one or a few rows (decoding).
+//
+// A block serves one (request, kv head, key range): the request's `n` new rows times the
+// `ratio = heads / kv_heads` query heads of the group form at most 16 query rows that share
+// every key and value they read, so each page is fetched once for the whole group.
+//
+//   producer warp    walks the request's block table and fetches its pages with TMA
+//                    (boxes of [16 slots, 64 columns], 128-byte swizzle), four pages a stage,
+//                    three stages in flight
+//   4 consumer warps each takes one page of a stage: S = Q K^T (mma.sync m16n8k16, bfloat16 in,
+//                    float32 out), masks (causal, window, tail of the last page), online softmax
+//                    in float32 (base 2), O += P V
+//   at the end       the four warps' (m, l, O) are merged through shared memory; with one key
+//                    range the result is written, else a partial (m, l, O) goes to the
+//                    workspace and `attn_merge_kernel` combines the ranges.
+//
+// This kernel is bound by the cache bytes it reads; the matrix work on 16-row tiles is a
+// small fraction of what the SM can do, which is why it uses the warp-level instruction rather
+// than tcgen05 (whose 64/128-row tiles would be 75-97 % padding here).
+// Reference counterpart: llmx_attention_vec and its merge (src/backends/gpu/kernels/f32.gpu:1640-1715, :1863).
+#include "attn_common.cuh"
+#include <math.h>
+
+namespace {
+
+constexpr int PAGE = 16;
+constexpr int PAGES_PER_STAGE = 4;
+constexpr int STAGES = 3;
+constexpr int CONSUMERS = 4;
+constexpr int THREADS = (CONSUMERS + 1) * 32;
+constexpr int MAX_ROWS = 16;
+enum : int { ERR_DEC_PRODUCER = 201, ERR_DEC_CONSUMER = 202 };
+
+template <int D>
+struct Cfg {
+    static constexpr int BOXES = D / attn::BOX_COLS;
+    static constexpr int BOX_BYTES = PAGE * 128;
+    static constexpr int PLANE_BYTES = BOXES * BOX_BYTES;       // one page's keys (or values) of one head
+    static constexpr int PAGE_BYTES = 2 * PLANE_BYTES;
+    static constexpr int STAGE_BYTES = PAGES_PER_STAGE * PAGE_BYTES;
+    static constexpr int MERGE_BYTES = CONSUMERS * MAX_ROWS * (D + 2) * 4;
+    static constexpr int TILE_BYTES = STAGES * STAGE_BYTES > MERGE_BYTES ? STAGES * STAGE_BYTES : MERGE_BYTES;
+    static constexpr int SMEM_BYTES = TILE_BYTES + 1024 + 128;
+};
+
+template <int D>
+__global__ void __launch_bounds__(THREADS)
+attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfloat16* __restrict__ q,
+                   __nv_bfloat16* __restrict__ out, float* __restrict__ partial, const int* __restrict__ req_list,
+                   const int* __restrict__ row_start, const int* __restrict__ row_count,
+                   const int* __restrict__ history, const int* __restrict__ block_tables, int table_stride, int heads,
+                   int kv_heads, int window, float scale_log2, int splits, const int* __restrict__ chunk_ptr,
+                   int chunk_keys, int* error_word) {
+    using cfg = Cfg<D>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full_bar = (uint64_t*)(tiles + cfg::TILE_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    volatile int* abort_flag = (volatile int*)(empty_bar + STAGES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int split = blockIdx.x, g = blockIdx.y, r = req_list[blockIdx.z];
+    const int ratio = heads / kv_heads;
+    const int n_q = row_count[r], q0 = row_start[r], hist = history[r];
+    const int M = n_q * ratio;
+    const int len = hist + n_q;
+    const int chunk = chunk_ptr ? *chunk_ptr : chunk_keys;
+    int kv_begin = split * chunk;
+    const int kv_end = min(len, kv_begin + chunk);
+    if (window > 0) {
+        const int lowest = max(0, hist - window + 1);          // the first row's lowest key
+        kv_begin = max(kv_begin, (lowest / PAGE) * PAGE);
+    }
+    const int n_pages = kv_end > kv_begin ? (kv_end - kv_begin + PAGE - 1) / PAGE : 0;
+    const int iters = (n_pages + PAGES_PER_STAGE - 1) / PAGES_PER_STAGE;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            tc::mbar_init(&full_bar[s], 1);
+            tc::mbar_init(&empty_bar[s], CONSUMERS);
+        }
+        *abort_flag = 0;
+        tc::fence_barrier_init();
+    }
+    __syncthreads();
+
+    // Per-thread accumulators of the consumer warps (rows r0 = lane / 4 and r0 + 8 of the 16-row tile).
+    float o[D / 8][4];
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int t = 0; t < D / 8; ++t)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[t][e] = 0.0f;
+
+    if (warp == CONSUMERS) {
+        if (n_pages > 0 && tc::elect_one()) {
+            tc::tma_prefetch_desc(&cache_map);
+            const int* table = block_tables + (size_t)r * table_stride + kv_begin / PAGE;
+            for (int it = 0; it < iters; ++it) {
+                const int stage = it % STAGES;
+                const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
+                if (!tc::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, error_word, ERR_DEC_PRODUCER)) break;
+                const int here = min(PAGES_PER_STAGE, n_pages - it * PAGES_PER_STAGE);
+                tc::mbar_expect_tx(&full_bar[stage], (uint32_t)(here * cfg::PAGE_BYTES));
+                for (int p = 0; p < here; ++p) {
+                    const int page = table[it * PAGES_PER_STAGE + p];
+                    uint8_t* dst = tiles + stage * cfg::STAGE_BYTES + p * cfg::PAGE_BYTES;
+                    const int key_row = ((page * 2 + 0) * kv_heads + g) * PAGE;
+                    const int value_row = ((page * 2 + 1) * kv_heads + g) * PAGE;
+#pragma unroll
+                    for (int b = 0; b < cfg::BOXES; ++b) {
+                        tc::tma_load_2d(dst + b * cfg::BOX_BYTES, &cache_map, b * attn::BOX_COLS, key_row, &full_bar[stage]);
+                        tc::tma_load_2d(dst + cfg::PLANE_BYTES + b * cfg::BOX_BYTES, &cache_map, b * attn::BOX_COLS,
+                                        value_row, &full_bar[stage]);
+                    }
+                }
+            }
+        }
+    } else {
+        // ---- query fragments: row i of the tile is (new row i / ratio, head g * ratio + i % ratio)
+        uint32_t qa[D / 16][4];
+        const int r0 = lane >> 2, r1 = r0 + 8;
+        int pos[2], lo[2];
+        bool valid[2];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int row = half ? r1 : r0;
+            valid[half] = row < M;
+            const int ti = row / ratio;
+            pos[half] = hist + ti;
+            lo[half] = window > 0 ? max(0, pos[half] - window + 1) : 0;
+            const __nv_bfloat16* src = q + ((size_t)(q0 + ti) * heads + g * ratio + row % ratio) * D;
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const int d = kk * 16 + (lane & 3) * 2;
+                qa[kk][half] = valid[half] ? *reinterpret_cast<const uint32_t*>(src + d) : 0u;
+                qa[kk][half + 2] = valid[half] ? *reinterpret_cast<const uint32_t*>(src + d + 8) : 0u;
+            }
+        }
+        for (int it = 0; it < iters; ++it) {
+            const int stage = it % STAGES;
+            const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
+            if (!tc::mbar_wait(&full_bar[stage], phase, abort_flag, error_word, ERR_DEC_CONSUMER)) break;
+            const int page_index = it * PAGES_PER_STAGE + warp;
+            if (page_index < n_pages) {
+                const int key0 = kv_begin + page_index * PAGE;
+                const uint32_t kbase = tc::smem_u32(tiles + stage * cfg::STAGE_BYTES + warp * cfg::PAGE_BYTES);
+                const uint32_t vbase = kbase + cfg::PLANE_BYTES;
+                if (key0 + PAGE > len) {
+                    // Slots past the request's last key hold whatever an earlier owner left: zero those values
+                    // so that a stale non-finite number cannot reach the sum through a zero weight.
+                    const int first_bad = len - key0;
+                    for (int i = lane; i < (PAGE - first_bad) * cfg::BOXES * 8; i += 32) {
+                        const int row = first_bad + i / (cfg::BOXES * 8), c = i % (cfg::BOXES * 8);
+                        const uint32_t addr = vbase + (c >> 3) * cfg::BOX_BYTES + attn::swz(row, c & 7);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
+                    }
+                    __syncwarp();
+                }
+                // ---- S = Q K^T for the page's 16 keys
+                float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const int dchunk = 2 * kk + ((lane >> 3) & 1);
+                    const int key = ((lane >> 4) << 3) + (lane & 7);
+                    uint32_t b0, b1, b2, b3;
+                    attn::ldmatrix_x4(kbase + (dchunk >> 3) * cfg::BOX_BYTES + attn::swz(key, dchunk & 7), b0, b1, b2, b3);
+                    attn::mma_16816(s[0], qa[kk], b0, b1);
+                    attn::mma_16816(s[1], qa[kk], b2, b3);
+                }
+                // ---- mask, online softmax (base 2)
+                float rowmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int half = e >> 1;
+                        const int key = key0 + 8 * j + (lane & 3) * 2 + (e & 1);
+                        const bool ok = valid[half] && key >= lo[half] && key <= pos[half];
+                        s[j][e] = ok ? s[j][e] * scale_log2 : -INFINITY;
+                        rowmax[half] = fmaxf(rowmax[half], s[j][e]);
+                    }
+                float alpha[2], base[2];
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    rowmax[half] = fmaxf(rowmax[half], __shfl_xor_sync(0xffffffffu, rowmax[half], 1));
+                    rowmax[half] = fmaxf(rowmax[half], __shfl_xor_sync(0xffffffffu, rowmax[half], 2));
+                    const float m_new = fmaxf(m_run[half], rowmax[half]);
+                    alpha[half] = m_new == -INFINITY ? 1.0f : exp2f(m_run[half] - m_new);
+                    base[half] = m_new == -INFINITY ? 0.0f : m_new;
+                    m_run[half] = m_new;
+                }
+                float psum[2] = {0.0f, 0.0f};
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        s[j][e] = exp2f(s[j][e] - base[e >> 1]);
+                        psum[e >> 1] += s[j][e];
+                    }
+                l_run[0] = l_run[0] * alpha[0] + psum[0];
+                l_run[1] = l_run[1] * alpha[1] + psum[1];
+                uint32_t pa[4];
+                pa[0] = attn::pack_bf16(s[0][0], s[0][1]);
+                pa[1] = attn::pack_bf16(s[0][2], s[0][3]);
+                pa[2] = attn::pack_bf16(s[1][0], s[1][1]);
+                pa[3] = attn::pack_bf16(s[1][2], s[1][3]);
+                // ---- O = O * alpha + P V
+#pragma unroll
+                for (int t = 0; t < D / 8; t += 2) {
+                    o[t][0] *= alpha[0]; o[t][1] *= alpha[0]; o[t][2] *= alpha[1]; o[t][3] *= alpha[1];
+                    o[t + 1][0] *= alpha[0]; o[t + 1][1] *= alpha[0]; o[t + 1][2] *= alpha[1]; o[t + 1][3] *= alpha[1];
+                    const int key = (((lane >> 3) & 1) << 3) + (lane & 7);
+                    const int dchunk = t + (lane >> 4);
+                    uint32_t b0, b1, b2, b3;
+                    attn::ldmatrix_x4_trans(vbase + (dchunk >> 3) * cfg::BOX_BYTES + attn::swz(key, dchunk & 7), b0, b1, b2, b3);
+                    attn::mma_16816(o[t], pa, b0, b1);
+                    attn::mma_16816(o[t + 1], pa, b2, b3);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&empty_bar[stage]);
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            l_run[half] += __shfl_xor_sync(0xffffffffu, l_run[half], 1);
+            l_run[half] += __shfl_xor_sync(0xffffffffu, l_run[half], 2);
+        }
+    }
+    __syncthreads();   // every page has been consumed: the tile memory can hold the merge buffer
+
+    float* merge = (float*)tiles;   // [CONSUMERS][MAX_ROWS][D + 2]
+    if (warp < CONSUMERS) {
+        const int r0 = lane >> 2;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int row = r0 + 8 * half;
+            if (row < M) {
+                float* mine = merge + ((size_t)warp * MAX_ROWS + row) * (D + 2);
+#pragma unroll
+                for (int t = 0; t < D / 8; ++t) {
+                    const int d = 8 * t + (lane & 3) * 2;
+                    mine[d] = o[t][2 * half];
+                    mine[d + 1] = o[t][2 * half + 1];
+                }
+                if ((lane & 3) == 0) {
+                    mine[D] = m_run[half];
+                    mine[D + 1] = l_run[half];
+                }
+            }
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < M * D; idx += THREADS) {
+        const int row = idx / D, d = idx % D;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < CONSUMERS; ++w) mm = fmaxf(mm, merge[((size_t)w * MAX_ROWS + row) * (D + 2) + D]);
+        float acc = 0.0f, l = 0.0f;
+#pragma unroll
+        for (int w = 0; w < CONSUMERS; ++w) {
+            const float* src = merge + ((size_t)w * MAX_ROWS + row) * (D + 2);
+            const float f = src[D] == -INFINITY ? 0.0f : exp2f(src[D] - mm);
+            acc += src[d] * f;
+            l += src[D + 1] * f;
+        }
+        const int ti = row / ratio, h = g * ratio + row % ratio;
+        const size_t out_row = (size_t)(q0 + ti) * heads + h;
+        if (splits == 1) {
+            out[out_row * D + d] = __float2bfloat16_rn(acc / l);
+        } else {
+            float* dst = partial + (out_row * splits + split) * (D + 2);
+            dst[d] = acc;
+            if (d == 0) {
+                dst[D] = mm;
+                dst[D + 1] = l;
+            }
+        }
+    }
+}
+
+// out[row, head, :] = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m) over the key ranges.
+template <int D>
+__global__ void attn_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
+                                  const int* __restrict__ req_list, const int* __restrict__ row_start,
+                                  const int* __restrict__ row_count, int heads, int splits) {
+    const int r = req_list[blockIdx.z];
+    if ((int)blockIdx.y >= row_count[r]) return;
+    const size_t out_row = (size_t)(row_start[r] + blockIdx.y) * heads + blockIdx.x;
+    const float* src = partial + out_row * splits * (D + 2);
+    float mm = -INFINITY;
+    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, src[(size_t)s * (D + 2) + D]);
+    float l = 0.0f;
+    for (int s = 0; s < splits; ++s) {
+        const float ms = src[(size_t)s * (D + 2) + D];
+        l += ms == -INFINITY ? 0.0f : src[(size_t)s * (D + 2) + D + 1] * exp2f(ms - mm);
+    }
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = src[(size_t)s * (D + 2) + D];
+            if (ms != -INFINITY) acc += src[(size_t)s * (D + 2) + d] * exp2f(ms - mm);
+        }
+        out[out_row * D + d] = __float2bfloat16_rn(acc / l);
+    }
+}
+
+template <int D>
+int launch(const CUtensorMap& map, const void* q, void* out, float* partial, const int* req_list, int n_req,
+           const int* row_start, const int* row_count, const int* history, const int* block_tables, int table_stride,
+           int heads, int kv_heads, int window, float scale, int splits, const int* chunk_ptr, int chunk_keys,
+           int max_rows, int* error_word, cudaStream_t stream) {
+    using cfg = Cfg<D>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES) !=
+            cudaSuccess)
+            return (int)cudaGetLastError();
+        configured = true;
+    }
+    dim3 grid(splits, kv_heads, n_req);
+    attn_decode_kernel<D><<<grid, THREADS, cfg::SMEM_BYTES, stream>>>(
+        map, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, partial, req_list, row_start, row_count, history,
+        block_tables, table_stride, heads, kv_heads, window, scale * attn::LOG2E, splits, chunk_ptr, chunk_keys,
+        error_word);
+    int e = launch_status();
+    if (e || splits == 1) return e;
+    dim3 mgrid(heads, max_rows, n_req);
+    attn_merge_kernel<D><<<mgrid, D < 128 ? D : 128, 0, stream>>>(partial, (__nv_bfloat16*)out, req_list, row_start,
+                                                               row_count, heads, splits);
+    return launch_status();
+}
+
+}  // namespace
+
+// The TMA descriptor of one layer's cache [pages, 2, kv_heads, page_size, head_dim] (bfloat16): 128 bytes at `out`.
+LLMX_EXPORT int llmx_attn_cache_map(void* out, const void* cache, long long pages, int kv_heads, int page_size,
+                                    int head_dim) {
+    if (head_dim % attn::BOX_COLS || page_size != PAGE || ((uintptr_t)cache & 15)) return LLMX_ERR_UNSUPPORTED;
+    return llmx_make_cache_map((CUtensorMap*)out, cache, (uint64_t)pages * 2 * kv_heads * page_size, (uint64_t)head_dim,
+                               (uint32_t)page_size);
+}
+
+// Attention for the requests req_list[0..n_req): each brings row_count[r] rows (at most 16 / (heads / kv_heads))
+// starting at row row_start[r] of q/out [rows, heads, head_dim]; history[r] keys precede them.
+// Key ranges: `splits` ranges of `chunk` keys (a multiple of 64; read from chunk_ptr on the device when given).
+// `partial` (float32, rows * heads * splits * (head_dim + 2)) is needed when splits > 1.
+LLMX_EXPORT int llmx_attn_decode(const void* cache_map, const void* q, void* out, float* partial, const int* req_list,
+                                 int n_req, const int* row_start, const int* row_count, const int* history,
+                                 const int* block_tables, int table_stride, int heads, int kv_heads, int head_dim,
+                                 int page_size, int window, float scale, int splits, const int* chunk_ptr,
+                                 int chunk_keys, int max_rows, int* error_word, cudaStream_t stream) {
+    if (n_req <= 0) return 0;
+    if (page_size != PAGE || heads % kv_heads || heads / kv_heads > MAX_ROWS || splits < 1 || n_req > 65535 ||
+        kv_heads > 65535 || (chunk_keys % 64) || max_rows < 1 || max_rows * (heads / kv_heads) > MAX_ROWS)
+        return LLMX_ERR_UNSUPPORTED;
+    if (splits > 1 && !partial) return LLMX_ERR_BAD_ARGUMENT;
+    const CUtensorMap& map = *(const CUtensorMap*)cache_map;
+    switch (head_dim) {
+        case 64: return launch<64>(map, q, out, partial, req_list, n_req, row_start, row_count, history, block_tables,
+                                   table_stride, heads, kv_heads, window, scale, splits, chunk_ptr, chunk_keys, max_rows,
+                                   error_word, stream);
+        case 128: return launch<128>(map, q, out, partial, req_list, n_req, row_start, row_count, history, block_tables,
+                                     table_stride, heads, kv_heads, window, scale, splits, chunk_ptr, chunk_keys,
+                                     max_rows, error_word, stream);
+        default: return LLMX_ERR_UNSUPPORTED;
+    }
+}

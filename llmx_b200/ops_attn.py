@@ -1,6 +1,120 @@
-"""Python face of the tiled bfloat16 attention kernels (csrc/attention_decode.cu, csrc/attention_prefill.cu)."""
+"""Python face of the tiled bfloat16 attention kernels (csrc/attention_decode.cu, csrc/attention_prefill.cu).
+
+Requests of a step are split by how many rows they bring: those whose rows times the head ratio
+fit a 16-row tile run the split-KV decode kernel, the others the tiled prefill kernel.  Both
+read the same pages; which kernel a request runs depends only on its own row count.
+"""
 from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .ops import KernelError, _check, _cuda, _fn, _need, _ptr, _stream, register_signature
+from .ops_tc import error_word
+
+_i, _p, _f, _ll = ctypes.c_int, ctypes.c_void_p, ctypes.c_float, ctypes.c_longlong
+register_signature("attention_decode", "llmx_attn_cache_map", [_p, _p, _ll, _i, _i, _i])
+register_signature("attention_decode", "llmx_attn_decode",
+                   [_p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p, _i, _i, _p, _p])
+register_signature("attention_prefill", "llmx_attn_prefill",
+                   [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p])
+
+PAGE = 16
+TARGET_BLOCKS = 148 * 4          # decode blocks wanted in flight: two per SM, two waves
+MIN_KEYS_PER_SPLIT = 256
 
 
 def supported(heads: int, kv_heads: int, head_dim: int, page_size: int) -> bool:
-    return False
+    return head_dim in (64, 128) and page_size == PAGE and heads % kv_heads == 0 and heads // kv_heads <= 16
+
+
+class CacheMap:
+    """The TMA descriptor of one cache entry's storage [pages, 2, kv_heads, 16, head_dim]."""
+
+    def __init__(self, cache: torch.Tensor):
+        self.cache = cache
+        self._raw = ctypes.create_string_buffer(128 + 64)
+        self.address = (ctypes.addressof(self._raw) + 63) & ~63
+        pages, _, kv_heads, page_size, head_dim = cache.shape
+        _check(_fn("attention_decode", "llmx_attn_cache_map")(ctypes.c_void_p(self.address), _ptr(cache), pages,
+                                                              kv_heads, page_size, head_dim), "attention cache map", 0)
+
+
+_maps: Dict[int, CacheMap] = {}
+
+
+def cache_map(cache: torch.Tensor) -> CacheMap:
+    m = _maps.get(cache.data_ptr())
+    if m is None or m.cache.shape != cache.shape:
+        m = CacheMap(cache)
+        _maps[cache.data_ptr()] = m
+    return m
+
+
+def decode_schedule(n_requests: int, kv_heads: int, max_context: int) -> Tuple[int, int]:
+    """(key ranges, keys per range) so that a decode launch has about TARGET_BLOCKS blocks."""
+    blocks = max(n_requests * kv_heads, 1)
+    splits = max(1, min(-(-TARGET_BLOCKS // blocks), -(-max_context // MIN_KEYS_PER_SPLIT)))
+    chunk = -(-(-(-max_context // 64)) // splits) * 64
+    splits = max(1, -(-max_context // chunk))
+    return splits, chunk
+
+
+def _request_lists(step, max_rows: int):
+    """Device lists of the requests that bring at most `max_rows` rows and of the others (cached on the step)."""
+    key = ("attn_lists", max_rows)
+    got = step.extras.get(key)
+    if got is None:
+        small = [r for r, n in enumerate(step.host_row_count) if n <= max_rows]
+        large = [r for r, n in enumerate(step.host_row_count) if n > max_rows]
+        host = torch.tensor(small + large + [0], dtype=torch.int32).pin_memory()
+        dev = host.to(step.token_ids.device, non_blocking=True)
+        ctx_small = max((step.host_history[r] + step.host_row_count[r] for r in small), default=0)
+        rows_large = max((step.host_row_count[r] for r in large), default=0)
+        rows_small = max((step.host_row_count[r] for r in small), default=0)
+        got = (dev[:len(small)], len(small), ctx_small, rows_small, dev[len(small):len(small) + len(large)],
+               len(large), rows_large)
+        step.extras[key] = got
+    return got
+
+
+def paged_attention_bf16(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, step, group, heads: int,
+                         kv_heads: int, head_dim: int, window: Optional[int], scale: float) -> None:
+    _cuda(q, cache, out)
+    _need(q.dtype is torch.bfloat16 and cache.dtype is torch.bfloat16 and out.dtype is torch.bfloat16,
+          "attention: bfloat16 queries, cache and output")
+    _need(q.shape == out.shape and q.shape[1] == heads * head_dim, "attention: q and out shapes do not fit")
+    ratio = heads // kv_heads
+    max_rows = 16 // ratio
+    cmap = cache_map(cache)
+    tables = group.block_tables
+    (small, n_small, ctx_small, rows_small, large, n_large, rows_large) = _request_lists(step, max_rows)
+    err = error_word(q.device)
+    win = int(window or 0)
+    if n_small:
+        sched = step.extras.get("decode_schedule")
+        if sched is None:
+            splits, chunk = decode_schedule(n_small, kv_heads, ctx_small)
+            chunk_ptr = None
+        else:                      # a recorded step: the grid is fixed, the keys per range come from the device
+            splits, chunk, chunk_ptr = sched
+        partial = None
+        if splits > 1:
+            key = ("attn_partial", splits, heads, head_dim)
+            partial = step.extras.get(key)
+            if partial is None:
+                partial = torch.empty((q.shape[0] * heads * splits * (head_dim + 2),), dtype=torch.float32,
+                                      device=q.device)
+                step.extras[key] = partial
+        _check(_fn("attention_decode", "llmx_attn_decode")(
+            ctypes.c_void_p(cmap.address), _ptr(q), _ptr(out), _ptr(partial), _ptr(small), n_small,
+            _ptr(step.row_start), _ptr(step.row_count), _ptr(step.history), _ptr(tables), tables.shape[1], heads,
+            kv_heads, head_dim, cache.shape[3], win, float(scale), splits, _ptr(chunk_ptr), chunk, max(rows_small, 1),
+            _ptr(err), _stream()), "attention_decode", 2 if splits > 1 else 1)
+    if n_large:
+        _check(_fn("attention_prefill", "llmx_attn_prefill")(
+            ctypes.c_void_p(cmap.address), _ptr(q), _ptr(out), _ptr(large), n_large, _ptr(step.row_start),
+            _ptr(step.row_count), _ptr(step.history), _ptr(tables), tables.shape[1], heads, kv_heads, head_dim,
+            cache.shape[3], win, float(scale), rows_large, _ptr(err), _stream()), "attention_prefill")

@@ -25,4 +25,12 @@ TINY_C = dict(
     head_dim=48, vocab_size=257, rope_theta=50000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
     max_position_embeddings=512)
 
-CONFIGS = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16)}   # config, seed, page size
+# D has the head width and page size the tiled bfloat16 attention kernels take, so the serving kernels
+# (tensor-core products, split-KV decode, tiled prefill) run under every cutting too.
+TINY_D = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=128, intermediate_size=200, num_attention_heads=6, num_key_value_heads=2,
+    head_dim=64, vocab_size=320, rope_theta=500000.0, rms_norm_eps=1e-6, tie_word_embeddings=True,
+    max_position_embeddings=2048)
+
+CONFIGS = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16), "D": (TINY_D, 3, 16)}   # config, seed, page size

@@ -49,7 +49,7 @@ def _check(engine, folder, steps, requests, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 class TestCuttings:
     def test_whole(self, model_dirs, name, dtype):
         requests = _requests(name)
@@ -106,10 +106,10 @@ class TestCuttings:
         assert worst <= TOL[dtype] * scale, f"largest difference {worst:.3e} at {where} (logit scale {scale:.3f})"
 
 
+@pytest.mark.parametrize("name", ["B", "D"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_long_decoding(model_dirs, dtype):
+def test_long_decoding(model_dirs, name, dtype):
     """A short prompt, then 300 tokens one by one across many pages."""
-    name = "B"
     vocab = CONFIGS[name][0]["vocab_size"]
     requests = {"long": helpers.random_ids(vocab, 320, seed=7)}
     steps = helpers.trace_tail_decoded(requests, tail=300)
@@ -118,7 +118,7 @@ def test_long_decoding(model_dirs, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
 def test_first_tokens_of_a_sequence(model_dirs, name, dtype):
     """Positions 0, 1, 2: a single key, the first page's first slots, decoded one by one from nothing."""
     vocab = CONFIGS[name][0]["vocab_size"]

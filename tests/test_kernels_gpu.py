@@ -1,0 +1,357 @@
+"""Each kernel alone against a plain float32 reference of the same operation, at sizes other than the
+engine's tiny models: ragged edges, widths that are no power of two, one row, many rows."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _bf16(t):
+    return t.to(torch.bfloat16)
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,width,vocab", [(1, 96, 50), (37, 100, 257), (300, 4096, 1000)])
+def test_embed(dtype, rows, width, vocab):
+    from llmx_b200 import ops
+    g = torch.Generator().manual_seed(1)
+    table = torch.randn(vocab, width, generator=g).to(dtype).to(DEV)
+    ids = torch.randint(0, vocab, (rows,), generator=g, dtype=torch.int32).to(DEV)
+    out = torch.empty(rows, width, dtype=torch.float32, device=DEV)
+    ops.embed(table, ids, out)
+    assert torch.equal(out, table.float()[ids.long()])
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,width,eps", [(1, 16, 1e-6), (33, 100, 1e-5), (7, 4096, 1e-6), (5, 5000, 1e-3)])
+def test_rmsnorm(out_dtype, rows, width, eps):
+    from llmx_b200 import ops
+    g = torch.Generator().manual_seed(2)
+    x = (torch.randn(rows, width, generator=g) * 3).to(DEV)
+    w = (1 + 0.1 * torch.randn(width, generator=g)).to(DEV)
+    out = torch.empty(rows, width, dtype=out_dtype, device=DEV)
+    ops.rmsnorm(x, w, eps, out)
+    ref = plain.rms_norm(x.cpu().numpy(), w.cpu().numpy(), eps)
+    if out_dtype is torch.bfloat16:
+        ref = plain.round_bf16(ref)
+        assert np.abs(out.float().cpu().numpy() - ref).max() <= np.abs(ref).max() * 2 ** -7
+    else:
+        assert np.abs(out.cpu().numpy() - ref).max() <= 1e-5 * np.abs(ref).max()
+    # Gathered rows: the head's pick of rows folded into the norm.
+    idx = torch.tensor([rows - 1, 0], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(2, width, dtype=out_dtype, device=DEV)
+    ops.rmsnorm(x, w, eps, out2, row_index=idx)
+    assert torch.equal(out2, out[idx.long()])
+
+
+@pytest.mark.parametrize("rows,width", [(1, 8), (19, 172), (64, 12288)])
+def test_swiglu(rows, width):
+    from llmx_b200 import ops
+    g = torch.Generator().manual_seed(3)
+    gu = (torch.randn(rows, 2 * width, generator=g) * 4).to(DEV)
+    out = torch.empty(rows, width, dtype=torch.float32, device=DEV)
+    ops.swiglu(gu, out)
+    a = gu.cpu().numpy()
+    ref = plain.silu(a[:, :width]) * a[:, width:]
+    assert np.abs(out.cpu().numpy() - ref).max() <= 1e-5 * max(1.0, np.abs(ref).max())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,rot,norm", [(4, 2, 16, 16, True), (6, 3, 32, 32, True), (3, 1, 48, 24, False),
+                                                              (32, 8, 128, 128, True), (2, 2, 256, 64, True)])
+def test_head_norm_rope_kv(dtype, heads, kv_heads, head_dim, rot, norm):
+    """Per-head norm, rotation (whole or partial width) and the write into scattered cache slots."""
+    from llmx_b200 import ops
+    rows, page, pages = 11, 8, 9
+    g = torch.Generator().manual_seed(4)
+    qkv = torch.randn(rows, (heads + 2 * kv_heads) * head_dim, generator=g).to(DEV)
+    qw = (1 + 0.1 * torch.randn(head_dim, generator=g)).to(DEV) if norm else None
+    kw = (1 + 0.1 * torch.randn(head_dim, generator=g)).to(DEV) if norm else None
+    positions = torch.randint(0, 40, (rows,), generator=g, dtype=torch.int32)
+    cos_np, sin_np = plain.rope_tables(40, rot, 10000.0)
+    cos, sin = torch.from_numpy(cos_np).to(DEV), torch.from_numpy(sin_np).to(DEV)
+    slots = torch.randperm(pages * page, generator=g)[:rows].to(torch.int32)
+    slots[3] = -1                                                   # one row's write is skipped
+    cache = torch.zeros(pages, 2, kv_heads, page, head_dim, dtype=dtype, device=DEV)
+    q_out = torch.empty(rows, heads * head_dim, dtype=dtype, device=DEV)
+    ops.head_norm_rope_kv(qkv, heads, kv_heads, head_dim, qw, kw, 1e-6, cos, sin, positions.to(DEV), slots.to(DEV),
+                          q_out, cache)
+    a = qkv.cpu().numpy()
+    q = a[:, :heads * head_dim].reshape(rows, heads, head_dim)
+    k = a[:, heads * head_dim:(heads + kv_heads) * head_dim].reshape(rows, kv_heads, head_dim)
+    v = a[:, (heads + kv_heads) * head_dim:].reshape(rows, kv_heads, head_dim)
+    if norm:
+        q, k = plain.rms_norm(q, qw.cpu().numpy(), 1e-6), plain.rms_norm(k, kw.cpu().numpy(), 1e-6)
+    c, s = cos_np[positions.numpy()], sin_np[positions.numpy()]
+
+    def rotate(x):
+        out = x.copy()
+        out[..., :rot] = plain.rope_rotate(x[..., :rot], c, s)
+        return out
+    q, k = rotate(q), rotate(k)
+    tol = 2 ** -7 if dtype is torch.bfloat16 else 1e-5
+    got_q = q_out.float().cpu().numpy().reshape(rows, heads, head_dim)
+    assert np.abs(got_q - q).max() <= tol * np.abs(q).max()
+    cache_np = cache.float().cpu().numpy()
+    for r in range(rows):
+        sl = int(slots[r])
+        if sl < 0:
+            continue
+        assert np.abs(cache_np[sl // page, 0, :, sl % page] - k[r]).max() <= tol * np.abs(k).max()
+        assert np.abs(cache_np[sl // page, 1, :, sl % page] - v[r]).max() <= tol * np.abs(v).max()
+    written = {int(s) for s in slots if s >= 0}
+    for sl in range(pages * page):
+        if sl not in written:
+            assert not cache_np[sl // page, :, :, sl % page].any()
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("m,n,k", [(1, 64, 16), (5, 100, 37), (70, 257, 100), (130, 384, 96)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gemm_plain(dtype, m, n, k):
+    from llmx_b200 import ops
+    g = torch.Generator().manual_seed(5)
+    a = torch.randn(m, k, generator=g).to(dtype).to(DEV)
+    w = torch.randn(n, k, generator=g).to(dtype).to(DEV)
+    base = torch.randn(m, n, generator=g).to(DEV)
+    ref = a.float().cpu().double() @ w.float().cpu().double().T
+    out = torch.empty(m, n, dtype=torch.float32, device=DEV)
+    ops.gemm_plain(a, w, out)
+    assert (out.cpu().double() - ref).abs().max() <= 1e-5 * ref.abs().max()
+    acc = base.clone()
+    ops.gemm_plain(a, w, acc, accumulate=True)
+    assert (acc.cpu().double() - (ref + base.cpu().double())).abs().max() <= 1e-5 * ref.abs().max()
+
+
+@pytest.mark.parametrize("m", [1, 3, 16, 17, 64, 65, 128, 200, 513])
+@pytest.mark.parametrize("n,k", [(128, 64), (100, 72), (384, 96), (1000, 160), (6144, 1024)])
+def test_gemm_tensor_core(m, n, k):
+    """The tcgen05 product at ragged sizes: M, N beyond a tile's edge, K that is no multiple of 64."""
+    from llmx_b200 import ops_tc
+    g = torch.Generator().manual_seed(6)
+    a = _bf16(torch.randn(m, k, generator=g)).to(DEV)
+    w = _bf16(torch.randn(n, k, generator=g) * 0.1).to(DEV)
+    ref = a.float().cpu().double() @ w.float().cpu().double().T
+    guard = torch.full((m + 2, n), 7.0, device=DEV)             # rows around the output must stay untouched
+    out = guard[1:m + 1]
+    ops_tc.gemm_tc(a, w, out)
+    torch.cuda.synchronize()
+    ops_tc.check_errors()
+    assert (out.cpu().double() - ref).abs().max() <= 2e-5 * max(1.0, ref.abs().max())
+    assert torch.all(guard[0] == 7.0) and torch.all(guard[m + 1] == 7.0)
+    base = torch.randn(m, n, generator=g).to(DEV)
+    for splits in (1, 2, 5):
+        acc = base.clone()
+        ops_tc.gemm_tc(a, w, acc, accumulate=True, splits=splits)
+        assert (acc.cpu().double() - (ref + base.cpu().double())).abs().max() <= 3e-5 * max(1.0, ref.abs().max())
+    ops_tc.check_errors()
+
+
+@pytest.mark.parametrize("tile", [16, 32, 64, 128, 256])
+def test_gemm_tensor_core_every_token_tile(tile):
+    from llmx_b200 import ops_tc
+    g = torch.Generator().manual_seed(7)
+    m, n, k = 300, 260, 200
+    a = _bf16(torch.randn(m, k, generator=g)).to(DEV)
+    w = _bf16(torch.randn(n, k, generator=g)).to(DEV)
+    out = torch.empty(m, n, device=DEV)
+    ops_tc.gemm_tc(a, w, out, token_tile=tile)
+    ref = a.float().cpu().double() @ w.float().cpu().double().T
+    ops_tc.check_errors()
+    assert (out.cpu().double() - ref).abs().max() <= 2e-5 * ref.abs().max()
+
+
+def test_gemm_tensor_core_refuses_unaligned_width():
+    from llmx_b200 import ops_tc
+    from llmx_b200.ops import KernelError
+    a = torch.zeros(4, 100, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(8, 100, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(KernelError):
+        ops_tc.gemm_tc(a, w, torch.empty(4, 8, device=DEV))
+
+
+# ---------------------------------------------------------------------------------------------
+def _attention_case(dtype, heads, kv_heads, head_dim, page, layout, window, seed, spike=False):
+    """A batch laid out as `layout` = [(history, new rows), ...] over a shuffled pool of pages.
+
+    Returns everything the kernels need plus the plain result.  With `spike`, one far key of every
+    request is made to stand out (its score dominates), so a kernel that drops or misplaces a page
+    shows a large error instead of one that random values average away."""
+    from llmx_b200.parts.base import GroupView, StepBatch
+    g = torch.Generator().manual_seed(seed)
+    n_req = len(layout)
+    lens = [h + n for h, n in layout]
+    pages_needed = [-(-l // page) for l in lens]
+    total_pages = sum(pages_needed) + 3
+    perm = torch.randperm(total_pages, generator=g).tolist()
+    cache = torch.randn(total_pages, 2, kv_heads, page, head_dim, generator=g)      # stale values everywhere
+    tables = np.zeros((n_req, max(pages_needed)), dtype=np.int32)
+    ks, vs, qs = [], [], []
+    rows = sum(n for _, n in layout)
+    row_start, at = [], 0
+    for r, (h, n) in enumerate(layout):
+        row_start.append(at)
+        at += n
+        k = torch.randn(lens[r], kv_heads, head_dim, generator=g)
+        v = torch.randn(lens[r], kv_heads, head_dim, generator=g)
+        q = torch.randn(n, heads, head_dim, generator=g)
+        if spike and lens[r] > 3:
+            far = max(0, lens[r] - (window or lens[r]) + 1) if window else 1
+            far = min(far, lens[r] - 1)
+            k[far] = q[-1, ::heads // kv_heads] * 4.0          # every group's key lines up with the last row's query
+        ks.append(k); vs.append(v); qs.append(q)
+        mine = [perm.pop() for _ in range(pages_needed[r])]
+        tables[r, :len(mine)] = mine
+        for t in range(lens[r]):
+            cache[mine[t // page], 0, :, t % page] = k[t]
+            cache[mine[t // page], 1, :, t % page] = v[t]
+    cache = cache.to(dtype)
+    q_all = torch.cat(qs).to(dtype)
+    ref = np.zeros((rows, heads, head_dim), dtype=np.float32)
+    for r, (h, n) in enumerate(layout):
+        full_q = np.zeros((lens[r], heads, head_dim), dtype=np.float32)
+        full_q[h:] = q_all[row_start[r]:row_start[r] + n].float().numpy()
+        kk = ks[r].to(dtype).float().numpy()
+        vv = vs[r].to(dtype).float().numpy()
+        ref[row_start[r]:row_start[r] + n] = plain.attention(full_q, kk, vv, window=window)[h:]
+    positions = np.concatenate([np.arange(h, h + n) for h, n in layout]).astype(np.int32)
+    row_request = np.concatenate([np.full(n, r) for r, (h, n) in enumerate(layout)]).astype(np.int32)
+
+    def dev(a):
+        return torch.as_tensor(np.asarray(a, dtype=np.int32)).to(DEV)
+    group = GroupView(dev(tables), dev(np.zeros(rows)), page)
+    step = StepBatch(rows=rows, requests=n_req, token_ids=dev(np.zeros(rows)), positions=dev(positions),
+                     row_request=dev(row_request), row_start=dev(row_start), row_count=dev([n for _, n in layout]),
+                     history=dev([h for h, _ in layout]), state_slots=dev([-1] * n_req), logit_rows=dev([]),
+                     groups=[group], caches=None, host_row_start=row_start, host_row_count=[n for _, n in layout],
+                     host_history=[h for h, _ in layout], max_row_count=max(n for _, n in layout), max_context=max(lens))
+    return q_all.reshape(rows, heads * head_dim).to(DEV).contiguous(), cache.to(DEV), step, group, ref.reshape(rows, -1)
+
+
+LAYOUTS = {
+    "decode": [(0, 1), (1, 1), (15, 1), (16, 1), (17, 1), (200, 1), (1027, 1)],
+    "prefill": [(0, 1), (0, 2), (0, 17), (0, 130), (0, 300)],
+    "mixed": [(40, 1), (0, 70), (128, 2), (63, 65), (5, 3), (300, 1), (16, 16)],
+}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(4, 2, 16, 8), (6, 3, 32, 16), (3, 1, 48, 4), (8, 8, 80, 16), (2, 1, 256, 32)])
+@pytest.mark.parametrize("layout", ["decode", "prefill", "mixed"])
+@pytest.mark.parametrize("window", [None, 19])
+def test_attention_plain(dtype, heads, kv_heads, head_dim, page, layout, window):
+    from llmx_b200 import ops
+    q, cache, step, group, ref = _attention_case(dtype, heads, kv_heads, head_dim, page, LAYOUTS[layout], window, seed=8)
+    out = torch.empty_like(q)
+    ops.attention_plain(q, cache, out, step.row_request, step.positions, group.block_tables, heads, kv_heads, head_dim,
+                        window, 1.0 / math.sqrt(head_dim))
+    tol = 2e-2 if dtype is torch.bfloat16 else 2e-5
+    assert np.abs(out.float().cpu().numpy() - ref).max() <= tol * max(1.0, np.abs(ref).max())
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim", [(32, 8, 128), (4, 4, 64), (16, 1, 128), (6, 2, 64), (8, 8, 128)])
+@pytest.mark.parametrize("layout", ["decode", "prefill", "mixed"])
+@pytest.mark.parametrize("window", [None, 100])
+@pytest.mark.parametrize("spike", [False, True])
+def test_attention_tiled_bf16(heads, kv_heads, head_dim, layout, window, spike):
+    """The split-KV decode kernel and the tiled prefill kernel behind the one dispatch the mixer calls."""
+    from llmx_b200 import ops_attn, ops_tc
+    assert ops_attn.supported(heads, kv_heads, head_dim, 16)
+    q, cache, step, group, ref = _attention_case(torch.bfloat16, heads, kv_heads, head_dim, 16, LAYOUTS[layout], window,
+                                                 seed=9, spike=spike)
+    out = torch.full_like(q, float("nan"))
+    ops_attn.paged_attention_bf16(q, cache, out, step, group, heads, kv_heads, head_dim, window, 1.0 / math.sqrt(head_dim))
+    torch.cuda.synchronize()
+    ops_tc.check_errors()
+    got = out.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    assert np.abs(got - ref).max() <= 2e-2 * max(1.0, np.abs(ref).max())
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 7, 16])
+def test_attention_decode_any_number_of_key_ranges(splits):
+    from llmx_b200 import ops_attn, ops_tc
+    heads, kv_heads, head_dim = 8, 2, 128
+    layout = [(1500, 1), (63, 1), (64, 1), (700, 2), (0, 1)]
+    q, cache, step, group, ref = _attention_case(torch.bfloat16, heads, kv_heads, head_dim, 16, layout, None, seed=10, spike=True)
+    chunk = -(-(-(-1501 // 64)) // splits) * 64
+    step.extras["decode_schedule"] = (splits, chunk, None)
+    out = torch.full_like(q, float("nan"))
+    ops_attn.paged_attention_bf16(q, cache, out, step, group, heads, kv_heads, head_dim, None, 1.0 / math.sqrt(head_dim))
+    torch.cuda.synchronize()
+    ops_tc.check_errors()
+    assert np.abs(out.float().cpu().numpy() - ref).max() <= 2e-2 * max(1.0, np.abs(ref).max())
+
+
+# ---------------------------------------------------------------------------------------------
+def _sample_rows(logits, settings):
+    from llmx_b200.sampling import RequestSampling, SamplingParams, sample
+    states = []
+    for s in settings:
+        st = RequestSampling(SamplingParams(**{k: v for k, v in s.items() if k not in ("gen", "masked")}),
+                             eos_id=s.get("masked", -1))
+        st.masked = s.get("masked", -1)
+        for t in s.get("gen", ()):
+            st.saw(t)
+        states.append(st)
+    got = sample(torch.from_numpy(logits).to(DEV).contiguous(), states)
+    return got, states
+
+
+@pytest.mark.parametrize("vocab", [5, 257, 5000, 151936])
+def test_sampling_against_the_plain_sampler(vocab):
+    """Every mode of the device sampler against the plain one, the same uniform number for both."""
+    rng = np.random.default_rng(vocab)
+    settings = [
+        dict(temp=0.0, top_k=0, top_p=1.0),
+        dict(temp=0.0, top_k=0, top_p=1.0, masked=0),
+        dict(temp=1.0, top_k=0, top_p=1.0, seed=3),
+        dict(temp=0.7, top_k=40, top_p=1.0, seed=4),
+        dict(temp=1.3, top_k=0, top_p=0.9, seed=5),
+        dict(temp=0.8, top_k=40, top_p=0.95, seed=6),
+        dict(temp=1.0, top_k=3, top_p=0.5, min_p=0.2, seed=7),
+        dict(temp=2.0, top_k=0, top_p=1.0, min_p=0.05, seed=8),
+        dict(temp=1.0, top_k=0, top_p=0.8, min_p=0.1, seed=9, masked=1),
+        dict(temp=0.0, top_k=0, top_p=1.0, penalty=1.5, presence_penalty=0.2, frequency_penalty=0.1, gen=[1, 2, 2, 4]),
+        dict(temp=0.9, top_k=10, top_p=0.9, penalty=1.2, seed=11, gen=[0, 3]),
+    ]
+    logits = (rng.standard_normal((len(settings), vocab)) * 3).astype(np.float32)
+    logits[0, :] = 0.0
+    logits[0, [2, 4]] = 5.0                                  # a tie: the lowest id wins
+    logits[3, :min(vocab, 60)] = 2.0                         # ties across the top-k edge: lowest ids are kept
+    expected = []
+    for row, s in zip(logits, settings):
+        r = 0.0 if s["temp"] <= 0 else plain.XorShift64(s.get("seed", 0)).unit()
+        expected.append(plain.sample(row, s["temp"], s["top_k"], s["top_p"], s.get("min_p", 0.0), r,
+                                     penalty=s.get("penalty", 1.0), presence=s.get("presence_penalty", 0.0),
+                                     frequency=s.get("frequency_penalty", 0.0), gen=list(s.get("gen", ())),
+                                     masked=s.get("masked", -1)))
+    got, _ = _sample_rows(logits.copy(), settings)
+    assert got == expected
+
+
+def test_sampling_distribution_and_independence_of_the_batch():
+    """Draws follow the softmax, and a request's draws do not depend on what shares its batch."""
+    from llmx_b200.sampling import RequestSampling, SamplingParams, sample
+    logits = torch.tensor([[0.0, 1.0, 2.0, -1.0]], device=DEV)
+    st = RequestSampling(SamplingParams(temp=1.0, top_k=0, top_p=1.0, seed=99))
+    counts = np.zeros(4)
+    alone = []
+    for _ in range(2000):
+        t = sample(logits, [st])[0]
+        alone.append(t)
+        counts[t] += 1
+    p = np.exp([0, 1, 2, -1.0]); p /= p.sum()
+    assert np.abs(counts / counts.sum() - p).max() < 0.04
+    st2 = RequestSampling(SamplingParams(temp=1.0, top_k=0, top_p=1.0, seed=99))
+    other = RequestSampling(SamplingParams(temp=0.5, top_k=2, top_p=0.9, seed=5))
+    both = torch.cat([torch.randn(1, 4, device=DEV), logits])
+    batched = [sample(both, [other, st2])[1] for _ in range(200)]
+    assert batched == alone[:200]
