@@ -63,6 +63,12 @@ def launch_count() -> int:
     return _launches
 
 
+def count_launches(n: int) -> None:
+    """Adds the kernels a replayed recording launches."""
+    global _launches
+    _launches += n
+
+
 def _check(status: int, what: str, launches: int = 1) -> None:
     global _launches
     _launches += launches
