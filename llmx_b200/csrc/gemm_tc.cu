@@ -10,14 +10,23 @@
 // memory, one elected thread issues tcgen05.mma, and the epilogue reads the accumulator with
 // tcgen05.ld and writes C with one warp store per 32 consecutive outputs of a token.
 //
-// The kernel is persistent: a block walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ...
-// with three roles:  warp 0 loads (TMA producer), warp 1 issues the matrix instructions,
-// warps 2-5 are the epilogue.  Two accumulators in tensor memory let the epilogue of one tile
-// overlap the products of the next.  `splits` > 1 cuts K into ranges that are added into C
-// with float atomics (only with accumulate, where C already holds the residual).
+// The kernel is persistent with three roles:  warp 0 loads (TMA producer), warp 1 issues the
+// matrix instructions, warps 2-5 are the epilogue.  Two accumulators in tensor memory let the
+// epilogue of one piece of work overlap the products of the next.  Work is handed out in one
+// of two ways:
+//   tiles     a block walks whole output tiles (blockIdx.x, + gridDim.x, ...), optionally with K
+//             cut into `splits` ranges that are added with float atomics; used for many tokens.
+//   stream-K  all (tile, k block) units are cut into gridDim.x equal runs; a block's run may end
+//             one tile and begin the next, and every piece is added to C with float atomics
+//             (C is zeroed first when the product is to be stored).  A few tokens make few
+//             tiles; this keeps every SM streaming weights whatever N is.
+// A third form, DUAL, computes two products that share the token tile -- rows n and n + N/2 of
+// the weight (gate and up of a gated feed-forward) -- into two accumulators and writes
+// silu(gate) * up as bfloat16, so the [tokens, 2 * intermediate] float32 matrix never exists.
 //
 // The reference has no tensor-core path for this product (its kernels: f32.gpu:1034-1084).
 #include "tc_common.cuh"
+#include <math.h>
 
 namespace {
 
@@ -27,24 +36,73 @@ constexpr int UMMA_K = 16;
 constexpr int EPI_WARPS = 4;
 constexpr int THREADS = 64 + EPI_WARPS * 32;
 
-enum : int { MODE_STORE = 0, MODE_ACCUMULATE = 1 };
+enum : int { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_ATOMIC = 2, MODE_SWIGLU = 3 };
 enum : int { ERR_PRODUCER = 101, ERR_MMA_FULL = 102, ERR_MMA_ACC = 103, ERR_EPILOGUE = 104 };
 
-template <int BN>
+template <int BN, bool DUAL>
 struct Cfg {
-    static constexpr int A_BYTES = BM * BK * 2;          // weight tile
+    static constexpr int A_TILES = DUAL ? 2 : 1;
+    static constexpr int A_BYTES = BM * BK * 2;          // one weight tile
     static constexpr int B_BYTES = BN * BK * 2;          // token tile
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
     static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
-    static constexpr int TMEM_COLS = (2 * BN) < 32 ? 32 : (2 * BN);
+    static constexpr int ACC_COLS = A_TILES * BN;        // columns of one accumulator set
+    static constexpr int TMEM_COLS = (2 * ACC_COLS) < 32 ? 32 : (2 * ACC_COLS);
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    static_assert(TMEM_COLS <= 512, "two accumulator sets must fit tensor memory");
 };
 
-template <int BN>
+struct Work {
+    int nt, mt, kb0, kb1;
+};
+
+// Hands a block its pieces of work, the same sequence in every role.
+template <bool STREAMK>
+struct Scheduler {
+    int n_tiles, m_tiles, k_blocks, splits;
+    long long cur, end;
+    __device__ Scheduler(int n_tiles_, int m_tiles_, int k_blocks_, int splits_)
+        : n_tiles(n_tiles_), m_tiles(m_tiles_), k_blocks(k_blocks_), splits(splits_) {
+        if (STREAMK) {
+            const long long units = (long long)n_tiles * m_tiles * k_blocks;
+            const long long per = (units + gridDim.x - 1) / gridDim.x;
+            cur = per * blockIdx.x;
+            end = cur + per < units ? cur + per : units;
+        } else {
+            cur = blockIdx.x;
+            end = (long long)n_tiles * m_tiles * splits;
+        }
+    }
+    __device__ bool next(Work& w) {
+        if (cur >= end) return false;
+        if (STREAMK) {
+            const long long tile = cur / k_blocks;
+            w.kb0 = (int)(cur % k_blocks);
+            const long long left = end - cur;
+            w.kb1 = (k_blocks - w.kb0) < left ? k_blocks : (int)(w.kb0 + left);
+            w.mt = (int)(tile % m_tiles);
+            w.nt = (int)(tile / m_tiles);
+            cur += w.kb1 - w.kb0;
+        } else {
+            // Token tiles vary fastest, so neighbouring blocks share a weight tile.
+            w.mt = (int)(cur % m_tiles);
+            const long long rest = cur / m_tiles;
+            w.nt = (int)(rest % n_tiles);
+            const int sp = (int)(rest / n_tiles);
+            const int per = (k_blocks + splits - 1) / splits;
+            w.kb0 = sp * per;
+            w.kb1 = min(k_blocks, w.kb0 + per);
+            cur += gridDim.x;
+        }
+        return true;
+    }
+};
+
+template <int BN, bool STREAMK, bool DUAL>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
-               float* __restrict__ C, int M, int N, int K, int mode, int splits, int* error_word) {
-    using cfg = Cfg<BN>;
+               void* __restrict__ C_, int M, int N, int K, int mode, int splits, int* error_word) {
+    using cfg = Cfg<BN, DUAL>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* tiles = smem;
@@ -56,10 +114,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // DUAL: N counts the outputs (half the weight's rows); rows n and n + N belong together.
     const int n_tiles = (N + BM - 1) / BM, m_tiles = (M + BN - 1) / BN;
-    const int k_blocks_total = (K + BK - 1) / BK;
-    const int k_per_split = (k_blocks_total + splits - 1) / splits;
-    const int total = n_tiles * m_tiles * splits;
+    const int k_blocks = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < cfg::STAGES; ++s) {
@@ -84,23 +141,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     tc::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    // A work item is (n tile, m tile, k split); m tiles vary fastest so neighbouring blocks share a weight tile.
     if (warp == 0) {
         if (tc::elect_one()) {
+            Scheduler<STREAMK> sched(n_tiles, m_tiles, k_blocks, splits);
+            Work w;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
-                const int mt = item % m_tiles, rest = item / m_tiles;
-                const int nt = rest % n_tiles, sp = rest / n_tiles;
-                const int kb0 = sp * k_per_split, kb1 = min(k_blocks_total, kb0 + k_per_split);
-                for (int kb = kb0; kb < kb1; ++kb) {
+            while (ok && sched.next(w)) {
+                for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     ok = tc::mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, error_word, ERR_PRODUCER);
                     if (!ok) break;
                     uint8_t* a_dst = tiles + stage * cfg::STAGE_BYTES;
-                    uint8_t* b_dst = a_dst + cfg::A_BYTES;
+                    uint8_t* b_dst = a_dst + cfg::A_TILES * cfg::A_BYTES;
                     tc::mbar_expect_tx(&full_bar[stage], cfg::STAGE_BYTES);
-                    tc::tma_load_2d(a_dst, &map_w, kb * BK, nt * BM, &full_bar[stage]);
-                    tc::tma_load_2d(b_dst, &map_a, kb * BK, mt * BN, &full_bar[stage]);
+                    tc::tma_load_2d(a_dst, &map_w, kb * BK, w.nt * BM, &full_bar[stage]);
+                    if (DUAL) tc::tma_load_2d(a_dst + cfg::A_BYTES, &map_w, kb * BK, N + w.nt * BM, &full_bar[stage]);
+                    tc::tma_load_2d(b_dst, &map_a, kb * BK, w.mt * BN, &full_bar[stage]);
                     if (++stage == cfg::STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -108,26 +164,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     } else if (warp == 1) {
         if (tc::elect_one()) {
             constexpr uint32_t idesc = tc::instr_desc_bf16(BM, BN);
+            Scheduler<STREAMK> sched(n_tiles, m_tiles, k_blocks, splits);
+            Work w;
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
-            for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
-                const int sp = item / (m_tiles * n_tiles);
-                const int kb0 = sp * k_per_split, kb1 = min(k_blocks_total, kb0 + k_per_split);
+            while (ok && sched.next(w)) {
                 ok = tc::mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, error_word, ERR_MMA_ACC);
                 if (!ok) break;
                 tc::tc_fence_after();
-                const uint32_t tmem_d = tmem_base + acc * BN;
-                for (int kb = kb0; kb < kb1; ++kb) {
+                const uint32_t tmem_d = tmem_base + acc * cfg::ACC_COLS;
+                for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     ok = tc::mbar_wait(&full_bar[stage], phase, abort_flag, error_word, ERR_MMA_FULL);
                     if (!ok) break;
                     tc::tc_fence_after();
                     const uint32_t a_addr = tc::smem_u32(tiles + stage * cfg::STAGE_BYTES);
                     const uint64_t desc_a = tc::smem_desc_k_sw128(a_addr);
-                    const uint64_t desc_b = tc::smem_desc_k_sw128(a_addr + cfg::A_BYTES);
+                    const uint64_t desc_b = tc::smem_desc_k_sw128(a_addr + cfg::A_TILES * cfg::A_BYTES);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         // 16 elements = 32 bytes further along the swizzled row: +2 in the descriptor's 16-byte units.
-                        tc::mma_bf16_ss(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        const uint32_t accumulate = (kb > w.kb0 || k > 0) ? 1u : 0u;
+                        tc::mma_bf16_ss(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, accumulate);
+                        if (DUAL) {
+                            const uint64_t desc_a2 = tc::smem_desc_k_sw128(a_addr + cfg::A_BYTES);
+                            tc::mma_bf16_ss(tmem_d + BN, desc_a2 + 2 * k, desc_b + 2 * k, idesc, accumulate);
+                        }
                     }
                     tc::mma_commit(&empty_bar[stage]);   // the stage is free once these instructions have read it
                     if (++stage == cfg::STAGES) { stage = 0; phase ^= 1; }
@@ -140,36 +201,54 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     } else {
         // Epilogue: warp w may read the tensor-memory lanes 32 * (w % 4) .. + 31.
         const int quarter = warp & 3;
+        Scheduler<STREAMK> sched(n_tiles, m_tiles, k_blocks, splits);
+        Work w;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
-        for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
-            const int mt = item % m_tiles, rest = item / m_tiles;
-            const int nt = rest % n_tiles, sp = rest / n_tiles;
-            const int kb0 = sp * k_per_split, kb1 = min(k_blocks_total, kb0 + k_per_split);
+        const bool atomic = STREAMK || mode == MODE_ATOMIC || (mode == MODE_ACCUMULATE && splits > 1);
+        while (ok && sched.next(w)) {
             ok = tc::mbar_wait(&acc_full[acc], acc_phase, abort_flag, error_word, ERR_EPILOGUE);
             if (!ok) break;
             tc::tc_fence_after();
-            const int n = nt * BM + quarter * 32 + lane;
-            const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
-            const bool atomic = splits > 1;
-            if (kb1 > kb0) {
+            const int n = w.nt * BM + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + acc * cfg::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+            if (w.kb1 > w.kb0) {
                 constexpr int CH = BN < 32 ? 16 : 32;
 #pragma unroll 1
                 for (int c = 0; c < BN; c += CH) {
                     uint32_t r[CH];
                     if constexpr (CH == 32) tc::tmem_ld_32x32(taddr + c, r);
                     else tc::tmem_ld_32x16(taddr + c, r);
-                    tc::tmem_wait_ld();
-                    if (n < N) {
+                    if constexpr (DUAL) {
+                        uint32_t u[CH];
+                        if constexpr (CH == 32) tc::tmem_ld_32x32(taddr + BN + c, u);
+                        else tc::tmem_ld_32x16(taddr + BN + c, u);
+                        tc::tmem_wait_ld();
+                        if (n < N) {
+                            __nv_bfloat16* C = (__nv_bfloat16*)C_;
 #pragma unroll
-                        for (int j = 0; j < CH; ++j) {
-                            const int m = mt * BN + c + j;
-                            if (m < M) {
-                                float* dst = C + (size_t)m * N + n;
-                                const float v = __uint_as_float(r[j]);
-                                if (mode == MODE_STORE) *dst = v;
-                                else if (atomic) atomicAdd(dst, v);
-                                else *dst += v;
+                            for (int j = 0; j < CH; ++j) {
+                                const int m = w.mt * BN + c + j;
+                                if (m < M) {
+                                    const float g = __uint_as_float(r[j]), up = __uint_as_float(u[j]);
+                                    C[(size_t)m * N + n] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * up);
+                                }
+                            }
+                        }
+                    } else {
+                        tc::tmem_wait_ld();
+                        if (n < N) {
+                            float* C = (float*)C_;
+#pragma unroll
+                            for (int j = 0; j < CH; ++j) {
+                                const int m = w.mt * BN + c + j;
+                                if (m < M) {
+                                    float* dst = C + (size_t)m * N + n;
+                                    const float v = __uint_as_float(r[j]);
+                                    if (atomic) atomicAdd(dst, v);
+                                    else if (mode == MODE_STORE) *dst = v;
+                                    else *dst += v;
+                                }
                             }
                         }
                     }
@@ -191,24 +270,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
 int g_sm_count = 0;
 
-template <int BN>
-int launch(const CUtensorMap& map_w, const void* A, float* C, int M, int N, int K, int mode, int splits,
+template <int BN, bool STREAMK, bool DUAL>
+int launch(const CUtensorMap& map_w, const void* A, void* C, int M, int N, int K, int mode, int splits,
            int* error_word, cudaStream_t stream) {
-    using cfg = Cfg<BN>;
+    using cfg = Cfg<BN, DUAL>;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES) !=
-            cudaSuccess)
+        if (cudaFuncSetAttribute(gemm_tc_kernel<BN, STREAMK, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 cfg::SMEM_BYTES) != cudaSuccess)
             return (int)cudaGetLastError();
         configured = true;
     }
     CUtensorMap map_a;
     if (int e = llmx_make_map_bf16_2d(&map_a, A, (uint64_t)M, (uint64_t)K, BN, BK)) return e;
-    const int n_tiles = (N + BM - 1) / BM, m_tiles = (M + BN - 1) / BN;
-    const int total = n_tiles * m_tiles * splits;
-    const int grid = total < g_sm_count ? total : g_sm_count;
-    gemm_tc_kernel<BN><<<grid, THREADS, cfg::SMEM_BYTES, stream>>>(map_w, map_a, C, M, N, K, mode, splits, error_word);
+    const int n_tiles = (N + BM - 1) / BM, m_tiles = (M + BN - 1) / BN, k_blocks = (K + BK - 1) / BK;
+    long long grid;
+    if (STREAMK) {
+        // Every block at least four k blocks, so that a tiny product does not pay 148 prologues.
+        const long long units = (long long)n_tiles * m_tiles * k_blocks;
+        grid = (units + 3) / 4;
+    } else {
+        grid = (long long)n_tiles * m_tiles * splits;
+    }
+    if (grid > g_sm_count) grid = g_sm_count;
+    if (grid < 1) grid = 1;
+    gemm_tc_kernel<BN, STREAMK, DUAL><<<(unsigned)grid, THREADS, cfg::SMEM_BYTES, stream>>>(
+        map_w, map_a, C, M, N, K, mode, splits, error_word);
     return launch_status();
+}
+
+void ensure_sm_count() {
+    if (!g_sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (g_sm_count <= 0) g_sm_count = 148;
+    }
 }
 
 }  // namespace
@@ -219,30 +316,56 @@ LLMX_EXPORT int llmx_gemm_tc_weight_map(void* out, const void* W, int N, int K) 
     return llmx_make_map_bf16_2d((CUtensorMap*)out, W, (uint64_t)N, (uint64_t)K, BM, BK);
 }
 
-// mode 0: C = A W^T;  mode 1: C += A W^T.  `splits` > 1 (only with mode 1) cuts K and adds with atomics.
+// mode 0: C = A W^T;  mode 1: C += A W^T (float32 C [M, N]).
+// schedule 0 (tiles): `splits` > 1 (only with mode 1) cuts K and adds with atomics.
+// schedule 1 (stream-K): every piece is added with atomics; with mode 0 the caller zeroes C first.
 // `token_tile` is 16, 32, 64, 128 or 256 (0: chosen from M).  `error_word`: device int, zero before first use.
 LLMX_EXPORT int llmx_gemm_tc(const void* weight_map, const void* A, float* C, int M, int N, int K, int mode,
-                             int splits, int token_tile, int* error_word, cudaStream_t stream) {
+                             int splits, int token_tile, int schedule, int* error_word, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || ((uintptr_t)A & 15) || ((uintptr_t)C & 3)) return LLMX_ERR_UNSUPPORTED;
+    if (mode != MODE_STORE && mode != MODE_ACCUMULATE) return LLMX_ERR_BAD_ARGUMENT;
     if (splits < 1 || (splits > 1 && mode != MODE_ACCUMULATE)) return LLMX_ERR_BAD_ARGUMENT;
-    if (!g_sm_count) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (g_sm_count <= 0) g_sm_count = 148;
-    }
+    ensure_sm_count();
     const int k_blocks = (K + BK - 1) / BK;
     if (splits > k_blocks) splits = k_blocks;
     int bn = token_tile;
     if (bn == 0) bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
     const CUtensorMap& map_w = *(const CUtensorMap*)weight_map;
+    if (schedule == 1) {
+        switch (bn) {
+            case 16: return launch<16, true, false>(map_w, A, C, M, N, K, mode, 1, error_word, stream);
+            case 32: return launch<32, true, false>(map_w, A, C, M, N, K, mode, 1, error_word, stream);
+            case 64: return launch<64, true, false>(map_w, A, C, M, N, K, mode, 1, error_word, stream);
+            case 128: return launch<128, true, false>(map_w, A, C, M, N, K, mode, 1, error_word, stream);
+            case 256: return launch<256, true, false>(map_w, A, C, M, N, K, mode, 1, error_word, stream);
+            default: return LLMX_ERR_BAD_ARGUMENT;
+        }
+    }
     switch (bn) {
-        case 16: return launch<16>(map_w, A, C, M, N, K, mode, splits, error_word, stream);
-        case 32: return launch<32>(map_w, A, C, M, N, K, mode, splits, error_word, stream);
-        case 64: return launch<64>(map_w, A, C, M, N, K, mode, splits, error_word, stream);
-        case 128: return launch<128>(map_w, A, C, M, N, K, mode, splits, error_word, stream);
-        case 256: return launch<256>(map_w, A, C, M, N, K, mode, splits, error_word, stream);
+        case 16: return launch<16, false, false>(map_w, A, C, M, N, K, mode, splits, error_word, stream);
+        case 32: return launch<32, false, false>(map_w, A, C, M, N, K, mode, splits, error_word, stream);
+        case 64: return launch<64, false, false>(map_w, A, C, M, N, K, mode, splits, error_word, stream);
+        case 128: return launch<128, false, false>(map_w, A, C, M, N, K, mode, splits, error_word, stream);
+        case 256: return launch<256, false, false>(map_w, A, C, M, N, K, mode, splits, error_word, stream);
+        default: return LLMX_ERR_BAD_ARGUMENT;
+    }
+}
+
+// out[m, n] = silu(A W[n]^T) * (A W[n + N]^T) as bfloat16 [M, N]; the weight has 2 N rows (gate rows, then up rows).
+LLMX_EXPORT int llmx_gemm_tc_swiglu(const void* weight_map, const void* A, void* out, int M, int N, int K,
+                                    int token_tile, int* error_word, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || ((uintptr_t)A & 15) || ((uintptr_t)out & 1)) return LLMX_ERR_UNSUPPORTED;
+    ensure_sm_count();
+    int bn = token_tile;
+    if (bn == 0) bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+    const CUtensorMap& map_w = *(const CUtensorMap*)weight_map;
+    switch (bn) {
+        case 16: return launch<16, false, true>(map_w, A, out, M, N, K, MODE_SWIGLU, 1, error_word, stream);
+        case 32: return launch<32, false, true>(map_w, A, out, M, N, K, MODE_SWIGLU, 1, error_word, stream);
+        case 64: return launch<64, false, true>(map_w, A, out, M, N, K, MODE_SWIGLU, 1, error_word, stream);
+        case 128: return launch<128, false, true>(map_w, A, out, M, N, K, MODE_SWIGLU, 1, error_word, stream);
         default: return LLMX_ERR_BAD_ARGUMENT;
     }
 }

@@ -57,9 +57,71 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_float<OutT>(src[i] * (rr * w[i]));
 }
 
+// The same for widths that are a multiple of 4 and at most 4 * VEC_MAX * blockDim: each thread keeps its
+// values in registers (one read of the row, 16-byte loads all issued before the first is used).
+constexpr int NORM_VEC_MAX = 8;
+
+__device__ __forceinline__ void store4(float* dst, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* dst, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 v;
+    v.x = *reinterpret_cast<uint32_t*>(&lo);
+    v.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = v;
+}
+
+template <typename OutT>
+__global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, OutT* __restrict__ y,
+                                   const int* __restrict__ row_index, int width, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const float4* src = reinterpret_cast<const float4*>(x + (size_t)(row_index ? row_index[r] : r) * width);
+    const float4* wv = reinterpret_cast<const float4*>(w);
+    const int n4 = width >> 2;
+    float4 v[NORM_VEC_MAX];
+#pragma unroll
+    for (int k = 0; k < NORM_VEC_MAX; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        v[k] = i < n4 ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float s = 0.0f;
+#pragma unroll
+    for (int k = 0; k < NORM_VEC_MAX; ++k) {
+        s = fmaf(v[k].x, v[k].x, s);
+        s = fmaf(v[k].y, v[k].y, s);
+        s = fmaf(v[k].z, v[k].z, s);
+        s = fmaf(v[k].w, v[k].w, s);
+    }
+    s = block_sum(s, scratch);
+    const float rr = 1.0f / sqrtf(s / (float)width + eps);
+    OutT* dst = y + (size_t)r * width;
+#pragma unroll
+    for (int k = 0; k < NORM_VEC_MAX; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < n4) {
+            const float4 ww = wv[i];
+            store4(dst + 4 * i, v[k].x * (rr * ww.x), v[k].y * (rr * ww.y), v[k].z * (rr * ww.z), v[k].w * (rr * ww.w));
+        }
+    }
+}
+
 LLMX_EXPORT int llmx_rmsnorm(const float* x, const float* w, void* y, int out_dtype, const int* row_index, int rows,
                              int width, float eps, cudaStream_t stream) {
     if (rows <= 0) return 0;
+    const bool aligned = width % 4 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)w & 15) && !((uintptr_t)y & 15);
+    if (aligned && width <= 4 * NORM_VEC_MAX * 256) {
+        const int n4 = width / 4;
+        // The block width depends on the row width alone, so a row's sum has one order whatever the batch.
+        int threads = ((n4 + 3) / 4 + 31) / 32 * 32;
+        threads = threads < 32 ? 32 : threads > 256 ? 256 : threads;
+        if (out_dtype == LLMX_BF16)
+            rmsnorm_vec_kernel<<<rows, threads, 0, stream>>>(x, w, (__nv_bfloat16*)y, row_index, width, eps);
+        else
+            rmsnorm_vec_kernel<<<rows, threads, 0, stream>>>(x, w, (float*)y, row_index, width, eps);
+        return launch_status();
+    }
     const int threads = width >= 1024 ? 256 : 128;
     if (out_dtype == LLMX_BF16)
         rmsnorm_kernel<<<rows, threads, 0, stream>>>(x, w, (__nv_bfloat16*)y, row_index, width, eps);

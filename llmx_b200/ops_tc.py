@@ -11,7 +11,8 @@ from .ops import KernelError, _check, _cuda, _fn, _need, _ptr, _stream, register
 
 _i, _p = ctypes.c_int, ctypes.c_void_p
 register_signature("gemm_tc", "llmx_gemm_tc_weight_map", [_p, _p, _i, _i])
-register_signature("gemm_tc", "llmx_gemm_tc", [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _p])
+register_signature("gemm_tc", "llmx_gemm_tc", [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p])
+register_signature("gemm_tc", "llmx_gemm_tc_swiglu", [_p, _p, _p, _i, _i, _i, _i, _p, _p])
 
 _error_words: Dict[int, torch.Tensor] = {}
 _ERROR_NAMES = {101: "the TMA producer waited for a free stage", 102: "the MMA issuer waited for a loaded stage",
@@ -64,20 +65,23 @@ def weight_map(weight: torch.Tensor) -> WeightMap:
     return m
 
 
-def _splits(m: int, n: int, k: int, accumulate: bool, sms: int = 148) -> int:
-    """K splits for a product whose tiles alone would leave most of the GPU idle."""
-    if not accumulate:
-        return 1
-    tiles = -(-n // 128) * -(-m // 256 if m > 128 else 1)
-    if tiles >= sms // 2:
-        return 1
-    k_blocks = -(-k // 64)
-    return max(1, min(sms // tiles, k_blocks // 8, 8))
+STREAM_K_MAX_ROWS = 64          # at most this many tokens: few tiles, so (tile, k block) units are shared out evenly
+STREAM_K_MAX_TILES = 4 * 148    # ... unless the weight alone makes plenty of tiles (the logits head)
+
+
+def _schedule(m: int, n: int) -> int:
+    return 1 if m <= STREAM_K_MAX_ROWS and -(-n // 128) < STREAM_K_MAX_TILES else 0
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
-            wmap: Optional[WeightMap] = None, splits: Optional[int] = None, token_tile: int = 0) -> torch.Tensor:
-    """out (+)= a @ w.T; a [M, K] bfloat16, w [N, K] bfloat16, out float32 [M, N]."""
+            wmap: Optional[WeightMap] = None, splits: Optional[int] = None, token_tile: int = 0,
+            schedule: Optional[int] = None) -> torch.Tensor:
+    """out (+)= a @ w.T; a [M, K] bfloat16, w [N, K] bfloat16, out float32 [M, N].
+
+    schedule 0 walks whole tiles (`splits` > 1 cuts K, only with accumulate); schedule 1 (stream-K) shares
+    out (tile, k block) units evenly and adds every piece with atomics, zeroing `out` first unless
+    accumulating.  By default few tokens take stream-K and many take tiles.
+    """
     _cuda(a, w, out)
     m, k = a.shape
     n = w.shape[0]
@@ -86,9 +90,29 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
     _need(w.shape[1] == k and tuple(out.shape) == (m, n), "gemm_tc: shapes do not fit")
     _need(k % 8 == 0, "gemm_tc: the input width must be a multiple of 8 (TMA row stride of 16 bytes)")
     wmap = wmap or weight_map(w)
+    if schedule is None:
+        schedule = _schedule(m, n) if splits is None else 0
     if splits is None:
-        splits = _splits(m, n, k, accumulate)
+        splits = 1
+    if schedule == 1 and not accumulate:
+        out.zero_()
     _check(_fn("gemm_tc", "llmx_gemm_tc")(ctypes.c_void_p(wmap.address), _ptr(a), _ptr(out), m, n, k,
-                                          1 if accumulate else 0, splits, token_tile,
+                                          1 if accumulate else 0, splits, token_tile, schedule,
                                           _ptr(error_word(a.device)), _stream()), "gemm_tc")
+    return out
+
+
+def gemm_tc_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, wmap: Optional[WeightMap] = None,
+                   token_tile: int = 0) -> torch.Tensor:
+    """out = silu(a @ w[:F].T) * (a @ w[F:].T) as bfloat16 [M, F]; w [2F, K] holds the gate rows, then the up rows."""
+    _cuda(a, w, out)
+    m, k = a.shape
+    f = w.shape[0] // 2
+    _need(a.dtype is torch.bfloat16 and w.dtype is torch.bfloat16 and out.dtype is torch.bfloat16,
+          "gemm_tc_swiglu: bfloat16 inputs and output")
+    _need(w.shape[0] == 2 * f and w.shape[1] == k and tuple(out.shape) == (m, f), "gemm_tc_swiglu: shapes do not fit")
+    _need(k % 8 == 0, "gemm_tc_swiglu: the input width must be a multiple of 8")
+    wmap = wmap or weight_map(w)
+    _check(_fn("gemm_tc", "llmx_gemm_tc_swiglu")(ctypes.c_void_p(wmap.address), _ptr(a), _ptr(out), m, f, k,
+                                                 token_tile, _ptr(error_word(a.device)), _stream()), "gemm_tc_swiglu")
     return out

@@ -40,3 +40,17 @@ class Linear:
                 self._tc = ops_tc.WeightMap(self.weight)
             return ops_tc.gemm_tc(a, self.weight, out, accumulate, wmap=self._tc)
         return ops.gemm_plain(a, self.weight, out, accumulate)
+
+    def gated(self, a: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """out = silu(a @ Wg.T) * (a @ Wu.T) for a weight that stacks gate rows on up rows, in one kernel
+        (tensor-core path only; the caller checks `fused_gate`)."""
+        from .. import ops_tc
+        if self._tc is None:
+            self._tc = ops_tc.WeightMap(self.weight)
+        return ops_tc.gemm_tc_swiglu(a, self.weight, out, wmap=self._tc)
+
+    def fused_gate(self, rows: int) -> bool:
+        """Whether the gated form runs for this many rows: with few rows the product is spread over the
+        SMs by k ranges, whose partial sums cannot pass through the activation."""
+        from .. import ops_tc
+        return self.tensor_core and rows > ops_tc.STREAM_K_MAX_ROWS

@@ -35,7 +35,9 @@ class GatedMLP(Part):
         self.down = Linear(tensors["down_proj.weight"], precision)
 
     def forward(self, h: torch.Tensor, step: StepBatch, residual: torch.Tensor) -> None:
-        gu = self.gate_up(h)
         act = torch.empty((h.shape[0], self.intermediate), dtype=self.precision.act, device=h.device)
-        ops.swiglu(gu, act)
+        if self.gate_up.fused_gate(h.shape[0]):
+            self.gate_up.gated(h, act)
+        else:
+            ops.swiglu(self.gate_up(h), act)
         self.down(act, out=residual, accumulate=True)

@@ -355,3 +355,38 @@ def test_sampling_distribution_and_independence_of_the_batch():
     both = torch.cat([torch.randn(1, 4, device=DEV), logits])
     batched = [sample(both, [other, st2])[1] for _ in range(200)]
     assert batched == alone[:200]
+
+
+@pytest.mark.parametrize("m", [1, 8, 33, 64])
+@pytest.mark.parametrize("n,k", [(128, 64), (100, 72), (1000, 160), (6144, 1024), (4096, 4096)])
+def test_gemm_tensor_core_stream_k(m, n, k):
+    """Few tokens: (tile, k block) units shared out evenly, pieces added with atomics."""
+    from llmx_b200 import ops_tc
+    g = torch.Generator().manual_seed(12)
+    a = _bf16(torch.randn(m, k, generator=g)).to(DEV)
+    w = _bf16(torch.randn(n, k, generator=g) * 0.1).to(DEV)
+    ref = a.float().cpu().double() @ w.float().cpu().double().T
+    out = torch.full((m, n), 5.0, device=DEV)
+    ops_tc.gemm_tc(a, w, out, schedule=1)
+    assert (out.cpu().double() - ref).abs().max() <= 3e-5 * max(1.0, ref.abs().max())
+    base = torch.randn(m, n, generator=g).to(DEV)
+    acc = base.clone()
+    ops_tc.gemm_tc(a, w, acc, accumulate=True, schedule=1)
+    ops_tc.check_errors()
+    assert (acc.cpu().double() - (ref + base.cpu().double())).abs().max() <= 3e-5 * max(1.0, ref.abs().max())
+
+
+@pytest.mark.parametrize("m", [1, 16, 70, 128, 300])
+@pytest.mark.parametrize("f,k", [(128, 64), (172, 104), (200, 128), (1536, 512)])
+def test_gemm_tensor_core_gated(m, f, k):
+    """silu(gate) * up in the product's epilogue, for intermediate widths that are no multiple of a tile."""
+    from llmx_b200 import ops_tc
+    g = torch.Generator().manual_seed(13)
+    a = _bf16(torch.randn(m, k, generator=g)).to(DEV)
+    w = _bf16(torch.randn(2 * f, k, generator=g) * 0.2).to(DEV)
+    out = torch.empty(m, f, dtype=torch.bfloat16, device=DEV)
+    ops_tc.gemm_tc_swiglu(a, w, out)
+    ops_tc.check_errors()
+    gu = (a.float().cpu().double() @ w.float().cpu().double().T).numpy()
+    ref = plain.silu(gu[:, :f].astype(np.float32)) * gu[:, f:].astype(np.float32)
+    assert np.abs(out.float().cpu().numpy() - ref).max() <= 2 ** -7 * max(1.0, np.abs(ref).max())
