@@ -29,7 +29,7 @@ class DecodeSession:
     def __init__(self, engine: Engine, request_ids: Sequence[Hashable], use_graph: bool = True):
         self.engine = engine
         self.request_ids = list(request_ids)
-        self.use_graph = use_graph
+        self.use_graph = use_graph and engine.model.recordable
         self.h2d_bytes_per_step = 0
         self.graph_launches = 0          # kernels one replay launches
         self._graph: Optional[torch.cuda.CUDAGraph] = None

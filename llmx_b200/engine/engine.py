@@ -193,6 +193,7 @@ class Engine:
                          row_start=dsec(3), row_count=dsec(4), history=dsec(5), state_slots=dsec(6),
                          logit_rows=dsec(7), groups=groups, caches=self.cache,
                          host_row_start=[int(s) for s in starts], host_row_count=counts, host_history=history,
+                         host_state_slots=[rc.state_slot for rc in caches],
                          max_row_count=max(counts), max_context=max(h + c for h, c in zip(history, counts)))
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:

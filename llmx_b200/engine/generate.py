@@ -15,6 +15,7 @@ from typing import Dict, Hashable, Iterable, List, Optional, Sequence, Union
 import torch
 
 from ..sampling import RequestSampling, SamplingParams, sample
+from .decode_loop import DecodeSession
 from .engine import Engine, EngineOptions, StepEntry
 from .scheduler import PlannedEntry, Request, Scheduler
 
@@ -61,6 +62,8 @@ class LLM:
         self.ubatch, self.max_seqs, self.reserve = int(ubatch), int(max_seqs), reserve
         self.stats = GenerationStats()
         self._next_id = 0
+        self._session: Optional[DecodeSession] = None
+        self._session_ids = None
 
     @staticmethod
     def _default_kv_tokens(model_dir: str, dtype: str, page_size: int, device: str) -> int:
@@ -83,6 +86,24 @@ class LLM:
                          max_positions=self.engine.max_positions, max_batch_tokens=self.ubatch,
                          max_requests=min(self.max_seqs, self.engine.options.max_requests), max_queue=1 << 30,
                          reserve=self.reserve, page_size=cache.page_size, eos_ids=self.engine.model.eos_ids)
+
+    def _run(self, entries: Sequence[PlannedEntry]) -> Optional[torch.Tensor]:
+        """One step.  While the same requests decode step after step, the step is a decode session's
+        (recorded once, replayed); any other step goes through `Engine.step`."""
+        ids = tuple(e.request.request_id for e in entries)
+        if all(len(e.tokens) == 1 and e.want_last and e.request.decoding for e in entries):
+            if self._session is None or self._session_ids != ids:
+                self._close_session()
+                self._session, self._session_ids = DecodeSession(self.engine, ids), ids
+            return self._session.step([e.tokens[0] for e in entries])
+        self._close_session()
+        return self.engine.step([StepEntry(e.request.request_id, e.tokens, [len(e.tokens) - 1] if e.want_last else [])
+                                 for e in entries])
+
+    def _close_session(self) -> None:
+        if self._session is not None:
+            self._session.close()
+        self._session, self._session_ids = None, None
 
     def generate(self, prompts: Sequence[Sequence[int]],
                  params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
@@ -117,9 +138,7 @@ class LLM:
                     break
                 raise RuntimeError("the scheduler planned an empty step while requests are waiting")
             t0 = time.perf_counter()
-            step = [StepEntry(e.request.request_id, e.tokens, [len(e.tokens) - 1] if e.want_last else [])
-                    for e in entries]
-            logits = self.engine.step(step)
+            logits = self._run(entries)
             sampled: Dict[Hashable, int] = {}
             wanting = [e for e in entries if e.want_last]
             if wanting:
@@ -145,6 +164,7 @@ class LLM:
                         on_token(index[r.request_id], r.output[-1])
             for rid in sched.take_releases():
                 self.engine.end(rid)
+        self._close_session()
         stats.preemptions += sched.preemptions
         from .. import ops_tc
         ops_tc.check_errors()

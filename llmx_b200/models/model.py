@@ -124,6 +124,11 @@ class Model:
         for _, part in self._parts():
             part.prepare(max_positions, device)
 
+    @property
+    def recordable(self) -> bool:
+        """Whether a decode step of this model can be recorded and replayed (every part only enqueues work)."""
+        return all(part.all_recordable() for _, part in self._parts())
+
     # -- one step ------------------------------------------------------------------
     def forward(self, step: StepBatch) -> Optional[torch.Tensor]:
         """Run the step's rows through every layer; logits [wanted, vocab] float32, or None if none is wanted."""

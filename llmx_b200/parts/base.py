@@ -52,7 +52,13 @@ class Precision:
 
 
 class Part:
-    """Base of every part: tensors by role, loaded once."""
+    """Base of every part: tensors by role, loaded once.
+
+    `recordable`: whether the part's forward only enqueues work on the stream (no host read of device
+    data), so that a decode step can be recorded in a CUDA graph.  A part that reads results on the
+    host sets it to False and is then always run step by step.
+    """
+    recordable = True
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         return {}
@@ -87,6 +93,9 @@ class Part:
         for child in self.children().values():
             child.prepare(max_positions, device)
 
+    def all_recordable(self) -> bool:
+        return self.recordable and all(c.all_recordable() for c in self.children().values())
+
 
 @dataclass
 class GroupView:
@@ -119,6 +128,7 @@ class StepBatch:
     host_row_start: List[int] = field(default_factory=list)
     host_row_count: List[int] = field(default_factory=list)
     host_history: List[int] = field(default_factory=list)
+    host_state_slots: List[int] = field(default_factory=list)
     max_row_count: int = 0
     max_context: int = 0
     extras: Dict[str, Any] = field(default_factory=dict)   # per-step scratch shared by kernels (schedules)

@@ -1,0 +1,122 @@
+"""Generation through the Python entry point and the command line."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import helpers
+import plain_qwen3 as plain
+from configs import CONFIGS
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _check_greedy(folder, prompt, tokens, bf16):
+    """Every generated token is the plain implementation's argmax given what came before (a near tie may
+    fall either way under different rounding; anything else must agree)."""
+    cfg, w = plain.load_folder(folder)
+    ids = list(prompt)
+    for t in tokens:
+        logits = plain.forward(cfg, w, ids, act_round=plain.round_bf16 if bf16 else None)[-1]
+        best = int(np.argmax(logits))
+        gap = 2e-2 if bf16 else 1e-4
+        assert t == best or logits[best] - logits[t] <= gap * np.abs(logits).max(), (len(ids), t, best)
+        ids.append(t)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "D"])
+def test_greedy_generation(model_dirs, name, dtype):
+    from llmx_b200.engine.generate import LLM
+    from llmx_b200.sampling import SamplingParams
+    d16, d32, page = model_dirs[name]
+    folder = d32 if dtype == "float32" else d16
+    vocab = CONFIGS[name][0]["vocab_size"]
+    prompts = [helpers.random_ids(vocab, n, seed=n) for n in (5, 17, 33)]
+    llm = LLM(folder, dtype=dtype, kv_tokens=256, page_size=page, ubatch=24, max_seqs=3)
+    outs = llm.generate(prompts, SamplingParams(max_tokens=16, temp=0.0, top_k=0, top_p=1.0, ignore_eos=True))
+    assert [len(o.tokens) for o in outs] == [16, 16, 16] and all(o.finish_reason == "length" for o in outs)
+    for p, o in zip(prompts, outs):
+        _check_greedy(folder, p, o.tokens, dtype == "bfloat16")
+    assert llm.engine.cache.used_pages() == [0]
+    assert llm.stats.generated_tokens == 48 and llm.stats.prompt_tokens == 55
+
+
+def test_temperature_sampling_is_reproducible_and_independent_of_the_batch(model_dirs):
+    """Four requests (prompts of 1, 9, 40 and 70 tokens) as mixed portions and decoded tokens, temperature 0.8
+    with fixed seeds: the same seeds give the same replies, and a request's reply is the one it gets alone."""
+    from llmx_b200.engine.generate import LLM
+    from llmx_b200.sampling import SamplingParams
+    _, folder, page = model_dirs["B"]
+    vocab = CONFIGS["B"][0]["vocab_size"]
+    prompts = [helpers.random_ids(vocab, n, seed=n) for n in (1, 9, 40, 70)]
+    params = [SamplingParams(max_tokens=12, temp=0.8, top_k=40, top_p=0.95, seed=100 + i, ignore_eos=True) for i in range(4)]
+    llm = LLM(folder, dtype="float32", kv_tokens=512, page_size=page, ubatch=32, max_seqs=4)
+    first = [o.tokens for o in llm.generate(prompts, params)]
+    again = [o.tokens for o in llm.generate(prompts, params)]
+    assert first == again and all(len(t) == 12 for t in first)
+    alone = [llm.generate([p], [q])[0].tokens for p, q in zip(prompts, params)]
+    assert alone == first
+    other = [o.tokens for o in llm.generate(prompts, [SamplingParams(max_tokens=12, temp=0.8, seed=7 + i, ignore_eos=True) for i in range(4)])]
+    assert other != first
+
+
+def test_end_of_sequence_and_length(model_dirs):
+    from llmx_b200.engine.generate import LLM
+    from llmx_b200.sampling import SamplingParams
+    _, folder, page = model_dirs["A"]
+    llm = LLM(folder, dtype="float32", kv_tokens=256, page_size=page)
+    prompt = helpers.random_ids(256, 9, seed=1)
+    greedy = llm.generate([prompt], SamplingParams(max_tokens=10, temp=0.0, ignore_eos=True))[0].tokens
+    # Make the third generated token the end-of-sequence id: the reply stops before it.
+    llm.engine.model.eos_ids = (greedy[2],)
+    out = llm.generate([prompt], SamplingParams(max_tokens=10, temp=0.0))[0]
+    stop_at = greedy.index(greedy[2])
+    assert out.tokens == greedy[:stop_at] and out.finish_reason == "eos"
+    masked = llm.generate([prompt], SamplingParams(max_tokens=10, temp=0.0, ignore_eos=True))[0]
+    assert greedy[2] not in masked.tokens and masked.finish_reason == "length"   # masked out of the draw
+
+
+def test_pages_running_out_pauses_and_recomputes_with_the_same_replies(model_dirs):
+    from llmx_b200.engine.generate import LLM
+    from llmx_b200.sampling import SamplingParams
+    _, folder, page = model_dirs["A"]
+    prompts = [helpers.random_ids(256, 28, seed=s) for s in range(3)]
+    params = SamplingParams(max_tokens=40, temp=0.0, ignore_eos=True)
+    roomy = LLM(folder, dtype="float32", kv_tokens=512, page_size=16, ubatch=64, max_seqs=3)
+    want = [o.tokens for o in roomy.generate(prompts, params)]
+    tight = LLM(folder, dtype="float32", kv_tokens=96, page_size=16, ubatch=64, max_seqs=3, reserve="prompt")
+    got = [o.tokens for o in tight.generate(prompts, params)]
+    assert tight.stats.preemptions > 0 and got == want
+    tight.engine.cache.check()
+    assert tight.engine.cache.used_pages() == [0]
+
+
+def test_command_line(model_dirs, tmp_path):
+    d16, _, _ = model_dirs["D"]
+    exe = [sys.executable, os.path.join(ROOT, "bin", "llmx")]
+    run = subprocess.run(exe + ["generate", d16, "5,17,3,99", "-n", "6", "--temp", "0", "--ignore-eos", "--verbose"],
+                         capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0, run.stderr[-2000:]
+    lines = run.stdout.splitlines()
+    ids = next(l for l in lines if l.startswith("ids: "))
+    assert len(ids[5:].split(",")) == 6
+    assert any(l.startswith("pp: 4 tok") for l in lines) and any(l.startswith("tg: 6 tok") for l in lines)
+    tokens = [int(t) for t in ids[5:].split(",")]
+    _check_greedy(d16, [5, 17, 3, 99], tokens, True)
+    f = tmp_path / "prompt.txt"
+    f.write_text("5 17 3 99")
+    again = subprocess.run(exe + ["generate", d16, "--file", str(f), "-n", "6", "--temp", "0", "--ignore-eos"],
+                           capture_output=True, text=True, timeout=600)
+    assert again.returncode == 0 and ids in again.stdout
+    for bad in (["generate", d16, "1,2", "--temp", "-1"], ["generate", d16, "1,2", "-n", "3", "-n", "4"],
+                ["generate", d16], ["generate", d16, "1,2", "--bogus"], ["generate", d16, "1,2", "--topp", "1.5"],
+                ["frobnicate"]):
+        r = subprocess.run(exe + bad, capture_output=True, text=True, timeout=120)
+        assert r.returncode == 2 and "usage:" in r.stderr, bad
+    bench = subprocess.run(exe + ["bench", "--model", d16, "--p", "40", "--n", "5", "--r", "1", "--seqs", "2"],
+                           capture_output=True, text=True, timeout=600)
+    assert bench.returncode == 0 and "pp40:" in bench.stdout and "tg5 x2" in bench.stdout, bench.stderr[-2000:]

@@ -1,0 +1,362 @@
+"""The parts of a layer alone, and an architecture made in this file from the framework's parts plus a
+toy mixer with state of its own, registered, built and stepped without a change to the framework.
+
+The toy model exercises what Qwen3 does not: a mixer with fixed-size per-request state, a windowed
+attention layer whose pages are given back, a partially rotated and an unrotated attention layer, a
+block that runs twice (each run with a cache entry of its own), and a block that reads the keys
+another run of it wrote.  Its plain implementation below is whole-sequence numpy built from
+tests/plain_qwen3.py's functions.
+"""
+import json
+import math
+import os
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+# ---------------------------------------------------------------------------------------------
+# A toy mixer with state: s_t = decay * s_{t-1} + h_t per request; output s_t W^T.
+def _toy_mixer_class():
+    from llmx_b200.cache import StateSpec
+    from llmx_b200.parts import Part
+    from llmx_b200.weights import TensorSpec
+
+    class RunningSumMixer(Part):
+        recordable = False          # it walks the batch on the host
+
+        def __init__(self, hidden, decay):
+            self.hidden, self.decay = hidden, decay
+
+        def cache_spec(self):
+            return StateSpec((self.hidden,), "float32")
+
+        def tensor_specs(self):
+            return {"proj.weight": TensorSpec((self.hidden, self.hidden))}
+
+        def load(self, tensors, precision):
+            super().load(tensors, precision)
+            self.weight = tensors["proj.weight"].float()
+
+        def forward(self, h, step, cache_entry, residual, write_cache=True):
+            state = step.state(cache_entry)
+            for r in range(step.requests):
+                a, n = step.host_row_start[r], step.host_row_count[r]
+                slot = step.host_state_slots[r]
+                # A request's first token reads a zero state whatever the slot holds.
+                s = state[slot].clone() if step.host_history[r] > 0 else torch.zeros(self.hidden, device=h.device)
+                outs = []
+                for t in range(n):
+                    s = self.decay * s + h[a + t].float()
+                    outs.append(s)
+                state[slot] = s
+                residual[a:a + n] += torch.stack(outs) @ self.weight.T
+
+    return RunningSumMixer
+
+
+@dataclass(frozen=True)
+class ToyConfig:
+    hidden_size: int = 64
+    intermediate_size: int = 96
+    num_attention_heads: int = 4
+    num_key_value_heads: int = 2
+    head_dim: int = 16
+    vocab_size: int = 128
+    window: int = 12
+    decay: float = 0.5
+    rms_norm_eps: float = 1e-5
+    max_position_embeddings: int = 512
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(**{k: v for k, v in raw.items() if k not in ("architectures", "model_type")})
+
+    def to_dict(self):
+        return dict(self.__dict__, architectures=["ToyForCausalLM"], model_type="toy")
+
+
+def _build_toy(cfg: ToyConfig):
+    from llmx_b200.models import LayerStep, Model
+    from llmx_b200.parts import (Attention, GatedMLP, LogitsHead, NoPositionEncoding, PreNormBlock, RMSNorm,
+                                 RotaryEmbedding, TokenEmbedding)
+    E, H, G, D = cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    norm = lambda: RMSNorm(E, cfg.rms_norm_eps)   # noqa: E731
+    mlp = lambda: GatedMLP(E, cfg.intermediate_size)   # noqa: E731
+    blocks = [
+        PreNormBlock(norm(), Attention(E, H, G, D, RotaryEmbedding(D, 10000.0, rot_dim=8), qk_norm_eps=cfg.rms_norm_eps),
+                     norm(), mlp()),                                                    # 0: partial rotation
+        PreNormBlock(norm(), _toy_mixer_class()(E, cfg.decay), norm(), mlp()),          # 1: state
+        PreNormBlock(norm(), Attention(E, H, G, D, NoPositionEncoding(), qk_norm_eps=None, window=cfg.window),
+                     norm(), mlp()),                                                    # 2: window, no rotation, no q/k norm
+    ]
+    order = [LayerStep(0, 0), LayerStep(1, 1), LayerStep(2, 2), LayerStep(0, 3), LayerStep(2, 2, write_cache=False)]
+    emb = TokenEmbedding(cfg.vocab_size, E)
+    head = LogitsHead(norm(), cfg.vocab_size, E, tied_to=emb)
+    return Model(embedding=emb, blocks=blocks, head=head, order=order, vocab_size=cfg.vocab_size,
+                 max_positions=cfg.max_position_embeddings)
+
+
+def _plain_toy(cfg: ToyConfig, w, ids):
+    """Whole sequence, no cache: the toy model's layer order written out."""
+    T, E, H, G, D = len(ids), cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    eps = cfg.rms_norm_eps
+    cos, sin = plain.rope_tables(T, 8, 10000.0)
+    x = plain.embedding(w["model.embed_tokens.weight"], ids)
+
+    def qkv(h, pre):
+        q = (h @ w[pre + "q_proj.weight"].T).reshape(T, H, D)
+        k = (h @ w[pre + "k_proj.weight"].T).reshape(T, G, D)
+        v = (h @ w[pre + "v_proj.weight"].T).reshape(T, G, D)
+        return q, k, v
+
+    def rot8(a):
+        out = a.copy()
+        out[..., :8] = plain.rope_rotate(a[..., :8], cos, sin)
+        return out
+
+    def mlp(x, pre):
+        h = plain.rms_norm(x, w[pre + "post_attention_layernorm.weight"], eps)
+        return x + plain.swiglu_ffn(h, w[pre + "mlp.gate_proj.weight"], w[pre + "mlp.up_proj.weight"], w[pre + "mlp.down_proj.weight"])
+
+    def block0(x):
+        pre = "model.layers.0."
+        h = plain.rms_norm(x, w[pre + "input_layernorm.weight"], eps)
+        q, k, v = qkv(h, pre + "self_attn.")
+        q = rot8(plain.rms_norm(q, w[pre + "self_attn.q_norm.weight"], eps))
+        k = rot8(plain.rms_norm(k, w[pre + "self_attn.k_norm.weight"], eps))
+        o = plain.attention(q, k, v).reshape(T, H * D)
+        return mlp(x + o @ w[pre + "self_attn.o_proj.weight"].T, pre)
+
+    def block1(x):
+        pre = "model.layers.1."
+        h = plain.rms_norm(x, w[pre + "input_layernorm.weight"], eps)
+        s, outs = np.zeros(E, dtype=np.float32), []
+        for t in range(T):
+            s = np.float32(cfg.decay) * s + h[t]
+            outs.append(s)
+        return mlp(x + np.stack(outs) @ w[pre + "self_attn.proj.weight"].T, pre)
+
+    def block2(x, kv=None):
+        pre = "model.layers.2."
+        h = plain.rms_norm(x, w[pre + "input_layernorm.weight"], eps)
+        q, k, v = qkv(h, pre + "self_attn.")
+        if kv is not None:
+            k, v = kv                                  # the keys and values another run of the block wrote
+        o = plain.attention(q, k, v, window=cfg.window).reshape(T, H * D)
+        return mlp(x + o @ w[pre + "self_attn.o_proj.weight"].T, pre), (k, v)
+
+    x = block0(x)
+    x = block1(x)
+    x, kv = block2(x)
+    x = block0(x)
+    x, _ = block2(x, kv)
+    h = plain.rms_norm(x, w["model.norm.weight"], eps)
+    return (h @ w["model.embed_tokens.weight"].T).astype(np.float32)
+
+
+@pytest.fixture(scope="module")
+def toy(tmp_path_factory):
+    from llmx_b200.registry import register_architecture, unregister_architecture
+    from llmx_b200.weights import RandomSource, write_safetensors
+    register_architecture(["ToyForCausalLM", "toy"], ToyConfig, _build_toy)
+    cfg = ToyConfig()
+    d = str(tmp_path_factory.mktemp("toy"))
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(cfg.to_dict(), f)
+    model = _build_toy(cfg)
+    src = RandomSource(model.tensor_specs(), 11, dtype=torch.float32, skip_optional=True)
+    tensors = {n: src.tensor(n) * (4.0 if n.endswith("proj.weight") else 1.0) for n in src.names()}
+    write_safetensors(os.path.join(d, "model.safetensors"), tensors)
+    yield cfg, d, {n: t.numpy() for n, t in tensors.items()}
+    unregister_architecture(["ToyForCausalLM", "toy"])
+
+
+def test_toy_architecture_is_registered_built_and_stepped(toy):
+    """config.json names the toy; the framework builds it from the registry and runs it under every cutting,
+    mixed with other requests, with so few pages that they are used again."""
+    from llmx_b200.engine import Engine, EngineOptions
+    cfg, folder, w = toy
+    requests = {f"t{i}": helpers.random_ids(cfg.vocab_size, n, seed=i) for i, n in enumerate([50, 3, 77, 20, 1, 64])}
+    refs = {rid: _plain_toy(cfg, w, ids) for rid, ids in requests.items()}
+    for make in (helpers.trace_whole, helpers.trace_tail_decoded, helpers.trace_portions, helpers.trace_mixed):
+        steps = make(requests)
+        engine = Engine.from_dir(folder, EngineOptions(dtype="float32", kv_tokens=helpers.tokens_needed(steps),
+                                                       page_size=4, max_requests=4))
+        assert len(engine.cache.groups) == 2 and engine.cache.state_entries == [1]
+        assert not engine.model.recordable
+        got = helpers.run_trace(engine, steps)
+        engine.cache.check()
+        assert engine.cache.used_pages() == [0, 0] and engine.cache.state_slots.free_slots == 4
+        worst = max(float(np.abs(got[(rid, p)] - refs[rid][p]).max()) for rid, ids in requests.items() for p in range(len(ids)))
+        scale = max(float(np.abs(r).max()) for r in refs.values())
+        assert worst <= 1e-4 * scale, f"{make.__name__}: {worst:.3e} (scale {scale:.3f})"
+
+
+def test_windowed_group_gives_pages_back_while_the_full_group_keeps_them(toy):
+    from llmx_b200.engine import Engine, EngineOptions, StepEntry
+    cfg, folder, w = toy
+    engine = Engine.from_dir(folder, EngineOptions(dtype="float32", kv_tokens=256, page_size=4, max_requests=2))
+    ids = helpers.random_ids(cfg.vocab_size, 100, seed=5)
+    engine.step([StepEntry("a", ids[:60], [])])
+    full = next(i for i, g in enumerate(engine.cache.groups) if g.spec.window is None)
+    assert engine.cache.used_pages()[full] == 15 * 2 // 2 and engine.cache.used_pages()[1 - full] <= 4
+    for t in ids[60:]:
+        engine.step([StepEntry("a", [t], [0])])
+        assert engine.cache.used_pages()[1 - full] <= 4
+    assert engine.cache.used_pages()[full] == 25
+
+
+# ---------------------------------------------------------------------------------------------
+# Each part of a layer alone, against the plain functions, through the same StepBatch a step builds.
+def _single_request_step(n, hidden_unused=None, history=0, page=8, kv_heads=2, head_dim=16, dtype=torch.float32, window=None):
+    from llmx_b200.cache import CacheManager, KVSpec
+    from llmx_b200.parts.base import GroupView, StepBatch
+    cache = CacheManager([KVSpec(kv_heads, head_dim, window)], page, 256, 2, kv_dtype=dtype, device=DEV)
+    rc = cache.new_request("r")
+    if history:
+        rc.prepare(history)
+        rc.commit()
+    rc.prepare(n)
+    pages = rc.tables[0].pages
+    pos = np.arange(history, history + n)
+
+    def dev(a):
+        return torch.as_tensor(np.asarray(a, dtype=np.int32)).to(DEV)
+    slots = [pages[p // page] * page + p % page for p in pos]
+    group = GroupView(dev([pages]), dev(slots), page)
+    return StepBatch(rows=n, requests=1, token_ids=dev(np.zeros(n)), positions=dev(pos), row_request=dev(np.zeros(n)),
+                     row_start=dev([0]), row_count=dev([n]), history=dev([history]), state_slots=dev([-1]),
+                     logit_rows=dev([n - 1]), groups=[group], caches=cache, host_row_start=[0], host_row_count=[n],
+                     host_history=[history], host_state_slots=[-1], max_row_count=n, max_context=history + n)
+
+
+@pytest.mark.parametrize("precision", ["float32", "bfloat16"])
+def test_rmsnorm_part(precision):
+    from llmx_b200.parts import Precision, RMSNorm
+    part = RMSNorm(96, 1e-5)
+    w = torch.rand(96) + 0.5
+    part.load({"weight": w.to(DEV)}, Precision.of(precision))
+    x = torch.randn(7, 96)
+    out = part.forward(x.to(DEV))
+    assert out.dtype is Precision.of(precision).act
+    ref = plain.rms_norm(x.numpy(), w.numpy(), 1e-5)
+    assert np.abs(out.float().cpu().numpy() - ref).max() <= (2 ** -7 if precision == "bfloat16" else 1e-5) * np.abs(ref).max()
+
+
+def test_rotary_tables_match_the_plain_ones_with_and_without_yarn():
+    from llmx_b200.config.qwen3 import YarnScaling
+    from llmx_b200.parts import RotaryEmbedding
+    for yarn in (None, dict(factor=4.0, original_max_position_embeddings=64, beta_fast=32.0, beta_slow=1.0)):
+        part = RotaryEmbedding(32, 1e6, yarn=YarnScaling(**yarn) if yarn else None)
+        part.prepare(300, DEV)
+        cos, sin = plain.rope_tables(300, 32, 1e6, yarn)
+        assert np.abs(part.cos.cpu().numpy() - cos).max() <= 1e-6 and np.abs(part.sin.cpu().numpy() - sin).max() <= 1e-6
+    with pytest.raises(ValueError):
+        RotaryEmbedding(32, 1e4, rot_dim=34)
+
+
+@pytest.mark.parametrize("precision,tol", [("float32", 1e-5), ("bfloat16", 2e-2)])
+def test_gated_mlp_part(precision, tol):
+    from llmx_b200.parts import GatedMLP, Precision
+    p = Precision.of(precision)
+    E, F = 96, 200
+    part = GatedMLP(E, F)
+    g = torch.Generator().manual_seed(0)
+    w = {n: (torch.randn(s, generator=g) * 0.1).to(p.act) for n, s in
+         (("gate_proj.weight", (F, E)), ("up_proj.weight", (F, E)), ("down_proj.weight", (E, F)))}
+    part.load({n: t.to(DEV) for n, t in w.items()}, p)
+    for rows in (3, 100):          # few rows: separate activation kernel; many rows (bfloat16): the gated product
+        h = torch.randn(rows, E, generator=g).to(p.act)
+        x = torch.randn(rows, E, generator=g)
+        res = x.clone().to(DEV)
+        part.forward(h.to(DEV), None, res)
+        rnd = plain.round_bf16 if precision == "bfloat16" else None
+        ref = x.numpy() + plain.swiglu_ffn(h.float().numpy(), *(w[n].float().numpy() for n in w), act_round=rnd)
+        assert np.abs(res.cpu().numpy() - ref).max() <= tol * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("precision,tol", [("float32", 2e-5), ("bfloat16", 3e-2)])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(4, 2, 16, None), (6, 2, 64, None), (4, 4, 64, 9)])
+def test_attention_part_in_two_portions(precision, tol, heads, kv_heads, head_dim, window):
+    """The mixer alone: a first portion fills the cache, a second reads it; together they equal the whole sequence."""
+    from llmx_b200.parts import Attention, Precision, RotaryEmbedding
+    p = Precision.of(precision)
+    E = 64
+    part = Attention(E, heads, kv_heads, head_dim, RotaryEmbedding(head_dim, 10000.0), qk_norm_eps=1e-6, window=window)
+    g = torch.Generator().manual_seed(1)
+    w = {n: (torch.randn(s.shape, generator=g) * (0.2 if s.kind == "matrix" else 0.1) + (0 if s.kind == "matrix" else 1)).to(p.act if s.kind == "matrix" else torch.float32)
+         for n, s in part.tensor_specs().items()}
+    part.load({n: t.to(DEV) for n, t in w.items()}, p)
+    part.prepare(128, DEV)
+    T, cut = 37, 21
+    h = torch.randn(T, E, generator=g).to(p.act)
+    x = torch.zeros(T, E)
+    step1 = _single_request_step(cut, kv_heads=kv_heads, head_dim=head_dim, dtype=p.act, page=16 if head_dim == 64 else 8, window=window)
+    res1 = x[:cut].clone().to(DEV)
+    part.forward(h[:cut].to(DEV), step1, 0, res1)
+    rc = step1.caches.live["r"]
+    rc.commit()
+    page = step1.groups[0].page_size
+    rc.prepare(T - cut)
+    from llmx_b200.parts.base import GroupView
+    pages = rc.tables[0].pages
+    dev = lambda a: torch.as_tensor(np.asarray(a, dtype=np.int32)).to(DEV)   # noqa: E731
+    pos = np.arange(cut, T)
+    step2 = _single_request_step(T - cut, kv_heads=kv_heads, head_dim=head_dim, dtype=p.act, page=page, window=window)
+    step2.caches = step1.caches
+    step2.groups = [GroupView(dev([pages]), dev([pages[q // page] * page + q % page for q in pos]), page)]
+    step2.positions, step2.history, step2.host_history = dev(pos), dev([cut]), [cut]
+    res2 = x[cut:].clone().to(DEV)
+    part.forward(h[cut:].to(DEV), step2, 0, res2)
+    got = torch.cat([res1, res2]).cpu().numpy()
+    cfg = dict(num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim, rms_norm_eps=1e-6)
+    cos, sin = plain.rope_tables(T, head_dim, 10000.0)
+    wf = {"p." + n: t.float().numpy() for n, t in w.items()}
+    ref = plain.attention_block(h.float().numpy(), wf, "p.", cfg, cos, sin,
+                                act_round=plain.round_bf16 if precision == "bfloat16" else None, window=window)
+    assert np.abs(got - ref).max() <= tol * np.abs(ref).max()
+
+
+def test_embedding_and_tied_head_parts():
+    from llmx_b200.parts import LogitsHead, Precision, RMSNorm, TokenEmbedding
+    p = Precision.of("float32")
+    emb = TokenEmbedding(50, 24)
+    table = torch.randn(50, 24)
+    emb.load({"weight": table.to(DEV)}, p)
+    head = LogitsHead(RMSNorm(24, 1e-6), 50, 24, tied_to=emb)
+    head.norm.load({"weight": torch.ones(24, device=DEV)}, p)
+    head.load({}, p)
+    head.bind_tied()
+    ids = torch.tensor([3, 49, 0, 7], dtype=torch.int32, device=DEV)
+    x = emb.forward(ids)
+    assert torch.equal(x.cpu(), table[ids.cpu().long()])
+    logits = head.forward(x, torch.tensor([3, 1], dtype=torch.int32, device=DEV))
+    ref = plain.rms_norm(table[[7, 49]].numpy(), np.ones(24, np.float32), 1e-6) @ table.numpy().T
+    assert head.linear.weight.data_ptr() == emb.table.data_ptr()      # tied: the same memory, not a copy
+    assert np.abs(logits.cpu().numpy() - ref).max() <= 1e-4 * np.abs(ref).max()
+
+
+def test_layer_order_is_checked():
+    from llmx_b200.models import LayerStep, Model
+    cfg = ToyConfig()
+    m = _build_toy(cfg)
+    kw = dict(embedding=m.embedding, blocks=m.blocks, head=m.head, vocab_size=cfg.vocab_size, max_positions=64)
+    with pytest.raises(ValueError, match="both write"):
+        Model(order=[LayerStep(0, 0), LayerStep(0, 0)], **kw)
+    with pytest.raises(ValueError, match="before any step wrote"):
+        Model(order=[LayerStep(0, 0, write_cache=False)], **kw)
+    with pytest.raises(ValueError, match="needs a cache entry"):
+        Model(order=[LayerStep(0, None)], **kw)
+    with pytest.raises(ValueError, match="different needs"):
+        Model(order=[LayerStep(0, 0), LayerStep(2, 0, write_cache=False)], **kw).cache_entry_specs()
+    with pytest.raises(ValueError, match="without gaps"):
+        Model(order=[LayerStep(0, 1)], **kw)
