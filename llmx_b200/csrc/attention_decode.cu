@@ -366,3 +366,42 @@ LLMX_EXPORT int llmx_attn_decode(const void* cache_map, const void* q, void* out
         default: return LLMX_ERR_UNSUPPORTED;
     }
 }
+
+// ---------------------------------------------------------------------------------------------
+// A variant of llmx_attn_decode for callers that cannot allocate device memory (declared in
+// attention_decode_static.h).  The partial results of the key ranges go to a fixed array in this
+// library's own device memory instead of a workspace the caller provides.
+// ---------------------------------------------------------------------------------------------
+#include "attention_decode_static.h"
+
+namespace {
+// Held by every GPU that loads this library, from load until the process exits.
+static __device__ __align__(256) float g_static_partial[LLMX_ATTN_DECODE_STATIC_FLOATS];
+constexpr int MAX_DEVICES = 64;
+float* g_static_partial_ptr[MAX_DEVICES] = {nullptr};
+}  // namespace
+
+LLMX_EXPORT int llmx_attn_decode_static(const void* cache_map, const void* q, void* out, const int* req_list,
+                                        int n_req, const int* row_start, const int* row_count, const int* history,
+                                        const int* block_tables, int table_stride, int total_rows, int heads,
+                                        int kv_heads, int head_dim, int page_size, int window, float scale,
+                                        int splits, int chunk_keys, int max_rows, int* error_word,
+                                        cudaStream_t stream) {
+    if (n_req <= 0) return 0;
+    if (total_rows <= 0 || heads <= 0 || splits < 1 || head_dim <= 0) return LLMX_ERR_BAD_ARGUMENT;
+    // The partial results of every (row, head, key range): refuse what the fixed array cannot hold.
+    const long long need = (long long)total_rows * heads * splits * (head_dim + 2);
+    if (splits > 1 && need > (long long)LLMX_ATTN_DECODE_STATIC_FLOATS) return LLMX_ERR_TOO_LARGE;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= MAX_DEVICES) return LLMX_ERR_BAD_ARGUMENT;
+    if (!g_static_partial_ptr[device]) {
+        // In host code the array's name is only a handle; the kernel needs its address on this device.
+        float* ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_static_partial);
+        if (e != cudaSuccess || !ptr) return e != cudaSuccess ? (int)e : LLMX_ERR_BAD_ARGUMENT;
+        g_static_partial_ptr[device] = ptr;
+    }
+    return llmx_attn_decode(cache_map, q, out, g_static_partial_ptr[device], req_list, n_req, row_start, row_count,
+                            history, block_tables, table_stride, heads, kv_heads, head_dim, page_size, window, scale,
+                            splits, nullptr, chunk_keys, max_rows, error_word, stream);
+}
