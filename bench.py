@@ -112,6 +112,8 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run one part only (for profiling); the line then holds only that part")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -218,6 +220,16 @@ def main() -> int:
             + L * 2 * cfg.num_attention_heads * cfg.head_dim * T * T + 2 * V * E
         return T * 1e3 / ms, ms, flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops"]
 
+    if args.only == "prefill":
+        pf_value, pf_ms, pf_frac = run_prefill(args.prefill_tokens, 2, 2)
+        print(json.dumps({"only": "prefill", "value": round(pf_value, 1), "ms": round(pf_ms, 3), "frac": round(pf_frac, 4),
+                          "layers": args.layers}))
+        return 0
+    if args.only == "decode":
+        value, ms, launches, _ = run_decode(args.batch, args.steps, args.warmup, e2e=False)
+        print(json.dumps({"only": "decode", "value": round(value, 1), "ms_per_step": round(ms, 4), "batch": args.batch,
+                          "context": args.context, "layers": args.layers, "gpu_launches": launches}))
+        return 0
     clocks = ClockSampler()
     clocks.start()
     value, ms, launches, _ = run_decode(args.batch, args.steps, args.warmup, e2e=False)

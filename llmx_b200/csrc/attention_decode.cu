@@ -50,9 +50,12 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
                    const int* __restrict__ row_start, const int* __restrict__ row_count,
                    const int* __restrict__ history, const int* __restrict__ block_tables, int table_stride, int heads,
                    int kv_heads, int window, float scale_log2, int splits, const int* __restrict__ chunk_ptr,
-                   int chunk_keys, int* error_word) {
+                   int chunk_keys, int* __restrict__ counters, int* error_word) {
+    pdl_trigger();
+    pdl_wait();
     using cfg = Cfg<D>;
     extern __shared__ uint8_t smem_raw[];
+    __shared__ int is_last;
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full_bar = (uint64_t*)(tiles + cfg::TILE_BYTES);
     uint64_t* empty_bar = full_bar + STAGES;
@@ -96,23 +99,29 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
         if (n_pages > 0 && tc::elect_one()) {
             tc::tma_prefetch_desc(&cache_map);
             const int* table = block_tables + (size_t)r * table_stride + kv_begin / PAGE;
+            // The page ids of a stage are read one stage ahead, so the table's latency is off the critical path.
+            int ids[PAGES_PER_STAGE], ids_next[PAGES_PER_STAGE];
+#pragma unroll
+            for (int p = 0; p < PAGES_PER_STAGE; ++p) ids_next[p] = p < n_pages ? table[p] : 0;
             for (int it = 0; it < iters; ++it) {
                 const int stage = it % STAGES;
                 const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
+#pragma unroll
+                for (int p = 0; p < PAGES_PER_STAGE; ++p) {
+                    ids[p] = ids_next[p];
+                    const int nxt = (it + 1) * PAGES_PER_STAGE + p;
+                    ids_next[p] = nxt < n_pages ? table[nxt] : 0;
+                }
                 if (!tc::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, error_word, ERR_DEC_PRODUCER)) break;
                 const int here = min(PAGES_PER_STAGE, n_pages - it * PAGES_PER_STAGE);
                 tc::mbar_expect_tx(&full_bar[stage], (uint32_t)(here * cfg::PAGE_BYTES));
-                for (int p = 0; p < here; ++p) {
-                    const int page = table[it * PAGES_PER_STAGE + p];
-                    uint8_t* dst = tiles + stage * cfg::STAGE_BYTES + p * cfg::PAGE_BYTES;
-                    const int key_row = ((page * 2 + 0) * kv_heads + g) * PAGE;
-                    const int value_row = ((page * 2 + 1) * kv_heads + g) * PAGE;
 #pragma unroll
-                    for (int b = 0; b < cfg::BOXES; ++b) {
-                        tc::tma_load_2d(dst + b * cfg::BOX_BYTES, &cache_map, b * attn::BOX_COLS, key_row, &full_bar[stage]);
-                        tc::tma_load_2d(dst + cfg::PLANE_BYTES + b * cfg::BOX_BYTES, &cache_map, b * attn::BOX_COLS,
-                                        value_row, &full_bar[stage]);
-                    }
+                for (int p = 0; p < PAGES_PER_STAGE; ++p) {
+                    if (p >= here) break;
+                    const int page = ids[p];
+                    uint8_t* dst = tiles + stage * cfg::STAGE_BYTES + p * cfg::PAGE_BYTES;
+                    // One copy brings the head's keys and values of the page: [plane][half][slot][64 columns].
+                    tc::tma_load_5d(dst, &cache_map, 0, 0, 0, g, page * 2, &full_bar[stage]);
                 }
             }
         }
@@ -277,6 +286,53 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
             }
         }
     }
+    if (splits > 1 && counters) {
+        // The block that finishes last among the key ranges of this (request, kv head) combines them.
+        // Nobody waits: each block counts itself in and only the one that sees the others' count goes on.
+        __threadfence();
+        __syncthreads();
+        int* counter = counters + (size_t)blockIdx.z * kv_heads + g;
+        if (threadIdx.x == 0) is_last = atomicAdd(counter, 1) == splits - 1;
+        __syncthreads();
+        if (is_last) {
+            __threadfence();
+            // Weights of the ranges first (rows x ranges values through shared memory), then one pass over
+            // the partial outputs with every load independent of the others.
+            float* factor = (float*)tiles;                       // [MAX_ROWS][splits]
+            for (int idx = threadIdx.x; idx < M * splits; idx += THREADS) {
+                const int row = idx / splits, s2 = idx % splits;
+                const size_t orow = (size_t)(q0 + row / ratio) * heads + g * ratio + row % ratio;
+                factor[row * splits + s2] = __ldcg(partial + (orow * splits + s2) * (D + 2) + D);
+            }
+            __syncthreads();
+            float* row_scale = factor + MAX_ROWS * splits;       // [MAX_ROWS]: 1 / l, and the rows' maxima
+            if (threadIdx.x < M) {
+                const int row = threadIdx.x;
+                const size_t orow = (size_t)(q0 + row / ratio) * heads + g * ratio + row % ratio;
+                float mm = -INFINITY;
+                for (int s2 = 0; s2 < splits; ++s2) mm = fmaxf(mm, factor[row * splits + s2]);
+                float l = 0.0f;
+                for (int s2 = 0; s2 < splits; ++s2) {
+                    const float ms = factor[row * splits + s2];
+                    const float f = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
+                    factor[row * splits + s2] = f;
+                    l += __ldcg(partial + (orow * splits + s2) * (D + 2) + D + 1) * f;
+                }
+                row_scale[row] = 1.0f / l;
+            }
+            __syncthreads();
+            for (int idx = threadIdx.x; idx < M * D; idx += THREADS) {
+                const int row = idx / D, d = idx % D;
+                const size_t out_row = (size_t)(q0 + row / ratio) * heads + g * ratio + row % ratio;
+                const float* src = partial + out_row * splits * (D + 2) + d;
+                float acc = 0.0f;
+#pragma unroll 8
+                for (int s2 = 0; s2 < splits; ++s2) acc = fmaf(__ldcg(src + (size_t)s2 * (D + 2)), factor[row * splits + s2], acc);
+                out[out_row * D + d] = __float2bfloat16_rn(acc * row_scale[row]);
+            }
+            if (threadIdx.x == 0) *counter = 0;      // ready for the next launch
+        }
+    }
 }
 
 // out[row, head, :] = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m) over the key ranges.
@@ -284,6 +340,8 @@ template <int D>
 __global__ void attn_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
                                   const int* __restrict__ req_list, const int* __restrict__ row_start,
                                   const int* __restrict__ row_count, int heads, int splits) {
+    pdl_trigger();
+    pdl_wait();
     const int r = req_list[blockIdx.z];
     if ((int)blockIdx.y >= row_count[r]) return;
     const size_t out_row = (size_t)(row_start[r] + blockIdx.y) * heads + blockIdx.x;
@@ -309,7 +367,7 @@ template <int D>
 int launch(const CUtensorMap& map, const void* q, void* out, float* partial, const int* req_list, int n_req,
            const int* row_start, const int* row_count, const int* history, const int* block_tables, int table_stride,
            int heads, int kv_heads, int window, float scale, int splits, const int* chunk_ptr, int chunk_keys,
-           int max_rows, int* error_word, cudaStream_t stream) {
+           int max_rows, int* counters, int* error_word, cudaStream_t stream) {
     using cfg = Cfg<D>;
     static bool configured = false;
     if (!configured) {
@@ -319,15 +377,15 @@ int launch(const CUtensorMap& map, const void* q, void* out, float* partial, con
         configured = true;
     }
     dim3 grid(splits, kv_heads, n_req);
-    attn_decode_kernel<D><<<grid, THREADS, cfg::SMEM_BYTES, stream>>>(
+    launch_kernel(attn_decode_kernel<D>, grid, dim3(THREADS), cfg::SMEM_BYTES, stream,
         map, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, partial, req_list, row_start, row_count, history,
         block_tables, table_stride, heads, kv_heads, window, scale * attn::LOG2E, splits, chunk_ptr, chunk_keys,
-        error_word);
+        counters, error_word);
     int e = launch_status();
-    if (e || splits == 1) return e;
+    if (e || splits == 1 || counters) return e;
     dim3 mgrid(heads, max_rows, n_req);
-    attn_merge_kernel<D><<<mgrid, D < 128 ? D : 128, 0, stream>>>(partial, (__nv_bfloat16*)out, req_list, row_start,
-                                                               row_count, heads, splits);
+    launch_kernel(attn_merge_kernel<D>, mgrid, dim3(D < 128 ? D : 128), 0, stream, (const float*)partial,
+                  (__nv_bfloat16*)out, req_list, row_start, row_count, heads, splits);
     return launch_status();
 }
 
@@ -337,34 +395,49 @@ int launch(const CUtensorMap& map, const void* q, void* out, float* partial, con
 LLMX_EXPORT int llmx_attn_cache_map(void* out, const void* cache, long long pages, int kv_heads, int page_size,
                                     int head_dim) {
     if (head_dim % attn::BOX_COLS || page_size != PAGE || ((uintptr_t)cache & 15)) return LLMX_ERR_UNSUPPORTED;
-    return llmx_make_cache_map((CUtensorMap*)out, cache, (uint64_t)pages * 2 * kv_heads * page_size, (uint64_t)head_dim,
-                               (uint32_t)page_size);
+    return llmx_make_cache_map((CUtensorMap*)out, cache, (uint64_t)pages, (uint64_t)kv_heads, (uint32_t)page_size,
+                               (uint64_t)head_dim);
 }
 
 // Attention for the requests req_list[0..n_req): each brings row_count[r] rows (at most 16 / (heads / kv_heads))
 // starting at row row_start[r] of q/out [rows, heads, head_dim]; history[r] keys precede them.
 // Key ranges: `splits` ranges of `chunk` keys (a multiple of 64; read from chunk_ptr on the device when given).
 // `partial` (float32, rows * heads * splits * (head_dim + 2)) is needed when splits > 1.
-LLMX_EXPORT int llmx_attn_decode(const void* cache_map, const void* q, void* out, float* partial, const int* req_list,
-                                 int n_req, const int* row_start, const int* row_count, const int* history,
-                                 const int* block_tables, int table_stride, int heads, int kv_heads, int head_dim,
-                                 int page_size, int window, float scale, int splits, const int* chunk_ptr,
-                                 int chunk_keys, int max_rows, int* error_word, cudaStream_t stream) {
+// `counters` (optional): n_req * kv_heads ints, zero before the first use and left zero by every launch; with
+// them the block that finishes a (request, kv head) last combines its key ranges and no second kernel runs.
+LLMX_EXPORT int llmx_attn_decode_fused(const void* cache_map, const void* q, void* out, float* partial,
+                                       const int* req_list, int n_req, const int* row_start, const int* row_count,
+                                       const int* history, const int* block_tables, int table_stride, int heads,
+                                       int kv_heads, int head_dim, int page_size, int window, float scale, int splits,
+                                       const int* chunk_ptr, int chunk_keys, int max_rows, int* counters,
+                                       int* error_word, cudaStream_t stream) {
     if (n_req <= 0) return 0;
     if (page_size != PAGE || heads % kv_heads || heads / kv_heads > MAX_ROWS || splits < 1 || n_req > 65535 ||
         kv_heads > 65535 || (chunk_keys % 64) || max_rows < 1 || max_rows * (heads / kv_heads) > MAX_ROWS)
         return LLMX_ERR_UNSUPPORTED;
     if (splits > 1 && !partial) return LLMX_ERR_BAD_ARGUMENT;
+    if (counters && splits > 256) return LLMX_ERR_UNSUPPORTED;     // the ranges' weights go through shared memory
     const CUtensorMap& map = *(const CUtensorMap*)cache_map;
     switch (head_dim) {
         case 64: return launch<64>(map, q, out, partial, req_list, n_req, row_start, row_count, history, block_tables,
                                    table_stride, heads, kv_heads, window, scale, splits, chunk_ptr, chunk_keys, max_rows,
-                                   error_word, stream);
+                                   counters, error_word, stream);
         case 128: return launch<128>(map, q, out, partial, req_list, n_req, row_start, row_count, history, block_tables,
                                      table_stride, heads, kv_heads, window, scale, splits, chunk_ptr, chunk_keys,
-                                     max_rows, error_word, stream);
+                                     max_rows, counters, error_word, stream);
         default: return LLMX_ERR_UNSUPPORTED;
     }
+}
+
+// The same with a second kernel combining the key ranges (no counters needed).
+LLMX_EXPORT int llmx_attn_decode(const void* cache_map, const void* q, void* out, float* partial, const int* req_list,
+                                 int n_req, const int* row_start, const int* row_count, const int* history,
+                                 const int* block_tables, int table_stride, int heads, int kv_heads, int head_dim,
+                                 int page_size, int window, float scale, int splits, const int* chunk_ptr,
+                                 int chunk_keys, int max_rows, int* error_word, cudaStream_t stream) {
+    return llmx_attn_decode_fused(cache_map, q, out, partial, req_list, n_req, row_start, row_count, history,
+                                  block_tables, table_stride, heads, kv_heads, head_dim, page_size, window, scale, splits,
+                                  chunk_ptr, chunk_keys, max_rows, nullptr, error_word, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

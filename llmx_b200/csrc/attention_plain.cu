@@ -22,6 +22,8 @@ attention_plain_kernel(const QT* __restrict__ q, const KVT* __restrict__ cache, 
                        const int* __restrict__ row_request, const int* __restrict__ positions,
                        const int* __restrict__ block_tables, int table_stride, int heads, int kv_heads, int head_dim,
                        int page_size, int window, float scale) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float smem[];  // WARPS * (head_dim + 2)
     const int row = blockIdx.x, h = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -101,11 +103,11 @@ LLMX_EXPORT int llmx_attention_plain(const void* q, const void* cache, void* out
     dim3 grid(rows, heads);
     const size_t shmem = (size_t)WARPS * (head_dim + 2) * sizeof(float);
     if (dtype == LLMX_BF16)
-        attention_plain_kernel<<<grid, WARPS * 32, shmem, stream>>>(
+        launch_kernel(attention_plain_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(WARPS * 32), shmem, stream, 
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, row_request, positions,
             block_tables, table_stride, heads, kv_heads, head_dim, page_size, window, scale);
     else
-        attention_plain_kernel<<<grid, WARPS * 32, shmem, stream>>>(
+        launch_kernel(attention_plain_kernel<float, float>, dim3(grid), dim3(WARPS * 32), shmem, stream, 
             (const float*)q, (const float*)cache, (float*)out, row_request, positions, block_tables, table_stride,
             heads, kv_heads, head_dim, page_size, window, scale);
     return launch_status();

@@ -46,6 +46,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bf
                     const int* __restrict__ row_start, const int* __restrict__ row_count,
                     const int* __restrict__ history, const int* __restrict__ block_tables, int table_stride,
                     int heads, int kv_heads, int window, float scale_log2, int tokens_per_tile, int* error_word) {
+    pdl_trigger();
+    pdl_wait();
     using cfg = Cfg<D>;
     const int r = req_list[blockIdx.z], g = blockIdx.y;
     const int n_q = row_count[r];
@@ -86,23 +88,29 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bf
             tc::tma_prefetch_desc(&cache_map);
             const int* table = block_tables + (size_t)r * table_stride + kv_begin / PAGE;
             const int n_pages = (kv_end - kv_begin + PAGE - 1) / PAGE;
+            // The page ids of a stage are read one stage ahead, so the table's latency is off the critical path.
+            int ids[PAGES_PER_STAGE], ids_next[PAGES_PER_STAGE];
+#pragma unroll
+            for (int p = 0; p < PAGES_PER_STAGE; ++p) ids_next[p] = p < n_pages ? table[p] : 0;
             for (int it = 0; it < iters; ++it) {
                 const int stage = it % STAGES;
                 const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
+#pragma unroll
+                for (int p = 0; p < PAGES_PER_STAGE; ++p) {
+                    ids[p] = ids_next[p];
+                    const int nxt = (it + 1) * PAGES_PER_STAGE + p;
+                    ids_next[p] = nxt < n_pages ? table[nxt] : 0;
+                }
                 if (!tc::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, error_word, ERR_PRE_PRODUCER)) break;
                 const int here = min(PAGES_PER_STAGE, n_pages - it * PAGES_PER_STAGE);
                 tc::mbar_expect_tx(&full_bar[stage], (uint32_t)(here * cfg::PAGE_BYTES));
-                for (int p = 0; p < here; ++p) {
-                    const int page = table[it * PAGES_PER_STAGE + p];
-                    uint8_t* dst = tiles + stage * cfg::STAGE_BYTES + p * cfg::PAGE_BYTES;
-                    const int key_row = ((page * 2 + 0) * kv_heads + g) * PAGE;
-                    const int value_row = ((page * 2 + 1) * kv_heads + g) * PAGE;
 #pragma unroll
-                    for (int b = 0; b < cfg::BOXES; ++b) {
-                        tc::tma_load_2d(dst + b * cfg::BOX_BYTES, &cache_map, b * attn::BOX_COLS, key_row, &full_bar[stage]);
-                        tc::tma_load_2d(dst + cfg::PLANE_BYTES + b * cfg::BOX_BYTES, &cache_map, b * attn::BOX_COLS,
-                                        value_row, &full_bar[stage]);
-                    }
+                for (int p = 0; p < PAGES_PER_STAGE; ++p) {
+                    if (p >= here) break;
+                    const int page = ids[p];
+                    uint8_t* dst = tiles + stage * cfg::STAGE_BYTES + p * cfg::PAGE_BYTES;
+                    // One copy brings the head's keys and values of the page: [plane][half][slot][64 columns].
+                    tc::tma_load_5d(dst, &cache_map, 0, 0, 0, g, page * 2, &full_bar[stage]);
                 }
             }
         }
@@ -277,7 +285,7 @@ int launch(const CUtensorMap& map, const void* q, void* out, const int* req_list
     const int ratio = heads / kv_heads;
     const int tokens_per_tile = ROWS / ratio;
     dim3 grid((max_rows + tokens_per_tile - 1) / tokens_per_tile, kv_heads, n_req);
-    attn_prefill_kernel<D><<<grid, THREADS, cfg::SMEM_BYTES, stream>>>(
+    launch_kernel(attn_prefill_kernel<D>, grid, dim3(THREADS), cfg::SMEM_BYTES, stream,
         map, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, req_list, row_start, row_count, history, block_tables,
         table_stride, heads, kv_heads, window, scale * attn::LOG2E, tokens_per_tile, error_word);
     return launch_status();

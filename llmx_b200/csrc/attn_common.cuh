@@ -41,9 +41,23 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 }  // namespace attn
 
-// A cache [pages, 2, kv_heads, page_size, head_dim] seen as rows of head_dim bfloat16, in boxes of
-// [page_size rows, 64 columns].  Row of (page, plane, head, slot) = ((page * 2 + plane) * kv_heads + head) * page_size + slot.
-static inline int llmx_make_cache_map(CUtensorMap* map, const void* cache, uint64_t rows, uint64_t head_dim,
-                                      uint32_t page_size) {
-    return llmx_make_map_bf16_2d(map, cache, rows, head_dim, page_size, attn::BOX_COLS);
+// A cache [pages, 2, kv_heads, page_size, head_dim] (bfloat16) as a five-dimensional tensor
+//   (column in a 64-wide half: 64) x (slot: page_size) x (half of the head: head_dim / 64) x (kv head) x (page * 2 + plane)
+// so that one box {64, page_size, head_dim / 64, 1, 2} is everything one kv head needs of one page: its keys
+// and its values.  In shared memory the box lies as [plane][half][slot][64 columns]: per plane and half one
+// run of page_size rows of 128 bytes under the 128-byte swizzle.
+static inline int llmx_make_cache_map(CUtensorMap* map, const void* cache, uint64_t pages, uint64_t kv_heads,
+                                      uint32_t page_size, uint64_t head_dim) {
+    llmx_encode_tiled_fn enc = llmx_encode_tiled();
+    if (!enc) return 10003;
+    const uint64_t halves = head_dim / attn::BOX_COLS;
+    const cuuint64_t dims[5] = {(cuuint64_t)attn::BOX_COLS, page_size, halves, kv_heads, pages * 2};
+    const cuuint64_t strides[4] = {head_dim * 2, (cuuint64_t)attn::BOX_COLS * 2, (cuuint64_t)page_size * head_dim * 2,
+                                   kv_heads * page_size * head_dim * 2};
+    const cuuint32_t box[5] = {(cuuint32_t)attn::BOX_COLS, page_size, (cuuint32_t)halves, 1, 2};
+    const cuuint32_t elem[5] = {1, 1, 1, 1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), dims, strides, box, elem,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 10003;
 }

@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define LLMX_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -50,3 +51,39 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
+
+// ---- programmatic dependent launch --------------------------------------------------------------
+// Kernels of a step run one after another on one stream.  Launched with the "programmatic stream
+// serialization" attribute, a kernel's blocks may be placed on the SMs and run their prologue (barriers,
+// tensor memory, descriptor prefetch) while the kernel before it drains.  The rule every kernel here
+// keeps: `pdl_trigger()` first (the next kernel may start arriving), then `pdl_wait()` before the first
+// access to global memory another kernel writes or reads.  `pdl_wait()` returns only when the kernel
+// before has finished and its writes are visible, so nothing after it can race; without the attribute
+// both are no-ops.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+static inline bool llmx_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("LLMX_PDL");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = llmx_pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}

@@ -14,6 +14,8 @@ constexpr int BM = 64, BN = 64, BK = 16;
 template <typename AT, typename WT>
 __global__ void __launch_bounds__(256) gemm_plain_kernel(const AT* __restrict__ A, const WT* __restrict__ W,
                                                          float* __restrict__ C, int M, int N, int K, int accumulate) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -71,9 +73,9 @@ LLMX_EXPORT int llmx_gemm_plain(const void* A, int a_dtype, const void* W, int w
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) return LLMX_ERR_UNSUPPORTED;
     if (a_dtype == LLMX_F32 && w_dtype == LLMX_F32)
-        gemm_plain_kernel<<<grid, 256, 0, stream>>>((const float*)A, (const float*)W, C, M, N, K, accumulate);
+        launch_kernel(gemm_plain_kernel<float, float>, dim3(grid), dim3(256), 0, stream, (const float*)A, (const float*)W, C, M, N, K, accumulate);
     else if (a_dtype == LLMX_BF16 && w_dtype == LLMX_BF16)
-        gemm_plain_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)A, (const __nv_bfloat16*)W, C, M, N, K, accumulate);
+        launch_kernel(gemm_plain_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(256), 0, stream, (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, C, M, N, K, accumulate);
     else
         return LLMX_ERR_UNSUPPORTED;
     return launch_status();

@@ -45,7 +45,11 @@ struct Cfg {
     static constexpr int A_BYTES = BM * BK * 2;          // one weight tile
     static constexpr int B_BYTES = BN * BK * 2;          // token tile
     static constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
-    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
+    // Narrow token tiles (few tokens: the product streams weights) take half an SM's shared memory, so two
+    // blocks share an SM and one's prologue and epilogue hide behind the other's loads; wide tiles take it all.
+    static constexpr int CTAS_PER_SM = BN <= 64 ? 2 : 1;
+    static constexpr int BUDGET = (BN <= 64 ? 100 : 200) * 1024;
+    static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 8 ? 8 : (BUDGET / STAGE_BYTES);
     static constexpr int ACC_COLS = A_TILES * BN;        // columns of one accumulator set
     static constexpr int TMEM_COLS = (2 * ACC_COLS) < 32 ? 32 : (2 * ACC_COLS);
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
@@ -103,6 +107,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                void* __restrict__ C_, int M, int N, int K, int mode, int splits, int* error_word) {
     using cfg = Cfg<BN, DUAL>;
+    pdl_trigger();      // the next kernel's blocks may start arriving; they wait for this one to finish
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* tiles = smem;
@@ -140,6 +145,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __syncthreads();
     tc::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Barriers, tensor memory and descriptors are ready; everything from here on touches memory other
+    // kernels write, so the kernel before must have finished.
+    pdl_wait();
 
     if (warp == 0) {
         if (tc::elect_one()) {
@@ -238,17 +246,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     } else {
                         tc::tmem_wait_ld();
                         if (n < N) {
-                            float* C = (float*)C_;
+                            float* C = (float*)C_ + (size_t)(w.mt * BN + c) * N + n;
+                            const int m_left = M - (w.mt * BN + c);        // rows of this chunk inside the matrix
+                            if (atomic) {
 #pragma unroll
-                            for (int j = 0; j < CH; ++j) {
-                                const int m = w.mt * BN + c + j;
-                                if (m < M) {
-                                    float* dst = C + (size_t)m * N + n;
-                                    const float v = __uint_as_float(r[j]);
-                                    if (atomic) atomicAdd(dst, v);
-                                    else if (mode == MODE_STORE) *dst = v;
-                                    else *dst += v;
-                                }
+                                for (int j = 0; j < CH; ++j)
+                                    if (j < m_left) atomicAdd(C + (size_t)j * N, __uint_as_float(r[j]));
+                            } else if (mode == MODE_STORE) {
+#pragma unroll
+                                for (int j = 0; j < CH; ++j)
+                                    if (j < m_left) C[(size_t)j * N] = __uint_as_float(r[j]);
+                            } else {
+                                // All of the chunk's old values are requested before the first is used: one
+                                // memory round trip per chunk, not one per row.
+                                float old[CH];
+#pragma unroll
+                                for (int j = 0; j < CH; ++j) old[j] = j < m_left ? __ldcg(C + (size_t)j * N) : 0.0f;
+#pragma unroll
+                                for (int j = 0; j < CH; ++j)
+                                    if (j < m_left) C[(size_t)j * N] = old[j] + __uint_as_float(r[j]);
                             }
                         }
                     }
@@ -292,9 +308,9 @@ int launch(const CUtensorMap& map_w, const void* A, void* C, int M, int N, int K
     } else {
         grid = (long long)n_tiles * m_tiles * splits;
     }
-    if (grid > g_sm_count) grid = g_sm_count;
+    if (grid > (long long)g_sm_count * cfg::CTAS_PER_SM) grid = (long long)g_sm_count * cfg::CTAS_PER_SM;
     if (grid < 1) grid = 1;
-    gemm_tc_kernel<BN, STREAMK, DUAL><<<(unsigned)grid, THREADS, cfg::SMEM_BYTES, stream>>>(
+    launch_kernel(gemm_tc_kernel<BN, STREAMK, DUAL>, dim3((unsigned)grid), dim3(THREADS), cfg::SMEM_BYTES, stream, 
         map_w, map_a, C, M, N, K, mode, splits, error_word);
     return launch_status();
 }

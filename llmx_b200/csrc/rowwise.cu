@@ -13,6 +13,8 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ x,
                              int width, int table_rows) {
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     const int id = ids[r];
     float* dst = x + (size_t)r * width;
@@ -28,9 +30,9 @@ LLMX_EXPORT int llmx_embed(const void* table, int table_dtype, const int* ids, f
                            int table_rows, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (table_dtype == LLMX_BF16)
-        embed_kernel<<<rows, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, x, width, table_rows);
+        launch_kernel(embed_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, (const __nv_bfloat16*)table, ids, x, width, table_rows);
     else
-        embed_kernel<<<rows, 256, 0, stream>>>((const float*)table, ids, x, width, table_rows);
+        launch_kernel(embed_kernel<float>, dim3(rows), dim3(256), 0, stream, (const float*)table, ids, x, width, table_rows);
     return launch_status();
 }
 
@@ -43,6 +45,8 @@ LLMX_EXPORT int llmx_embed(const void* table, int table_dtype, const int* ids, f
 template <typename OutT>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, OutT* __restrict__ y,
                                const int* __restrict__ row_index, int width, float eps) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const float* src = x + (size_t)(row_index ? row_index[r] : r) * width;
@@ -72,11 +76,23 @@ __device__ __forceinline__ void store4(__nv_bfloat16* dst, float a, float b, flo
     *reinterpret_cast<uint2*>(dst) = v;
 }
 
+// `zero` (optional): a float buffer of `zero_count` values (a multiple of 4, 16-byte aligned) that the launch
+// clears, shared out over its blocks: the output of the product that follows, when that product adds its
+// pieces with atomics.
 template <typename OutT>
 __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, OutT* __restrict__ y,
-                                   const int* __restrict__ row_index, int width, float eps) {
+                                   const int* __restrict__ row_index, int width, float eps, float* __restrict__ zero,
+                                   long long zero_count) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
+    if (zero) {
+        float4* z = reinterpret_cast<float4*>(zero);
+        const long long n4 = zero_count >> 2;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x)
+            z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     const float4* src = reinterpret_cast<const float4*>(x + (size_t)(row_index ? row_index[r] : r) * width);
     const float4* wv = reinterpret_cast<const float4*>(w);
     const int n4 = width >> 2;
@@ -108,8 +124,9 @@ __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __r
 }
 
 LLMX_EXPORT int llmx_rmsnorm(const float* x, const float* w, void* y, int out_dtype, const int* row_index, int rows,
-                             int width, float eps, cudaStream_t stream) {
+                             int width, float eps, float* zero, long long zero_count, cudaStream_t stream) {
     if (rows <= 0) return 0;
+    if (zero && (zero_count % 4 || ((uintptr_t)zero & 15))) return LLMX_ERR_BAD_ARGUMENT;
     const bool aligned = width % 4 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)w & 15) && !((uintptr_t)y & 15);
     if (aligned && width <= 4 * NORM_VEC_MAX * 256) {
         const int n4 = width / 4;
@@ -117,16 +134,17 @@ LLMX_EXPORT int llmx_rmsnorm(const float* x, const float* w, void* y, int out_dt
         int threads = ((n4 + 3) / 4 + 31) / 32 * 32;
         threads = threads < 32 ? 32 : threads > 256 ? 256 : threads;
         if (out_dtype == LLMX_BF16)
-            rmsnorm_vec_kernel<<<rows, threads, 0, stream>>>(x, w, (__nv_bfloat16*)y, row_index, width, eps);
+            launch_kernel(rmsnorm_vec_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, x, w, (__nv_bfloat16*)y, row_index, width, eps, zero, zero_count);
         else
-            rmsnorm_vec_kernel<<<rows, threads, 0, stream>>>(x, w, (float*)y, row_index, width, eps);
+            launch_kernel(rmsnorm_vec_kernel<float>, dim3(rows), dim3(threads), 0, stream, x, w, (float*)y, row_index, width, eps, zero, zero_count);
         return launch_status();
     }
+    if (zero && cudaMemsetAsync(zero, 0, (size_t)zero_count * sizeof(float), stream) != cudaSuccess) return launch_status();
     const int threads = width >= 1024 ? 256 : 128;
     if (out_dtype == LLMX_BF16)
-        rmsnorm_kernel<<<rows, threads, 0, stream>>>(x, w, (__nv_bfloat16*)y, row_index, width, eps);
+        launch_kernel(rmsnorm_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, x, w, (__nv_bfloat16*)y, row_index, width, eps);
     else
-        rmsnorm_kernel<<<rows, threads, 0, stream>>>(x, w, (float*)y, row_index, width, eps);
+        launch_kernel(rmsnorm_kernel<float>, dim3(rows), dim3(threads), 0, stream, x, w, (float*)y, row_index, width, eps);
     return launch_status();
 }
 
@@ -150,6 +168,8 @@ __global__ void head_norm_rope_kernel(const float* __restrict__ qkv, int qkv_str
                                       int rot_half, const int* __restrict__ positions, const int* __restrict__ slots,
                                       QT* __restrict__ q_out, KVT* __restrict__ cache, int rows, int heads, int kv_heads,
                                       int head_dim, int page_size) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int per_row = heads + kv_heads;
@@ -206,6 +226,68 @@ __global__ void head_norm_rope_kernel(const float* __restrict__ qkv, int qkv_str
     }
 }
 
+// The same for the common shape -- a head of 128 values rotated whole (64 pairs) -- with each lane holding
+// four consecutive values (16-byte loads, 8-byte stores); a pair's partner sits 16 lanes away.
+template <typename QT, typename KVT>
+__global__ void head_norm_rope_128_kernel(const float* __restrict__ qkv, int qkv_stride, int k_offset, int v_offset,
+                                          const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+                                          float eps, const float* __restrict__ cos_table,
+                                          const float* __restrict__ sin_table, const int* __restrict__ positions,
+                                          const int* __restrict__ slots, QT* __restrict__ q_out, KVT* __restrict__ cache,
+                                          int rows, int heads, int kv_heads, int page_size) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int D = 128;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int per_row = heads + kv_heads;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (item >= (long long)rows * per_row) return;
+    const int row = (int)(item / per_row), j = (int)(item % per_row);
+    const bool is_q = j < heads;
+    const int g = is_q ? 0 : j - heads;
+    int slot = 0;
+    if (!is_q) {
+        slot = slots[row];
+        if (slot < 0) return;
+    }
+    const float* src = qkv + (size_t)row * qkv_stride + (is_q ? j * D : k_offset + g * D);
+    const float* weight = is_q ? q_weight : k_weight;
+    float4 v = reinterpret_cast<const float4*>(src)[lane];
+    if (weight) {
+        float s = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
+        s = warp_sum(s);
+        const float rr = 1.0f / sqrtf(s / (float)D + eps);
+        const float4 w4 = reinterpret_cast<const float4*>(weight)[lane];
+        v.x *= rr * w4.x; v.y *= rr * w4.y; v.z *= rr * w4.z; v.w *= rr * w4.w;
+    }
+    if (cos_table) {
+        // Lane l < 16 holds a = x[4l..4l+3], lane l + 16 holds b = x[64 + 4l ..]; both need cos/sin[4 (l % 16) ..].
+        const size_t base = (size_t)positions[row] * 64 + 4 * (lane & 15);
+        const float4 c = *reinterpret_cast<const float4*>(cos_table + base);
+        const float4 sn = *reinterpret_cast<const float4*>(sin_table + base);
+        float4 o;
+        o.x = __shfl_xor_sync(0xffffffffu, v.x, 16); o.y = __shfl_xor_sync(0xffffffffu, v.y, 16);
+        o.z = __shfl_xor_sync(0xffffffffu, v.z, 16); o.w = __shfl_xor_sync(0xffffffffu, v.w, 16);
+        if (lane < 16) {        // a' = fma(-b, sin, a cos)
+            v.x = fmaf(-o.x, sn.x, v.x * c.x); v.y = fmaf(-o.y, sn.y, v.y * c.y);
+            v.z = fmaf(-o.z, sn.z, v.z * c.z); v.w = fmaf(-o.w, sn.w, v.w * c.w);
+        } else {                // b' = fma(a, sin, b cos)
+            v.x = fmaf(o.x, sn.x, v.x * c.x); v.y = fmaf(o.y, sn.y, v.y * c.y);
+            v.z = fmaf(o.z, sn.z, v.z * c.z); v.w = fmaf(o.w, sn.w, v.w * c.w);
+        }
+    }
+    if (is_q) {
+        store4(q_out + ((size_t)row * heads + j) * D + 4 * lane, v.x, v.y, v.z, v.w);
+    } else {
+        const int page = slot / page_size, off = slot % page_size;
+        const size_t key_base = ((((size_t)page * 2 + 0) * kv_heads + g) * page_size + off) * D;
+        const size_t value_base = ((((size_t)page * 2 + 1) * kv_heads + g) * page_size + off) * D;
+        store4(cache + key_base + 4 * lane, v.x, v.y, v.z, v.w);
+        const float4 vv = reinterpret_cast<const float4*>(qkv + (size_t)row * qkv_stride + v_offset + g * D)[lane];
+        store4(cache + value_base + 4 * lane, vv.x, vv.y, vv.z, vv.w);
+    }
+}
+
 LLMX_EXPORT int llmx_head_norm_rope_kv(const float* qkv, int qkv_stride, int k_offset, int v_offset,
                                        const float* q_weight, const float* k_weight, float eps,
                                        const float* cos_table, const float* sin_table, int rot_half,
@@ -217,13 +299,28 @@ LLMX_EXPORT int llmx_head_norm_rope_kv(const float* qkv, int qkv_stride, int k_o
     const int warps = 4;
     const long long items = (long long)rows * (heads + kv_heads);
     const unsigned blocks = (unsigned)((items + warps - 1) / warps);
+    const bool fast = head_dim == 128 && (!cos_table || rot_half == 64) && qkv_stride % 4 == 0 && k_offset % 4 == 0 &&
+                      v_offset % 4 == 0 && !((uintptr_t)qkv & 15) && !((uintptr_t)q_out & 15) && !((uintptr_t)cache & 15) &&
+                      !((uintptr_t)q_weight & 15) && !((uintptr_t)k_weight & 15) && !((uintptr_t)cos_table & 15) &&
+                      !((uintptr_t)sin_table & 15);
+    if (fast) {
+        if (q_dtype == LLMX_BF16)
+            launch_kernel(head_norm_rope_128_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(blocks), dim3(warps * 32), 0, stream, 
+                qkv, qkv_stride, k_offset, v_offset, q_weight, k_weight, eps, cos_table, sin_table, positions, slots,
+                (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, rows, heads, kv_heads, page_size);
+        else
+            launch_kernel(head_norm_rope_128_kernel<float, float>, dim3(blocks), dim3(warps * 32), 0, stream, 
+                qkv, qkv_stride, k_offset, v_offset, q_weight, k_weight, eps, cos_table, sin_table, positions, slots,
+                (float*)q_out, (float*)cache, rows, heads, kv_heads, page_size);
+        return launch_status();
+    }
     const size_t shmem = (size_t)warps * head_dim * sizeof(float);
     if (q_dtype == LLMX_BF16)
-        head_norm_rope_kernel<<<blocks, warps * 32, shmem, stream>>>(
+        launch_kernel(head_norm_rope_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(blocks), dim3(warps * 32), shmem, stream, 
             qkv, qkv_stride, k_offset, v_offset, q_weight, k_weight, eps, cos_table, sin_table, rot_half, positions,
             slots, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, rows, heads, kv_heads, head_dim, page_size);
     else
-        head_norm_rope_kernel<<<blocks, warps * 32, shmem, stream>>>(
+        launch_kernel(head_norm_rope_kernel<float, float>, dim3(blocks), dim3(warps * 32), shmem, stream, 
             qkv, qkv_stride, k_offset, v_offset, q_weight, k_weight, eps, cos_table, sin_table, rot_half, positions,
             slots, (float*)q_out, (float*)cache, rows, heads, kv_heads, head_dim, page_size);
     return launch_status();
@@ -236,6 +333,8 @@ LLMX_EXPORT int llmx_head_norm_rope_kv(const float* qkv, int qkv_stride, int k_o
 // ---------------------------------------------------------------------------
 template <typename OutT>
 __global__ void swiglu_kernel(const float* __restrict__ gu, OutT* __restrict__ act, long long total, int width) {
+    pdl_trigger();
+    pdl_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long long r = i / width;
@@ -248,7 +347,7 @@ LLMX_EXPORT int llmx_swiglu(const float* gu, void* act, int out_dtype, int rows,
     const long long total = (long long)rows * width;
     if (total <= 0) return 0;
     const unsigned blocks = (unsigned)((total + 255) / 256);
-    if (out_dtype == LLMX_BF16) swiglu_kernel<<<blocks, 256, 0, stream>>>(gu, (__nv_bfloat16*)act, total, width);
-    else swiglu_kernel<<<blocks, 256, 0, stream>>>(gu, (float*)act, total, width);
+    if (out_dtype == LLMX_BF16) launch_kernel(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, gu, (__nv_bfloat16*)act, total, width);
+    else launch_kernel(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, gu, (float*)act, total, width);
     return launch_status();
 }

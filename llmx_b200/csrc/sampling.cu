@@ -228,6 +228,8 @@ __device__ double total_weight(const float* row, int n, const Sets& sets, float 
 
 __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict__ logits, int vocab,
                                                          const RowParams* __restrict__ params, int* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ Shared sh;
     const float* row = logits + (size_t)blockIdx.x * vocab;
     const RowParams p = params[blockIdx.x];
@@ -367,6 +369,8 @@ __global__ void penalty_kernel(float* __restrict__ logits, int vocab, const int*
                                const int* __restrict__ token, const int* __restrict__ count,
                                const float* __restrict__ repetition, const float* __restrict__ presence,
                                const float* __restrict__ frequency, int items) {
+    pdl_trigger();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= items) return;
     const int r = row_of[i], t = token[i];
@@ -386,7 +390,7 @@ LLMX_EXPORT int llmx_sample(const float* logits, int rows, int vocab, const void
                             cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return LLMX_ERR_BAD_ARGUMENT;
-    sample_kernel<<<rows, THREADS, 0, stream>>>(logits, vocab, (const RowParams*)params, out);
+    launch_kernel(sample_kernel, dim3(rows), dim3(THREADS), 0, stream, logits, vocab, (const RowParams*)params, out);
     return launch_status();
 }
 
@@ -394,7 +398,7 @@ LLMX_EXPORT int llmx_penalize(float* logits, int vocab, const int* row_of, const
                               const float* repetition, const float* presence, const float* frequency, int items,
                               cudaStream_t stream) {
     if (items <= 0) return 0;
-    penalty_kernel<<<(items + 255) / 256, 256, 0, stream>>>(logits, vocab, row_of, token, count, repetition, presence,
-                                                          frequency, items);
+    launch_kernel(penalty_kernel, dim3((items + 255) / 256), dim3(256), 0, stream, logits, vocab, row_of, token, count,
+                  repetition, presence, frequency, items);
     return launch_status();
 }

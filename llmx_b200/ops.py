@@ -80,7 +80,7 @@ def _check(status: int, what: str, launches: int = 1) -> None:
 _i, _f, _p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 _SIGNATURES = {
     ("rowwise", "llmx_embed"): [_p, _i, _p, _p, _i, _i, _i, _p],
-    ("rowwise", "llmx_rmsnorm"): [_p, _p, _p, _i, _p, _i, _i, _f, _p],
+    ("rowwise", "llmx_rmsnorm"): [_p, _p, _p, _i, _p, _i, _i, _f, _p, ctypes.c_longlong, _p],
     ("rowwise", "llmx_head_norm_rope_kv"): [_p, _i, _i, _i, _p, _p, _f, _p, _p, _i, _p, _p, _p, _i, _p, _i,
                                             _i, _i, _i, _i, _i, _p],
     ("rowwise", "llmx_swiglu"): [_p, _p, _i, _i, _i, _p],
@@ -118,9 +118,14 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Te
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-            row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[i] = x[row_index[i] or i] * (rsqrt(mean x^2 + eps) * weight); x float32, out float32 or bfloat16."""
-    _cuda(x, weight, out, row_index)
+            row_index: Optional[torch.Tensor] = None, zero: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[i] = x[row_index[i] or i] * (rsqrt(mean x^2 + eps) * weight); x float32, out float32 or bfloat16.
+
+    `zero` (optional): a float32 tensor the same launch clears (the output of a product that follows and
+    adds its pieces with atomics)."""
+    _cuda(x, weight, out, row_index, zero)
+    if zero is not None:
+        _need(zero.dtype == torch.float32 and zero.numel() % 4 == 0, "rmsnorm: the buffer to clear must be float32, a multiple of 4 long")
     rows, width = out.shape
     _need(x.dtype == torch.float32 and weight.dtype == torch.float32, "rmsnorm: input and weight must be float32")
     _need(x.dim() == 2 and x.shape[1] == width and weight.numel() == width, "rmsnorm: widths do not fit")
@@ -129,7 +134,8 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
     else:
         _need(row_index.dtype == torch.int32 and row_index.numel() == rows, "rmsnorm: row_index must be int32 per row")
     _check(_fn("rowwise", "llmx_rmsnorm")(_ptr(x), _ptr(weight), _ptr(out), _code(out), _ptr(row_index), rows, width,
-                                          float(eps), _stream()), "rmsnorm")
+                                          float(eps), _ptr(zero), 0 if zero is None else zero.numel(), _stream()),
+           "rmsnorm")
     return out
 
 

@@ -18,12 +18,14 @@ _i, _p, _f, _ll = ctypes.c_int, ctypes.c_void_p, ctypes.c_float, ctypes.c_longlo
 register_signature("attention_decode", "llmx_attn_cache_map", [_p, _p, _ll, _i, _i, _i])
 register_signature("attention_decode", "llmx_attn_decode",
                    [_p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p, _i, _i, _p, _p])
+register_signature("attention_decode", "llmx_attn_decode_fused",
+                   [_p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p, _i, _i, _p, _p, _p])
 register_signature("attention_prefill", "llmx_attn_prefill",
                    [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p])
 
 PAGE = 16
-TARGET_BLOCKS = 148 * 4          # decode blocks wanted in flight: two per SM, two waves
-MIN_KEYS_PER_SPLIT = 256
+WAVE_BLOCKS = 148 * 2            # decode blocks that run at once: two per SM
+MIN_KEYS_PER_SPLIT = 1024        # below this a range's fixed cost (start-up, combining) outweighs what it saves
 
 
 def supported(heads: int, kv_heads: int, head_dim: int, page_size: int) -> bool:
@@ -43,6 +45,19 @@ class CacheMap:
 
 
 _maps: Dict[int, CacheMap] = {}
+_counters: Dict[int, torch.Tensor] = {}
+MAX_COUNTERS = 65536
+
+
+def _counter_buffer(device) -> torch.Tensor:
+    """Ints (one per request and kv head) the decode kernel's blocks count themselves into; every launch
+    leaves them zero."""
+    idx = torch.device(device).index or 0
+    c = _counters.get(idx)
+    if c is None:
+        c = torch.zeros(MAX_COUNTERS, dtype=torch.int32, device=device)
+        _counters[idx] = c
+    return c
 
 
 def cache_map(cache: torch.Tensor) -> CacheMap:
@@ -54,9 +69,11 @@ def cache_map(cache: torch.Tensor) -> CacheMap:
 
 
 def decode_schedule(n_requests: int, kv_heads: int, max_context: int) -> Tuple[int, int]:
-    """(key ranges, keys per range) so that a decode launch has about TARGET_BLOCKS blocks."""
+    """(key ranges, keys per range): as many ranges as fit one wave of blocks, none shorter than
+    MIN_KEYS_PER_SPLIT keys (measured on a B200: 1 request at 8,192 keys is fastest with 8-9 ranges, 8 requests
+    with 3-4, 64 requests with 1)."""
     blocks = max(n_requests * kv_heads, 1)
-    splits = max(1, min(-(-TARGET_BLOCKS // blocks), -(-max_context // MIN_KEYS_PER_SPLIT)))
+    splits = max(1, min(WAVE_BLOCKS // blocks, max_context // MIN_KEYS_PER_SPLIT))
     chunk = -(-(-(-max_context // 64)) // splits) * 64
     splits = max(1, -(-max_context // chunk))
     return splits, chunk
@@ -108,11 +125,12 @@ def paged_attention_bf16(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
                 partial = torch.empty((q.shape[0] * heads * splits * (head_dim + 2),), dtype=torch.float32,
                                       device=q.device)
                 step.extras[key] = partial
-        _check(_fn("attention_decode", "llmx_attn_decode")(
+        counters = _counter_buffer(q.device) if splits > 1 and n_small * kv_heads <= MAX_COUNTERS else None
+        _check(_fn("attention_decode", "llmx_attn_decode_fused")(
             ctypes.c_void_p(cmap.address), _ptr(q), _ptr(out), _ptr(partial), _ptr(small), n_small,
             _ptr(step.row_start), _ptr(step.row_count), _ptr(step.history), _ptr(tables), tables.shape[1], heads,
             kv_heads, head_dim, cache.shape[3], win, float(scale), splits, _ptr(chunk_ptr), chunk, max(rows_small, 1),
-            _ptr(err), _stream()), "attention_decode", 2 if splits > 1 else 1)
+            _ptr(counters), _ptr(err), _stream()), "attention_decode", 2 if splits > 1 and counters is None else 1)
     if n_large:
         _check(_fn("attention_prefill", "llmx_attn_prefill")(
             ctypes.c_void_p(cmap.address), _ptr(q), _ptr(out), _ptr(large), n_large, _ptr(step.row_start),

@@ -69,11 +69,17 @@ class Attention(Part):
     def prepare(self, max_positions: int, device) -> None:
         self.position_encoding.prepare(max_positions, device)
 
+    def wants_cleared(self, rows: int, device) -> Optional[torch.Tensor]:
+        """A buffer this mixer wants zeroed before `forward` (the norm before it clears it in passing)."""
+        self._qkv_out = self.qkv.output_to_clear(rows, device)
+        return self._qkv_out
+
     def forward(self, h: torch.Tensor, step: StepBatch, cache_entry: int, residual: torch.Tensor,
                 write_cache: bool = True) -> None:
         rows = h.shape[0]
         group, cache = step.kv(cache_entry)
-        qkv = self.qkv(h)
+        out, self._qkv_out = getattr(self, "_qkv_out", None), None
+        qkv = self.qkv(h, out=out, cleared=out is not None) if out is not None and out.shape[0] == rows else self.qkv(h)
         q = torch.empty((rows, self.q_width), dtype=self.precision.act, device=h.device)
         pe = self.position_encoding
         slots = group.slots

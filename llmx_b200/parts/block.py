@@ -26,7 +26,11 @@ class PreNormBlock(Part):
 
     def forward(self, x: torch.Tensor, step: StepBatch, cache_entry: Optional[int], write_cache: bool = True) -> None:
         """x: the float32 residual stream [rows, hidden], updated in place."""
-        h = self.mixer_norm.forward(x)
+        rows = x.shape[0]
+        # A part may ask for a buffer to be zeroed before it runs; the norm in front of it does that in passing.
+        clear = getattr(self.mixer, "wants_cleared", None)
+        h = self.mixer_norm.forward(x, zero=clear(rows, x.device) if clear else None)
         self.mixer.forward(h, step, cache_entry, x, write_cache)
-        h = self.ffn_norm.forward(x)
+        clear = getattr(self.ffn, "wants_cleared", None)
+        h = self.ffn_norm.forward(x, zero=clear(rows, x.device) if clear else None)
         self.ffn.forward(h, step, x)

@@ -28,8 +28,10 @@ class Linear:
         self.tensor_core = precision.act is torch.bfloat16 and self.in_features % 8 == 0
         self._tc = None
 
-    def __call__(self, a: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
-        """out (+)= a @ W.T; a [rows, in] of the path's activation type; out float32 [rows, out]."""
+    def __call__(self, a: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False,
+                 cleared: bool = False) -> torch.Tensor:
+        """out (+)= a @ W.T; a [rows, in] of the path's activation type; out float32 [rows, out].
+        `cleared`: `out` already holds zeros (see `output_to_clear`)."""
         if out is None:
             if accumulate:
                 raise ValueError("accumulate needs an output to add to")
@@ -38,8 +40,24 @@ class Linear:
             from .. import ops_tc
             if self._tc is None:
                 self._tc = ops_tc.WeightMap(self.weight)
-            return ops_tc.gemm_tc(a, self.weight, out, accumulate, wmap=self._tc)
+            return ops_tc.gemm_tc(a, self.weight, out, accumulate or cleared and self.adds_pieces(a.shape[0]),
+                                  wmap=self._tc)
         return ops.gemm_plain(a, self.weight, out, accumulate)
+
+    def adds_pieces(self, rows: int) -> bool:
+        """Whether the product for this many rows adds its pieces into the output with atomics, which then
+        must start from zeros when the product is to be stored."""
+        if not self.tensor_core:
+            return False
+        from .. import ops_tc
+        return ops_tc._schedule(rows, self.out_features) == 1
+
+    def output_to_clear(self, rows: int, device) -> Optional[torch.Tensor]:
+        """A fresh output for `rows` rows if the product wants it cleared by whoever runs before it
+        (then pass it back with `cleared=True`), else None."""
+        if not self.adds_pieces(rows) or (rows * self.out_features) % 4:
+            return None
+        return torch.empty((rows, self.out_features), dtype=torch.float32, device=device)
 
     def gated(self, a: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """out = silu(a @ Wg.T) * (a @ Wu.T) for a weight that stacks gate rows on up rows, in one kernel

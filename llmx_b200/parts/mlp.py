@@ -34,10 +34,18 @@ class GatedMLP(Part):
         self.gate_up = Linear(torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0), precision)
         self.down = Linear(tensors["down_proj.weight"], precision)
 
+    def wants_cleared(self, rows: int, device):
+        """A buffer this part wants zeroed before `forward` (the norm before it clears it in passing)."""
+        self._gu_out = None if self.gate_up.fused_gate(rows) else self.gate_up.output_to_clear(rows, device)
+        return self._gu_out
+
     def forward(self, h: torch.Tensor, step: StepBatch, residual: torch.Tensor) -> None:
         act = torch.empty((h.shape[0], self.intermediate), dtype=self.precision.act, device=h.device)
+        out, self._gu_out = getattr(self, "_gu_out", None), None
         if self.gate_up.fused_gate(h.shape[0]):
             self.gate_up.gated(h, act)
+        elif out is not None and out.shape[0] == h.shape[0]:
+            ops.swiglu(self.gate_up(h, out=out, cleared=True), act)
         else:
             ops.swiglu(self.gate_up(h), act)
         self.down(act, out=residual, accumulate=True)

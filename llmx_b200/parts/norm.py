@@ -27,8 +27,10 @@ class RMSNorm(Part):
         self.weight = tensors["weight"].to(torch.float32).contiguous()
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
-                row_index: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+                row_index: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+                zero: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """`zero`: a float32 buffer the part that follows wants cleared; the norm's launch clears it on the way."""
         rows = x.shape[0] if row_index is None else row_index.numel()
         if out is None:
             out = torch.empty((rows, self.width), dtype=out_dtype or self.precision.act, device=x.device)
-        return ops.rmsnorm(x, self.weight, self.eps, out, row_index)
+        return ops.rmsnorm(x, self.weight, self.eps, out, row_index, zero)
