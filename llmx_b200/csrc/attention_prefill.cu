@@ -2,7 +2,8 @@
 //
 // A block serves one (request, kv head, tile of new rows): `tokens_per_tile` consecutive new rows
 // times the `ratio` query heads of the group make up to 128 query rows, 16 per consumer warp, that
-// share the keys and values streamed through shared memory:
+// share the keys and values streamed through shared memory (measured: eight consumer warps in one
+// block per SM beat four in each of two blocks, 32.9 against 34.9 ms for a 36-layer 2,048-token step):
 //
 //   producer warp     fetches the request's pages with TMA (boxes of [16 slots, 64 columns],
 //                     128-byte swizzle), 64 keys a stage, three stages in flight
