@@ -40,6 +40,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "gemm_tc": ["gemm_tc.cu"],
     "attention_decode": ["attention_decode.cu"],
     "attention_prefill": ["attention_prefill.cu"],
+    "attention_prefill_tc": ["attention_prefill_tc.cu"],
     "sampling": ["sampling.cu"],
 }
 

@@ -20,6 +20,9 @@ register_signature("attention_decode", "llmx_attn_decode",
                    [_p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p, _i, _i, _p, _p])
 register_signature("attention_decode", "llmx_attn_decode_fused",
                    [_p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p, _i, _i, _p, _p, _p])
+register_signature("attention_prefill_tc", "llmx_attn_prefill_tc_cache_map", [_p, _p, _ll, _i, _i, _i])
+register_signature("attention_prefill_tc", "llmx_attn_prefill_tc",
+                   [_p, _p, _p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p])
 register_signature("attention_prefill", "llmx_attn_prefill",
                    [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p])
 
@@ -42,6 +45,34 @@ class CacheMap:
         pages, _, kv_heads, page_size, head_dim = cache.shape
         _check(_fn("attention_decode", "llmx_attn_cache_map")(ctypes.c_void_p(self.address), _ptr(cache), pages,
                                                               kv_heads, page_size, head_dim), "attention cache map", 0)
+
+
+class CacheHalfMap:
+    """The descriptor the tcgen05 prefill kernel reads the same storage through (boxes of half a page-head)."""
+
+    def __init__(self, cache: torch.Tensor):
+        self.cache = cache
+        self._raw = ctypes.create_string_buffer(128 + 64)
+        self.address = (ctypes.addressof(self._raw) + 63) & ~63
+        pages, _, kv_heads, page_size, head_dim = cache.shape
+        _check(_fn("attention_prefill_tc", "llmx_attn_prefill_tc_cache_map")(
+            ctypes.c_void_p(self.address), _ptr(cache), pages, kv_heads, page_size, head_dim), "attention cache map", 0)
+
+
+_half_maps: Dict[int, CacheHalfMap] = {}
+
+
+def cache_half_map(cache: torch.Tensor) -> CacheHalfMap:
+    m = _half_maps.get(cache.data_ptr())
+    if m is None or m.cache.shape != cache.shape:
+        m = CacheHalfMap(cache)
+        _half_maps[cache.data_ptr()] = m
+    return m
+
+
+def tensor_core_prefill(heads: int, kv_heads: int, head_dim: int, page_size: int) -> bool:
+    """Whether prompt portions run the tcgen05 kernel (head width 128, a head ratio dividing 128)."""
+    return head_dim == 128 and page_size == PAGE and heads % kv_heads == 0 and 128 % (heads // kv_heads) == 0
 
 
 _maps: Dict[int, CacheMap] = {}
@@ -131,7 +162,13 @@ def paged_attention_bf16(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
             _ptr(step.row_start), _ptr(step.row_count), _ptr(step.history), _ptr(tables), tables.shape[1], heads,
             kv_heads, head_dim, cache.shape[3], win, float(scale), splits, _ptr(chunk_ptr), chunk, max(rows_small, 1),
             _ptr(counters), _ptr(err), _stream()), "attention_decode", 2 if splits > 1 and counters is None else 1)
-    if n_large:
+    if n_large and tensor_core_prefill(heads, kv_heads, head_dim, cache.shape[3]) and not step.extras.get("no_tc_attention"):
+        hmap = cache_half_map(cache)
+        _check(_fn("attention_prefill_tc", "llmx_attn_prefill_tc")(
+            ctypes.c_void_p(hmap.address), _ptr(q), _ptr(out), q.shape[0], _ptr(large), n_large, _ptr(step.row_start),
+            _ptr(step.row_count), _ptr(step.history), _ptr(tables), tables.shape[1], heads, kv_heads, head_dim,
+            cache.shape[3], win, float(scale), rows_large, _ptr(err), _stream()), "attention_prefill_tc")
+    elif n_large:
         _check(_fn("attention_prefill", "llmx_attn_prefill")(
             ctypes.c_void_p(cmap.address), _ptr(q), _ptr(out), _ptr(large), n_large, _ptr(step.row_start),
             _ptr(step.row_count), _ptr(step.history), _ptr(tables), tables.shape[1], heads, kv_heads, head_dim,
