@@ -11,7 +11,8 @@
 //               MN-major operand of P V, so neither is transposed)
 //   warp 1      allocates tensor memory (two S and two P V accumulators, 512 columns) and issues the
 //               products: Q K^T of tile j + 1 goes out before P V of tile j, so the tensor core works
-//               while tile j's softmax runs
+//               while tile j's softmax runs; P has two buffers too, so tile j + 1's P is written while
+//               P V of tile j reads its own
 //   warps 2-9   two threads per query row, each with 64 of the row's 128 columns: read S from tensor
 //               memory (tcgen05.ld), mask (causal, window), online softmax in float32 (base 2; the two
 //               halves of a row exchange their maxima through shared memory), write P as bfloat16
@@ -39,8 +40,8 @@ constexpr int THREADS = 64 + SOFTMAX_WARPS * 32;
 constexpr int HALF_BYTES = 128 * 128;     // 128 rows of 128 bytes: one 64-column half of an operand
 constexpr int OPERAND_BYTES = 2 * HALF_BYTES;
 constexpr int STAGE_BYTES = 2 * OPERAND_BYTES;                      // keys, then values
-constexpr int SMEM_Q = 0, SMEM_P = OPERAND_BYTES, SMEM_KV = 2 * OPERAND_BYTES;
-constexpr int SMEM_TILES = SMEM_KV + KV_STAGES * STAGE_BYTES;       // 196,608 bytes
+constexpr int SMEM_Q = 0, SMEM_P = OPERAND_BYTES, SMEM_KV = 3 * OPERAND_BYTES;    // Q, two P buffers, then the stages
+constexpr int SMEM_TILES = SMEM_KV + KV_STAGES * STAGE_BYTES;       // 229,376 bytes
 constexpr int SMEM_BYTES = SMEM_TILES + 1024 + 256 + 2 * ROWS * 4;   // + the rows' maxima of both column halves
 constexpr uint32_t TMEM_COLS = 512;
 enum : int { ERR_TCA_PRODUCER = 401, ERR_TCA_MMA = 402, ERR_TCA_SOFTMAX = 403 };
@@ -57,6 +58,13 @@ __device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t smem_addr, uint3
            (1ull << 46) | (2ull << 61);
 }
 
+// 2^x in one instruction; -inf gives 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap cache_map,
                        __nv_bfloat16* __restrict__ out, const int* __restrict__ req_list,
@@ -69,14 +77,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     uint64_t* bars = (uint64_t*)(smem + SMEM_TILES);
     uint64_t* q_full = bars;                 // [1]
     uint64_t* kv_full = bars + 1;            // [2]
-    uint64_t* kv_empty = bars + 3;           // [2]
+    uint64_t* k_empty = bars + 3;            // [2]  keys of a stage are free once Q K^T has read them
     uint64_t* s_full = bars + 5;             // [2]
     uint64_t* s_empty = bars + 7;            // [2]
     uint64_t* o_full = bars + 9;             // [2]
     uint64_t* o_empty = bars + 11;           // [2]
-    uint64_t* p_full = bars + 13;            // [1]
-    uint64_t* p_empty = bars + 14;           // [1]
-    uint32_t* tmem_slot = (uint32_t*)(bars + 15);
+    uint64_t* p_full = bars + 13;            // [2]
+    uint64_t* p_empty = bars + 15;           // [2]
+    uint64_t* v_empty = bars + 17;           // [2]  values of a stage are free once P V has read them
+    uint64_t* k_full = bars + 19;            // [2]
+    uint32_t* tmem_slot = (uint32_t*)(bars + 21);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     float* half_max = (float*)(smem + SMEM_TILES + 256);         // [2][ROWS]
 
@@ -87,15 +97,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     if (threadIdx.x == 0) {
         tc::mbar_init(q_full, 1);
         for (int i = 0; i < 2; ++i) {
-            tc::mbar_init(&kv_full[i], 1);
-            tc::mbar_init(&kv_empty[i], 1);
+            tc::mbar_init(&kv_full[i], 1);      // values
+            tc::mbar_init(&k_full[i], 1);       // keys
+            tc::mbar_init(&k_empty[i], 1);
+            tc::mbar_init(&v_empty[i], 1);
+            tc::mbar_init(&p_full[i], SOFTMAX_WARPS);
+            tc::mbar_init(&p_empty[i], 1);
             tc::mbar_init(&s_full[i], 1);
             tc::mbar_init(&s_empty[i], SOFTMAX_WARPS);
             tc::mbar_init(&o_full[i], 1);
             tc::mbar_init(&o_empty[i], SOFTMAX_WARPS);
         }
-        tc::mbar_init(p_full, SOFTMAX_WARPS);
-        tc::mbar_init(p_empty, 1);
         *abort_flag = 0;
         tc::fence_barrier_init();
         tc::tma_prefetch_desc(&q_map);
@@ -141,22 +153,42 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             tc::tma_load_5d(smem + SMEM_Q, &q_map, 0, 0, q0 + t0, 0, g, q_full);
             const int* table = block_tables + (size_t)r * table_stride + kv_begin / PAGE;
             const int n_pages = (kv_end - kv_begin + PAGE - 1) / PAGE;
+            // The page ids of a stage are read one stage ahead (the copies' memory clobber keeps the compiler from
+            // moving loads across them, and a table load is a round trip to L2 the copies must not wait for).
+            int ids[PAGES_PER_STAGE], ids_next[PAGES_PER_STAGE];
+#pragma unroll
+            for (int p = 0; p < PAGES_PER_STAGE; ++p) ids_next[p] = p < n_pages ? table[p] : 0;
             for (int j = 0; j < n_iter; ++j) {
                 const int st = j % KV_STAGES;
-                if (!tc::mbar_wait(&kv_empty[st], ((uint32_t)(j / KV_STAGES) & 1u) ^ 1u, abort_flag, error_word,
-                                   ERR_TCA_PRODUCER))
-                    break;
+                const uint32_t ph = ((uint32_t)(j / KV_STAGES) & 1u) ^ 1u;
                 const int here = min(PAGES_PER_STAGE, n_pages - j * PAGES_PER_STAGE);
-                tc::mbar_expect_tx(&kv_full[st], (uint32_t)(here * 2 * PAGE * D * 2));
                 uint8_t* kbase = smem + SMEM_KV + st * STAGE_BYTES;
-                for (int p = 0; p < here; ++p) {
-                    const int page = table[j * PAGES_PER_STAGE + p];
 #pragma unroll
-                    for (int plane = 0; plane < 2; ++plane)
+                for (int p = 0; p < PAGES_PER_STAGE; ++p) {
+                    ids[p] = ids_next[p];
+                    const int nxt = (j + 1) * PAGES_PER_STAGE + p;
+                    ids_next[p] = nxt < n_pages ? table[nxt] : 0;
+                }
+                // Keys first (their slot is free as soon as Q K^T of the tile two back has run), then values.
+                if (!tc::mbar_wait(&k_empty[st], ph, abort_flag, error_word, ERR_TCA_PRODUCER)) break;
+                tc::mbar_expect_tx(&k_full[st], (uint32_t)(here * PAGE * D * 2));
 #pragma unroll
-                        for (int half = 0; half < 2; ++half)
-                            tc::tma_load_5d(kbase + plane * OPERAND_BYTES + half * HALF_BYTES + p * PAGE * 128, &cache_map,
-                                            0, 0, half, g, page * 2 + plane, &kv_full[st]);
+                for (int p = 0; p < PAGES_PER_STAGE; ++p) {
+                    if (p >= here) break;
+#pragma unroll
+                    for (int half = 0; half < 2; ++half)
+                        tc::tma_load_5d(kbase + half * HALF_BYTES + p * PAGE * 128, &cache_map, 0, 0, half, g, ids[p] * 2,
+                                        &k_full[st]);
+                }
+                if (!tc::mbar_wait(&v_empty[st], ph, abort_flag, error_word, ERR_TCA_PRODUCER)) break;
+                tc::mbar_expect_tx(&kv_full[st], (uint32_t)(here * PAGE * D * 2));
+#pragma unroll
+                for (int p = 0; p < PAGES_PER_STAGE; ++p) {
+                    if (p >= here) break;
+#pragma unroll
+                    for (int half = 0; half < 2; ++half)
+                        tc::tma_load_5d(kbase + OPERAND_BYTES + half * HALF_BYTES + p * PAGE * 128, &cache_map, 0, 0, half,
+                                        g, ids[p] * 2 + 1, &kv_full[st]);
                 }
             }
         }
@@ -166,24 +198,25 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             const uint32_t q_addr = tc::smem_u32(smem + SMEM_Q), p_addr = tc::smem_u32(smem + SMEM_P);
             auto issue_pv = [&](int i) -> bool {
                 const int bi = i & 1, st = i % KV_STAGES;
-                if (!tc::mbar_wait(p_full, (uint32_t)i & 1u, abort_flag, error_word, ERR_TCA_MMA)) return false;
+                if (!tc::mbar_wait(&kv_full[st], (uint32_t)(i / KV_STAGES) & 1u, abort_flag, error_word, ERR_TCA_MMA)) return false;
+                if (!tc::mbar_wait(&p_full[bi], (uint32_t)(i / 2) & 1u, abort_flag, error_word, ERR_TCA_MMA)) return false;
                 if (!tc::mbar_wait(&o_empty[bi], ((uint32_t)(i / 2) & 1u) ^ 1u, abort_flag, error_word, ERR_TCA_MMA)) return false;
                 tc::tc_fence_after();
                 const uint32_t v_addr = tc::smem_u32(smem + SMEM_KV + st * STAGE_BYTES + OPERAND_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < KEYS / 16; ++kk) {
-                    const uint64_t da = tc::smem_desc_k_sw128(p_addr + (kk >> 2) * HALF_BYTES + (kk & 3) * 32);
+                    const uint64_t da = tc::smem_desc_k_sw128(p_addr + bi * OPERAND_BYTES + (kk >> 2) * HALF_BYTES + (kk & 3) * 32);
                     const uint64_t db = smem_desc_mn_sw128(v_addr + kk * 16 * 128, HALF_BYTES);
                     tc::mma_bf16_ss(tmem_base + 2 * KEYS + bi * D, da, db, IDESC_PV, kk > 0 ? 1u : 0u);
                 }
                 tc::mma_commit(&o_full[bi]);
-                tc::mma_commit(p_empty);
-                tc::mma_commit(&kv_empty[st]);
+                tc::mma_commit(&p_empty[bi]);
+                tc::mma_commit(&v_empty[st]);
                 return true;
             };
             for (int j = 0; j < n_iter && ok; ++j) {
                 const int b = j & 1, st = j % KV_STAGES;
-                ok = tc::mbar_wait(&kv_full[st], (uint32_t)(j / KV_STAGES) & 1u, abort_flag, error_word, ERR_TCA_MMA) &&
+                ok = tc::mbar_wait(&k_full[st], (uint32_t)(j / KV_STAGES) & 1u, abort_flag, error_word, ERR_TCA_MMA) &&
                      tc::mbar_wait(&s_empty[b], ((uint32_t)(j / 2) & 1u) ^ 1u, abort_flag, error_word, ERR_TCA_MMA);
                 if (!ok) break;
                 tc::tc_fence_after();
@@ -195,6 +228,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                                     tc::smem_desc_k_sw128(k_addr + off), IDESC_QK, kk > 0 ? 1u : 0u);
                 }
                 tc::mma_commit(&s_full[b]);
+                tc::mma_commit(&k_empty[st]);
                 if (j >= 1) ok = issue_pv(j - 1);
             }
             if (ok) issue_pv(n_iter - 1);
@@ -240,7 +274,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             if (ok) ok = tc::mbar_wait(&s_full[b], (uint32_t)(j / 2) & 1u, abort_flag, error_word, ERR_TCA_SOFTMAX);
             tc::tc_fence_after();
             const bool need_mask = key0 + HC - 1 > pos || key0 < lo;
-            // ---- this half's scores (kept in registers) and their maximum
+            // ---- this half's raw scores (kept in registers) and their maximum; masked ones become -inf.
+            // The scale is positive, so it is applied after the maximum and folded into the exponent's
+            // multiply-add: one instruction per score here, three in the pass below.
             float sc[HC];
             float rowmax = -INFINITY;
             if (ok) {
@@ -249,18 +285,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     uint32_t v[32];
                     tc::tmem_ld_32x32(tmem_base + b * KEYS + half * HC + c + lane_addr, v);
                     tc::tmem_wait_ld();
+                    if (need_mask) {
 #pragma unroll
-                    for (int k = 0; k < 32; ++k) {
-                        float sv = __uint_as_float(v[k]) * scale_log2;
-                        if (need_mask) {
+                        for (int k = 0; k < 32; ++k) {
                             const int key = key0 + c + k;
-                            if (key > pos || key < lo) sv = -INFINITY;
+                            sc[c + k] = (key > pos || key < lo) ? -INFINITY : __uint_as_float(v[k]);
+                            rowmax = fmaxf(rowmax, sc[c + k]);
                         }
-                        sc[c + k] = sv;
-                        rowmax = fmaxf(rowmax, sv);
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 32; ++k) {
+                            sc[c + k] = __uint_as_float(v[k]);
+                            rowmax = fmaxf(rowmax, sc[c + k]);
+                        }
                     }
                 }
             }
+            rowmax *= scale_log2;
             // S has been read: the tensor core may write the tile after next into it.
             tc::tc_fence_before();
             __syncwarp();
@@ -276,16 +317,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             const float base = m_new == -INFINITY ? 0.0f : m_new;
             m_run = m_new;
             // ---- P = 2^(s - m) as bfloat16 into the operand layout; P V of the tile before must have read P
-            ok = tc::mbar_wait(p_empty, ((uint32_t)j & 1u) ^ 1u, abort_flag, error_word, ERR_TCA_SOFTMAX);
+            ok = tc::mbar_wait(&p_empty[b], ((uint32_t)(j / 2) & 1u) ^ 1u, abort_flag, error_word, ERR_TCA_SOFTMAX);
             if (!ok) continue;
             float rowsum = 0.0f;
-            uint8_t* p_row = smem + SMEM_P + half * HALF_BYTES + row * 128;
+            uint8_t* p_row = smem + SMEM_P + b * OPERAND_BYTES + half * HALF_BYTES + row * 128;
 #pragma unroll
             for (int c8 = 0; c8 < HC / 8; ++c8) {
                 uint32_t packed[4];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    const float p0 = exp2f(sc[c8 * 8 + 2 * k] - base), p1 = exp2f(sc[c8 * 8 + 2 * k + 1] - base);
+                    const float p0 = fast_exp2(fmaf(sc[c8 * 8 + 2 * k], scale_log2, -base));
+                    const float p1 = fast_exp2(fmaf(sc[c8 * 8 + 2 * k + 1], scale_log2, -base));
                     rowsum += p0 + p1;
                     packed[k] = attn::pack_bf16(p0, p1);
                 }
@@ -294,7 +336,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             l_run = l_run * alpha + rowsum;
             tc::fence_proxy_async();          // the tensor core reads P through the async proxy
             __syncwarp();
-            if (lane == 0) tc::mbar_arrive(p_full);
+            if (lane == 0) tc::mbar_arrive(&p_full[b]);
             // ---- fold the tile before into the running output while this tile's P V runs
             if (j >= 1) ok = accumulate(j - 1);
             alpha_pending = alpha;
