@@ -96,7 +96,7 @@ class ClockSampler:
 
 def reference_arm():
     why = ("mxxm-t/llmx is a C++/CMake project with no Python packaging and no sm_100 build target; "
-           "pip install of /root/reference fails (neither setup.py nor pyproject.toml)")
+           "pip install of its source tree fails (neither setup.py nor pyproject.toml)")
     print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 
@@ -230,16 +230,16 @@ def main() -> int:
         print(json.dumps({"only": "decode", "value": round(value, 1), "ms_per_step": round(ms, 4), "batch": args.batch,
                           "context": args.context, "layers": args.layers, "gpu_launches": launches}))
         return 0
-    clocks = ClockSampler()
+    clocks = ClockSampler()          # clocks and throttle reasons over every timed region below
     clocks.start()
     value, ms, launches, _ = run_decode(args.batch, args.steps, args.warmup, e2e=False)
-    clock_record = clocks.stop()
     e2e_value, e2e_ms, _, h2d = run_decode(args.batch, args.steps, args.warmup, e2e=True)
     pf_value, pf_ms, pf_frac = run_prefill(args.prefill_tokens, 3, 3)
     points = {}
     if not args.no_points:
         points["decode_b1"] = round(run_decode(1, args.steps, args.warmup, e2e=False)[0], 1)
         points["decode_b64"] = round(run_decode(64, max(args.steps // 2, 8), args.warmup, e2e=False)[0], 1)
+    clock_record = clocks.stop()
     ops_tc.check_errors()
     achieved = decode_bytes(args.batch, args.context) / (ms * 1e-3) / 1e9
     line = {

@@ -364,6 +364,53 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
     if (threadIdx.x == 0) out[blockIdx.x] = chosen;
 }
 
+// Greedy rows only: the largest score, ties to the lowest id, a NaN only as the first token taking part
+// (src/inference/sampler.hpp:88-132), with 16-byte loads.  Used when no row of the batch draws.
+__global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict__ logits, int vocab,
+                                                         const RowParams* __restrict__ params, int* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float best_score[32];
+    __shared__ int best_id[32];
+    const float* row = logits + (size_t)blockIdx.x * vocab;
+    const int masked = params[blockIdx.x].masked;
+    const int skip = (masked >= 0 && masked < vocab && vocab > 1) ? masked : -1;
+    const int first = skip == 0 ? 1 : 0;
+    float bs = -INFINITY;
+    int bi = first;
+    const bool vec = (vocab % 4 == 0) && (((uintptr_t)row & 15) == 0);
+    if (vec) {
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        for (int i = threadIdx.x; i < vocab / 4; i += THREADS) {
+            const float4 v = row4[i];
+            const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int id = 4 * i + k;
+                if (id != skip && (e[k] > bs || (e[k] == bs && id < bi))) { bs = e[k]; bi = id; }
+            }
+        }
+    } else {
+        for (int id = threadIdx.x; id < vocab; id += THREADS) {
+            const float s = row[id];
+            if (id != skip && (s > bs || (s == bs && id < bi))) { bs = s; bi = id; }
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float os = __shfl_xor_sync(0xffffffffu, bs, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (os > bs || (os == bs && oi < bi)) { bs = os; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { best_score[threadIdx.x >> 5] = bs; best_id[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < THREADS / 32; ++w)
+            if (best_score[w] > bs || (best_score[w] == bs && best_id[w] < bi)) { bs = best_score[w]; bi = best_id[w]; }
+        if (isnan(row[first])) bi = first;
+        out[blockIdx.x] = bi;
+    }
+}
+
 // One thread per (row, seen token): the repetition penalty, then the additive ones.
 __global__ void penalty_kernel(float* __restrict__ logits, int vocab, const int* __restrict__ row_of,
                                const int* __restrict__ token, const int* __restrict__ count,
@@ -386,10 +433,15 @@ __global__ void penalty_kernel(float* __restrict__ logits, int vocab, const int*
 }  // namespace
 
 // params: rows x {temperature, top_p, min_p, r, top_k, masked} (24 bytes each) on the device.
-LLMX_EXPORT int llmx_sample(const float* logits, int rows, int vocab, const void* params, int* out,
+// `all_greedy` != 0: every row has temperature <= 0 (the caller knows); the argmax kernel alone runs.
+LLMX_EXPORT int llmx_sample(const float* logits, int rows, int vocab, const void* params, int* out, int all_greedy,
                             cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return LLMX_ERR_BAD_ARGUMENT;
+    if (all_greedy) {
+        launch_kernel(argmax_kernel, dim3(rows), dim3(THREADS), 0, stream, logits, vocab, (const RowParams*)params, out);
+        return launch_status();
+    }
     launch_kernel(sample_kernel, dim3(rows), dim3(THREADS), 0, stream, logits, vocab, (const RowParams*)params, out);
     return launch_status();
 }

@@ -9,7 +9,8 @@ knows which model it is in; the architecture's builder names the tensors.
 Interfaces (what another part of the same kind must provide):
 
   Part            tensor_specs() -> {role: TensorSpec};  load(tensors, precision)
-  Norm            forward(x_f32[T, E], out=None, row_index=None) -> act[T, E]
+  Norm            forward(x_f32[T, E], out=None, row_index=None, out_dtype=None, zero=None) -> act[T, E]
+                  (`zero`: a float32 buffer the part after it wants cleared; see PreNormBlock)
   PositionEncoding  prepare(max_positions, device); the tables a mixer's kernel reads
   Mixer           cache_spec() -> KVSpec | StateSpec | None
                   forward(h, step, cache_entry, residual, write_cache) adds its output into `residual`

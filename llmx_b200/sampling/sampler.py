@@ -19,7 +19,7 @@ from ..ops import _check, _cuda, _fn, _need, _ptr, _stream, register_signature
 from .params import SamplingParams
 
 _i, _p = ctypes.c_int, ctypes.c_void_p
-register_signature("sampling", "llmx_sample", [_p, _i, _i, _p, _p, _p])
+register_signature("sampling", "llmx_sample", [_p, _i, _i, _p, _p, _i, _p])
 register_signature("sampling", "llmx_penalize", [_p, _i, _p, _p, _p, _p, _p, _p, _i, _p])
 
 _MASK = (1 << 64) - 1
@@ -83,7 +83,11 @@ def sample(logits: torch.Tensor, states: Sequence[RequestSampling]) -> List[int]
         p = s.params
         u = 0.0 if p.greedy else s.rng.unit()
         _ROW.pack_into(raw, r * _ROW.size, p.temp, p.top_p, p.min_p, u, p.top_k, s.masked)
-    params = torch.frombuffer(raw, dtype=torch.uint8).to(dev)
+    host = torch.empty(len(raw), dtype=torch.uint8, pin_memory=True)
+    host.numpy()[:] = np.frombuffer(raw, dtype=np.uint8)
+    params = host.to(dev, non_blocking=True)
     out = torch.empty(rows, dtype=torch.int32, device=dev)
-    _check(_fn("sampling", "llmx_sample")(_ptr(logits), rows, vocab, _ptr(params), _ptr(out), _stream()), "sample")
+    all_greedy = all(s.params.greedy for s in states)
+    _check(_fn("sampling", "llmx_sample")(_ptr(logits), rows, vocab, _ptr(params), _ptr(out), 1 if all_greedy else 0,
+                                          _stream()), "sample")
     return out.cpu().tolist()

@@ -1,8 +1,8 @@
 #!/usr/bin/env python3
 """Makes tests/golden/*.npz: logits of mxxm-t/llmx's own CPU float32 code on tiny random models.
 
-Run by hand where the reference is mounted (REFERENCE=/path/to/llmx, default /root/reference):
-    python tests/golden/make_golden.py
+Run by hand where a checkout of mxxm-t/llmx is at hand:
+    REFERENCE=/path/to/llmx python tests/golden/make_golden.py
 It writes each tiny model's weights with this repository's random-weights mode, compiles
 tests/golden/reference_driver.cpp against the reference's headers (CPU only), runs it, and stores
 the token ids and the reference's logits (whole prompt and token by token).  tests/test_plain.py
@@ -20,7 +20,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
-REFERENCE = os.environ.get("REFERENCE", "/root/reference")
+REFERENCE = os.environ.get("REFERENCE")
+if not REFERENCE:
+    sys.exit("set REFERENCE to a checkout of mxxm-t/llmx")
 
 from configs import TINY_A, TINY_B  # noqa: E402
 from llmx_b200.config import Qwen3Config  # noqa: E402

@@ -175,3 +175,48 @@ def test_step_refusals(model_dirs):
     assert engine.step([StepEntry("b", list(range(40)), [0])]).shape == (1, 256)
     engine.end("b")
     assert engine.cache.used_pages() == [0]
+
+
+@pytest.fixture(scope="module")
+def sharp_model_dirs(model_dirs, tmp_path_factory):
+    """Models whose attention is sharp: the q/k norm weights are scaled by 4, so scores spread over +-16 and a
+    row's output hangs on a few keys anywhere in its history.  With the random weights' nearly uniform attention
+    a key that is dropped or read from the wrong page changes a row by ~1/length; here it changes it outright."""
+    import torch
+    from llmx_b200.weights import TensorDirectory, write_safetensors
+    out = {}
+    for name in ("B", "D"):
+        made = []
+        for src in model_dirs[name][:2]:
+            d = str(tmp_path_factory.mktemp(f"sharp_{name}"))
+            t = TensorDirectory(src)
+            tensors = {}
+            for n in t.names():
+                x = t.tensor(n).clone()
+                if n.endswith("q_norm.weight") or n.endswith("k_norm.weight"):
+                    x = x * 4.0
+                tensors[n] = x
+            write_safetensors(os.path.join(d, "model.safetensors"), tensors)
+            with open(os.path.join(src, "config.json")) as f, open(os.path.join(d, "config.json"), "w") as g:
+                g.write(f.read())
+            made.append(d)
+        out[name] = (made[0], made[1], model_dirs[name][2])
+    return out
+
+
+@pytest.mark.parametrize("name", ["B", "D"])
+@pytest.mark.parametrize("cutting", ["whole", "tail", "portions", "mixed"])
+def test_sharp_attention_under_cutting(sharp_model_dirs, name, cutting):
+    """The float32 path against the plain implementation with attention that hangs on single far keys.
+
+    Only float32: with scores of +-16 one bfloat16 step in q or k moves a softmax weight by several per cent, so in
+    bfloat16 the comparison would measure that rounding, not the cache (two bfloat16 runs of the same prompt cut
+    differently differ by 4 % of the logit scale here, from the order of float sums alone).  The bfloat16 kernels
+    meet keys that stand out in tests/test_kernels_gpu.py (spike=True), on inputs that are bfloat16 to begin with."""
+    vocab = CONFIGS[name][0]["vocab_size"]
+    requests = {f"s{i}": helpers.random_ids(vocab, n, seed=300 + i) for i, n in enumerate([200, 37, 150, 9, 64])}
+    make = {"whole": helpers.trace_whole, "tail": helpers.trace_tail_decoded, "portions": helpers.trace_portions,
+            "mixed": helpers.trace_mixed}[cutting]
+    steps = make(requests)
+    folder, engine = _engine(sharp_model_dirs, name, "float32", helpers.tokens_needed(steps))
+    _check(engine, folder, steps, requests, "float32")
