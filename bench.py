@@ -38,6 +38,16 @@ QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidd
                 max_position_embeddings=40960)
 
 
+# The other sizes BASELINE.json lists (same architecture, other widths), for `--size`.
+SIZES = {
+    "8b": {},
+    "0.6b": dict(num_hidden_layers=28, hidden_size=1024, intermediate_size=3072, num_attention_heads=16,
+                 num_key_value_heads=8, tie_word_embeddings=True),
+    "32b": dict(num_hidden_layers=64, hidden_size=5120, intermediate_size=25600, num_attention_heads=64,
+                num_key_value_heads=8),
+}
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -107,7 +117,8 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--layers", type=int, default=36, help="fewer layers than the model has (both numbers are reported)")
+    ap.add_argument("--size", choices=sorted(SIZES), default="8b", help="layer sizes: Qwen3-8B (the default), 0.6B or 32B")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (both numbers are reported)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
@@ -132,6 +143,10 @@ def main() -> int:
 
     pk = peaks()
     raw = dict(QWEN3_8B)
+    raw.update(SIZES[args.size])
+    model_layers = raw["num_hidden_layers"]
+    if args.layers is None:
+        args.layers = model_layers
     raw["num_hidden_layers"] = args.layers
     cfg = Qwen3Config.from_dict(raw)
     page = 16
@@ -156,6 +171,7 @@ def main() -> int:
     # ---- bytes a decode step must read ------------------------------------------------------------
     E, F, Q, KV, V, L = cfg.hidden_size, cfg.intermediate_size, cfg.q_width, cfg.kv_width, cfg.vocab_size, args.layers
     weight_bytes = 2 * (L * ((Q + 2 * KV) * E + E * Q + 2 * F * E + E * F) + V * E) + 4 * (L * (2 * E + 2 * cfg.head_dim) + E)
+    # (a tied head reads the embedding table as its weight: the same V * E bytes)
     kv_bytes_per_token = L * 2 * KV * 2
 
     def decode_bytes(batch, context):
@@ -243,11 +259,11 @@ def main() -> int:
     ops_tc.check_errors()
     achieved = decode_bytes(args.batch, args.context) / (ms * 1e-3) / 1e9
     line = {
-        "metric": "decode tok/s at batch 8, context 8192 (Qwen3-8B sizes, bf16, random weights)",
+        "metric": f"decode tok/s at batch {args.batch}, context {args.context} (Qwen3-{args.size.upper()} sizes, bf16, random weights)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic", "impl": "ours",
-        "config": {"model": "Qwen3-8B sizes, random weights", "layers": args.layers, "model_layers": 36,
+        "config": {"model": f"Qwen3-{args.size.upper()} sizes, random weights", "layers": args.layers, "model_layers": model_layers,
                    "hidden": E, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": F, "vocab": V, "global_batch": args.batch,
                    "seq_len": args.context, "page_size": page, "prefill_tokens": args.prefill_tokens,
