@@ -52,31 +52,41 @@ class DecodeSession:
         return sizes, offsets, at
 
     def _fill(self, host: np.ndarray, tokens: Sequence[int], caches, chunk: int) -> None:
+        """Write the step's metadata into `host`.  The master copy is kept between steps and only what a step
+        changes is touched: tokens, positions, slots, and a block-table entry when a request enters a new page."""
         b = len(caches)
         sizes, offsets = self._sizes, self._offsets
+        m = self._master
 
         def sec(i):
-            return host[offsets[i]:offsets[i] + sizes[i]]
+            return m[offsets[i]:offsets[i] + sizes[i]]
         hist = [rc.length for rc in caches]
+        if not self._master_ready:
+            sec(2)[:] = np.arange(b)
+            sec(3)[:] = np.arange(b)
+            sec(4)[:] = 1
+            sec(6)[:] = [rc.state_slot for rc in caches]
+            sec(7)[:] = np.arange(b)
+            sec(8)[:b] = np.arange(b)
+            self._pages_seen = [[0] * b for _ in self.engine.cache.groups]
+            self._master_ready = True
         sec(0)[:] = tokens
         sec(1)[:] = hist
-        sec(2)[:] = np.arange(b)
-        sec(3)[:] = np.arange(b)
-        sec(4)[:] = 1
         sec(5)[:] = hist
-        sec(6)[:] = [rc.state_slot for rc in caches]
-        sec(7)[:] = np.arange(b)
-        sec(8)[:b] = np.arange(b)
         sec(9)[0] = chunk
         for g, grp in enumerate(self.engine.cache.groups):
             ps = grp.page_size
             mp = self._max_pages[g]
             bt = sec(10 + 2 * g).reshape(b, mp)
             sl = sec(11 + 2 * g)
+            seen = self._pages_seen[g]
             for r, rc in enumerate(caches):
                 pages = rc.tables[g].pages
-                bt[r, :len(pages)] = pages
+                if seen[r] != len(pages):
+                    bt[r, :len(pages)] = pages          # released pages (-1) are never addressed
+                    seen[r] = len(pages)
                 sl[r] = pages[hist[r] // ps] * ps + hist[r] % ps
+        host[:] = m
 
     def _record(self, caches) -> None:
         from .. import ops, ops_attn
@@ -92,6 +102,8 @@ class DecodeSession:
         self._ring_events = [None] * len(self._ring)
         self._ring_at = 0
         self._dev = torch.zeros(total, dtype=torch.int32, device=eng.device)
+        self._master = np.zeros(total, dtype=np.int32)
+        self._master_ready = False
         self._room = room
         # Key ranges of the split-KV kernel: the grid is fixed by the recording, the keys per range are data.
         kv_heads = max((g.spec.kv_heads for g in eng.cache.groups), default=1)

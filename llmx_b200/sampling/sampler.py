@@ -78,16 +78,29 @@ def sample(logits: torch.Tensor, states: Sequence[RequestSampling]) -> List[int]
         _check(_fn("sampling", "llmx_penalize")(_ptr(logits), vocab, _ptr(arr[0]), _ptr(arr[1]), _ptr(arr[2]),
                                                 _ptr(pen[0]), _ptr(pen[1]), _ptr(pen[2]), len(items), _stream()),
                "penalize")
-    raw = bytearray(_ROW.size * rows)
-    for r, s in enumerate(states):
-        p = s.params
-        u = 0.0 if p.greedy else s.rng.unit()
-        _ROW.pack_into(raw, r * _ROW.size, p.temp, p.top_p, p.min_p, u, p.top_k, s.masked)
-    host = torch.empty(len(raw), dtype=torch.uint8, pin_memory=True)
-    host.numpy()[:] = np.frombuffer(raw, dtype=np.uint8)
-    params = host.to(dev, non_blocking=True)
-    out = torch.empty(rows, dtype=torch.int32, device=dev)
     all_greedy = all(s.params.greedy for s in states)
+    key = None
+    if all_greedy:
+        # Greedy rows draw nothing: their parameters are the same from step to step and stay on the device.
+        key = (dev.index, tuple(s.masked for s in states))
+    params = _greedy_params.get(key) if key is not None else None
+    if params is None:
+        raw = bytearray(_ROW.size * rows)
+        for r, s in enumerate(states):
+            p = s.params
+            u = 0.0 if p.greedy else s.rng.unit()
+            _ROW.pack_into(raw, r * _ROW.size, p.temp, p.top_p, p.min_p, u, p.top_k, s.masked)
+        host = torch.empty(len(raw), dtype=torch.uint8, pin_memory=True)
+        host.numpy()[:] = np.frombuffer(raw, dtype=np.uint8)
+        params = host.to(dev, non_blocking=True)
+        if key is not None:
+            if len(_greedy_params) > 64:
+                _greedy_params.clear()
+            _greedy_params[key] = params
+    out = torch.empty(rows, dtype=torch.int32, device=dev)
     _check(_fn("sampling", "llmx_sample")(_ptr(logits), rows, vocab, _ptr(params), _ptr(out), 1 if all_greedy else 0,
                                           _stream()), "sample")
     return out.cpu().tolist()
+
+
+_greedy_params: Dict[tuple, torch.Tensor] = {}
