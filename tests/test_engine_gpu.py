@@ -220,3 +220,35 @@ def test_sharp_attention_under_cutting(sharp_model_dirs, name, cutting):
     steps = make(requests)
     folder, engine = _engine(sharp_model_dirs, name, "float32", helpers.tokens_needed(steps))
     _check(engine, folder, steps, requests, "float32")
+
+
+WIDE = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=4096, intermediate_size=12288, num_attention_heads=32, num_key_value_heads=8,
+    head_dim=128, vocab_size=32003, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+    max_position_embeddings=4096)
+
+
+@pytest.fixture(scope="module")
+def wide_model_dir(tmp_path_factory):
+    """Two layers with the widths of Qwen3-8B (and a vocabulary that is no multiple of anything), so that the
+    kernels run at the sizes they are built for: full tensor-core tiles, 64 k blocks, 32 heads over 8 kv heads."""
+    import torch
+    from llmx_b200.config import Qwen3Config
+    from llmx_b200.weights import write_random_model
+    d = str(tmp_path_factory.mktemp("wide"))
+    write_random_model(d, Qwen3Config.from_dict(WIDE), seed=9, dtype=torch.bfloat16)
+    return d
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_of_8b_width_under_cutting(wide_model_dir, dtype):
+    """The stored weights are bfloat16, exact in both paths; the float32 path widens them."""
+    from llmx_b200.engine import Engine, EngineOptions
+    requests = {f"w{i}": helpers.random_ids(WIDE["vocab_size"], n, seed=40 + i) for i, n in enumerate([150, 70, 33, 2])}
+    for make in (helpers.trace_whole, helpers.trace_mixed):
+        steps = make(requests)
+        engine = Engine.from_dir(wide_model_dir, EngineOptions(dtype=dtype, kv_tokens=helpers.tokens_needed(steps),
+                                                               page_size=16, max_requests=4))
+        _check(engine, wide_model_dir, steps, requests, dtype)
+        del engine
