@@ -1,4 +1,4 @@
-"""The command line: `llmx generate MODEL PROMPT_IDS [flags]` and `llmx bench`.
+"""The command line: `llmx generate MODEL PROMPT_IDS [flags]`, `llmx logits` and `llmx bench`.
 
 Names and meanings of the options are the reference's where it has them
 (src/cli/main.cpp:2018-2040 for generate's flags, :544-574 for the execution flags,
@@ -20,6 +20,9 @@ USAGE = """usage:
                 [--device D] [--verbose]
       MODEL   a folder with config.json and model.safetensors
       IDS     the prompt as token ids, e.g. 1,2,3
+  llmx logits MODEL (IDS | --file F) [--top K] [--last N] [--per-token] [--dtype auto|bf16|f32] [--ubatch N]
+      the K best next tokens (default 5) after each of the last N positions (default 1); --per-token feeds
+      the ids one at a time instead of in portions of --ubatch
   llmx bench --model MODEL [--p P] [--n G] [--r R] [--seqs S] [--depth D] [--dtype auto|bf16|f32]
       prompt of P tokens (default 512), G generated tokens (default 128), R repeats (default 3),
       S sequences decoded together (default 1) after a history of D tokens each (default P)
@@ -156,6 +159,45 @@ def cmd_generate(argv: List[str]) -> int:
     return 0
 
 
+def cmd_logits(argv: List[str]) -> int:
+    """Top logits per position (the reference's `logits`, src/cli/main.cpp:934-980)."""
+    import torch
+    from ..engine import Engine, EngineOptions, StepEntry
+    valued = {k: k for k in ("--top", "--last", "--dtype", "--ubatch", "--device", "--file")}
+    given, pos = _parse(argv, valued, ("--per-token",))
+    if not pos:
+        raise UsageError("missing the model")
+    if "--file" in given:
+        with open(given["--file"], "r", encoding="utf-8") as fh:
+            ids = _ids(fh.read())
+        if len(pos) > 1:
+            raise UsageError(f"a second text, '{pos[1]}'")
+    else:
+        if len(pos) != 2:
+            raise UsageError("missing the ids" if len(pos) < 2 else f"a second text, '{pos[2]}'")
+        ids = _ids(pos[1])
+    top = _int("--top", given.get("--top", "5"), 1)
+    last = min(_int("--last", given.get("--last", "1"), 1), len(ids))
+    ubatch = 1 if "--per-token" in given else _int("--ubatch", given.get("--ubatch", "512"), 1)
+    engine = Engine.from_dir(pos[0], EngineOptions(dtype=_dtype(given.get("--dtype", "auto")),
+                                                   kv_tokens=-(-len(ids) // 64) * 64, max_requests=1,
+                                                   device=given.get("--device", "cuda:0")))
+    first_wanted = len(ids) - last
+    rows = []
+    for at in range(0, len(ids), ubatch):
+        part = ids[at:at + ubatch]
+        want = [i for i in range(len(part)) if at + i >= first_wanted]
+        out = engine.step([StepEntry("logits", part, want)])
+        if out is not None:
+            rows.append(out.float().cpu())
+    logits = torch.cat(rows)
+    for r, row in enumerate(logits):
+        values, tokens = torch.topk(row, min(top, row.numel()))
+        best = " ".join(f"{int(t)}:{float(v):.4f}" for v, t in zip(values, tokens))
+        print(f"pos {first_wanted + r} after {ids[first_wanted + r]}: {best}")
+    return 0
+
+
 def cmd_bench(argv: List[str]) -> int:
     import torch
     from ..engine import Engine, EngineOptions, StepEntry
@@ -233,6 +275,8 @@ def main(argv: Optional[List[str]] = None) -> int:
             return cmd_generate(rest)
         if cmd == "bench":
             return cmd_bench(rest)
+        if cmd == "logits":
+            return cmd_logits(rest)
         raise UsageError(f"unknown command: {cmd}")
     except UsageError as e:
         print(f"llmx: {e}\n{USAGE}", file=sys.stderr)

@@ -117,6 +117,15 @@ def test_command_line(model_dirs, tmp_path):
                 ["frobnicate"]):
         r = subprocess.run(exe + bad, capture_output=True, text=True, timeout=120)
         assert r.returncode == 2 and "usage:" in r.stderr, bad
+    lg = subprocess.run(exe + ["logits", d16, "5,17,3,99", "--top", "3", "--last", "2"], capture_output=True, text=True, timeout=600)
+    per = subprocess.run(exe + ["logits", d16, "5,17,3,99", "--top", "3", "--last", "2", "--per-token"], capture_output=True,
+                         text=True, timeout=600)
+    assert lg.returncode == 0 and per.returncode == 0, lg.stderr[-2000:] + per.stderr[-2000:]
+    lines = [l for l in lg.stdout.splitlines() if l.startswith("pos ")]
+    assert [l.split(":")[0] for l in lines] == ["pos 2 after 3", "pos 3 after 99"]
+    assert int(lines[1].split(": ")[1].split(":")[0]) == tokens[0]          # the best token after the prompt is what greedy drew
+    assert [l.split()[4].split(":")[0] for l in per.stdout.splitlines() if l.startswith("pos ")] == \
+           [l.split()[4].split(":")[0] for l in lines]
     bench = subprocess.run(exe + ["bench", "--model", d16, "--p", "40", "--n", "5", "--r", "1", "--seqs", "2"],
                            capture_output=True, text=True, timeout=600)
     assert bench.returncode == 0 and "pp40:" in bench.stdout and "tg5 x2" in bench.stdout, bench.stderr[-2000:]
