@@ -1,7 +1,8 @@
 """The parts of a layer alone, and an architecture made in this file from the framework's parts plus a
 toy mixer with state of its own, registered, built and stepped without a change to the framework.
 
-The toy model exercises what Qwen3 does not: a mixer with fixed-size per-request state, a windowed
+The toy model exercises what Qwen3 does not: a mixer with fixed-size per-request state, a feed-forward
+with a router and experts, a windowed
 attention layer whose pages are given back, a partially rotated and an unrotated attention layer, a
 block that runs twice (each run with a cache entry of its own), and a block that reads the keys
 another run of it wrote.  Its plain implementation below is whole-sequence numpy built from
@@ -63,6 +64,43 @@ def _toy_mixer_class():
     return RunningSumMixer
 
 
+# A toy feed-forward with routing: a float32 router picks one of `experts` small gated MLPs per row.
+def _toy_routed_ffn_class():
+    from llmx_b200.parts import Part
+    from llmx_b200.weights import TensorSpec
+
+    class RoutedFFN(Part):
+        recordable = False          # it picks rows on the host side of torch ops
+
+        def __init__(self, hidden, inner, experts):
+            self.hidden, self.inner, self.experts = hidden, inner, experts
+
+        def tensor_specs(self):
+            specs = {"router.weight": TensorSpec((self.experts, self.hidden))}
+            for e in range(self.experts):
+                specs[f"experts.{e}.gate_proj.weight"] = TensorSpec((self.inner, self.hidden))
+                specs[f"experts.{e}.up_proj.weight"] = TensorSpec((self.inner, self.hidden))
+                specs[f"experts.{e}.down_proj.weight"] = TensorSpec((self.hidden, self.inner))
+            return specs
+
+        def load(self, tensors, precision):
+            super().load(tensors, precision)
+            self.w = {n: t.float() for n, t in tensors.items()}
+
+        def forward(self, h, step, residual):
+            hf = h.float()
+            choice = (hf @ self.w["router.weight"].T).argmax(dim=-1)            # router logits in float32
+            for e in range(self.experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                x = hf[rows]
+                g, u = x @ self.w[f"experts.{e}.gate_proj.weight"].T, x @ self.w[f"experts.{e}.up_proj.weight"].T
+                residual[rows] += (torch.nn.functional.silu(g) * u) @ self.w[f"experts.{e}.down_proj.weight"].T
+
+    return RoutedFFN
+
+
 @dataclass(frozen=True)
 class ToyConfig:
     hidden_size: int = 64
@@ -94,7 +132,8 @@ def _build_toy(cfg: ToyConfig):
     blocks = [
         PreNormBlock(norm(), Attention(E, H, G, D, RotaryEmbedding(D, 10000.0, rot_dim=8), qk_norm_eps=cfg.rms_norm_eps),
                      norm(), mlp()),                                                    # 0: partial rotation
-        PreNormBlock(norm(), _toy_mixer_class()(E, cfg.decay), norm(), mlp()),          # 1: state
+        PreNormBlock(norm(), _toy_mixer_class()(E, cfg.decay), norm(),
+                     _toy_routed_ffn_class()(E, 48, 3)),                                # 1: state; routed feed-forward
         PreNormBlock(norm(), Attention(E, H, G, D, NoPositionEncoding(), qk_norm_eps=None, window=cfg.window),
                      norm(), mlp()),                                                    # 2: window, no rotation, no q/k norm
     ]
@@ -143,7 +182,15 @@ def _plain_toy(cfg: ToyConfig, w, ids):
         for t in range(T):
             s = np.float32(cfg.decay) * s + h[t]
             outs.append(s)
-        return mlp(x + np.stack(outs) @ w[pre + "self_attn.proj.weight"].T, pre)
+        x = x + np.stack(outs) @ w[pre + "self_attn.proj.weight"].T
+        h = plain.rms_norm(x, w[pre + "post_attention_layernorm.weight"], eps)
+        choice = (h @ w[pre + "mlp.router.weight"].T).argmax(axis=-1)
+        out = x.copy()
+        for t in range(T):
+            e = int(choice[t])
+            out[t] += plain.swiglu_ffn(h[t:t + 1], w[pre + f"mlp.experts.{e}.gate_proj.weight"],
+                                       w[pre + f"mlp.experts.{e}.up_proj.weight"], w[pre + f"mlp.experts.{e}.down_proj.weight"])[0]
+        return out
 
     def block2(x, kv=None):
         pre = "model.layers.2."
