@@ -1,7 +1,7 @@
 // Blackwell building blocks in inline PTX: mbarriers with bounded waits, TMA tile loads,
 // tensor-memory allocation, tcgen05 matrix instructions and their descriptors.
 //
-// Waiting.  Every wait on an mbarrier has an iteration limit.  A wait that runs out records
+// Waiting.  Every wait on an mbarrier has a limit of two seconds.  A wait that runs out records
 // a code in the kernel's error word (global memory, read by the host) and raises the block's
 // abort flag; every later wait of the block returns at once, the block frees its tensor
 // memory and returns.  Nothing in these kernels waits on another block.
@@ -50,14 +50,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return done != 0;
 }
 
-constexpr uint32_t WAIT_LIMIT = 1u << 24;  // try_wait suspends for a while each time; this is seconds
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // two seconds of wall time
 
-// Returns false when the wait ran out or the block is aborting.
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Returns false when the wait ran out (two seconds) or the block is aborting.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* error_word,
                                           int code) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long start = global_ns();
+    for (uint32_t i = 1;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 255u && *abort_flag) return false;
+        if ((i & 255u) == 0u) {
+            if (*abort_flag) return false;
+            if (global_ns() - start > WAIT_LIMIT_NS) break;
+        }
     }
     *abort_flag = 1;
     if (error_word) atomicCAS(error_word, 0, code);
