@@ -145,18 +145,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __syncthreads();
     tc::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // Barriers, tensor memory and descriptors are ready; everything from here on touches memory other
-    // kernels write, so the kernel before must have finished.
-    pdl_wait();
-
+    // Barriers, tensor memory and descriptors are ready.  The weights are written by no kernel, so the
+    // producer fetches its first stages of them at once; whatever another kernel writes (the activations,
+    // the output) is touched only after pdl_wait(), when the kernel before has finished.
     if (warp == 0) {
         if (tc::elect_one()) {
             Scheduler<STREAMK> sched(n_tiles, m_tiles, k_blocks, splits);
             Work w;
             uint32_t stage = 0, phase = 0;
-            bool ok = true;
+            bool ok = true, waited = false;
+            // Units (tile, k block) whose weights are in flight but whose activations are not yet asked for.
+            int early_kb[cfg::STAGES], early_mt[cfg::STAGES], early = 0;
             while (ok && sched.next(w)) {
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
+                    if (!waited && early == cfg::STAGES) {
+                        pdl_wait();
+                        waited = true;
+#pragma unroll
+                        for (int e = 0; e < cfg::STAGES; ++e)
+                            tc::tma_load_2d(tiles + e * cfg::STAGE_BYTES + cfg::A_TILES * cfg::A_BYTES, &map_a,
+                                            early_kb[e] * BK, early_mt[e] * BN, &full_bar[e]);
+                    }
                     ok = tc::mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, error_word, ERR_PRODUCER);
                     if (!ok) break;
                     uint8_t* a_dst = tiles + stage * cfg::STAGE_BYTES;
@@ -164,9 +173,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     tc::mbar_expect_tx(&full_bar[stage], cfg::STAGE_BYTES);
                     tc::tma_load_2d(a_dst, &map_w, kb * BK, w.nt * BM, &full_bar[stage]);
                     if (DUAL) tc::tma_load_2d(a_dst + cfg::A_BYTES, &map_w, kb * BK, N + w.nt * BM, &full_bar[stage]);
-                    tc::tma_load_2d(b_dst, &map_a, kb * BK, w.mt * BN, &full_bar[stage]);
+                    if (waited) {
+                        tc::tma_load_2d(b_dst, &map_a, kb * BK, w.mt * BN, &full_bar[stage]);
+                    } else {
+                        early_kb[early] = kb;
+                        early_mt[early] = w.mt;
+                        ++early;
+                    }
                     if (++stage == cfg::STAGES) { stage = 0; phase ^= 1; }
                 }
+            }
+            if (!waited) {
+                // Fewer units than stages: their activations are still to be asked for.
+                pdl_wait();
+                for (int e = 0; e < early; ++e)
+                    tc::tma_load_2d(tiles + e * cfg::STAGE_BYTES + cfg::A_TILES * cfg::A_BYTES, &map_a,
+                                    early_kb[e] * BK, early_mt[e] * BN, &full_bar[e]);
             }
         }
     } else if (warp == 1) {
@@ -214,6 +236,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
         const bool atomic = STREAMK || mode == MODE_ATOMIC || (mode == MODE_ACCUMULATE && splits > 1);
+        pdl_wait();     // the output may be read or cleared by the kernel before
         while (ok && sched.next(w)) {
             ok = tc::mbar_wait(&acc_full[acc], acc_phase, abort_flag, error_word, ERR_EPILOGUE);
             if (!ok) break;
