@@ -1,24 +1,26 @@
 // Tiled causal attention for prompt portions on the 5th-generation tensor cores (head width 128).
 //
-// A block serves one (request, kv head, tile of new rows): 128 / ratio consecutive new rows times the
-// `ratio` query heads of the group are the 128 rows of both products,
+// A block serves one (request, kv head, 2 * 128 / ratio consecutive new rows): two row tiles, each 128 / ratio
+// new rows times the `ratio` query heads of the group = the 128 rows of both products,
 //     S[128 rows, 128 keys] = Q K^T        O[128 rows, 128 columns] += P V
-// issued as tcgen05.mma by one thread, with S and P V in tensor memory:
+// issued as tcgen05.mma by one thread.  The two row tiles share every key stage and take turns on the tensor
+// core: while one tile's softmax runs, the other's products do.
 //
-//   warp 0      TMA producer: the Q tile once (a 5-D box that lays [token][head] rows out as the
-//               instruction's K-major operand), then 128 keys a stage, two stages: the request's pages
-//               into [half of the head][key][64 columns] (keys K-major for Q K^T, values as the
-//               MN-major operand of P V, so neither is transposed)
-//   warp 1      allocates tensor memory (two S and two P V accumulators, 512 columns) and issues the
-//               products: Q K^T of tile j + 1 goes out before P V of tile j, so the tensor core works
-//               while tile j's softmax runs; P has two buffers too, so tile j + 1's P is written while
-//               P V of tile j reads its own
-//   warps 2-9   two threads per query row, each with 64 of the row's 128 columns: read S from tensor
-//               memory (tcgen05.ld), mask (causal, window), online softmax in float32 (base 2; the two
-//               halves of a row exchange their maxima through shared memory), write P as bfloat16
-//               into shared memory in the operand layout, then fold the finished P V of the tile
-//               before into the row's running output (registers): O = O * 2^(m_old - m_new) + P V.
-//               At the end O / l is written.
+//   tensor memory   S of tile 0, S of tile 1, O of tile 0, O of tile 1: 4 x 128 columns.  P (bfloat16, two to a
+//                   column) is written over the first 64 columns of the tile's S and is the P V product's A
+//                   operand straight from tensor memory; O stays in tensor memory for the whole block.
+//   warp 0          TMA producer: both Q tiles once (a 5-D box lays [token][head] rows out as the instruction's
+//                   K-major operand), then 128 keys a stage, two stages, keys and values on barriers of their
+//                   own; every lane issues one of the stage's 32 copies (8 pages x 2 halves x keys/values).
+//                   Keys are K-major for Q K^T, values the MN-major operand of P V: neither is transposed.
+//   warp 1          allocates tensor memory and issues the products in the order
+//                   P V (tile 0, j), Q K^T (tile 0, j + 1), P V (tile 1, j), Q K^T (tile 1, j + 1), ...
+//   warps 2-5, 6-9  one thread per query row of tile 0 / tile 1: read the row's 128 scores (tcgen05.ld), mask
+//                   (causal, window), online softmax in float32 (base 2), write P (tcgen05.st).  The exponent
+//                   uses a row maximum that is only raised when the true one has grown by more than 2^8; then
+//                   the thread rescales its row of O in tensor memory.  P <= 256 and the sums stay exact
+//                   in the same sense: O / l does not depend on which maximum was used, beyond rounding.
+//                   At the end O / l is written.
 //
 // Every wait on an mbarrier is bounded (see tc_common.cuh).  Shapes this kernel does not take (head width
 // other than 128, a head ratio that does not divide 128, page size other than 16) run the warp-level
@@ -31,19 +33,22 @@ namespace {
 
 constexpr int D = 128;
 constexpr int PAGE = 16;
-constexpr int ROWS = 128;                 // query rows of a tile (the instruction's M)
+constexpr int ROWS = 128;                 // query rows of a row tile (the instruction's M)
 constexpr int KEYS = 128;                 // keys per stage (the instruction's N for Q K^T, its K for P V)
 constexpr int PAGES_PER_STAGE = KEYS / PAGE;
 constexpr int KV_STAGES = 2;
-constexpr int SOFTMAX_WARPS = 8;          // two warps per 32 rows: each takes 64 of a row's 128 columns
+constexpr int TILE_WARPS = 4;             // softmax warps per row tile: one thread per row
+constexpr int SOFTMAX_WARPS = 2 * TILE_WARPS;
 constexpr int THREADS = 64 + SOFTMAX_WARPS * 32;
 constexpr int HALF_BYTES = 128 * 128;     // 128 rows of 128 bytes: one 64-column half of an operand
 constexpr int OPERAND_BYTES = 2 * HALF_BYTES;
 constexpr int STAGE_BYTES = 2 * OPERAND_BYTES;                      // keys, then values
-constexpr int SMEM_Q = 0, SMEM_P = OPERAND_BYTES, SMEM_KV = 3 * OPERAND_BYTES;    // Q, two P buffers, then the stages
-constexpr int SMEM_TILES = SMEM_KV + KV_STAGES * STAGE_BYTES;       // 229,376 bytes
-constexpr int SMEM_BYTES = SMEM_TILES + 1024 + 256 + 2 * ROWS * 4;   // + the rows' maxima of both column halves
+constexpr int SMEM_Q = 0, SMEM_KV = 2 * OPERAND_BYTES;             // two Q tiles, then the stages
+constexpr int SMEM_TILES = SMEM_KV + KV_STAGES * STAGE_BYTES;       // 196,608 bytes
+constexpr int SMEM_BYTES = SMEM_TILES + 1024 + 256;
 constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t TMEM_O = 2 * KEYS;     // first column of the outputs
+constexpr float RAISE = 8.0f;             // the exponent's maximum follows the true one when it is this far behind
 enum : int { ERR_TCA_PRODUCER = 401, ERR_TCA_MMA = 402, ERR_TCA_SOFTMAX = 403 };
 
 // Instruction descriptors: bfloat16 in, float32 out, M = 128, N = 128; A K-major; B K-major (keys) or MN-major (values).
@@ -65,6 +70,31 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// Three-input maximum and two float32 operations per instruction (packed pairs in 64-bit registers).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 __global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap cache_map,
                        __nv_bfloat16* __restrict__ out, const int* __restrict__ req_list,
@@ -76,19 +106,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + SMEM_TILES);
     uint64_t* q_full = bars;                 // [1]
-    uint64_t* kv_full = bars + 1;            // [2]
-    uint64_t* k_empty = bars + 3;            // [2]  keys of a stage are free once Q K^T has read them
-    uint64_t* s_full = bars + 5;             // [2]
-    uint64_t* s_empty = bars + 7;            // [2]
-    uint64_t* o_full = bars + 9;             // [2]
-    uint64_t* o_empty = bars + 11;           // [2]
-    uint64_t* p_full = bars + 13;            // [2]
-    uint64_t* p_empty = bars + 15;           // [2]
-    uint64_t* v_empty = bars + 17;           // [2]  values of a stage are free once P V has read them
-    uint64_t* k_full = bars + 19;            // [2]
-    uint32_t* tmem_slot = (uint32_t*)(bars + 21);
+    uint64_t* k_full = bars + 1;             // [2 stages]
+    uint64_t* v_full = bars + 3;             // [2 stages]
+    uint64_t* k_empty = bars + 5;            // [2 stages]  free once the last Q K^T that reads the stage has run
+    uint64_t* v_empty = bars + 7;            // [2 stages]  free once the last P V that reads the stage has run
+    uint64_t* s_full = bars + 9;             // [2 tiles]   S of the tile is written (and, once more at the end, O)
+    uint64_t* p_full = bars + 11;            // [2 tiles]   P of the tile is written, O rescaled if need be
+    uint32_t* tmem_slot = (uint32_t*)(bars + 13);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-    float* half_max = (float*)(smem + SMEM_TILES + 256);         // [2][ROWS]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ratio = heads / kv_heads;
@@ -97,16 +122,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     if (threadIdx.x == 0) {
         tc::mbar_init(q_full, 1);
         for (int i = 0; i < 2; ++i) {
-            tc::mbar_init(&kv_full[i], 1);      // values
-            tc::mbar_init(&k_full[i], 1);       // keys
+            tc::mbar_init(&k_full[i], 1);
+            tc::mbar_init(&v_full[i], 1);
             tc::mbar_init(&k_empty[i], 1);
             tc::mbar_init(&v_empty[i], 1);
-            tc::mbar_init(&p_full[i], SOFTMAX_WARPS);
-            tc::mbar_init(&p_empty[i], 1);
             tc::mbar_init(&s_full[i], 1);
-            tc::mbar_init(&s_empty[i], SOFTMAX_WARPS);
-            tc::mbar_init(&o_full[i], 1);
-            tc::mbar_init(&o_empty[i], SOFTMAX_WARPS);
+            tc::mbar_init(&p_full[i], TILE_WARPS);
         }
         *abort_flag = 0;
         tc::fence_barrier_init();
@@ -117,7 +138,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         tc::tmem_alloc(tmem_slot, TMEM_COLS);
         tc::tmem_relinquish();
     }
-    // The value halves start as zeros: a stage's pages that are not fetched (past the tile's last key)
+    // The value halves start as zeros: a stage's pages that are not fetched (past the block's last key)
     // then hold zeros or older finite values, never what the memory held before the launch.
     for (int i = threadIdx.x; i < KV_STAGES * OPERAND_BYTES / 16; i += THREADS) {
         const int stage = i / (OPERAND_BYTES / 16), off = i % (OPERAND_BYTES / 16);
@@ -130,230 +151,230 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();
 
-    // Which tile this block serves (after the wait: the metadata may come from the step's copy).
+    // Which rows this block serves (after the wait: the metadata may come from the step's copy).
     const int r = req_list[blockIdx.z], g = blockIdx.y;
     const int n_q = row_count[r];
-    const int n_tiles = (n_q + tokens_per_tile - 1) / tokens_per_tile;
-    const bool active = (int)blockIdx.x < n_tiles;
-    const int tile = active ? n_tiles - 1 - blockIdx.x : 0;          // the tiles with the most keys start first
+    const int n_blocks = (n_q + 2 * tokens_per_tile - 1) / (2 * tokens_per_tile);
+    const bool active = (int)blockIdx.x < n_blocks;
+    const int blk = active ? n_blocks - 1 - blockIdx.x : 0;          // the rows with the most keys start first
     const int q0 = row_start[r], hist = history[r];
-    const int t0 = tile * tokens_per_tile;
-    const int t_count = min(tokens_per_tile, n_q - t0);
-    const int M = t_count * ratio;
-    const int last_pos = hist + t0 + t_count - 1;
+    const int t0 = blk * 2 * tokens_per_tile;
     int kv_begin = 0;
     if (window > 0) kv_begin = (max(0, hist + t0 - window + 1) / KEYS) * KEYS;
-    const int kv_end = last_pos + 1;
-    const int n_iter = active ? (kv_end - kv_begin + KEYS - 1) / KEYS : 0;
+    // Per row tile: its first new row, how many it has, and how many key stages reach its last row.
+    int tile_t0[2], tile_rows[2], tile_iters[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        tile_t0[t] = t0 + t * tokens_per_tile;
+        const int count = active ? max(0, min(tokens_per_tile, n_q - tile_t0[t])) : 0;
+        tile_rows[t] = count * ratio;
+        tile_iters[t] = count > 0 ? (hist + tile_t0[t] + count - kv_begin + KEYS - 1) / KEYS : 0;
+    }
+    const int last_tile = tile_iters[1] > 0 ? 1 : 0;                 // the later rows see the most keys
+    const int n_iter = tile_iters[last_tile];
+    const int kv_end = hist + min(n_q, t0 + 2 * tokens_per_tile);
 
     if (warp == 0) {
-        if (n_iter > 0 && tc::elect_one()) {
-            // Q: rows [token][head of the group], both 64-column halves, one box.
-            tc::mbar_expect_tx(q_full, (uint32_t)OPERAND_BYTES);
-            tc::tma_load_5d(smem + SMEM_Q, &q_map, 0, 0, q0 + t0, 0, g, q_full);
+        if (n_iter > 0) {
+            if (lane == 0) {
+                // Q: rows [token][head of the group], both 64-column halves, one box per row tile.
+                tc::mbar_expect_tx(q_full, (uint32_t)((last_tile + 1) * OPERAND_BYTES));
+                tc::tma_load_5d(smem + SMEM_Q, &q_map, 0, 0, q0 + tile_t0[0], 0, g, q_full);
+                if (last_tile) tc::tma_load_5d(smem + SMEM_Q + OPERAND_BYTES, &q_map, 0, 0, q0 + tile_t0[1], 0, g, q_full);
+            }
+            // Lane = (keys or values, page of the stage, half of the head): one copy of 16 slots x 64 columns each.
+            const int plane = lane >> 4, p = (lane >> 1) & 7, half = lane & 1;
+            uint64_t* full = plane ? v_full : k_full;
+            uint64_t* empty = plane ? v_empty : k_empty;
             const int* table = block_tables + (size_t)r * table_stride + kv_begin / PAGE;
             const int n_pages = (kv_end - kv_begin + PAGE - 1) / PAGE;
-            // The page ids of a stage are read one stage ahead (the copies' memory clobber keeps the compiler from
-            // moving loads across them, and a table load is a round trip to L2 the copies must not wait for).
-            int ids[PAGES_PER_STAGE], ids_next[PAGES_PER_STAGE];
-#pragma unroll
-            for (int p = 0; p < PAGES_PER_STAGE; ++p) ids_next[p] = p < n_pages ? table[p] : 0;
+            // A stage's page id is read one stage ahead, so the table's latency is off the copies' path.
+            int id_next = p < n_pages ? table[p] : 0;
             for (int j = 0; j < n_iter; ++j) {
                 const int st = j % KV_STAGES;
                 const uint32_t ph = ((uint32_t)(j / KV_STAGES) & 1u) ^ 1u;
                 const int here = min(PAGES_PER_STAGE, n_pages - j * PAGES_PER_STAGE);
-                uint8_t* kbase = smem + SMEM_KV + st * STAGE_BYTES;
-#pragma unroll
-                for (int p = 0; p < PAGES_PER_STAGE; ++p) {
-                    ids[p] = ids_next[p];
-                    const int nxt = (j + 1) * PAGES_PER_STAGE + p;
-                    ids_next[p] = nxt < n_pages ? table[nxt] : 0;
-                }
-                // Keys first (their slot is free as soon as Q K^T of the tile two back has run), then values.
-                if (!tc::mbar_wait(&k_empty[st], ph, abort_flag, error_word, ERR_TCA_PRODUCER)) break;
-                tc::mbar_expect_tx(&k_full[st], (uint32_t)(here * PAGE * D * 2));
-#pragma unroll
-                for (int p = 0; p < PAGES_PER_STAGE; ++p) {
-                    if (p >= here) break;
-#pragma unroll
-                    for (int half = 0; half < 2; ++half)
-                        tc::tma_load_5d(kbase + half * HALF_BYTES + p * PAGE * 128, &cache_map, 0, 0, half, g, ids[p] * 2,
-                                        &k_full[st]);
-                }
-                if (!tc::mbar_wait(&v_empty[st], ph, abort_flag, error_word, ERR_TCA_PRODUCER)) break;
-                tc::mbar_expect_tx(&kv_full[st], (uint32_t)(here * PAGE * D * 2));
-#pragma unroll
-                for (int p = 0; p < PAGES_PER_STAGE; ++p) {
-                    if (p >= here) break;
-#pragma unroll
-                    for (int half = 0; half < 2; ++half)
-                        tc::tma_load_5d(kbase + OPERAND_BYTES + half * HALF_BYTES + p * PAGE * 128, &cache_map, 0, 0, half,
-                                        g, ids[p] * 2 + 1, &kv_full[st]);
-                }
+                const int id = id_next;
+                const int nxt = (j + 1) * PAGES_PER_STAGE + p;
+                id_next = nxt < n_pages ? table[nxt] : 0;
+                if (!tc::mbar_wait(&empty[st], ph, abort_flag, error_word, ERR_TCA_PRODUCER)) break;
+                if ((lane & 15) == 0) tc::mbar_expect_tx(&full[st], (uint32_t)(here * PAGE * D * 2));
+                if (p < here)
+                    tc::tma_load_5d(smem + SMEM_KV + st * STAGE_BYTES + plane * OPERAND_BYTES + half * HALF_BYTES + p * PAGE * 128,
+                                    &cache_map, 0, 0, half, g, id * 2 + plane, &full[st]);
             }
         }
     } else if (warp == 1) {
         if (n_iter > 0 && tc::elect_one()) {
             bool ok = tc::mbar_wait(q_full, 0, abort_flag, error_word, ERR_TCA_MMA);
-            const uint32_t q_addr = tc::smem_u32(smem + SMEM_Q), p_addr = tc::smem_u32(smem + SMEM_P);
-            auto issue_pv = [&](int i) -> bool {
-                const int bi = i & 1, st = i % KV_STAGES;
-                if (!tc::mbar_wait(&kv_full[st], (uint32_t)(i / KV_STAGES) & 1u, abort_flag, error_word, ERR_TCA_MMA)) return false;
-                if (!tc::mbar_wait(&p_full[bi], (uint32_t)(i / 2) & 1u, abort_flag, error_word, ERR_TCA_MMA)) return false;
-                if (!tc::mbar_wait(&o_empty[bi], ((uint32_t)(i / 2) & 1u) ^ 1u, abort_flag, error_word, ERR_TCA_MMA)) return false;
-                tc::tc_fence_after();
-                const uint32_t v_addr = tc::smem_u32(smem + SMEM_KV + st * STAGE_BYTES + OPERAND_BYTES);
-#pragma unroll
-                for (int kk = 0; kk < KEYS / 16; ++kk) {
-                    const uint64_t da = tc::smem_desc_k_sw128(p_addr + bi * OPERAND_BYTES + (kk >> 2) * HALF_BYTES + (kk & 3) * 32);
-                    const uint64_t db = smem_desc_mn_sw128(v_addr + kk * 16 * 128, HALF_BYTES);
-                    tc::mma_bf16_ss(tmem_base + 2 * KEYS + bi * D, da, db, IDESC_PV, kk > 0 ? 1u : 0u);
-                }
-                tc::mma_commit(&o_full[bi]);
-                tc::mma_commit(&p_empty[bi]);
-                tc::mma_commit(&v_empty[st]);
-                return true;
-            };
-            for (int j = 0; j < n_iter && ok; ++j) {
-                const int b = j & 1, st = j % KV_STAGES;
-                ok = tc::mbar_wait(&k_full[st], (uint32_t)(j / KV_STAGES) & 1u, abort_flag, error_word, ERR_TCA_MMA) &&
-                     tc::mbar_wait(&s_empty[b], ((uint32_t)(j / 2) & 1u) ^ 1u, abort_flag, error_word, ERR_TCA_MMA);
-                if (!ok) break;
-                tc::tc_fence_after();
-                const uint32_t k_addr = tc::smem_u32(smem + SMEM_KV + st * STAGE_BYTES);
+            // S of tile t = Q_t K_j^T.  The products of one thread run in the order they are issued, so this
+            // one, issued after P V of (t, j - 1), also finds that product done with the columns it writes.
+            auto issue_qk = [&](int t, int j) {
+                const uint32_t q_addr = tc::smem_u32(smem + SMEM_Q + t * OPERAND_BYTES);
+                const uint32_t k_addr = tc::smem_u32(smem + SMEM_KV + (j % KV_STAGES) * STAGE_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-                    tc::mma_bf16_ss(tmem_base + b * KEYS, tc::smem_desc_k_sw128(q_addr + off),
+                    tc::mma_bf16_ss(tmem_base + t * KEYS, tc::smem_desc_k_sw128(q_addr + off),
                                     tc::smem_desc_k_sw128(k_addr + off), IDESC_QK, kk > 0 ? 1u : 0u);
                 }
-                tc::mma_commit(&s_full[b]);
-                tc::mma_commit(&k_empty[st]);
-                if (j >= 1) ok = issue_pv(j - 1);
-            }
-            if (ok) issue_pv(n_iter - 1);
-        }
-    } else if (n_iter > 0) {
-        // ---- two threads per query row: warp s serves rows 32 (s % 4) .. + 31, columns 64 (s / 4) .. + 63
-        const int sw = warp - 2;
-        const int quarter = warp & 3, half = sw >> 2;
-        const int row = quarter * 32 + lane;
-        const bool valid = row < M;
-        const int ti = t0 + min(row, M - 1) / ratio;
-        const int pos = hist + ti;
-        const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        constexpr int HC = 64;                                   // columns per thread
-        float o[HC];
+                tc::mma_commit(&s_full[t]);
+            };
+            // O of tile t += P V_j, P from the tile's tensor-memory columns.
+            auto issue_pv = [&](int t, int j) -> bool {
+                const int st = j % KV_STAGES;
+                if (!tc::mbar_wait(&v_full[st], (uint32_t)(j / KV_STAGES) & 1u, abort_flag, error_word, ERR_TCA_MMA)) return false;
+                if (!tc::mbar_wait(&p_full[t], (uint32_t)j & 1u, abort_flag, error_word, ERR_TCA_MMA)) return false;
+                tc::tc_fence_after();
+                const uint32_t v_addr = tc::smem_u32(smem + SMEM_KV + st * STAGE_BYTES + OPERAND_BYTES);
 #pragma unroll
-        for (int d = 0; d < HC; ++d) o[d] = 0.0f;
-        float m_run = -INFINITY, l_run = 0.0f, alpha_pending = 0.0f;
-        bool ok = true;
-
-        auto accumulate = [&](int i) -> bool {
-            const int bi = i & 1;
-            if (!tc::mbar_wait(&o_full[bi], (uint32_t)(i / 2) & 1u, abort_flag, error_word, ERR_TCA_SOFTMAX)) return false;
-            tc::tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < HC; c += 32) {
-                uint32_t v[32];
-                tc::tmem_ld_32x32(tmem_base + 2 * KEYS + bi * D + half * HC + c + lane_addr, v);
-                tc::tmem_wait_ld();
-#pragma unroll
-                for (int k = 0; k < 32; ++k) o[c + k] = fmaf(o[c + k], alpha_pending, __uint_as_float(v[k]));
-            }
-            tc::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) tc::mbar_arrive(&o_empty[bi]);
-            return true;
-        };
-
-        for (int j = 0; j < n_iter; ++j) {
-            const int b = j & 1;
-            const int key0 = kv_begin + j * KEYS + half * HC;
-            if (ok) ok = tc::mbar_wait(&s_full[b], (uint32_t)(j / 2) & 1u, abort_flag, error_word, ERR_TCA_SOFTMAX);
-            tc::tc_fence_after();
-            const bool need_mask = key0 + HC - 1 > pos || key0 < lo;
-            // ---- this half's raw scores (kept in registers) and their maximum; masked ones become -inf.
-            // The scale is positive, so it is applied after the maximum and folded into the exponent's
-            // multiply-add: one instruction per score here, three in the pass below.
-            float sc[HC];
-            float rowmax = -INFINITY;
+                for (int kk = 0; kk < KEYS / 16; ++kk)
+                    tc::mma_bf16_ts(tmem_base + TMEM_O + t * D, tmem_base + t * KEYS + kk * 8,
+                                    smem_desc_mn_sw128(v_addr + kk * 16 * 128, HALF_BYTES), IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
+                return true;
+            };
+            if (ok) ok = tc::mbar_wait(&k_full[0], 0, abort_flag, error_word, ERR_TCA_MMA);
             if (ok) {
-#pragma unroll
-                for (int c = 0; c < HC; c += 32) {
-                    uint32_t v[32];
-                    tc::tmem_ld_32x32(tmem_base + b * KEYS + half * HC + c + lane_addr, v);
-                    tc::tmem_wait_ld();
-                    if (need_mask) {
-#pragma unroll
-                        for (int k = 0; k < 32; ++k) {
-                            const int key = key0 + c + k;
-                            sc[c + k] = (key > pos || key < lo) ? -INFINITY : __uint_as_float(v[k]);
-                            rowmax = fmaxf(rowmax, sc[c + k]);
-                        }
+                tc::tc_fence_after();
+                for (int t = 0; t <= last_tile; ++t) issue_qk(t, 0);
+                tc::mma_commit(&k_empty[0]);
+            }
+            for (int j = 0; j < n_iter && ok; ++j) {
+                for (int t = 0; t <= last_tile && ok; ++t) {
+                    if (j >= tile_iters[t]) continue;
+                    ok = issue_pv(t, j);
+                    if (!ok) break;
+                    if (t == last_tile) tc::mma_commit(&v_empty[j % KV_STAGES]);
+                    if (j + 1 < tile_iters[t]) {
+                        const int st = (j + 1) % KV_STAGES;
+                        ok = tc::mbar_wait(&k_full[st], (uint32_t)((j + 1) / KV_STAGES) & 1u, abort_flag, error_word, ERR_TCA_MMA);
+                        if (!ok) break;
+                        tc::tc_fence_after();
+                        issue_qk(t, j + 1);
+                        if (t == last_tile) tc::mma_commit(&k_empty[st]);
                     } else {
-#pragma unroll
-                        for (int k = 0; k < 32; ++k) {
-                            sc[c + k] = __uint_as_float(v[k]);
-                            rowmax = fmaxf(rowmax, sc[c + k]);
-                        }
+                        tc::mma_commit(&s_full[t]);          // the tile's output is complete
                     }
                 }
             }
-            rowmax *= scale_log2;
-            // S has been read: the tensor core may write the tile after next into it.
-            tc::tc_fence_before();
-            __syncwarp();
-            if (lane == 0 && ok) tc::mbar_arrive(&s_empty[b]);
-            // ---- the row's maximum over both halves (every softmax thread comes here, also after a failed wait)
-            half_max[half * ROWS + row] = rowmax;
-            asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_WARPS * 32) : "memory");
-            rowmax = fmaxf(rowmax, half_max[(half ^ 1) * ROWS + row]);
-            asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_WARPS * 32) : "memory");
-            if (!ok) continue;
-            const float m_new = fmaxf(m_run, rowmax);
-            const float alpha = m_new == -INFINITY ? 1.0f : exp2f(m_run - m_new);
-            const float base = m_new == -INFINITY ? 0.0f : m_new;
-            m_run = m_new;
-            // ---- P = 2^(s - m) as bfloat16 into the operand layout; P V of the tile before must have read P
-            ok = tc::mbar_wait(&p_empty[b], ((uint32_t)(j / 2) & 1u) ^ 1u, abort_flag, error_word, ERR_TCA_SOFTMAX);
-            if (!ok) continue;
-            float rowsum = 0.0f;
-            uint8_t* p_row = smem + SMEM_P + b * OPERAND_BYTES + half * HALF_BYTES + row * 128;
-#pragma unroll
-            for (int c8 = 0; c8 < HC / 8; ++c8) {
-                uint32_t packed[4];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const float p0 = fast_exp2(fmaf(sc[c8 * 8 + 2 * k], scale_log2, -base));
-                    const float p1 = fast_exp2(fmaf(sc[c8 * 8 + 2 * k + 1], scale_log2, -base));
-                    rowsum += p0 + p1;
-                    packed[k] = attn::pack_bf16(p0, p1);
-                }
-                *reinterpret_cast<uint4*>(p_row + ((c8 ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            }
-            l_run = l_run * alpha + rowsum;
-            tc::fence_proxy_async();          // the tensor core reads P through the async proxy
-            __syncwarp();
-            if (lane == 0) tc::mbar_arrive(&p_full[b]);
-            // ---- fold the tile before into the running output while this tile's P V runs
-            if (j >= 1) ok = accumulate(j - 1);
-            alpha_pending = alpha;
         }
-        if (ok) ok = accumulate(n_iter - 1);
-        // The row's sum over both halves.
-        half_max[half * ROWS + row] = l_run;
-        asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_WARPS * 32) : "memory");
-        const float l_total = l_run + half_max[(half ^ 1) * ROWS + row];
-        if (ok && valid) {
-            const float inv = 1.0f / l_total;
-            __nv_bfloat16* dst = out + ((size_t)(q0 + ti) * heads + g * ratio + row % ratio) * D + half * HC;
+    } else {
+        // ---- one thread per query row: warps 2-5 serve tile 0, warps 6-9 tile 1; a warp may touch the
+        // tensor-memory lanes 32 (warp % 4) .. + 31
+        const int t = (warp - 2) / TILE_WARPS;
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const int M = tile_rows[t], iters = tile_iters[t];
+        if (iters > 0) {
+            const bool valid = row < M;
+            const int ti = tile_t0[t] + min(row, M - 1) / ratio;
+            const int pos = hist + ti;
+            const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+            const uint32_t s_addr = tmem_base + t * KEYS + ((uint32_t)(quarter * 32) << 16);
+            const uint32_t o_addr = tmem_base + TMEM_O + t * D + ((uint32_t)(quarter * 32) << 16);
+            float m_used = -INFINITY, l_run = 0.0f;
+            bool ok = true;
+            for (int j = 0; j < iters; ++j) {
+                ok = tc::mbar_wait(&s_full[t], (uint32_t)j & 1u, abort_flag, error_word, ERR_TCA_SOFTMAX);
+                if (!ok) break;
+                tc::tc_fence_after();
+                const int key0 = kv_begin + j * KEYS;
+                const bool need_mask = key0 + KEYS - 1 > pos || key0 < lo;
+                // ---- the row's raw scores (kept in registers) and their maximum; masked ones become -inf.
+                // The scale is positive, so it is applied after the maximum and folded into the exponent's
+                // multiply-add.
+                uint32_t sc[KEYS];
 #pragma unroll
-            for (int d = 0; d < HC; d += 8) {
-                uint4 val = make_uint4(attn::pack_bf16(o[d] * inv, o[d + 1] * inv), attn::pack_bf16(o[d + 2] * inv, o[d + 3] * inv),
-                                       attn::pack_bf16(o[d + 4] * inv, o[d + 5] * inv), attn::pack_bf16(o[d + 6] * inv, o[d + 7] * inv));
-                *reinterpret_cast<uint4*>(dst + d) = val;
+                for (int c = 0; c < KEYS; c += 32) tc::tmem_ld_32x32(s_addr + c, *reinterpret_cast<uint32_t(*)[32]>(&sc[c]));
+                tc::tmem_wait_ld();
+                if (need_mask) {
+#pragma unroll
+                    for (int k = 0; k < KEYS; ++k) {
+                        const int key = key0 + k;
+                        if (key > pos || key < lo) sc[k] = __float_as_uint(-INFINITY);
+                    }
+                }
+                // Four running maxima, three inputs an instruction: no long chain of dependent instructions.
+                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int k = 0; k < KEYS; k += 8) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        mx[u] = max3(mx[u], __uint_as_float(sc[k + 2 * u]), __uint_as_float(sc[k + 2 * u + 1]));
+                }
+                const float rowmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+                const float cand = fmaxf(m_used, rowmax * scale_log2);
+                // The maximum the exponent uses follows when, for some row of the warp, the true one is far ahead.
+                const bool raise = j > 0 && __any_sync(0xffffffffu, cand > m_used + RAISE);
+                const float factor = !raise || cand == -INFINITY ? 1.0f : exp2f(m_used - cand);
+                if (j == 0 || raise) m_used = cand;
+                const float base = m_used == -INFINITY ? 0.0f : m_used;
+                // ---- P = 2^(s - m) as bfloat16, two keys to a column, over the scores' first 64 columns
+                const uint64_t scale2 = pack2(scale_log2, scale_log2), minus_base2 = pack2(-base, -base);
+                uint64_t sum2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
+#pragma unroll
+                for (int c = 0; c < KEYS; c += 32) {
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) {
+                        const uint64_t x = fma2(pack2(__uint_as_float(sc[c + 2 * k]), __uint_as_float(sc[c + 2 * k + 1])),
+                                                scale2, minus_base2);
+                        float x0, x1;
+                        unpack2(x, x0, x1);
+                        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                        sum2[k & 1] = add2(sum2[k & 1], pack2(p0, p1));
+                        packed[k] = attn::pack_bf16(p0, p1);
+                    }
+                    tc::tmem_st_32x16(s_addr + c / 2, packed);
+                }
+                float r0, r1, r2, r3;
+                unpack2(sum2[0], r0, r1);
+                unpack2(sum2[1], r2, r3);
+                const float rowsum = (r0 + r1) + (r2 + r3);
+                if (raise) {
+                    // The row's output so far was summed against the old maximum.  P V of the stage before has
+                    // finished (this stage's scores were written after it) and this stage's has not been
+                    // issued (it waits for the arrival below), so O may be rewritten here.
+#pragma unroll
+                    for (int c = 0; c < D; c += 32) {
+                        uint32_t v[32];
+                        tc::tmem_ld_32x32(o_addr + c, v);
+                        tc::tmem_wait_ld();
+#pragma unroll
+                        for (int k = 0; k < 32; ++k) v[k] = __float_as_uint(__uint_as_float(v[k]) * factor);
+                        tc::tmem_st_32x32(o_addr + c, v);
+                    }
+                    l_run *= factor;
+                }
+                l_run += rowsum;
+                tc::tmem_wait_st();
+                tc::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive(&p_full[t]);
+            }
+            // ---- O / l once the last P V has run
+            if (ok) ok = tc::mbar_wait(&s_full[t], (uint32_t)iters & 1u, abort_flag, error_word, ERR_TCA_SOFTMAX);
+            if (ok) {
+                tc::tc_fence_after();
+                const float inv = 1.0f / l_run;
+                __nv_bfloat16* dst = out + ((size_t)(q0 + ti) * heads + g * ratio + row % ratio) * D;
+#pragma unroll
+                for (int c = 0; c < D; c += 32) {
+                    uint32_t v[32];
+                    tc::tmem_ld_32x32(o_addr + c, v);
+                    tc::tmem_wait_ld();
+                    if (valid) {
+#pragma unroll
+                        for (int d = 0; d < 32; d += 8) {
+                            const uint4 val = make_uint4(
+                                attn::pack_bf16(__uint_as_float(v[d]) * inv, __uint_as_float(v[d + 1]) * inv),
+                                attn::pack_bf16(__uint_as_float(v[d + 2]) * inv, __uint_as_float(v[d + 3]) * inv),
+                                attn::pack_bf16(__uint_as_float(v[d + 4]) * inv, __uint_as_float(v[d + 5]) * inv),
+                                attn::pack_bf16(__uint_as_float(v[d + 6]) * inv, __uint_as_float(v[d + 7]) * inv));
+                            *reinterpret_cast<uint4*>(dst + c + d) = val;
+                        }
+                    }
+                }
             }
         }
     }
@@ -425,8 +446,8 @@ LLMX_EXPORT int llmx_attn_prefill_tc(const void* cache_map, const void* q, void*
     }
     CUtensorMap q_map;
     if (int e = make_q_map(&q_map, q, (uint64_t)total_rows, heads, kv_heads)) return e;
-    const int tokens_per_tile = ROWS / (heads / kv_heads);
-    dim3 grid((max_rows + tokens_per_tile - 1) / tokens_per_tile, kv_heads, n_req);
+    const int tokens_per_block = 2 * ROWS / (heads / kv_heads);
+    dim3 grid((max_rows + tokens_per_block - 1) / tokens_per_block, kv_heads, n_req);
     launch_kernel(attn_prefill_tc_kernel, grid, dim3(THREADS), (size_t)SMEM_BYTES, stream, q_map,
                   *(const CUtensorMap*)cache_map, (__nv_bfloat16*)out, req_list, row_start, row_count, history,
                   block_tables, table_stride, heads, kv_heads, window, scale * attn::LOG2E, error_word);
