@@ -1,16 +1,19 @@
-"""A decode session: a fixed set of live requests, one token each per step, recorded once and replayed.
+"""Decode sessions and recordings: one token each for a set of live requests, recorded once and replayed.
 
 This is the inner loop of generation once prompts are in the cache.  The work of such a step has
-the same shape every time (same rows, same kernels, same grids), so the session records it in a
-CUDA graph and replays it: a step then costs one host-to-device copy of the step's metadata and
-one graph launch instead of several hundred kernel launches.  What the session runs is the
-model's own forward pass over the engine's own cache; what changes from step to step (token ids,
-positions, cache slots, block tables, the keys per range of the split-KV kernel) lives in one
-device buffer the kernels read.
+the same shape every time (same rows, same kernels, same grids), so it is recorded in a CUDA graph
+and replayed: a step then costs one host-to-device copy of the step's metadata and one graph
+launch instead of several hundred kernel launches.  What is recorded is the model's own forward
+pass over the engine's own cache; what changes from step to step (token ids, positions, cache
+slots, block tables, the keys per range of the split-KV kernel) lives in one device buffer the
+kernels read.
 
-The graph is recorded again when a request outgrows the block-table width or the key ranges it
-was recorded for.  The first step of a session always runs through `Engine.step` (it also warms
-the kernels up).
+A recording depends on two numbers only: how many requests decode, and how many tokens of context
+its block tables have room for (in steps of `ROOM_STEP`).  The engine keeps the recordings it has
+made, so a session over other requests -- one has finished, another has joined -- finds its
+recording ready; a session only keeps the host's copy of its requests' metadata.  The first
+decode step at a new batch size runs through `Engine.step`, which also loads and warms the
+kernels that the recording will hold.
 """
 from __future__ import annotations
 
@@ -22,25 +25,57 @@ import torch
 from ..parts.base import GroupView, StepBatch
 from .engine import Engine, StepEntry, StepError, _pad4
 
+ROOM_STEP = 2048           # a recording's room for context is a multiple of this
+MAX_RECORDINGS = 32        # recordings an engine keeps (least recently used goes first)
 
-class DecodeSession:
-    GROWTH = 2048          # tokens of room a recording leaves before it must be made again
 
-    def __init__(self, engine: Engine, request_ids: Sequence[Hashable], use_graph: bool = True):
-        self.engine = engine
-        self.request_ids = list(request_ids)
-        self.use_graph = use_graph and engine.model.recordable
-        self.h2d_bytes_per_step = 0
-        self.graph_launches = 0          # kernels one replay launches
-        self._graph: Optional[torch.cuda.CUDAGraph] = None
-        self._steps = 0
-        for rid in self.request_ids:
-            if rid not in engine.cache.live:
-                raise StepError(f"request {rid!r} is not live; a decode session continues requests that are")
+def room_for(context: int, max_positions: int) -> int:
+    """Tokens of context the recording for a step at `context` tokens has room for: at least one
+    `ROOM_STEP` ahead, so that a session changes recordings rarely."""
+    return min((context // ROOM_STEP + 2) * ROOM_STEP, max(max_positions, 1))
 
-    # -- layout of the static metadata buffer -----------------------------------------------
-    def _layout(self, max_pages: List[int]):
-        b = len(self.request_ids)
+
+class DecodeRecording:
+    """The graph of one decode step for `b` requests with room for `room` tokens of context each, and the
+    buffers it reads its metadata from."""
+
+    def __init__(self, engine: Engine, b: int, room: int):
+        from .. import ops, ops_attn
+        eng = self.engine = engine
+        self.b, self.room = b, room
+        self.max_pages = [max(1, -(-room // g.page_size)) for g in eng.cache.groups]
+        self.sizes, self.offsets, self.total = self._layout(b, self.max_pages)
+        # The host may run several steps ahead of the device: a ring of pinned buffers, each reused only
+        # once the copy that read it has finished.
+        self._ring = [torch.zeros(self.total, dtype=torch.int32, pin_memory=True) for _ in range(4)]
+        self._ring_events = [None] * len(self._ring)
+        self._ring_at = 0
+        self._dev = torch.zeros(self.total, dtype=torch.int32, device=eng.device)
+        # Key ranges of the split-KV kernel: the grid is fixed by the recording, the keys per range are data.
+        kv_heads = max((g.spec.kv_heads for g in eng.cache.groups), default=1)
+        self.splits, _ = ops_attn.decode_schedule(b, kv_heads, room)
+
+        def dsec(i):
+            return self._dev[self.offsets[i]:self.offsets[i] + self.sizes[i]]
+        groups = [GroupView(dsec(10 + 2 * g).view(b, self.max_pages[g]), dsec(11 + 2 * g), grp.page_size)
+                  for g, grp in enumerate(eng.cache.groups)]
+        step = StepBatch(rows=b, requests=b, token_ids=dsec(0), positions=dsec(1), row_request=dsec(2),
+                         row_start=dsec(3), row_count=dsec(4), history=dsec(5), state_slots=dsec(6),
+                         logit_rows=dsec(7), groups=groups, caches=eng.cache, host_row_start=list(range(b)),
+                         host_row_count=[1] * b, host_history=[0] * b, max_row_count=1, max_context=room)
+        step.extras["decode_schedule"] = (self.splits, 64, dsec(9))
+        step.extras["recorded"] = True
+        for ratio_rows in range(1, 17):       # every mixer's list of "requests with few rows" is all of them
+            step.extras[("attn_lists", ratio_rows)] = (dsec(8)[:b], b, room, 1, dsec(8)[b:b], 0, 0)
+        self._step = step
+        self._graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count()
+        with torch.cuda.graph(self._graph):
+            self.logits = eng.model.forward(step)
+        self.graph_launches = ops.launch_count() - before
+
+    @staticmethod
+    def _layout(b: int, max_pages: List[int]):
         sizes = [b, b, b, b, b, b, b, b, b + 1, 1]    # tokens, positions, row_request, row_start, row_count, history,
         #                                               state slots, logit rows, request list, keys per range
         for mp in max_pages:
@@ -51,11 +86,59 @@ class DecodeSession:
             at += _pad4(s)
         return sizes, offsets, at
 
+    def chunk(self, ctx: int) -> int:
+        return max(64, -(-(-(-ctx // 64)) // self.splits) * 64)
+
+    def launch(self, fill) -> torch.Tensor:
+        """Copy the step's metadata (written into a pinned buffer by `fill(array)`) and replay the graph."""
+        slot = self._ring_at
+        self._ring_at = (slot + 1) % len(self._ring)
+        if self._ring_events[slot] is not None:
+            self._ring_events[slot].synchronize()
+        host = self._ring[slot]
+        fill(host.numpy())
+        self._dev.copy_(host, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._ring_events[slot] = ev
+        self._graph.replay()
+        return self.logits
+
+
+def recording_of(engine: Engine, b: int, room: int, make: bool = True) -> Optional[DecodeRecording]:
+    """The engine's recording for (`b`, `room`), made now if there is none (unless `make` is false)."""
+    kept = engine.decode_recordings
+    rec = kept.get((b, room))
+    if rec is not None:
+        kept.move_to_end((b, room))
+        return rec
+    if not make:
+        return None
+    rec = DecodeRecording(engine, b, room)
+    kept[(b, room)] = rec
+    while len(kept) > MAX_RECORDINGS:
+        kept.popitem(last=False)
+    return rec
+
+
+class DecodeSession:
+    def __init__(self, engine: Engine, request_ids: Sequence[Hashable], use_graph: bool = True):
+        self.engine = engine
+        self.request_ids = list(request_ids)
+        self.use_graph = use_graph and engine.model.recordable
+        self.h2d_bytes_per_step = 0
+        self.graph_launches = 0          # kernels one replay launches
+        self._rec: Optional[DecodeRecording] = None
+        for rid in self.request_ids:
+            if rid not in engine.cache.live:
+                raise StepError(f"request {rid!r} is not live; a decode session continues requests that are")
+
     def _fill(self, host: np.ndarray, tokens: Sequence[int], caches, chunk: int) -> None:
         """Write the step's metadata into `host`.  The master copy is kept between steps and only what a step
         changes is touched: tokens, positions, slots, and a block-table entry when a request enters a new page."""
         b = len(caches)
-        sizes, offsets = self._sizes, self._offsets
+        rec = self._rec
+        sizes, offsets = rec.sizes, rec.offsets
         m = self._master
 
         def sec(i):
@@ -76,7 +159,7 @@ class DecodeSession:
         sec(9)[0] = chunk
         for g, grp in enumerate(self.engine.cache.groups):
             ps = grp.page_size
-            mp = self._max_pages[g]
+            mp = rec.max_pages[g]
             bt = sec(10 + 2 * g).reshape(b, mp)
             sl = sec(11 + 2 * g)
             seen = self._pages_seen[g]
@@ -88,62 +171,22 @@ class DecodeSession:
                 sl[r] = pages[hist[r] // ps] * ps + hist[r] % ps
         host[:] = m
 
-    def _record(self, caches) -> None:
-        from .. import ops, ops_attn
-        eng = self.engine
-        b = len(caches)
-        ctx_now = max(rc.length + rc.pending for rc in caches)
-        room = min(ctx_now + self.GROWTH, eng.max_positions)
-        self._max_pages = [max(1, -(-room // g.page_size)) for g in eng.cache.groups]
-        self._sizes, self._offsets, total = self._layout(self._max_pages)
-        # The host may run several steps ahead of the device: a ring of pinned buffers, each reused only
-        # once the copy that read it has finished.
-        self._ring = [torch.zeros(total, dtype=torch.int32, pin_memory=True) for _ in range(4)]
-        self._ring_events = [None] * len(self._ring)
-        self._ring_at = 0
-        self._dev = torch.zeros(total, dtype=torch.int32, device=eng.device)
-        self._master = np.zeros(total, dtype=np.int32)
-        self._master_ready = False
-        self._room = room
-        # Key ranges of the split-KV kernel: the grid is fixed by the recording, the keys per range are data.
-        kv_heads = max((g.spec.kv_heads for g in eng.cache.groups), default=1)
-        self._splits, _ = ops_attn.decode_schedule(b, kv_heads, room)
-
-        def dsec(i):
-            return self._dev[self._offsets[i]:self._offsets[i] + self._sizes[i]]
-        groups = [GroupView(dsec(10 + 2 * g).view(b, self._max_pages[g]), dsec(11 + 2 * g), grp.page_size)
-                  for g, grp in enumerate(eng.cache.groups)]
-        step = StepBatch(rows=b, requests=b, token_ids=dsec(0), positions=dsec(1), row_request=dsec(2),
-                         row_start=dsec(3), row_count=dsec(4), history=dsec(5), state_slots=dsec(6),
-                         logit_rows=dsec(7), groups=groups, caches=eng.cache, host_row_start=list(range(b)),
-                         host_row_count=[1] * b, host_history=[0] * b, max_row_count=1, max_context=room)
-        chunk_dev = dsec(9)
-        step.extras["decode_schedule"] = (self._splits, 64, chunk_dev)
-        step.extras["recorded"] = True
-        for ratio_rows in range(1, 17):       # every mixer's list of "requests with few rows" is all of them
-            step.extras[("attn_lists", ratio_rows)] = (dsec(8)[:b], b, room, 1, dsec(8)[b:b], 0, 0)
-        self._step = step
-        self._graph = torch.cuda.CUDAGraph()
-        before = ops.launch_count()
-        with torch.cuda.graph(self._graph):
-            self._logits = eng.model.forward(step)
-        self.graph_launches = ops.launch_count() - before
-
-    def _chunk(self, ctx: int) -> int:
-        return max(64, -(-(-(-ctx // 64)) // self._splits) * 64)
-
     def step(self, tokens: Sequence[int]) -> torch.Tensor:
         """Feed one token per request (in the session's order); float32 logits [requests, vocab] on the
         device, valid until the next step."""
         eng = self.engine
-        if len(tokens) != len(self.request_ids):
+        b = len(self.request_ids)
+        if len(tokens) != b:
             raise StepError("a decode step needs one token for every request of the session")
-        self._steps += 1
-        if not self.use_graph or self._steps == 1:
+        caches = [eng.cache.live[rid] for rid in self.request_ids]
+        ctx = max(rc.length + 1 for rc in caches)
+        room = room_for(ctx, eng.max_positions)
+        warmed = eng.decode_warmed
+        if not self.use_graph or (b not in warmed and recording_of(eng, b, room, make=False) is None):
             logits = eng.step([StepEntry(rid, [int(t)], [0]) for rid, t in zip(self.request_ids, tokens)])
+            warmed.add(b)
             self.h2d_bytes_per_step = eng.last_h2d_bytes
             return logits
-        caches = [eng.cache.live[rid] for rid in self.request_ids]
         for t, rc in zip(tokens, caches):
             if not 0 <= int(t) < eng.model.vocab_size:
                 raise StepError(f"token id {t} is outside the vocabulary of {eng.model.vocab_size}")
@@ -154,21 +197,13 @@ class DecodeSession:
             for rc in caches:
                 rc.prepare(1)
                 prepared.append(rc)
-            ctx = max(rc.length + 1 for rc in caches)
             with torch.cuda.device(eng.device):
-                if self._graph is None or ctx > self._room:
-                    self._record(caches)
-                slot = self._ring_at
-                self._ring_at = (slot + 1) % len(self._ring)
-                if self._ring_events[slot] is not None:
-                    self._ring_events[slot].synchronize()
-                host = self._ring[slot]
-                self._fill(host.numpy(), [int(t) for t in tokens], caches, self._chunk(ctx))
-                self._dev.copy_(host, non_blocking=True)
-                ev = torch.cuda.Event()
-                ev.record()
-                self._ring_events[slot] = ev
-                self._graph.replay()
+                rec = recording_of(eng, b, room)
+                if rec is not self._rec:
+                    self._rec = rec
+                    self._master = np.zeros(rec.total, dtype=np.int32)
+                    self._master_ready = False
+                logits = rec.launch(lambda host: self._fill(host, [int(t) for t in tokens], caches, rec.chunk(ctx)))
         except BaseException:
             for rc in prepared:
                 rc.abort()
@@ -177,11 +212,11 @@ class DecodeSession:
             rc.commit()
         eng.steps_run += 1
         from .. import ops
-        ops.count_launches(self.graph_launches)
-        self.h2d_bytes_per_step = self._dev.numel() * 4
-        return self._logits
+        self.graph_launches = rec.graph_launches
+        ops.count_launches(rec.graph_launches)
+        self.h2d_bytes_per_step = rec.total * 4
+        return logits
 
     def close(self) -> None:
-        self._graph = None
-        self._logits = None
-        self._step = None
+        """The session is over.  Its recording stays with the engine for the next session of its size."""
+        self._rec = None

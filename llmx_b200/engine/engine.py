@@ -15,6 +15,7 @@ Generation (`llmx_b200.engine.generate`), the scheduler, the command line and
 from __future__ import annotations
 
 from dataclasses import dataclass, field
+from collections import OrderedDict
 from typing import Dict, Hashable, List, Optional, Sequence
 
 import numpy as np
@@ -68,6 +69,10 @@ class Engine:
                                   options.max_requests, kv_dtype=self.precision.act, device=self.device)
         model.prepare(min(self.max_positions, max(options.kv_tokens, 1)), self.device)
         self.steps_run = 0
+        # Recorded decode steps by (requests, room for context), least recently used first, and the batch
+        # sizes whose kernels a plain step has already run (see decode_loop.py).
+        self.decode_recordings = OrderedDict()
+        self.decode_warmed = set()
         self.last_h2d_bytes = 0
 
     # -- construction ------------------------------------------------------------
