@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import ctypes
+import functools
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -73,14 +74,73 @@ def _schedule(m: int, n: int) -> int:
     return 1 if m <= STREAM_K_MAX_ROWS and -(-n // 128) < STREAM_K_MAX_TILES else 0
 
 
+_sm_count = 0
+
+
+def _sms() -> int:
+    global _sm_count
+    if not _sm_count:
+        _sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return _sm_count
+
+
+@functools.lru_cache(maxsize=None)
+def _plan(m: int, n: int, k: int, accumulate: bool, sms: int) -> Tuple[int, int, int]:
+    """(schedule, token tile, k ranges) for out[m, n] (+)= a[m, k] w[n, k]^T.
+
+    Few tokens: stream-K.  Else whole tiles, and the token tile and the number of k ranges are chosen so
+    that the tiles fill the SMs: with a few hundred tokens a [4096, 4096] weight makes 32 to 128 tiles,
+    which would leave most of the 148 SMs idle, while two to four k ranges (added with atomics) fill them.
+    The estimate below was fitted to timings of the layer's products at 96 to 2,048 tokens: a tile's time
+    is its bytes over what one SM takes in (110 GB/s) or its multiply-adds at the SM's share of the
+    tensor rate; atomics run beside the main loop at 500 G a second and show at the end of a block's
+    last tile; a stored output that is added to in pieces must be cleared first.
+    """
+    if _schedule(m, n) == 1:
+        return 1, 0, 1
+    n_tiles, k_blocks = -(-n // 128), -(-k // 64)
+    best = None
+    for bn in (128, 256):
+        if bn == 256 and m <= 128:
+            continue
+        m_tiles = -(-m // bn)
+        for splits in (1, 2, 3, 4):
+            if splits > k_blocks:
+                break
+            tiles = n_tiles * m_tiles * splits
+            waves = -(-tiles // sms)
+            kk = -(-k_blocks // splits) * 64
+            per_tile = max(kk * (128 + bn) * 2 / 110e3, 2.0 * 128 * bn * kk / 9.4e6)
+            t = waves * per_tile
+            if splits > 1:
+                t = max(t, m * n * splits / 500e3) + min(bn, m) * 128 / 8e3
+                if not accumulate:
+                    t += m * n * 4 / 5e6
+            t *= 1.0 + 0.03 * (splits - 1)
+            if best is None or t < best[0]:
+                best = (t, bn, splits)
+    return 0, best[1], best[2]
+
+
+def plan(m: int, n: int, k: int, accumulate: bool) -> Tuple[int, int, int]:
+    return _plan(m, n, k, bool(accumulate), _sms())
+
+
+def adds_pieces(m: int, n: int, k: int) -> bool:
+    """Whether a stored product of this shape adds its pieces into the output, which then must start as zeros."""
+    schedule, _, splits = plan(m, n, k, False)
+    return schedule == 1 or splits > 1
+
+
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
             wmap: Optional[WeightMap] = None, splits: Optional[int] = None, token_tile: int = 0,
             schedule: Optional[int] = None) -> torch.Tensor:
     """out (+)= a @ w.T; a [M, K] bfloat16, w [N, K] bfloat16, out float32 [M, N].
 
-    schedule 0 walks whole tiles (`splits` > 1 cuts K, only with accumulate); schedule 1 (stream-K) shares
-    out (tile, k block) units evenly and adds every piece with atomics, zeroing `out` first unless
-    accumulating.  By default few tokens take stream-K and many take tiles.
+    schedule 0 walks whole tiles (`splits` > 1 cuts K and adds the pieces with atomics); schedule 1
+    (stream-K) shares out (tile, k block) units evenly and adds every piece with atomics.  Whenever pieces
+    are added, `out` is zeroed first unless accumulating.  By default `plan` chooses: stream-K for few
+    tokens, else the token tile and k ranges that fill the SMs.
     """
     _cuda(a, w, out)
     m, k = a.shape
@@ -90,12 +150,15 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
     _need(w.shape[1] == k and tuple(out.shape) == (m, n), "gemm_tc: shapes do not fit")
     _need(k % 8 == 0, "gemm_tc: the input width must be a multiple of 8 (TMA row stride of 16 bytes)")
     wmap = wmap or weight_map(w)
+    if schedule is None and splits is None and token_tile == 0:
+        schedule, token_tile, splits = plan(m, n, k, accumulate)
     if schedule is None:
         schedule = _schedule(m, n) if splits is None else 0
     if splits is None:
         splits = 1
-    if schedule == 1 and not accumulate:
+    if (schedule == 1 or splits > 1) and not accumulate:
         out.zero_()
+        accumulate = True
     _check(_fn("gemm_tc", "llmx_gemm_tc")(ctypes.c_void_p(wmap.address), _ptr(a), _ptr(out), m, n, k,
                                           1 if accumulate else 0, splits, token_tile, schedule,
                                           _ptr(error_word(a.device)), _stream()), "gemm_tc")

@@ -50,7 +50,7 @@ class Linear:
         if not self.tensor_core:
             return False
         from .. import ops_tc
-        return ops_tc._schedule(rows, self.out_features) == 1
+        return ops_tc.adds_pieces(rows, self.out_features, self.in_features)
 
     def output_to_clear(self, rows: int, device) -> Optional[torch.Tensor]:
         """A fresh output for `rows` rows if the product wants it cleared by whoever runs before it
