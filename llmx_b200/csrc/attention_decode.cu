@@ -296,39 +296,70 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
         __syncthreads();
         if (is_last) {
             __threadfence();
-            // Weights of the ranges first (rows x ranges values through shared memory), then one pass over
-            // the partial outputs with every load independent of the others.
-            float* factor = (float*)tiles;                       // [MAX_ROWS][splits]
+            // One round trip to memory: every thread first asks for the maxima and sums of the ranges
+            // (rows x ranges pairs, to shared memory) and for its share of the partial outputs (to
+            // registers), and only then are the ranges' weights worked out and applied.
+            float* stats = (float*)tiles;                        // [MAX_ROWS][splits][2]: maximum, sum
+            constexpr int PER_THREAD = (MAX_ROWS * D + THREADS - 1) / THREADS;
+            constexpr int SPLITS_IN_REGS = 8;
+            float held[PER_THREAD][SPLITS_IN_REGS];
+            const bool in_regs = splits <= SPLITS_IN_REGS;
+            if (in_regs) {
+#pragma unroll
+                for (int i = 0; i < PER_THREAD; ++i) {
+                    const int idx = threadIdx.x + i * THREADS;
+                    if (idx < M * D) {
+                        const int row = idx / D, d = idx % D;
+                        const size_t out_row = (size_t)(q0 + row / ratio) * heads + g * ratio + row % ratio;
+                        const float* src = partial + out_row * splits * (D + 2) + d;
+#pragma unroll
+                        for (int s2 = 0; s2 < SPLITS_IN_REGS; ++s2)
+                            if (s2 < splits) held[i][s2] = __ldcg(src + (size_t)s2 * (D + 2));
+                    }
+                }
+            }
             for (int idx = threadIdx.x; idx < M * splits; idx += THREADS) {
                 const int row = idx / splits, s2 = idx % splits;
                 const size_t orow = (size_t)(q0 + row / ratio) * heads + g * ratio + row % ratio;
-                factor[row * splits + s2] = __ldcg(partial + (orow * splits + s2) * (D + 2) + D);
+                const float2 ml = __ldcg(reinterpret_cast<const float2*>(partial + (orow * splits + s2) * (D + 2) + D));
+                stats[2 * idx] = ml.x;
+                stats[2 * idx + 1] = ml.y;
             }
             __syncthreads();
-            float* row_scale = factor + MAX_ROWS * splits;       // [MAX_ROWS]: 1 / l, and the rows' maxima
+            float* row_scale = stats + 2 * MAX_ROWS * splits;    // [MAX_ROWS]: 1 / l
             if (threadIdx.x < M) {
                 const int row = threadIdx.x;
-                const size_t orow = (size_t)(q0 + row / ratio) * heads + g * ratio + row % ratio;
                 float mm = -INFINITY;
-                for (int s2 = 0; s2 < splits; ++s2) mm = fmaxf(mm, factor[row * splits + s2]);
+                for (int s2 = 0; s2 < splits; ++s2) mm = fmaxf(mm, stats[2 * (row * splits + s2)]);
                 float l = 0.0f;
                 for (int s2 = 0; s2 < splits; ++s2) {
-                    const float ms = factor[row * splits + s2];
+                    const float ms = stats[2 * (row * splits + s2)];
                     const float f = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
-                    factor[row * splits + s2] = f;
-                    l += __ldcg(partial + (orow * splits + s2) * (D + 2) + D + 1) * f;
+                    l += stats[2 * (row * splits + s2) + 1] * f;
+                    stats[2 * (row * splits + s2)] = f;          // the range's weight from here on
                 }
                 row_scale[row] = 1.0f / l;
             }
             __syncthreads();
-            for (int idx = threadIdx.x; idx < M * D; idx += THREADS) {
-                const int row = idx / D, d = idx % D;
-                const size_t out_row = (size_t)(q0 + row / ratio) * heads + g * ratio + row % ratio;
-                const float* src = partial + out_row * splits * (D + 2) + d;
-                float acc = 0.0f;
+#pragma unroll
+            for (int i = 0; i < PER_THREAD; ++i) {
+                const int idx = threadIdx.x + i * THREADS;
+                if (idx < M * D) {
+                    const int row = idx / D, d = idx % D;
+                    const size_t out_row = (size_t)(q0 + row / ratio) * heads + g * ratio + row % ratio;
+                    float acc = 0.0f;
+                    if (in_regs) {
+#pragma unroll
+                        for (int s2 = 0; s2 < SPLITS_IN_REGS; ++s2)
+                            if (s2 < splits) acc = fmaf(held[i][s2], stats[2 * (row * splits + s2)], acc);
+                    } else {
+                        const float* src = partial + out_row * splits * (D + 2) + d;
 #pragma unroll 8
-                for (int s2 = 0; s2 < splits; ++s2) acc = fmaf(__ldcg(src + (size_t)s2 * (D + 2)), factor[row * splits + s2], acc);
-                out[out_row * D + d] = __float2bfloat16_rn(acc * row_scale[row]);
+                        for (int s2 = 0; s2 < splits; ++s2)
+                            acc = fmaf(__ldcg(src + (size_t)s2 * (D + 2)), stats[2 * (row * splits + s2)], acc);
+                    }
+                    out[out_row * D + d] = __float2bfloat16_rn(acc * row_scale[row]);
+                }
             }
             if (threadIdx.x == 0) *counter = 0;      // ready for the next launch
         }

@@ -17,6 +17,7 @@ kernels that the recording will hold.
 """
 from __future__ import annotations
 
+import gc
 from typing import Hashable, List, Optional, Sequence
 
 import numpy as np
@@ -41,7 +42,7 @@ class DecodeRecording:
 
     def __init__(self, engine: Engine, b: int, room: int):
         from .. import ops, ops_attn
-        eng = self.engine = engine
+        eng = engine                     # not kept: the engine owns its recordings, not the other way round
         self.b, self.room = b, room
         self.max_pages = [max(1, -(-room // g.page_size)) for g in eng.cache.groups]
         self.sizes, self.offsets, self.total = self._layout(b, self.max_pages)
@@ -70,8 +71,17 @@ class DecodeRecording:
         self._step = step
         self._graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
-        with torch.cuda.graph(self._graph):
-            self.logits = eng.model.forward(step)
+        # Nothing may be freed on the device or in pinned memory while the stream is capturing, and Python's
+        # collector frees what it finds whenever it runs: it runs now, and not again until the capture is over.
+        gc.collect()
+        was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self._graph):
+                self.logits = eng.model.forward(step)
+        finally:
+            if was_enabled:
+                gc.enable()
         self.graph_launches = ops.launch_count() - before
 
     @staticmethod
