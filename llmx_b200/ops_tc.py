@@ -98,6 +98,8 @@ def _plan(m: int, n: int, k: int, accumulate: bool, sms: int) -> Tuple[int, int,
     """
     if _schedule(m, n) == 1:
         return 1, 0, 1
+    if m <= STREAM_K_MAX_ROWS:
+        return 0, 0, 1              # few tokens, plenty of weight tiles (the logits head): the narrowest token tile
     n_tiles, k_blocks = -(-n // 128), -(-k // 64)
     best = None
     for bn in (128, 256):

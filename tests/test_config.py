@@ -100,3 +100,22 @@ def test_registering_another_architecture():
             register_architecture(["toy"], Qwen3Config, lambda c: None)
     finally:
         unregister_architecture(["ToyForCausalLM", "toy"])
+
+
+def test_matrix_product_plan_fills_the_sms():
+    """The host-side choice of schedule, token tile and k ranges (a pure function of the shape)."""
+    from llmx_b200 import ops_tc
+    sms = 148
+    # few tokens: stream-K; the logits head has tiles enough and keeps whole tiles, unsplit
+    assert ops_tc._plan(8, 4096, 4096, True, sms) == (1, 0, 1)
+    assert ops_tc._plan(8, 151936, 4096, False, sms) == (0, 0, 1)
+    # a few hundred tokens on a [4096, 4096] weight: 32 to 64 tiles would idle most SMs, so K is cut
+    for m in (96, 128, 256, 512):
+        schedule, tile, splits = ops_tc._plan(m, 4096, 4096, True, sms)
+        assert schedule == 0 and tile in (128, 256) and splits >= 2
+        tiles = -(-4096 // 128) * -(-m // tile) * splits
+        assert tiles >= 96
+    # many tokens: whole tiles fill the SMs by themselves
+    assert ops_tc._plan(4096, 6144, 4096, False, sms)[2] == 1
+    # k ranges never outnumber the k blocks
+    assert ops_tc._plan(128, 4096, 64, True, sms)[2] == 1
