@@ -5,10 +5,11 @@
 // every key and value they read, so each page is fetched once for the whole group.
 //
 //   producer warp    walks the request's block table and fetches its pages with TMA
-//                    (boxes of [16 slots, 64 columns], 128-byte swizzle), four pages a stage,
-//                    three stages in flight
-//   4 consumer warps each takes one page of a stage: S = Q K^T (mma.sync m16n8k16, bfloat16 in,
-//                    float32 out), masks (causal, window, tail of the last page), online softmax
+//                    (boxes of [16 slots, 64 columns], 128-byte swizzle), four pages a stage, one
+//                    lane issuing each page's copy, three stages in flight
+//   4 consumer warps warps 0-1 take the even stages, warps 2-3 the odd ones; of a stage's four pages a warp
+//                    takes two as one tile of 32 keys: S = Q K^T (mma.sync m16n8k16, bfloat16 in,
+//                    float32 out), masks (causal, window, end of the key range), online softmax
 //                    in float32 (base 2), O += P V
 //   at the end       the four warps' (m, l, O) are merged through shared memory; with one key
 //                    range the result is written, else a partial (m, l, O) goes to the
@@ -80,7 +81,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             tc::mbar_init(&full_bar[s], 1);
-            tc::mbar_init(&empty_bar[s], CONSUMERS);
+            tc::mbar_init(&empty_bar[s], CONSUMERS / 2);      // the two warps that read the stage
         }
         *abort_flag = 0;
         tc::fence_barrier_init();
@@ -96,33 +97,26 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
         for (int e = 0; e < 4; ++e) o[t][e] = 0.0f;
 
     if (warp == CONSUMERS) {
-        if (n_pages > 0 && tc::elect_one()) {
-            tc::tma_prefetch_desc(&cache_map);
+        // One lane per page of a stage: each reads its page's id from the block table (one stage ahead, so the
+        // table's latency is off the copies' path) and issues its copy; a single thread issuing all of a
+        // stage's copies was what bounded a block's rate.
+        if (n_pages > 0 && lane < PAGES_PER_STAGE) {
+            if (lane == 0) tc::tma_prefetch_desc(&cache_map);
             const int* table = block_tables + (size_t)r * table_stride + kv_begin / PAGE;
-            // The page ids of a stage are read one stage ahead, so the table's latency is off the critical path.
-            int ids[PAGES_PER_STAGE], ids_next[PAGES_PER_STAGE];
-#pragma unroll
-            for (int p = 0; p < PAGES_PER_STAGE; ++p) ids_next[p] = p < n_pages ? table[p] : 0;
+            int id_next = lane < n_pages ? table[lane] : 0;
             for (int it = 0; it < iters; ++it) {
                 const int stage = it % STAGES;
                 const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
-#pragma unroll
-                for (int p = 0; p < PAGES_PER_STAGE; ++p) {
-                    ids[p] = ids_next[p];
-                    const int nxt = (it + 1) * PAGES_PER_STAGE + p;
-                    ids_next[p] = nxt < n_pages ? table[nxt] : 0;
-                }
+                const int id = id_next;
+                const int nxt = (it + 1) * PAGES_PER_STAGE + lane;
+                id_next = nxt < n_pages ? table[nxt] : 0;
                 if (!tc::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, error_word, ERR_DEC_PRODUCER)) break;
                 const int here = min(PAGES_PER_STAGE, n_pages - it * PAGES_PER_STAGE);
-                tc::mbar_expect_tx(&full_bar[stage], (uint32_t)(here * cfg::PAGE_BYTES));
-#pragma unroll
-                for (int p = 0; p < PAGES_PER_STAGE; ++p) {
-                    if (p >= here) break;
-                    const int page = ids[p];
-                    uint8_t* dst = tiles + stage * cfg::STAGE_BYTES + p * cfg::PAGE_BYTES;
-                    // One copy brings the head's keys and values of the page: [plane][half][slot][64 columns].
-                    tc::tma_load_5d(dst, &cache_map, 0, 0, 0, g, page * 2, &full_bar[stage]);
-                }
+                if (lane == 0) tc::mbar_expect_tx(&full_bar[stage], (uint32_t)(here * cfg::PAGE_BYTES));
+                // One copy brings the head's keys and values of the page: [plane][half][slot][64 columns].
+                if (lane < here)
+                    tc::tma_load_5d(tiles + stage * cfg::STAGE_BYTES + lane * cfg::PAGE_BYTES, &cache_map, 0, 0, 0, g,
+                                    id * 2, &full_bar[stage]);
             }
         }
     } else {
@@ -146,46 +140,63 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
                 qa[kk][half + 2] = valid[half] ? *reinterpret_cast<const uint32_t*>(src + d + 8) : 0u;
             }
         }
+        // Warps 0 and 1 take the even stages, warps 2 and 3 the odd ones; of a stage's four pages a warp takes
+        // two, as one tile of 32 keys: twice the independent work between a warp's waits, half the rescaling.
+        // Every warp waits for every stage, also those it does not read: a wait tells a barrier's phases apart
+        // by their parity only, so a warp must not skip one.
+        const int pair = warp & 1, group = warp >> 1;
         for (int it = 0; it < iters; ++it) {
             const int stage = it % STAGES;
             const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
             if (!tc::mbar_wait(&full_bar[stage], phase, abort_flag, error_word, ERR_DEC_CONSUMER)) break;
-            const int page_index = it * PAGES_PER_STAGE + warp;
+            if ((it & 1) != group) continue;
+            const int page_index = it * PAGES_PER_STAGE + 2 * pair;
             if (page_index < n_pages) {
                 const int key0 = kv_begin + page_index * PAGE;
-                const uint32_t kbase = tc::smem_u32(tiles + stage * cfg::STAGE_BYTES + warp * cfg::PAGE_BYTES);
+                const uint32_t kbase = tc::smem_u32(tiles + stage * cfg::STAGE_BYTES + 2 * pair * cfg::PAGE_BYTES);
                 const uint32_t vbase = kbase + cfg::PLANE_BYTES;
-                if (key0 + PAGE > len) {
-                    // Slots past the request's last key hold whatever an earlier owner left: zero those values
-                    // so that a stale non-finite number cannot reach the sum through a zero weight.
-                    const int first_bad = len - key0;
-                    for (int i = lane; i < (PAGE - first_bad) * cfg::BOXES * 8; i += 32) {
+                if (key0 + 2 * PAGE > kv_end) {
+                    // Slots past the request's last key hold whatever an earlier owner left, and a page past
+                    // the range's last one was not fetched at all: zero those values so that a stale
+                    // non-finite number cannot reach the sum through a zero weight.
+                    const int first_bad = kv_end - key0;                 // 1 .. 31, counted over both pages
+                    for (int i = lane; i < (2 * PAGE - first_bad) * cfg::BOXES * 8; i += 32) {
                         const int row = first_bad + i / (cfg::BOXES * 8), c = i % (cfg::BOXES * 8);
-                        const uint32_t addr = vbase + (c >> 3) * cfg::BOX_BYTES + attn::swz(row, c & 7);
+                        const uint32_t addr = vbase + (row / PAGE) * cfg::PAGE_BYTES + (c >> 3) * cfg::BOX_BYTES +
+                                              attn::swz(row % PAGE, c & 7);
                         asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
                     }
                     __syncwarp();
                 }
-                // ---- S = Q K^T for the page's 16 keys
-                float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                // ---- S = Q K^T for the 32 keys: s[2 * page + j] is the 8-key column block j of the page
+                float s[4][4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[j][e] = 0.0f;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const int dchunk = 2 * kk + ((lane >> 3) & 1);
                     const int key = ((lane >> 4) << 3) + (lane & 7);
-                    uint32_t b0, b1, b2, b3;
-                    attn::ldmatrix_x4(kbase + (dchunk >> 3) * cfg::BOX_BYTES + attn::swz(key, dchunk & 7), b0, b1, b2, b3);
+                    const uint32_t off = (dchunk >> 3) * cfg::BOX_BYTES + attn::swz(key, dchunk & 7);
+                    uint32_t b0, b1, b2, b3, c0, c1, c2, c3;
+                    attn::ldmatrix_x4(kbase + off, b0, b1, b2, b3);
+                    attn::ldmatrix_x4(kbase + cfg::PAGE_BYTES + off, c0, c1, c2, c3);
                     attn::mma_16816(s[0], qa[kk], b0, b1);
                     attn::mma_16816(s[1], qa[kk], b2, b3);
+                    attn::mma_16816(s[2], qa[kk], c0, c1);
+                    attn::mma_16816(s[3], qa[kk], c2, c3);
                 }
                 // ---- mask, online softmax (base 2)
                 float rowmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-                for (int j = 0; j < 2; ++j)
+                for (int j = 0; j < 4; ++j)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int half = e >> 1;
                         const int key = key0 + 8 * j + (lane & 3) * 2 + (e & 1);
-                        const bool ok = valid[half] && key >= lo[half] && key <= pos[half];
+                        // (a pair's second page may lie past the range: those keys are another block's)
+                        const bool ok = valid[half] && key >= lo[half] && key <= pos[half] && key < kv_end;
                         s[j][e] = ok ? s[j][e] * scale_log2 : -INFINITY;
                         rowmax[half] = fmaxf(rowmax[half], s[j][e]);
                     }
@@ -201,7 +212,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
                 }
                 float psum[2] = {0.0f, 0.0f};
 #pragma unroll
-                for (int j = 0; j < 2; ++j)
+                for (int j = 0; j < 4; ++j)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         s[j][e] = exp2f(s[j][e] - base[e >> 1]);
@@ -209,11 +220,14 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
                     }
                 l_run[0] = l_run[0] * alpha[0] + psum[0];
                 l_run[1] = l_run[1] * alpha[1] + psum[1];
-                uint32_t pa[4];
-                pa[0] = attn::pack_bf16(s[0][0], s[0][1]);
-                pa[1] = attn::pack_bf16(s[0][2], s[0][3]);
-                pa[2] = attn::pack_bf16(s[1][0], s[1][1]);
-                pa[3] = attn::pack_bf16(s[1][2], s[1][3]);
+                uint32_t pa[2][4];          // P of the first and of the second page as A operands (16 x 16 each)
+#pragma unroll
+                for (int pg = 0; pg < 2; ++pg) {
+                    pa[pg][0] = attn::pack_bf16(s[2 * pg][0], s[2 * pg][1]);
+                    pa[pg][1] = attn::pack_bf16(s[2 * pg][2], s[2 * pg][3]);
+                    pa[pg][2] = attn::pack_bf16(s[2 * pg + 1][0], s[2 * pg + 1][1]);
+                    pa[pg][3] = attn::pack_bf16(s[2 * pg + 1][2], s[2 * pg + 1][3]);
+                }
                 // ---- O = O * alpha + P V
 #pragma unroll
                 for (int t = 0; t < D / 8; t += 2) {
@@ -221,10 +235,14 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
                     o[t + 1][0] *= alpha[0]; o[t + 1][1] *= alpha[0]; o[t + 1][2] *= alpha[1]; o[t + 1][3] *= alpha[1];
                     const int key = (((lane >> 3) & 1) << 3) + (lane & 7);
                     const int dchunk = t + (lane >> 4);
-                    uint32_t b0, b1, b2, b3;
-                    attn::ldmatrix_x4_trans(vbase + (dchunk >> 3) * cfg::BOX_BYTES + attn::swz(key, dchunk & 7), b0, b1, b2, b3);
-                    attn::mma_16816(o[t], pa, b0, b1);
-                    attn::mma_16816(o[t + 1], pa, b2, b3);
+                    const uint32_t off = (dchunk >> 3) * cfg::BOX_BYTES + attn::swz(key, dchunk & 7);
+                    uint32_t b0, b1, b2, b3, c0, c1, c2, c3;
+                    attn::ldmatrix_x4_trans(vbase + off, b0, b1, b2, b3);
+                    attn::ldmatrix_x4_trans(vbase + cfg::PAGE_BYTES + off, c0, c1, c2, c3);
+                    attn::mma_16816(o[t], pa[0], b0, b1);
+                    attn::mma_16816(o[t + 1], pa[0], b2, b3);
+                    attn::mma_16816(o[t], pa[1], c0, c1);
+                    attn::mma_16816(o[t + 1], pa[1], c2, c3);
                 }
             }
             __syncwarp();
