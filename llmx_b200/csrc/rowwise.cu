@@ -227,8 +227,10 @@ __global__ void head_norm_rope_kernel(const float* __restrict__ qkv, int qkv_str
 }
 
 // The same for the common shape -- a head of 128 values rotated whole (64 pairs) -- with each lane holding
-// four consecutive values (16-byte loads, 8-byte stores); a pair's partner sits 16 lanes away.
-template <typename QT, typename KVT>
+// four consecutive values (16-byte loads, 8-byte stores); a pair's partner sits 16 lanes away.  A warp takes
+// U consecutive (row, head) items of one row (U divides heads + kv_heads): their loads are all asked for
+// before the first is used, and the row's position, cosines and sines are fetched once.
+template <typename QT, typename KVT, int U>
 __global__ void head_norm_rope_128_kernel(const float* __restrict__ qkv, int qkv_stride, int k_offset, int v_offset,
                                           const float* __restrict__ q_weight, const float* __restrict__ k_weight,
                                           float eps, const float* __restrict__ cos_table,
@@ -240,52 +242,76 @@ __global__ void head_norm_rope_128_kernel(const float* __restrict__ qkv, int qkv
     constexpr int D = 128;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int per_row = heads + kv_heads;
-    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
-    if (item >= (long long)rows * per_row) return;
-    const int row = (int)(item / per_row), j = (int)(item % per_row);
-    const bool is_q = j < heads;
-    const int g = is_q ? 0 : j - heads;
-    int slot = 0;
-    if (!is_q) {
-        slot = slots[row];
-        if (slot < 0) return;
+    const long long first = ((long long)blockIdx.x * (blockDim.x >> 5) + warp) * U;
+    if (first >= (long long)rows * per_row) return;
+    const int row = (int)(first / per_row), j0 = (int)(first % per_row);
+    const float* row_src = qkv + (size_t)row * qkv_stride;
+    const int slot = slots[row];
+    float4 v[U], raw[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int j = j0 + u;
+        const bool is_q = j < heads;
+        const int g = is_q ? 0 : j - heads;
+        v[u] = reinterpret_cast<const float4*>(row_src + (is_q ? j * D : k_offset + g * D))[lane];
+        if (!is_q && slot >= 0) raw[u] = reinterpret_cast<const float4*>(row_src + v_offset + g * D)[lane];
     }
-    const float* src = qkv + (size_t)row * qkv_stride + (is_q ? j * D : k_offset + g * D);
-    const float* weight = is_q ? q_weight : k_weight;
-    float4 v = reinterpret_cast<const float4*>(src)[lane];
-    if (weight) {
-        float s = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
-        s = warp_sum(s);
-        const float rr = 1.0f / sqrtf(s / (float)D + eps);
-        const float4 w4 = reinterpret_cast<const float4*>(weight)[lane];
-        v.x *= rr * w4.x; v.y *= rr * w4.y; v.z *= rr * w4.z; v.w *= rr * w4.w;
-    }
+    float4 c = make_float4(1.f, 1.f, 1.f, 1.f), sn = make_float4(0.f, 0.f, 0.f, 0.f);
     if (cos_table) {
         // Lane l < 16 holds a = x[4l..4l+3], lane l + 16 holds b = x[64 + 4l ..]; both need cos/sin[4 (l % 16) ..].
         const size_t base = (size_t)positions[row] * 64 + 4 * (lane & 15);
-        const float4 c = *reinterpret_cast<const float4*>(cos_table + base);
-        const float4 sn = *reinterpret_cast<const float4*>(sin_table + base);
-        float4 o;
-        o.x = __shfl_xor_sync(0xffffffffu, v.x, 16); o.y = __shfl_xor_sync(0xffffffffu, v.y, 16);
-        o.z = __shfl_xor_sync(0xffffffffu, v.z, 16); o.w = __shfl_xor_sync(0xffffffffu, v.w, 16);
-        if (lane < 16) {        // a' = fma(-b, sin, a cos)
-            v.x = fmaf(-o.x, sn.x, v.x * c.x); v.y = fmaf(-o.y, sn.y, v.y * c.y);
-            v.z = fmaf(-o.z, sn.z, v.z * c.z); v.w = fmaf(-o.w, sn.w, v.w * c.w);
-        } else {                // b' = fma(a, sin, b cos)
-            v.x = fmaf(o.x, sn.x, v.x * c.x); v.y = fmaf(o.y, sn.y, v.y * c.y);
-            v.z = fmaf(o.z, sn.z, v.z * c.z); v.w = fmaf(o.w, sn.w, v.w * c.w);
+        c = *reinterpret_cast<const float4*>(cos_table + base);
+        sn = *reinterpret_cast<const float4*>(sin_table + base);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int j = j0 + u;
+        const bool is_q = j < heads;
+        const int g = is_q ? 0 : j - heads;
+        if (!is_q && slot < 0) continue;
+        const float* weight = is_q ? q_weight : k_weight;
+        float4 x = v[u];
+        if (weight) {
+            float s = fmaf(x.x, x.x, fmaf(x.y, x.y, fmaf(x.z, x.z, x.w * x.w)));
+            s = warp_sum(s);
+            const float rr = 1.0f / sqrtf(s / (float)D + eps);
+            const float4 w4 = reinterpret_cast<const float4*>(weight)[lane];
+            x.x *= rr * w4.x; x.y *= rr * w4.y; x.z *= rr * w4.z; x.w *= rr * w4.w;
+        }
+        if (cos_table) {
+            float4 o;
+            o.x = __shfl_xor_sync(0xffffffffu, x.x, 16); o.y = __shfl_xor_sync(0xffffffffu, x.y, 16);
+            o.z = __shfl_xor_sync(0xffffffffu, x.z, 16); o.w = __shfl_xor_sync(0xffffffffu, x.w, 16);
+            if (lane < 16) {        // a' = fma(-b, sin, a cos)
+                x.x = fmaf(-o.x, sn.x, x.x * c.x); x.y = fmaf(-o.y, sn.y, x.y * c.y);
+                x.z = fmaf(-o.z, sn.z, x.z * c.z); x.w = fmaf(-o.w, sn.w, x.w * c.w);
+            } else {                // b' = fma(a, sin, b cos)
+                x.x = fmaf(o.x, sn.x, x.x * c.x); x.y = fmaf(o.y, sn.y, x.y * c.y);
+                x.z = fmaf(o.z, sn.z, x.z * c.z); x.w = fmaf(o.w, sn.w, x.w * c.w);
+            }
+        }
+        if (is_q) {
+            store4(q_out + ((size_t)row * heads + j) * D + 4 * lane, x.x, x.y, x.z, x.w);
+        } else {
+            const int page = slot / page_size, off = slot % page_size;
+            const size_t key_base = ((((size_t)page * 2 + 0) * kv_heads + g) * page_size + off) * D;
+            const size_t value_base = ((((size_t)page * 2 + 1) * kv_heads + g) * page_size + off) * D;
+            store4(cache + key_base + 4 * lane, x.x, x.y, x.z, x.w);
+            store4(cache + value_base + 4 * lane, raw[u].x, raw[u].y, raw[u].z, raw[u].w);
         }
     }
-    if (is_q) {
-        store4(q_out + ((size_t)row * heads + j) * D + 4 * lane, v.x, v.y, v.z, v.w);
-    } else {
-        const int page = slot / page_size, off = slot % page_size;
-        const size_t key_base = ((((size_t)page * 2 + 0) * kv_heads + g) * page_size + off) * D;
-        const size_t value_base = ((((size_t)page * 2 + 1) * kv_heads + g) * page_size + off) * D;
-        store4(cache + key_base + 4 * lane, v.x, v.y, v.z, v.w);
-        const float4 vv = reinterpret_cast<const float4*>(qkv + (size_t)row * qkv_stride + v_offset + g * D)[lane];
-        store4(cache + value_base + 4 * lane, vv.x, vv.y, vv.z, vv.w);
-    }
+}
+
+template <typename T, int U>
+static void launch_head_norm_rope_128(const float* qkv, int qkv_stride, int k_offset, int v_offset, const float* q_weight,
+                                      const float* k_weight, float eps, const float* cos_table, const float* sin_table,
+                                      const int* positions, const int* slots, void* q_out, void* cache, int rows,
+                                      int heads, int kv_heads, int page_size, cudaStream_t stream) {
+    const int warps = 4;
+    const long long groups = (long long)rows * (heads + kv_heads) / U;
+    launch_kernel(head_norm_rope_128_kernel<T, T, U>, dim3((unsigned)((groups + warps - 1) / warps)), dim3(warps * 32), 0,
+                  stream, qkv, qkv_stride, k_offset, v_offset, q_weight, k_weight, eps, cos_table, sin_table, positions,
+                  slots, (T*)q_out, (T*)cache, rows, heads, kv_heads, page_size);
 }
 
 LLMX_EXPORT int llmx_head_norm_rope_kv(const float* qkv, int qkv_stride, int k_offset, int v_offset,
@@ -304,14 +330,17 @@ LLMX_EXPORT int llmx_head_norm_rope_kv(const float* qkv, int qkv_stride, int k_o
                       !((uintptr_t)q_weight & 15) && !((uintptr_t)k_weight & 15) && !((uintptr_t)cos_table & 15) &&
                       !((uintptr_t)sin_table & 15);
     if (fast) {
-        if (q_dtype == LLMX_BF16)
-            launch_kernel(head_norm_rope_128_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(blocks), dim3(warps * 32), 0, stream, 
-                qkv, qkv_stride, k_offset, v_offset, q_weight, k_weight, eps, cos_table, sin_table, positions, slots,
-                (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, rows, heads, kv_heads, page_size);
-        else
-            launch_kernel(head_norm_rope_128_kernel<float, float>, dim3(blocks), dim3(warps * 32), 0, stream, 
-                qkv, qkv_stride, k_offset, v_offset, q_weight, k_weight, eps, cos_table, sin_table, positions, slots,
-                (float*)q_out, (float*)cache, rows, heads, kv_heads, page_size);
+        // Many rows: four items a warp keep enough loads in flight; few rows: one item a warp keeps more warps busy.
+        const int per_row = heads + kv_heads;
+        const int u = rows >= 64 && per_row % 4 == 0 ? 4 : rows >= 64 && per_row % 2 == 0 ? 2 : 1;
+#define LLMX_HNR(T, U) launch_head_norm_rope_128<T, U>(qkv, qkv_stride, k_offset, v_offset, q_weight, k_weight, eps, cos_table, \
+                                                       sin_table, positions, slots, q_out, cache, rows, heads, kv_heads, page_size, stream)
+        if (q_dtype == LLMX_BF16) {
+            if (u == 4) LLMX_HNR(__nv_bfloat16, 4); else if (u == 2) LLMX_HNR(__nv_bfloat16, 2); else LLMX_HNR(__nv_bfloat16, 1);
+        } else {
+            if (u == 4) LLMX_HNR(float, 4); else if (u == 2) LLMX_HNR(float, 2); else LLMX_HNR(float, 1);
+        }
+#undef LLMX_HNR
         return launch_status();
     }
     const size_t shmem = (size_t)warps * head_dim * sizeof(float);

@@ -66,10 +66,12 @@ def test_swiglu(rows, width):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,head_dim,rot,norm", [(4, 2, 16, 16, True), (6, 3, 32, 32, True), (3, 1, 48, 24, False),
                                                               (32, 8, 128, 128, True), (2, 2, 256, 64, True)])
-def test_head_norm_rope_kv(dtype, heads, kv_heads, head_dim, rot, norm):
-    """Per-head norm, rotation (whole or partial width) and the write into scattered cache slots."""
+@pytest.mark.parametrize("rows", [11, 70])
+def test_head_norm_rope_kv(dtype, heads, kv_heads, head_dim, rot, norm, rows):
+    """Per-head norm, rotation (whole or partial width) and the write into scattered cache slots
+    (few rows and many: the kernel shares its work out differently)."""
     from llmx_b200 import ops
-    rows, page, pages = 11, 8, 9
+    page, pages = 8, 9
     g = torch.Generator().manual_seed(4)
     qkv = torch.randn(rows, (heads + 2 * kv_heads) * head_dim, generator=g).to(DEV)
     qw = (1 + 0.1 * torch.randn(head_dim, generator=g)).to(DEV) if norm else None
