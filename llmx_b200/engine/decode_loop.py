@@ -72,8 +72,7 @@ class DecodeRecording:
         self._graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
         # Nothing may be freed on the device or in pinned memory while the stream is capturing, and Python's
-        # collector frees what it finds whenever it runs: it runs now, and not again until the capture is over.
-        gc.collect()
+        # collector frees what it finds whenever it runs: it does not run until the capture is over.
         was_enabled = gc.isenabled()
         gc.disable()
         try:
@@ -132,8 +131,14 @@ def recording_of(engine: Engine, b: int, room: int, make: bool = True) -> Option
 
 
 class DecodeSession:
-    def __init__(self, engine: Engine, request_ids: Sequence[Hashable], use_graph: bool = True):
+    def __init__(self, engine: Engine, request_ids: Sequence[Hashable], use_graph: bool = True,
+                 plain_steps: int = 1):
+        """`plain_steps`: how many steps a session runs through `Engine.step` before it has a missing
+        recording made (at least the one that warms a new batch size up).  Making a recording costs about
+        as much as ten to twenty plain steps, so a caller whose sessions may be short asks for a few."""
         self.engine = engine
+        self.plain_steps = max(1, int(plain_steps))
+        self._plain_run = 0
         self.request_ids = list(request_ids)
         self.use_graph = use_graph and engine.model.recordable
         self.h2d_bytes_per_step = 0
@@ -192,9 +197,11 @@ class DecodeSession:
         ctx = max(rc.length + 1 for rc in caches)
         room = room_for(ctx, eng.max_positions)
         warmed = eng.decode_warmed
-        if not self.use_graph or (b not in warmed and recording_of(eng, b, room, make=False) is None):
+        have = recording_of(eng, b, room, make=False) is not None
+        if not self.use_graph or (not have and (b not in warmed or self._plain_run < self.plain_steps)):
             logits = eng.step([StepEntry(rid, [int(t)], [0]) for rid, t in zip(self.request_ids, tokens)])
             warmed.add(b)
+            self._plain_run += 1
             self.h2d_bytes_per_step = eng.last_h2d_bytes
             return logits
         for t, rc in zip(tokens, caches):

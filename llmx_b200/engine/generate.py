@@ -94,7 +94,7 @@ class LLM:
         if all(len(e.tokens) == 1 and e.want_last and e.request.decoding for e in entries):
             if self._session is None or self._session_ids != ids:
                 self._close_session()
-                self._session, self._session_ids = DecodeSession(self.engine, ids), ids
+                self._session, self._session_ids = DecodeSession(self.engine, ids, plain_steps=4), ids
             return self._session.step([e.tokens[0] for e in entries])
         self._close_session()
         return self.engine.step([StepEntry(e.request.request_id, e.tokens, [len(e.tokens) - 1] if e.want_last else [])
