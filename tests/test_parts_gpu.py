@@ -4,8 +4,10 @@ toy mixer with state of its own, registered, built and stepped without a change 
 The toy model exercises what Qwen3 does not: a mixer with fixed-size per-request state, a feed-forward
 with a router and experts, a windowed
 attention layer whose pages are given back, a partially rotated and an unrotated attention layer, a
-block that runs twice (each run with a cache entry of its own), and a block that reads the keys
-another run of it wrote.  Its plain implementation below is whole-sequence numpy built from
+block that runs twice (each run with a cache entry of its own), a block that reads the keys
+another run of it wrote, and -- all three defined in this file -- a norm that centres and has a bias,
+a position encoding that rotates by half the position, and an arrangement in which mixer and
+feed-forward read the same normed input.  Its plain implementation below is whole-sequence numpy built from
 tests/plain_qwen3.py's functions.
 """
 import json
@@ -101,6 +103,72 @@ def _toy_routed_ffn_class():
     return RoutedFFN
 
 
+# A toy norm (centred, with a bias), a toy position encoding (rotation by half the position) and a toy
+# arrangement (mixer and feed-forward side by side on one normed input), with the interfaces the framework's
+# own norm, position encoding and block have.
+def _toy_extra_classes():
+    from llmx_b200.parts import Part
+    from llmx_b200.weights import TensorSpec
+
+    class CentredNorm(Part):
+        def __init__(self, width, eps):
+            self.width, self.eps = width, eps
+
+        def tensor_specs(self):
+            return {"weight": TensorSpec((self.width,), "vector", init="one_plus_normal", std=0.05),
+                    "bias": TensorSpec((self.width,), "vector", std=0.05)}
+
+        def load(self, tensors, precision):
+            super().load(tensors, precision)
+            self.weight, self.bias = tensors["weight"].float(), tensors["bias"].float()
+
+        def forward(self, x, out=None, row_index=None, out_dtype=None, zero=None):
+            if zero is not None:
+                zero.zero_()                         # this norm has no launch of its own to clear it in passing
+            if row_index is not None:
+                x = x[row_index.long()]
+            xf = x.float()
+            xc = xf - xf.mean(dim=-1, keepdim=True)
+            y = xc * torch.rsqrt((xc * xc).mean(dim=-1, keepdim=True) + self.eps) * self.weight + self.bias
+            y = y.to(out_dtype or self.precision.act)
+            if out is not None:
+                out.copy_(y)
+                return out
+            return y
+
+    class HalvedPositions(Part):
+        """cos/sin tables [positions, rot_dim / 2] of the angles (position / 2) * theta^(-2i / rot_dim)."""
+
+        def __init__(self, head_dim, theta):
+            self.rot_dim, self.theta = head_dim, theta
+            self.cos = self.sin = None
+
+        def prepare(self, max_positions, device):
+            freq = np.power(np.float32(self.theta), np.float32(-2.0) * np.arange(self.rot_dim // 2, dtype=np.float32) / np.float32(self.rot_dim))
+            angle = (np.arange(max_positions, dtype=np.float32)[:, None] * np.float32(0.5) * freq[None, :]).astype(np.float32)
+            self.cos = torch.from_numpy(np.cos(angle).astype(np.float32)).to(device)
+            self.sin = torch.from_numpy(np.sin(angle).astype(np.float32)).to(device)
+
+    class ParallelBlock(Part):
+        """x += mixer(norm(x)) + ffn(norm(x)): one norm, both parts read its output."""
+
+        def __init__(self, norm, mixer, ffn):
+            self.norm, self.mixer, self.ffn = norm, mixer, ffn
+
+        def children(self):
+            return {"ln": self.norm, "self_attn": self.mixer, "mlp": self.ffn}
+
+        def cache_spec(self):
+            return self.mixer.cache_spec()
+
+        def forward(self, x, step, cache_entry, write_cache=True):
+            h = self.norm.forward(x)
+            self.mixer.forward(h, step, cache_entry, x, write_cache)
+            self.ffn.forward(h, step, x)
+
+    return CentredNorm, HalvedPositions, ParallelBlock
+
+
 @dataclass(frozen=True)
 class ToyConfig:
     hidden_size: int = 64
@@ -137,7 +205,12 @@ def _build_toy(cfg: ToyConfig):
         PreNormBlock(norm(), Attention(E, H, G, D, NoPositionEncoding(), qk_norm_eps=None, window=cfg.window),
                      norm(), mlp()),                                                    # 2: window, no rotation, no q/k norm
     ]
-    order = [LayerStep(0, 0), LayerStep(1, 1), LayerStep(2, 2), LayerStep(0, 3), LayerStep(2, 2, write_cache=False)]
+    CentredNorm, HalvedPositions, ParallelBlock = _toy_extra_classes()
+    blocks.append(ParallelBlock(CentredNorm(E, cfg.rms_norm_eps),
+                                Attention(E, H, G, D, HalvedPositions(D, 10000.0), qk_norm_eps=None),
+                                mlp()))                                                 # 3: the file's own norm, encoding, arrangement
+    order = [LayerStep(0, 0), LayerStep(1, 1), LayerStep(2, 2), LayerStep(0, 3), LayerStep(2, 2, write_cache=False),
+             LayerStep(3, 4)]
     emb = TokenEmbedding(cfg.vocab_size, E)
     head = LogitsHead(norm(), cfg.vocab_size, E, tied_to=emb)
     return Model(embedding=emb, blocks=blocks, head=head, order=order, vocab_size=cfg.vocab_size,
@@ -201,11 +274,25 @@ def _plain_toy(cfg: ToyConfig, w, ids):
         o = plain.attention(q, k, v, window=cfg.window).reshape(T, H * D)
         return mlp(x + o @ w[pre + "self_attn.o_proj.weight"].T, pre), (k, v)
 
+    def block3(x):
+        pre = "model.layers.3."
+        xc = x - x.mean(axis=-1, keepdims=True)
+        h = (xc / np.sqrt((xc * xc).mean(axis=-1, keepdims=True) + np.float32(eps)) * w[pre + "ln.weight"] + w[pre + "ln.bias"]).astype(np.float32)
+        q, k, v = qkv(h, pre + "self_attn.")
+        freq = np.power(np.float32(10000.0), np.float32(-2.0) * np.arange(D // 2, dtype=np.float32) / np.float32(D))
+        angle = (np.arange(T, dtype=np.float32)[:, None] * np.float32(0.5) * freq[None, :]).astype(np.float32)
+        c, s_ = np.cos(angle).astype(np.float32), np.sin(angle).astype(np.float32)
+        q, k = plain.rope_rotate(q, c, s_), plain.rope_rotate(k, c, s_)
+        o = plain.attention(q, k, v).reshape(T, H * D)
+        ffn = plain.swiglu_ffn(h, w[pre + "mlp.gate_proj.weight"], w[pre + "mlp.up_proj.weight"], w[pre + "mlp.down_proj.weight"])
+        return x + o @ w[pre + "self_attn.o_proj.weight"].T + ffn
+
     x = block0(x)
     x = block1(x)
     x, kv = block2(x)
     x = block0(x)
     x, _ = block2(x, kv)
+    x = block3(x)
     h = plain.rms_norm(x, w["model.norm.weight"], eps)
     return (h @ w["model.embed_tokens.weight"].T).astype(np.float32)
 
@@ -238,7 +325,7 @@ def test_toy_architecture_is_registered_built_and_stepped(toy):
         steps = make(requests)
         engine = Engine.from_dir(folder, EngineOptions(dtype="float32", kv_tokens=helpers.tokens_needed(steps),
                                                        page_size=4, max_requests=4))
-        assert len(engine.cache.groups) == 2 and engine.cache.state_entries == [1]
+        assert len(engine.cache.groups) == 2 and engine.cache.state_entries == [1]      # full and windowed keys; one state
         assert not engine.model.recordable
         got = helpers.run_trace(engine, steps)
         engine.cache.check()
