@@ -41,8 +41,59 @@ struct Cfg {
     static constexpr int STAGE_BYTES = PAGES_PER_STAGE * PAGE_BYTES;
     static constexpr int MERGE_BYTES = CONSUMERS * MAX_ROWS * (D + 2) * 4;
     static constexpr int TILE_BYTES = STAGES * STAGE_BYTES > MERGE_BYTES ? STAGES * STAGE_BYTES : MERGE_BYTES;
-    static constexpr int SMEM_BYTES = TILE_BYTES + 1024 + 128;
+    static constexpr int MADE_BYTES = 3 * MAX_ROWS * D * 2 + 64;     // queries, new keys, new values (bfloat16), flags
+    static constexpr int SMEM_BYTES = TILE_BYTES + 1024 + 128 + MADE_BYTES;
 };
+
+// Optional input for blocks that make their own queries and new keys and values from the product's float32
+// output (head width 128, rotated whole or not at all): what the separate norm / rotation / cache-write kernel
+// would have done for these rows, in the same arithmetic.
+struct QkvInput {
+    const float* qkv;              // [rows, stride]: q heads, then k heads at k_offset, v heads at v_offset; null: unused
+    int stride, k_offset, v_offset;
+    const float* q_weight;         // per-head norm weights [128] or null
+    const float* k_weight;
+    float eps;
+    const float* cos_table;        // [positions, 64] or null
+    const float* sin_table;
+    const int* slots;              // per row: page * page_size + slot of its key and value, negative: not written
+    __nv_bfloat16* cache;          // [pages, 2, kv_heads, 16, 128]
+};
+
+// One row of 128 values by one warp, lane l holding values 4l .. 4l+3: RMSNorm with `weight` (skipped when
+// null), then rotation of the pairs (i, i + 64) by the angles of `pos` (skipped when the tables are null).
+// The arithmetic is that of head_norm_rope_128_kernel (rowwise.cu), operation for operation.
+__device__ __forceinline__ float4 norm_rope_row_128(const float* src, const float* weight, float eps,
+                                                    const float* cos_table, const float* sin_table, int pos, int lane) {
+    float4 v = reinterpret_cast<const float4*>(src)[lane];
+    if (weight) {
+        float s = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
+        s = warp_sum(s);
+        const float rr = 1.0f / sqrtf(s / 128.0f + eps);
+        const float4 w4 = reinterpret_cast<const float4*>(weight)[lane];
+        v.x *= rr * w4.x; v.y *= rr * w4.y; v.z *= rr * w4.z; v.w *= rr * w4.w;
+    }
+    if (cos_table) {
+        const size_t base = (size_t)pos * 64 + 4 * (lane & 15);
+        const float4 c = *reinterpret_cast<const float4*>(cos_table + base);
+        const float4 sn = *reinterpret_cast<const float4*>(sin_table + base);
+        float4 o;
+        o.x = __shfl_xor_sync(0xffffffffu, v.x, 16); o.y = __shfl_xor_sync(0xffffffffu, v.y, 16);
+        o.z = __shfl_xor_sync(0xffffffffu, v.z, 16); o.w = __shfl_xor_sync(0xffffffffu, v.w, 16);
+        if (lane < 16) {
+            v.x = fmaf(-o.x, sn.x, v.x * c.x); v.y = fmaf(-o.y, sn.y, v.y * c.y);
+            v.z = fmaf(-o.z, sn.z, v.z * c.z); v.w = fmaf(-o.w, sn.w, v.w * c.w);
+        } else {
+            v.x = fmaf(o.x, sn.x, v.x * c.x); v.y = fmaf(o.y, sn.y, v.y * c.y);
+            v.z = fmaf(o.z, sn.z, v.z * c.z); v.w = fmaf(o.w, sn.w, v.w * c.w);
+        }
+    }
+    return v;
+}
+
+__device__ __forceinline__ uint2 pack4_bf16(float4 v) {
+    return make_uint2(attn::pack_bf16(v.x, v.y), attn::pack_bf16(v.z, v.w));
+}
 
 template <int D>
 __global__ void __launch_bounds__(THREADS)
@@ -51,7 +102,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
                    const int* __restrict__ row_start, const int* __restrict__ row_count,
                    const int* __restrict__ history, const int* __restrict__ block_tables, int table_stride, int heads,
                    int kv_heads, int window, float scale_log2, int splits, const int* __restrict__ chunk_ptr,
-                   int chunk_keys, int* __restrict__ counters, int* error_word) {
+                   int chunk_keys, int* __restrict__ counters, int* error_word, const QkvInput made) {
     pdl_trigger();
     pdl_wait();
     using cfg = Cfg<D>;
@@ -85,6 +136,43 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
         }
         *abort_flag = 0;
         tc::fence_barrier_init();
+    }
+    // What the block makes itself when it is given the product's output instead of finished queries.
+    __nv_bfloat16* q_made = (__nv_bfloat16*)(tiles + cfg::TILE_BYTES + 128);      // [MAX_ROWS][D]
+    __nv_bfloat16* kv_made = q_made + MAX_ROWS * D;                              // [MAX_ROWS][2][D]
+    int* kv_patch = (int*)(kv_made + 2 * MAX_ROWS * D);                          // [MAX_ROWS]: the row is to be used
+    if constexpr (D == 128) {
+        if (made.qkv) {
+            for (int i = warp; i < M; i += THREADS / 32) {
+                const int ti = i / ratio, h = g * ratio + i % ratio;
+                const float4 v = norm_rope_row_128(made.qkv + (size_t)(q0 + ti) * made.stride + h * D, made.q_weight,
+                                                   made.eps, made.cos_table, made.sin_table, hist + ti, lane);
+                *reinterpret_cast<uint2*>(q_made + i * D + 4 * lane) = pack4_bf16(v);
+            }
+            // The new keys and values that lie in this block's key range: to the cache for later steps, and kept
+            // here to be laid over their page when it arrives (the copy may have read the page before or after
+            // the store above landed).
+            for (int t = warp; t < n_q; t += THREADS / 32) {
+                const int p = hist + t;
+                const int slot = made.slots[q0 + t];
+                const bool mine = p >= kv_begin && p < kv_end && slot >= 0;
+                if (lane == 0) kv_patch[t] = mine ? 1 : 0;
+                if (mine) {
+                    const float* row = made.qkv + (size_t)(q0 + t) * made.stride;
+                    const float4 k = norm_rope_row_128(row + made.k_offset + g * D, made.k_weight, made.eps,
+                                                       made.cos_table, made.sin_table, p, lane);
+                    const float4 v = reinterpret_cast<const float4*>(row + made.v_offset + g * D)[lane];
+                    const uint2 kb = pack4_bf16(k), vb = pack4_bf16(v);
+                    *reinterpret_cast<uint2*>(kv_made + (t * 2 + 0) * D + 4 * lane) = kb;
+                    *reinterpret_cast<uint2*>(kv_made + (t * 2 + 1) * D + 4 * lane) = vb;
+                    const int page = slot / PAGE, off = slot % PAGE;
+                    const size_t key_base = ((((size_t)page * 2 + 0) * kv_heads + g) * PAGE + off) * D;
+                    const size_t value_base = ((((size_t)page * 2 + 1) * kv_heads + g) * PAGE + off) * D;
+                    *reinterpret_cast<uint2*>(made.cache + key_base + 4 * lane) = kb;
+                    *reinterpret_cast<uint2*>(made.cache + value_base + 4 * lane) = vb;
+                }
+            }
+        }
     }
     __syncthreads();
 
@@ -132,7 +220,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
             const int ti = row / ratio;
             pos[half] = hist + ti;
             lo[half] = window > 0 ? max(0, pos[half] - window + 1) : 0;
-            const __nv_bfloat16* src = q + ((size_t)(q0 + ti) * heads + g * ratio + row % ratio) * D;
+            const __nv_bfloat16* src = made.qkv ? q_made + min(row, MAX_ROWS - 1) * D
+                                                : q + ((size_t)(q0 + ti) * heads + g * ratio + row % ratio) * D;
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
                 const int d = kk * 16 + (lane & 3) * 2;
@@ -155,6 +244,21 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
                 const int key0 = kv_begin + page_index * PAGE;
                 const uint32_t kbase = tc::smem_u32(tiles + stage * cfg::STAGE_BYTES + 2 * pair * cfg::PAGE_BYTES);
                 const uint32_t vbase = kbase + cfg::PLANE_BYTES;
+                if (D == 128 && made.qkv && key0 + 2 * PAGE > hist) {
+                    // The step's own keys and values among these 32: laid over what the copy brought.
+                    for (int t = 0; t < n_q; ++t) {
+                        const int at = hist + t - key0;
+                        if (at >= 0 && at < 2 * PAGE && kv_patch[t]) {
+                            const int plane = lane >> 4, c = lane & 15;           // 16 chunks of 8 values a row
+                            const uint4 val = *reinterpret_cast<const uint4*>(kv_made + (t * 2 + plane) * D + c * 8);
+                            const uint32_t addr = kbase + (at / PAGE) * cfg::PAGE_BYTES + plane * cfg::PLANE_BYTES +
+                                                  (c >> 3) * cfg::BOX_BYTES + attn::swz(at % PAGE, c & 7);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(val.x), "r"(val.y),
+                                         "r"(val.z), "r"(val.w) : "memory");
+                        }
+                    }
+                    __syncwarp();
+                }
                 if (key0 + 2 * PAGE > kv_end) {
                     // Slots past the request's last key hold whatever an earlier owner left, and a page past
                     // the range's last one was not fetched at all: zero those values so that a stale
@@ -416,7 +520,7 @@ template <int D>
 int launch(const CUtensorMap& map, const void* q, void* out, float* partial, const int* req_list, int n_req,
            const int* row_start, const int* row_count, const int* history, const int* block_tables, int table_stride,
            int heads, int kv_heads, int window, float scale, int splits, const int* chunk_ptr, int chunk_keys,
-           int max_rows, int* counters, int* error_word, cudaStream_t stream) {
+           int max_rows, int* counters, int* error_word, cudaStream_t stream, const QkvInput& made = QkvInput{}) {
     using cfg = Cfg<D>;
     static bool configured = false;
     if (!configured) {
@@ -429,7 +533,7 @@ int launch(const CUtensorMap& map, const void* q, void* out, float* partial, con
     launch_kernel(attn_decode_kernel<D>, grid, dim3(THREADS), cfg::SMEM_BYTES, stream,
         map, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, partial, req_list, row_start, row_count, history,
         block_tables, table_stride, heads, kv_heads, window, scale * attn::LOG2E, splits, chunk_ptr, chunk_keys,
-        counters, error_word);
+        counters, error_word, made);
     int e = launch_status();
     if (e || splits == 1 || counters) return e;
     dim3 mgrid(heads, max_rows, n_req);
@@ -476,6 +580,40 @@ LLMX_EXPORT int llmx_attn_decode_fused(const void* cache_map, const void* q, voi
                                      max_rows, counters, error_word, stream);
         default: return LLMX_ERR_UNSUPPORTED;
     }
+}
+
+// The same for a step in which every request brings few rows, given the float32 output of the q/k/v product
+// [rows, qkv_stride] instead of finished queries: each block norms and rotates its own queries, and the block
+// whose key range holds a new row norms and rotates that key, stores key and value to the cache and lays them
+// over the page it has fetched.  Head width 128, rotated whole (cos/sin [positions, 64]) or not at all (null).
+// `slots` [rows]: page * 16 + slot of a row's key and value, negative when this layer does not write them.
+LLMX_EXPORT int llmx_attn_decode_qkv(const void* cache_map, const float* qkv, int qkv_stride, int k_offset,
+                                     int v_offset, const float* q_weight, const float* k_weight, float eps,
+                                     const float* cos_table, const float* sin_table, const int* slots, void* cache,
+                                     void* out, float* partial, const int* req_list, int n_req, const int* row_start,
+                                     const int* row_count, const int* history, const int* block_tables,
+                                     int table_stride, int heads, int kv_heads, int head_dim, int page_size, int window,
+                                     float scale, int splits, const int* chunk_ptr, int chunk_keys, int max_rows,
+                                     int* counters, int* error_word, cudaStream_t stream) {
+    if (n_req <= 0) return 0;
+    if (head_dim != 128 || page_size != PAGE || heads % kv_heads || heads / kv_heads > MAX_ROWS || splits < 1 ||
+        n_req > 65535 || kv_heads > 65535 || (chunk_keys % 64) || max_rows < 1 ||
+        max_rows * (heads / kv_heads) > MAX_ROWS)
+        return LLMX_ERR_UNSUPPORTED;
+    if (!qkv || !slots || !cache || (splits > 1 && (!partial || !counters)) || (!cos_table) != (!sin_table))
+        return LLMX_ERR_BAD_ARGUMENT;
+    if (qkv_stride % 4 || k_offset % 4 || v_offset % 4 || ((uintptr_t)qkv & 15) || ((uintptr_t)cache & 15) ||
+        ((uintptr_t)q_weight & 15) || ((uintptr_t)k_weight & 15) || ((uintptr_t)cos_table & 15) ||
+        ((uintptr_t)sin_table & 15))
+        return LLMX_ERR_UNSUPPORTED;
+    if (splits > 256) return LLMX_ERR_UNSUPPORTED;
+    QkvInput made;
+    made.qkv = qkv; made.stride = qkv_stride; made.k_offset = k_offset; made.v_offset = v_offset;
+    made.q_weight = q_weight; made.k_weight = k_weight; made.eps = eps;
+    made.cos_table = cos_table; made.sin_table = sin_table; made.slots = slots; made.cache = (__nv_bfloat16*)cache;
+    return launch<128>(*(const CUtensorMap*)cache_map, nullptr, out, partial, req_list, n_req, row_start, row_count,
+                       history, block_tables, table_stride, heads, kv_heads, window, scale, splits, chunk_ptr, chunk_keys,
+                       max_rows, counters, error_word, stream, made);
 }
 
 // The same with a second kernel combining the key ranges (no counters needed).

@@ -20,6 +20,12 @@ register_signature("attention_decode", "llmx_attn_decode",
                    [_p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p, _i, _i, _p, _p])
 register_signature("attention_decode", "llmx_attn_decode_fused",
                    [_p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p, _i, _i, _p, _p, _p])
+# cache_map, qkv, stride, k_offset, v_offset, q_weight, k_weight, eps, cos, sin, slots, cache, out, partial, req_list,
+# n_req, row_start, row_count, history, tables, table_stride, heads, kv_heads, head_dim, page, window, scale, splits,
+# chunk_ptr, chunk, max_rows, counters, error_word, stream
+register_signature("attention_decode", "llmx_attn_decode_qkv",
+                   [_p, _p, _i, _i, _i, _p, _p, _f, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i,
+                    _i, _f, _i, _p, _i, _i, _p, _p, _p])
 register_signature("attention_prefill_tc", "llmx_attn_prefill_tc_cache_map", [_p, _p, _ll, _i, _i, _i])
 register_signature("attention_prefill_tc", "llmx_attn_prefill_tc",
                    [_p, _p, _p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p])
@@ -173,3 +179,49 @@ def paged_attention_bf16(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
             ctypes.c_void_p(cmap.address), _ptr(q), _ptr(out), _ptr(large), n_large, _ptr(step.row_start),
             _ptr(step.row_count), _ptr(step.history), _ptr(tables), tables.shape[1], heads, kv_heads, head_dim,
             cache.shape[3], win, float(scale), rows_large, _ptr(err), _stream()), "attention_prefill")
+
+
+def decode_from_qkv(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                    cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], slots: torch.Tensor,
+                    cache: torch.Tensor, out: torch.Tensor, step, group, heads: int, kv_heads: int, head_dim: int,
+                    window: Optional[int], scale: float) -> bool:
+    """Attention for a step in which every request brings few rows, straight from the q/k/v product's float32
+    output: the decode kernel's blocks norm and rotate their own queries, and the new keys and values are
+    stored (and used) by the blocks whose key range holds them, so the separate norm / rotation / cache-write
+    kernel does not run.  Returns False, having done nothing, when the step or the shapes do not qualify."""
+    if (head_dim != 128 or cache.shape[3] != PAGE or cache.dtype is not torch.bfloat16 or out.dtype is not torch.bfloat16
+            or qkv.dtype is not torch.float32 or not supported(heads, kv_heads, head_dim, cache.shape[3])
+            or step.extras.get("no_qkv_attention")):
+        return False
+    if cos is not None and (cos.shape[1] != 64 or sin is None):
+        return False
+    ratio = heads // kv_heads
+    (small, n_small, ctx_small, rows_small, large, n_large, rows_large) = _request_lists(step, 16 // ratio)
+    if n_large or not n_small or n_small * kv_heads > MAX_COUNTERS:
+        return False
+    _cuda(qkv, q_weight, k_weight, cos, sin, slots, cache, out)
+    _need(qkv.shape[1] == (heads + 2 * kv_heads) * head_dim and out.shape == (qkv.shape[0], heads * head_dim),
+          "attention: the product's output and the attention output do not fit the head counts")
+    sched = step.extras.get("decode_schedule")
+    if sched is None:
+        splits, chunk = decode_schedule(n_small, kv_heads, ctx_small)
+        chunk_ptr = None
+    else:
+        splits, chunk, chunk_ptr = sched
+    partial = None
+    if splits > 1:
+        key = ("attn_partial", splits, heads, head_dim)
+        partial = step.extras.get(key)
+        if partial is None:
+            partial = torch.empty((qkv.shape[0] * heads * splits * (head_dim + 2),), dtype=torch.float32, device=qkv.device)
+            step.extras[key] = partial
+    cmap = cache_map(cache)
+    tables = group.block_tables
+    _check(_fn("attention_decode", "llmx_attn_decode_qkv")(
+        ctypes.c_void_p(cmap.address), _ptr(qkv), qkv.shape[1], heads * head_dim, (heads + kv_heads) * head_dim,
+        _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos), _ptr(sin), _ptr(slots), _ptr(cache), _ptr(out),
+        _ptr(partial), _ptr(small), n_small, _ptr(step.row_start), _ptr(step.row_count), _ptr(step.history),
+        _ptr(tables), tables.shape[1], heads, kv_heads, head_dim, cache.shape[3], int(window or 0), float(scale), splits,
+        _ptr(chunk_ptr), chunk, max(rows_small, 1), _ptr(_counter_buffer(qkv.device)), _ptr(error_word(qkv.device)),
+        _stream()), "attention_decode")
+    return True

@@ -80,7 +80,6 @@ class Attention(Part):
         group, cache = step.kv(cache_entry)
         out, self._qkv_out = getattr(self, "_qkv_out", None), None
         qkv = self.qkv(h, out=out, cleared=out is not None) if out is not None and out.shape[0] == rows else self.qkv(h)
-        q = torch.empty((rows, self.q_width), dtype=self.precision.act, device=h.device)
         pe = self.position_encoding
         slots = group.slots
         if not write_cache:
@@ -89,9 +88,13 @@ class Attention(Part):
             if key not in step.extras:
                 step.extras[key] = torch.full_like(group.slots, -1)
             slots = step.extras[key]
-        ops.head_norm_rope_kv(qkv, self.heads, self.kv_heads, self.head_dim, self.q_norm, self.k_norm,
-                              self.qk_norm_eps or 0.0, pe.cos, pe.sin, step.positions, slots, q, cache)
-        o = torch.empty_like(q)
-        from .attention_dispatch import paged_attention
-        paged_attention(q, cache, o, step, group, self.heads, self.kv_heads, self.head_dim, self.window, self.scale)
+        o = torch.empty((rows, self.q_width), dtype=self.precision.act, device=h.device)
+        from .attention_dispatch import decode_from_qkv, paged_attention
+        # A step of decoding rows only: the attention kernel makes its queries and new keys itself.
+        if not decode_from_qkv(qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, pe.cos, pe.sin, slots, cache, o,
+                               step, group, self.heads, self.kv_heads, self.head_dim, self.window, self.scale):
+            q = torch.empty_like(o)
+            ops.head_norm_rope_kv(qkv, self.heads, self.kv_heads, self.head_dim, self.q_norm, self.k_norm,
+                                  self.qk_norm_eps or 0.0, pe.cos, pe.sin, step.positions, slots, q, cache)
+            paged_attention(q, cache, o, step, group, self.heads, self.kv_heads, self.head_dim, self.window, self.scale)
         self.o(o, out=residual, accumulate=True)

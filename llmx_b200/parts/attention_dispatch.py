@@ -25,3 +25,15 @@ def paged_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, ste
             return
     ops.attention_plain(q, cache, out, step.row_request, step.positions, group.block_tables, heads, kv_heads,
                         head_dim, window, scale)
+
+
+def decode_from_qkv(qkv: torch.Tensor, q_weight, k_weight, eps: float, cos, sin, slots: torch.Tensor,
+                    cache: torch.Tensor, out: torch.Tensor, step: StepBatch, group: GroupView, heads: int,
+                    kv_heads: int, head_dim: int, window: Optional[int], scale: float) -> bool:
+    """On the bfloat16 path, when every request of the step brings few rows and the shapes allow it, the decode
+    kernel takes the q/k/v product's output as it is (see ops_attn.decode_from_qkv); else False and nothing done."""
+    if out.dtype is not torch.bfloat16:
+        return False
+    from .. import ops_attn
+    return ops_attn.decode_from_qkv(qkv, q_weight, k_weight, eps, cos, sin, slots, cache, out, step, group, heads,
+                                    kv_heads, head_dim, window, scale)

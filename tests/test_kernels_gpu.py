@@ -292,6 +292,56 @@ def test_attention_decode_any_number_of_key_ranges(splits):
     assert np.abs(out.float().cpu().numpy() - ref).max() <= 2e-2 * max(1.0, np.abs(ref).max())
 
 
+@pytest.mark.parametrize("heads,kv_heads", [(32, 8), (16, 1), (8, 8), (4, 2)])
+@pytest.mark.parametrize("window", [None, 100])
+@pytest.mark.parametrize("rotate,norm", [(True, True), (False, True), (True, False)])
+@pytest.mark.parametrize("splits", [None, 3])
+def test_attention_decode_from_the_products_output(heads, kv_heads, window, rotate, norm, splits):
+    """The decode kernel that norms and rotates its own queries and new keys, against the separate kernel
+    followed by the decode kernel: the same bits in the output and in the cache.  Histories put new rows at
+    the first and last slot of a page, at the edge of a key range, and (with several new rows) across two pages;
+    one request's write is skipped, as for a layer that reads another layer's cache."""
+    from llmx_b200 import ops, ops_attn, ops_tc
+    head_dim, page = 128, 16
+    max_new = 16 // (heads // kv_heads)
+    layout = [(0, 1), (15, 1), (16, 1), (63, min(2, max_new)), (64, 1), (127, min(3, max_new)), (700, max_new), (1500, 1)]
+    _, cache, step, group, _ = _attention_case(torch.bfloat16, heads, kv_heads, head_dim, page, layout, window, seed=12)
+    rows = step.rows
+    g = torch.Generator().manual_seed(13)
+    qkv = torch.randn(rows, (heads + 2 * kv_heads) * head_dim, generator=g).to(DEV)
+    qw = (1 + 0.1 * torch.randn(head_dim, generator=g)).to(DEV) if norm else None
+    kw = (1 + 0.1 * torch.randn(head_dim, generator=g)).to(DEV) if norm else None
+    cos = sin = None
+    if rotate:
+        cos_np, sin_np = plain.rope_tables(1600, head_dim, 10000.0)
+        cos, sin = torch.from_numpy(cos_np).to(DEV), torch.from_numpy(sin_np).to(DEV)
+    tables = group.block_tables.cpu().numpy()
+    positions = step.positions.cpu().numpy()
+    row_request = step.row_request.cpu().numpy()
+    slots = np.array([tables[row_request[i], positions[i] // page] * page + positions[i] % page for i in range(rows)], dtype=np.int32)
+    slots[step.host_row_start[4]] = -1                              # this row's key and value are not written
+    slots = torch.from_numpy(slots).to(DEV)
+    if splits:
+        step.extras["decode_schedule"] = (splits, -(-(-(-1501 // 64)) // splits) * 64, None)
+    scale = 1.0 / math.sqrt(head_dim)
+    # the separate kernels
+    cache_a = cache.clone()
+    q = torch.empty(rows, heads * head_dim, dtype=torch.bfloat16, device=DEV)
+    ops.head_norm_rope_kv(qkv, heads, kv_heads, head_dim, qw, kw, 1e-6, cos, sin, step.positions, slots, q, cache_a)
+    out_a = torch.full_like(q, float("nan"))
+    ops_attn.paged_attention_bf16(q, cache_a, out_a, step, group, heads, kv_heads, head_dim, window, scale)
+    # the one kernel
+    cache_b = cache.clone()
+    out_b = torch.full_like(q, float("nan"))
+    assert ops_attn.decode_from_qkv(qkv, qw, kw, 1e-6, cos, sin, slots, cache_b, out_b, step, group, heads, kv_heads,
+                                    head_dim, window, scale)
+    torch.cuda.synchronize()
+    ops_tc.check_errors()
+    assert torch.isfinite(out_b.float()).all()
+    assert torch.equal(cache_a, cache_b)
+    assert torch.equal(out_a, out_b)
+
+
 # ---------------------------------------------------------------------------------------------
 def _sample_rows(logits, settings):
     from llmx_b200.sampling import RequestSampling, SamplingParams, sample
