@@ -8,15 +8,17 @@ sizes of Qwen3-8B (36 layers unless --layers says otherwise), a batch of 8 and a
 tokens per request.  One JSON line is printed:
 
   value        decoded tokens a second, the K steps timed on the device with CUDA events
-  e2e          the same through the Python entry point: host token ids in, sampled ids out, every step
+  e2e          the same through the Python entry point, `LLM.generate`: prompts of the context's length as host
+               token ids in (it prefills them itself), sampled ids out; every step copies its metadata from
+               pinned host memory and reads the drawn ids back; timed on the host between two tokens K steps apart
   prefill      a 2,048-token prompt from an empty cache: tokens a second and the fraction of the
                measured bf16 peak its flops reach
   roofline     the bytes a decode step must read (every weight once, the cache of the live requests)
                divided by its time, against the measured copy bandwidth
   points       decode tokens a second at batch 1 and batch 64
 
-The histories of the decoding requests are synthetic cache contents (pages taken and filled with
-random values): what a decode step costs depends on how much it reads, not on what it reads.
+For `value` and `points` the histories of the decoding requests are synthetic cache contents (pages taken and
+filled with random values): what a decode step costs depends on how much it reads, not on what it reads.
 """
 from __future__ import annotations
 
@@ -151,7 +153,8 @@ def main() -> int:
     cfg = Qwen3Config.from_dict(raw)
     page = 16
     max_batch = max(args.batch, 1 if args.no_points else 64)
-    per_request = -(-(args.context + args.steps + args.warmup + 64) // page) * page
+    head_start = -(-args.context // 2048) * (args.batch - 1)          # see run_generate
+    per_request = -(-(args.context + args.steps + max(args.warmup, 8) + head_start + 64) // page) * page
     kv_tokens = max(max_batch * per_request, args.prefill_tokens + page)
     torch.cuda.set_device(0)
     engine = Engine.from_config(cfg, seed=0, options=EngineOptions(dtype="bfloat16", kv_tokens=kv_tokens,
@@ -218,6 +221,30 @@ def main() -> int:
                 engine.end(rid)
         return batch * 1e3 / ms, ms, launches, h2d
 
+    def run_generate(batch, steps, warmup):
+        """The same decode rate through the Python entry point, `LLM.generate`: host token ids in (prompts of
+        `context` tokens, which it prefills itself), sampled ids out.  Every step copies its metadata from pinned
+        host memory and reads the drawn ids back; the clock runs between the callbacks of two tokens of the
+        batch's last request, `steps` steps apart, after `warmup` decode steps."""
+        from llmx_b200.engine.generate import LLM
+        llm = LLM(engine, ubatch=2048, max_seqs=batch)
+        prompts = [ids(args.context) for _ in range(batch)]
+        seen, marks = [0], {}
+
+        def on_token(i, token):
+            if i == batch - 1:
+                seen[0] += 1
+                if seen[0] in (warmup + 1, warmup + 1 + steps):
+                    marks[seen[0]] = time.perf_counter()
+        # The requests' prompts end one after the other, so the first request decodes `head_start` steps before
+        # the last one starts; all must still be decoding when the last one's timed tokens are drawn.
+        head_start = -(-args.context // 2048) * (batch - 1)
+        llm.generate(prompts, SamplingParams(max_tokens=head_start + warmup + steps + 4, temp=0.0, top_k=0, top_p=1.0,
+                                             ignore_eos=True), on_token)
+        ms = (marks[warmup + 1 + steps] - marks[warmup + 1]) * 1e3 / steps
+        h2d = max((rec.total * 4 for (b, _), rec in engine.decode_recordings.items() if b == batch), default=0)
+        return batch * 1e3 / ms, ms, h2d
+
     def run_prefill(tokens_n, reps, warmup):
         prompt = ids(tokens_n)
         times = []
@@ -249,7 +276,7 @@ def main() -> int:
     clocks = ClockSampler()          # clocks and throttle reasons over every timed region below
     clocks.start()
     value, ms, launches, _ = run_decode(args.batch, args.steps, args.warmup, e2e=False)
-    e2e_value, e2e_ms, _, h2d = run_decode(args.batch, args.steps, args.warmup, e2e=True)
+    e2e_value, e2e_ms, h2d = run_generate(args.batch, args.steps, max(args.warmup, 8))
     pf_value, pf_ms, pf_frac = run_prefill(args.prefill_tokens, 3, 3)
     points = {}
     if not args.no_points:

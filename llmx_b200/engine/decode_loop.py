@@ -98,8 +98,9 @@ class DecodeRecording:
     def chunk(self, ctx: int) -> int:
         return max(64, -(-(-(-ctx // 64)) // self.splits) * 64)
 
-    def launch(self, fill) -> torch.Tensor:
-        """Copy the step's metadata (written into a pinned buffer by `fill(array)`) and replay the graph."""
+    def launch(self, fill, device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Copy the step's metadata (written into a pinned buffer by `fill(array)`) and replay the graph.
+        `device_tokens` (int32 [b] on the device): the step's token ids, laid over what the host wrote."""
         slot = self._ring_at
         self._ring_at = (slot + 1) % len(self._ring)
         if self._ring_events[slot] is not None:
@@ -110,6 +111,8 @@ class DecodeRecording:
         ev = torch.cuda.Event()
         ev.record()
         self._ring_events[slot] = ev
+        if device_tokens is not None:
+            self._dev[:self.b].copy_(device_tokens, non_blocking=True)
         self._graph.replay()
         return self.logits
 
@@ -186,26 +189,31 @@ class DecodeSession:
                 sl[r] = pages[hist[r] // ps] * ps + hist[r] % ps
         host[:] = m
 
-    def step(self, tokens: Sequence[int]) -> torch.Tensor:
+    def step(self, tokens) -> torch.Tensor:
         """Feed one token per request (in the session's order); float32 logits [requests, vocab] on the
-        device, valid until the next step."""
+        device, valid until the next step.  `tokens`: a sequence of ids, or an int32 tensor on the device
+        (what the sampler drew for the step before: the host then need not have seen the ids yet)."""
         eng = self.engine
         b = len(self.request_ids)
         if len(tokens) != b:
             raise StepError("a decode step needs one token for every request of the session")
+        device_tokens = tokens if isinstance(tokens, torch.Tensor) else None
         caches = [eng.cache.live[rid] for rid in self.request_ids]
         ctx = max(rc.length + 1 for rc in caches)
         room = room_for(ctx, eng.max_positions)
         warmed = eng.decode_warmed
         have = recording_of(eng, b, room, make=False) is not None
         if not self.use_graph or (not have and (b not in warmed or self._plain_run < self.plain_steps)):
+            if device_tokens is not None:
+                tokens = device_tokens.cpu().tolist()          # a plain step builds its batch on the host
             logits = eng.step([StepEntry(rid, [int(t)], [0]) for rid, t in zip(self.request_ids, tokens)])
             warmed.add(b)
             self._plain_run += 1
             self.h2d_bytes_per_step = eng.last_h2d_bytes
             return logits
-        for t, rc in zip(tokens, caches):
-            if not 0 <= int(t) < eng.model.vocab_size:
+        host_tokens = [0] * b if device_tokens is not None else [int(t) for t in tokens]
+        for t, rc in zip(host_tokens, caches):
+            if not 0 <= t < eng.model.vocab_size:
                 raise StepError(f"token id {t} is outside the vocabulary of {eng.model.vocab_size}")
             if rc.length + 1 > eng.max_positions:
                 raise StepError(f"request {rc.request_id!r}: context length of {eng.max_positions} exceeded")
@@ -220,7 +228,7 @@ class DecodeSession:
                     self._rec = rec
                     self._master = np.zeros(rec.total, dtype=np.int32)
                     self._master_ready = False
-                logits = rec.launch(lambda host: self._fill(host, [int(t) for t in tokens], caches, rec.chunk(ctx)))
+                logits = rec.launch(lambda host: self._fill(host, host_tokens, caches, rec.chunk(ctx)), device_tokens)
         except BaseException:
             for rc in prepared:
                 rc.abort()
@@ -233,6 +241,14 @@ class DecodeSession:
         ops.count_launches(rec.graph_launches)
         self.h2d_bytes_per_step = rec.total * 4
         return logits
+
+    def replays(self) -> bool:
+        """Whether the next step replays a recording (and so can take its tokens from the device)."""
+        if not self.use_graph:
+            return False
+        eng = self.engine
+        ctx = max(eng.cache.live[rid].length + 1 for rid in self.request_ids)
+        return recording_of(eng, len(self.request_ids), room_for(ctx, eng.max_positions), make=False) is not None
 
     def close(self) -> None:
         """The session is over.  Its recording stays with the engine for the next session of its size."""

@@ -14,7 +14,7 @@ from typing import Dict, Hashable, Iterable, List, Optional, Sequence, Union
 
 import torch
 
-from ..sampling import RequestSampling, SamplingParams, sample
+from ..sampling import RequestSampling, SamplingParams, sample, sample_async
 from .decode_loop import DecodeSession
 from .engine import Engine, EngineOptions, StepEntry
 from .scheduler import PlannedEntry, Request, Scheduler
@@ -64,6 +64,7 @@ class LLM:
         self._next_id = 0
         self._session: Optional[DecodeSession] = None
         self._session_ids = None
+        self.last_decode_h2d_bytes = 0      # metadata bytes the last recorded decode step copied to the device
 
     @staticmethod
     def _default_kv_tokens(model_dir: str, dtype: str, page_size: int, device: str) -> int:
@@ -105,6 +106,68 @@ class LLM:
             self._session.close()
         self._session, self._session_ids = None, None
 
+    def _account(self, sched: Scheduler, entries: Sequence[PlannedEntry], sampled: Dict[Hashable, int], index,
+                 on_token) -> List[Request]:
+        """Book a finished step: the scheduler's record, the sampling states, the statistics, the callback."""
+        wanting = [e for e in entries if e.want_last]
+        before = {e.request.request_id: len(e.request.output) for e in wanting}
+        done = sched.complete(entries, sampled)
+        self.stats.steps += 1
+        for e in wanting:
+            r = e.request
+            if len(r.output) > before[r.request_id]:
+                r.sampling.saw(r.output[-1])
+                self.stats.generated_tokens += 1
+                if on_token:
+                    on_token(index[r.request_id], r.output[-1])
+        return done
+
+    def _burst_length(self, entries: Sequence[PlannedEntry]) -> int:
+        """How many decode steps these entries can run back to back without a decision of the scheduler: none can
+        reach its max_tokens before the last of them, nothing depends on pages (full reservation), and no draw
+        needs the token before it on the host (no penalties).  Such steps run one ahead of the host: a step is
+        enqueued with the ids the device drew for the step before, and those ids are read while it runs."""
+        if self.reserve != "full" or not entries:
+            return 0
+        for e in entries:
+            r = e.request
+            if not (len(e.tokens) == 1 and e.want_last and r.decoding) or r.params.penalized:
+                return 0
+        return min(e.request.params.max_tokens - len(e.request.output) for e in entries) - 1
+
+    def _decode_burst(self, sched: Scheduler, entries: Sequence[PlannedEntry], steps: int, index, on_token) -> None:
+        requests = [e.request for e in entries]
+        ids = tuple(r.request_id for r in requests)
+        if self._session is None or self._session_ids != ids:
+            self._close_session()
+            self._session, self._session_ids = DecodeSession(self.engine, ids, plain_steps=4), ids
+        session = self._session
+        states = [r.sampling for r in requests]
+
+        def book(live: List[Request], tokens: List[int]) -> bool:
+            """The step that fed every live request's last token drew `tokens` (in the session's order)."""
+            fed = [PlannedEntry(r, [r.output[-1]], True) for r in live]
+            sampled = {r.request_id: tokens[requests.index(r)] for r in live}
+            return bool(self._account(sched, fed, sampled, index, on_token))
+
+        pending = None                      # the draw of the step before, not yet read
+        for _ in range(steps):
+            if pending is not None and not session.replays():
+                if book(requests, pending.result()):          # a plain step wants its tokens on the host
+                    return
+                pending = None
+            feed = pending.ids if pending is not None else [r.output[-1] for r in requests]
+            drawn = sample_async(session.step(feed), states)
+            if pending is not None and book(requests, pending.result()):
+                # Some request ended with the step before; the step in flight ran it once more for nothing.
+                live = [r for r in requests if r.state != "finished"]
+                book(live, drawn.result())
+                return
+            pending = drawn
+        if pending is not None:
+            book(requests, pending.result())
+        self.last_decode_h2d_bytes = session.h2d_bytes_per_step
+
     def generate(self, prompts: Sequence[Sequence[int]],
                  params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
                  on_token=None) -> List[GenerationOutput]:
@@ -138,6 +201,13 @@ class LLM:
                     break
                 raise RuntimeError("the scheduler planned an empty step while requests are waiting")
             t0 = time.perf_counter()
+            burst = self._burst_length(entries)
+            if burst >= 2:
+                self._decode_burst(sched, entries, burst, index, on_token)
+                stats.decode_seconds += time.perf_counter() - t0
+                for rid in sched.take_releases():
+                    self.engine.end(rid)
+                continue
             logits = self._run(entries)
             sampled: Dict[Hashable, int] = {}
             wanting = [e for e in entries if e.want_last]
@@ -152,16 +222,7 @@ class LLM:
                 stats.prefill_seconds += dt
             else:
                 stats.decode_seconds += dt
-            stats.steps += 1
-            before = {e.request.request_id: len(e.request.output) for e in wanting}
-            sched.complete(entries, sampled)
-            for e in wanting:
-                r = e.request
-                if len(r.output) > before[r.request_id]:
-                    r.sampling.saw(r.output[-1])
-                    stats.generated_tokens += 1
-                    if on_token:
-                        on_token(index[r.request_id], r.output[-1])
+            self._account(sched, entries, sampled, index, on_token)
             for rid in sched.take_releases():
                 self.engine.end(rid)
         self._close_session()

@@ -1,5 +1,5 @@
 """Sampling: settings, per-request state, the device draw."""
 from .params import GREEDY, SamplingParams
-from .sampler import RequestSampling, XorShift64, sample
+from .sampler import PendingSample, RequestSampling, XorShift64, sample, sample_async
 
-__all__ = ["GREEDY", "SamplingParams", "RequestSampling", "XorShift64", "sample"]
+__all__ = ["GREEDY", "SamplingParams", "PendingSample", "RequestSampling", "XorShift64", "sample", "sample_async"]

@@ -61,13 +61,33 @@ class RequestSampling:
 _ROW = struct.Struct("<ffffii")
 
 
+class PendingSample:
+    """Ids that have been drawn on the device and are on their way to the host.  `ids` is the device tensor
+    (int32 [rows]), which a next step may take as its input at once; `result()` waits for the copy."""
+    __slots__ = ("ids", "_host", "_event")
+
+    def __init__(self, ids: torch.Tensor, host: Optional[torch.Tensor], event):
+        self.ids, self._host, self._event = ids, host, event
+
+    def result(self) -> List[int]:
+        if self._host is None:
+            return []
+        self._event.synchronize()
+        return self._host.tolist()
+
+
 def sample(logits: torch.Tensor, states: Sequence[RequestSampling]) -> List[int]:
     """One token per row of `logits` (float32 [rows, vocab] on the device), row i drawn for states[i]."""
+    return sample_async(logits, states).result()
+
+
+def sample_async(logits: torch.Tensor, states: Sequence[RequestSampling]) -> PendingSample:
+    """As `sample`, but returns once the draw and the copy of the ids to the host are enqueued."""
     rows, vocab = logits.shape
     _cuda(logits)
     _need(logits.dtype is torch.float32 and len(states) == rows, "sample: float32 logits, one state per row")
     if rows == 0:
-        return []
+        return PendingSample(torch.empty(0, dtype=torch.int32, device=logits.device), None, None)
     dev = logits.device
     # Penalties first, in place: the logits are this step's own.
     items = [(r, t, c) for r, s in enumerate(states) if s.params.penalized for t, c in s.counts.items()]
@@ -100,7 +120,11 @@ def sample(logits: torch.Tensor, states: Sequence[RequestSampling]) -> List[int]
     out = torch.empty(rows, dtype=torch.int32, device=dev)
     _check(_fn("sampling", "llmx_sample")(_ptr(logits), rows, vocab, _ptr(params), _ptr(out), 1 if all_greedy else 0,
                                           _stream()), "sample")
-    return out.cpu().tolist()
+    host = torch.empty(rows, dtype=torch.int32, pin_memory=True)
+    host.copy_(out, non_blocking=True)
+    event = torch.cuda.Event()
+    event.record()
+    return PendingSample(out, host, event)
 
 
 _greedy_params: Dict[tuple, torch.Tensor] = {}

@@ -80,6 +80,33 @@ def test_end_of_sequence_and_length(model_dirs):
     assert greedy[2] not in masked.tokens and masked.finish_reason == "length"   # masked out of the draw
 
 
+def test_requests_end_at_different_steps_while_decoding_runs_ahead(model_dirs):
+    """Decoding steps are enqueued one ahead of the host, which reads a step's ids while the next one runs.  A
+    request that draws the end-of-sequence id is therefore seen a step late: its reply must stop where it would
+    have, the others' replies must not change, and every token is handed to the callback once, in order."""
+    from llmx_b200.engine.generate import LLM
+    from llmx_b200.sampling import SamplingParams
+    _, folder, page = model_dirs["A"]
+    llm = LLM(folder, dtype="float32", kv_tokens=1024, page_size=page, max_seqs=4)
+    llm.engine.model.eos_ids = ()
+    prompts = [helpers.random_ids(256, n, seed=40 + s) for s, n in enumerate([9, 17, 5, 12])]
+    limits = [30, 30, 30, 22]
+    alone = [llm.generate([p], SamplingParams(max_tokens=n, temp=0.0))[0].tokens for p, n in zip(prompts, limits)]
+    eos = alone[1][11]                                   # the second request ends at its twelfth token at the latest
+    llm.engine.model.eos_ids = (eos,)
+    want = [t[:t.index(eos)] if eos in t else t for t in alone]
+    assert any(len(w) < len(a) for w, a in zip(want, alone))
+    streamed = {i: [] for i in range(4)}
+    outs = llm.generate(prompts, [SamplingParams(max_tokens=n, temp=0.0) for n in limits],
+                        on_token=lambda i, t: streamed[i].append(t))
+    for i, out in enumerate(outs):
+        assert out.tokens == want[i], i
+        assert out.finish_reason == ("eos" if len(want[i]) < len(alone[i]) else "length")
+        assert streamed[i] == want[i]
+    llm.engine.cache.check()
+    assert llm.engine.cache.used_pages() == [0]
+
+
 def test_pages_running_out_pauses_and_recomputes_with_the_same_replies(model_dirs):
     from llmx_b200.engine.generate import LLM
     from llmx_b200.sampling import SamplingParams
