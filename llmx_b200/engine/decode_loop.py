@@ -9,7 +9,7 @@ slots, block tables, the keys per range of the split-KV kernel) lives in one dev
 kernels read.
 
 A recording depends on two numbers only: how many requests decode, and how many tokens of context
-its block tables have room for (in steps of `ROOM_STEP`).  The engine keeps the recordings it has
+its block tables have room for (in steps of 2,048 tokens).  The engine keeps the recordings it has
 made, so a session over other requests -- one has finished, another has joined -- finds its
 recording ready; a session only keeps the host's copy of its requests' metadata.  The first
 decode step at a new batch size runs through `Engine.step`, which also loads and warms the
@@ -24,16 +24,9 @@ import numpy as np
 import torch
 
 from ..parts.base import GroupView, StepBatch
-from .engine import Engine, StepEntry, StepError, _pad4
+from .engine import Engine, StepEntry, StepError, _pad4, room_for
 
-ROOM_STEP = 2048           # a recording's room for context is a multiple of this
 MAX_RECORDINGS = 32        # recordings an engine keeps (least recently used goes first)
-
-
-def room_for(context: int, max_positions: int) -> int:
-    """Tokens of context the recording for a step at `context` tokens has room for: at least one
-    `ROOM_STEP` ahead, so that a session changes recordings rarely."""
-    return min((context // ROOM_STEP + 2) * ROOM_STEP, max(max_positions, 1))
 
 
 class DecodeRecording:

@@ -53,6 +53,44 @@ def _pad4(n: int) -> int:
     return (n + 3) & ~3
 
 
+ROOM_STEP = 2048           # a recording's room for context is a multiple of this
+
+
+def room_for(context: int, max_positions: int) -> int:
+    """Tokens of context a recorded step at `context` tokens has room for: at least one `ROOM_STEP`
+    ahead, so that recordings change rarely."""
+    return min((context // ROOM_STEP + 2) * ROOM_STEP, max(max_positions, 1))
+
+
+class StepLayout:
+    """Where a step's metadata lies in its one int32 buffer (sections padded to 16 bytes):
+    0 token ids [rows], 1 positions [rows], 2 request of each row [rows], 3 first row [requests],
+    4 row count [requests], 5 history [requests], 6 state slots [requests], 7 rows whose logits are wanted,
+    then for every cache group its block tables [requests, max_pages] and the rows' cache slots [rows],
+    then `extra` ints (a recorded step keeps the keys per range of the split-KV kernel there)."""
+
+    def __init__(self, counts: Sequence[int], wanted: int, max_pages: Sequence[int], extra: int = 0):
+        self.counts = [int(c) for c in counts]
+        self.requests, self.rows, self.wanted = len(self.counts), sum(self.counts), wanted
+        self.max_pages = list(max_pages)
+        self.starts = [0] * self.requests
+        for r in range(1, self.requests):
+            self.starts[r] = self.starts[r - 1] + self.counts[r - 1]
+        self.sizes = [self.rows, self.rows, self.rows, self.requests, self.requests, self.requests, self.requests, wanted]
+        for mp in self.max_pages:
+            self.sizes += [self.requests * mp, self.rows]
+        if extra:
+            self.sizes.append(extra)
+        self.offsets, at = [], 0
+        for size in self.sizes:
+            self.offsets.append(at)
+            at += _pad4(max(size, 1))
+        self.total = at
+
+    def section(self, buf, i: int):
+        return buf[self.offsets[i]:self.offsets[i] + self.sizes[i]]
+
+
 class Engine:
     def __init__(self, model, options: EngineOptions):
         """`model` must be loaded (`Model.load`) on `options.device` in `options.dtype`."""
@@ -133,73 +171,65 @@ class Engine:
         if len(self.cache.live) + new > self.options.max_requests:
             raise StepError(f"more than {self.options.max_requests} live requests")
 
-    def _build_batch(self, entries: Sequence[StepEntry], caches) -> StepBatch:
-        n_req = len(entries)
-        counts = [len(e.tokens) for e in entries]
-        rows = sum(counts)
+    def _fill_batch(self, buf: np.ndarray, layout: StepLayout, entries: Sequence[StepEntry], caches) -> List[int]:
+        """Write the step's metadata into `buf` (int32, `layout.total` values); returns the histories."""
         history = [rc.length for rc in caches]
-        starts = np.zeros(n_req, dtype=np.int64)
-        np.cumsum(counts[:-1], out=starts[1:])
-        wanted = sum(len(e.want) for e in entries)
-        n_groups = len(self.cache.groups)
-        max_pages = [max(1, max(len(rc.tables[g].pages) for rc in caches)) for g in range(n_groups)]
-
-        # One int32 buffer for the whole step: sections padded to 16 bytes, one host-to-device copy.
-        sizes = [rows, rows, rows, n_req, n_req, n_req, n_req, wanted]
-        for g in range(n_groups):
-            sizes += [n_req * max_pages[g], rows]
-        offsets, at = [], 0
-        for s in sizes:
-            offsets.append(at)
-            at += _pad4(max(s, 1))
-        host = torch.empty(at, dtype=torch.int32, pin_memory=True)
-        buf = host.numpy()
         buf[:] = 0
-
-        def sec(i):
-            return buf[offsets[i]:offsets[i] + sizes[i]]
-
-        tok, pos, rreq = sec(0), sec(1), sec(2)
+        tok, pos, rreq = layout.section(buf, 0), layout.section(buf, 1), layout.section(buf, 2)
         for r, e in enumerate(entries):
-            a, n = int(starts[r]), counts[r]
+            a, n = layout.starts[r], layout.counts[r]
             tok[a:a + n] = np.asarray(e.tokens, dtype=np.int64)
             pos[a:a + n] = np.arange(history[r], history[r] + n)
             rreq[a:a + n] = r
-        sec(3)[:] = starts
-        sec(4)[:] = counts
-        sec(5)[:] = history
-        sec(6)[:] = [rc.state_slot for rc in caches]
-        lr, k = sec(7), 0
+        layout.section(buf, 3)[:] = layout.starts
+        layout.section(buf, 4)[:] = layout.counts
+        layout.section(buf, 5)[:] = history
+        layout.section(buf, 6)[:] = [rc.state_slot for rc in caches]
+        lr, k = layout.section(buf, 7), 0
         for r, e in enumerate(entries):
             for w in e.want:
-                lr[k] = int(starts[r]) + int(w)
+                lr[k] = layout.starts[r] + int(w)
                 k += 1
-        for g in range(n_groups):
-            ps = self.cache.groups[g].page_size
-            bt = sec(8 + 2 * g).reshape(n_req, max_pages[g])
-            sl = sec(9 + 2 * g)
+        for g, grp in enumerate(self.cache.groups):
+            ps = grp.page_size
+            bt = layout.section(buf, 8 + 2 * g).reshape(layout.requests, layout.max_pages[g])
+            sl = layout.section(buf, 9 + 2 * g)
             for r, rc in enumerate(caches):
                 pages = rc.tables[g].pages
                 bt[r, :len(pages)] = pages
                 parr = np.asarray(pages, dtype=np.int64)
-                p = np.arange(history[r], history[r] + counts[r])
-                a = int(starts[r])
-                sl[a:a + counts[r]] = parr[p // ps] * ps + p % ps
+                p = np.arange(history[r], history[r] + layout.counts[r])
+                a = layout.starts[r]
+                sl[a:a + layout.counts[r]] = parr[p // ps] * ps + p % ps
             # A released page (-1) is never addressed: the window keeps queries above it.
+        return history
+
+    def _batch_views(self, dev: torch.Tensor, layout: StepLayout, caches, history: Sequence[int],
+                     max_context: int) -> StepBatch:
+        """The StepBatch whose device tensors are the sections of `dev`."""
+        n_req = layout.requests
+        groups = [GroupView(layout.section(dev, 8 + 2 * g).view(n_req, layout.max_pages[g]), layout.section(dev, 9 + 2 * g),
+                            grp.page_size) for g, grp in enumerate(self.cache.groups)]
+        return StepBatch(rows=layout.rows, requests=n_req, token_ids=layout.section(dev, 0),
+                         positions=layout.section(dev, 1), row_request=layout.section(dev, 2),
+                         row_start=layout.section(dev, 3), row_count=layout.section(dev, 4),
+                         history=layout.section(dev, 5), state_slots=layout.section(dev, 6),
+                         logit_rows=layout.section(dev, 7), groups=groups, caches=self.cache,
+                         host_row_start=list(layout.starts), host_row_count=list(layout.counts),
+                         host_history=list(history), host_state_slots=[rc.state_slot for rc in caches],
+                         max_row_count=max(layout.counts), max_context=max_context)
+
+    def _build_batch(self, entries: Sequence[StepEntry], caches) -> StepBatch:
+        counts = [len(e.tokens) for e in entries]
+        n_groups = len(self.cache.groups)
+        max_pages = [max(1, max(len(rc.tables[g].pages) for rc in caches)) for g in range(n_groups)]
+        layout = StepLayout(counts, sum(len(e.want) for e in entries), max_pages)
+        # One int32 buffer for the whole step, one host-to-device copy.
+        host = torch.empty(layout.total, dtype=torch.int32, pin_memory=True)
+        history = self._fill_batch(host.numpy(), layout, entries, caches)
         dev = host.to(self.device, non_blocking=True)
         self.last_h2d_bytes = host.numel() * 4
-
-        def dsec(i):
-            return dev[offsets[i]:offsets[i] + sizes[i]]
-
-        groups = [GroupView(dsec(8 + 2 * g).view(n_req, max_pages[g]), dsec(9 + 2 * g), self.cache.groups[g].page_size)
-                  for g in range(n_groups)]
-        return StepBatch(rows=rows, requests=n_req, token_ids=dsec(0), positions=dsec(1), row_request=dsec(2),
-                         row_start=dsec(3), row_count=dsec(4), history=dsec(5), state_slots=dsec(6),
-                         logit_rows=dsec(7), groups=groups, caches=self.cache,
-                         host_row_start=[int(s) for s in starts], host_row_count=counts, host_history=history,
-                         host_state_slots=[rc.state_slot for rc in caches],
-                         max_row_count=max(counts), max_context=max(h + c for h, c in zip(history, counts)))
+        return self._batch_views(dev, layout, caches, history, max(h + c for h, c in zip(history, counts)))
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run one batch.  Returns float32 logits [wanted, vocab] on the device, in the order of the
