@@ -158,7 +158,8 @@ def main() -> int:
     kv_tokens = max(max_batch * per_request, args.prefill_tokens + page)
     torch.cuda.set_device(0)
     engine = Engine.from_config(cfg, seed=0, options=EngineOptions(dtype="bfloat16", kv_tokens=kv_tokens,
-                                                                   page_size=page, max_requests=max_batch))
+                                                                   page_size=page, max_requests=max_batch,
+                                                                   record_after=2))
     model = engine.model
     gen = torch.Generator(device="cuda")
     gen.manual_seed(1)
@@ -251,7 +252,7 @@ def main() -> int:
         for i in range(warmup + reps):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            engine.step([StepEntry("prefill", prompt, [tokens_n - 1])])
+            engine.step([StepEntry("prefill", prompt, [tokens_n - 1])], record=True)
             e1.record()
             torch.cuda.synchronize()
             engine.end("prefill")

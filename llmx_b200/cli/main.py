@@ -213,9 +213,9 @@ def cmd_bench(argv: List[str]) -> int:
     seqs = _int("--seqs", given.get("--seqs", "1"), 1)
     depth = _int("--depth", given.get("--depth", str(p)), 1)
     dtype = _dtype(given.get("--dtype", "auto"))
-    kv = -(-(max(p, depth) + g + 64) // 64) * 64 * seqs
+    kv = -(-(max(p, depth) + g + 2 + 64) // 64) * 64 * seqs
     engine = Engine.from_dir(given["--model"], EngineOptions(dtype=dtype, kv_tokens=kv, max_requests=seqs,
-                                                             device=given.get("--device", "cuda:0")))
+                                                             device=given.get("--device", "cuda:0"), record_after=2))
     vocab = engine.model.vocab_size
     # Fixed ids spread over the vocabulary (the reference's bench_ids, src/cli/main.cpp:1185-1189).
     state = 12345
@@ -235,25 +235,33 @@ def cmd_bench(argv: List[str]) -> int:
         torch.cuda.synchronize()
         return time.perf_counter() - t
 
+    from ..engine.decode_loop import DecodeSession
     prompt = ids(p)
     pp, tg = [], []
-    for rep in range(reps + 1):                       # the first repeat is the untimed warm-up
-        dt = timed(lambda: engine.step([StepEntry("p", prompt, [p - 1])]))
+    for rep in range(reps + 3):                       # the first repeats are the untimed warm-up: they load the
+        timed_rep = rep >= 3                          # kernels, and a shape that comes again gets recorded
+        dt = timed(lambda: engine.step([StepEntry("p", prompt, [p - 1])], record=True))
         engine.end("p")
-        if rep:
+        if timed_rep:
             pp.append(p / dt)
+        if not timed_rep and rep:
+            continue                                  # one warm-up round of decoding is enough
         hist = ids(depth)
         for s in range(seqs):
             engine.step([StepEntry(s, hist, [])])
         toks = ids(seqs)
+        session = DecodeSession(engine, list(range(seqs)))
+        for _ in range(2):                            # the session's plain step and its recording are not timed
+            session.step(toks)
 
         def decode():
             for _ in range(g):
-                engine.step([StepEntry(s, [toks[s]], [0]) for s in range(seqs)])
+                session.step(toks)
         dt = timed(decode)
+        session.close()
         for s in range(seqs):
             engine.end(s)
-        if rep:
+        if timed_rep:
             tg.append(g * seqs / dt)
 
     def stat(v):

@@ -47,6 +47,8 @@ class EngineOptions:
     page_size: int = 16
     max_requests: int = 64           # live requests (state slots; block-table rows)
     device: str = "cuda:0"
+    record_after: int = 16           # plain steps of one shape before `step(..., record=True)` records it: making
+    #                                  a recording costs about as much as ten to twenty plain steps save
 
 
 def _pad4(n: int) -> int:
@@ -111,6 +113,10 @@ class Engine:
         # sizes whose kernels a plain step has already run (see decode_loop.py).
         self.decode_recordings = OrderedDict()
         self.decode_warmed = set()
+        # Recorded steps of other shapes by (rows per request, wanted places, room), and how often a shape
+        # that has no recording yet has come (see recorded_step.py).
+        self.step_recordings = OrderedDict()
+        self._shapes_seen: Dict[tuple, int] = {}
         self.last_h2d_bytes = 0
 
     # -- construction ------------------------------------------------------------
@@ -231,9 +237,37 @@ class Engine:
         self.last_h2d_bytes = host.numel() * 4
         return self._batch_views(dev, layout, caches, history, max(h + c for h, c in zip(history, counts)))
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def _recording_for(self, entries: Sequence[StepEntry], caches):
+        """The recording of this step's shape, made now if the shape has been seen often enough; else None."""
+        from . import recorded_step
+        counts = tuple(len(e.tokens) for e in entries)
+        wants = tuple(tuple(int(w) for w in e.want) for e in entries)
+        context = max(rc.length + n for rc, n in zip(caches, counts))
+        key = (counts, wants, room_for(context, self.max_positions))
+        rec = self.step_recordings.get(key)
+        if rec is not None:
+            self.step_recordings.move_to_end(key)
+            return rec
+        seen = self._shapes_seen.get(key, 0)
+        if seen < self.options.record_after:
+            if len(self._shapes_seen) > 4096:
+                self._shapes_seen.clear()
+            self._shapes_seen[key] = seen + 1
+            return None
+        rec = recorded_step.StepRecording(self, counts, wants, key[2])
+        self.step_recordings[key] = rec
+        self._shapes_seen.pop(key, None)
+        while len(self.step_recordings) > recorded_step.MAX_STEP_RECORDINGS:
+            self.step_recordings.popitem(last=False)
+        return rec
+
+    def step(self, entries: Sequence[StepEntry], record: bool = False) -> Optional[torch.Tensor]:
         """Run one batch.  Returns float32 logits [wanted, vocab] on the device, in the order of the
         entries and of each entry's `want`, or None when nothing is wanted.
+
+        `record`: the caller expects steps of this shape (rows per request, wanted places) to come again;
+        once one has, the step is recorded as a CUDA graph and replayed from then on (recorded_step.py).
+        The logits of a replayed step are valid until the next step of the same shape.
 
         Raises StepError for a batch it refuses, CacheExhausted when the pages do not suffice;
         in both cases no request has changed.
@@ -252,8 +286,12 @@ class Engine:
                 rc.prepare(len(e.tokens))
                 prepared.append(rc)
             with torch.cuda.device(self.device):
-                batch = self._build_batch(entries, caches)
-                logits = self.model.forward(batch)
+                recording = self._recording_for(entries, caches) if record and self.model.recordable else None
+                if recording is not None:
+                    logits = recording.run(self, entries, caches)
+                else:
+                    batch = self._build_batch(entries, caches)
+                    logits = self.model.forward(batch)
         except BaseException:
             for rc in prepared:
                 rc.abort()

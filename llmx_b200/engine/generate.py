@@ -99,7 +99,7 @@ class LLM:
             return self._session.step([e.tokens[0] for e in entries])
         self._close_session()
         return self.engine.step([StepEntry(e.request.request_id, e.tokens, [len(e.tokens) - 1] if e.want_last else [])
-                                 for e in entries])
+                                 for e in entries], record=True)
 
     def _close_session(self) -> None:
         if self._session is not None:

@@ -105,14 +105,14 @@ def tokens_needed(steps: List[dict], page: int = 64) -> int:
     return worst
 
 
-def run_trace(engine, steps: List[dict]) -> Dict[Tuple[str, int], np.ndarray]:
+def run_trace(engine, steps: List[dict], record: bool = False) -> Dict[Tuple[str, int], np.ndarray]:
     """Drive Engine.step with a trace; returns {(request, position): logits row}."""
     from llmx_b200.engine import StepEntry
     out: Dict[Tuple[str, int], np.ndarray] = {}
     at: Dict[str, int] = {}
     for s in steps:
         entries = [StepEntry(e["id"], e["tokens"], e["want"]) for e in s["entries"]]
-        logits = engine.step(entries)
+        logits = engine.step(entries, record=record)
         rows = None if logits is None else logits.float().cpu().numpy()
         k = 0
         for e in s["entries"]:

@@ -252,3 +252,42 @@ def test_layers_of_8b_width_under_cutting(wide_model_dir, dtype):
                                                                page_size=16, max_requests=4))
         _check(engine, wide_model_dir, steps, requests, dtype)
         del engine
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "wide"])
+def test_recorded_steps_of_any_shape(model_dirs, wide_model_dir, name, dtype):
+    """A step's shape that comes again is recorded and replayed (prompt portions, portions beside decoding rows,
+    several rows of one request): the same trace run four times over, the last runs from recordings, each against
+    the plain implementation; the pool is so small that later runs find their pages elsewhere."""
+    from llmx_b200 import ops_tc
+    from llmx_b200.engine import Engine, EngineOptions
+    if name == "wide":
+        folder, page, vocab = wide_model_dir, 16, WIDE["vocab_size"]
+        lengths = [150, 70, 33, 2]
+    else:
+        d16, d32, page = model_dirs[name]
+        folder, vocab = (d32 if dtype == "float32" else d16), CONFIGS[name][0]["vocab_size"]
+        lengths = [70, 9, 40, 33]
+    requests = {f"q{i}": helpers.random_ids(vocab, n, seed=7 + i) for i, n in enumerate(lengths)}
+    steps = helpers.trace_mixed(requests)
+    engine = Engine.from_dir(folder, EngineOptions(dtype=dtype, kv_tokens=helpers.tokens_needed(steps) + 3 * page,
+                                                   page_size=page, max_requests=5, record_after=2))
+    for run in range(4):
+        if run == 2:                                   # shift the pool: the recorded steps must not remember pages
+            engine.step([helpers_entry("pad", helpers.random_ids(vocab, 2 * page + 1, seed=1))])
+        got = helpers.run_trace(engine, steps, record=True)
+        ops_tc.check_errors()
+        worst, scale, where = helpers.compare(got, requests, folder, dtype == "bfloat16")
+        assert worst <= TOL[dtype] * scale, f"run {run}: largest difference {worst:.3e} at {where} (logit scale {scale:.3f})"
+    assert len(engine.step_recordings) > 0
+    replayed = sum(1 for s in steps if (tuple(len(e["tokens"]) for e in s["entries"])) in {k[0] for k in engine.step_recordings})
+    assert replayed >= len(steps) // 2
+    engine.end("pad")
+    engine.cache.check()
+    assert engine.cache.used_pages() == [0] * len(engine.cache.groups)
+
+
+def helpers_entry(rid, tokens):
+    from llmx_b200.engine import StepEntry
+    return StepEntry(rid, tokens, [])
