@@ -281,8 +281,11 @@ def main() -> int:
     pf_value, pf_ms, pf_frac = run_prefill(args.prefill_tokens, 3, 3)
     points = {}
     if not args.no_points:
-        points["decode_b1"] = round(run_decode(1, args.steps, args.warmup, e2e=False)[0], 1)
-        points["decode_b64"] = round(run_decode(64, max(args.steps // 2, 8), args.warmup, e2e=False)[0], 1)
+        for name, b, k in (("decode_b1", 1, args.steps), ("decode_b64", 64, max(args.steps // 2, 8))):
+            v, step_ms, _, _ = run_decode(b, k, args.warmup, e2e=False)
+            points[name] = round(v, 1)
+            # the same roofline as the headline's: bytes the step must read over its time, against the copy bandwidth
+            points[name + "_hbm_frac"] = round(decode_bytes(b, args.context) / (step_ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
     clock_record = clocks.stop()
     ops_tc.check_errors()
     achieved = decode_bytes(args.batch, args.context) / (ms * 1e-3) / 1e9
