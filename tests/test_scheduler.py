@@ -172,3 +172,23 @@ def test_a_request_that_cannot_fit_even_alone_ends_with_reason_cache():
     sched.total_pages = [3]                        # ...but the pool then turns out smaller (3 pages = 48 tokens)
     FakeEngine(cache).run(sched)
     assert r.finish_reason == "cache" and 0 < len(r.output) < 34
+
+
+def test_step_layout_and_room():
+    """Where a step's metadata lies in its buffer, and the room a recorded step leaves for context."""
+    from llmx_b200.engine.engine import StepLayout, room_for
+    lay = StepLayout([3, 1, 5], wanted=2, max_pages=[4, 2], extra=1)
+    assert (lay.requests, lay.rows, lay.starts) == (3, 9, [0, 3, 4])
+    assert lay.sizes == [9, 9, 9, 3, 3, 3, 3, 2, 12, 9, 6, 9, 1]
+    # sections do not overlap, start on 16-byte boundaries and fill the buffer
+    ends = [o + max(s, 1) for o, s in zip(lay.offsets, lay.sizes)]
+    assert all(o % 4 == 0 for o in lay.offsets)
+    assert all(e <= nxt for e, nxt in zip(ends, lay.offsets[1:] + [lay.total]))
+    import numpy as np
+    buf = np.arange(lay.total, dtype=np.int32)
+    assert lay.section(buf, 3).tolist() == list(range(lay.offsets[3], lay.offsets[3] + 3))
+    # an empty section (nothing wanted) still has a place of its own
+    assert StepLayout([2], wanted=0, max_pages=[1]).sizes[7] == 0
+    # room: a multiple of 2,048 at least one multiple ahead, never beyond what the model can address
+    assert room_for(1, 1 << 20) == 4096 and room_for(2047, 1 << 20) == 4096 and room_for(2048, 1 << 20) == 6144
+    assert room_for(8193, 1 << 20) == 12288 and room_for(8193, 9000) == 9000
