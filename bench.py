@@ -265,7 +265,7 @@ def main() -> int:
         return T * 1e3 / ms, ms, flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops"]
 
     if args.only == "prefill":
-        pf_value, pf_ms, pf_frac = run_prefill(args.prefill_tokens, 2, 2)
+        pf_value, pf_ms, pf_frac = run_prefill(args.prefill_tokens, 3, 3)
         print(json.dumps({"only": "prefill", "value": round(pf_value, 1), "ms": round(pf_ms, 3), "frac": round(pf_frac, 4),
                           "layers": args.layers}))
         return 0

@@ -242,9 +242,11 @@ __global__ void head_norm_rope_128_kernel(const float* __restrict__ qkv, int qkv
     constexpr int D = 128;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int per_row = heads + kv_heads;
-    const long long first = ((long long)blockIdx.x * (blockDim.x >> 5) + warp) * U;
-    if (first >= (long long)rows * per_row) return;
-    const int row = (int)(first / per_row), j0 = (int)(first % per_row);
+    // 32-bit arithmetic (the launcher sees to it that rows * per_row fits): a 64-bit division costs this
+    // kernel, which is bound by the instructions it issues, a tenth of its time.
+    const unsigned first = (blockIdx.x * (blockDim.x >> 5) + warp) * U;
+    if (first >= (unsigned)rows * (unsigned)per_row) return;
+    const int row = (int)(first / (unsigned)per_row), j0 = (int)(first - (unsigned)row * (unsigned)per_row);
     const float* row_src = qkv + (size_t)row * qkv_stride;
     const int slot = slots[row];
     float4 v[U], raw[U];
@@ -332,6 +334,7 @@ LLMX_EXPORT int llmx_head_norm_rope_kv(const float* qkv, int qkv_stride, int k_o
     if (fast) {
         // Many rows: four items a warp keep enough loads in flight; few rows: one item a warp keeps more warps busy.
         const int per_row = heads + kv_heads;
+        if ((long long)rows * per_row >= (1ll << 31)) return LLMX_ERR_UNSUPPORTED;
         const int u = rows >= 64 && per_row % 4 == 0 ? 4 : rows >= 64 && per_row % 2 == 0 ? 2 : 1;
 #define LLMX_HNR(T, U) launch_head_norm_rope_128<T, U>(qkv, qkv_stride, k_offset, v_offset, q_weight, k_weight, eps, cos_table, \
                                                        sin_table, positions, slots, q_out, cache, rows, heads, kv_heads, page_size, stream)
