@@ -122,6 +122,58 @@ def test_pages_running_out_pauses_and_recomputes_with_the_same_replies(model_dir
     assert tight.engine.cache.used_pages() == [0]
 
 
+@pytest.mark.parametrize("reserve,kv_tokens", [("full", 640), ("prompt", 208)])
+def test_random_workloads_against_each_request_alone(model_dirs, reserve, kv_tokens):
+    """Rounds of random prompts, limits and end-of-sequence ids through `generate` -- with recorded steps of every
+    shape that comes twice, decoding run ahead of the host, and (with the small pool) requests paused and
+    recomputed -- each reply against the same request continued alone, one plain step a token."""
+    import random
+    import torch
+    from llmx_b200.engine import Engine, EngineOptions, StepEntry
+    from llmx_b200.engine.generate import LLM
+    from llmx_b200.sampling import SamplingParams
+    _, folder, _ = model_dirs["A"]
+    vocab = CONFIGS["A"][0]["vocab_size"]
+    rng = random.Random(5)
+    ref = Engine.from_dir(folder, EngineOptions(dtype="float32", kv_tokens=256, page_size=16, max_requests=1))
+
+    def alone(prompt, limit, eos):
+        out, logits = [], ref.step([StepEntry("ref", prompt, [len(prompt) - 1])])
+        while True:
+            token = int(torch.argmax(logits[0]).item())
+            if token == eos:
+                reason = "eos"
+                break
+            out.append(token)
+            if len(out) >= limit:
+                reason = "length"
+                break
+            logits = ref.step([StepEntry("ref", [token], [0])])
+        ref.end("ref")
+        return out, reason
+
+    engine = Engine.from_dir(folder, EngineOptions(dtype="float32", kv_tokens=kv_tokens, page_size=16, max_requests=4,
+                                                   record_after=2))
+    llm = LLM(engine, ubatch=48, max_seqs=4, reserve=reserve)
+    for _ in range(12):
+        eos = rng.randrange(vocab) if rng.random() < 0.7 else -1
+        engine.model.eos_ids = (eos,) if eos >= 0 else ()
+        n = rng.randrange(1, 9)
+        prompts = [[rng.randrange(vocab) for _ in range(rng.randrange(1, 90))] for _ in range(n)]
+        limits = [rng.randrange(1, 45) for _ in range(n)]
+        streamed = {i: [] for i in range(n)}
+        outs = llm.generate(prompts, [SamplingParams(max_tokens=k, temp=0.0) for k in limits],
+                            on_token=lambda i, t: streamed[i].append(t))
+        for i, out in enumerate(outs):
+            want, reason = alone(prompts[i], limits[i], eos)
+            assert (out.tokens, out.finish_reason, streamed[i]) == (want, reason, want), (i, len(prompts[i]), limits[i])
+        engine.cache.check()
+        assert engine.cache.used_pages() == [0]
+    assert engine.decode_recordings and engine.step_recordings
+    if reserve == "prompt":
+        assert llm.stats.preemptions > 0
+
+
 def test_command_line(model_dirs, tmp_path):
     d16, _, _ = model_dirs["D"]
     exe = [sys.executable, os.path.join(ROOT, "bin", "llmx")]
