@@ -291,3 +291,52 @@ def test_recorded_steps_of_any_shape(model_dirs, wide_model_dir, name, dtype):
 def helpers_entry(rid, tokens):
     from llmx_b200.engine import StepEntry
     return StepEntry(rid, tokens, [])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["D", "wide"])
+def test_decode_sessions_replay_their_recordings(model_dirs, wide_model_dir, name, dtype):
+    """Prompts by plain steps, then their last tokens one by one through decode sessions: the first step of a new
+    batch size is plain, the next records, the rest replay; token ids come from the host or from a device tensor;
+    a request leaves and the remaining ones carry on in a new session; every row against the plain implementation."""
+    import torch
+    from llmx_b200 import ops_tc
+    from llmx_b200.engine import Engine, EngineOptions, StepEntry
+    from llmx_b200.engine.decode_loop import DecodeSession
+    if name == "wide":
+        folder, page, vocab = wide_model_dir, 16, WIDE["vocab_size"]
+    else:
+        d16, d32, page = model_dirs[name]
+        folder, vocab = (d32 if dtype == "float32" else d16), CONFIGS[name][0]["vocab_size"]
+    lengths = {"a": 70, "b": 41, "c": 55}
+    requests = {rid: helpers.random_ids(vocab, n, seed=90 + n) for rid, n in lengths.items()}
+    tail = 24
+    engine = Engine.from_dir(folder, EngineOptions(dtype=dtype, kv_tokens=4 * 96, page_size=page, max_requests=4))
+    got = {}
+    for rid, ids in requests.items():
+        head = len(ids) - tail
+        logits = engine.step([StepEntry(rid, ids[:head], list(range(head)))]).float().cpu().numpy()
+        for p in range(head):
+            got[(rid, p)] = logits[p]
+    live = list(requests)
+    at = {rid: len(requests[rid]) - tail for rid in live}
+    session = DecodeSession(engine, live)
+    for step in range(tail):
+        if step == 10:                      # "b" leaves: the others carry on in a session (and a recording) of two
+            session.close()
+            engine.end("b")
+            live.remove("b")
+            session = DecodeSession(engine, live)
+        tokens = [requests[rid][at[rid]] for rid in live]
+        feed = torch.tensor(tokens, dtype=torch.int32, device="cuda") if step % 3 == 2 else tokens
+        logits = session.step(feed).float().cpu().numpy()
+        for k, rid in enumerate(live):
+            got[(rid, at[rid])] = logits[k]
+            at[rid] += 1
+    session.close()
+    ops_tc.check_errors()
+    assert {b for (b, _room) in engine.decode_recordings} == {3, 2}
+    requests_seen = {rid: requests[rid][:at[rid]] for rid in requests}
+    worst, scale, where = helpers.compare({k: v for k, v in got.items() if k[1] < len(requests_seen[k[0]])}, requests_seen,
+                                          folder, dtype == "bfloat16")
+    assert worst <= TOL[dtype] * scale, f"largest difference {worst:.3e} at {where} (logit scale {scale:.3f})"
