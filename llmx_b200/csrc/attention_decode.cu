@@ -132,7 +132,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             tc::mbar_init(&full_bar[s], 1);
-            tc::mbar_init(&empty_bar[s], CONSUMERS / 2);      // the two warps that read the stage
+            tc::mbar_init(&empty_bar[s], CONSUMERS);          // every consumer warp has seen the stage full (two read it)
         }
         *abort_flag = 0;
         tc::fence_barrier_init();
@@ -198,9 +198,13 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
                 const int id = id_next;
                 const int nxt = (it + 1) * PAGES_PER_STAGE + lane;
                 id_next = nxt < n_pages ? table[nxt] : 0;
-                if (!tc::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, error_word, ERR_DEC_PRODUCER)) break;
+                bool ok = tc::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, error_word, ERR_DEC_PRODUCER);
                 const int here = min(PAGES_PER_STAGE, n_pages - it * PAGES_PER_STAGE);
-                if (lane == 0) tc::mbar_expect_tx(&full_bar[stage], (uint32_t)(here * cfg::PAGE_BYTES));
+                // The bytes a phase expects must be announced before any of its copies can land (a copy that
+                // completes first is not counted later): lane 0 announces, then the lanes issue.
+                if (lane == 0 && ok) tc::mbar_expect_tx(&full_bar[stage], (uint32_t)(here * cfg::PAGE_BYTES));
+                ok = __all_sync((1u << PAGES_PER_STAGE) - 1u, ok);
+                if (!ok) break;
                 // One copy brings the head's keys and values of the page: [plane][half][slot][64 columns].
                 if (lane < here)
                     tc::tma_load_5d(tiles + stage * cfg::STAGE_BYTES + lane * cfg::PAGE_BYTES, &cache_map, 0, 0, 0, g,
@@ -231,14 +235,18 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
         }
         // Warps 0 and 1 take the even stages, warps 2 and 3 the odd ones; of a stage's four pages a warp takes
         // two, as one tile of 32 keys: twice the independent work between a warp's waits, half the rescaling.
-        // Every warp waits for every stage, also those it does not read: a wait tells a barrier's phases apart
-        // by their parity only, so a warp must not skip one.
+        // Every warp waits for every stage, also those it does not read, and tells the producer so: a wait tells
+        // a barrier's phases apart by their parity only, so a warp must neither skip a phase nor be so far behind
+        // that the stage is filled again before it has looked.
         const int pair = warp & 1, group = warp >> 1;
         for (int it = 0; it < iters; ++it) {
             const int stage = it % STAGES;
             const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
             if (!tc::mbar_wait(&full_bar[stage], phase, abort_flag, error_word, ERR_DEC_CONSUMER)) break;
-            if ((it & 1) != group) continue;
+            if ((it & 1) != group) {
+                if (lane == 0) tc::mbar_arrive(&empty_bar[stage]);
+                continue;
+            }
             const int page_index = it * PAGES_PER_STAGE + 2 * pair;
             if (page_index < n_pages) {
                 const int key0 = kv_begin + page_index * PAGE;

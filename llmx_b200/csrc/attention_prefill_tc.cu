@@ -1,10 +1,12 @@
 // Tiled causal attention for prompt portions on the 5th-generation tensor cores (head width 128).
 //
-// A block serves one (request, kv head, 2 * 128 / ratio consecutive new rows): two row tiles, each 128 / ratio
+// A work item is one (request, kv head, 2 * 128 / ratio consecutive new rows): two row tiles, each 128 / ratio
 // new rows times the `ratio` query heads of the group = the 128 rows of both products,
 //     S[128 rows, 128 keys] = Q K^T        O[128 rows, 128 columns] += P V
 // issued as tcgen05.mma by one thread.  The two row tiles share every key stage and take turns on the tensor
-// core: while one tile's softmax runs, the other's products do.
+// core: while one tile's softmax runs, the other's products do.  A launch has one block of threads per SM at
+// most; a block walks its share of the items (heavy and light ones in turn) without giving up its barriers
+// and tensor memory, and fetches an item's first keys while the item before drains.
 //
 //   tensor memory   S of tile 0, S of tile 1, O of tile 0, O of tile 1: 4 x 128 columns.  P (bfloat16, two to a
 //                   column) is written over the first 64 columns of the tile's S and is the P V product's A
@@ -100,7 +102,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                        __nv_bfloat16* __restrict__ out, const int* __restrict__ req_list,
                        const int* __restrict__ row_start, const int* __restrict__ row_count,
                        const int* __restrict__ history, const int* __restrict__ block_tables, int table_stride,
-                       int heads, int kv_heads, int window, float scale_log2, int* error_word) {
+                       int heads, int kv_heads, int window, float scale_log2, int n_req, int max_blocks,
+                       int* error_word) {
     pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -112,7 +115,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     uint64_t* v_empty = bars + 7;            // [2 stages]  free once the last P V that reads the stage has run
     uint64_t* s_full = bars + 9;             // [2 tiles]   S of the tile is written (and, once more at the end, O)
     uint64_t* p_full = bars + 11;            // [2 tiles]   P of the tile is written, O rescaled if need be
-    uint32_t* tmem_slot = (uint32_t*)(bars + 13);
+    uint64_t* q_empty = bars + 13;           // [1]         the item's last Q K^T has run: Q may be overwritten
+    uint64_t* o_read = bars + 14;            // [2 tiles]   the tile's softmax warps have read the item's output
+    uint32_t* tmem_slot = (uint32_t*)(bars + 16);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -121,6 +126,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 
     if (threadIdx.x == 0) {
         tc::mbar_init(q_full, 1);
+        tc::mbar_init(q_empty, 1);
         for (int i = 0; i < 2; ++i) {
             tc::mbar_init(&k_full[i], 1);
             tc::mbar_init(&v_full[i], 1);
@@ -128,6 +134,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             tc::mbar_init(&v_empty[i], 1);
             tc::mbar_init(&s_full[i], 1);
             tc::mbar_init(&p_full[i], TILE_WARPS);
+            tc::mbar_init(&o_read[i], TILE_WARPS);
         }
         *abort_flag = 0;
         tc::fence_barrier_init();
@@ -151,111 +158,166 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();
 
-    // Which rows this block serves (after the wait: the metadata may come from the step's copy).
-    const int r = req_list[blockIdx.z], g = blockIdx.y;
-    const int n_q = row_count[r];
-    const int n_blocks = (n_q + 2 * tokens_per_tile - 1) / (2 * tokens_per_tile);
-    const bool active = (int)blockIdx.x < n_blocks;
-    const int blk = active ? n_blocks - 1 - blockIdx.x : 0;          // the rows with the most keys start first
-    const int q0 = row_start[r], hist = history[r];
-    const int t0 = blk * 2 * tokens_per_tile;
-    int kv_begin = 0;
-    if (window > 0) kv_begin = (max(0, hist + t0 - window + 1) / KEYS) * KEYS;
-    // Per row tile: its first new row, how many it has, and how many key stages reach its last row.
-    int tile_t0[2], tile_rows[2], tile_iters[2];
+    // ---- The work: items (request, kv head, block of 2 x 128 / ratio new rows), the blocks with the most keys first.
+    // A launch has at most one block of threads per SM; block c takes the items c, 2G - 1 - c, 2G + c, ... (G blocks:
+    // back and forth over the list, so that each gets heavy and light ones), one after the other without giving up
+    // its barriers and tensor memory.  Every role walks the same items and keeps count of the barrier phases it has
+    // used, which go on from item to item.
+    const int per_block_row = kv_heads * n_req;
+    const int total_items = max_blocks * per_block_row;
+    struct Item {
+        int r, g, q0, hist, kv_begin, kv_end, n_iter, last_tile;
+        int tile_t0[2], tile_rows[2], tile_iters[2];
+    };
+    auto item_at = [&](int k, Item& it) -> bool {
+        const int G = gridDim.x, c = blockIdx.x;
+        const long long idx = (k & 1) ? (long long)(k + 1) * G - 1 - c : (long long)k * G + c;
+        if (idx >= total_items) return false;
+        const int xi = (int)(idx / per_block_row), rem = (int)(idx % per_block_row);
+        it.g = rem % kv_heads;
+        it.r = req_list[rem / kv_heads];
+        const int n_q = row_count[it.r];
+        const int n_blocks = (n_q + 2 * tokens_per_tile - 1) / (2 * tokens_per_tile);
+        const bool active = xi < n_blocks;
+        const int blk = active ? n_blocks - 1 - xi : 0;
+        it.q0 = row_start[it.r];
+        it.hist = history[it.r];
+        const int t0 = blk * 2 * tokens_per_tile;
+        it.kv_begin = window > 0 ? (max(0, it.hist + t0 - window + 1) / KEYS) * KEYS : 0;
+        // Per row tile: its first new row, how many it has, and how many key stages reach its last row.
 #pragma unroll
-    for (int t = 0; t < 2; ++t) {
-        tile_t0[t] = t0 + t * tokens_per_tile;
-        const int count = active ? max(0, min(tokens_per_tile, n_q - tile_t0[t])) : 0;
-        tile_rows[t] = count * ratio;
-        tile_iters[t] = count > 0 ? (hist + tile_t0[t] + count - kv_begin + KEYS - 1) / KEYS : 0;
-    }
-    const int last_tile = tile_iters[1] > 0 ? 1 : 0;                 // the later rows see the most keys
-    const int n_iter = tile_iters[last_tile];
-    const int kv_end = hist + min(n_q, t0 + 2 * tokens_per_tile);
+        for (int t = 0; t < 2; ++t) {
+            it.tile_t0[t] = t0 + t * tokens_per_tile;
+            const int count = active ? max(0, min(tokens_per_tile, n_q - it.tile_t0[t])) : 0;
+            it.tile_rows[t] = count * ratio;
+            it.tile_iters[t] = count > 0 ? (it.hist + it.tile_t0[t] + count - it.kv_begin + KEYS - 1) / KEYS : 0;
+        }
+        it.last_tile = it.tile_iters[1] > 0 ? 1 : 0;                 // the later rows see the most keys
+        it.n_iter = it.tile_iters[it.last_tile];
+        it.kv_end = it.hist + min(n_q, t0 + 2 * tokens_per_tile);
+        return true;
+    };
 
     if (warp == 0) {
-        if (n_iter > 0) {
+        // Lane = (keys or values, page of the stage, half of the head): one copy of 16 slots x 64 columns each.
+        const int plane = lane >> 4, p = (lane >> 1) & 7, half = lane & 1;
+        uint64_t* full = plane ? v_full : k_full;
+        uint64_t* empty = plane ? v_empty : k_empty;
+        uint32_t kv_uses = 0, items_done = 0;      // stage uses and items so far: they number the barriers' phases
+        bool ok = true;
+        Item it;
+        for (int k = 0; ok && item_at(k, it); ++k) {
+            if (it.n_iter == 0) continue;
             if (lane == 0) {
-                // Q: rows [token][head of the group], both 64-column halves, one box per row tile.
-                tc::mbar_expect_tx(q_full, (uint32_t)((last_tile + 1) * OPERAND_BYTES));
-                tc::tma_load_5d(smem + SMEM_Q, &q_map, 0, 0, q0 + tile_t0[0], 0, g, q_full);
-                if (last_tile) tc::tma_load_5d(smem + SMEM_Q + OPERAND_BYTES, &q_map, 0, 0, q0 + tile_t0[1], 0, g, q_full);
+                // Q: rows [token][head of the group], both 64-column halves, one box per row tile; the item
+                // before must be done with the buffer (its last Q K^T has run).
+                ok = tc::mbar_wait(q_empty, (items_done & 1u) ^ 1u, abort_flag, error_word, ERR_TCA_PRODUCER);
+                if (ok) {
+                    tc::mbar_expect_tx(q_full, (uint32_t)((it.last_tile + 1) * OPERAND_BYTES));
+                    tc::tma_load_5d(smem + SMEM_Q, &q_map, 0, 0, it.q0 + it.tile_t0[0], 0, it.g, q_full);
+                    if (it.last_tile)
+                        tc::tma_load_5d(smem + SMEM_Q + OPERAND_BYTES, &q_map, 0, 0, it.q0 + it.tile_t0[1], 0, it.g, q_full);
+                }
             }
-            // Lane = (keys or values, page of the stage, half of the head): one copy of 16 slots x 64 columns each.
-            const int plane = lane >> 4, p = (lane >> 1) & 7, half = lane & 1;
-            uint64_t* full = plane ? v_full : k_full;
-            uint64_t* empty = plane ? v_empty : k_empty;
-            const int* table = block_tables + (size_t)r * table_stride + kv_begin / PAGE;
-            const int n_pages = (kv_end - kv_begin + PAGE - 1) / PAGE;
+            ++items_done;
+            const int* table = block_tables + (size_t)it.r * table_stride + it.kv_begin / PAGE;
+            const int n_pages = (it.kv_end - it.kv_begin + PAGE - 1) / PAGE;
             // A stage's page id is read one stage ahead, so the table's latency is off the copies' path.
             int id_next = p < n_pages ? table[p] : 0;
-            for (int j = 0; j < n_iter; ++j) {
-                const int st = j % KV_STAGES;
-                const uint32_t ph = ((uint32_t)(j / KV_STAGES) & 1u) ^ 1u;
+            for (int j = 0; j < it.n_iter; ++j, ++kv_uses) {
+                const int st = kv_uses % KV_STAGES;
+                const uint32_t ph = ((kv_uses / KV_STAGES) & 1u) ^ 1u;
                 const int here = min(PAGES_PER_STAGE, n_pages - j * PAGES_PER_STAGE);
                 const int id = id_next;
                 const int nxt = (j + 1) * PAGES_PER_STAGE + p;
                 id_next = nxt < n_pages ? table[nxt] : 0;
-                if (!tc::mbar_wait(&empty[st], ph, abort_flag, error_word, ERR_TCA_PRODUCER)) break;
-                if ((lane & 15) == 0) tc::mbar_expect_tx(&full[st], (uint32_t)(here * PAGE * D * 2));
+                if (!tc::mbar_wait(&empty[st], ph, abort_flag, error_word, ERR_TCA_PRODUCER)) ok = false;
+                // The bytes a phase expects must be announced before any of its copies can land (a copy that
+                // completes first is not counted later): the half-warp's first lane announces, then all issue.
+                if ((lane & 15) == 0 && ok) tc::mbar_expect_tx(&full[st], (uint32_t)(here * PAGE * D * 2));
+                ok = __all_sync(plane ? 0xffff0000u : 0x0000ffffu, ok);
+                if (!ok) break;
                 if (p < here)
                     tc::tma_load_5d(smem + SMEM_KV + st * STAGE_BYTES + plane * OPERAND_BYTES + half * HALF_BYTES + p * PAGE * 128,
-                                    &cache_map, 0, 0, half, g, id * 2 + plane, &full[st]);
+                                    &cache_map, 0, 0, half, it.g, id * 2 + plane, &full[st]);
             }
+            ok = __all_sync(0xffffffffu, ok);
         }
     } else if (warp == 1) {
-        if (n_iter > 0 && tc::elect_one()) {
-            bool ok = tc::mbar_wait(q_full, 0, abort_flag, error_word, ERR_TCA_MMA);
-            // S of tile t = Q_t K_j^T.  The products of one thread run in the order they are issued, so this
-            // one, issued after P V of (t, j - 1), also finds that product done with the columns it writes.
-            auto issue_qk = [&](int t, int j) {
-                const uint32_t q_addr = tc::smem_u32(smem + SMEM_Q + t * OPERAND_BYTES);
-                const uint32_t k_addr = tc::smem_u32(smem + SMEM_KV + (j % KV_STAGES) * STAGE_BYTES);
+        if (tc::elect_one()) {
+            uint32_t kv_uses = 0, items_done = 0, p_done[2] = {0, 0}, tile_items[2] = {0, 0};
+            bool ok = true;
+            Item it;
+            for (int k = 0; ok && item_at(k, it); ++k) {
+                if (it.n_iter == 0) continue;
+                ok = tc::mbar_wait(q_full, items_done & 1u, abort_flag, error_word, ERR_TCA_MMA);
+                ++items_done;
+                const uint32_t kv0 = kv_uses;              // the item's stage j is stage use kv0 + j
+                // S of tile t = Q_t K_j^T.  The products of one thread run in the order they are issued, so this
+                // one, issued after P V of (t, j - 1), also finds that product done with the columns it writes.
+                auto issue_qk = [&](int t, int j) {
+                    const uint32_t q_addr = tc::smem_u32(smem + SMEM_Q + t * OPERAND_BYTES);
+                    const uint32_t k_addr = tc::smem_u32(smem + SMEM_KV + ((kv0 + j) % KV_STAGES) * STAGE_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-                    tc::mma_bf16_ss(tmem_base + t * KEYS, tc::smem_desc_k_sw128(q_addr + off),
-                                    tc::smem_desc_k_sw128(k_addr + off), IDESC_QK, kk > 0 ? 1u : 0u);
+                    for (int kk = 0; kk < D / 16; ++kk) {
+                        const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+                        tc::mma_bf16_ss(tmem_base + t * KEYS, tc::smem_desc_k_sw128(q_addr + off),
+                                        tc::smem_desc_k_sw128(k_addr + off), IDESC_QK, kk > 0 ? 1u : 0u);
+                    }
+                    tc::mma_commit(&s_full[t]);
+                };
+                // O of tile t += P V_j, P from the tile's tensor-memory columns.
+                auto issue_pv = [&](int t, int j) -> bool {
+                    const uint32_t use = kv0 + j;
+                    const int st = use % KV_STAGES;
+                    if (!tc::mbar_wait(&v_full[st], (use / KV_STAGES) & 1u, abort_flag, error_word, ERR_TCA_MMA)) return false;
+                    if (!tc::mbar_wait(&p_full[t], p_done[t] & 1u, abort_flag, error_word, ERR_TCA_MMA)) return false;
+                    ++p_done[t];
+                    tc::tc_fence_after();
+                    const uint32_t v_addr = tc::smem_u32(smem + SMEM_KV + st * STAGE_BYTES + OPERAND_BYTES);
+#pragma unroll
+                    for (int kk = 0; kk < KEYS / 16; ++kk)
+                        tc::mma_bf16_ts(tmem_base + TMEM_O + t * D, tmem_base + t * KEYS + kk * 8,
+                                        smem_desc_mn_sw128(v_addr + kk * 16 * 128, HALF_BYTES), IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
+                    return true;
+                };
+                if (ok) ok = tc::mbar_wait(&k_full[kv0 % KV_STAGES], (kv0 / KV_STAGES) & 1u, abort_flag, error_word, ERR_TCA_MMA);
+                // A tile's first scores of an item complete s_full right after the item before completed it with
+                // the tile's output; a waiter tells phases apart by parity only, so the tile's softmax warps must
+                // have seen the one (and read the output) before the other may happen.
+                for (int t = 0; t <= it.last_tile && ok; ++t) {
+                    if (tile_items[t] > 0)
+                        ok = tc::mbar_wait(&o_read[t], (tile_items[t] - 1) & 1u, abort_flag, error_word, ERR_TCA_MMA);
+                    ++tile_items[t];
                 }
-                tc::mma_commit(&s_full[t]);
-            };
-            // O of tile t += P V_j, P from the tile's tensor-memory columns.
-            auto issue_pv = [&](int t, int j) -> bool {
-                const int st = j % KV_STAGES;
-                if (!tc::mbar_wait(&v_full[st], (uint32_t)(j / KV_STAGES) & 1u, abort_flag, error_word, ERR_TCA_MMA)) return false;
-                if (!tc::mbar_wait(&p_full[t], (uint32_t)j & 1u, abort_flag, error_word, ERR_TCA_MMA)) return false;
-                tc::tc_fence_after();
-                const uint32_t v_addr = tc::smem_u32(smem + SMEM_KV + st * STAGE_BYTES + OPERAND_BYTES);
-#pragma unroll
-                for (int kk = 0; kk < KEYS / 16; ++kk)
-                    tc::mma_bf16_ts(tmem_base + TMEM_O + t * D, tmem_base + t * KEYS + kk * 8,
-                                    smem_desc_mn_sw128(v_addr + kk * 16 * 128, HALF_BYTES), IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
-                return true;
-            };
-            if (ok) ok = tc::mbar_wait(&k_full[0], 0, abort_flag, error_word, ERR_TCA_MMA);
-            if (ok) {
-                tc::tc_fence_after();
-                for (int t = 0; t <= last_tile; ++t) issue_qk(t, 0);
-                tc::mma_commit(&k_empty[0]);
-            }
-            for (int j = 0; j < n_iter && ok; ++j) {
-                for (int t = 0; t <= last_tile && ok; ++t) {
-                    if (j >= tile_iters[t]) continue;
-                    ok = issue_pv(t, j);
-                    if (!ok) break;
-                    if (t == last_tile) tc::mma_commit(&v_empty[j % KV_STAGES]);
-                    if (j + 1 < tile_iters[t]) {
-                        const int st = (j + 1) % KV_STAGES;
-                        ok = tc::mbar_wait(&k_full[st], (uint32_t)((j + 1) / KV_STAGES) & 1u, abort_flag, error_word, ERR_TCA_MMA);
+                if (ok) {
+                    tc::tc_fence_after();
+                    for (int t = 0; t <= it.last_tile; ++t) issue_qk(t, 0);
+                    tc::mma_commit(&k_empty[kv0 % KV_STAGES]);
+                    if (it.n_iter == 1) tc::mma_commit(q_empty);          // the item's last Q K^T
+                }
+                for (int j = 0; j < it.n_iter && ok; ++j) {
+                    for (int t = 0; t <= it.last_tile && ok; ++t) {
+                        if (j >= it.tile_iters[t]) continue;
+                        ok = issue_pv(t, j);
                         if (!ok) break;
-                        tc::tc_fence_after();
-                        issue_qk(t, j + 1);
-                        if (t == last_tile) tc::mma_commit(&k_empty[st]);
-                    } else {
-                        tc::mma_commit(&s_full[t]);          // the tile's output is complete
+                        if (t == it.last_tile) tc::mma_commit(&v_empty[(kv0 + j) % KV_STAGES]);
+                        if (j + 1 < it.tile_iters[t]) {
+                            const uint32_t use = kv0 + j + 1;
+                            ok = tc::mbar_wait(&k_full[use % KV_STAGES], (use / KV_STAGES) & 1u, abort_flag, error_word, ERR_TCA_MMA);
+                            if (!ok) break;
+                            tc::tc_fence_after();
+                            issue_qk(t, j + 1);
+                            if (t == it.last_tile) {
+                                tc::mma_commit(&k_empty[use % KV_STAGES]);
+                                if (j + 2 == it.n_iter) tc::mma_commit(q_empty);      // the item's last Q K^T
+                            }
+                        } else {
+                            tc::mma_commit(&s_full[t]);          // the tile's output is complete
+                        }
                     }
                 }
+                kv_uses += it.n_iter;
             }
         }
     } else {
@@ -264,19 +326,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         const int t = (warp - 2) / TILE_WARPS;
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
-        const int M = tile_rows[t], iters = tile_iters[t];
-        if (iters > 0) {
+        const uint32_t s_addr = tmem_base + t * KEYS + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t o_addr = tmem_base + TMEM_O + t * D + ((uint32_t)(quarter * 32) << 16);
+        uint32_t s_done = 0;                        // completions of this tile's s_full that have been waited for
+        bool ok = true;
+        Item it;
+        for (int k = 0; ok && item_at(k, it); ++k) {
+            const int M = it.tile_rows[t], iters = it.tile_iters[t];
+            if (iters == 0) continue;
+            const int g = it.g, q0 = it.q0, hist = it.hist, kv_begin = it.kv_begin;
             const bool valid = row < M;
-            const int ti = tile_t0[t] + min(row, M - 1) / ratio;
+            const int ti = it.tile_t0[t] + min(row, M - 1) / ratio;
             const int pos = hist + ti;
             const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-            const uint32_t s_addr = tmem_base + t * KEYS + ((uint32_t)(quarter * 32) << 16);
-            const uint32_t o_addr = tmem_base + TMEM_O + t * D + ((uint32_t)(quarter * 32) << 16);
             float m_used = -INFINITY, l_run = 0.0f;
-            bool ok = true;
             for (int j = 0; j < iters; ++j) {
-                ok = tc::mbar_wait(&s_full[t], (uint32_t)j & 1u, abort_flag, error_word, ERR_TCA_SOFTMAX);
+                ok = tc::mbar_wait(&s_full[t], s_done & 1u, abort_flag, error_word, ERR_TCA_SOFTMAX);
                 if (!ok) break;
+                ++s_done;
                 tc::tc_fence_after();
                 const int key0 = kv_begin + j * KEYS;
                 const bool need_mask = key0 + KEYS - 1 > pos || key0 < lo;
@@ -353,8 +420,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 if (lane == 0) tc::mbar_arrive(&p_full[t]);
             }
             // ---- O / l once the last P V has run
-            if (ok) ok = tc::mbar_wait(&s_full[t], (uint32_t)iters & 1u, abort_flag, error_word, ERR_TCA_SOFTMAX);
+            if (ok) ok = tc::mbar_wait(&s_full[t], s_done & 1u, abort_flag, error_word, ERR_TCA_SOFTMAX);
             if (ok) {
+                ++s_done;
                 tc::tc_fence_after();
                 const float inv = 1.0f / l_run;
                 __nv_bfloat16* dst = out + ((size_t)(q0 + ti) * heads + g * ratio + row % ratio) * D;
@@ -375,6 +443,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                         }
                     }
                 }
+                // The output has been read: the next item's products may write the tile's columns.
+                tc::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive(&o_read[t]);
             }
         }
     }
@@ -447,9 +519,19 @@ LLMX_EXPORT int llmx_attn_prefill_tc(const void* cache_map, const void* q, void*
     CUtensorMap q_map;
     if (int e = make_q_map(&q_map, q, (uint64_t)total_rows, heads, kv_heads)) return e;
     const int tokens_per_block = 2 * ROWS / (heads / kv_heads);
-    dim3 grid((max_rows + tokens_per_block - 1) / tokens_per_block, kv_heads, n_req);
+    const int max_blocks = (max_rows + tokens_per_block - 1) / tokens_per_block;
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+    }
+    // One block of threads per SM at most (a block takes the SM's shared and tensor memory); each walks its items.
+    const long long items = (long long)max_blocks * kv_heads * n_req;
+    if (items >= (1ll << 31)) return LLMX_ERR_UNSUPPORTED;
+    dim3 grid((unsigned)(items < sm_count ? items : sm_count), 1, 1);
     launch_kernel(attn_prefill_tc_kernel, grid, dim3(THREADS), (size_t)SMEM_BYTES, stream, q_map,
                   *(const CUtensorMap*)cache_map, (__nv_bfloat16*)out, req_list, row_start, row_count, history,
-                  block_tables, table_stride, heads, kv_heads, window, scale * attn::LOG2E, error_word);
+                  block_tables, table_stride, heads, kv_heads, window, scale * attn::LOG2E, n_req, max_blocks, error_word);
     return launch_status();
 }

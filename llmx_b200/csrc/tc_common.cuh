@@ -32,6 +32,9 @@ __device__ __forceinline__ void fence_barrier_init() {
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// Arrive and announce `bytes` of copies that will complete on the barrier in this phase.  The announcement must be
+// made before any of those copies can land: bytes that land first are not made up for by a later announcement, and
+// the phase then never completes (seen when the announcing lane lagged the issuing lanes by microseconds).
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }

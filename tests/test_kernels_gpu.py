@@ -277,6 +277,26 @@ def test_attention_tiled_bf16(heads, kv_heads, head_dim, layout, window, spike):
     assert np.abs(got - ref).max() <= 2e-2 * max(1.0, np.abs(ref).max())
 
 
+@pytest.mark.parametrize("history", [0, 320, 448])
+def test_attention_prefill_blocks_walk_several_items(history):
+    """More work items than SMs: a block of the tcgen05 prefill kernel then walks several (request, kv head, rows)
+    items one after the other, its barriers' phases going on from item to item.  Forty requests of 64 new rows
+    after the same history make 320 items of equal length, which is what once let a barrier complete twice
+    before a waiting warp had looked."""
+    from llmx_b200 import ops_attn, ops_tc
+    heads, kv_heads, head_dim = 32, 8, 128
+    layout = [(history, 64)] * 38 + [(history + 100, 33), (7, 130)]
+    q, cache, step, group, ref = _attention_case(torch.bfloat16, heads, kv_heads, head_dim, 16, layout, None, seed=21, spike=True)
+    for _ in range(3):                                   # the fault was one of timing: run it more than once
+        out = torch.full_like(q, float("nan"))
+        ops_attn.paged_attention_bf16(q, cache, out, step, group, heads, kv_heads, head_dim, None, 1.0 / math.sqrt(head_dim))
+        torch.cuda.synchronize()
+        ops_tc.check_errors()
+        got = out.float().cpu().numpy()
+        assert np.isfinite(got).all()
+        assert np.abs(got - ref).max() <= 2e-2 * max(1.0, np.abs(ref).max())
+
+
 @pytest.mark.parametrize("splits", [1, 2, 3, 7, 16])
 def test_attention_decode_any_number_of_key_ranges(splits):
     from llmx_b200 import ops_attn, ops_tc
