@@ -155,8 +155,24 @@ def main() -> int:
     max_batch = max(args.batch, 1 if args.no_points else 64)
     head_start = -(-args.context // 2048) * (args.batch - 1)          # see run_generate
     per_request = -(-(args.context + args.steps + max(args.warmup, 8) + head_start + 64) // page) * page
-    kv_tokens = max(max_batch * per_request, args.prefill_tokens + page)
     torch.cuda.set_device(0)
+    if args.only == "prefill":
+        max_batch = 1
+    # What fits: the weights and the cache of `max_batch` requests must leave room for the steps' buffers.  The
+    # batch 64 point is given up first (said in the line), then the run is refused.
+    kv_bytes_token = 2 * args.layers * cfg.num_key_value_heads * cfg.head_dim * 2
+    weights = 2 * (args.layers * (cfg.hidden_size * (cfg.q_width + 2 * cfg.kv_width) + cfg.q_width * cfg.hidden_size
+                                  + 3 * cfg.hidden_size * cfg.intermediate_size)
+                   + cfg.vocab_size * cfg.hidden_size * (1 if cfg.tie_word_embeddings else 2))
+    room = torch.cuda.get_device_properties(0).total_memory * 0.9 - weights - (8 << 30)
+    if max_batch > args.batch and max_batch * per_request * kv_bytes_token > room:
+        max_batch, args.no_points = args.batch, True
+        print(f"note: the batch 64 point does not fit beside {weights / 1e9:.0f} GB of weights and is left out", file=sys.stderr)
+    if max_batch * per_request * kv_bytes_token > room and args.only != "prefill":
+        print(f"bench: a cache of {max_batch} x {per_request} tokens ({max_batch * per_request * kv_bytes_token / 1e9:.0f} GB) does not "
+              f"fit beside the weights ({weights / 1e9:.0f} GB); give a smaller --batch, --context or --layers", file=sys.stderr)
+        return 1
+    kv_tokens = max(max_batch * per_request, args.prefill_tokens + page) if args.only != "prefill" else args.prefill_tokens + page
     engine = Engine.from_config(cfg, seed=0, options=EngineOptions(dtype="bfloat16", kv_tokens=kv_tokens,
                                                                    page_size=page, max_requests=max_batch,
                                                                    record_after=2))
