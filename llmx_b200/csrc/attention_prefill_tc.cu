@@ -10,7 +10,7 @@
 //
 //   tensor memory   S of tile 0, S of tile 1, O of tile 0, O of tile 1: 4 x 128 columns.  P (bfloat16, two to a
 //                   column) is written over the first 64 columns of the tile's S and is the P V product's A
-//                   operand straight from tensor memory; O stays in tensor memory for the whole block.
+//                   operand straight from tensor memory; O stays in tensor memory for the whole item.
 //   warp 0          TMA producer: both Q tiles once (a 5-D box lays [token][head] rows out as the instruction's
 //                   K-major operand), then 128 keys a stage, two stages, keys and values on barriers of their
 //                   own; every lane issues one of the stage's 32 copies (8 pages x 2 halves x keys/values).
