@@ -256,14 +256,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         else tc::tmem_ld_32x16(taddr + BN + c, u);
                         tc::tmem_wait_ld();
                         if (n < N) {
-                            __nv_bfloat16* C = (__nv_bfloat16*)C_;
+                            // silu(g) * u in float32 with the fast exponential and reciprocal (a few units in the
+                            // last place, far below the bfloat16 rounding that follows): with short inner widths
+                            // this epilogue, not the products, sets the kernel's time.
+                            __nv_bfloat16* C = (__nv_bfloat16*)C_ + (size_t)(w.mt * BN + c) * N + n;
+                            const int m_left = M - (w.mt * BN + c);
 #pragma unroll
                             for (int j = 0; j < CH; ++j) {
-                                const int m = w.mt * BN + c + j;
-                                if (m < M) {
-                                    const float g = __uint_as_float(r[j]), up = __uint_as_float(u[j]);
-                                    C[(size_t)m * N + n] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * up);
-                                }
+                                const float g = __uint_as_float(r[j]), up = __uint_as_float(u[j]);
+                                const float act = __fdividef(g, 1.0f + __expf(-g)) * up;
+                                if (j < m_left) C[(size_t)j * N] = __float2bfloat16_rn(act);
                             }
                         }
                     } else {
