@@ -34,7 +34,6 @@ register_signature("attention_prefill", "llmx_attn_prefill",
 
 PAGE = 16
 WAVE_BLOCKS = 148 * 2            # decode blocks that run at once: two per SM
-MIN_KEYS_PER_SPLIT = 1024        # below this a range's fixed cost (start-up, combining) outweighs what it saves
 
 
 def supported(heads: int, kv_heads: int, head_dim: int, page_size: int) -> bool:
@@ -106,11 +105,21 @@ def cache_map(cache: torch.Tensor) -> CacheMap:
 
 
 def decode_schedule(n_requests: int, kv_heads: int, max_context: int) -> Tuple[int, int]:
-    """(key ranges, keys per range): as many ranges as fit one wave of blocks, none shorter than
-    MIN_KEYS_PER_SPLIT keys (measured on a B200: 1 request at 8,192 keys is fastest with 8-9 ranges, 8 requests
-    with 3-4, 64 requests with 1)."""
+    """(key ranges, keys per range).  As many ranges as fit one wave of blocks, but no more than pay: measured on a
+    B200 (32 heads over 8, graph-timed), 1 to 4 requests are fastest with 8 ranges from 1,024 keys on (16 from
+    8,192), 8 requests with 4, 16 requests with 2 from 2,048 keys on, 32 and more with 1; below 1,024 keys one range
+    is best whatever the batch (combining ranges costs about 3 us)."""
     blocks = max(n_requests * kv_heads, 1)
-    splits = max(1, min(WAVE_BLOCKS // blocks, max_context // MIN_KEYS_PER_SPLIT))
+    wave = WAVE_BLOCKS // blocks
+    if max_context < 1024:
+        want = 1
+    elif blocks >= 128:
+        want = max_context // 1024
+    elif max_context < 8192:
+        want = min(8, max_context // 128)
+    else:
+        want = 16
+    splits = max(1, min(wave, want))
     chunk = -(-(-(-max_context // 64)) // splits) * 64
     splits = max(1, -(-max_context // chunk))
     return splits, chunk
