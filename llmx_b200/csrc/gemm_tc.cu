@@ -23,6 +23,11 @@
 // A third form, DUAL, computes two products that share the token tile -- rows n and n + N/2 of
 // the weight (gate and up of a gated feed-forward) -- into two accumulators and writes
 // silu(gate) * up as bfloat16, so the [tokens, 2 * intermediate] float32 matrix never exists.
+// A fourth form, HEADS, is the q/k/v product of an attention layer with heads of 128: the operands
+// change sides (128 tokens on the instruction's M side, 128 or 256 weight rows = one or two whole heads on
+// the narrow side), so that a thread of the epilogue holds whole heads of one token.  It norms and rotates
+// them there and writes the queries and the cache rows as bfloat16: the float32 [tokens, q + 2 kv] matrix and
+// the kernel that read it back never exist (src/model/arch/qwen3.hpp:280-290 for the order of operations).
 //
 // The reference has no tensor-core path for this product (its kernels: f32.gpu:1034-1084).
 #include "tc_common.cuh"
@@ -39,6 +44,22 @@ constexpr int THREADS = 64 + EPI_WARPS * 32;
 enum : int { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_ATOMIC = 2, MODE_SWIGLU = 3 };
 enum : int { ERR_PRODUCER = 101, ERR_MMA_FULL = 102, ERR_MMA_ACC = 103, ERR_EPILOGUE = 104 };
 
+// What the HEADS epilogue needs to finish heads of 128 values: norm weights (null: no norm), the rotation's
+// tables [positions, 64] (null: no rotation), each token's position and cache slot (negative: not stored),
+// the queries' output [tokens, heads * 128] and the layer's cache [pages, 2, kv_heads, page_size, 128].
+struct HeadsEpilogue {
+    const float* q_weight;
+    const float* k_weight;
+    const float* cos_table;
+    const float* sin_table;
+    const int* positions;
+    const int* slots;
+    __nv_bfloat16* q_out;
+    __nv_bfloat16* cache;
+    float eps;
+    int heads, kv_heads, page_size;
+};
+
 template <int BN, bool DUAL>
 struct Cfg {
     static constexpr int A_TILES = DUAL ? 2 : 1;
@@ -52,7 +73,7 @@ struct Cfg {
     static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 8 ? 8 : (BUDGET / STAGE_BYTES);
     static constexpr int ACC_COLS = A_TILES * BN;        // columns of one accumulator set
     static constexpr int TMEM_COLS = (2 * ACC_COLS) < 32 ? 32 : (2 * ACC_COLS);
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/ + 1024 /*norm weights*/;
     static_assert(TMEM_COLS <= 512, "two accumulator sets must fit tensor memory");
 };
 
@@ -102,10 +123,123 @@ struct Scheduler {
     }
 };
 
-template <int BN, bool STREAMK, bool DUAL>
+
+__device__ __forceinline__ uint32_t pack2_bf16(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// The HEADS epilogue for one thread: token `tok` (this thread's lane of tensor memory), the tile's heads in the
+// columns from `tcol` on.  A query or key head is normed (the sum of squares in the order of the per-head kernel
+// in rowwise.cu: lane partials of four values, then the butterfly's tree, so both give the same bits), rotated
+// as pairs (i, i + 64) and stored; a value head is stored as it is.  Every thread issues the tensor-memory loads
+// (they are warp-wide); only those with a token, and for keys and values a cache slot, store.
+template <int BN>
+__device__ __forceinline__ void heads_epilogue(const HeadsEpilogue& hp, const float* norm_w, uint32_t tcol, int tok,
+                                               int tokens, int feature0, int features) {
+    const bool live = tok < tokens;
+    const int pos = live ? hp.positions[tok] : 0;
+    const int slot = live ? hp.slots[tok] : -1;
+    const int q_width = hp.heads * 128, kv_width = hp.kv_heads * 128;
+#pragma unroll 1
+    for (int hh = 0; hh < BN / 128; ++hh, tcol += 128) {
+        const int f = feature0 + hh * 128;
+        if (f >= features) break;
+        const float* weight = nullptr;
+        __nv_bfloat16* dst = nullptr;
+        bool rotate = false, normed = false;
+        if (f < q_width) {
+            weight = norm_w;
+            normed = hp.q_weight != nullptr;
+            rotate = hp.cos_table != nullptr;
+            if (live) dst = hp.q_out + ((size_t)tok * hp.heads + f / 128) * 128;
+        } else {
+            const bool is_k = f < q_width + kv_width;
+            const int g = (f - q_width - (is_k ? 0 : kv_width)) / 128;
+            weight = norm_w + 128;
+            normed = is_k && hp.k_weight != nullptr;
+            rotate = is_k && hp.cos_table != nullptr;
+            if (slot >= 0) {
+                const int page = slot / hp.page_size, off = slot % hp.page_size;
+                dst = hp.cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * hp.kv_heads + g) * hp.page_size + off) * 128;
+            }
+        }
+        float rr = 1.0f;
+        if (normed) {
+            float p[32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tc::tmem_ld_32x32(tcol + 32 * c, r);
+                tc::tmem_wait_ld();
+#pragma unroll
+                for (int l = 0; l < 8; ++l) {
+                    const float x0 = __uint_as_float(r[4 * l]), x1 = __uint_as_float(r[4 * l + 1]);
+                    const float x2 = __uint_as_float(r[4 * l + 2]), x3 = __uint_as_float(r[4 * l + 3]);
+                    p[8 * c + l] = fmaf(x0, x0, fmaf(x1, x1, fmaf(x2, x2, x3 * x3)));
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int i = 0; i < o; ++i) p[i] = p[i] + p[i + o];
+            rr = 1.0f / sqrtf(p[0] / 128.0f + hp.eps);
+        }
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+            // values 32 half .. + 31 (a) and their partners 64 further on (b)
+            uint32_t a[32], b[32];
+            tc::tmem_ld_32x32(tcol + 32 * half, a);
+            tc::tmem_ld_32x32(tcol + 64 + 32 * half, b);
+            tc::tmem_wait_ld();
+            if (dst == nullptr) continue;
+            const float* cs = rotate ? hp.cos_table + (size_t)pos * 64 + 32 * half : nullptr;
+            const float* sn = rotate ? hp.sin_table + (size_t)pos * 64 + 32 * half : nullptr;
+#pragma unroll
+            for (int j8 = 0; j8 < 32; j8 += 8) {
+                float ya[8], yb[8];
+#pragma unroll
+                for (int j4 = 0; j4 < 8; j4 += 4) {
+                    float4 c4 = make_float4(1.f, 1.f, 1.f, 1.f), s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (rotate) {
+                        c4 = *reinterpret_cast<const float4*>(cs + j8 + j4);
+                        s4 = *reinterpret_cast<const float4*>(sn + j8 + j4);
+                    }
+                    const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int j = j8 + j4 + e;
+                        float xa = __uint_as_float(a[j]), xb = __uint_as_float(b[j]);
+                        if (normed) {
+                            xa *= rr * weight[32 * half + j];
+                            xb *= rr * weight[64 + 32 * half + j];
+                        }
+                        if (rotate) {
+                            ya[j4 + e] = fmaf(-xb, ss[e], xa * cc[e]);
+                            yb[j4 + e] = fmaf(xa, ss[e], xb * cc[e]);
+                        } else {
+                            ya[j4 + e] = xa;
+                            yb[j4 + e] = xb;
+                        }
+                    }
+                }
+                *reinterpret_cast<uint4*>(dst + 32 * half + j8) =
+                    make_uint4(pack2_bf16(ya[0], ya[1]), pack2_bf16(ya[2], ya[3]), pack2_bf16(ya[4], ya[5]),
+                               pack2_bf16(ya[6], ya[7]));
+                *reinterpret_cast<uint4*>(dst + 64 + 32 * half + j8) =
+                    make_uint4(pack2_bf16(yb[0], yb[1]), pack2_bf16(yb[2], yb[3]), pack2_bf16(yb[4], yb[5]),
+                               pack2_bf16(yb[6], yb[7]));
+            }
+        }
+    }
+}
+
+template <int BN, bool STREAMK, bool DUAL, bool HEADS>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
-               void* __restrict__ C_, int M, int N, int K, int mode, int splits, int* error_word) {
+               void* __restrict__ C_, int M, int N, int K, int mode, int splits, int* error_word,
+               const HeadsEpilogue hp) {
+    // HEADS: `map_w` is the tokens' map and N their number, `map_a` the weight's and M its rows.
     using cfg = Cfg<BN, DUAL>;
     pdl_trigger();      // the next kernel's blocks may start arriving; they wait for this one to finish
     extern __shared__ uint8_t smem_raw[];
@@ -117,6 +251,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     uint64_t* acc_empty = acc_full + 2;               // [2]
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    float* norm_w = (float*)(smem + cfg::STAGES * cfg::STAGE_BYTES + 256);      // HEADS: q weights, then k weights
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // DUAL: N counts the outputs (half the weight's rows); rows n and n + N belong together.
@@ -141,6 +276,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         tc::tmem_alloc(tmem_slot, cfg::TMEM_COLS);
         tc::tmem_relinquish();
     }
+    if (HEADS && threadIdx.x >= 64) {
+        // Norm weights are written by no kernel: they may be read before pdl_wait().
+        const int i = threadIdx.x - 64;
+        norm_w[i] = hp.q_weight ? hp.q_weight[i] : 1.0f;
+        norm_w[128 + i] = hp.k_weight ? hp.k_weight[i] : 1.0f;
+    }
     tc::tc_fence_before();
     __syncthreads();
     tc::tc_fence_after();
@@ -154,30 +295,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             Work w;
             uint32_t stage = 0, phase = 0;
             bool ok = true, waited = false;
-            // Units (tile, k block) whose weights are in flight but whose activations are not yet asked for.
-            int early_kb[cfg::STAGES], early_mt[cfg::STAGES], early = 0;
+            // The weight is the 128-row operand (A_TILES tiles at the stage's start) or, with HEADS, the BN-row one
+            // behind it; the activations are the other.  Units (tile, k block) whose weights are in flight but
+            // whose activations are not yet asked for:
+            int early_kb[cfg::STAGES], early_row[cfg::STAGES], early = 0;
+            constexpr int ACT_OFFSET = HEADS ? 0 : cfg::A_TILES * cfg::A_BYTES;
+            const CUtensorMap* map_act = HEADS ? &map_w : &map_a;
             while (ok && sched.next(w)) {
+                const int act_row = HEADS ? w.nt * BM : w.mt * BN;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     if (!waited && early == cfg::STAGES) {
                         pdl_wait();
                         waited = true;
 #pragma unroll
                         for (int e = 0; e < cfg::STAGES; ++e)
-                            tc::tma_load_2d(tiles + e * cfg::STAGE_BYTES + cfg::A_TILES * cfg::A_BYTES, &map_a,
-                                            early_kb[e] * BK, early_mt[e] * BN, &full_bar[e]);
+                            tc::tma_load_2d(tiles + e * cfg::STAGE_BYTES + ACT_OFFSET, map_act, early_kb[e] * BK,
+                                            early_row[e], &full_bar[e]);
                     }
                     ok = tc::mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, error_word, ERR_PRODUCER);
                     if (!ok) break;
                     uint8_t* a_dst = tiles + stage * cfg::STAGE_BYTES;
                     uint8_t* b_dst = a_dst + cfg::A_TILES * cfg::A_BYTES;
                     tc::mbar_expect_tx(&full_bar[stage], cfg::STAGE_BYTES);
-                    tc::tma_load_2d(a_dst, &map_w, kb * BK, w.nt * BM, &full_bar[stage]);
-                    if (DUAL) tc::tma_load_2d(a_dst + cfg::A_BYTES, &map_w, kb * BK, N + w.nt * BM, &full_bar[stage]);
-                    if (waited) {
+                    if (HEADS) {
                         tc::tma_load_2d(b_dst, &map_a, kb * BK, w.mt * BN, &full_bar[stage]);
                     } else {
+                        tc::tma_load_2d(a_dst, &map_w, kb * BK, w.nt * BM, &full_bar[stage]);
+                        if (DUAL)
+                            tc::tma_load_2d(a_dst + cfg::A_BYTES, &map_w, kb * BK, N + w.nt * BM, &full_bar[stage]);
+                    }
+                    if (waited) {
+                        tc::tma_load_2d(a_dst + ACT_OFFSET, map_act, kb * BK, act_row, &full_bar[stage]);
+                    } else {
                         early_kb[early] = kb;
-                        early_mt[early] = w.mt;
+                        early_row[early] = act_row;
                         ++early;
                     }
                     if (++stage == cfg::STAGES) { stage = 0; phase ^= 1; }
@@ -187,8 +338,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 // Fewer units than stages: their activations are still to be asked for.
                 pdl_wait();
                 for (int e = 0; e < early; ++e)
-                    tc::tma_load_2d(tiles + e * cfg::STAGE_BYTES + cfg::A_TILES * cfg::A_BYTES, &map_a,
-                                    early_kb[e] * BK, early_mt[e] * BN, &full_bar[e]);
+                    tc::tma_load_2d(tiles + e * cfg::STAGE_BYTES + ACT_OFFSET, map_act, early_kb[e] * BK, early_row[e],
+                                    &full_bar[e]);
             }
         }
     } else if (warp == 1) {
@@ -243,7 +394,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             tc::tc_fence_after();
             const int n = w.nt * BM + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + acc * cfg::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
-            if (w.kb1 > w.kb0) {
+            if constexpr (HEADS) {
+                if constexpr (BN % 128 == 0) heads_epilogue<BN>(hp, norm_w, taddr, n, N, w.mt * BN, M);
+            } else if (w.kb1 > w.kb0) {
                 constexpr int CH = BN < 32 ? 16 : 32;
 #pragma unroll 1
                 for (int c = 0; c < BN; c += CH) {
@@ -317,7 +470,7 @@ int launch(const CUtensorMap& map_w, const void* A, void* C, int M, int N, int K
     using cfg = Cfg<BN, DUAL>;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(gemm_tc_kernel<BN, STREAMK, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(gemm_tc_kernel<BN, STREAMK, DUAL, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  cfg::SMEM_BYTES) != cudaSuccess)
             return (int)cudaGetLastError();
         configured = true;
@@ -335,8 +488,29 @@ int launch(const CUtensorMap& map_w, const void* A, void* C, int M, int N, int K
     }
     if (grid > (long long)g_sm_count * cfg::CTAS_PER_SM) grid = (long long)g_sm_count * cfg::CTAS_PER_SM;
     if (grid < 1) grid = 1;
-    launch_kernel(gemm_tc_kernel<BN, STREAMK, DUAL>, dim3((unsigned)grid), dim3(THREADS), cfg::SMEM_BYTES, stream, 
-        map_w, map_a, C, M, N, K, mode, splits, error_word);
+    launch_kernel(gemm_tc_kernel<BN, STREAMK, DUAL, false>, dim3((unsigned)grid), dim3(THREADS), cfg::SMEM_BYTES, stream, 
+        map_w, map_a, C, M, N, K, mode, splits, error_word, HeadsEpilogue{});
+    return launch_status();
+}
+
+// HEADS: the weight's map has boxes of BN rows; the tokens take the 128-row side.
+template <int BN>
+int launch_heads(const CUtensorMap& map_weight, const void* A, int tokens, int features, int K,
+                 const HeadsEpilogue& hp, int* error_word, cudaStream_t stream) {
+    using cfg = Cfg<BN, false>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_tc_kernel<BN, false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 cfg::SMEM_BYTES) != cudaSuccess)
+            return (int)cudaGetLastError();
+        configured = true;
+    }
+    CUtensorMap map_tokens;
+    if (int e = llmx_make_map_bf16_2d(&map_tokens, A, (uint64_t)tokens, (uint64_t)K, BM, BK)) return e;
+    long long grid = (long long)((tokens + BM - 1) / BM) * ((features + BN - 1) / BN);
+    if (grid > g_sm_count) grid = g_sm_count;
+    launch_kernel(gemm_tc_kernel<BN, false, false, true>, dim3((unsigned)grid), dim3(THREADS), cfg::SMEM_BYTES, stream,
+        map_tokens, map_weight, (void*)nullptr, features, tokens, K, (int)MODE_STORE, 1, error_word, hp);
     return launch_status();
 }
 
@@ -355,6 +529,44 @@ void ensure_sm_count() {
 LLMX_EXPORT int llmx_gemm_tc_weight_map(void* out, const void* W, int N, int K) {
     if (K % 8 || ((uintptr_t)W & 15)) return LLMX_ERR_UNSUPPORTED;
     return llmx_make_map_bf16_2d((CUtensorMap*)out, W, (uint64_t)N, (uint64_t)K, BM, BK);
+}
+
+// A weight's map with boxes of `box_rows` (128 or 256) rows, for the side of the product that `box_rows` names.
+LLMX_EXPORT int llmx_gemm_tc_weight_map_box(void* out, const void* W, int N, int K, int box_rows) {
+    if (K % 8 || ((uintptr_t)W & 15) || (box_rows != 128 && box_rows != 256)) return LLMX_ERR_UNSUPPORTED;
+    return llmx_make_map_bf16_2d((CUtensorMap*)out, W, (uint64_t)N, (uint64_t)K, (uint32_t)box_rows, BK);
+}
+
+// The q/k/v product of a layer whose heads are 128 wide, finished in the epilogue: A [tokens, K] bfloat16; the
+// weight [(heads + 2 kv_heads) * 128, K] (query rows, key rows, value rows) by a map of `head_tile`-row boxes
+// (128 or 256); queries and keys normed (weights may be null) and rotated (tables [positions, 64], may be
+// null), queries to q_out [tokens, heads * 128], keys and values to the cache [pages, 2, kv_heads, page_size,
+// 128] at slots[token] (negative: not stored), all bfloat16.
+LLMX_EXPORT int llmx_gemm_tc_heads(const void* weight_map, const void* A, int tokens, int K, int head_tile,
+                                   const float* q_weight, const float* k_weight, float eps, const float* cos_table,
+                                   const float* sin_table, const int* positions, const int* slots, void* q_out,
+                                   void* cache, int heads, int kv_heads, int page_size, int* error_word,
+                                   cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (K <= 0 || K % 8 || ((uintptr_t)A & 15) || ((uintptr_t)q_out & 15) || ((uintptr_t)cache & 15))
+        return LLMX_ERR_UNSUPPORTED;
+    if (heads <= 0 || kv_heads <= 0 || page_size <= 0 || !positions || !slots || !q_out || !cache ||
+        (cos_table == nullptr) != (sin_table == nullptr))
+        return LLMX_ERR_BAD_ARGUMENT;
+    if (((uintptr_t)cos_table & 15) || ((uintptr_t)sin_table & 15)) return LLMX_ERR_UNSUPPORTED;
+    ensure_sm_count();
+    HeadsEpilogue hp;
+    hp.q_weight = q_weight; hp.k_weight = k_weight; hp.cos_table = cos_table; hp.sin_table = sin_table;
+    hp.positions = positions; hp.slots = slots;
+    hp.q_out = (__nv_bfloat16*)q_out; hp.cache = (__nv_bfloat16*)cache;
+    hp.eps = eps; hp.heads = heads; hp.kv_heads = kv_heads; hp.page_size = page_size;
+    const int features = (heads + 2 * kv_heads) * 128;
+    const CUtensorMap& map_w = *(const CUtensorMap*)weight_map;
+    switch (head_tile) {
+        case 128: return launch_heads<128>(map_w, A, tokens, features, K, hp, error_word, stream);
+        case 256: return launch_heads<256>(map_w, A, tokens, features, K, hp, error_word, stream);
+        default: return LLMX_ERR_BAD_ARGUMENT;
+    }
 }
 
 // mode 0: C = A W^T;  mode 1: C += A W^T (float32 C [M, N]).

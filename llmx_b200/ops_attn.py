@@ -143,6 +143,12 @@ def _request_lists(step, max_rows: int):
     return got
 
 
+def decoding_rows_only(step, heads: int, kv_heads: int) -> bool:
+    """Whether every request of the step brings so few rows that the decode kernel serves them all."""
+    lists = _request_lists(step, 16 // (heads // kv_heads))
+    return lists[1] > 0 and lists[5] == 0
+
+
 def paged_attention_bf16(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, step, group, heads: int,
                          kv_heads: int, head_dim: int, window: Optional[int], scale: float) -> None:
     _cuda(q, cache, out)

@@ -14,6 +14,9 @@ _i, _p = ctypes.c_int, ctypes.c_void_p
 register_signature("gemm_tc", "llmx_gemm_tc_weight_map", [_p, _p, _i, _i])
 register_signature("gemm_tc", "llmx_gemm_tc", [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p])
 register_signature("gemm_tc", "llmx_gemm_tc_swiglu", [_p, _p, _p, _i, _i, _i, _i, _p, _p])
+register_signature("gemm_tc", "llmx_gemm_tc_weight_map_box", [_p, _p, _i, _i, _i])
+register_signature("gemm_tc", "llmx_gemm_tc_heads", [_p, _p, _i, _i, _i, _p, _p, ctypes.c_float, _p, _p, _p, _p, _p, _p,
+                                                     _i, _i, _i, _p, _p])
 
 _error_words: Dict[int, torch.Tensor] = {}
 _ERROR_NAMES = {101: "the TMA producer waited for a free stage", 102: "the MMA issuer waited for a loaded stage",
@@ -40,18 +43,26 @@ def check_errors() -> None:
 
 
 class WeightMap:
-    """The TMA descriptor of a bfloat16 weight [N, K], made once; 64-byte aligned host memory."""
+    """The TMA descriptor of a bfloat16 weight [N, K], made once; 64-byte aligned host memory.
+    `box_rows`: the rows one copy brings (128: the weight on the instruction's wide side; 128 or 256 with
+    `heads=True`: the weight on the narrow side, whole heads a tile)."""
 
-    def __init__(self, weight: torch.Tensor):
+    def __init__(self, weight: torch.Tensor, box_rows: int = 128, heads: bool = False):
         _need(weight.dtype is torch.bfloat16 and weight.dim() == 2 and weight.is_contiguous() and weight.is_cuda,
               "gemm_tc: the weight must be a contiguous bfloat16 CUDA matrix")
         self.weight = weight
+        self.box_rows = box_rows
         self._raw = ctypes.create_string_buffer(128 + 64)
         base = ctypes.addressof(self._raw)
         self.address = (base + 63) & ~63
         n, k = weight.shape
-        _check(_fn("gemm_tc", "llmx_gemm_tc_weight_map")(ctypes.c_void_p(self.address), _ptr(weight), n, k),
-               "gemm_tc weight map")
+        if heads:
+            _check(_fn("gemm_tc", "llmx_gemm_tc_weight_map_box")(ctypes.c_void_p(self.address), _ptr(weight), n, k,
+                                                                 box_rows), "gemm_tc weight map")
+        else:
+            _need(box_rows == 128, "gemm_tc: the wide side takes 128 weight rows a tile")
+            _check(_fn("gemm_tc", "llmx_gemm_tc_weight_map")(ctypes.c_void_p(self.address), _ptr(weight), n, k),
+                   "gemm_tc weight map")
 
 
 _maps: Dict[Tuple[int, int, int], WeightMap] = {}
@@ -181,3 +192,52 @@ def gemm_tc_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, wmap: Op
     _check(_fn("gemm_tc", "llmx_gemm_tc_swiglu")(ctypes.c_void_p(wmap.address), _ptr(a), _ptr(out), m, f, k,
                                                  token_tile, _ptr(error_word(a.device)), _stream()), "gemm_tc_swiglu")
     return out
+
+
+HEADS_MIN_ROWS = 256        # from this many tokens on the q/k/v product finishes its heads itself
+HEADS_WIDE_ROWS = 1024      # above this many, with two heads (256 weight rows) a tile
+
+
+def heads_tile(m: int, heads: int, kv_heads: int) -> int:
+    """Weight rows per tile (128, 256) of the q/k/v product that finishes its heads in the epilogue, or 0 when
+    the tokens are few: the plain product then fills the SMs by cutting k, and its float32 output goes through
+    the per-head kernel.  Timed at 32 heads over 8, width 4,096 (us, product + per-head kernel -> this):
+    256 tokens 27 -> 22, 512: 38 -> 35, 1,024: 63 -> 53, 2,048: 100 -> 91, 8,192: 423 -> 332."""
+    if m < HEADS_MIN_ROWS:
+        return 0
+    return 128 if m <= HEADS_WIDE_ROWS else 256
+
+
+def gemm_tc_heads(a: torch.Tensor, wmap: WeightMap, heads: int, kv_heads: int, q_weight: Optional[torch.Tensor],
+                  k_weight: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor],
+                  sin: Optional[torch.Tensor], positions: torch.Tensor, slots: torch.Tensor, q_out: torch.Tensor,
+                  cache: torch.Tensor) -> None:
+    """The q/k/v product of a layer with heads of 128, finished in its epilogue: queries and keys normed per head
+    and rotated, queries to `q_out` [M, heads * 128], keys and values to their cache slots.
+
+    a [M, K] bfloat16; `wmap` a `WeightMap(w, 128 | 256, heads=True)` of the stacked weight
+    [(heads + 2 kv_heads) * 128, K]; cache [pages, 2, kv_heads, page_size, 128] bfloat16; cos/sin float32
+    [positions, 64] or None; positions and slots int32 [M] (a negative slot: the row's key and value are not stored).
+    """
+    _cuda(a, wmap.weight, q_weight, k_weight, cos, sin, positions, slots, q_out, cache)
+    m, k = a.shape
+    w = wmap.weight
+    _need(a.dtype is torch.bfloat16 and a.is_contiguous() and w.shape[1] == k and k % 8 == 0,
+          "gemm_tc_heads: bfloat16 rows of the weight's input width (a multiple of 8)")
+    _need(w.shape[0] == (heads + 2 * kv_heads) * 128, "gemm_tc_heads: the weight does not hold heads of 128")
+    _need(q_out.dtype is torch.bfloat16 and tuple(q_out.shape) == (m, heads * 128) and q_out.is_contiguous(),
+          "gemm_tc_heads: q_out shape does not fit")
+    _need(cache.dtype is torch.bfloat16 and cache.dim() == 5 and cache.shape[1] == 2 and cache.shape[2] == kv_heads
+          and cache.shape[4] == 128 and cache.is_contiguous(), "gemm_tc_heads: cache layout does not fit")
+    _need(positions.dtype == torch.int32 and slots.dtype == torch.int32 and positions.numel() >= m
+          and slots.numel() >= m, "gemm_tc_heads: positions and slots must be int32 per row")
+    if cos is not None:
+        _need(sin is not None and cos.shape == sin.shape and cos.dtype == torch.float32 and cos.dim() == 2
+              and cos.shape[1] == 64 and cos.is_contiguous() and sin.is_contiguous(),
+              "gemm_tc_heads: cos and sin tables [positions, 64]")
+    for nw in (q_weight, k_weight):
+        _need(nw is None or (nw.dtype == torch.float32 and nw.numel() == 128), "gemm_tc_heads: norm weight")
+    _check(_fn("gemm_tc", "llmx_gemm_tc_heads")(
+        ctypes.c_void_p(wmap.address), _ptr(a), m, k, wmap.box_rows, _ptr(q_weight), _ptr(k_weight), float(eps),
+        _ptr(cos), _ptr(sin), _ptr(positions), _ptr(slots), _ptr(q_out), _ptr(cache), heads, kv_heads,
+        cache.shape[3], _ptr(error_word(a.device)), _stream()), "gemm_tc_heads")

@@ -71,7 +71,11 @@ class Attention(Part):
 
     def wants_cleared(self, rows: int, device) -> Optional[torch.Tensor]:
         """A buffer this mixer wants zeroed before `forward` (the norm before it clears it in passing)."""
-        self._qkv_out = self.qkv.output_to_clear(rows, device)
+        from .attention_dispatch import heads_tile
+        if heads_tile(self.qkv, rows, self.heads, self.kv_heads, self.head_dim, self.position_encoding.cos):
+            self._qkv_out = None        # the product finishes its heads itself: no float32 output to clear
+        else:
+            self._qkv_out = self.qkv.output_to_clear(rows, device)
         return self._qkv_out
 
     def forward(self, h: torch.Tensor, step: StepBatch, cache_entry: int, residual: torch.Tensor,
@@ -79,7 +83,6 @@ class Attention(Part):
         rows = h.shape[0]
         group, cache = step.kv(cache_entry)
         out, self._qkv_out = getattr(self, "_qkv_out", None), None
-        qkv = self.qkv(h, out=out, cleared=out is not None) if out is not None and out.shape[0] == rows else self.qkv(h)
         pe = self.position_encoding
         slots = group.slots
         if not write_cache:
@@ -89,7 +92,16 @@ class Attention(Part):
                 step.extras[key] = torch.full_like(group.slots, -1)
             slots = step.extras[key]
         o = torch.empty((rows, self.q_width), dtype=self.precision.act, device=h.device)
-        from .attention_dispatch import decode_from_qkv, paged_attention
+        from .attention_dispatch import decode_from_qkv, heads_from_product, heads_tile, paged_attention
+        tile = heads_tile(self.qkv, rows, self.heads, self.kv_heads, self.head_dim, pe.cos)
+        q = torch.empty_like(o) if tile else None
+        if tile and heads_from_product(self.qkv, h, tile, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, pe.cos,
+                                       pe.sin, slots, q, cache, step, self.heads, self.kv_heads):
+            # Many rows: the product normed, rotated and stored its heads in its own epilogue.
+            paged_attention(q, cache, o, step, group, self.heads, self.kv_heads, self.head_dim, self.window, self.scale)
+            self.o(o, out=residual, accumulate=True)
+            return
+        qkv = self.qkv(h, out=out, cleared=out is not None) if out is not None and out.shape[0] == rows else self.qkv(h)
         # A step of decoding rows only: the attention kernel makes its queries and new keys itself.
         if not decode_from_qkv(qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, pe.cos, pe.sin, slots, cache, o,
                                step, group, self.heads, self.kv_heads, self.head_dim, self.window, self.scale):

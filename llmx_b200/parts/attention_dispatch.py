@@ -37,3 +37,27 @@ def decode_from_qkv(qkv: torch.Tensor, q_weight, k_weight, eps: float, cos, sin,
     from .. import ops_attn
     return ops_attn.decode_from_qkv(qkv, q_weight, k_weight, eps, cos, sin, slots, cache, out, step, group, heads,
                                     kv_heads, head_dim, window, scale)
+
+
+def heads_tile(linear, rows: int, heads: int, kv_heads: int, head_dim: int, cos) -> int:
+    """Weight rows per tile when the q/k/v product can finish its heads itself for this many rows (bfloat16 path,
+    heads of 128, rotation of the whole head or none), else 0."""
+    if not linear.tensor_core or head_dim != 128 or (cos is not None and cos.shape[1] != 64):
+        return 0
+    from .. import ops_tc
+    return ops_tc.heads_tile(rows, heads, kv_heads)
+
+
+def heads_from_product(linear, h: torch.Tensor, tile: int, q_weight, k_weight, eps: float, cos, sin,
+                       slots: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, step: StepBatch, heads: int,
+                       kv_heads: int) -> bool:
+    """Run the q/k/v product with the per-head norm, the rotation and the cache write in its epilogue
+    (ops_tc.gemm_tc_heads).  False, having done nothing, when the cache is not bfloat16 or the step is one of
+    decoding rows only (the decode kernel then takes the product's output itself)."""
+    if cache.dtype is not torch.bfloat16 or q.dtype is not torch.bfloat16:
+        return False
+    from .. import ops_attn
+    if not step.extras.get("no_qkv_attention") and ops_attn.decoding_rows_only(step, heads, kv_heads):
+        return False
+    linear.heads(h, tile, heads, kv_heads, q_weight, k_weight, eps, cos, sin, step.positions, slots, q, cache)
+    return True

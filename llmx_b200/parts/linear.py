@@ -27,6 +27,7 @@ class Linear:
         self.precision = precision
         self.tensor_core = precision.act is torch.bfloat16 and self.in_features % 8 == 0
         self._tc = None
+        self._head_maps = {}
 
     def __call__(self, a: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False,
                  cleared: bool = False) -> torch.Tensor:
@@ -72,3 +73,13 @@ class Linear:
         SMs by k ranges, whose partial sums cannot pass through the activation."""
         from .. import ops_tc
         return self.tensor_core and rows > ops_tc.STREAM_K_MAX_ROWS
+
+    def heads(self, a: torch.Tensor, tile: int, heads: int, kv_heads: int, q_weight, k_weight, eps: float, cos, sin,
+              positions: torch.Tensor, slots: torch.Tensor, q_out: torch.Tensor, cache: torch.Tensor) -> None:
+        """The q/k/v product of heads of 128 finished in its epilogue (see ops_tc.gemm_tc_heads; tensor-core path
+        only): `tile` weight rows a tile, as `ops_tc.heads_tile` chose."""
+        from .. import ops_tc
+        wmap = self._head_maps.get(tile)
+        if wmap is None:
+            wmap = self._head_maps[tile] = ops_tc.WeightMap(self.weight, tile, heads=True)
+        ops_tc.gemm_tc_heads(a, wmap, heads, kv_heads, q_weight, k_weight, eps, cos, sin, positions, slots, q_out, cache)

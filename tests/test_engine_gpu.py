@@ -254,6 +254,28 @@ def test_layers_of_8b_width_under_cutting(wide_model_dir, dtype):
         del engine
 
 
+def test_long_prompts_at_8b_width(wide_model_dir):
+    """Steps of 256 rows and more let the q/k/v product norm, rotate and store its heads itself (one head a tile; two
+    above 1,024 rows); shorter steps go through the float32 output and the per-head kernel.  Long prompts whole, in
+    portions on both sides of those sizes, and two prompts in one step: every logit against the plain
+    implementation, so keys stored by either way serve rows computed by the other."""
+    from llmx_b200 import ops_tc
+    from llmx_b200.engine import Engine, EngineOptions
+    vocab = WIDE["vocab_size"]
+    requests = {"L": helpers.random_ids(vocab, 1100, seed=61), "M": helpers.random_ids(vocab, 300, seed=62)}
+    together = [{"step": 0, "entries": [{"id": rid, "tokens": ids, "want": list(range(len(ids)))}
+                                        for rid, ids in requests.items()], "end": list(requests)}]
+    traces = [helpers.trace_whole(requests), helpers.trace_portions(requests, portions=(520, 7, 260, 64, 249, 300)),
+              together]
+    assert ops_tc.heads_tile(1100, 32, 8) == 256 and ops_tc.heads_tile(300, 32, 8) == 128
+    assert ops_tc.heads_tile(249, 32, 8) == 0
+    for steps in traces:
+        engine = Engine.from_dir(wide_model_dir, EngineOptions(dtype="bfloat16", kv_tokens=helpers.tokens_needed(steps),
+                                                               page_size=16, max_requests=4))
+        _check(engine, wide_model_dir, steps, requests, "bfloat16")
+        del engine
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["B", "wide"])
 def test_recorded_steps_of_any_shape(model_dirs, wide_model_dir, name, dtype):

@@ -462,3 +462,54 @@ def test_gemm_tensor_core_gated(m, f, k):
     gu = (a.float().cpu().double() @ w.float().cpu().double().T).numpy()
     ref = plain.silu(gu[:, :f].astype(np.float32)) * gu[:, f:].astype(np.float32)
     assert np.abs(out.float().cpu().numpy() - ref).max() <= 2 ** -7 * max(1.0, np.abs(ref).max())
+
+
+@pytest.mark.parametrize("tile", [128, 256])
+@pytest.mark.parametrize("m,heads,kv_heads,k,rotate,norm", [(70, 4, 2, 64, True, True), (300, 3, 1, 200, True, True),
+                                                            (129, 2, 2, 512, False, True), (1000, 5, 1, 136, True, False)])
+def test_gemm_tensor_core_finishes_heads(tile, m, heads, kv_heads, k, rotate, norm):
+    """The q/k/v product with the per-head norm, the rotation and the cache write in its epilogue: against the
+    plain formulas, and bit for bit against the product followed by the per-head kernel (a prompt's keys must
+    not depend on which of the two a portion's size chose).  Odd head counts leave half-empty 256-row tiles."""
+    from llmx_b200 import ops, ops_tc
+    D, page, pages = 128, 16, 80
+    g = torch.Generator().manual_seed(21)
+    a = _bf16(torch.randn(m, k, generator=g)).to(DEV)
+    w = _bf16(torch.randn((heads + 2 * kv_heads) * D, k, generator=g) * 0.2).to(DEV)
+    qw = (1 + 0.1 * torch.randn(D, generator=g)).to(DEV) if norm else None
+    kw = (1 + 0.1 * torch.randn(D, generator=g)).to(DEV) if norm else None
+    positions = torch.randint(0, 300, (m,), generator=g, dtype=torch.int32)
+    cos_np, sin_np = plain.rope_tables(300, D, 10000.0)
+    cos = torch.from_numpy(cos_np).to(DEV) if rotate else None
+    sin = torch.from_numpy(sin_np).to(DEV) if rotate else None
+    slots = torch.randperm(pages * page, generator=g)[:m].to(torch.int32)
+    slots[5] = -1
+    cache = torch.zeros(pages, 2, kv_heads, page, D, dtype=torch.bfloat16, device=DEV)
+    q_out = torch.zeros(m, heads * D, dtype=torch.bfloat16, device=DEV)
+    ops_tc.gemm_tc_heads(a, ops_tc.WeightMap(w, tile, heads=True), heads, kv_heads, qw, kw, 1e-6, cos, sin,
+                         positions.to(DEV), slots.to(DEV), q_out, cache)
+    ops_tc.check_errors()
+
+    qkv = torch.empty(m, w.shape[0], device=DEV)
+    ops_tc.gemm_tc(a, w, qkv, schedule=0, splits=1)
+    cache2, q2 = torch.zeros_like(cache), torch.zeros_like(q_out)
+    ops.head_norm_rope_kv(qkv, heads, kv_heads, D, qw, kw, 1e-6, cos, sin, positions.to(DEV), slots.to(DEV), q2, cache2)
+    assert torch.equal(q_out, q2) and torch.equal(cache, cache2)
+
+    full = (a.float().cpu().double() @ w.float().cpu().double().T).numpy().astype(np.float32)
+    q = full[:, :heads * D].reshape(m, heads, D)
+    kk = full[:, heads * D:(heads + kv_heads) * D].reshape(m, kv_heads, D)
+    v = full[:, (heads + kv_heads) * D:].reshape(m, kv_heads, D)
+    if norm:
+        q, kk = plain.rms_norm(q, qw.cpu().numpy(), 1e-6), plain.rms_norm(kk, kw.cpu().numpy(), 1e-6)
+    if rotate:
+        c, s = cos_np[positions.numpy()], sin_np[positions.numpy()]
+        q, kk = plain.rope_rotate(q, c, s), plain.rope_rotate(kk, c, s)
+    tol = 2 ** -7
+    assert np.abs(q_out.float().cpu().numpy().reshape(m, heads, D) - q).max() <= tol * np.abs(q).max()
+    cache_np = cache.float().cpu().numpy()
+    for r in range(m):
+        sl = int(slots[r])
+        if sl >= 0:
+            assert np.abs(cache_np[sl // page, 0, :, sl % page] - kk[r]).max() <= tol * np.abs(kk).max()
+            assert np.abs(cache_np[sl // page, 1, :, sl % page] - v[r]).max() <= tol * np.abs(v).max()
