@@ -195,17 +195,21 @@ def gemm_tc_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, wmap: Op
 
 
 HEADS_MIN_ROWS = 256        # from this many tokens on the q/k/v product finishes its heads itself
-HEADS_WIDE_ROWS = 1024      # above this many, with two heads (256 weight rows) a tile
 
 
 def heads_tile(m: int, heads: int, kv_heads: int) -> int:
-    """Weight rows per tile (128, 256) of the q/k/v product that finishes its heads in the epilogue, or 0 when
-    the tokens are few: the plain product then fills the SMs by cutting k, and its float32 output goes through
-    the per-head kernel.  Timed at 32 heads over 8, width 4,096 (us, product + per-head kernel -> this):
-    256 tokens 27 -> 22, 512: 38 -> 35, 1,024: 63 -> 53, 2,048: 100 -> 91, 8,192: 423 -> 332."""
+    """Weight rows per tile (128: one head, 256: two) of the q/k/v product that finishes its heads in the
+    epilogue, or 0 when the tokens are few: the plain product then fills the SMs by cutting k, and its float32
+    output goes through the per-head kernel.  Of the two tiles the one whose waves over the SMs take less time (a
+    two-head tile takes about 1.55 times a one-head tile).  Timed at 32 heads over 8, width 4,096 (us, product +
+    per-head kernel -> this): 256 tokens 27 -> 21, 512: 38 -> 32, 1,024: 63 -> 52, 2,048: 100 -> 88,
+    8,192: 497 -> 342."""
     if m < HEADS_MIN_ROWS:
         return 0
-    return 128 if m <= HEADS_WIDE_ROWS else 256
+    token_tiles, width, sms = -(-m // 128), heads + 2 * kv_heads, _sms()
+    one = -(-token_tiles * width // sms)
+    two = -(-token_tiles * -(-width // 2) // sms)
+    return 128 if one * 1.0 <= two * 1.55 else 256
 
 
 def gemm_tc_heads(a: torch.Tensor, wmap: WeightMap, heads: int, kv_heads: int, q_weight: Optional[torch.Tensor],

@@ -255,8 +255,7 @@ def test_layers_of_8b_width_under_cutting(wide_model_dir, dtype):
 
 
 def test_long_prompts_at_8b_width(wide_model_dir):
-    """Steps of 256 rows and more let the q/k/v product norm, rotate and store its heads itself (one head a tile; two
-    above 1,024 rows); shorter steps go through the float32 output and the per-head kernel.  Long prompts whole, in
+    """Steps of 256 rows and more let the q/k/v product norm, rotate and store its heads itself (one head or two a tile); shorter steps go through the float32 output and the per-head kernel.  Long prompts whole, in
     portions on both sides of those sizes, and two prompts in one step: every logit against the plain
     implementation, so keys stored by either way serve rows computed by the other."""
     from llmx_b200 import ops_tc
@@ -267,7 +266,7 @@ def test_long_prompts_at_8b_width(wide_model_dir):
                                         for rid, ids in requests.items()], "end": list(requests)}]
     traces = [helpers.trace_whole(requests), helpers.trace_portions(requests, portions=(520, 7, 260, 64, 249, 300)),
               together]
-    assert ops_tc.heads_tile(1100, 32, 8) == 256 and ops_tc.heads_tile(300, 32, 8) == 128
+    assert {ops_tc.heads_tile(n, 32, 8) for n in (1100, 520, 300, 260)} == {128, 256}
     assert ops_tc.heads_tile(249, 32, 8) == 0
     for steps in traces:
         engine = Engine.from_dir(wide_model_dir, EngineOptions(dtype="bfloat16", kv_tokens=helpers.tokens_needed(steps),
