@@ -297,6 +297,73 @@ def test_attention_prefill_blocks_walk_several_items(history):
         assert np.abs(got - ref).max() <= 2e-2 * max(1.0, np.abs(ref).max())
 
 
+@pytest.mark.parametrize("window", [None, 5000])
+def test_attention_over_long_histories(window):
+    """Tens of thousands of keys behind a request: block tables of over a thousand pages, sixteen key ranges for the
+    decoding rows, hundreds of key stages for a prompt portion.  One key near the start of every request (or of
+    its window) is made to stand out for the last row, so a page that is dropped or misplaced anywhere shows."""
+    from llmx_b200 import ops_attn, ops_tc
+    from llmx_b200.parts.base import GroupView, StepBatch
+    heads, kv_heads, D, page = 32, 8, 128, 16
+    layout = [(20000, 1), (9001, 3), (12345, 70), (33, 1)]
+    g = torch.Generator().manual_seed(31)
+    lens = [h + n for h, n in layout]
+    pages_needed = [-(-l // page) for l in lens]
+    total_pages = sum(pages_needed) + 5
+    perm = torch.randperm(total_pages, generator=g).tolist()
+    cache = torch.randn(total_pages, 2, kv_heads, page, D, generator=g).to(torch.bfloat16)
+    tables = np.zeros((len(layout), max(pages_needed)), dtype=np.int32)
+    qs, refs, row_start, at = [], [], [], 0
+    for r, (h, n) in enumerate(layout):
+        row_start.append(at)
+        at += n
+        k = torch.randn(lens[r], kv_heads, D, generator=g)
+        v = torch.randn(lens[r], kv_heads, D, generator=g)
+        q = torch.randn(n, heads, D, generator=g).to(torch.bfloat16)
+        far = max(1, lens[r] - window + 1) if window else 1
+        k[far] = q[-1, ::heads // kv_heads].float() * 4.0
+        k, v = k.to(torch.bfloat16), v.to(torch.bfloat16)
+        mine = [perm.pop() for _ in range(pages_needed[r])]
+        tables[r, :len(mine)] = mine
+        idx = torch.tensor(mine).repeat_interleave(page)[:lens[r]]
+        off = torch.arange(lens[r]) % page
+        cache[idx, 0, :, off] = k
+        cache[idx, 1, :, off] = v
+        # plain reference for the new rows alone: row at position p sees keys lo..p
+        kk = k.double().repeat_interleave(heads // kv_heads, dim=1)      # [L, heads, D]
+        vv = v.double().repeat_interleave(heads // kv_heads, dim=1)
+        scores = torch.einsum("nhd,lhd->nhl", q.double(), kk) / math.sqrt(D)
+        pos = torch.arange(h, h + n)[:, None, None]
+        keys = torch.arange(lens[r])[None, None, :]
+        seen = keys <= pos
+        if window:
+            seen &= keys > pos - window
+        scores = scores.masked_fill(~seen, float("-inf"))
+        refs.append(torch.einsum("nhl,lhd->nhd", torch.softmax(scores, dim=-1), vv))
+        qs.append(q)
+    rows = at
+    ref = torch.cat(refs).reshape(rows, -1).numpy()
+    q_all = torch.cat(qs).reshape(rows, heads * D).to(DEV).contiguous()
+
+    def dev(a):
+        return torch.as_tensor(np.asarray(a, dtype=np.int32)).to(DEV)
+    positions = np.concatenate([np.arange(h, h + n) for h, n in layout])
+    row_request = np.concatenate([np.full(n, r) for r, (h, n) in enumerate(layout)])
+    group = GroupView(dev(tables), dev(np.zeros(rows)), page)
+    step = StepBatch(rows=rows, requests=len(layout), token_ids=dev(np.zeros(rows)), positions=dev(positions),
+                     row_request=dev(row_request), row_start=dev(row_start), row_count=dev([n for _, n in layout]),
+                     history=dev([h for h, _ in layout]), state_slots=dev([-1] * len(layout)), logit_rows=dev([]),
+                     groups=[group], caches=None, host_row_start=row_start, host_row_count=[n for _, n in layout],
+                     host_history=[h for h, _ in layout], max_row_count=max(n for _, n in layout), max_context=max(lens))
+    out = torch.full_like(q_all, float("nan"))
+    ops_attn.paged_attention_bf16(q_all, cache.to(DEV), out, step, group, heads, kv_heads, D, window, 1.0 / math.sqrt(D))
+    torch.cuda.synchronize()
+    ops_tc.check_errors()
+    got = out.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    assert np.abs(got - ref).max() <= 2e-2 * max(1.0, np.abs(ref).max())
+
+
 @pytest.mark.parametrize("splits", [1, 2, 3, 7, 16])
 def test_attention_decode_any_number_of_key_ranges(splits):
     from llmx_b200 import ops_attn, ops_tc
