@@ -28,7 +28,7 @@ register_signature("attention_decode", "llmx_attn_decode_qkv",
                     _i, _f, _i, _p, _i, _i, _p, _p, _p])
 register_signature("attention_prefill_tc", "llmx_attn_prefill_tc_cache_map", [_p, _p, _ll, _i, _i, _i])
 register_signature("attention_prefill_tc", "llmx_attn_prefill_tc",
-                   [_p, _p, _p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p])
+                   [_p, _p, _p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p])
 register_signature("attention_prefill", "llmx_attn_prefill",
                    [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p])
 
@@ -188,7 +188,8 @@ def paged_attention_bf16(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
         _check(_fn("attention_prefill_tc", "llmx_attn_prefill_tc")(
             ctypes.c_void_p(hmap.address), _ptr(q), _ptr(out), q.shape[0], _ptr(large), n_large, _ptr(step.row_start),
             _ptr(step.row_count), _ptr(step.history), _ptr(tables), tables.shape[1], heads, kv_heads, head_dim,
-            cache.shape[3], win, float(scale), rows_large, _ptr(err), _stream()), "attention_prefill_tc")
+            cache.shape[3], win, float(scale), rows_large, int(step.extras.get("attn_item_tiles", 0)), _ptr(err),
+            _stream()), "attention_prefill_tc")
     elif n_large:
         _check(_fn("attention_prefill", "llmx_attn_prefill")(
             ctypes.c_void_p(cmap.address), _ptr(q), _ptr(out), _ptr(large), n_large, _ptr(step.row_start),

@@ -277,6 +277,24 @@ def test_attention_tiled_bf16(heads, kv_heads, head_dim, layout, window, spike):
     assert np.abs(got - ref).max() <= 2e-2 * max(1.0, np.abs(ref).max())
 
 
+@pytest.mark.parametrize("item_tiles", [1, 2])
+@pytest.mark.parametrize("heads,kv_heads", [(32, 8), (16, 8), (8, 8)])
+def test_attention_prefill_items_of_one_row_tile_or_two(item_tiles, heads, kv_heads):
+    """The tcgen05 prefill kernel pairs two row tiles in a work item, or takes one an item when pairs would be
+    fewer than the SMs (the launcher's choice; forced both ways here)."""
+    from llmx_b200 import ops_attn, ops_tc
+    layout = [(0, 300), (77, 130), (500, 64), (3, 33), (40, 1)]
+    q, cache, step, group, ref = _attention_case(torch.bfloat16, heads, kv_heads, 128, 16, layout, None, seed=23, spike=True)
+    step.extras["attn_item_tiles"] = item_tiles
+    out = torch.full_like(q, float("nan"))
+    ops_attn.paged_attention_bf16(q, cache, out, step, group, heads, kv_heads, 128, None, 1.0 / math.sqrt(128))
+    torch.cuda.synchronize()
+    ops_tc.check_errors()
+    got = out.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    assert np.abs(got - ref).max() <= 2e-2 * max(1.0, np.abs(ref).max())
+
+
 @pytest.mark.parametrize("history", [0, 320, 448])
 def test_attention_prefill_blocks_walk_several_items(history):
     """More work items than SMs: a block of the tcgen05 prefill kernel then walks several (request, kv head, rows)
