@@ -51,6 +51,7 @@ constexpr int SMEM_BYTES = SMEM_TILES + 1024 + 256;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t TMEM_O = 2 * KEYS;     // first column of the outputs
 constexpr float RAISE = 8.0f;             // the exponent's maximum follows the true one when it is this far behind
+constexpr int PART = D + 4;      // floats of one row's partial result: the output, the maximum, the sum (16-byte rows)
 enum : int { ERR_TCA_PRODUCER = 401, ERR_TCA_MMA = 402, ERR_TCA_SOFTMAX = 403 };
 
 // Instruction descriptors: bfloat16 in, float32 out, M = 128, N = 128; A K-major; B K-major (keys) or MN-major (values).
@@ -103,7 +104,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                        const int* __restrict__ row_start, const int* __restrict__ row_count,
                        const int* __restrict__ history, const int* __restrict__ block_tables, int table_stride,
                        int heads, int kv_heads, int window, float scale_log2, int n_req, int max_blocks, int item_tiles,
-                       int* error_word) {
+                       int key_splits, float* __restrict__ partial, int* error_word) {
     pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -163,17 +164,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     // back and forth over the list, so that each gets heavy and light ones), one after the other without giving up
     // its barriers and tensor memory.  Every role walks the same items and keeps count of the barrier phases it has
     // used, which go on from item to item.
+    // With `key_splits` > 1 an item is further one of that many ranges of the block's key stages; its rows' sums over
+    // the range (output not yet divided, maximum, sum) go to `partial`, and a second kernel adds the ranges up.
     const int per_block_row = kv_heads * n_req;
-    const int total_items = max_blocks * per_block_row;
+    const int per_block = per_block_row * key_splits;
+    const int total_items = max_blocks * per_block;
     struct Item {
-        int r, g, q0, hist, kv_begin, kv_end, n_iter, last_tile;
+        int r, g, q0, hist, kv_begin, kv_end, n_iter, first_tile, last_tile, split;
         int tile_t0[2], tile_rows[2], tile_iters[2];
     };
     auto item_at = [&](int k, Item& it) -> bool {
         const int G = gridDim.x, c = blockIdx.x;
         const long long idx = (k & 1) ? (long long)(k + 1) * G - 1 - c : (long long)k * G + c;
         if (idx >= total_items) return false;
-        const int xi = (int)(idx / per_block_row), rem = (int)(idx % per_block_row);
+        const int xi = (int)(idx / per_block), rem2 = (int)(idx % per_block);
+        const int rem = rem2 % per_block_row;
+        it.split = rem2 / per_block_row;
         it.g = rem % kv_heads;
         it.r = req_list[rem / kv_heads];
         const int n_q = row_count[it.r];
@@ -183,18 +189,27 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         it.q0 = row_start[it.r];
         it.hist = history[it.r];
         const int t0 = blk * item_tiles * tokens_per_tile;
-        it.kv_begin = window > 0 ? (max(0, it.hist + t0 - window + 1) / KEYS) * KEYS : 0;
+        const int begin0 = window > 0 ? (max(0, it.hist + t0 - window + 1) / KEYS) * KEYS : 0;
         // Per row tile: its first new row, how many it has, and how many key stages reach its last row.
+        int full[2];
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
             it.tile_t0[t] = t0 + t * tokens_per_tile;
             const int count = active && t < item_tiles ? max(0, min(tokens_per_tile, n_q - it.tile_t0[t])) : 0;
             it.tile_rows[t] = count * ratio;
-            it.tile_iters[t] = count > 0 ? (it.hist + it.tile_t0[t] + count - it.kv_begin + KEYS - 1) / KEYS : 0;
+            full[t] = count > 0 ? (it.hist + it.tile_t0[t] + count - begin0 + KEYS - 1) / KEYS : 0;
         }
-        it.last_tile = it.tile_iters[1] > 0 ? 1 : 0;                 // the later rows see the most keys
+        // This item's share of the stages: the later rows see the most keys, so the block has max(full) of them.
+        const int stages = max(full[0], full[1]);
+        const int per = (stages + key_splits - 1) / key_splits;
+        const int j0 = min(stages, it.split * per), j1 = min(stages, j0 + per);
+#pragma unroll
+        for (int t = 0; t < 2; ++t) it.tile_iters[t] = max(0, min(full[t], j1) - j0);
+        it.first_tile = it.tile_iters[0] > 0 ? 0 : 1;
+        it.last_tile = it.tile_iters[1] > 0 ? 1 : 0;
         it.n_iter = it.tile_iters[it.last_tile];
-        it.kv_end = it.hist + min(n_q, t0 + item_tiles * tokens_per_tile);
+        it.kv_begin = begin0 + j0 * KEYS;
+        it.kv_end = min(it.hist + min(n_q, t0 + item_tiles * tokens_per_tile), begin0 + j1 * KEYS);
         return true;
     };
 
@@ -285,14 +300,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 // A tile's first scores of an item complete s_full right after the item before completed it with
                 // the tile's output; a waiter tells phases apart by parity only, so the tile's softmax warps must
                 // have seen the one (and read the output) before the other may happen.
-                for (int t = 0; t <= it.last_tile && ok; ++t) {
+                for (int t = it.first_tile; t <= it.last_tile && ok; ++t) {
                     if (tile_items[t] > 0)
                         ok = tc::mbar_wait(&o_read[t], (tile_items[t] - 1) & 1u, abort_flag, error_word, ERR_TCA_MMA);
                     ++tile_items[t];
                 }
                 if (ok) {
                     tc::tc_fence_after();
-                    for (int t = 0; t <= it.last_tile; ++t) issue_qk(t, 0);
+                    for (int t = it.first_tile; t <= it.last_tile; ++t) issue_qk(t, 0);
                     tc::mma_commit(&k_empty[kv0 % KV_STAGES]);
                     if (it.n_iter == 1) tc::mma_commit(q_empty);          // the item's last Q K^T
                 }
@@ -333,10 +348,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         Item it;
         for (int k = 0; ok && item_at(k, it); ++k) {
             const int M = it.tile_rows[t], iters = it.tile_iters[t];
-            if (iters == 0) continue;
             const int g = it.g, q0 = it.q0, hist = it.hist, kv_begin = it.kv_begin;
             const bool valid = row < M;
-            const int ti = it.tile_t0[t] + min(row, M - 1) / ratio;
+            const int ti = it.tile_t0[t] + min(row, max(M, 1) - 1) / ratio;
+            // Where this row's sums over the item's key range go when the keys are cut into ranges.
+            float* part = key_splits > 1
+                ? partial + (((size_t)(q0 + ti) * heads + g * ratio + row % ratio) * key_splits + it.split) * PART
+                : nullptr;
+            if (iters == 0) {
+                // None of the range's keys reach these rows: say so (maximum -inf, sum 0) and go on.
+                if (part && valid) {
+                    part[D] = -INFINITY;
+                    part[D + 1] = 0.0f;
+                }
+                continue;
+            }
             const int pos = hist + ti;
             const int lo = window > 0 ? max(0, pos - window + 1) : 0;
             float m_used = -INFINITY, l_run = 0.0f;
@@ -426,12 +452,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 tc::tc_fence_after();
                 const float inv = 1.0f / l_run;
                 __nv_bfloat16* dst = out + ((size_t)(q0 + ti) * heads + g * ratio + row % ratio) * D;
+                if (part && valid) {
+                    part[D] = m_used;
+                    part[D + 1] = l_run;
+                }
 #pragma unroll
                 for (int c = 0; c < D; c += 32) {
                     uint32_t v[32];
                     tc::tmem_ld_32x32(o_addr + c, v);
                     tc::tmem_wait_ld();
-                    if (valid) {
+                    if (part) {
+                        if (valid) {
+#pragma unroll
+                            for (int d = 0; d < 32; d += 4)
+                                *reinterpret_cast<uint4*>(part + c + d) = make_uint4(v[d], v[d + 1], v[d + 2], v[d + 3]);
+                        }
+                    } else if (valid) {
 #pragma unroll
                         for (int d = 0; d < 32; d += 8) {
                             const uint4 val = make_uint4(
@@ -456,6 +492,40 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         tc::tc_fence_after();
         tc::tmem_dealloc(tmem_base, TMEM_COLS);
     }
+}
+
+// Adds up the key ranges of a launch with `key_splits` > 1: one warp per (new row, head) reads the ranges' partial
+// outputs o_s with their maxima m_s and sums l_s and writes  sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s.
+__global__ void __launch_bounds__(128)
+attn_prefill_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
+                          const int* __restrict__ req_list, const int* __restrict__ row_start,
+                          const int* __restrict__ row_count, int heads, int key_splits) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = req_list[blockIdx.y];
+    const int lane = threadIdx.x & 31;
+    const long long idx = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int ti = (int)(idx / heads), head = (int)(idx % heads);
+    if (ti >= row_count[r]) return;
+    const size_t slot = (size_t)(row_start[r] + ti) * heads + head;
+    const float* base = partial + slot * key_splits * PART;
+    float m = -INFINITY;
+    for (int s = 0; s < key_splits; ++s) m = fmaxf(m, base[s * PART + D]);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float l = 0.0f;
+    for (int s = 0; s < key_splits; ++s) {
+        const float ls = base[s * PART + D + 1];
+        if (ls > 0.0f) {                      // a range none of whose keys reached the row left its output unwritten
+            const float w = exp2f(base[s * PART + D] - m);
+            const float4 o = *reinterpret_cast<const float4*>(base + s * PART + 4 * lane);
+            acc.x = fmaf(w, o.x, acc.x); acc.y = fmaf(w, o.y, acc.y);
+            acc.z = fmaf(w, o.z, acc.z); acc.w = fmaf(w, o.w, acc.w);
+            l = fmaf(w, ls, l);
+        }
+    }
+    const float inv = 1.0f / l;
+    *reinterpret_cast<uint2*>(out + slot * D + 4 * lane) =
+        make_uint2(attn::pack_bf16(acc.x * inv, acc.y * inv), attn::pack_bf16(acc.z * inv, acc.w * inv));
 }
 
 // q [rows, heads, 128] bfloat16 as (64 columns) x (head within the group) x (row) x (half of the head) x (kv head):
@@ -500,11 +570,14 @@ LLMX_EXPORT int llmx_attn_prefill_tc_cache_map(void* out, const void* cache, lon
 
 // Attention for the requests req_list[0..n_req), each bringing row_count[r] (<= max_rows) new rows after history[r]
 // keys; q/out [total_rows, heads, 128] bfloat16.  `item_tiles`: row tiles a work item holds (1 or 2; 0: chosen here).
+// `key_splits` > 1 cuts every item's keys into that many ranges, whose results meet in `partial` (float32,
+// total_rows * heads * key_splits * 132 values, 16-byte aligned) and are added up by a second kernel.
 LLMX_EXPORT int llmx_attn_prefill_tc(const void* cache_map, const void* q, void* out, int total_rows,
                                      const int* req_list, int n_req, const int* row_start, const int* row_count,
                                      const int* history, const int* block_tables, int table_stride, int heads,
                                      int kv_heads, int head_dim, int page_size, int window, float scale, int max_rows,
-                                     int item_tiles, int* error_word, cudaStream_t stream) {
+                                     int item_tiles, int key_splits, float* partial, int* error_word,
+                                     cudaStream_t stream) {
     if (n_req <= 0 || max_rows <= 0) return 0;
     if (head_dim != D || page_size != PAGE || heads % kv_heads || ROWS % (heads / kv_heads) || n_req > 65535 ||
         kv_heads > 65535 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15))
@@ -518,7 +591,8 @@ LLMX_EXPORT int llmx_attn_prefill_tc(const void* cache_map, const void* q, void*
     }
     CUtensorMap q_map;
     if (int e = make_q_map(&q_map, q, (uint64_t)total_rows, heads, kv_heads)) return e;
-    if (item_tiles < 0 || item_tiles > 2) return LLMX_ERR_BAD_ARGUMENT;
+    if (item_tiles < 0 || item_tiles > 2 || key_splits < 1 || (key_splits > 1 && (!partial || ((uintptr_t)partial & 15))))
+        return LLMX_ERR_BAD_ARGUMENT;
     static int sm_count = 0;
     if (!sm_count) {
         int dev = 0;
@@ -536,12 +610,18 @@ LLMX_EXPORT int llmx_attn_prefill_tc(const void* cache_map, const void* q, void*
     const int tokens_per_block = item_tiles * tokens_per_tile;
     const int max_blocks = (max_rows + tokens_per_block - 1) / tokens_per_block;
     // One block of threads per SM at most (a block takes the SM's shared and tensor memory); each walks its items.
-    const long long items = (long long)max_blocks * kv_heads * n_req;
+    const long long items = (long long)max_blocks * kv_heads * n_req * key_splits;
     if (items >= (1ll << 31)) return LLMX_ERR_UNSUPPORTED;
     dim3 grid((unsigned)(items < sm_count ? items : sm_count), 1, 1);
     launch_kernel(attn_prefill_tc_kernel, grid, dim3(THREADS), (size_t)SMEM_BYTES, stream, q_map,
                   *(const CUtensorMap*)cache_map, (__nv_bfloat16*)out, req_list, row_start, row_count, history,
                   block_tables, table_stride, heads, kv_heads, window, scale * attn::LOG2E, n_req, max_blocks, item_tiles,
-                  error_word);
+                  key_splits, partial, error_word);
+    if (int e = launch_status()) return e;
+    if (key_splits > 1) {
+        const long long warps = (long long)max_rows * heads;
+        launch_kernel(attn_prefill_merge_kernel, dim3((unsigned)((warps + 3) / 4), (unsigned)n_req, 1), dim3(128), 0, stream,
+                      (const float*)partial, (__nv_bfloat16*)out, req_list, row_start, row_count, heads, key_splits);
+    }
     return launch_status();
 }

@@ -28,7 +28,7 @@ register_signature("attention_decode", "llmx_attn_decode_qkv",
                     _i, _f, _i, _p, _i, _i, _p, _p, _p])
 register_signature("attention_prefill_tc", "llmx_attn_prefill_tc_cache_map", [_p, _p, _ll, _i, _i, _i])
 register_signature("attention_prefill_tc", "llmx_attn_prefill_tc",
-                   [_p, _p, _p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p])
+                   [_p, _p, _p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _p, _p, _p])
 register_signature("attention_prefill", "llmx_attn_prefill",
                    [_p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p])
 
@@ -125,6 +125,34 @@ def decode_schedule(n_requests: int, kv_heads: int, max_context: int) -> Tuple[i
     return splits, chunk
 
 
+PREFILL_PART = 132             # floats of one (row, head, key range) partial result of the tcgen05 prefill kernel
+PREFILL_MAX_PARTIAL = 1 << 26  # floats (256 MiB) the key ranges' partial results may take
+
+
+def prefill_shape(n_requests: int, kv_heads: int, ratio: int, max_rows: int, max_context: int, window: int,
+                  sms: int = 148) -> Tuple[int, int]:
+    """(row tiles an item, key ranges) for the tcgen05 prefill kernel.  Its work items are (request, kv head, block of
+    rows); a block of threads walks an item's key stages one after the other, so when items are fewer than the SMs
+    the longest item is the kernel's time.  Two row tiles an item share their key stages and keep the tensor core
+    busier (about 1.05 us a tile and stage of 128 keys against 1.9 us for a tile alone); cutting the keys into
+    ranges makes more, shorter items at the price of a second small kernel that adds the ranges up.  The estimate
+    below takes the cheapest of the combinations."""
+    per_tile = max(1, 128 // ratio)
+    reach = min(max_context, window + max_rows) if window else max_context
+    stages = -(-reach // 128)
+    best = None
+    for tiles, rate in ((2, 2.1), (1, 1.9)):
+        items = -(-max_rows // (tiles * per_tile)) * kv_heads * n_requests
+        for splits in (1, 2, 3, 4, 6, 8):
+            if splits > 1 and (stages < 8 * splits or max_rows * kv_heads * ratio * n_requests * splits * PREFILL_PART
+                               > PREFILL_MAX_PARTIAL):
+                break
+            t = -(-items * splits // sms) * -(-stages // splits) * rate + (6.0 if splits > 1 else 0.0)
+            if best is None or t < best[0] - 1e-9:
+                best = (t, tiles, splits)
+    return best[1], best[2]
+
+
 def _request_lists(step, max_rows: int):
     """Device lists of the requests that bring at most `max_rows` rows and of the others (cached on the step)."""
     key = ("attn_lists", max_rows)
@@ -185,11 +213,23 @@ def paged_attention_bf16(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
             _ptr(counters), _ptr(err), _stream()), "attention_decode", 2 if splits > 1 and counters is None else 1)
     if n_large and tensor_core_prefill(heads, kv_heads, head_dim, cache.shape[3]) and not step.extras.get("no_tc_attention"):
         hmap = cache_half_map(cache)
+        ctx_large = step.extras.get("attn_ctx_large")
+        if ctx_large is None:
+            ctx_large = max(step.host_history[r] + n for r, n in enumerate(step.host_row_count) if n > max_rows)
+        tiles, splits = step.extras.get("attn_prefill_shape") or prefill_shape(n_large, kv_heads, ratio, rows_large,
+                                                                               ctx_large, int(window or 0))
+        partial = None
+        if splits > 1:
+            key = ("attn_prefill_partial", splits, heads)
+            partial = step.extras.get(key)
+            if partial is None:
+                partial = torch.empty((q.shape[0] * heads * splits * PREFILL_PART,), dtype=torch.float32, device=q.device)
+                step.extras[key] = partial
         _check(_fn("attention_prefill_tc", "llmx_attn_prefill_tc")(
             ctypes.c_void_p(hmap.address), _ptr(q), _ptr(out), q.shape[0], _ptr(large), n_large, _ptr(step.row_start),
             _ptr(step.row_count), _ptr(step.history), _ptr(tables), tables.shape[1], heads, kv_heads, head_dim,
-            cache.shape[3], win, float(scale), rows_large, int(step.extras.get("attn_item_tiles", 0)), _ptr(err),
-            _stream()), "attention_prefill_tc")
+            cache.shape[3], win, float(scale), rows_large, tiles, splits, _ptr(partial), _ptr(err), _stream()),
+            "attention_prefill_tc", 2 if splits > 1 else 1)
     elif n_large:
         _check(_fn("attention_prefill", "llmx_attn_prefill")(
             ctypes.c_void_p(cmap.address), _ptr(q), _ptr(out), _ptr(large), n_large, _ptr(step.row_start),

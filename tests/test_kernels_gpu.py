@@ -277,17 +277,19 @@ def test_attention_tiled_bf16(heads, kv_heads, head_dim, layout, window, spike):
     assert np.abs(got - ref).max() <= 2e-2 * max(1.0, np.abs(ref).max())
 
 
-@pytest.mark.parametrize("item_tiles", [1, 2])
+@pytest.mark.parametrize("item_tiles,key_splits", [(1, 1), (2, 1), (1, 2), (2, 2), (2, 3), (1, 5)])
 @pytest.mark.parametrize("heads,kv_heads", [(32, 8), (16, 8), (8, 8)])
-def test_attention_prefill_items_of_one_row_tile_or_two(item_tiles, heads, kv_heads):
-    """The tcgen05 prefill kernel pairs two row tiles in a work item, or takes one an item when pairs would be
-    fewer than the SMs (the launcher's choice; forced both ways here)."""
+@pytest.mark.parametrize("window", [None, 300])
+def test_attention_prefill_items_of_any_shape(item_tiles, key_splits, heads, kv_heads, window):
+    """The tcgen05 prefill kernel's work items hold one row tile or two, and all of a block's keys or one of
+    several ranges of them (a second kernel then adds the ranges up); the launcher chooses, here every
+    combination is forced.  Short requests leave ranges without keys and rows that a range's keys do not reach."""
     from llmx_b200 import ops_attn, ops_tc
-    layout = [(0, 300), (77, 130), (500, 64), (3, 33), (40, 1)]
-    q, cache, step, group, ref = _attention_case(torch.bfloat16, heads, kv_heads, 128, 16, layout, None, seed=23, spike=True)
-    step.extras["attn_item_tiles"] = item_tiles
+    layout = [(0, 300), (77, 130), (1500, 64), (3, 33), (40, 1), (700, 200)]
+    q, cache, step, group, ref = _attention_case(torch.bfloat16, heads, kv_heads, 128, 16, layout, window, seed=23, spike=True)
+    step.extras["attn_prefill_shape"] = (item_tiles, key_splits)
     out = torch.full_like(q, float("nan"))
-    ops_attn.paged_attention_bf16(q, cache, out, step, group, heads, kv_heads, 128, None, 1.0 / math.sqrt(128))
+    ops_attn.paged_attention_bf16(q, cache, out, step, group, heads, kv_heads, 128, window, 1.0 / math.sqrt(128))
     torch.cuda.synchronize()
     ops_tc.check_errors()
     got = out.float().cpu().numpy()
