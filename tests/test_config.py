@@ -119,3 +119,32 @@ def test_matrix_product_plan_fills_the_sms():
     assert ops_tc._plan(4096, 6144, 4096, False, sms)[2] == 1
     # k ranges never outnumber the k blocks
     assert ops_tc._plan(128, 4096, 64, True, sms)[2] == 1
+
+
+def test_attention_shapes_fill_the_sms():
+    """The host-side choices for attention (pure functions of the step's shape): row tiles an item and key ranges
+    for prompt portions, key ranges for decoding rows, weight rows a tile for the q/k/v product."""
+    from llmx_b200 import ops_attn, ops_tc
+    # a whole prompt makes items enough: pairs of row tiles, all keys
+    assert ops_attn.prefill_shape(1, 8, 4, 2048, 2048, 0) == (2, 1)
+    # a short portion: fewer pairs than half the SMs, so single tiles; few key stages, so no ranges
+    assert ops_attn.prefill_shape(1, 8, 4, 256, 256, 0) == (1, 1)
+    # a portion after a long history: the keys are cut into ranges, more of them the fewer the items
+    tiles, ranges = ops_attn.prefill_shape(1, 8, 4, 512, 4608, 0)
+    assert ranges >= 2
+    assert ops_attn.prefill_shape(1, 8, 4, 256, 8448, 0)[1] > ranges
+    # a window bounds the keys an item walks, whatever the history
+    assert ops_attn.prefill_shape(1, 8, 4, 512, 40000, 512)[1] == 1
+    # the partial results stay within their bound
+    for rows, ctx in ((512, 4608), (2048, 40000), (8192, 40000)):
+        t, r = ops_attn.prefill_shape(4, 8, 4, rows, ctx, 0)
+        assert r == 1 or rows * 32 * 4 * r * ops_attn.PREFILL_PART <= ops_attn.PREFILL_MAX_PARTIAL
+    # decoding rows: one range below 1,024 keys, never more blocks than a wave
+    assert ops_attn.decode_schedule(8, 8, 512)[0] == 1
+    for n, ctx in ((1, 8192), (8, 8192), (64, 8192), (4, 32768)):
+        splits, chunk = ops_attn.decode_schedule(n, 8, ctx)
+        assert splits * chunk >= ctx and chunk % 64 == 0 and (splits == 1 or n * 8 * splits <= ops_attn.WAVE_BLOCKS)
+    # the q/k/v product finishes its heads itself from 256 rows on
+    ops_tc._sm_count = ops_tc._sm_count or 148
+    assert ops_tc.heads_tile(255, 32, 8) == 0 and ops_tc.heads_tile(256, 32, 8) in (128, 256)
+    assert ops_tc.heads_tile(2048, 32, 8) == 256
