@@ -275,6 +275,31 @@ def test_long_prompts_at_8b_width(wide_model_dir):
         del engine
 
 
+def test_long_portions_recorded_at_8b_width(wide_model_dir):
+    """The same shapes of long steps come again and are replayed from recordings: the q/k/v product that finishes its
+    heads and the prefill attention's key ranges (chosen when the step is recorded) inside a recording, on other
+    pages from the second time on, against the plain implementation."""
+    from llmx_b200 import ops_tc
+    from llmx_b200.engine import Engine, EngineOptions
+    vocab = WIDE["vocab_size"]
+    engine = Engine.from_dir(wide_model_dir, EngineOptions(dtype="bfloat16", kv_tokens=4096, page_size=16, max_requests=4,
+                                                           record_after=1))
+    from llmx_b200 import ops_attn
+    assert ops_attn.prefill_shape(1, 8, 4, 280, 2200, 0)[1] > 1                # 280 rows after 1,920 keys: key ranges
+    requests = {"x": helpers.random_ids(vocab, 2200, seed=70)}
+    steps = helpers.trace_portions(requests, portions=(1920, 280))
+    for run in range(3):
+        if run == 1:
+            engine.step([helpers_entry("pad", helpers.random_ids(vocab, 50, seed=1))])      # other pages from here on
+        got = helpers.run_trace(engine, steps, record=True)
+        ops_tc.check_errors()
+        worst, scale, where = helpers.compare(got, requests, wide_model_dir, True)
+        assert worst <= TOL["bfloat16"] * scale, f"run {run}: largest difference {worst:.3e} at {where}"
+    assert len(engine.step_recordings) == 2
+    engine.end("pad")
+    engine.cache.check()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["B", "wide"])
 def test_recorded_steps_of_any_shape(model_dirs, wide_model_dir, name, dtype):
