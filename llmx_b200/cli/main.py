@@ -17,9 +17,11 @@ USAGE = """usage:
   llmx generate MODEL (IDS | --file F) [-n N|--max-tokens N] [--temp T] [--topk K] [--topp P] [--min-p P]
                 [--penalty P] [--presence-penalty P] [--frequency-penalty P] [--seed S] [--ignore-eos]
                 [--dtype auto|bf16|f32] [--ubatch N] [--kv-tokens N] [--cache-type-k T] [--cache-type-v T]
-                [--device D] [--verbose]
+                [--yarn F] [--yarn-original-ctx N] [--device D] [--verbose]
       MODEL   a folder with config.json and model.safetensors
       IDS     the prompt as token ids, e.g. 1,2,3
+      --yarn F   the rope scaled by YaRN at factor F over the trained length (--yarn-original-ctx N, default the
+                 files' declared one, else their context); the model's context becomes F times that length
   llmx logits MODEL (IDS | --file F) [--top K] [--last N] [--per-token] [--dtype auto|bf16|f32] [--ubatch N]
       the K best next tokens (default 5) after each of the last N positions (default 1); --per-token feeds
       the ids one at a time instead of in portions of --ubatch
@@ -73,6 +75,17 @@ def _dtype(value: str) -> str:
     return table[value]
 
 
+def _yarn(given: Dict[str, str]) -> Tuple[Optional[float], Optional[int]]:
+    """--yarn F and --yarn-original-ctx N (src/cli/main.cpp:567-571, :597)."""
+    yarn = _float("--yarn", given["--yarn"], 1.0, 3.4028234e38) if "--yarn" in given else None
+    if yarn == 1.0:
+        raise UsageError("--yarn: a factor above 1")
+    original = _int("--yarn-original-ctx", given["--yarn-original-ctx"], 1) if "--yarn-original-ctx" in given else None
+    if original is not None and yarn is None:
+        raise UsageError("--yarn-original-ctx is the length --yarn scales from; give --yarn")
+    return yarn, original
+
+
 def _parse(argv: List[str], valued: Dict[str, str], switches: Tuple[str, ...]):
     """Splits argv into ({flag: text}, [positional]); refuses unknown and repeated flags."""
     given: Dict[str, str] = {}
@@ -103,7 +116,7 @@ def cmd_generate(argv: List[str]) -> int:
     from ..sampling import SamplingParams
     valued = {k: k for k in ("--max-tokens", "--temp", "--topk", "--topp", "--min-p", "--penalty", "--presence-penalty",
                              "--frequency-penalty", "--seed", "--dtype", "--ubatch", "--kv-tokens", "--cache-type-k",
-                             "--cache-type-v", "--device", "--file")}
+                             "--cache-type-v", "--device", "--file", "--yarn", "--yarn-original-ctx")}
     given, pos = _parse(argv, valued, ("--ignore-eos", "--verbose"))
     if not pos:
         raise UsageError("missing the model")
@@ -140,10 +153,12 @@ def cmd_generate(argv: List[str]) -> int:
     kv_tokens = _int("--kv-tokens", given["--kv-tokens"], 1) if "--kv-tokens" in given else None
     if kv_tokens is None:
         kv_tokens = -(-(len(prompt) + params.max_tokens) // 64) * 64
+    yarn, yarn_original = _yarn(given)
 
     from ..engine.generate import LLM
     t0 = time.perf_counter()
-    llm = LLM(model, dtype=dtype, kv_tokens=kv_tokens, ubatch=ubatch, max_seqs=1, device=given.get("--device", "cuda:0"))
+    llm = LLM(model, dtype=dtype, kv_tokens=kv_tokens, ubatch=ubatch, max_seqs=1, device=given.get("--device", "cuda:0"),
+              yarn=yarn, yarn_original_ctx=yarn_original)
     if "--verbose" in given:
         print(f"load: {time.perf_counter() - t0:.2f} s", file=sys.stderr)
         print(f"prompt tokens: {len(prompt)}")

@@ -8,7 +8,7 @@ src/model/arch/hf_config.hpp:125-155 and src/model/rope.hpp:105-146).
 from __future__ import annotations
 
 import math
-from dataclasses import dataclass, field, asdict
+from dataclasses import dataclass, field, asdict, replace
 from typing import Any, Dict, Optional
 
 from .base import ConfigError, ModelConfig, Rule, apply_rules, _is_int
@@ -154,6 +154,28 @@ class Qwen3Config(ModelConfig):
         if isinstance(e, list):
             return tuple(int(x) for x in e)
         return (int(e),)
+
+    def with_yarn(self, factor: float, original: Optional[int] = None) -> "Qwen3Config":
+        """This configuration with its rope scaled by YaRN at `factor` (what --yarn asks, src/model/rope.hpp:131-146):
+        over `original` positions if given (at most the model's context), else over the original length the file
+        declares, else over the file's context; the context becomes floor(factor x original).  The file's beta_fast
+        and beta_slow are kept when it declares YaRN itself."""
+        if not (isinstance(factor, (int, float)) and math.isfinite(factor) and factor > 1):
+            raise ConfigError("qwen3: --yarn must be a finite factor above 1")
+        declared = self.rope_scaling
+        if original is not None:
+            if not _is_int(original) or original < 1 or original > self.max_position_embeddings:
+                raise ConfigError(f"qwen3: --yarn-original-ctx {original} is past the model's context of "
+                                  f"{self.max_position_embeddings}")
+            base = int(original)
+        else:
+            base = declared.original_max_position_embeddings if declared else self.max_position_embeddings
+        context = math.floor(float(factor) * base)
+        if context > 2 ** 31 - 1:
+            raise ConfigError(f"qwen3: --yarn {factor} over {base} is past the context limit")
+        scaling = YarnScaling(float(factor), base, declared.beta_fast if declared else 32.0,
+                              declared.beta_slow if declared else 1.0)
+        return replace(self, rope_scaling=scaling, max_position_embeddings=int(context))
 
     @classmethod
     def from_dict(cls, raw: Dict[str, Any]) -> "Qwen3Config":

@@ -49,6 +49,19 @@ class EngineOptions:
     device: str = "cuda:0"
     record_after: int = 16           # plain steps of one shape before `step(..., record=True)` records it: making
     #                                  a recording costs about as much as ten to twenty plain steps save
+    yarn: Optional[float] = None     # the rope scaled by YaRN at this factor, whatever the files say (--yarn)
+    yarn_original_ctx: Optional[int] = None   # the trained length `yarn` scales from (default: the files')
+
+
+def _scaled(config, options: "EngineOptions"):
+    """The configuration with the rope scaling the options force on it, if any."""
+    if options.yarn is None:
+        if options.yarn_original_ctx is not None:
+            raise StepError("yarn_original_ctx is the length `yarn` scales from; give `yarn`")
+        return config
+    if not hasattr(config, "with_yarn"):
+        raise StepError(f"{type(config).__name__} has no rope that YaRN could scale")
+    return config.with_yarn(options.yarn, options.yarn_original_ctx)
 
 
 def _pad4(n: int) -> int:
@@ -125,6 +138,7 @@ class Engine:
         """Load a folder with config.json and safetensors; the model class is chosen by config.json."""
         options = options or EngineOptions()
         entry, config = config_from_dir(model_dir)
+        config = _scaled(config, options)
         model = entry.build(config)
         source = TensorDirectory(model_dir)
         with torch.cuda.device(torch.device(options.device)):
@@ -137,6 +151,7 @@ class Engine:
         """A model of `config` with random weights made on the device (no files)."""
         from ..weights.random_init import RandomSource
         options = options or EngineOptions()
+        config = _scaled(config, options)
         entry = architecture_of(config.to_dict())
         model = entry.build(config)
         src = RandomSource(model.tensor_specs(), seed, dtype=torch.bfloat16, device=options.device, skip_optional=True)

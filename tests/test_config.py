@@ -148,3 +148,31 @@ def test_attention_shapes_fill_the_sms():
     ops_tc._sm_count = ops_tc._sm_count or 148
     assert ops_tc.heads_tile(255, 32, 8) == 0 and ops_tc.heads_tile(256, 32, 8) in (128, 256)
     assert ops_tc.heads_tile(2048, 32, 8) == 256
+
+
+def test_yarn_forced_over_the_files_rope():
+    """--yarn F [--yarn-original-ctx N]: the length it scales is N, else the files' declared original, else their
+    context; the context becomes F times that; the files' betas stay when they declare YaRN themselves."""
+    plain = Qwen3Config.from_dict(TINY_A)                       # no rope_scaling, context 512
+    c = plain.with_yarn(4.0)
+    assert c.rope_scaling.factor == 4.0 and c.rope_scaling.original_max_position_embeddings == 512
+    assert c.max_position_embeddings == 2048 and (c.rope_scaling.beta_fast, c.rope_scaling.beta_slow) == (32.0, 1.0)
+    c = plain.with_yarn(2.5, 100)
+    assert c.rope_scaling.original_max_position_embeddings == 100 and c.max_position_embeddings == 250
+    declared = Qwen3Config.from_dict(dict(TINY_B, rope_scaling=dict(rope_type="yarn", factor=2.0, beta_fast=16.0,
+                                                                    original_max_position_embeddings=512)))
+    c = declared.with_yarn(3.0)
+    assert c.rope_scaling.original_max_position_embeddings == 512 and c.max_position_embeddings == 1536
+    assert c.rope_scaling.beta_fast == 16.0
+    for bad in (1.0, 0.5, float("inf"), float("nan")):
+        with pytest.raises(ConfigError):
+            plain.with_yarn(bad)
+    with pytest.raises(ConfigError) as e:
+        plain.with_yarn(2.0, 513)
+    assert "past the model's context of 512" in str(e.value)
+    # the command line's two flags
+    from llmx_b200.cli.main import UsageError, _yarn
+    assert _yarn({}) == (None, None) and _yarn({"--yarn": "4", "--yarn-original-ctx": "128"}) == (4.0, 128)
+    for given in ({"--yarn": "1"}, {"--yarn": "0.5"}, {"--yarn-original-ctx": "128"}, {"--yarn": "2", "--yarn-original-ctx": "0"}):
+        with pytest.raises(UsageError):
+            _yarn(given)

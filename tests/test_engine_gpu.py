@@ -222,6 +222,30 @@ def test_sharp_attention_under_cutting(sharp_model_dirs, name, cutting):
     _check(engine, folder, steps, requests, "float32")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_yarn_forced_by_the_options(model_dirs, tmp_path, dtype):
+    """`EngineOptions.yarn` (the command line's --yarn) scales the rope of a model whose files declare none and
+    stretches its context: the same weights under a config.json that declares that scaling give the plain
+    implementation's logits, on a prompt longer than the files' own context."""
+    import json
+    import shutil
+    from llmx_b200.engine import Engine, EngineOptions
+    d16, d32, page = model_dirs["A"]
+    folder = d32 if dtype == "float32" else d16
+    declared = dict(CONFIGS["A"][0], max_position_embeddings=1024,
+                    rope_scaling=dict(rope_type="yarn", factor=4.0, original_max_position_embeddings=256))
+    twin = tmp_path / "declared"
+    twin.mkdir()
+    shutil.copy(f"{folder}/model.safetensors", twin / "model.safetensors")
+    (twin / "config.json").write_text(json.dumps(declared))
+    requests = {"y": helpers.random_ids(CONFIGS["A"][0]["vocab_size"], 600, seed=5)}      # past the files' 512
+    steps = helpers.trace_portions(requests, portions=(300, 2, 170, 128))
+    engine = Engine.from_dir(folder, EngineOptions(dtype=dtype, kv_tokens=helpers.tokens_needed(steps), page_size=page,
+                                                   max_requests=2, yarn=4.0, yarn_original_ctx=256))
+    assert engine.max_positions == 1024
+    _check(engine, str(twin), steps, requests, dtype)
+
+
 WIDE = dict(
     architectures=["Qwen3ForCausalLM"], model_type="qwen3",
     num_hidden_layers=2, hidden_size=4096, intermediate_size=12288, num_attention_heads=32, num_key_value_heads=8,
