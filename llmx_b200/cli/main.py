@@ -25,9 +25,10 @@ USAGE = """usage:
   llmx logits MODEL (IDS | --file F) [--top K] [--last N] [--per-token] [--dtype auto|bf16|f32] [--ubatch N]
       the K best next tokens (default 5) after each of the last N positions (default 1); --per-token feeds
       the ids one at a time instead of in portions of --ubatch
-  llmx bench --model MODEL [--p P] [--n G] [--r R] [--seqs S] [--depth D] [--dtype auto|bf16|f32]
+  llmx bench --model MODEL [--p P] [--n G] [--r R] [--seqs S] [--depth D] [--dtype auto|bf16|f32] [--profile]
       prompt of P tokens (default 512), G generated tokens (default 128), R repeats (default 3),
-      S sequences decoded together (default 1) after a history of D tokens each (default P)
+      S sequences decoded together (default 1) after a history of D tokens each (default P);
+      --profile adds the device time of each kernel in one prompt pass and one decode pass
 """
 
 SHORT = {"-n": "--max-tokens", "-ctk": "--cache-type-k", "-ctv": "--cache-type-v", "-f": "--file"}
@@ -217,7 +218,7 @@ def cmd_bench(argv: List[str]) -> int:
     import torch
     from ..engine import Engine, EngineOptions, StepEntry
     valued = {k: k for k in ("--model", "--p", "--n", "--r", "--seqs", "--depth", "--dtype", "--device")}
-    given, pos = _parse(argv, valued, ())
+    given, pos = _parse(argv, valued, ("--profile",))
     if pos:
         raise UsageError(f"bench takes flags only, not '{pos[0]}'")
     if "--model" not in given:
@@ -284,6 +285,22 @@ def cmd_bench(argv: List[str]) -> int:
         return m, (sum((x - m) ** 2 for x in v) / len(v)) ** 0.5
     print("pp%d: %.2f +- %.2f tok/s" % ((p,) + stat(pp)))
     print("tg%d x%d @%d: %.2f +- %.2f tok/s" % ((g, seqs, depth) + stat(tg)))
+    if "--profile" in given:
+        # One prompt pass and one decode pass as plain steps (a replayed recording makes no calls to time).
+        from .. import ops
+        with ops.kernel_times() as times:
+            engine.step([StepEntry("p", prompt, [p - 1])])
+        engine.end("p")
+        print("\n".join(times.lines(f"pp{p}")))
+        hist = ids(depth)
+        for s in range(seqs):
+            engine.step([StepEntry(s, hist, [])])
+        toks = ids(seqs)
+        with ops.kernel_times() as times:
+            engine.step([StepEntry(s, [toks[s]], [0]) for s in range(seqs)])
+        for s in range(seqs):
+            engine.end(s)
+        print("\n".join(times.lines(f"tg x{seqs} @{depth}")))
     return 0
 
 

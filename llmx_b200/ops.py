@@ -97,6 +97,9 @@ _SIGNATURES = {
 _fns = {}
 
 
+_timed_calls = None       # while `kernel_times` is open: [(exported function, start event, end event)]
+
+
 def _fn(lib: str, name: str):
     key = (lib, name)
     f = _fns.get(key)
@@ -105,7 +108,52 @@ def _fn(lib: str, name: str):
         f.argtypes = _SIGNATURES[key]
         f.restype = ctypes.c_int
         _fns[key] = f
-    return f
+    if _timed_calls is None:
+        return f
+
+    def timed(*args):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        status = f(*args)
+        end.record()
+        _timed_calls.append((name, start, end))
+        return status
+    return timed
+
+
+class kernel_times:
+    """Device time of every kernel call made inside the `with` block, by exported function (the reference's
+    `bench --profile`, src/cli/main.cpp:1326-1352): CUDA events around each call on the current stream.  For plain
+    steps only: a step that replays a recording makes no calls, and events must not be recorded into one.
+    The events keep a kernel from starting while the one before drains, so the times are those of kernels alone."""
+
+    def __enter__(self) -> "kernel_times":
+        global _timed_calls
+        if _timed_calls is not None:
+            raise KernelError("kernel_times is already open")
+        _timed_calls = []
+        return self
+
+    def __exit__(self, *exc) -> None:
+        global _timed_calls
+        calls, _timed_calls = _timed_calls, None
+        torch.cuda.synchronize()
+        self.calls = len(calls)
+        self.by_function = {}
+        for name, start, end in calls:
+            n, ms = self.by_function.get(name, (0, 0.0))
+            self.by_function[name] = (n + 1, ms + start.elapsed_time(end))
+        self.total_ms = sum(ms for _, ms in self.by_function.values())
+        self.idle_ms = sum(max(0.0, calls[i][2].elapsed_time(calls[i + 1][1])) for i in range(len(calls) - 1))
+
+    def lines(self, what: str):
+        """The report, most expensive first."""
+        out = [f"profile {what}: {self.total_ms:.3f} ms of device time over {self.calls} kernel calls"]
+        for name, (n, ms) in sorted(self.by_function.items(), key=lambda kv: -kv[1][1]):
+            share = 100.0 * ms / self.total_ms if self.total_ms > 0 else 0.0
+            out.append(f"profile:   {name} x{n} {ms:.3f} ms ({share:.1f}%)")
+        out.append(f"profile {what}: idle {self.idle_ms:.3f} ms between timed calls")
+        return out
 
 
 def register_signature(lib: str, name: str, argtypes) -> None:

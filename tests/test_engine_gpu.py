@@ -246,6 +246,33 @@ def test_yarn_forced_by_the_options(model_dirs, tmp_path, dtype):
     _check(engine, str(twin), steps, requests, dtype)
 
 
+def test_kernel_times_of_a_plain_step(model_dirs):
+    """`ops.kernel_times`: device time by exported kernel function over the calls of a plain step (what
+    `llmx bench --profile` prints); the step's result is what it is without the timing."""
+    import torch
+    from llmx_b200 import ops
+    from llmx_b200.engine import StepEntry
+    folder, engine = _engine(model_dirs, "B", "bfloat16", 256)
+    ids = helpers.random_ids(CONFIGS["B"][0]["vocab_size"], 40, seed=3)
+    plain = engine.step([StepEntry("a", ids, [39])]).clone()
+    engine.end("a")
+    with ops.kernel_times() as times:
+        timed = engine.step([StepEntry("a", ids, [39])]).clone()
+    engine.end("a")
+    assert torch.equal(plain, timed)
+    layers = CONFIGS["B"][0]["num_hidden_layers"]
+    assert times.calls >= 6 * layers and times.total_ms > 0 and times.idle_ms >= 0
+    assert times.by_function["llmx_rmsnorm"][0] == 2 * layers + 1
+    assert sum(n for n, _ in times.by_function.values()) == times.calls
+    report = times.lines("pp40")
+    assert report[0].startswith("profile pp40:") and report[-1].startswith("profile pp40: idle")
+    with pytest.raises(ops.KernelError):
+        with ops.kernel_times():
+            with ops.kernel_times():
+                pass
+    assert ops._timed_calls is None
+
+
 WIDE = dict(
     architectures=["Qwen3ForCausalLM"], model_type="qwen3",
     num_hidden_layers=2, hidden_size=4096, intermediate_size=12288, num_attention_heads=32, num_key_value_heads=8,
