@@ -25,10 +25,14 @@ USAGE = """usage:
   llmx logits MODEL (IDS | --file F) [--top K] [--last N] [--per-token] [--dtype auto|bf16|f32] [--ubatch N]
       the K best next tokens (default 5) after each of the last N positions (default 1); --per-token feeds
       the ids one at a time instead of in portions of --ubatch
-  llmx bench --model MODEL [--p P] [--n G] [--r R] [--seqs S] [--depth D] [--dtype auto|bf16|f32] [--profile]
-      prompt of P tokens (default 512), G generated tokens (default 128), R repeats (default 3),
-      S sequences decoded together (default 1) after a history of D tokens each (default P);
+  llmx bench --model MODEL [--p P] [--n G] [--r R] [--seqs S] [--depth D] [--dtype auto|bf16|f32] [--ubatch N]
+             [--profile]
+      prompt of P tokens (default 64) and G decoded tokens (default 64), each after a history of D tokens
+      (default 0), R repeats (default 3); with --seqs S, S sequences decode together after the prompt each;
       --profile adds the device time of each kernel in one prompt pass and one decode pass
+  llmx bench [--size N] [--iters I] [--p P] [--n G]
+      without a model: one row through an N x N weight (default 1024), a norm and a per-head norm with rotation
+      at width N, I repeats (default 5), then a two-layer model of random weights end to end
 """
 
 SHORT = {"-n": "--max-tokens", "-ctk": "--cache-type-k", "-ctv": "--cache-type-v", "-f": "--file"}
@@ -214,93 +218,180 @@ def cmd_logits(argv: List[str]) -> int:
     return 0
 
 
+def _bench_ids(seed: int, n: int, vocab: int) -> List[int]:
+    """Fixed ids spread over the vocabulary (the reference's bench_ids, src/cli/main.cpp:1185-1189)."""
+    state, out = seed & 0xFFFFFFFF, []
+    for _ in range(n):
+        state = (1664525 * state + 1013904223) & 0xFFFFFFFF
+        out.append((state >> 8) % vocab)
+    return out
+
+
+def _timed(fn) -> float:
+    import torch
+    torch.cuda.synchronize()
+    t = time.perf_counter()
+    fn()
+    torch.cuda.synchronize()
+    return time.perf_counter() - t
+
+
+def _bench_synthetic(size: int, iters: int, p: int, g: int, device: str) -> int:
+    """`llmx bench` without a model (src/cli/main.cpp:1097-1167): one row through a square weight, a norm and a
+    per-head norm with rotation at width `size`, then a two-layer model with random weights end to end."""
+    import torch
+    from .. import ops, ops_tc
+    from ..config import Qwen3Config
+    from ..engine import Engine, EngineOptions, StepEntry
+    from ..engine.decode_loop import DecodeSession
+    dev = torch.device(device)
+    with torch.cuda.device(dev):
+        x = torch.full((1, size), 0.5, device=dev)
+        w = (torch.randn(size, size, device=dev) * 0.02).to(torch.bfloat16)
+        out = torch.zeros(1, size, device=dev)
+        xb = x.to(torch.bfloat16)
+        if size % 8 == 0:
+            product = lambda: ops_tc.gemm_tc(xb, w, out)
+        else:                                   # the tensor-core product wants rows of 16 bytes
+            product = lambda: ops.gemm_plain(xb, w, out, False)
+        src = torch.sin(torch.arange(size, device=dev, dtype=torch.float32) * 0.01).reshape(1, size)
+        weight = torch.full((size,), 0.1, device=dev)
+        dst = torch.empty(1, size, device=dev)
+        half = size // 2
+        cos = torch.full((1, half), 0.99500417, device=dev)
+        sin = torch.full((1, half), 0.09983342, device=dev)
+        zero = torch.zeros(1, dtype=torch.int32, device=dev)
+        cache = torch.zeros(1, 2, 1, 16, size, device=dev)
+        q_out = torch.empty(1, size, device=dev)
+        qkv = torch.cat([src, src, src], dim=1).contiguous()
+        rope = lambda: ops.head_norm_rope_kv(qkv, 1, 1, size, weight, weight, 1e-6, cos, sin, zero, zero, q_out, cache)
+        results = []
+        for fn in (product, lambda: ops.rmsnorm(src, weight, 1e-6, dst), rope):
+            fn()
+            results.append(_timed(lambda: [fn() for _ in range(iters)]) / iters * 1e3)
+        mm_ms, rn_ms, rp_ms = results
+        print("bench: matmul %dx%d  %8.3f ms  %8.2f GFLOPS" % (size, size, mm_ms, 2.0 * size * size / (mm_ms * 1e6)))
+        print("bench: rms_norm n=%d  %8.3f ms" % (size, rn_ms))
+        print("bench: norm_rope n=%d  %8.3f ms" % (size, rp_ms))
+        # End to end on a small model of random weights: 2 layers, width 256 (src/cli/main.cpp:1150-1165).
+        cfg = Qwen3Config.from_dict(dict(num_hidden_layers=2, hidden_size=256, intermediate_size=1024, num_attention_heads=8,
+                                         num_key_value_heads=2, head_dim=32, vocab_size=512,
+                                         max_position_embeddings=max(2048, p + g + 64)))
+        engine = Engine.from_config(cfg, 12345, EngineOptions(kv_tokens=-(-(p + g + 64) // 64) * 64, max_requests=1,
+                                                              device=device))
+        prompt, gen = _bench_ids(12345, p, 512), _bench_ids(777, g, 512)
+        engine.step([StepEntry("w", prompt, [p - 1])])                    # untimed: loads the kernels
+        engine.end("w")
+        pre = _timed(lambda: engine.step([StepEntry("s", prompt, [p - 1])]))
+        session = DecodeSession(engine, ["s"], use_graph=False)
+        dec = _timed(lambda: [session.step([t]) for t in gen])
+        engine.end("s")
+        print("bench: prefill %3d tok  %8.3f ms  %8.1f tok/s" % (p, pre * 1e3, p / pre))
+        print("bench: decode  %3d tok  %8.3f ms  %8.1f tok/s" % (g, dec * 1e3, g / dec))
+    ops_tc.check_errors()
+    return 0
+
+
 def cmd_bench(argv: List[str]) -> int:
+    """`llmx bench` (src/cli/main.cpp:1192-1320, :2181-2222): with --model, prompt and decode rates of the model as
+    mean +- sd over R runs after one untimed warm-up, fixed ids, sampling outside the timer; the prompt
+    test and a single sequence's decode test run after a history of --depth tokens, --seqs S sequences decode
+    together after the prompt each.
+    Without --model, the kernels at width --size and a two-layer random model."""
     import torch
     from ..engine import Engine, EngineOptions, StepEntry
-    valued = {k: k for k in ("--model", "--p", "--n", "--r", "--seqs", "--depth", "--dtype", "--device")}
+    valued = {k: k for k in ("--model", "--p", "--n", "--r", "--seqs", "--depth", "--dtype", "--device", "--ubatch",
+                             "--size", "--iters")}
     given, pos = _parse(argv, valued, ("--profile",))
     if pos:
         raise UsageError(f"bench takes flags only, not '{pos[0]}'")
+    p = _int("--p", given.get("--p", "64"), 1)
+    g = _int("--n", given.get("--n", "64"), 1)
+    model_only = next((f for f in ("--r", "--seqs", "--depth", "--profile", "--dtype", "--ubatch") if f in given), None)
+    synthetic_only = next((f for f in ("--size", "--iters") if f in given), None)
     if "--model" not in given:
-        raise UsageError("bench needs --model (a model folder)")
-    p = _int("--p", given.get("--p", "512"), 1)
-    g = _int("--n", given.get("--n", "128"), 1)
+        if model_only:
+            raise UsageError(f"{model_only} takes --model")
+        return _bench_synthetic(_int("--size", given.get("--size", "1024"), 32), _int("--iters", given.get("--iters", "5"), 1),
+                                p, g, given.get("--device", "cuda:0"))
+    if synthetic_only:
+        raise UsageError(f"{synthetic_only} is for the synthetic bench, not --model")
     reps = _int("--r", given.get("--r", "3"), 1)
     seqs = _int("--seqs", given.get("--seqs", "1"), 1)
-    depth = _int("--depth", given.get("--depth", str(p)), 1)
+    depth = _int("--depth", given.get("--depth", "0"), 0)
+    ubatch = _int("--ubatch", given.get("--ubatch", "512"), 1)
     dtype = _dtype(given.get("--dtype", "auto"))
-    kv = -(-(max(p, depth) + g + 2 + 64) // 64) * 64 * seqs
+    reach = max(p + g, depth + p) if seqs > 1 else depth + max(p, g)
+    kv = (-(-(reach + 2) // 64) * 64 + 64) * seqs
     engine = Engine.from_dir(given["--model"], EngineOptions(dtype=dtype, kv_tokens=kv, max_requests=seqs,
                                                              device=given.get("--device", "cuda:0"), record_after=2))
+    if reach > engine.max_positions:
+        raise UsageError(f"the tests reach {reach} tokens, past the model's context of {engine.max_positions}")
     vocab = engine.model.vocab_size
-    # Fixed ids spread over the vocabulary (the reference's bench_ids, src/cli/main.cpp:1185-1189).
-    state = 12345
-
-    def ids(n):
-        nonlocal state
-        out = []
-        for _ in range(n):
-            state = (1664525 * state + 1013904223) & 0xFFFFFFFF
-            out.append((state >> 8) % vocab)
-        return out
-
-    def timed(fn):
-        torch.cuda.synchronize()
-        t = time.perf_counter()
-        fn()
-        torch.cuda.synchronize()
-        return time.perf_counter() - t
+    prompt, gen, history = _bench_ids(12345, p, vocab), _bench_ids(777, g, vocab), _bench_ids(4242, depth, vocab)
 
     from ..engine.decode_loop import DecodeSession
-    prompt = ids(p)
-    pp, tg = [], []
-    for rep in range(reps + 3):                       # the first repeats are the untimed warm-up: they load the
-        timed_rep = rep >= 3                          # kernels, and a shape that comes again gets recorded
-        dt = timed(lambda: engine.step([StepEntry("p", prompt, [p - 1])], record=True))
-        engine.end("p")
-        if timed_rep:
-            pp.append(p / dt)
-        if not timed_rep and rep:
-            continue                                  # one warm-up round of decoding is enough
-        hist = ids(depth)
-        for s in range(seqs):
-            engine.step([StepEntry(s, hist, [])])
-        toks = ids(seqs)
-        session = DecodeSession(engine, list(range(seqs)))
+
+    def feed(rid, ids, want_last, record=True):
+        for at in range(0, len(ids), ubatch):
+            part = ids[at:at + ubatch]
+            last = at + ubatch >= len(ids)
+            engine.step([StepEntry(rid, part, [len(part) - 1] if want_last and last else [])], record=record)
+
+    def pp(record=True) -> float:
+        if depth:
+            feed("s", history, False)
+        dt = _timed(lambda: feed("s", prompt, True, record))
+        engine.end("s")
+        return p / dt
+
+    def tg(profile=None) -> float:
+        ids = list(range(seqs)) if seqs > 1 else ["s"]
+        for rid in ids:
+            feed(rid, prompt if seqs > 1 else (history or [gen[0]]), False)
+        session = DecodeSession(engine, ids, use_graph=profile is None)
         for _ in range(2):                            # the session's plain step and its recording are not timed
-            session.step(toks)
+            session.step([gen[0]] * seqs)
+        if profile is not None:
+            with profile:
+                session.step([gen[0]] * seqs)
 
         def decode():
-            for _ in range(g):
-                session.step(toks)
-        dt = timed(decode)
+            for t in gen:
+                session.step([t] * seqs)               # a server reads each pass's logits; here they stay on the device
+        dt = _timed(decode)
         session.close()
-        for s in range(seqs):
-            engine.end(s)
-        if timed_rep:
-            tg.append(g * seqs / dt)
+        for rid in ids:
+            engine.end(rid)
+        return g * seqs / dt
 
-    def stat(v):
+    tg()                                               # untimed: loads the kernels
+    for _ in range(4):                                 # untimed: a shape that keeps coming gets recorded
+        pp()
+    ppv = [pp() for _ in range(reps)]
+    tgv = [tg() for _ in range(reps)]
+
+    def report(what: str, n: int, v: List[float]) -> None:
         m = sum(v) / len(v)
-        return m, (sum((x - m) ** 2 for x in v) / len(v)) ** 0.5
-    print("pp%d: %.2f +- %.2f tok/s" % ((p,) + stat(pp)))
-    print("tg%d x%d @%d: %.2f +- %.2f tok/s" % ((g, seqs, depth) + stat(tg)))
+        sd = (sum((x - m) ** 2 for x in v) / (len(v) - 1)) ** 0.5 if len(v) > 1 else 0.0
+        at = f" @ d{depth}" if depth else ""
+        print("bench: %s%d%s  %8.2f +- %.2f tok/s  (%d runs)" % (what, n, at, m, sd, len(v)))
+    report("pp", p, ppv)
+    report(f"x{seqs} tg" if seqs > 1 else "tg", g, tgv)
     if "--profile" in given:
         # One prompt pass and one decode pass as plain steps (a replayed recording makes no calls to time).
         from .. import ops
+        if depth:
+            feed("s", history, False)
         with ops.kernel_times() as times:
-            engine.step([StepEntry("p", prompt, [p - 1])])
-        engine.end("p")
+            feed("s", prompt, True, record=False)
+        engine.end("s")
         print("\n".join(times.lines(f"pp{p}")))
-        hist = ids(depth)
-        for s in range(seqs):
-            engine.step([StepEntry(s, hist, [])])
-        toks = ids(seqs)
-        with ops.kernel_times() as times:
-            engine.step([StepEntry(s, [toks[s]], [0]) for s in range(seqs)])
-        for s in range(seqs):
-            engine.end(s)
-        print("\n".join(times.lines(f"tg x{seqs} @{depth}")))
+        times = ops.kernel_times()
+        tg(profile=times)
+        print("\n".join(times.lines(f"x{seqs} tg" if seqs > 1 else "tg")))
+    from .. import ops_tc
+    ops_tc.check_errors()
     return 0
 
 

@@ -207,4 +207,17 @@ def test_command_line(model_dirs, tmp_path):
            [l.split()[4].split(":")[0] for l in lines]
     bench = subprocess.run(exe + ["bench", "--model", d16, "--p", "40", "--n", "5", "--r", "1", "--seqs", "2"],
                            capture_output=True, text=True, timeout=600)
-    assert bench.returncode == 0 and "pp40:" in bench.stdout and "tg5 x2" in bench.stdout, bench.stderr[-2000:]
+    assert bench.returncode == 0 and "bench: pp40 " in bench.stdout and "bench: x2 tg5 " in bench.stdout, bench.stderr[-2000:]
+    deep = subprocess.run(exe + ["bench", "--model", d16, "--p", "20", "--n", "4", "--r", "2", "--depth", "70", "--ubatch", "16",
+                                 "--profile"], capture_output=True, text=True, timeout=600)
+    assert deep.returncode == 0 and "bench: pp20 @ d70 " in deep.stdout and "bench: tg4 @ d70 " in deep.stdout, deep.stderr[-2000:]
+    assert "profile pp20:" in deep.stdout and "profile tg:" in deep.stdout and "llmx_rmsnorm" in deep.stdout
+    synthetic = subprocess.run(exe + ["bench", "--size", "96", "--iters", "2", "--p", "12", "--n", "3"], capture_output=True,
+                               text=True, timeout=600)
+    assert synthetic.returncode == 0, synthetic.stderr[-2000:]
+    for line in ("bench: matmul 96x96", "bench: rms_norm n=96", "bench: norm_rope n=96", "bench: prefill  12 tok",
+                 "bench: decode    3 tok"):
+        assert line in synthetic.stdout, synthetic.stdout
+    for bad in (["bench", "--r", "2"], ["bench", "--model", d16, "--size", "64"]):
+        r = subprocess.run(exe + bad, capture_output=True, text=True, timeout=120)
+        assert r.returncode == 2 and "usage:" in r.stderr, bad
