@@ -60,6 +60,32 @@ struct QkvInput {
     __nv_bfloat16* cache;          // [pages, 2, kv_heads, 16, 128]
 };
 
+// ---- thread-block clusters: a barrier over all threads of all blocks of the cluster, this block's rank, and loads
+// from another block's shared memory.
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_map(uint32_t smem_addr, uint32_t rank) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_addr), "r"(rank));
+    return a;
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+
 // One row of 128 values by one warp, lane l holding values 4l .. 4l+3: RMSNorm with `weight` (skipped when
 // null), then rotation of the pairs (i, i + 64) by the angles of `pos` (skipped when the tables are null).
 // The arithmetic is that of head_norm_rope_128_kernel (rowwise.cu), operation for operation.
@@ -102,7 +128,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
                    const int* __restrict__ row_start, const int* __restrict__ row_count,
                    const int* __restrict__ history, const int* __restrict__ block_tables, int table_stride, int heads,
                    int kv_heads, int window, float scale_log2, int splits, const int* __restrict__ chunk_ptr,
-                   int chunk_keys, int* __restrict__ counters, int* error_word, const QkvInput made) {
+                   int chunk_keys, int* __restrict__ counters, int* error_word, const QkvInput made, int cluster_merge) {
     pdl_trigger();
     pdl_wait();
     using cfg = Cfg<D>;
@@ -369,6 +395,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
     __syncthreads();   // every page has been consumed: the tile memory can hold the merge buffer
 
     float* merge = (float*)tiles;   // [CONSUMERS][MAX_ROWS][D + 2]
+    constexpr int XCHG_STRIDE = D + 4;                                        // rows of 16 bytes' multiple
+    float* xchg = merge + CONSUMERS * MAX_ROWS * (D + 2);                     // [MAX_ROWS][XCHG_STRIDE]: this range's result
     if (warp < CONSUMERS) {
         const int r0 = lane >> 2;
 #pragma unroll
@@ -407,6 +435,15 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
         const size_t out_row = (size_t)(q0 + ti) * heads + h;
         if (splits == 1) {
             out[out_row * D + d] = __float2bfloat16_rn(acc / l);
+        } else if (cluster_merge) {
+            // The key ranges' blocks are one cluster: the range's result stays in this block's shared memory,
+            // where the others read it.
+            float* dst = xchg + row * XCHG_STRIDE;
+            dst[d] = acc;
+            if (d == 0) {
+                dst[D] = mm;
+                dst[D + 1] = l;
+            }
         } else {
             float* dst = partial + (out_row * splits + split) * (D + 2);
             dst[d] = acc;
@@ -416,7 +453,39 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
             }
         }
     }
-    if (splits > 1 && counters) {
+    if (splits > 1 && cluster_merge) {
+        // The ranges' blocks of a (request, kv head) are a thread-block cluster.  When all have their results in
+        // shared memory (first barrier), each block combines its share of the (row, four values) items, reading
+        // every range's maximum, sum and values through distributed shared memory; no block leaves before all
+        // have read (second barrier).  Every thread of every block gets here on every path: nothing above returns.
+        cluster_barrier();
+        const uint32_t rank = cluster_rank();
+        const int items = M * (D / 4);
+        const int per = (items + splits - 1) / splits;
+        const int last = min(items, (int)(rank + 1) * per);
+        for (int idx = (int)rank * per + threadIdx.x; idx < last; idx += THREADS) {
+            const int row = idx / (D / 4), d = (idx % (D / 4)) * 4;
+            const uint32_t mine = tc::smem_u32(xchg + row * XCHG_STRIDE);
+            float mm = -INFINITY;
+            for (int s2 = 0; s2 < splits; ++s2) mm = fmaxf(mm, ld_cluster_f32(cluster_map(mine + D * 4, s2)));
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            float l = 0.0f;
+            for (int s2 = 0; s2 < splits; ++s2) {
+                const uint32_t theirs = cluster_map(mine, s2);
+                const float ms = ld_cluster_f32(theirs + D * 4);
+                const float f = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
+                const float4 o = ld_cluster_f32x4(theirs + d * 4);
+                acc.x = fmaf(o.x, f, acc.x); acc.y = fmaf(o.y, f, acc.y);
+                acc.z = fmaf(o.z, f, acc.z); acc.w = fmaf(o.w, f, acc.w);
+                l = fmaf(ld_cluster_f32(theirs + (D + 1) * 4), f, l);
+            }
+            const float inv = 1.0f / l;
+            const size_t out_row = (size_t)(q0 + row / ratio) * heads + g * ratio + row % ratio;
+            *reinterpret_cast<uint2*>(out + out_row * D + d) =
+                make_uint2(attn::pack_bf16(acc.x * inv, acc.y * inv), attn::pack_bf16(acc.z * inv, acc.w * inv));
+        }
+        cluster_barrier();
+    } else if (splits > 1 && counters) {
         // The block that finishes last among the key ranges of this (request, kv head) combines them.
         // Nobody waits: each block counts itself in and only the one that sees the others' count goes on.
         __threadfence();
@@ -524,6 +593,36 @@ __global__ void attn_merge_kernel(const float* __restrict__ partial, __nv_bfloat
     }
 }
 
+constexpr int MAX_CLUSTER = 8;      // blocks a cluster may have on every device
+int g_cluster_merge = 1;            // llmx_attn_decode_cluster_merge(0) turns the clusters off
+
+// Whether a cluster of `size` of these blocks can run at all on this device (asked once per size).
+// How many clusters of `size` of these blocks the device runs at once (0: such a cluster cannot run; -1: the device
+// gave no answer; asked once).
+template <int D>
+int max_clusters(int size) {
+    static int known[MAX_CLUSTER + 1] = {0};         // 0: not asked yet, -1: none, -2: no answer, else the number
+    if (!known[size]) {
+        cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::SMEM_BYTES);
+        cudaLaunchConfig_t lc = {};
+        lc.gridDim = dim3(size, 1, 1);
+        lc.blockDim = dim3(THREADS);
+        lc.dynamicSmemBytes = Cfg<D>::SMEM_BYTES;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)size;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        lc.attrs = attr;
+        lc.numAttrs = 1;
+        int clusters = 0;
+        const cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, attn_decode_kernel<D>, &lc);
+        if (e != cudaSuccess) cudaGetLastError();
+        known[size] = e != cudaSuccess ? -2 : clusters > 0 ? clusters : -1;
+    }
+    return known[size] > 0 ? known[size] : known[size] == -2 ? -1 : 0;
+}
+
 template <int D>
 int launch(const CUtensorMap& map, const void* q, void* out, float* partial, const int* req_list, int n_req,
            const int* row_start, const int* row_count, const int* history, const int* block_tables, int table_stride,
@@ -538,10 +637,32 @@ int launch(const CUtensorMap& map, const void* q, void* out, float* partial, con
         configured = true;
     }
     dim3 grid(splits, kv_heads, n_req);
+    // Key ranges that are few enough to be one thread-block cluster meet in shared memory (no trip through
+    // memory, no counter); the caller's `counters` say that it wants the ranges combined by this launch.
+    if (counters && splits > 1 && splits <= MAX_CLUSTER && g_cluster_merge && max_clusters<D>(splits) > 0) {
+        cudaLaunchConfig_t lc = {};
+        lc.gridDim = grid;
+        lc.blockDim = dim3(THREADS);
+        lc.dynamicSmemBytes = cfg::SMEM_BYTES;
+        lc.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)splits;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        lc.attrs = attr;
+        lc.numAttrs = llmx_pdl_enabled() ? 2 : 1;
+        cudaLaunchKernelEx(&lc, attn_decode_kernel<D>, map, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, partial, req_list,
+                           row_start, row_count, history, block_tables, table_stride, heads, kv_heads, window,
+                           scale * attn::LOG2E, splits, chunk_ptr, chunk_keys, counters, error_word, made, 1);
+        return launch_status();
+    }
     launch_kernel(attn_decode_kernel<D>, grid, dim3(THREADS), cfg::SMEM_BYTES, stream,
         map, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, partial, req_list, row_start, row_count, history,
         block_tables, table_stride, heads, kv_heads, window, scale * attn::LOG2E, splits, chunk_ptr, chunk_keys,
-        counters, error_word, made);
+        counters, error_word, made, 0);
     int e = launch_status();
     if (e || splits == 1 || counters) return e;
     dim3 mgrid(heads, max_rows, n_req);
@@ -551,6 +672,23 @@ int launch(const CUtensorMap& map, const void* q, void* out, float* partial, con
 }
 
 }  // namespace
+
+// Key ranges of up to eight meet in a thread-block cluster's shared memory (on, the default) or, like more ranges,
+// through memory and a counter (off); returns the setting before.
+LLMX_EXPORT int llmx_attn_decode_cluster_merge(int on) {
+    const int before = g_cluster_merge;
+    g_cluster_merge = on ? 1 : 0;
+    return before;
+}
+
+// How many clusters of `size` blocks (2..8) of the kernel for this head width the device runs at once; 0 if none
+// (or if clusters are turned off), -1 if the device could not be asked: more (request, kv head) pairs than this and some clusters wait for a second round.
+LLMX_EXPORT int llmx_attn_decode_max_clusters(int head_dim, int size) {
+    if (size < 2 || size > MAX_CLUSTER || !g_cluster_merge) return 0;
+    if (head_dim == 128) return max_clusters<128>(size);
+    if (head_dim == 64) return max_clusters<64>(size);
+    return 0;
+}
 
 // The TMA descriptor of one layer's cache [pages, 2, kv_heads, page_size, head_dim] (bfloat16): 128 bytes at `out`.
 LLMX_EXPORT int llmx_attn_cache_map(void* out, const void* cache, long long pages, int kv_heads, int page_size,

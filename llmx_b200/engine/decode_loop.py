@@ -47,7 +47,8 @@ class DecodeRecording:
         self._dev = torch.zeros(self.total, dtype=torch.int32, device=eng.device)
         # Key ranges of the split-KV kernel: the grid is fixed by the recording, the keys per range are data.
         kv_heads = max((g.spec.kv_heads for g in eng.cache.groups), default=1)
-        self.splits, _ = ops_attn.decode_schedule(b, kv_heads, room)
+        head_dim = max((g.spec.head_dim for g in eng.cache.groups), default=128)
+        self.splits, _ = ops_attn.decode_schedule(b, kv_heads, room, head_dim)
 
         def dsec(i):
             return self._dev[self.offsets[i]:self.offsets[i] + self.sizes[i]]

@@ -52,7 +52,8 @@ class StepRecording:
         # Key ranges of the split-KV kernel: the grid is fixed by the recording, the keys per range are data.
         kv_heads = max((g.spec.kv_heads for g in eng.cache.groups), default=1)
         decoding = sum(1 for c in self.counts if c <= FEW_ROWS)
-        self.splits = ops_attn.decode_schedule(max(decoding, 1), kv_heads, room)[0]
+        head_dim = max((g.spec.head_dim for g in eng.cache.groups), default=128)
+        self.splits = ops_attn.decode_schedule(max(decoding, 1), kv_heads, room, head_dim)[0]
         step = eng._batch_views(self._dev, self.layout, [_NoCache()] * n, [0] * n, room)
         step.extras["decode_schedule"] = (self.splits, 64, self.layout.section(self._dev, len(self.layout.sizes) - 1))
         step.extras["recorded"] = True

@@ -26,6 +26,8 @@ register_signature("attention_decode", "llmx_attn_decode_fused",
 register_signature("attention_decode", "llmx_attn_decode_qkv",
                    [_p, _p, _i, _i, _i, _p, _p, _f, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i,
                     _i, _f, _i, _p, _i, _i, _p, _p, _p])
+register_signature("attention_decode", "llmx_attn_decode_cluster_merge", [_i])
+register_signature("attention_decode", "llmx_attn_decode_max_clusters", [_i, _i])
 register_signature("attention_prefill_tc", "llmx_attn_prefill_tc_cache_map", [_p, _p, _ll, _i, _i, _i])
 register_signature("attention_prefill_tc", "llmx_attn_prefill_tc",
                    [_p, _p, _p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _p, _p, _p])
@@ -104,22 +106,55 @@ def cache_map(cache: torch.Tensor) -> CacheMap:
     return m
 
 
-def decode_schedule(n_requests: int, kv_heads: int, max_context: int) -> Tuple[int, int]:
-    """(key ranges, keys per range).  As many ranges as fit one wave of blocks, but no more than pay: measured on a
-    B200 (32 heads over 8, graph-timed), 1 to 4 requests are fastest with 8 ranges from 1,024 keys on (16 from
-    8,192), 8 requests with 4, 16 requests with 2 from 2,048 keys on, 32 and more with 1; below 1,024 keys one range
-    is best whatever the batch (combining ranges costs about 3 us)."""
+def cluster_merge(on: bool) -> bool:
+    """Up to eight key ranges of a (request, kv head) are launched as one thread-block cluster and combined through
+    its shared memory (on, the default); off, they are combined like more ranges, through memory and a counter.
+    Returns the setting before."""
+    _cluster_counts.clear()
+    return bool(_fn("attention_decode", "llmx_attn_decode_cluster_merge")(1 if on else 0))
+
+
+# Clusters of 2..8 decode blocks (head width 128) that a B200 runs at once: what is assumed where the device
+# cannot be asked (no GPU at hand); `max_clusters` asks it.
+_B200_CLUSTERS = {2: 148, 3: 93, 4: 71, 5: 56, 6: 45, 7: 37, 8: 33}
+_cluster_counts: Dict[Tuple[int, int], int] = {}
+CLUSTER_SIZES = (8, 6, 4, 3, 2)
+CLUSTER_FILL = 0.92            # of the clusters that fit at once, as many are planned for
+
+
+def max_clusters(head_dim: int, size: int) -> int:
+    """Clusters of `size` decode blocks the device runs at once (0: clusters are turned off or cannot run)."""
+    key = (head_dim, size)
+    if key not in _cluster_counts:
+        try:
+            n = int(_fn("attention_decode", "llmx_attn_decode_max_clusters")(head_dim, size))
+        except Exception:               # no compiler
+            n = -1
+        if n < 0:                       # no device to ask: plan as for a B200
+            return _B200_CLUSTERS.get(size, 0) * (2 if head_dim == 64 else 1)
+        _cluster_counts[key] = n
+    return _cluster_counts[key]
+
+
+def decode_schedule(n_requests: int, kv_heads: int, max_context: int, head_dim: int = 128) -> Tuple[int, int]:
+    """(key ranges, keys per range) for requests that bring few rows.
+
+    Up to eight ranges of a (request, kv head) run as one thread-block cluster and meet in its shared memory; more
+    ranges meet through memory and a counter, which costs about 4 us more a launch.  A cluster starts only when
+    all its blocks find room in one part of the chip, so no more clusters are planned than the device runs at once
+    (with a margin: 32 clusters of 8 where 33 fit ran slower than 32 of 6): a second round would double the kernel's
+    time.  Measured on a B200 inside the decode step (32 heads over 8; 1 to 16 requests, 1,024 to 8,192 keys) and
+    alone (512 to 32,768 keys): one range per 128 keys below 1,024 keys, else as many as fit, eight at most; for one
+    or two requests with 16,384 keys and more, sixteen ranges through memory."""
     blocks = max(n_requests * kv_heads, 1)
     wave = WAVE_BLOCKS // blocks
-    if max_context < 1024:
-        want = 1
-    elif blocks >= 128:
-        want = max_context // 1024
-    elif max_context < 8192:
-        want = min(8, max_context // 128)
+    want = max(1, max_context // 128) if max_context < 1024 else 8
+    if max_context >= 16384 and wave >= 16:
+        splits = 16
+    elif max_clusters(head_dim, 2) > 0:
+        splits = next((s for s in CLUSTER_SIZES if s <= want and blocks <= CLUSTER_FILL * max_clusters(head_dim, s)), 1)
     else:
-        want = 16
-    splits = max(1, min(wave, want))
+        splits = max(1, min(wave, want))
     chunk = -(-(-(-max_context // 64)) // splits) * 64
     splits = max(1, -(-max_context // chunk))
     return splits, chunk
@@ -193,7 +228,7 @@ def paged_attention_bf16(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
     if n_small:
         sched = step.extras.get("decode_schedule")
         if sched is None:
-            splits, chunk = decode_schedule(n_small, kv_heads, ctx_small)
+            splits, chunk = decode_schedule(n_small, kv_heads, ctx_small, head_dim)
             chunk_ptr = None
         else:                      # a recorded step: the grid is fixed, the keys per range come from the device
             splits, chunk, chunk_ptr = sched
@@ -260,7 +295,7 @@ def decode_from_qkv(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weigh
           "attention: the product's output and the attention output do not fit the head counts")
     sched = step.extras.get("decode_schedule")
     if sched is None:
-        splits, chunk = decode_schedule(n_small, kv_heads, ctx_small)
+        splits, chunk = decode_schedule(n_small, kv_heads, ctx_small, head_dim)
         chunk_ptr = None
     else:
         splits, chunk, chunk_ptr = sched

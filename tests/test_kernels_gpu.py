@@ -384,8 +384,20 @@ def test_attention_over_long_histories(window):
     assert np.abs(got - ref).max() <= 2e-2 * max(1.0, np.abs(ref).max())
 
 
-@pytest.mark.parametrize("splits", [1, 2, 3, 7, 16])
-def test_attention_decode_any_number_of_key_ranges(splits):
+@pytest.mark.parametrize("cluster", [True, False])
+@pytest.mark.parametrize("splits", [1, 2, 3, 4, 7, 8, 16])
+def test_attention_decode_any_number_of_key_ranges(splits, cluster):
+    """Key ranges are combined through the shared memory of a thread-block cluster (up to eight ranges, unless
+    turned off) or through memory by the block that finishes last; short requests leave ranges without keys."""
+    from llmx_b200 import ops_attn, ops_tc
+    before = ops_attn.cluster_merge(cluster)
+    try:
+        _decode_with_key_ranges(splits)
+    finally:
+        ops_attn.cluster_merge(before)
+
+
+def _decode_with_key_ranges(splits):
     from llmx_b200 import ops_attn, ops_tc
     heads, kv_heads, head_dim = 8, 2, 128
     layout = [(1500, 1), (63, 1), (64, 1), (700, 2), (0, 1)]
