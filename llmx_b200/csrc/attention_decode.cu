@@ -167,9 +167,12 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
     __nv_bfloat16* q_made = (__nv_bfloat16*)(tiles + cfg::TILE_BYTES + 128);      // [MAX_ROWS][D]
     __nv_bfloat16* kv_made = q_made + MAX_ROWS * D;                              // [MAX_ROWS][2][D]
     int* kv_patch = (int*)(kv_made + 2 * MAX_ROWS * D);                          // [MAX_ROWS]: the row is to be used
+    __syncthreads();          // the barriers are ready
+    // The producer warp starts the key stages at once; the other warps meanwhile make the block's queries and new
+    // keys (if it is given the product's output) and meet at a barrier of their own before they use them.
     if constexpr (D == 128) {
-        if (made.qkv) {
-            for (int i = warp; i < M; i += THREADS / 32) {
+        if (made.qkv && warp < CONSUMERS) {
+            for (int i = warp; i < M; i += CONSUMERS) {
                 const int ti = i / ratio, h = g * ratio + i % ratio;
                 const float4 v = norm_rope_row_128(made.qkv + (size_t)(q0 + ti) * made.stride + h * D, made.q_weight,
                                                    made.eps, made.cos_table, made.sin_table, hist + ti, lane);
@@ -178,7 +181,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
             // The new keys and values that lie in this block's key range: to the cache for later steps, and kept
             // here to be laid over their page when it arrives (the copy may have read the page before or after
             // the store above landed).
-            for (int t = warp; t < n_q; t += THREADS / 32) {
+            for (int t = warp; t < n_q; t += CONSUMERS) {
                 const int p = hist + t;
                 const int slot = made.slots[q0 + t];
                 const bool mine = p >= kv_begin && p < kv_end && slot >= 0;
@@ -200,7 +203,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
             }
         }
     }
-    __syncthreads();
+    if (warp < CONSUMERS) asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory");
 
     // Per-thread accumulators of the consumer warps (rows r0 = lane / 4 and r0 + 8 of the 16-row tile).
     float o[D / 8][4];
