@@ -596,7 +596,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ partial, __nv_bfloat
     }
 }
 
-constexpr int MAX_CLUSTER = 8;      // blocks a cluster may have on every device
+constexpr int MAX_CLUSTER = 16;     // blocks a cluster may have (more than 8 is allowed on request: B200 takes 16)
 int g_cluster_merge = 1;            // llmx_attn_decode_cluster_merge(0) turns the clusters off
 
 // Whether a cluster of `size` of these blocks can run at all on this device (asked once per size).
@@ -607,6 +607,9 @@ int max_clusters(int size) {
     static int known[MAX_CLUSTER + 1] = {0};         // 0: not asked yet, -1: none, -2: no answer, else the number
     if (!known[size]) {
         cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::SMEM_BYTES);
+        if (size > 8 && cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) !=
+                            cudaSuccess)
+            cudaGetLastError();         // then the query below says that such a cluster cannot run
         cudaLaunchConfig_t lc = {};
         lc.gridDim = dim3(size, 1, 1);
         lc.blockDim = dim3(THREADS);
@@ -676,7 +679,7 @@ int launch(const CUtensorMap& map, const void* q, void* out, float* partial, con
 
 }  // namespace
 
-// Key ranges of up to eight meet in a thread-block cluster's shared memory (on, the default) or, like more ranges,
+// Key ranges of up to sixteen meet in a thread-block cluster's shared memory (on, the default) or, like more ranges,
 // through memory and a counter (off); returns the setting before.
 LLMX_EXPORT int llmx_attn_decode_cluster_merge(int on) {
     const int before = g_cluster_merge;
@@ -684,7 +687,7 @@ LLMX_EXPORT int llmx_attn_decode_cluster_merge(int on) {
     return before;
 }
 
-// How many clusters of `size` blocks (2..8) of the kernel for this head width the device runs at once; 0 if none
+// How many clusters of `size` blocks (2..16) of the kernel for this head width the device runs at once; 0 if none
 // (or if clusters are turned off), -1 if the device could not be asked: more (request, kv head) pairs than this and some clusters wait for a second round.
 LLMX_EXPORT int llmx_attn_decode_max_clusters(int head_dim, int size) {
     if (size < 2 || size > MAX_CLUSTER || !g_cluster_merge) return 0;

@@ -107,18 +107,17 @@ def cache_map(cache: torch.Tensor) -> CacheMap:
 
 
 def cluster_merge(on: bool) -> bool:
-    """Up to eight key ranges of a (request, kv head) are launched as one thread-block cluster and combined through
+    """Up to sixteen key ranges of a (request, kv head) are launched as one thread-block cluster and combined through
     its shared memory (on, the default); off, they are combined like more ranges, through memory and a counter.
     Returns the setting before."""
     _cluster_counts.clear()
     return bool(_fn("attention_decode", "llmx_attn_decode_cluster_merge")(1 if on else 0))
 
 
-# Clusters of 2..8 decode blocks (head width 128) that a B200 runs at once: what is assumed where the device
+# Clusters of 2..16 decode blocks (head width 128) that a B200 runs at once: what is assumed where the device
 # cannot be asked (no GPU at hand); `max_clusters` asks it.
-_B200_CLUSTERS = {2: 148, 3: 93, 4: 71, 5: 56, 6: 45, 7: 37, 8: 33}
+_B200_CLUSTERS = {2: 148, 3: 93, 4: 71, 5: 56, 6: 45, 7: 37, 8: 33, 12: 21, 16: 14}
 _cluster_counts: Dict[Tuple[int, int], int] = {}
-CLUSTER_SIZES = (8, 6, 4, 3, 2)
 CLUSTER_FILL = 0.92            # of the clusters that fit at once, as many are planned for
 
 
@@ -139,22 +138,28 @@ def max_clusters(head_dim: int, size: int) -> int:
 def decode_schedule(n_requests: int, kv_heads: int, max_context: int, head_dim: int = 128) -> Tuple[int, int]:
     """(key ranges, keys per range) for requests that bring few rows.
 
-    Up to eight ranges of a (request, kv head) run as one thread-block cluster and meet in its shared memory; more
-    ranges meet through memory and a counter, which costs about 4 us more a launch.  A cluster starts only when
+    Up to sixteen ranges of a (request, kv head) run as one thread-block cluster and meet in its shared memory; more
+    would meet through memory and a counter, which costs about 4 us more a launch.  A cluster starts only when
     all its blocks find room in one part of the chip, so no more clusters are planned than the device runs at once
     (with a margin: 32 clusters of 8 where 33 fit ran slower than 32 of 6): a second round would double the kernel's
-    time.  Measured on a B200 inside the decode step (32 heads over 8; 1 to 16 requests, 1,024 to 8,192 keys) and
-    alone (512 to 32,768 keys): one range per 128 keys below 1,024 keys, else as many as fit, eight at most; for one
-    or two requests with 16,384 keys and more, sixteen ranges through memory."""
+    time.  Measured on a B200 inside the decode step (32 heads over 8; 1 to 16 requests, 1,024 to 32,768 keys) and
+    alone (512 to 32,768 keys): one range per 128 keys below 1,024 keys; then as many as fit, eight at most below
+    4,096 keys, sixteen from there on (one request: 3.54 -> 3.37 ms a step at 8,192 keys), twelve where sixteen do
+    not fit only from 16,384 keys on."""
     blocks = max(n_requests * kv_heads, 1)
     wave = WAVE_BLOCKS // blocks
-    want = max(1, max_context // 128) if max_context < 1024 else 8
-    if max_context >= 16384 and wave >= 16:
-        splits = 16
-    elif max_clusters(head_dim, 2) > 0:
-        splits = next((s for s in CLUSTER_SIZES if s <= want and blocks <= CLUSTER_FILL * max_clusters(head_dim, s)), 1)
+    if max_context < 1024:
+        want, sizes = max(1, max_context // 128), (8, 6, 4, 3, 2)
+    elif max_context < 4096:
+        want, sizes = 8, (8, 6, 4, 3, 2)
+    elif max_context < 16384:
+        want, sizes = 16, (16, 8, 6, 4, 3, 2)
     else:
-        splits = max(1, min(wave, want))
+        want, sizes = 16, (16, 12, 8, 6, 4, 3, 2)
+    if max_clusters(head_dim, 2) > 0:
+        splits = next((s for s in sizes if s <= want and blocks <= CLUSTER_FILL * max_clusters(head_dim, s)), 1)
+    else:                          # clusters turned off: ranges meet through memory, a wave of blocks at most
+        splits = max(1, min(wave, want if max_context >= 16384 else min(want, 8)))
     chunk = -(-(-(-max_context // 64)) // splits) * 64
     splits = max(1, -(-max_context // chunk))
     return splits, chunk

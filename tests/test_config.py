@@ -139,10 +139,11 @@ def test_attention_shapes_fill_the_sms():
     for rows, ctx in ((512, 4608), (2048, 40000), (8192, 40000)):
         t, r = ops_attn.prefill_shape(4, 8, 4, rows, ctx, 0)
         assert r == 1 or rows * 32 * 4 * r * ops_attn.PREFILL_PART <= ops_attn.PREFILL_MAX_PARTIAL
-    # decoding rows: a range per 128 keys at first, eight (one cluster) from 1,024 keys on, sixteen for one or two
-    # requests with very long histories; never more blocks than a wave
+    # decoding rows: a range per 128 keys at first, then as many as fit as clusters (eight at most below 4,096 keys,
+    # sixteen above); never more blocks than a wave
     assert ops_attn.decode_schedule(8, 8, 100)[0] == 1 and ops_attn.decode_schedule(1, 8, 512)[0] == 4
-    assert ops_attn.decode_schedule(1, 8, 8192)[0] == 8 and ops_attn.decode_schedule(1, 8, 32768)[0] == 16
+    assert ops_attn.decode_schedule(1, 8, 2048)[0] == 8 and ops_attn.decode_schedule(1, 8, 8192)[0] == 16
+    assert ops_attn.decode_schedule(2, 8, 8192)[0] == 8 and ops_attn.decode_schedule(2, 8, 32768)[0] == 12
     assert ops_attn.decode_schedule(8, 8, 8192)[0] == 4 and ops_attn.decode_schedule(64, 8, 8192)[0] == 1
     for n, ctx in ((1, 8192), (8, 8192), (64, 8192), (4, 32768)):
         splits, chunk = ops_attn.decode_schedule(n, 8, ctx)

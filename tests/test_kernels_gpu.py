@@ -385,9 +385,9 @@ def test_attention_over_long_histories(window):
 
 
 @pytest.mark.parametrize("cluster", [True, False])
-@pytest.mark.parametrize("splits", [1, 2, 3, 4, 7, 8, 16])
+@pytest.mark.parametrize("splits", [1, 2, 3, 4, 7, 8, 12, 16, 20])
 def test_attention_decode_any_number_of_key_ranges(splits, cluster):
-    """Key ranges are combined through the shared memory of a thread-block cluster (up to eight ranges, unless
+    """Key ranges are combined through the shared memory of a thread-block cluster (up to sixteen ranges, unless
     turned off) or through memory by the block that finishes last; short requests leave ranges without keys."""
     from llmx_b200 import ops_attn, ops_tc
     before = ops_attn.cluster_merge(cluster)
