@@ -39,6 +39,10 @@ constexpr int BM = 128;      // weight rows per tile (the instruction's M)
 constexpr int BK = 64;       // bfloat16 elements per k block: one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int EPI_WARPS = 4;
+// HEADS: with up to this many token tiles (2,048 tokens) neighbouring blocks take the same weight rows and
+// different tokens (2,048 tokens: 88 -> 85 us); with more, the same tokens and different weight rows (8,192: 342 us
+// against 359).
+constexpr int HEADS_TOKEN_FIRST_TILES = 16;
 constexpr int THREADS = 64 + EPI_WARPS * 32;
 
 enum : int { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_ATOMIC = 2, MODE_SWIGLU = 3 };
@@ -85,9 +89,10 @@ struct Work {
 template <bool STREAMK>
 struct Scheduler {
     int n_tiles, m_tiles, k_blocks, splits;
+    bool wide_first;            // tiles schedule: the 128-row side's tiles vary fastest instead of the narrow side's
     long long cur, end;
-    __device__ Scheduler(int n_tiles_, int m_tiles_, int k_blocks_, int splits_)
-        : n_tiles(n_tiles_), m_tiles(m_tiles_), k_blocks(k_blocks_), splits(splits_) {
+    __device__ Scheduler(int n_tiles_, int m_tiles_, int k_blocks_, int splits_, bool wide_first_ = false)
+        : n_tiles(n_tiles_), m_tiles(m_tiles_), k_blocks(k_blocks_), splits(splits_), wide_first(wide_first_) {
         if (STREAMK) {
             const long long units = (long long)n_tiles * m_tiles * k_blocks;
             const long long per = (units + gridDim.x - 1) / gridDim.x;
@@ -110,10 +115,19 @@ struct Scheduler {
             cur += w.kb1 - w.kb0;
         } else {
             // Token tiles vary fastest, so neighbouring blocks share a weight tile.
-            w.mt = (int)(cur % m_tiles);
-            const long long rest = cur / m_tiles;
-            w.nt = (int)(rest % n_tiles);
-            const int sp = (int)(rest / n_tiles);
+            long long rest;
+            if (wide_first) {
+                w.nt = (int)(cur % n_tiles);
+                rest = cur / n_tiles;
+                w.mt = (int)(rest % m_tiles);
+                rest /= m_tiles;
+            } else {
+                w.mt = (int)(cur % m_tiles);
+                rest = cur / m_tiles;
+                w.nt = (int)(rest % n_tiles);
+                rest /= n_tiles;
+            }
+            const int sp = (int)rest;
             const int per = (k_blocks + splits - 1) / splits;
             w.kb0 = sp * per;
             w.kb1 = min(k_blocks, w.kb0 + per);
@@ -306,7 +320,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // the output) is touched only after pdl_wait(), when the kernel before has finished.
     if (warp == 0) {
         if (tc::elect_one()) {
-            Scheduler<STREAMK> sched(n_tiles, m_tiles, k_blocks, splits);
+            Scheduler<STREAMK> sched(n_tiles, m_tiles, k_blocks, splits, HEADS && n_tiles <= HEADS_TOKEN_FIRST_TILES);
             Work w;
             uint32_t stage = 0, phase = 0;
             bool ok = true, waited = false;
@@ -360,7 +374,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     } else if (warp == 1) {
         if (tc::elect_one()) {
             constexpr uint32_t idesc = tc::instr_desc_bf16(BM, BN);
-            Scheduler<STREAMK> sched(n_tiles, m_tiles, k_blocks, splits);
+            Scheduler<STREAMK> sched(n_tiles, m_tiles, k_blocks, splits, HEADS && n_tiles <= HEADS_TOKEN_FIRST_TILES);
             Work w;
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
@@ -397,7 +411,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     } else {
         // Epilogue: warp w may read the tensor-memory lanes 32 * (w % 4) .. + 31.
         const int quarter = warp & 3;
-        Scheduler<STREAMK> sched(n_tiles, m_tiles, k_blocks, splits);
+        Scheduler<STREAMK> sched(n_tiles, m_tiles, k_blocks, splits, HEADS && n_tiles <= HEADS_TOKEN_FIRST_TILES);
         Work w;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
