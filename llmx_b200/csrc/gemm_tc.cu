@@ -463,19 +463,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                                 for (int j = 0; j < CH; ++j)
                                     if (j < m_left) atomicAdd(C + (size_t)j * N, __uint_as_float(r[j]));
-                            } else if (mode == MODE_STORE) {
+                            } else {        // MODE_STORE
 #pragma unroll
                                 for (int j = 0; j < CH; ++j)
                                     if (j < m_left) C[(size_t)j * N] = __uint_as_float(r[j]);
-                            } else {
-                                // All of the chunk's old values are requested before the first is used: one
-                                // memory round trip per chunk, not one per row.
-                                float old[CH];
-#pragma unroll
-                                for (int j = 0; j < CH; ++j) old[j] = j < m_left ? __ldcg(C + (size_t)j * N) : 0.0f;
-#pragma unroll
-                                for (int j = 0; j < CH; ++j)
-                                    if (j < m_left) C[(size_t)j * N] = old[j] + __uint_as_float(r[j]);
                             }
                         }
                     }
