@@ -40,7 +40,7 @@ QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidd
                 max_position_embeddings=40960)
 
 
-# The other sizes BASELINE.json lists (same architecture, other widths), for `--size`.
+# Other published sizes of the same architecture (other widths and depths), for `--size`.
 SIZES = {
     "8b": {},
     "0.6b": dict(num_hidden_layers=28, hidden_size=1024, intermediate_size=3072, num_attention_heads=16,
