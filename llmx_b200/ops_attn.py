@@ -253,11 +253,14 @@ def paged_attention_bf16(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
             _ptr(counters), _ptr(err), _stream()), "attention_decode", 2 if splits > 1 and counters is None else 1)
     if n_large and tensor_core_prefill(heads, kv_heads, head_dim, cache.shape[3]) and not step.extras.get("no_tc_attention"):
         hmap = cache_half_map(cache)
-        ctx_large = step.extras.get("attn_ctx_large")
-        if ctx_large is None:
-            ctx_large = max(step.host_history[r] + n for r, n in enumerate(step.host_row_count) if n > max_rows)
-        tiles, splits = step.extras.get("attn_prefill_shape") or prefill_shape(n_large, kv_heads, ratio, rows_large,
-                                                                               ctx_large, int(window or 0))
+        shape = step.extras.get("attn_prefill_shape")          # forced by a test, else chosen once a step and mixer shape
+        if shape is None:
+            key = ("attn_prefill_shape", kv_heads, ratio, win)
+            shape = step.extras.get(key)
+            if shape is None:
+                ctx_large = max(step.host_history[r] + n for r, n in enumerate(step.host_row_count) if n > max_rows)
+                shape = step.extras[key] = prefill_shape(n_large, kv_heads, ratio, rows_large, ctx_large, win)
+        tiles, splits = shape
         partial = None
         if splits > 1:
             key = ("attn_prefill_partial", splits, heads)
