@@ -106,11 +106,16 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def reference_arm():
-    why = ("mxxm-t/llmx is a C++/CMake project with no Python packaging and no sm_100 build target; "
-           "pip install of its source tree fails (neither setup.py nor pyproject.toml)")
-    print(json.dumps({"impl": "reference", "unavailable": why}))
-    return 0
+def reference_arm(args):
+    """The unmodified reference, built with its own CMake and timed by its own `llmx bench` on the same
+    configuration (baseline/reference_arm.py); nothing of llmx_b200 is imported on this path."""
+    from baseline import reference_arm as arm
+    raw = dict(QWEN3_8B)
+    raw.update(SIZES[args.size])
+    if args.layers is not None:
+        raw["num_hidden_layers"] = args.layers
+    raw["torch_dtype"] = "bfloat16"
+    return arm.main(args, raw, args.size)
 
 
 def main() -> int:
@@ -129,7 +134,7 @@ def main() -> int:
                     help="run one part only (for profiling); the line then holds only that part")
     args = ap.parse_args()
     if args.impl == "reference":
-        return reference_arm()
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not built in this engine")
         return 2

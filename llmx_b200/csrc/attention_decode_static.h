@@ -27,14 +27,29 @@
 //
 // Arguments are those of llmx_attn_decode without the workspace and the device-side chunk
 // pointer, plus `total_rows`, the number of rows of q/out (the partial results are indexed by row).
+//   * `total_rows` is taken on trust.  The rows a request brings (row_start, row_count) lie in
+//     device memory, where this host-side check cannot read them: the size test above uses
+//     total_rows alone.  A caller that passes fewer rows than row_start + row_count reach makes
+//     the kernel write partial results past what was checked, possibly past the array.  Pass the
+//     true row count of q/out.
+//
+// The header is plain C as well as C++ (a C caller links against the same exported symbol).
 #pragma once
 #include <cuda_runtime.h>
 
 #define LLMX_ATTN_DECODE_STATIC_FLOATS (4 * 1024 * 1024)
 #define LLMX_ERR_TOO_LARGE 10004
 
-extern "C" int llmx_attn_decode_static(const void* cache_map, const void* q, void* out, const int* req_list, int n_req,
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int llmx_attn_decode_static(const void* cache_map, const void* q, void* out, const int* req_list, int n_req,
                                        const int* row_start, const int* row_count, const int* history,
                                        const int* block_tables, int table_stride, int total_rows, int heads,
                                        int kv_heads, int head_dim, int page_size, int window, float scale, int splits,
                                        int chunk_keys, int max_rows, int* error_word, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -2,7 +2,8 @@
 
 A and B differ in every size and option: layers, widths, head counts and group
 ratio, head width, vocabulary, rope base, eps, tying, context, page size, and B
-has YaRN rope scaling (a frequency blend and an attention factor).  C has widths
+has YaRN rope scaling (a frequency blend and an attention factor).  They are BASELINE.json's
+tiny A and tiny B with a longer context (and B's YaRN); BASELINE_A and BASELINE_B below are those to the letter.  C has widths
 the tensor-core path cannot take (an input width that is no multiple of 8), a
 head width of 48 and an odd vocabulary.
 """
@@ -33,4 +34,21 @@ TINY_D = dict(
     head_dim=64, vocab_size=320, rope_theta=500000.0, rms_norm_eps=1e-6, tie_word_embeddings=True,
     max_position_embeddings=2048)
 
-CONFIGS = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16), "D": (TINY_D, 3, 16)}   # config, seed, page size
+# E has a head ratio that divides neither 16 nor 128 (five query heads a kv head, as Qwen3-14B's 40 over 8) at the
+# head width of the tensor-core attention, so a decoding request fills a 16-row tile with three rows and a prompt
+# portion's row tile holds 25 tokens and three rows of padding.
+TINY_E = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=192, intermediate_size=264, num_attention_heads=10, num_key_value_heads=2,
+    head_dim=128, vocab_size=300, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+    max_position_embeddings=2048)
+
+CONFIGS = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16), "D": (TINY_D, 3, 16),
+           "E": (TINY_E, 4, 16)}   # config, seed, page size
+
+# BASELINE.json's tiny A and tiny B to the letter.  A and B above are these with a longer context (512 and 1,024
+# instead of 128 and 256 positions, so that prompts of 133 tokens fit the cuttings) and, for B, a YaRN rope scaling
+# BASELINE's B does not declare (so that the scaled rope is under every cutting too): more is tested, not less.
+# These two run BASELINE's own workloads (tests/test_generate_gpu.py).
+BASELINE_A = dict(TINY_A, max_position_embeddings=128)
+BASELINE_B = {k: v for k, v in dict(TINY_B, max_position_embeddings=256).items() if k != "rope_scaling"}

@@ -49,7 +49,7 @@ def _check(engine, folder, steps, requests, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 class TestCuttings:
     def test_whole(self, model_dirs, name, dtype):
         requests = _requests(name)
@@ -297,7 +297,7 @@ def test_layers_of_8b_width_under_cutting(wide_model_dir, dtype):
     """The stored weights are bfloat16, exact in both paths; the float32 path widens them."""
     from llmx_b200.engine import Engine, EngineOptions
     requests = {f"w{i}": helpers.random_ids(WIDE["vocab_size"], n, seed=40 + i) for i, n in enumerate([150, 70, 33, 2])}
-    for make in (helpers.trace_whole, helpers.trace_mixed):
+    for make in (helpers.trace_whole, helpers.trace_tail_decoded, helpers.trace_portions, helpers.trace_mixed):
         steps = make(requests)
         engine = Engine.from_dir(wide_model_dir, EngineOptions(dtype=dtype, kv_tokens=helpers.tokens_needed(steps),
                                                                page_size=16, max_requests=4))
@@ -437,3 +437,38 @@ def test_decode_sessions_replay_their_recordings(model_dirs, wide_model_dir, nam
     worst, scale, where = helpers.compare({k: v for k, v in got.items() if k[1] < len(requests_seen[k[0]])}, requests_seen,
                                           folder, dtype == "bfloat16")
     assert worst <= TOL[dtype] * scale, f"largest difference {worst:.3e} at {where} (logit scale {scale:.3f})"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_hugging_face_golden_of_odd_sizes(tmp_path, dtype):
+    """The engine at width 37, head width 42, vocabulary 257 (sizes that are multiples of nothing), tied and untied,
+    against logits Hugging Face's Qwen3 gave (tests/hf_anchor.py): float32 within the reference's own bound for this
+    comparison, whole and with the last tokens decoded one by one; bfloat16 against the plain implementation."""
+    import json
+    import torch
+    import hf_anchor
+    from llmx_b200.engine import Engine, EngineOptions, StepEntry
+    from llmx_b200.weights import write_safetensors
+    fixtures = hf_anchor.fixtures()
+    if fixtures is None:
+        pytest.skip("the golden file is not at hand")
+    for tied, cfg, w, cases in fixtures:
+        folder = tmp_path / f"hf_{tied}_{dtype}"
+        folder.mkdir()
+        store = torch.float32 if dtype == "float32" else torch.bfloat16
+        write_safetensors(str(folder / "model.safetensors"), {n: torch.from_numpy(a).to(store) for n, a in w.items()})
+        (folder / "config.json").write_text(json.dumps(cfg))
+        engine = Engine.from_dir(str(folder), EngineOptions(dtype=dtype, kv_tokens=64, page_size=4, max_requests=2))
+        for ids, want in cases:
+            whole = engine.step([StepEntry("w", ids, [len(ids) - 1])]).float().cpu().numpy()[0]
+            engine.end("w")
+            for t in ids:
+                last = engine.step([StepEntry("d", [t], [0])]).float().cpu().numpy()[0]
+            engine.end("d")
+            if dtype == "float32":
+                assert np.abs(whole - want).max() <= hf_anchor.BOUND and np.abs(last - want).max() <= hf_anchor.BOUND
+            else:
+                ref = helpers.reference_logits(str(folder), ids, True)[-1]
+                scale = float(np.abs(ref).max())
+                assert np.abs(whole - ref).max() <= TOL[dtype] * scale and np.abs(last - ref).max() <= TOL[dtype] * scale
+        engine.cache.check()

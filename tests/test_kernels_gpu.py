@@ -258,7 +258,8 @@ def test_attention_plain(dtype, heads, kv_heads, head_dim, page, layout, window)
     assert np.abs(out.float().cpu().numpy() - ref).max() <= tol * max(1.0, np.abs(ref).max())
 
 
-@pytest.mark.parametrize("heads,kv_heads,head_dim", [(32, 8, 128), (4, 4, 64), (16, 1, 128), (6, 2, 64), (8, 8, 128)])
+@pytest.mark.parametrize("heads,kv_heads,head_dim", [(32, 8, 128), (4, 4, 64), (16, 1, 128), (6, 2, 64), (8, 8, 128),
+                                                     (40, 8, 128), (6, 2, 128), (12, 2, 128), (10, 2, 64), (7, 1, 128)])
 @pytest.mark.parametrize("layout", ["decode", "prefill", "mixed"])
 @pytest.mark.parametrize("window", [None, 100])
 @pytest.mark.parametrize("spike", [False, True])

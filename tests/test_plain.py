@@ -37,6 +37,20 @@ def test_plain_matches_reference_cpu_code(tag, raw):
     assert np.abs(logits - g["steps"]).max() <= 2e-5
 
 
+def test_plain_matches_the_reference_s_hugging_face_golden():
+    """The second anchor, independent of the reference's own code: float32 logits Hugging Face's Qwen3 gave for a
+    model of odd sizes (width 37, head width 42, vocabulary 257), tied and untied (tests/hf_anchor.py)."""
+    import hf_anchor
+    fixtures = hf_anchor.fixtures()
+    if fixtures is None:
+        pytest.skip("the golden file is not at hand")
+    assert {tied for tied, *_ in fixtures} == {True, False}
+    for tied, cfg, w, cases in fixtures:
+        for ids, want in cases:
+            got = plain.forward(cfg, w, ids)
+            assert np.abs(got[-1] - want).max() <= hf_anchor.BOUND, (tied, len(ids))
+
+
 def test_rms_norm_and_rope_by_hand():
     x = np.array([[3.0, 4.0]], dtype=np.float32)
     w = np.array([2.0, 0.5], dtype=np.float32)

@@ -58,6 +58,7 @@ def test_static_entry_point_matches_the_ordinary_one_on_two_calls_in_a_row():
         longest = max(h + n for h, n in layout)
         splits = 4
         chunk = -(-(-(-longest // 64)) // splits) * 64
+        _req_list = torch.arange(step.requests, dtype=torch.int32, device=q.device)
         step.extras["decode_schedule"] = (splits, chunk, None)
         want = torch.full_like(q, float("nan"))
         ops_attn.paged_attention_bf16(q, cache, want, step, group, heads, kv_heads, head_dim, None, 1.0 / math.sqrt(head_dim))
@@ -65,6 +66,24 @@ def test_static_entry_point_matches_the_ordinary_one_on_two_calls_in_a_row():
         torch.cuda.synchronize()
         ops_tc.check_errors()
         assert status == 0
+        if call == 1:
+            # The set-up (the array's address) happened in the first call.  From here on a call must leave the
+            # device's free memory exactly as it found it: were the entry point to allocate, even through a
+            # pool, cudaMemGetInfo would show it.  Inputs and output exist already; only the call is repeated.
+            out_again = torch.empty_like(q)
+            torch.cuda.synchronize()
+            free_before, _ = torch.cuda.mem_get_info()
+            reserved_before = torch.cuda.memory_reserved()
+            status = fn(ctypes.c_void_p(ops_attn.cache_map(cache).address), q.data_ptr(), out_again.data_ptr(),
+                        _req_list.data_ptr(), step.requests, step.row_start.data_ptr(), step.row_count.data_ptr(),
+                        step.history.data_ptr(), group.block_tables.data_ptr(), group.block_tables.shape[1], q.shape[0],
+                        heads, kv_heads, head_dim, cache.shape[3], 0, 1.0 / math.sqrt(head_dim), splits, chunk,
+                        max(step.host_row_count), ops_tc.error_word(q.device).data_ptr(),
+                        torch.cuda.current_stream().cuda_stream)
+            torch.cuda.synchronize()
+            assert status == 0
+            assert torch.cuda.mem_get_info()[0] == free_before and torch.cuda.memory_reserved() == reserved_before
+            assert torch.equal(out_again, got)
         got_np, want_np = got.float().cpu().numpy(), want.float().cpu().numpy()
         assert np.isfinite(got_np).all()
         scale = max(1.0, np.abs(ref).max())
