@@ -94,21 +94,25 @@ attention_plain_kernel(const QT* __restrict__ q, const KVT* __restrict__ cache, 
 }
 }  // namespace
 
-LLMX_EXPORT int llmx_attention_plain(const void* q, const void* cache, void* out, int dtype, const int* row_request,
-                                     const int* positions, const int* block_tables, int table_stride, int rows,
-                                     int heads, int kv_heads, int head_dim, int page_size, int window, float scale,
-                                     cudaStream_t stream) {
+// q/out [rows, heads, head_dim] of `q_dtype`; the cache [pages, 2, kv_heads, page_size, head_dim] of `cache_dtype`
+// (the two may differ: bfloat16 products over a float32 cache, or the reverse).
+LLMX_EXPORT int llmx_attention_plain(const void* q, int q_dtype, const void* cache, int cache_dtype, void* out,
+                                     const int* row_request, const int* positions, const int* block_tables,
+                                     int table_stride, int rows, int heads, int kv_heads, int head_dim, int page_size,
+                                     int window, float scale, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (head_dim <= 0 || head_dim > 32 * MAX_PER_LANE || heads % kv_heads || heads > 65535) return LLMX_ERR_UNSUPPORTED;
     dim3 grid(rows, heads);
     const size_t shmem = (size_t)WARPS * (head_dim + 2) * sizeof(float);
-    if (dtype == LLMX_BF16)
-        launch_kernel(attention_plain_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(WARPS * 32), shmem, stream, 
-            (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, row_request, positions,
-            block_tables, table_stride, heads, kv_heads, head_dim, page_size, window, scale);
-    else
-        launch_kernel(attention_plain_kernel<float, float>, dim3(grid), dim3(WARPS * 32), shmem, stream, 
-            (const float*)q, (const float*)cache, (float*)out, row_request, positions, block_tables, table_stride,
-            heads, kv_heads, head_dim, page_size, window, scale);
+#define LLMX_PLAIN(QT, KVT)                                                                                            \
+    launch_kernel(attention_plain_kernel<QT, KVT>, dim3(grid), dim3(WARPS * 32), shmem, stream, (const QT*)q,         \
+                  (const KVT*)cache, (QT*)out, row_request, positions, block_tables, table_stride, heads, kv_heads,   \
+                  head_dim, page_size, window, scale)
+    if (q_dtype == LLMX_BF16 && cache_dtype == LLMX_BF16) LLMX_PLAIN(__nv_bfloat16, __nv_bfloat16);
+    else if (q_dtype == LLMX_BF16 && cache_dtype == LLMX_F32) LLMX_PLAIN(__nv_bfloat16, float);
+    else if (q_dtype == LLMX_F32 && cache_dtype == LLMX_BF16) LLMX_PLAIN(float, __nv_bfloat16);
+    else if (q_dtype == LLMX_F32 && cache_dtype == LLMX_F32) LLMX_PLAIN(float, float);
+    else return LLMX_ERR_UNSUPPORTED;
+#undef LLMX_PLAIN
     return launch_status();
 }

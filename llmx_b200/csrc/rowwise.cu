@@ -323,11 +323,11 @@ LLMX_EXPORT int llmx_head_norm_rope_kv(const float* qkv, int qkv_stride, int k_o
                                        int cache_dtype, int rows, int heads, int kv_heads, int head_dim,
                                        int page_size, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    if (head_dim <= 0 || rot_half < 0 || 2 * rot_half > head_dim || q_dtype != cache_dtype) return LLMX_ERR_BAD_ARGUMENT;
+    if (head_dim <= 0 || rot_half < 0 || 2 * rot_half > head_dim) return LLMX_ERR_BAD_ARGUMENT;
     const int warps = 4;
     const long long items = (long long)rows * (heads + kv_heads);
     const unsigned blocks = (unsigned)((items + warps - 1) / warps);
-    const bool fast = head_dim == 128 && (!cos_table || rot_half == 64) && qkv_stride % 4 == 0 && k_offset % 4 == 0 &&
+    const bool fast = q_dtype == cache_dtype && head_dim == 128 && (!cos_table || rot_half == 64) && qkv_stride % 4 == 0 && k_offset % 4 == 0 &&
                       v_offset % 4 == 0 && !((uintptr_t)qkv & 15) && !((uintptr_t)q_out & 15) && !((uintptr_t)cache & 15) &&
                       !((uintptr_t)q_weight & 15) && !((uintptr_t)k_weight & 15) && !((uintptr_t)cos_table & 15) &&
                       !((uintptr_t)sin_table & 15);
@@ -348,14 +348,17 @@ LLMX_EXPORT int llmx_head_norm_rope_kv(const float* qkv, int qkv_stride, int k_o
         return launch_status();
     }
     const size_t shmem = (size_t)warps * head_dim * sizeof(float);
-    if (q_dtype == LLMX_BF16)
-        launch_kernel(head_norm_rope_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(blocks), dim3(warps * 32), shmem, stream, 
-            qkv, qkv_stride, k_offset, v_offset, q_weight, k_weight, eps, cos_table, sin_table, rot_half, positions,
-            slots, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, rows, heads, kv_heads, head_dim, page_size);
-    else
-        launch_kernel(head_norm_rope_kernel<float, float>, dim3(blocks), dim3(warps * 32), shmem, stream, 
-            qkv, qkv_stride, k_offset, v_offset, q_weight, k_weight, eps, cos_table, sin_table, rot_half, positions,
-            slots, (float*)q_out, (float*)cache, rows, heads, kv_heads, head_dim, page_size);
+    // The general form takes queries and cache of different types (bfloat16 products over a float32 cache, or the reverse).
+#define LLMX_HNR_ANY(QT, KVT)                                                                                           \
+    launch_kernel(head_norm_rope_kernel<QT, KVT>, dim3(blocks), dim3(warps * 32), shmem, stream, qkv, qkv_stride,      \
+                  k_offset, v_offset, q_weight, k_weight, eps, cos_table, sin_table, rot_half, positions, slots,       \
+                  (QT*)q_out, (KVT*)cache, rows, heads, kv_heads, head_dim, page_size)
+    if (q_dtype == LLMX_BF16 && cache_dtype == LLMX_BF16) LLMX_HNR_ANY(__nv_bfloat16, __nv_bfloat16);
+    else if (q_dtype == LLMX_BF16 && cache_dtype == LLMX_F32) LLMX_HNR_ANY(__nv_bfloat16, float);
+    else if (q_dtype == LLMX_F32 && cache_dtype == LLMX_BF16) LLMX_HNR_ANY(float, __nv_bfloat16);
+    else if (q_dtype == LLMX_F32 && cache_dtype == LLMX_F32) LLMX_HNR_ANY(float, float);
+    else return LLMX_ERR_BAD_ARGUMENT;
+#undef LLMX_HNR_ANY
     return launch_status();
 }
 
