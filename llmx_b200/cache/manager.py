@@ -46,7 +46,12 @@ CacheSpec = Union[KVSpec, StateSpec, None]
 
 
 class StateSlots:
-    """Slot ids for fixed-size per-request state."""
+    """Slot ids for fixed-size per-request state.
+
+    A live request holds two: the one its state lies in and a spare.  A step reads the first and writes the
+    second (`RequestCache.state_slot` / `state_slot_out`), and commit swaps them, so a step that fails leaves
+    the state as it was without anything being copied (the reference keeps checkpoints of its state slots for
+    the same end, src/model/kv_cache.hpp:183-278)."""
 
     def __init__(self, num_slots: int):
         self.num_slots = int(num_slots)
@@ -99,7 +104,15 @@ class RequestCache:
         self.manager = manager
         self.request_id = request_id
         self.tables: List[BlockTable] = [BlockTable(g.pool, g.page_size, g.spec.window) for g in manager.groups]
-        self.state_slot: int = manager.state_slots.take() if manager.has_state else -1
+        self.state_slot: int = -1          # where the request's state lies (read by a step)
+        self.state_slot_out: int = -1      # where a step writes the state it leaves; the two swap at commit
+        if manager.has_state:
+            self.state_slot = manager.state_slots.take()
+            try:
+                self.state_slot_out = manager.state_slots.take()
+            except CacheExhausted:
+                manager.state_slots.give_back(self.state_slot)
+                raise
         self.length = 0
         self.pending = 0
         self.freed = False
@@ -120,13 +133,37 @@ class RequestCache:
     def commit(self) -> None:
         for t in self.tables:
             t.commit()
+        if self.pending:
+            self.state_slot, self.state_slot_out = self.state_slot_out, self.state_slot
         self.length += self.pending
         self.pending = 0
 
     def abort(self) -> None:
+        """Undo a prepare: pages taken for the step go back; the state the step may have written went to the
+        spare slot, so the request's state is what it was."""
         for t in self.tables:
             t.abort()
         self.pending = 0
+
+    def truncate(self, length: int) -> None:
+        """Roll the request back to `length` tokens (the reference's KVSequence::truncate,
+        src/model/kv_cache.hpp:126-130).  Keys beyond are forgotten and their pages given back.  A request with
+        fixed-size state cannot be rolled back (the state has no history), nor can a windowed group below what
+        its window has given back."""
+        if self.pending:
+            raise RuntimeError("KV cache: a step is in progress for this request")
+        if not 0 <= length <= self.length:
+            raise ValueError(f"cannot truncate a request of {self.length} tokens to {length}")
+        if length == self.length:
+            return
+        if self.state_slot >= 0:
+            raise RuntimeError("a request whose layers keep fixed-size state cannot be rolled back")
+        for t in self.tables:
+            if t.window is not None and length < t._first_live * t.page_size:
+                raise RuntimeError("KV cache: cannot roll back into pages the window has given back")
+        for t in self.tables:
+            t.truncate(length)
+        self.length = length
 
     def held_pages(self) -> List[int]:
         return [t.held_pages for t in self.tables]
@@ -136,9 +173,10 @@ class RequestCache:
             raise RuntimeError(f"request {self.request_id!r}: cache freed twice")
         for t in self.tables:
             t.free()
-        if self.state_slot >= 0:
-            self.manager.state_slots.give_back(self.state_slot)
-            self.state_slot = -1
+        for slot in (self.state_slot, self.state_slot_out):
+            if slot >= 0:
+                self.manager.state_slots.give_back(slot)
+        self.state_slot = self.state_slot_out = -1
         self.freed = True
         self.length = self.pending = 0
 
@@ -152,30 +190,36 @@ class CacheManager:
     """
 
     def __init__(self, entry_specs: Sequence[CacheSpec], page_size: int, kv_tokens: int,
-                 max_requests: int, kv_dtype=None, device=None):
+                 max_requests: int, kv_dtype=None, device=None, window_kv_tokens: Optional[int] = None):
+        """`kv_tokens`: tokens the pool of every group that keeps all keys is made for; `window_kv_tokens`: the
+        same for groups that keep a window (default: as many; a windowed group holds at most its window, two
+        pages and the step's portion per request, so it can be made much smaller)."""
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.page_size = int(page_size)
         self.entry_specs = list(entry_specs)
         self.kv_tokens = int(kv_tokens)
+        self.window_kv_tokens = self.kv_tokens if window_kv_tokens is None else int(window_kv_tokens)
         self.max_requests = int(max_requests)
-        num_pages = self.kv_tokens // self.page_size
         by_spec: Dict[KVSpec, List[int]] = {}
         for i, s in enumerate(self.entry_specs):
             if isinstance(s, KVSpec):
                 by_spec.setdefault(s, []).append(i)
-        self.groups: List[CacheGroup] = [CacheGroup(s, m, self.page_size, num_pages) for s, m in by_spec.items()]
+        self.groups: List[CacheGroup] = [
+            CacheGroup(s, m, self.page_size, (self.kv_tokens if s.window is None else self.window_kv_tokens) // self.page_size)
+            for s, m in by_spec.items()]
         self.group_of_entry: Dict[int, Tuple[int, int]] = {}
         for gi, g in enumerate(self.groups):
             for mi, e in enumerate(g.members):
                 self.group_of_entry[e] = (gi, mi)
         self.state_entries = [i for i, s in enumerate(self.entry_specs) if isinstance(s, StateSpec)]
         self.has_state = bool(self.state_entries)
-        self.state_slots = StateSlots(self.max_requests if self.has_state else 0)
+        self.state_slots = StateSlots(2 * self.max_requests if self.has_state else 0)
         self.state_storage: Dict[int, object] = {}
         self.live: Dict[Hashable, RequestCache] = {}
         self.kv_dtype = kv_dtype
         self.device = device
+        self.views = None                 # the entries as the native runtime sees them (runtime.CacheViews)
         if device is not None:
             self._allocate()
 
@@ -190,6 +234,19 @@ class CacheManager:
             s = self.entry_specs[e]
             self.state_storage[e] = torch.zeros((self.state_slots.num_slots,) + tuple(s.shape),
                                                 dtype=getattr(torch, s.dtype), device=self.device)
+        if torch.device(self.device).type == "cuda":
+            from .. import runtime
+            # The runtime's view of the entries owns the kernels' descriptors of the storage, so that they go when
+            # the cache goes.
+            self.views = runtime.CacheViews(len(self.entry_specs))
+            for e in range(len(self.entry_specs)):
+                gi, storage = self.entry_storage(e) if (e in self.group_of_entry or e in self.state_storage) else (None, None)
+                if storage is None:
+                    continue
+                if gi >= 0:
+                    self.views.set_kv(e, gi, storage)
+                else:
+                    self.views.set_state(e, storage)
 
     # -- requests -------------------------------------------------------------
     def new_request(self, request_id: Hashable) -> RequestCache:

@@ -42,6 +42,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "attention_prefill": ["attention_prefill.cu"],
     "attention_prefill_tc": ["attention_prefill_tc.cu"],
     "sampling": ["sampling.cu"],
+    "runtime": ["runtime/runtime.cpp"],       # host code: the parts' forward passes (no kernels of its own)
 }
 
 _lock = threading.Lock()
@@ -96,10 +97,13 @@ def _includes(path: str, seen: set) -> None:
         for line in fh:
             line = line.strip()
             if line.startswith("#include \""):
-                inc = os.path.join(_HERE, line.split('"')[1])
-                if inc not in seen and os.path.exists(inc):
-                    seen.add(inc)
-                    _includes(inc, seen)
+                for base in (os.path.dirname(path), _HERE):
+                    inc = os.path.normpath(os.path.join(base, line.split('"')[1]))
+                    if os.path.exists(inc):
+                        if inc not in seen:
+                            seen.add(inc)
+                            _includes(inc, seen)
+                        break
 
 
 def _digest(name: str) -> str:
@@ -130,7 +134,7 @@ def build(name: str, verbose: bool = True) -> str:
     nvcc = _nvcc()
     srcs = [os.path.join(_HERE, s) for s in LIBRARIES[name]]
     tmp = f"{out}.{os.getpid()}.tmp"
-    cmd = [nvcc] + NVCC_FLAGS + ["-I", _HERE, "-o", tmp] + srcs
+    cmd = [nvcc] + NVCC_FLAGS + ["-I", _HERE, "-o", tmp] + srcs + (["-ldl"] if name == "runtime" else [])
     if verbose:
         print(f"[llmx_b200] compiling {name} for sm_100a ...", file=sys.stderr, flush=True)
     t0 = time.time()

@@ -48,6 +48,9 @@ int llmx_rt_load_kernels(const char* folder);              // every llmx_*.so of
 const char* llmx_rt_last_error(void);
 long long llmx_rt_launches(void);                          // kernels launched through the runtime so far
 void llmx_rt_count_launches(long long n);                  // ... plus those a replayed recording launched
+// Entry point i (from 0) that the last dry runs (llmx_*_workspace) would have called and found unbound; 0 at the end.
+int llmx_rt_missing(int i, const char** name);
+void llmx_rt_reset_caches(void);                           // forget what was learnt of the device and the kernel libraries
 // Device time by kernel entry point: while on, every kernel call is bracketed by events on its stream.
 int llmx_rt_profile(int on);
 // After llmx_rt_profile(0): entry i of the calls made while it was on.  Returns 0 when i is out of range.
@@ -61,6 +64,8 @@ int llmx_heads_tile(int m, int heads, int kv_heads, int sms);
 // at once (s = 0..16; 0 where unknown or off).
 void llmx_decode_schedule(int n_requests, int kv_heads, int max_context, int head_dim, const int* clusters,
                           int* splits, int* chunk);
+// 0: only the plain attention kernel takes this shape; 1: split-KV decode and warp-level prefill; 2: and tcgen05 prefill.
+int llmx_tiled_attention(int heads, int kv_heads, int head_dim, int page_size);
 void llmx_prefill_shape(int n_requests, int kv_heads, int ratio, int max_rows, int max_context, int window, int sms,
                         int* tiles, int* splits);
 
@@ -80,7 +85,8 @@ int llmx_caches_set_state(llmx_caches*, int entry, void* storage, long long slot
 typedef struct llmx_step {
     int rows, requests, wanted, groups, position_streams, room;   // room > 0: a recorded step with room for that context
     const int* meta;                  // device
-    int token_ids, positions, row_request, row_start, row_count, history, state_slots, logit_rows;   // offsets
+    int token_ids, positions, row_request, row_start, row_count, history, state_slots, logit_rows, state_slots_out;   // offsets
+    //  (state_slots: where each request's fixed-size state lies; state_slots_out: where the step leaves it)
     int block_tables[LLMX_MAX_GROUPS], table_stride[LLMX_MAX_GROUPS], slots[LLMX_MAX_GROUPS], page_size[LLMX_MAX_GROUPS];
     int plan_offset;                  // where the plan's ints lie in `meta`
     const llmx_plan* plan;            // launch decisions for this shape (may be null when no part needs any)
@@ -100,13 +106,15 @@ typedef struct llmx_step {
 // shapes a launch is taken for a context of `room` tokens and `histories` may be null; `llmx_plan_fill` then
 // writes the values that follow the actual histories.  The plan's ints go into the step's metadata at
 // llmx_step.plan_offset.
-llmx_plan* llmx_plan_make(const llmx_model* model, const llmx_part* part, const int* counts, const int* histories,
-                          int requests, int room);     // of a whole model, or of one part (model null)
+llmx_plan* llmx_plan_make(const llmx_model* model, llmx_part* const* parts, int n_parts, const int* counts,
+                          const int* histories, int requests, int room);     // of a whole model and/or of single parts
 int llmx_plan_ints(const llmx_plan*);
 int llmx_plan_fill(llmx_plan*, const int* histories, int* out);
 void llmx_plan_free(llmx_plan*);
 // Forces the tcgen05 prefill attention's item shape (tests): row tiles an item (1, 2; 0 free), key ranges (0 free).
 void llmx_plan_force_prefill_shape(llmx_plan*, int tiles, int splits);
+// Forces the split-KV decode kernel's key ranges and keys per range (a multiple of 64) (tests).
+void llmx_plan_force_decode(llmx_plan*, int splits, int chunk);
 // What the plan decided for the first attention shape: out[0..7] = small requests, large requests, splits, chunk,
 // prefill tiles, prefill splits, rows of the largest small request, rows of the largest large one.
 int llmx_plan_describe(const llmx_plan*, int* out);
@@ -169,8 +177,21 @@ int llmx_linear_gated(llmx_part*, const llmx_step*, const void* a, int rows, voi
 // norm in front of it clears them in passing.  The buffer itself is the caller's.
 long long llmx_part_wants_cleared(llmx_part*, const llmx_step*, int rows);
 int llmx_linear_adds_pieces(llmx_part*, int rows);
-// Workspace bytes one call of the part's forward needs at most for this step.
-size_t llmx_part_workspace(llmx_part*, const llmx_step*, int rows);
+// Workspace bytes one call of the part's forward (on this cache entry, where it has one) needs for this step.  The
+// walk also notes the kernels it would call and that are not bound (llmx_rt_missing).
+size_t llmx_part_workspace(llmx_part*, const llmx_step*, int rows, int cache_entry);
+
+// The attention kernels alone, as a mixer runs them once its queries are made: out = attention of the step's rows
+// (q/out [rows, heads * head_dim] of q_dtype) over cache entry `entry`.
+llmx_part* llmx_attention_shape(int heads, int kv_heads, int head_dim, int window);   // a mixer's shape alone, for plans
+int llmx_paged_attention(const llmx_step*, const void* q, int q_dtype, int entry, void* out, int heads, int kv_heads,
+                         int head_dim, int window, float scale);
+size_t llmx_paged_attention_workspace(const llmx_step*, int entry, int heads, int kv_heads, int head_dim, int window);
+// The decode kernel taking the q/k/v product's float32 output as it is (steps of decoding rows only).  0: ran;
+// -1: the step or the shapes do not qualify and nothing was done.
+int llmx_decode_from_qkv(const llmx_step*, const float* qkv, int entry, const float* q_weight, const float* k_weight,
+                         float eps, const float* cos, const float* sin, int rot_half, void* out, int heads, int kv_heads,
+                         int head_dim, int window, float scale);
 
 // ---- the model ------------------------------------------------------------------------------------------------
 typedef struct llmx_layer_step { int block, cache_entry, write_cache; } llmx_layer_step;   // cache_entry < 0: none

@@ -84,6 +84,13 @@ bool bind(const char* name, void* fn) {
 
 long long g_launches = 0;
 bool g_profile = false;
+// Entry points a dry run would have called and found unbound: the caller binds them before the real run.
+std::vector<const char*> g_missing;
+void note_missing(const char* name) {
+    for (const char* m : g_missing)
+        if (!strcmp(m, name)) return;
+    g_missing.push_back(name);
+}
 struct Timed { const char* name; cudaEvent_t a, b; };
 std::vector<Timed> g_timed;
 struct TimedResult { const char* name; float ms, idle; };
@@ -119,7 +126,10 @@ struct Ctx {
 // Calls a kernel entry point: counted, timed when profiling is on, skipped on a dry run.
 template <typename F, typename... A>
 int call(Ctx& c, const char* name, F fn, int launches, A... args) {
-    if (c.dry) return 0;
+    if (c.dry) {
+        if (!fn) note_missing(name);
+        return 0;
+    }
     if (c.status) return c.status;
     if (!fn) return c.status = fail(LLMX_RT_ERR_UNBOUND, std::string("kernel ") + name + " is not bound (its library was not loaded)");
     Timed t{name, nullptr, nullptr};
@@ -241,8 +251,9 @@ int b200_clusters(int size) {
     }
 }
 
+std::map<std::pair<int, int>, int> g_cluster_cache;
 int max_clusters(int head_dim, int size) {
-    static std::map<std::pair<int, int>, int> cache;
+    auto& cache = g_cluster_cache;
     auto it = cache.find({head_dim, size});
     if (it != cache.end()) return it->second;
     int n = -1;
@@ -408,7 +419,11 @@ struct Linear : llmx_part {
         return (long long)rows * N;
     }
     int ensure_map(Ctx& c) {
-        if (have_map || c.dry) return 0;
+        if (have_map) return 0;
+        if (c.dry) {
+            if (!kern.llmx_gemm_tc_weight_map) note_missing("llmx_gemm_tc_weight_map");
+            return 0;
+        }
         if (!kern.llmx_gemm_tc_weight_map) return c.status = fail(LLMX_RT_ERR_UNBOUND, "kernel llmx_gemm_tc_weight_map is not bound");
         const int e = kern.llmx_gemm_tc_weight_map(map128, w, N, K);
         if (e) return c.status = fail(e, "gemm_tc weight map could not be made");
@@ -443,7 +458,11 @@ struct Linear : llmx_part {
     }
     int ensure_head_map(Ctx& c, int tile) {
         const int i = tile == 256;
-        if (have_head_map[i] || c.dry) return 0;
+        if (have_head_map[i]) return 0;
+        if (c.dry) {
+            if (!kern.llmx_gemm_tc_weight_map_box) note_missing("llmx_gemm_tc_weight_map_box");
+            return 0;
+        }
         if (!kern.llmx_gemm_tc_weight_map_box) return c.status = fail(LLMX_RT_ERR_UNBOUND, "kernel llmx_gemm_tc_weight_map_box is not bound");
         const int e = kern.llmx_gemm_tc_weight_map_box(head_map[i], w, N, K, tile);
         if (e) return c.status = fail(e, "gemm_tc weight map could not be made");
@@ -525,7 +544,11 @@ struct Attention : Mixer {
     }
 
     int ensure_maps(Ctx& c, const CacheEntry& e, bool half) {
-        if (c.dry) return 0;
+        if (c.dry) {
+            if (!half && !kern.llmx_attn_cache_map) note_missing("llmx_attn_cache_map");
+            if (half && !kern.llmx_attn_prefill_tc_cache_map) note_missing("llmx_attn_prefill_tc_cache_map");
+            return 0;
+        }
         if (!half && !e.have_map) {
             if (!kern.llmx_attn_cache_map) return c.status = fail(LLMX_RT_ERR_UNBOUND, "kernel llmx_attn_cache_map is not bound");
             if (int err = kern.llmx_attn_cache_map(e.map, e.storage, e.pages, e.kv_heads, e.page_size, e.head_dim))
@@ -613,19 +636,8 @@ struct Attention : Mixer {
         float* qkv_out = cleared;
         if (!qkv_out) qkv_out = c.alloc_n<float>((size_t)rows * qkv.N);
         qkv.forward(c, h, rows, qkv_out, false, cleared != nullptr);
-        // A step of decoding rows only: the attention kernel norms and rotates its own queries, and the block whose key
-        // range holds a new row stores that key and value (head width 128, rotated whole or not at all).
-        const bool from_qkv = decoding_only && tiled(e) && d.head_dim == 128 && (!d.cos || d.rot_half == 64) &&
-                              p->n_small * d.kv_heads <= LLMX_COUNTERS && s.counters;
-        if (from_qkv) {
-            if (ensure_maps(c, e, false)) return c.status;
-            const int* list = c.meta(s.plan_offset + p->offset);
-            float* partial = p->splits > 1 ? c.alloc_n<float>((size_t)rows * d.heads * p->splits * (d.head_dim + 2)) : nullptr;
-            CALL(c, llmx_attn_decode_qkv, 1, (const void*)e.map, (const float*)qkv_out, qkv.N, q_width, q_width + kv_width, d.q_norm,
-                 d.k_norm, d.qk_norm_eps, d.cos, d.sin, slots, (void*)e.storage, o_buf, partial, list, p->n_small, c.meta(s.row_start),
-                 c.meta(s.row_count), c.meta(s.history), c.meta(s.block_tables[g]), s.table_stride[g], d.heads, d.kv_heads,
-                 d.head_dim, e.page_size, d.window, d.scale, p->splits, p->chunk_on_device ? list + p->order.size() : nullptr,
-                 p->chunk_on_device ? 64 : p->chunk, std::max(p->rows_small, 1), s.counters, s.error_word, c.stream);
+        if (!from_qkv(c, qkv_out, e, o_buf, rows, slots, g)) {
+            if (c.status) return c.status;
         } else {
             void* q = c.alloc((size_t)rows * q_width * elem(act));
             CALL(c, llmx_head_norm_rope_kv, 1, (const float*)qkv_out, qkv.N, q_width, q_width + kv_width, d.q_norm, d.k_norm,
@@ -634,6 +646,27 @@ struct Attention : Mixer {
             attend(c, q, e, o_buf, rows, g);
         }
         return o.forward(c, o_buf, rows, residual, true, false);
+    }
+
+    // A step of decoding rows only: the attention kernel norms and rotates its own queries, and the block whose key
+    // range holds a new row stores that key and value (head width 128, rotated whole or not at all).  False, having
+    // done nothing, when the step or the shapes do not qualify.
+    bool from_qkv(Ctx& c, const float* qkv_out, const CacheEntry& e, void* o_buf, int rows, const int* slots, int g) {
+        const llmx_step& s = *c.s;
+        const AttnPlan* p = plan_of(c);
+        const bool decoding_only = p && p->n_small > 0 && p->n_large == 0;
+        if (!(decoding_only && tiled(e) && d.head_dim == 128 && (!d.cos || d.rot_half == 64) &&
+              p->n_small * d.kv_heads <= LLMX_COUNTERS && s.counters))
+            return false;
+        if (ensure_maps(c, e, false)) return false;
+        const int* list = c.meta(s.plan_offset + p->offset);
+        float* partial = p->splits > 1 ? c.alloc_n<float>((size_t)rows * d.heads * p->splits * (d.head_dim + 2)) : nullptr;
+        CALL(c, llmx_attn_decode_qkv, 1, (const void*)e.map, qkv_out, qkv.N, q_width, q_width + kv_width, d.q_norm,
+             d.k_norm, d.qk_norm_eps, d.cos, d.sin, slots, (void*)e.storage, o_buf, partial, list, p->n_small, c.meta(s.row_start),
+             c.meta(s.row_count), c.meta(s.history), c.meta(s.block_tables[g]), s.table_stride[g], d.heads, d.kv_heads,
+             d.head_dim, e.page_size, d.window, d.scale, p->splits, p->chunk_on_device ? list + p->order.size() : nullptr,
+             p->chunk_on_device ? 64 : p->chunk, std::max(p->rows_small, 1), s.counters, s.error_word, c.stream);
+        return true;
     }
 };
 
@@ -799,6 +832,17 @@ LLMX_API int llmx_rt_load_kernels(const char* folder) {
     return bound;
 }
 
+LLMX_API int llmx_rt_missing(int i, const char** name) {
+    if (i < 0 || i >= (int)g_missing.size()) return 0;
+    *name = g_missing[i];
+    return 1;
+}
+// What the runtime remembers about the device and the kernel libraries (the clusters that fit, chosen schedules).
+LLMX_API void llmx_rt_reset_caches(void) {
+    g_missing.clear();
+    g_cluster_cache.clear();
+}
+
 LLMX_API int llmx_rt_profile(int on) {
     const bool before = g_profile;
     if (on && !g_profile) {
@@ -837,6 +881,10 @@ LLMX_API int llmx_rt_profile_read(int i, const char** name, float* ms, float* id
 LLMX_API void llmx_gemm_plan(int m, int n, int k, int accumulate, int n_sms, int* schedule, int* token_tile, int* splits) {
     const GemmPlan p = n_sms > 0 ? gemm_plan_compute(m, n, k, accumulate != 0, n_sms) : gemm_plan(m, n, k, accumulate != 0);
     *schedule = p.schedule, *token_tile = p.token_tile, *splits = p.splits;
+}
+LLMX_API int llmx_tiled_attention(int heads, int kv_heads, int head_dim, int page_size) {
+    if (kv_heads <= 0 || heads <= 0 || !tiled_attention_supported(heads, kv_heads, head_dim, page_size)) return 0;
+    return tensor_core_prefill(heads, kv_heads, head_dim, page_size) ? 2 : 1;
 }
 LLMX_API int llmx_heads_tile(int m, int heads, int kv_heads, int n_sms) { return heads_tile_compute(m, heads, kv_heads, n_sms > 0 ? n_sms : sms()); }
 LLMX_API void llmx_decode_schedule(int n_requests, int kv_heads, int max_context, int head_dim, const int* clusters, int* splits, int* chunk) {
@@ -905,8 +953,8 @@ void plan_attention(llmx_plan& plan, AttnPlan& a, const int* histories) {
 }
 }  // namespace
 
-LLMX_API llmx_plan* llmx_plan_make(const llmx_model* model, const llmx_part* part, const int* counts, const int* histories, int requests,
-                                   int room) {
+LLMX_API llmx_plan* llmx_plan_make(const llmx_model* model, llmx_part* const* parts, int n_parts, const int* counts, const int* histories,
+                                   int requests, int room) {
     if (requests <= 0 || !counts || (!histories && room <= 0)) {
         fail(LLMX_RT_ERR_BAD_ARGUMENT, "llmx_plan_make: the rows each request brings, and histories or room");
         return nullptr;
@@ -914,7 +962,8 @@ LLMX_API llmx_plan* llmx_plan_make(const llmx_model* model, const llmx_part* par
     std::vector<AttnKey> keys;
     if (model)
         for (const Block* b : model->blocks) b->collect(keys);
-    if (part) part->collect(keys);
+    for (int i = 0; i < n_parts; ++i)
+        if (parts && parts[i]) parts[i]->collect(keys);
     llmx_plan* plan = new llmx_plan;
     plan->requests = requests, plan->room = room;
     plan->counts.assign(counts, counts + requests);
@@ -939,6 +988,10 @@ LLMX_API void llmx_plan_force_prefill_shape(llmx_plan* p, int tiles, int splits)
         if (tiles) a.tiles = tiles;
         if (splits) a.psplits = splits;
     }
+}
+LLMX_API void llmx_plan_force_decode(llmx_plan* p, int splits, int chunk) {
+    if (!p || splits < 1 || chunk < 64 || chunk % 64) return;
+    for (AttnPlan& a : p->attn) a.splits = splits, a.chunk = chunk;
 }
 LLMX_API int llmx_plan_fill(llmx_plan* p, const int* histories, int* out) {
     if (!p) return 0;
@@ -1113,14 +1166,71 @@ LLMX_API int llmx_linear_adds_pieces(llmx_part* p, int rows) {
     Linear* l = as<Linear>(p, PART_LINEAR);
     return l && l->adds_pieces(rows) ? 1 : 0;
 }
-LLMX_API size_t llmx_part_workspace(llmx_part* p, const llmx_step* s, int rows) {
+LLMX_API size_t llmx_part_workspace(llmx_part* p, const llmx_step* s, int rows, int cache_entry) {
     if (!p || !good_step(s)) return 0;
     Ctx c(s, true);
-    if (Mixer* m = as<Mixer>(p, PART_MIXER)) m->forward(c, nullptr, rows, 0, nullptr, true, nullptr);
+    if (Mixer* m = as<Mixer>(p, PART_MIXER)) m->forward(c, nullptr, rows, cache_entry, nullptr, true, nullptr);
     else if (FeedForward* f = as<FeedForward>(p, PART_FFN)) f->forward(c, nullptr, rows, nullptr, nullptr);
-    else if (Block* b = as<Block>(p, PART_BLOCK)) b->forward(c, nullptr, rows, 0, true);
+    else if (Block* b = as<Block>(p, PART_BLOCK)) b->forward(c, nullptr, rows, cache_entry, true);
     else if (Head* h = as<Head>(p, PART_HEAD)) h->forward(c, nullptr, nullptr);
     return c.peak + 256;
+}
+
+// ---- the attention dispatch alone (what a mixer runs once its queries are made) ----
+namespace {
+Attention bare_attention(int q_dtype, int heads, int kv_heads, int head_dim, int window, float scale) {
+    llmx_attention_desc d = {};
+    d.heads = heads, d.kv_heads = kv_heads, d.head_dim = head_dim, d.window = window, d.scale = scale;
+    d.qkv.dtype = d.o.dtype = q_dtype;
+    d.qkv.out_features = (heads + 2 * kv_heads) * head_dim;
+    return Attention(d);
+}
+const CacheEntry* kv_entry(const llmx_step* s, int entry, int kv_heads, int head_dim) {
+    if (!good_step(s) || !s->caches || entry < 0 || entry >= (int)s->caches->entries.size()) return nullptr;
+    const CacheEntry& e = s->caches->entries[entry];
+    return e.kind == 1 && e.kv_heads == kv_heads && e.head_dim == head_dim ? &e : nullptr;
+}
+}  // namespace
+// An attention shape without weights: good for launch plans (llmx_plan_make) of callers that run the attention
+// kernels on queries of their own.
+LLMX_API llmx_part* llmx_attention_shape(int heads, int kv_heads, int head_dim, int window) {
+    if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || head_dim <= 0 || window < 0) {
+        fail(LLMX_RT_ERR_BAD_ARGUMENT, "llmx_attention_shape: head counts, a head width and a window");
+        return nullptr;
+    }
+    return new Attention(bare_attention(LLMX_DT_BF16, heads, kv_heads, head_dim, window, 1.0f));
+}
+// out = attention of the step's rows over cache entry `entry`; q/out [rows, heads * head_dim] of `q_dtype`.
+LLMX_API int llmx_paged_attention(const llmx_step* s, const void* q, int q_dtype, int entry, void* out, int heads, int kv_heads, int head_dim,
+                                  int window, float scale) {
+    const CacheEntry* e = kv_entry(s, entry, kv_heads, head_dim);
+    if (!e || heads <= 0 || heads % kv_heads) return fail(LLMX_RT_ERR_BAD_ARGUMENT, "llmx_paged_attention: the entry and the head counts do not fit");
+    Attention a = bare_attention(q_dtype, heads, kv_heads, head_dim, window, scale);
+    Ctx c(s, false);
+    a.attend(c, q, *e, out, s->rows, e->group);
+    return c.status;
+}
+LLMX_API size_t llmx_paged_attention_workspace(const llmx_step* s, int entry, int heads, int kv_heads, int head_dim, int window) {
+    const CacheEntry* e = kv_entry(s, entry, kv_heads, head_dim);
+    if (!e) return 0;
+    Attention a = bare_attention(LLMX_DT_BF16, heads, kv_heads, head_dim, window, 1.0f);
+    Ctx c(s, true);
+    a.attend(c, nullptr, *e, nullptr, s->rows, e->group);
+    a.from_qkv(c, nullptr, *e, nullptr, s->rows, nullptr, e->group);
+    return c.peak + 256;
+}
+// The decode kernel taking the q/k/v product's float32 output [rows, (heads + 2 kv_heads) * head_dim] as it is.
+// Returns 0 when it ran, -1 when the step or the shapes do not qualify (nothing was done), else an error code.
+LLMX_API int llmx_decode_from_qkv(const llmx_step* s, const float* qkv, int entry, const float* q_weight, const float* k_weight, float eps,
+                                  const float* cos, const float* sin, int rot_half, void* out, int heads, int kv_heads, int head_dim, int window,
+                                  float scale) {
+    const CacheEntry* e = kv_entry(s, entry, kv_heads, head_dim);
+    if (!e || heads <= 0 || heads % kv_heads) return fail(LLMX_RT_ERR_BAD_ARGUMENT, "llmx_decode_from_qkv: the entry and the head counts do not fit");
+    Attention a = bare_attention(LLMX_DT_BF16, heads, kv_heads, head_dim, window, scale);
+    a.d.q_norm = q_weight, a.d.k_norm = k_weight, a.d.qk_norm_eps = eps, a.d.cos = cos, a.d.sin = sin, a.d.rot_half = rot_half;
+    Ctx c(s, false);
+    const bool ran = a.from_qkv(c, qkv, *e, out, s->rows, c.meta(s->slots[e->group]), e->group);
+    return c.status ? c.status : ran ? 0 : -1;
 }
 
 // ---- the model ----

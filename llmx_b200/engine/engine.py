@@ -23,9 +23,11 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..cache.pages import CacheExhausted, RELEASED
-from ..parts.base import GroupView, Precision, StepBatch
+from ..parts.base import Precision, StepBatch, StepShape
 from ..registry import architecture_of, config_from_dir
 from ..weights.safetensors import TensorDirectory
+from . import batch as batching
+from .batch import StepLayout
 
 
 class StepError(ValueError):
@@ -38,13 +40,24 @@ class StepEntry:
     request_id: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    positions: Optional[Sequence[Sequence[int]]] = None   # the tokens' positions in the streams beyond the first
+    #                                                       (one list a stream; for position encodings with several
+    #                                                       axes; the first stream is always the place in the request)
 
 
 @dataclass
 class EngineOptions:
     dtype: str = "bfloat16"
+    kv_dtype: Optional[str] = None   # the cache's element type, "bfloat16" or "float32" (default: the path's).  The
+    #                                  reference's cache types are its own options too (ModelOptions.kv_k / kv_v,
+    #                                  src/model/runtime.hpp:80-84): bfloat16 products over a float32 cache separate the
+    #                                  products' rounding from the cache's; a cache the tiled kernels do not take
+    #                                  (anything but bfloat16) runs the plain attention kernel
     kv_tokens: int = 8192            # tokens the cache pool is made for
+    window_kv_tokens: Optional[int] = None   # ... the pools of layer groups that keep only a window (default: as many)
     page_size: int = 16
+    invariant: bool = False          # kernels and schedules chosen by sizes alone, never by the batch (parts.base.Precision)
+    seed: int = 0                    # of the random weights `from_config` makes when it is given none
     max_requests: int = 64           # live requests (state slots; block-table rows)
     device: str = "cuda:0"
     record_after: int = 16           # plain steps of one shape before `step(..., record=True)` records it: making
@@ -64,10 +77,6 @@ def _scaled(config, options: "EngineOptions"):
     return config.with_yarn(options.yarn, options.yarn_original_ctx)
 
 
-def _pad4(n: int) -> int:
-    return (n + 3) & ~3
-
-
 ROOM_STEP = 2048           # a recording's room for context is a multiple of this
 
 
@@ -75,35 +84,6 @@ def room_for(context: int, max_positions: int) -> int:
     """Tokens of context a recorded step at `context` tokens has room for: at least one `ROOM_STEP`
     ahead, so that recordings change rarely."""
     return min((context // ROOM_STEP + 2) * ROOM_STEP, max(max_positions, 1))
-
-
-class StepLayout:
-    """Where a step's metadata lies in its one int32 buffer (sections padded to 16 bytes):
-    0 token ids [rows], 1 positions [rows], 2 request of each row [rows], 3 first row [requests],
-    4 row count [requests], 5 history [requests], 6 state slots [requests], 7 rows whose logits are wanted,
-    then for every cache group its block tables [requests, max_pages] and the rows' cache slots [rows],
-    then `extra` ints (a recorded step keeps the keys per range of the split-KV kernel there)."""
-
-    def __init__(self, counts: Sequence[int], wanted: int, max_pages: Sequence[int], extra: int = 0):
-        self.counts = [int(c) for c in counts]
-        self.requests, self.rows, self.wanted = len(self.counts), sum(self.counts), wanted
-        self.max_pages = list(max_pages)
-        self.starts = [0] * self.requests
-        for r in range(1, self.requests):
-            self.starts[r] = self.starts[r - 1] + self.counts[r - 1]
-        self.sizes = [self.rows, self.rows, self.rows, self.requests, self.requests, self.requests, self.requests, wanted]
-        for mp in self.max_pages:
-            self.sizes += [self.requests * mp, self.rows]
-        if extra:
-            self.sizes.append(extra)
-        self.offsets, at = [], 0
-        for size in self.sizes:
-            self.offsets.append(at)
-            at += _pad4(max(size, 1))
-        self.total = at
-
-    def section(self, buf, i: int):
-        return buf[self.offsets[i]:self.offsets[i] + self.sizes[i]]
 
 
 class Engine:
@@ -114,13 +94,19 @@ class Engine:
         self.model = model
         self.options = options
         self.device = torch.device(options.device)
-        self.precision = Precision.of(options.dtype)
+        self.precision = Precision.of(options.dtype, options.invariant)
         if model.precision is None or model.precision.act is not self.precision.act:
             raise ValueError("the model was not loaded in the engine's dtype")
         self.max_positions = model.max_positions
-        self.cache = CacheManager(model.cache_entry_specs(), options.page_size, options.kv_tokens,
-                                  options.max_requests, kv_dtype=self.precision.act, device=self.device)
-        model.prepare(min(self.max_positions, max(options.kv_tokens, 1)), self.device)
+        kv_dtype = Precision.of(options.kv_dtype).act if options.kv_dtype else self.precision.act
+        specs = model.cache_entry_specs()
+        self.cache = CacheManager(specs, options.page_size, options.kv_tokens, options.max_requests, kv_dtype=kv_dtype,
+                                  device=self.device, window_kv_tokens=options.window_kv_tokens)
+        # Position tables reach as far as a request can: the pool's size where every request's keys all lie in it,
+        # the model's context where some group keeps a window only, or nothing but fixed-size state.
+        bounded = bool(self.cache.groups) and any(g.spec.window is None for g in self.cache.groups)
+        model.prepare(min(self.max_positions, max(options.kv_tokens, 1)) if bounded else self.max_positions, self.device)
+        self.position_streams = model.position_streams
         self.steps_run = 0
         # Recorded decode steps by (requests, room for context), least recently used first, and the batch
         # sizes whose kernels a plain step has already run (see decode_loop.py).
@@ -142,20 +128,21 @@ class Engine:
         model = entry.build(config)
         source = TensorDirectory(model_dir)
         with torch.cuda.device(torch.device(options.device)):
-            model.load(source, torch.device(options.device), Precision.of(options.dtype), where=model_dir)
+            model.load(source, torch.device(options.device), Precision.of(options.dtype, options.invariant), where=model_dir)
         source.close()
         return cls(model, options)
 
     @classmethod
-    def from_config(cls, config, seed: int, options: Optional[EngineOptions] = None) -> "Engine":
-        """A model of `config` with random weights made on the device (no files)."""
+    def from_config(cls, config, seed: Optional[int] = None, options: Optional[EngineOptions] = None) -> "Engine":
+        """A model of `config` with random weights made on the device (no files); `seed` defaults to the options'."""
         from ..weights.random_init import RandomSource
         options = options or EngineOptions()
+        seed = options.seed if seed is None else seed
         config = _scaled(config, options)
         entry = architecture_of(config.to_dict())
         model = entry.build(config)
         src = RandomSource(model.tensor_specs(), seed, dtype=torch.bfloat16, device=options.device, skip_optional=True)
-        model.load(src, torch.device(options.device), Precision.of(options.dtype), where="random weights")
+        model.load(src, torch.device(options.device), Precision.of(options.dtype, options.invariant), where="random weights")
         return cls(model, options)
 
     # -- requests ------------------------------------------------------------------
@@ -167,6 +154,16 @@ class Engine:
         """The request is finished: what it holds is given back."""
         if request_id in self.cache.live:
             self.cache.free_request(request_id)
+
+    def truncate(self, request_id: Hashable, length: int) -> None:
+        """Roll a live request back to its first `length` tokens: the keys beyond are forgotten and their pages
+        given back, and the next step continues from there (the reference's KVSequence::truncate,
+        src/model/kv_cache.hpp:126-130, which its runtime uses to rewind a prompt whose later chunk failed,
+        src/model/runtime.hpp:1347-1353).  Refused for a model with fixed-size state and below what a window gave back."""
+        rc = self.cache.live.get(request_id)
+        if rc is None:
+            raise StepError(f"request {request_id!r} is not live")
+        rc.truncate(int(length))
 
     # -- the step ------------------------------------------------------------------
     def _validate(self, entries: Sequence[StepEntry]) -> None:
@@ -188,73 +185,50 @@ class Engine:
             for w in e.want:
                 if not 0 <= int(w) < n:
                     raise StepError(f"request {e.request_id!r}: wanted place {w} is not among its {n} tokens")
+            if e.positions is not None and (len(e.positions) != self.position_streams - 1 or any(len(p) != n for p in e.positions)):
+                raise StepError(f"request {e.request_id!r}: positions must be {self.position_streams - 1} lists of {n} "
+                                "(one for every position stream of the model beyond the first)")
         new = sum(1 for e in entries if e.request_id not in self.cache.live)
         if len(self.cache.live) + new > self.options.max_requests:
             raise StepError(f"more than {self.options.max_requests} live requests")
 
-    def _fill_batch(self, buf: np.ndarray, layout: StepLayout, entries: Sequence[StepEntry], caches) -> List[int]:
+    def fill_batch(self, buf: np.ndarray, layout: StepLayout, entries: Sequence[StepEntry], caches) -> List[int]:
         """Write the step's metadata into `buf` (int32, `layout.total` values); returns the histories."""
         history = [rc.length for rc in caches]
-        buf[:] = 0
-        tok, pos, rreq = layout.section(buf, 0), layout.section(buf, 1), layout.section(buf, 2)
-        for r, e in enumerate(entries):
-            a, n = layout.starts[r], layout.counts[r]
-            tok[a:a + n] = np.asarray(e.tokens, dtype=np.int64)
-            pos[a:a + n] = np.arange(history[r], history[r] + n)
-            rreq[a:a + n] = r
-        layout.section(buf, 3)[:] = layout.starts
-        layout.section(buf, 4)[:] = layout.counts
-        layout.section(buf, 5)[:] = history
-        layout.section(buf, 6)[:] = [rc.state_slot for rc in caches]
-        lr, k = layout.section(buf, 7), 0
-        for r, e in enumerate(entries):
-            for w in e.want:
-                lr[k] = layout.starts[r] + int(w)
-                k += 1
-        for g, grp in enumerate(self.cache.groups):
-            ps = grp.page_size
-            bt = layout.section(buf, 8 + 2 * g).reshape(layout.requests, layout.max_pages[g])
-            sl = layout.section(buf, 9 + 2 * g)
-            for r, rc in enumerate(caches):
-                pages = rc.tables[g].pages
-                bt[r, :len(pages)] = pages
-                parr = np.asarray(pages, dtype=np.int64)
-                p = np.arange(history[r], history[r] + layout.counts[r])
-                a = layout.starts[r]
-                sl[a:a + layout.counts[r]] = parr[p // ps] * ps + p % ps
-            # A released page (-1) is never addressed: the window keeps queries above it.
+        pages = [[rc.tables[g].pages for rc in caches] for g in range(len(self.cache.groups))]
+        more = [e.positions for e in entries] if self.position_streams > 1 else None
+        batching.fill(buf, layout, [e.tokens for e in entries], history, [rc.state_slot for rc in caches],
+                      [e.want for e in entries], pages, [g.page_size for g in self.cache.groups], more,
+                      [rc.state_slot_out for rc in caches])
         return history
 
-    def _batch_views(self, dev: torch.Tensor, layout: StepLayout, caches, history: Sequence[int],
-                     max_context: int) -> StepBatch:
+    def batch_views(self, dev: torch.Tensor, layout: StepLayout, caches, history: Sequence[int], max_context: int,
+                    plan=None, room: int = 0) -> StepBatch:
         """The StepBatch whose device tensors are the sections of `dev`."""
-        n_req = layout.requests
-        groups = [GroupView(layout.section(dev, 8 + 2 * g).view(n_req, layout.max_pages[g]), layout.section(dev, 9 + 2 * g),
-                            grp.page_size) for g, grp in enumerate(self.cache.groups)]
-        return StepBatch(rows=layout.rows, requests=n_req, token_ids=layout.section(dev, 0),
-                         positions=layout.section(dev, 1), row_request=layout.section(dev, 2),
-                         row_start=layout.section(dev, 3), row_count=layout.section(dev, 4),
-                         history=layout.section(dev, 5), state_slots=layout.section(dev, 6),
-                         logit_rows=layout.section(dev, 7), groups=groups, caches=self.cache,
-                         host_row_start=list(layout.starts), host_row_count=list(layout.counts),
-                         host_history=list(history), host_state_slots=[rc.state_slot for rc in caches],
-                         max_row_count=max(layout.counts), max_context=max_context)
+        return batching.views(dev, layout, self.cache, [g.page_size for g in self.cache.groups], history,
+                              [rc.state_slot for rc in caches], max_context, plan, room,
+                              [rc.state_slot_out for rc in caches])
 
     def _build_batch(self, entries: Sequence[StepEntry], caches) -> StepBatch:
         counts = [len(e.tokens) for e in entries]
+        history = [rc.length for rc in caches]
         n_groups = len(self.cache.groups)
         max_pages = [max(1, max(len(rc.tables[g].pages) for rc in caches)) for g in range(n_groups)]
-        layout = StepLayout(counts, sum(len(e.want) for e in entries), max_pages)
+        # What the model's parts decide from the shape before anything is launched; their ints ride in the same buffer.
+        plan = self.model.plan_step(StepShape(counts, history, [tuple(e.want) for e in entries]))
+        layout = StepLayout(counts, sum(len(e.want) for e in entries), max_pages, self.position_streams, plan.ints)
         # One int32 buffer for the whole step, one host-to-device copy.
         host = torch.empty(layout.total, dtype=torch.int32, pin_memory=True)
-        history = self._fill_batch(host.numpy(), layout, entries, caches)
+        buf = host.numpy()
+        self.fill_batch(buf, layout, entries, caches)
+        plan.fill(history, layout.plan(buf))
         dev = host.to(self.device, non_blocking=True)
         self.last_h2d_bytes = host.numel() * 4
-        return self._batch_views(dev, layout, caches, history, max(h + c for h, c in zip(history, counts)))
+        return self.batch_views(dev, layout, caches, history, max(h + c for h, c in zip(history, counts)), plan)
 
     def _recording_for(self, entries: Sequence[StepEntry], caches):
         """The recording of this step's shape, made now if the shape has been seen often enough; else None."""
-        from . import recorded_step
+        from . import recording as recorded_step
         counts = tuple(len(e.tokens) for e in entries)
         wants = tuple(tuple(int(w) for w in e.want) for e in entries)
         context = max(rc.length + n for rc, n in zip(caches, counts))
@@ -269,7 +243,7 @@ class Engine:
                 self._shapes_seen.clear()
             self._shapes_seen[key] = seen + 1
             return None
-        rec = recorded_step.StepRecording(self, counts, wants, key[2])
+        rec = recorded_step.Recording(self, counts, wants, key[2])
         self.step_recordings[key] = rec
         self._shapes_seen.pop(key, None)
         while len(self.step_recordings) > recorded_step.MAX_STEP_RECORDINGS:
@@ -304,6 +278,8 @@ class Engine:
                 recording = self._recording_for(entries, caches) if record and self.model.recordable else None
                 if recording is not None:
                     logits = recording.run(self, entries, caches)
+                    from .. import runtime
+                    runtime.count_launches(recording.graph_launches)
                 else:
                     batch = self._build_batch(entries, caches)
                     logits = self.model.forward(batch)

@@ -14,11 +14,14 @@ gives the tensor names.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Callable, Dict, Iterable, List, Optional, Sequence, Set
+import ctypes
+from typing import Callable, Dict, Iterable, List, Optional, Sequence, Set, Tuple
 
+import numpy as np
 import torch
 
-from ..parts.base import Part, Precision, StepBatch
+from .. import runtime
+from ..parts.base import NativeHandle, Part, PartPlan, Precision, StepBatch, StepShape
 from ..parts.embedding import LogitsHead, TokenEmbedding
 from ..weights.loader import check_tensors, stored
 from ..weights.spec import TensorSpec
@@ -29,6 +32,49 @@ class LayerStep:
     block: int                          # index into Model.blocks
     cache_entry: Optional[int] = None   # index of the cache entry the mixer uses (None: the mixer has no cache)
     write_cache: bool = True            # False: read the entry another step wrote
+
+
+class ModelPlan:
+    """The launch plans of a model's parts for one step shape, laid out one after the other in the step's
+    metadata: first the native runtime's (all native parts share one), then those of parts written in Python."""
+
+    def __init__(self, native: Optional[PartPlan], python: List[Tuple[Part, PartPlan]]):
+        self.native = native
+        self.python = python
+        self.offsets: Dict[int, int] = {}
+        at = native.ints if native is not None else 0
+        for part, plan in python:
+            self.offsets[id(part)] = at
+            at += (plan.ints + 3) & ~3
+        self.ints = at
+        self.base = 0                     # where the plan's ints begin in the step's metadata (set by the engine)
+        self.device: Optional[torch.Tensor] = None
+
+    def fill(self, histories: Sequence[int], out: np.ndarray) -> None:
+        if self.native is not None:
+            self.native.fill(histories, out[:self.native.ints])
+        for part, plan in self.python:
+            at = self.offsets[id(part)]
+            plan.fill(histories, out[at:at + plan.ints])
+
+    def device_ints(self, part: Part) -> Optional[torch.Tensor]:
+        for p, plan in self.python:
+            if p is part:
+                at = self.offsets[id(part)]
+                return self.device[at:at + plan.ints]
+        return None
+
+    def plan_of(self, part: Part) -> Optional[PartPlan]:
+        for p, plan in self.python:
+            if p is part:
+                return plan
+        return None
+
+    def native_plan(self, part=None) -> Tuple[Optional[int], int]:
+        """(the runtime's plan handle, where its ints begin in the metadata)."""
+        if self.native is None:
+            return None, 0
+        return self.native.plan.handle, self.base
 
 
 class Model:
@@ -47,6 +93,8 @@ class Model:
         self.ignorable: Set[str] = set(ignorable)
         self.eos_ids = tuple(eos_ids)
         self.precision: Optional[Precision] = None
+        self._native: Optional[NativeHandle] = None
+        self._native_tried = False
         self._check_order()
 
     def _check_order(self) -> None:
@@ -119,6 +167,7 @@ class Model:
                 part.load_all(fetch, prefix, precision)
         self.head.bind_tied()
         self.precision = precision
+        self._native, self._native_tried = None, False
 
     def prepare(self, max_positions: int, device) -> None:
         for _, part in self._parts():
@@ -129,12 +178,79 @@ class Model:
         """Whether a decode step of this model can be recorded and replayed (every part only enqueues work)."""
         return all(part.all_recordable() for _, part in self._parts())
 
+    @property
+    def position_streams(self) -> int:
+        """How many position streams a step must carry for this model's parts."""
+        return max((p.position_streams for _, part in self._parts() for p in part.all_parts()), default=1)
+
+    # -- the native twin ---------------------------------------------------------
+    @property
+    def native(self) -> Optional[int]:
+        """The model's handle in the native runtime when every part has one (else None: the layer order is walked
+        from Python, each part running its own forward, native or not)."""
+        if not self._native_tried:
+            self._native_tried = True
+            blocks = [b.native for b in self.blocks]
+            emb, head = self.embedding.native, self.head.native
+            if emb and head and all(blocks):
+                arr = (ctypes.c_void_p * len(blocks))(*blocks)
+                order = (runtime.LayerStepStruct * len(self.order))(*[
+                    runtime.LayerStepStruct(s.block, -1 if s.cache_entry is None else s.cache_entry, 1 if s.write_cache else 0)
+                    for s in self.order])
+                handle = runtime.lib().llmx_model_create(emb, arr, len(blocks), order, len(self.order), head,
+                                                        self.embedding.hidden, self.vocab_size)
+                self._native = _ModelHandle(handle, keep=(self.embedding, self.blocks, self.head))
+        return self._native.handle if self._native is not None else None
+
+    # -- launch plans ------------------------------------------------------------
+    def plan_step(self, shape: StepShape) -> ModelPlan:
+        """What the model's parts decide on the host for steps of this shape (see parts/base.py)."""
+        from ..parts.attention import NativePlan
+        native = None
+        if self.native is not None:
+            native = NativePlan(self.native, (), shape)
+        else:
+            handles = [p.native for _, part in self._parts() for p in part.all_parts() if getattr(p, "native_planned", False)]
+            if handles:
+                native = NativePlan(None, handles, shape)
+        if native is not None and native.ints == 0:
+            native = None
+        python = []
+        if self.native is None:
+            seen = set()
+            for _, part in self._parts():
+                for p in part.all_parts():
+                    if id(p) in seen or getattr(p, "native_planned", False):
+                        continue
+                    seen.add(id(p))
+                    plan = p.plan_step(shape)
+                    if plan is not None and plan.ints:
+                        python.append((p, plan))
+        return ModelPlan(native, python)
+
     # -- one step ------------------------------------------------------------------
     def forward(self, step: StepBatch) -> Optional[torch.Tensor]:
         """Run the step's rows through every layer; logits [wanted, vocab] float32, or None if none is wanted."""
+        wanted = step.logit_rows.numel()
+        if self.native is not None:
+            rt = runtime.lib()
+            probe = step.struct_for(self)
+            need = rt.llmx_model_workspace(self.native, ctypes.byref(probe))
+            runtime.bind_missing()
+            s = step.struct_for(self, need)
+            logits = torch.empty((wanted, self.vocab_size), dtype=torch.float32, device=step.token_ids.device) if wanted else None
+            runtime.check(rt.llmx_model_forward(self.native, ctypes.byref(s), runtime.ptr(logits)), "forward")
+            return logits
         x = self.embedding.forward(step.token_ids)
         for s in self.order:
             self.blocks[s.block].forward(x, step, s.cache_entry, s.write_cache)
-        if step.logit_rows.numel() == 0:
+        if wanted == 0:
             return None
         return self.head.forward(x, step.logit_rows)
+
+
+class _ModelHandle(NativeHandle):
+    def __del__(self):
+        h, self.handle = getattr(self, "handle", None), None
+        if h and runtime._lib is not None:
+            runtime._lib.llmx_model_destroy(h)

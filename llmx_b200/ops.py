@@ -1,6 +1,8 @@
-"""Python faces of the CUDA kernels.
+"""Python faces of single CUDA kernels.
 
-Every function here launches hand-written sm_100a kernels from `csrc/` on the
+The model's forward pass calls the kernels from the native runtime (llmx_b200/runtime.py, csrc/runtime/); the
+functions here call one kernel each, for tests that hold a kernel to its plain reference and for parts written
+in Python.  Every function launches hand-written sm_100a kernels from `csrc/` on the
 current CUDA stream and returns at once.  Arguments are torch tensors on one
 CUDA device; shapes, types and contiguity are checked here, on the host, before
 a launch, so that a kernel is never handed memory it would read out of bounds.
@@ -20,8 +22,7 @@ F32, BF16 = 0, 1
 _CODE = {torch.float32: F32, torch.bfloat16: BF16}
 
 
-class KernelError(RuntimeError):
-    """A kernel refused its arguments or its launch failed."""
+from .runtime import KernelError      # noqa: E402  (one error type for kernels and runtime)
 
 
 def _code(t: torch.Tensor) -> int:
@@ -66,8 +67,10 @@ _launches = 0
 
 
 def launch_count() -> int:
-    """Kernels of this package launched so far (each call of an exported function counts its launches)."""
-    return _launches
+    """Kernels of this package launched so far: by the native runtime (the model's forward pass, replayed
+    recordings included) and by the single-kernel functions of this module."""
+    from . import runtime
+    return _launches + runtime.launches()
 
 
 def count_launches(n: int) -> None:
@@ -92,7 +95,7 @@ _SIGNATURES = {
                                             _i, _i, _i, _i, _i, _p],
     ("rowwise", "llmx_swiglu"): [_p, _p, _i, _i, _i, _p],
     ("gemm_plain", "llmx_gemm_plain"): [_p, _i, _p, _i, _p, _i, _i, _i, _i, _p],
-    ("attention_plain", "llmx_attention_plain"): [_p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _p],
+    ("attention_plain", "llmx_attention_plain"): [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _p],
 }
 _fns = {}
 
@@ -123,28 +126,38 @@ def _fn(lib: str, name: str):
 
 class kernel_times:
     """Device time of every kernel call made inside the `with` block, by exported function (the reference's
-    `bench --profile`, src/cli/main.cpp:1326-1352): CUDA events around each call on the current stream.  For plain
+    `bench --profile`, src/cli/main.cpp:1326-1352): CUDA events around each call on its stream, in the native
+    runtime (the model's forward pass) and in this module's single-kernel functions.  For plain
     steps only: a step that replays a recording makes no calls, and events must not be recorded into one.
     The events keep a kernel from starting while the one before drains, so the times are those of kernels alone."""
 
     def __enter__(self) -> "kernel_times":
         global _timed_calls
+        from . import runtime
         if _timed_calls is not None:
             raise KernelError("kernel_times is already open")
         _timed_calls = []
+        runtime.profile(True)
         return self
 
     def __exit__(self, *exc) -> None:
         global _timed_calls
+        from . import runtime
         calls, _timed_calls = _timed_calls, None
+        runtime.profile(False)                   # synchronises
         torch.cuda.synchronize()
-        self.calls = len(calls)
+        native = runtime.profile_results()
+        self.calls = len(calls) + len(native)
         self.by_function = {}
         for name, start, end in calls:
             n, ms = self.by_function.get(name, (0, 0.0))
             self.by_function[name] = (n + 1, ms + start.elapsed_time(end))
+        for name, ms_one, _ in native:
+            n, ms = self.by_function.get(name, (0, 0.0))
+            self.by_function[name] = (n + 1, ms + ms_one)
         self.total_ms = sum(ms for _, ms in self.by_function.values())
-        self.idle_ms = sum(max(0.0, calls[i][2].elapsed_time(calls[i + 1][1])) for i in range(len(calls) - 1))
+        self.idle_ms = sum(max(0.0, calls[i][2].elapsed_time(calls[i + 1][1])) for i in range(len(calls) - 1)) \
+            + sum(idle for _, _, idle in native)
 
     def lines(self, what: str):
         """The report, most expensive first."""
@@ -212,7 +225,6 @@ def head_norm_rope_kv(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: in
     _need(tuple(q_out.shape) == (rows, q_w), "head_norm_rope_kv: q_out shape does not fit")
     _need(cache.dim() == 5 and cache.shape[1] == 2 and cache.shape[2] == kv_heads and cache.shape[4] == head_dim,
           "head_norm_rope_kv: cache layout does not fit")
-    _need(q_out.dtype == cache.dtype, "head_norm_rope_kv: queries and cache must have one element type")
     _need(positions.dtype == torch.int32 and slots.dtype == torch.int32 and positions.numel() >= rows
           and slots.numel() >= rows, "head_norm_rope_kv: positions and slots must be int32 per row")
     rot_half = 0
@@ -254,11 +266,12 @@ def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: 
 def attention_plain(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, row_request: torch.Tensor,
                     positions: torch.Tensor, block_tables: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
                     window: Optional[int], scale: float) -> torch.Tensor:
-    """Paged attention, one block per (row, head); q/out [rows, heads * head_dim] of the cache's element type."""
+    """Paged attention, one block per (row, head); q/out [rows, heads * head_dim] of one element type, the cache of
+    its own (float32 or bfloat16 each)."""
     _cuda(q, cache, out, row_request, positions, block_tables)
     rows = q.shape[0]
     _need(q.shape == out.shape and q.shape[1] == heads * head_dim, "attention: q and out shapes do not fit")
-    _need(q.dtype == cache.dtype == out.dtype, "attention: q, cache and out must have one element type")
+    _need(q.dtype == out.dtype, "attention: q and out must have one element type")
     _need(cache.dim() == 5 and cache.shape[1] == 2 and cache.shape[2] == kv_heads and cache.shape[4] == head_dim,
           "attention: cache layout does not fit")
     for t in (row_request, positions, block_tables):
@@ -266,7 +279,7 @@ def attention_plain(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, row
     _need(block_tables.dim() == 2 and row_request.numel() >= rows and positions.numel() >= rows,
           "attention: metadata shapes do not fit")
     _check(_fn("attention_plain", "llmx_attention_plain")(
-        _ptr(q), _ptr(cache), _ptr(out), _code(q), _ptr(row_request), _ptr(positions), _ptr(block_tables),
+        _ptr(q), _code(q), _ptr(cache), _code(cache), _ptr(out), _ptr(row_request), _ptr(positions), _ptr(block_tables),
         block_tables.shape[1], rows, heads, kv_heads, head_dim, cache.shape[3], int(window or 0), float(scale),
         _stream()), "attention_plain")
     return out

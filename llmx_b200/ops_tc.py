@@ -18,28 +18,7 @@ register_signature("gemm_tc", "llmx_gemm_tc_weight_map_box", [_p, _p, _i, _i, _i
 register_signature("gemm_tc", "llmx_gemm_tc_heads", [_p, _p, _i, _i, _i, _p, _p, ctypes.c_float, _p, _p, _p, _p, _p, _p,
                                                      _i, _i, _i, _p, _p])
 
-_error_words: Dict[int, torch.Tensor] = {}
-_ERROR_NAMES = {101: "the TMA producer waited for a free stage", 102: "the MMA issuer waited for a loaded stage",
-                103: "the MMA issuer waited for a free accumulator", 104: "the epilogue waited for an accumulator"}
-
-
-def error_word(device) -> torch.Tensor:
-    """The device int a kernel of this module records a failed wait in (one per device)."""
-    idx = torch.device(device).index or 0
-    w = _error_words.get(idx)
-    if w is None:
-        w = torch.zeros(1, dtype=torch.int32, device=device)
-        _error_words[idx] = w
-    return w
-
-
-def check_errors() -> None:
-    """Raise if any tensor-core kernel gave up a wait (synchronises the devices that ran one)."""
-    for idx, w in _error_words.items():
-        code = int(w.item())
-        if code:
-            w.zero_()
-            raise KernelError(f"tensor-core kernel on device {idx} gave up: {_ERROR_NAMES.get(code, code)}")
+from .runtime import check_errors, error_word      # noqa: F401,E402  (the devices' shared error word lives with the runtime)
 
 
 class WeightMap:
@@ -78,12 +57,6 @@ def weight_map(weight: torch.Tensor) -> WeightMap:
 
 
 STREAM_K_MAX_ROWS = 64          # at most this many tokens: few tiles, so (tile, k block) units are shared out evenly
-STREAM_K_MAX_TILES = 4 * 148    # ... unless the weight alone makes plenty of tiles (the logits head)
-
-
-def _schedule(m: int, n: int) -> int:
-    return 1 if m <= STREAM_K_MAX_ROWS and -(-n // 128) < STREAM_K_MAX_TILES else 0
-
 
 _sm_count = 0
 
@@ -95,44 +68,12 @@ def _sms() -> int:
     return _sm_count
 
 
-@functools.lru_cache(maxsize=None)
 def _plan(m: int, n: int, k: int, accumulate: bool, sms: int) -> Tuple[int, int, int]:
-    """(schedule, token tile, k ranges) for out[m, n] (+)= a[m, k] w[n, k]^T.
-
-    Few tokens: stream-K.  Else whole tiles, and the token tile and the number of k ranges are chosen so
-    that the tiles fill the SMs: with a few hundred tokens a [4096, 4096] weight makes 32 to 128 tiles,
-    which would leave most of the 148 SMs idle, while two to four k ranges (added with atomics) fill them.
-    The estimate below was fitted to timings of the layer's products at 96 to 2,048 tokens: a tile's time
-    is its bytes over what one SM takes in (110 GB/s) or its multiply-adds at the SM's share of the
-    tensor rate; atomics run beside the main loop at 500 G a second and show at the end of a block's
-    last tile; a stored output that is added to in pieces must be cleared first.
-    """
-    if _schedule(m, n) == 1:
-        return 1, 0, 1
-    if m <= STREAM_K_MAX_ROWS:
-        return 0, 0, 1              # few tokens, plenty of weight tiles (the logits head): the narrowest token tile
-    n_tiles, k_blocks = -(-n // 128), -(-k // 64)
-    best = None
-    for bn in (128, 256):
-        if bn == 256 and m <= 128:
-            continue
-        m_tiles = -(-m // bn)
-        for splits in (1, 2, 3, 4):
-            if splits > k_blocks:
-                break
-            tiles = n_tiles * m_tiles * splits
-            waves = -(-tiles // sms)
-            kk = -(-k_blocks // splits) * 64
-            per_tile = max(kk * (128 + bn) * 2 / 110e3, 2.0 * 128 * bn * kk / 9.4e6)
-            t = waves * per_tile
-            if splits > 1:
-                t = max(t, m * n * splits / 500e3) + min(bn, m) * 128 / 8e3
-                if not accumulate:
-                    t += m * n * 4 / 5e6
-            t *= 1.0 + 0.03 * (splits - 1)
-            if best is None or t < best[0]:
-                best = (t, bn, splits)
-    return 0, best[1], best[2]
+    """(schedule, token tile, k ranges) for out[m, n] (+)= a[m, k] w[n, k]^T on a device of `sms` SMs: stream-K for few
+    tokens, else whole tiles whose token tile and number of k ranges fill the SMs.  The decision is the native
+    runtime's (`gemm_plan_compute` in csrc/runtime/runtime.cpp), which the model's forward pass uses."""
+    from . import runtime
+    return runtime.gemm_plan(m, n, k, bool(accumulate), sms)
 
 
 def plan(m: int, n: int, k: int, accumulate: bool) -> Tuple[int, int, int]:
@@ -166,7 +107,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
     if schedule is None and splits is None and token_tile == 0:
         schedule, token_tile, splits = plan(m, n, k, accumulate)
     if schedule is None:
-        schedule = _schedule(m, n) if splits is None else 0
+        schedule = (1 if plan(m, n, k, accumulate)[0] == 1 else 0) if splits is None else 0
     if splits is None:
         splits = 1
     if (schedule == 1 or splits > 1) and not accumulate:
@@ -194,22 +135,13 @@ def gemm_tc_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, wmap: Op
     return out
 
 
-HEADS_MIN_ROWS = 256        # from this many tokens on the q/k/v product finishes its heads itself
-
-
 def heads_tile(m: int, heads: int, kv_heads: int) -> int:
     """Weight rows per tile (128: one head, 256: two) of the q/k/v product that finishes its heads in the
-    epilogue, or 0 when the tokens are few: the plain product then fills the SMs by cutting k, and its float32
-    output goes through the per-head kernel.  Of the two tiles the one whose waves over the SMs take less time (a
-    two-head tile takes about 1.55 times a one-head tile).  Timed at 32 heads over 8, width 4,096 (us, product +
-    per-head kernel -> this): 256 tokens 27 -> 21, 512: 38 -> 32, 1,024: 63 -> 52, 2,048: 100 -> 88,
-    8,192: 497 -> 342."""
-    if m < HEADS_MIN_ROWS:
-        return 0
-    token_tiles, width, sms = -(-m // 128), heads + 2 * kv_heads, _sms()
-    one = -(-token_tiles * width // sms)
-    two = -(-token_tiles * -(-width // 2) // sms)
-    return 128 if one * 1.0 <= two * 1.55 else 256
+    epilogue, or 0 when the tokens are few (the runtime's decision, `heads_tile_compute`).  Timed at 32 heads over
+    8, width 4,096 (us, product + per-head kernel -> this): 256 tokens 27 -> 21, 512: 38 -> 32, 1,024: 63 -> 52,
+    2,048: 100 -> 88, 8,192: 497 -> 342."""
+    from . import runtime
+    return runtime.heads_tile(m, heads, kv_heads, _sm_count or 0)
 
 
 def gemm_tc_heads(a: torch.Tensor, wmap: WeightMap, heads: int, kv_heads: int, q_weight: Optional[torch.Tensor],

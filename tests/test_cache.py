@@ -112,7 +112,7 @@ def test_groups_by_need_and_all_or_nothing_prepare():
         m.new_request("a")
     m.free_request("a")
     m.free_request("b")
-    assert m.used_pages() == [0, 0] and m.state_slots.free_slots == 3
+    assert m.used_pages() == [0, 0] and m.state_slots.free_slots == 6      # two a request: its state and a spare
     m.check()
     assert m.pages_needed(100, step_tokens=4) == [25, 5]
 
@@ -159,5 +159,50 @@ def test_random_orders_of_requests_lose_no_page(seed):
     for rid in list(live):
         m.free_request(rid)
     m.check()
-    assert m.used_pages() == [0, 0] and m.state_slots.free_slots == 5
+    assert m.used_pages() == [0, 0] and m.state_slots.free_slots == 10
     assert reused, "the run never used a page again; it did not test reuse"
+
+
+def test_state_is_part_of_the_transaction_and_requests_roll_back():
+    """A step reads a request's state slot and writes its spare; commit swaps them, abort does not, so a failed
+    step leaves the state where it was.  A request without state can be rolled back to a shorter history."""
+    from llmx_b200.cache.manager import CacheManager, KVSpec, StateSpec
+    m = CacheManager([KVSpec(1, 8), StateSpec((4,))], page_size=4, kv_tokens=64, max_requests=2)
+    a = m.new_request("a")
+    first, spare = a.state_slot, a.state_slot_out
+    assert first != spare and min(first, spare) >= 0 and m.state_slots.free_slots == 2
+    a.prepare(5)
+    a.abort()
+    assert (a.state_slot, a.state_slot_out) == (first, spare) and a.length == 0
+    a.prepare(5)
+    a.commit()
+    assert (a.state_slot, a.state_slot_out) == (spare, first) and a.length == 5
+    with pytest.raises(RuntimeError, match="fixed-size state"):
+        a.truncate(2)
+    a.truncate(5)                                   # to where it is: nothing to do
+    m.free_request("a")
+    assert m.state_slots.free_slots == 4
+    m.check()
+
+    k = CacheManager([KVSpec(1, 8), KVSpec(1, 8, window=6)], page_size=4, kv_tokens=64, max_requests=2, window_kv_tokens=32)
+    assert k.total_pages() == [16, 8]               # the windowed group's pool is its own size
+    b = k.new_request("b")
+    b.prepare(10)
+    b.commit()
+    used = k.used_pages()
+    b.prepare(9)
+    b.commit()
+    assert b.length == 19
+    with pytest.raises(RuntimeError, match="window has given back"):
+        b.truncate(3)
+    b.truncate(17)
+    assert b.length == 17 and [t.length for t in b.tables] == [17, 17]
+    k.check()
+    with pytest.raises(ValueError):
+        b.truncate(18)
+    b.prepare(2)
+    b.commit()
+    assert b.length == 19
+    k.free_request("b")
+    assert k.used_pages() == [0, 0] and used != [0, 0]
+    k.check()

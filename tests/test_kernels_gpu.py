@@ -186,7 +186,6 @@ def _attention_case(dtype, heads, kv_heads, head_dim, page, layout, window, seed
     Returns everything the kernels need plus the plain result.  With `spike`, one far key of every
     request is made to stand out (its score dominates), so a kernel that drops or misplaces a page
     shows a large error instead of one that random values average away."""
-    from llmx_b200.parts.base import GroupView, StepBatch
     g = torch.Generator().manual_seed(seed)
     n_req = len(layout)
     lens = [h + n for h, n in layout]
@@ -223,17 +222,10 @@ def _attention_case(dtype, heads, kv_heads, head_dim, page, layout, window, seed
         kk = ks[r].to(dtype).float().numpy()
         vv = vs[r].to(dtype).float().numpy()
         ref[row_start[r]:row_start[r] + n] = plain.attention(full_q, kk, vv, window=window)[h:]
-    positions = np.concatenate([np.arange(h, h + n) for h, n in layout]).astype(np.int32)
-    row_request = np.concatenate([np.full(n, r) for r, (h, n) in enumerate(layout)]).astype(np.int32)
-
-    def dev(a):
-        return torch.as_tensor(np.asarray(a, dtype=np.int32)).to(DEV)
-    group = GroupView(dev(tables), dev(np.zeros(rows)), page)
-    step = StepBatch(rows=rows, requests=n_req, token_ids=dev(np.zeros(rows)), positions=dev(positions),
-                     row_request=dev(row_request), row_start=dev(row_start), row_count=dev([n for _, n in layout]),
-                     history=dev([h for h, _ in layout]), state_slots=dev([-1] * n_req), logit_rows=dev([]),
-                     groups=[group], caches=None, host_row_start=row_start, host_row_count=[n for _, n in layout],
-                     host_history=[h for h, _ in layout], max_row_count=max(n for _, n in layout), max_context=max(lens))
+    # The step (metadata on the device, launch plan of an attention of this shape) as the engine would make it.
+    from llmx_b200 import ops_attn
+    step = ops_attn.attention_step(DEV, layout, tables, heads, kv_heads, head_dim, window, page)
+    group = step.groups[0]
     return q_all.reshape(rows, heads * head_dim).to(DEV).contiguous(), cache.to(DEV), step, group, ref.reshape(rows, -1)
 
 
@@ -288,7 +280,7 @@ def test_attention_prefill_items_of_any_shape(item_tiles, key_splits, heads, kv_
     from llmx_b200 import ops_attn, ops_tc
     layout = [(0, 300), (77, 130), (1500, 64), (3, 33), (40, 1), (700, 200)]
     q, cache, step, group, ref = _attention_case(torch.bfloat16, heads, kv_heads, 128, 16, layout, window, seed=23, spike=True)
-    step.extras["attn_prefill_shape"] = (item_tiles, key_splits)
+    step.plan.native.plan.force_prefill_shape(item_tiles, key_splits)
     out = torch.full_like(q, float("nan"))
     ops_attn.paged_attention_bf16(q, cache, out, step, group, heads, kv_heads, 128, window, 1.0 / math.sqrt(128))
     torch.cuda.synchronize()
@@ -324,7 +316,6 @@ def test_attention_over_long_histories(window):
     decoding rows, hundreds of key stages for a prompt portion.  One key near the start of every request (or of
     its window) is made to stand out for the last row, so a page that is dropped or misplaced anywhere shows."""
     from llmx_b200 import ops_attn, ops_tc
-    from llmx_b200.parts.base import GroupView, StepBatch
     heads, kv_heads, D, page = 32, 8, 128, 16
     layout = [(20000, 1), (9001, 3), (12345, 70), (33, 1)]
     g = torch.Generator().manual_seed(31)
@@ -366,16 +357,8 @@ def test_attention_over_long_histories(window):
     ref = torch.cat(refs).reshape(rows, -1).numpy()
     q_all = torch.cat(qs).reshape(rows, heads * D).to(DEV).contiguous()
 
-    def dev(a):
-        return torch.as_tensor(np.asarray(a, dtype=np.int32)).to(DEV)
-    positions = np.concatenate([np.arange(h, h + n) for h, n in layout])
-    row_request = np.concatenate([np.full(n, r) for r, (h, n) in enumerate(layout)])
-    group = GroupView(dev(tables), dev(np.zeros(rows)), page)
-    step = StepBatch(rows=rows, requests=len(layout), token_ids=dev(np.zeros(rows)), positions=dev(positions),
-                     row_request=dev(row_request), row_start=dev(row_start), row_count=dev([n for _, n in layout]),
-                     history=dev([h for h, _ in layout]), state_slots=dev([-1] * len(layout)), logit_rows=dev([]),
-                     groups=[group], caches=None, host_row_start=row_start, host_row_count=[n for _, n in layout],
-                     host_history=[h for h, _ in layout], max_row_count=max(n for _, n in layout), max_context=max(lens))
+    step = ops_attn.attention_step(DEV, layout, tables, heads, kv_heads, D, window, page)
+    group = step.groups[0]
     out = torch.full_like(q_all, float("nan"))
     ops_attn.paged_attention_bf16(q_all, cache.to(DEV), out, step, group, heads, kv_heads, D, window, 1.0 / math.sqrt(D))
     torch.cuda.synchronize()
@@ -404,7 +387,7 @@ def _decode_with_key_ranges(splits):
     layout = [(1500, 1), (63, 1), (64, 1), (700, 2), (0, 1)]
     q, cache, step, group, ref = _attention_case(torch.bfloat16, heads, kv_heads, head_dim, 16, layout, None, seed=10, spike=True)
     chunk = -(-(-(-1501 // 64)) // splits) * 64
-    step.extras["decode_schedule"] = (splits, chunk, None)
+    step.plan.native.plan.force_decode(splits, chunk)
     out = torch.full_like(q, float("nan"))
     ops_attn.paged_attention_bf16(q, cache, out, step, group, heads, kv_heads, head_dim, None, 1.0 / math.sqrt(head_dim))
     torch.cuda.synchronize()
@@ -435,14 +418,10 @@ def test_attention_decode_from_the_products_output(heads, kv_heads, window, rota
     if rotate:
         cos_np, sin_np = plain.rope_tables(1600, head_dim, 10000.0)
         cos, sin = torch.from_numpy(cos_np).to(DEV), torch.from_numpy(sin_np).to(DEV)
-    tables = group.block_tables.cpu().numpy()
-    positions = step.positions.cpu().numpy()
-    row_request = step.row_request.cpu().numpy()
-    slots = np.array([tables[row_request[i], positions[i] // page] * page + positions[i] % page for i in range(rows)], dtype=np.int32)
+    slots = group.slots                                             # page * 16 + slot of every row's position
     slots[step.host_row_start[4]] = -1                              # this row's key and value are not written
-    slots = torch.from_numpy(slots).to(DEV)
     if splits:
-        step.extras["decode_schedule"] = (splits, -(-(-(-1501 // 64)) // splits) * 64, None)
+        step.plan.native.plan.force_decode(splits, -(-(-(-1501 // 64)) // splits) * 64)
     scale = 1.0 / math.sqrt(head_dim)
     # the separate kernels
     cache_a = cache.clone()
@@ -453,8 +432,8 @@ def test_attention_decode_from_the_products_output(heads, kv_heads, window, rota
     # the one kernel
     cache_b = cache.clone()
     out_b = torch.full_like(q, float("nan"))
-    assert ops_attn.decode_from_qkv(qkv, qw, kw, 1e-6, cos, sin, slots, cache_b, out_b, step, group, heads, kv_heads,
-                                    head_dim, window, scale)
+    assert ops_attn.decode_from_qkv(qkv, qw, kw, 1e-6, cos, sin, out_b, step, 0, heads, kv_heads, head_dim, window, scale,
+                                    cache=ops_attn.OneEntryCache(cache_b))
     torch.cuda.synchronize()
     ops_tc.check_errors()
     assert torch.isfinite(out_b.float()).all()

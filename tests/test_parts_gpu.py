@@ -53,14 +53,14 @@ def _toy_mixer_class():
             state = step.state(cache_entry)
             for r in range(step.requests):
                 a, n = step.host_row_start[r], step.host_row_count[r]
-                slot = step.host_state_slots[r]
+                slot, slot_out = step.host_state_slots[r], step.host_state_slots_out[r]
                 # A request's first token reads a zero state whatever the slot holds.
                 s = state[slot].clone() if step.host_history[r] > 0 else torch.zeros(self.hidden, device=h.device)
                 outs = []
                 for t in range(n):
                     s = self.decay * s + h[a + t].float()
                     outs.append(s)
-                state[slot] = s
+                state[slot_out] = s          # the request's spare slot: the two swap when the step is committed
                 residual[a:a + n] += torch.stack(outs) @ self.weight.T
 
     return RunningSumMixer
@@ -329,7 +329,7 @@ def test_toy_architecture_is_registered_built_and_stepped(toy):
         assert not engine.model.recordable
         got = helpers.run_trace(engine, steps)
         engine.cache.check()
-        assert engine.cache.used_pages() == [0, 0] and engine.cache.state_slots.free_slots == 4
+        assert engine.cache.used_pages() == [0, 0] and engine.cache.state_slots.free_slots == 8
         worst = max(float(np.abs(got[(rid, p)] - refs[rid][p]).max()) for rid, ids in requests.items() for p in range(len(ids)))
         scale = max(float(np.abs(r).max()) for r in refs.values())
         assert worst <= 1e-4 * scale, f"{make.__name__}: {worst:.3e} (scale {scale:.3f})"
@@ -351,26 +351,20 @@ def test_windowed_group_gives_pages_back_while_the_full_group_keeps_them(toy):
 
 # ---------------------------------------------------------------------------------------------
 # Each part of a layer alone, against the plain functions, through the same StepBatch a step builds.
-def _single_request_step(n, hidden_unused=None, history=0, page=8, kv_heads=2, head_dim=16, dtype=torch.float32, window=None):
+def _single_request_step(n, part, history=0, page=8, kv_heads=2, head_dim=16, dtype=torch.float32, window=None, cache=None):
+    """The step of one request that brings `n` rows after `history`, over a cache manager of its own (or `cache`,
+    whose request "r" goes on), planned for `part`."""
     from llmx_b200.cache import CacheManager, KVSpec
-    from llmx_b200.parts.base import GroupView, StepBatch
-    cache = CacheManager([KVSpec(kv_heads, head_dim, window)], page, 256, 2, kv_dtype=dtype, device=DEV)
-    rc = cache.new_request("r")
-    if history:
-        rc.prepare(history)
-        rc.commit()
+    from llmx_b200.engine.batch import step_from_requests
+    if cache is None:
+        cache = CacheManager([KVSpec(kv_heads, head_dim, window)], page, 256, 2, kv_dtype=dtype, device=DEV)
+        rc = cache.new_request("r")
+        if history:
+            rc.prepare(history)
+            rc.commit()
+    rc = cache.live["r"]
     rc.prepare(n)
-    pages = rc.tables[0].pages
-    pos = np.arange(history, history + n)
-
-    def dev(a):
-        return torch.as_tensor(np.asarray(a, dtype=np.int32)).to(DEV)
-    slots = [pages[p // page] * page + p % page for p in pos]
-    group = GroupView(dev([pages]), dev(slots), page)
-    return StepBatch(rows=n, requests=1, token_ids=dev(np.zeros(n)), positions=dev(pos), row_request=dev(np.zeros(n)),
-                     row_start=dev([0]), row_count=dev([n]), history=dev([history]), state_slots=dev([-1]),
-                     logit_rows=dev([n - 1]), groups=[group], caches=cache, host_row_start=[0], host_row_count=[n],
-                     host_history=[history], host_state_slots=[-1], max_row_count=n, max_context=history + n)
+    return step_from_requests(cache, [rc], [n], DEV, parts=[part], wants=[(n - 1,)])
 
 
 @pytest.mark.parametrize("precision", ["float32", "bfloat16"])
@@ -434,21 +428,12 @@ def test_attention_part_in_two_portions(precision, tol, heads, kv_heads, head_di
     T, cut = 37, 21
     h = torch.randn(T, E, generator=g).to(p.act)
     x = torch.zeros(T, E)
-    step1 = _single_request_step(cut, kv_heads=kv_heads, head_dim=head_dim, dtype=p.act, page=16 if head_dim == 64 else 8, window=window)
+    step1 = _single_request_step(cut, part, kv_heads=kv_heads, head_dim=head_dim, dtype=p.act, page=16 if head_dim == 64 else 8, window=window)
     res1 = x[:cut].clone().to(DEV)
     part.forward(h[:cut].to(DEV), step1, 0, res1)
-    rc = step1.caches.live["r"]
-    rc.commit()
-    page = step1.groups[0].page_size
-    rc.prepare(T - cut)
-    from llmx_b200.parts.base import GroupView
-    pages = rc.tables[0].pages
-    dev = lambda a: torch.as_tensor(np.asarray(a, dtype=np.int32)).to(DEV)   # noqa: E731
-    pos = np.arange(cut, T)
-    step2 = _single_request_step(T - cut, kv_heads=kv_heads, head_dim=head_dim, dtype=p.act, page=page, window=window)
-    step2.caches = step1.caches
-    step2.groups = [GroupView(dev([pages]), dev([pages[q // page] * page + q % page for q in pos]), page)]
-    step2.positions, step2.history, step2.host_history = dev(pos), dev([cut]), [cut]
+    step1.caches.live["r"].commit()
+    step2 = _single_request_step(T - cut, part, cache=step1.caches)
+    assert step2.host_history == [cut]
     res2 = x[cut:].clone().to(DEV)
     part.forward(h[cut:].to(DEV), step2, 0, res2)
     got = torch.cat([res1, res2]).cpu().numpy()

@@ -176,15 +176,18 @@ def test_a_request_that_cannot_fit_even_alone_ends_with_reason_cache():
 
 def test_step_layout_and_room():
     """Where a step's metadata lies in its buffer, and the room a recorded step leaves for context."""
+    import numpy as np
     from llmx_b200.engine.engine import StepLayout, room_for
-    lay = StepLayout([3, 1, 5], wanted=2, max_pages=[4, 2], extra=1)
+    lay = StepLayout([3, 1, 5], wanted=2, max_pages=[4, 2], streams=2, plan_ints=5)
     assert (lay.requests, lay.rows, lay.starts) == (3, 9, [0, 3, 4])
-    assert lay.sizes == [9, 9, 9, 3, 3, 3, 3, 2, 12, 9, 6, 9, 1]
+    # tokens, positions (two streams), row -> request, first row, rows, history, state slots read, wanted rows,
+    # state slots written, then tables and slots of two cache groups, then the parts' launch plans
+    assert lay.sizes == [9, 18, 9, 3, 3, 3, 3, 2, 3, 12, 9, 6, 9, 5]
+    assert lay.tables(np.zeros(lay.total, dtype=np.int32), 1).shape == (3, 2) and lay.plan(np.zeros(lay.total)).size == 5
     # sections do not overlap, start on 16-byte boundaries and fill the buffer
     ends = [o + max(s, 1) for o, s in zip(lay.offsets, lay.sizes)]
     assert all(o % 4 == 0 for o in lay.offsets)
     assert all(e <= nxt for e, nxt in zip(ends, lay.offsets[1:] + [lay.total]))
-    import numpy as np
     buf = np.arange(lay.total, dtype=np.int32)
     assert lay.section(buf, 3).tolist() == list(range(lay.offsets[3], lay.offsets[3] + 3))
     # an empty section (nothing wanted) still has a place of its own

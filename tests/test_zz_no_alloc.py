@@ -59,7 +59,7 @@ def test_static_entry_point_matches_the_ordinary_one_on_two_calls_in_a_row():
         splits = 4
         chunk = -(-(-(-longest // 64)) // splits) * 64
         _req_list = torch.arange(step.requests, dtype=torch.int32, device=q.device)
-        step.extras["decode_schedule"] = (splits, chunk, None)
+        step.plan.native.plan.force_decode(splits, chunk)
         want = torch.full_like(q, float("nan"))
         ops_attn.paged_attention_bf16(q, cache, want, step, group, heads, kv_heads, head_dim, None, 1.0 / math.sqrt(head_dim))
         status, got = _call_static(fn, q, cache, step, group, heads, kv_heads, head_dim, splits, chunk)
