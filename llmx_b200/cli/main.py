@@ -80,6 +80,20 @@ def _dtype(value: str) -> str:
     return table[value]
 
 
+def _cache_type(given) -> Optional[str]:
+    """The cache's element type from --cache-type-k / --cache-type-v (the reference's flags, src/cli/main.cpp:2018-2038),
+    or None for the path's own.  Keys and values lie in one storage here, so the two must agree; bf16 and f32 are
+    what the kernels take (the reference's f16 default has no kernel in this engine and is refused by name)."""
+    k, v = given.get("--cache-type-k"), given.get("--cache-type-v")
+    for f, t in (("--cache-type-k", k), ("--cache-type-v", v)):
+        if t is not None and t not in ("bf16", "f32"):
+            raise UsageError(f"{f} {t}: the cache is bf16 or f32 here (no kernel reads a cache of another type)")
+    if k is not None and v is not None and k != v:
+        raise UsageError("--cache-type-k and --cache-type-v must agree: keys and values share their pages here")
+    t = k if k is not None else v
+    return None if t is None else {"bf16": "bfloat16", "f32": "float32"}[t]
+
+
 def _yarn(given: Dict[str, str]) -> Tuple[Optional[float], Optional[int]]:
     """--yarn F and --yarn-original-ctx N (src/cli/main.cpp:567-571, :597)."""
     yarn = _float("--yarn", given["--yarn"], 1.0, 3.4028234e38) if "--yarn" in given else None
@@ -151,9 +165,7 @@ def cmd_generate(argv: List[str]) -> int:
         seed=_int("--seed", given.get("--seed", "0"), 0, 2 ** 64 - 1),
         ignore_eos="--ignore-eos" in given)
     dtype = _dtype(given.get("--dtype", "auto"))
-    for f in ("--cache-type-k", "--cache-type-v"):
-        if f in given and given[f] not in ("bf16", "f32"):
-            raise UsageError(f"{f}: the cache has the path's type here (bf16 with --dtype bf16, f32 with --dtype f32)")
+    kv_dtype = _cache_type(given)
     ubatch = _int("--ubatch", given.get("--ubatch", "512"), 1)
     kv_tokens = _int("--kv-tokens", given["--kv-tokens"], 1) if "--kv-tokens" in given else None
     if kv_tokens is None:
@@ -163,7 +175,7 @@ def cmd_generate(argv: List[str]) -> int:
     from ..engine.generate import LLM
     t0 = time.perf_counter()
     llm = LLM(model, dtype=dtype, kv_tokens=kv_tokens, ubatch=ubatch, max_seqs=1, device=given.get("--device", "cuda:0"),
-              yarn=yarn, yarn_original_ctx=yarn_original)
+              yarn=yarn, yarn_original_ctx=yarn_original, kv_dtype=kv_dtype)
     if "--verbose" in given:
         print(f"load: {time.perf_counter() - t0:.2f} s", file=sys.stderr)
         print(f"prompt tokens: {len(prompt)}")
@@ -201,7 +213,7 @@ def cmd_logits(argv: List[str]) -> int:
     ubatch = 1 if "--per-token" in given else _int("--ubatch", given.get("--ubatch", "512"), 1)
     engine = Engine.from_dir(pos[0], EngineOptions(dtype=_dtype(given.get("--dtype", "auto")),
                                                    kv_tokens=-(-len(ids) // 64) * 64, max_requests=1,
-                                                   device=given.get("--device", "cuda:0")))
+                                                   device=given.get("--device", "cuda:0"), kv_dtype=_cache_type(given)))
     first_wanted = len(ids) - last
     rows = []
     for at in range(0, len(ids), ubatch):
@@ -324,7 +336,8 @@ def cmd_bench(argv: List[str]) -> int:
     reach = max(p + g, depth + p) if seqs > 1 else depth + max(p, g)
     kv = (-(-(reach + 2) // 64) * 64 + 64) * seqs
     engine = Engine.from_dir(given["--model"], EngineOptions(dtype=dtype, kv_tokens=kv, max_requests=seqs,
-                                                             device=given.get("--device", "cuda:0"), record_after=2))
+                                                             device=given.get("--device", "cuda:0"), record_after=2,
+                                                             kv_dtype=_cache_type(given)))
     if reach > engine.max_positions:
         raise UsageError(f"the tests reach {reach} tokens, past the model's context of {engine.max_positions}")
     vocab = engine.model.vocab_size

@@ -220,13 +220,13 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
         if (n_pages > 0 && lane < PAGES_PER_STAGE) {
             if (lane == 0) tc::tma_prefetch_desc(&cache_map);
             const int* table = block_tables + (size_t)r * table_stride + kv_begin / PAGE;
-            int id_next = lane < n_pages ? table[lane] : 0;
+            int id_next = lane < n_pages ? max(table[lane], 0) : 0;      // (a page given back, -1, is never needed: see kv_begin)
             for (int it = 0; it < iters; ++it) {
                 const int stage = it % STAGES;
                 const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
                 const int id = id_next;
                 const int nxt = (it + 1) * PAGES_PER_STAGE + lane;
-                id_next = nxt < n_pages ? table[nxt] : 0;
+                id_next = nxt < n_pages ? max(table[nxt], 0) : 0;
                 bool ok = tc::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, error_word, ERR_DEC_PRODUCER);
                 const int here = min(PAGES_PER_STAGE, n_pages - it * PAGES_PER_STAGE);
                 // The bytes a phase expects must be announced before any of its copies can land (a copy that

@@ -89,10 +89,12 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bf
             tc::tma_prefetch_desc(&cache_map);
             const int* table = block_tables + (size_t)r * table_stride + kv_begin / PAGE;
             const int n_pages = (kv_end - kv_begin + PAGE - 1) / PAGE;
-            // The page ids of a stage are read one stage ahead, so the table's latency is off the critical path.
+            // The page ids of a stage are read one stage ahead, so the table's latency is off the critical path.  With a
+            // window the first stage starts at a stage boundary below the lowest key a row needs, where the request may
+            // have given its pages back (id -1): those keys are masked whatever they hold, so page 0 stands in.
             int ids[PAGES_PER_STAGE], ids_next[PAGES_PER_STAGE];
 #pragma unroll
-            for (int p = 0; p < PAGES_PER_STAGE; ++p) ids_next[p] = p < n_pages ? table[p] : 0;
+            for (int p = 0; p < PAGES_PER_STAGE; ++p) ids_next[p] = p < n_pages ? max(table[p], 0) : 0;
             for (int it = 0; it < iters; ++it) {
                 const int stage = it % STAGES;
                 const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
@@ -100,7 +102,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bf
                 for (int p = 0; p < PAGES_PER_STAGE; ++p) {
                     ids[p] = ids_next[p];
                     const int nxt = (it + 1) * PAGES_PER_STAGE + p;
-                    ids_next[p] = nxt < n_pages ? table[nxt] : 0;
+                    ids_next[p] = nxt < n_pages ? max(table[nxt], 0) : 0;
                 }
                 if (!tc::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, error_word, ERR_PRE_PRODUCER)) break;
                 const int here = min(PAGES_PER_STAGE, n_pages - it * PAGES_PER_STAGE);

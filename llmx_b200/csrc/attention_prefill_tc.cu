@@ -237,15 +237,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             ++items_done;
             const int* table = block_tables + (size_t)it.r * table_stride + it.kv_begin / PAGE;
             const int n_pages = (it.kv_end - it.kv_begin + PAGE - 1) / PAGE;
-            // A stage's page id is read one stage ahead, so the table's latency is off the copies' path.
-            int id_next = p < n_pages ? table[p] : 0;
+            // A stage's page id is read one stage ahead, so the table's latency is off the copies' path.  With a window
+            // the first stage starts at a stage boundary below the lowest key a row needs, where the request may have
+            // given its pages back (id -1): those keys are masked whatever they hold, so page 0 stands in.
+            int id_next = p < n_pages ? max(table[p], 0) : 0;
             for (int j = 0; j < it.n_iter; ++j, ++kv_uses) {
                 const int st = kv_uses % KV_STAGES;
                 const uint32_t ph = ((kv_uses / KV_STAGES) & 1u) ^ 1u;
                 const int here = min(PAGES_PER_STAGE, n_pages - j * PAGES_PER_STAGE);
                 const int id = id_next;
                 const int nxt = (j + 1) * PAGES_PER_STAGE + p;
-                id_next = nxt < n_pages ? table[nxt] : 0;
+                id_next = nxt < n_pages ? max(table[nxt], 0) : 0;
                 if (!tc::mbar_wait(&empty[st], ph, abort_flag, error_word, ERR_TCA_PRODUCER)) ok = false;
                 // The bytes a phase expects must be announced before any of its copies can land (a copy that
                 // completes first is not counted later): the half-warp's first lane announces, then all issue.

@@ -42,6 +42,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "attention_prefill": ["attention_prefill.cu"],
     "attention_prefill_tc": ["attention_prefill_tc.cu"],
     "sampling": ["sampling.cu"],
+    "selftest": ["selftest.cu"],              # the bounded wait made to run out on purpose (tests)
     "runtime": ["runtime/runtime.cpp"],       # host code: the parts' forward passes (no kernels of its own)
 }
 

@@ -31,7 +31,7 @@ extern "C" {
 
 enum { LLMX_DT_F32 = 0, LLMX_DT_BF16 = 1 };
 enum { LLMX_RT_ERR_BAD_ARGUMENT = 10001, LLMX_RT_ERR_UNSUPPORTED = 10002, LLMX_RT_ERR_TOO_LARGE = 10004,
-       LLMX_RT_ERR_UNBOUND = 10010, LLMX_RT_ERR_WORKSPACE = 10011, LLMX_RT_ERR_CALLBACK = 10012 };
+       LLMX_RT_ERR_UNBOUND = 10010, LLMX_RT_ERR_WORKSPACE = 10011, LLMX_RT_ERR_CALLBACK = 10012, LLMX_RT_ERR_INJECTED = 10013 };
 
 // Flags of a path (what `precision` means for every part built with them).
 enum { LLMX_FLAG_INVARIANT = 1 };   // schedules that do not depend on what else is in the batch (see llmx_attention_desc)
@@ -51,6 +51,9 @@ void llmx_rt_count_launches(long long n);                  // ... plus those a r
 // Entry point i (from 0) that the last dry runs (llmx_*_workspace) would have called and found unbound; 0 at the end.
 int llmx_rt_missing(int i, const char** name);
 void llmx_rt_reset_caches(void);                           // forget what was learnt of the device and the kernel libraries
+// For tests of what a failed step leaves behind: the nth call (from now) of the entry point `name` fails on the host,
+// before anything is launched, with LLMX_RT_ERR_INJECTED.  nth <= 0 or a null name: no failure is pending.
+void llmx_rt_fail_call(const char* name, int nth);
 // Device time by kernel entry point: while on, every kernel call is bracketed by events on its stream.
 int llmx_rt_profile(int on);
 // After llmx_rt_profile(0): entry i of the calls made while it was on.  Returns 0 when i is out of range.
@@ -107,7 +110,9 @@ typedef struct llmx_step {
 // writes the values that follow the actual histories.  The plan's ints go into the step's metadata at
 // llmx_step.plan_offset.
 llmx_plan* llmx_plan_make(const llmx_model* model, llmx_part* const* parts, int n_parts, const int* counts,
-                          const int* histories, int requests, int room);     // of a whole model and/or of single parts
+                          const int* histories, int requests, int room, int typical_context);
+//   (of a whole model and/or of single parts; typical_context: with room > 0, the context the recorded step is likely to
+//    meet, which shapes only what is a matter of speed; 0: none known)
 int llmx_plan_ints(const llmx_plan*);
 int llmx_plan_fill(llmx_plan*, const int* histories, int* out);
 void llmx_plan_free(llmx_plan*);

@@ -123,6 +123,12 @@ struct Ctx {
     const int* meta(int offset) const { return s->meta + offset; }
 };
 
+// A failure made on the host, for tests of what a failed step leaves behind: the nth call of one entry point from now
+// returns an error without launching anything (the reference's tests fail an operation of their CPU backend the same
+// way, tests/tiny_qwen.hpp:104-148).
+std::string g_fail_name;
+int g_fail_countdown = 0;
+
 // Calls a kernel entry point: counted, timed when profiling is on, skipped on a dry run.
 template <typename F, typename... A>
 int call(Ctx& c, const char* name, F fn, int launches, A... args) {
@@ -132,6 +138,8 @@ int call(Ctx& c, const char* name, F fn, int launches, A... args) {
     }
     if (c.status) return c.status;
     if (!fn) return c.status = fail(LLMX_RT_ERR_UNBOUND, std::string("kernel ") + name + " is not bound (its library was not loaded)");
+    if (g_fail_countdown > 0 && g_fail_name == name && --g_fail_countdown == 0)
+        return c.status = fail(LLMX_RT_ERR_INJECTED, std::string(name) + ": a failure asked for by llmx_rt_fail_call (nothing was launched)");
     Timed t{name, nullptr, nullptr};
     if (g_profile) {
         cudaEventCreate(&t.a);
@@ -369,7 +377,7 @@ struct AttnPlan {
 struct llmx_plan {
     std::vector<AttnPlan> attn;
     std::vector<int> counts;
-    int requests = 0, room = 0, ints = 0;
+    int requests = 0, room = 0, typical_context = 0, ints = 0;
     int force_tiles = 0, force_splits = 0;
     const AttnPlan* find(const AttnKey& k) const {
         for (const AttnPlan& a : attn)
@@ -638,7 +646,6 @@ struct Attention : Mixer {
         qkv.forward(c, h, rows, qkv_out, false, cleared != nullptr);
         if (!from_qkv(c, qkv_out, e, o_buf, rows, slots, g)) {
             if (c.status) return c.status;
-        } else {
             void* q = c.alloc((size_t)rows * q_width * elem(act));
             CALL(c, llmx_head_norm_rope_kv, 1, (const float*)qkv_out, qkv.N, q_width, q_width + kv_width, d.q_norm, d.k_norm,
                  d.qk_norm_eps, d.cos, d.sin, d.cos ? d.rot_half : 0, positions, slots, q, act, (void*)e.storage, e.dtype, rows, d.heads,
@@ -832,6 +839,10 @@ LLMX_API int llmx_rt_load_kernels(const char* folder) {
     return bound;
 }
 
+LLMX_API void llmx_rt_fail_call(const char* name, int nth) {
+    g_fail_name = name ? name : "";
+    g_fail_countdown = name && nth > 0 ? nth : 0;
+}
 LLMX_API int llmx_rt_missing(int i, const char** name) {
     if (i < 0 || i >= (int)g_missing.size()) return 0;
     *name = g_missing[i];
@@ -940,8 +951,11 @@ void plan_attention(llmx_plan& plan, AttnPlan& a, const int* histories) {
     for (int r = 0; r < n; ++r) {
         const int c = plan.counts[r];
         const int ctx = plan.room > 0 ? plan.room : (histories ? histories[r] : 0) + c;
+        // What a recorded step's grids must cover is its room; what its prompt portions are likely to meet (a matter
+        // of speed only: the prefill kernels take any history under any item shape) is the context it was made at.
+        const int likely = plan.room > 0 && plan.typical_context > 0 ? std::max(std::min(plan.typical_context, plan.room), c) : ctx;
         if (c <= a.max_rows) a.rows_small = std::max(a.rows_small, c), a.ctx_small = std::max(a.ctx_small, ctx);
-        else a.rows_large = std::max(a.rows_large, c), a.ctx_large = std::max(a.ctx_large, ctx);
+        else a.rows_large = std::max(a.rows_large, c), a.ctx_large = std::max(a.ctx_large, likely);
     }
     a.chunk_on_device = plan.room > 0;
     if (a.n_small) decode_schedule(a.n_small, a.key.kv_heads, a.ctx_small, a.key.head_dim, nullptr, &a.splits, &a.chunk);
@@ -954,7 +968,7 @@ void plan_attention(llmx_plan& plan, AttnPlan& a, const int* histories) {
 }  // namespace
 
 LLMX_API llmx_plan* llmx_plan_make(const llmx_model* model, llmx_part* const* parts, int n_parts, const int* counts, const int* histories,
-                                   int requests, int room) {
+                                   int requests, int room, int typical_context) {
     if (requests <= 0 || !counts || (!histories && room <= 0)) {
         fail(LLMX_RT_ERR_BAD_ARGUMENT, "llmx_plan_make: the rows each request brings, and histories or room");
         return nullptr;
@@ -965,7 +979,7 @@ LLMX_API llmx_plan* llmx_plan_make(const llmx_model* model, llmx_part* const* pa
     for (int i = 0; i < n_parts; ++i)
         if (parts && parts[i]) parts[i]->collect(keys);
     llmx_plan* plan = new llmx_plan;
-    plan->requests = requests, plan->room = room;
+    plan->requests = requests, plan->room = room, plan->typical_context = typical_context;
     plan->counts.assign(counts, counts + requests);
     int at = 0;
     for (const AttnKey& k : keys) {

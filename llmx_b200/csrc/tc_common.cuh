@@ -61,21 +61,27 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 
-// Returns false when the wait ran out (two seconds) or the block is aborting.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* error_word,
-                                          int code) {
+// Returns false when the wait ran out (`limit_ns` of wall time) or the block is aborting.
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* error_word,
+                                                int code, unsigned long long limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long start = global_ns();
     for (uint32_t i = 1;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 255u) == 0u) {
             if (*abort_flag) return false;
-            if (global_ns() - start > WAIT_LIMIT_NS) break;
+            if (global_ns() - start > limit_ns) break;
         }
     }
     *abort_flag = 1;
     if (error_word) atomicCAS(error_word, 0, code);
     return false;
+}
+
+// The kernels' waits: two seconds.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* error_word,
+                                          int code) {
+    return mbar_wait_limit(bar, parity, abort_flag, error_word, code, WAIT_LIMIT_NS);
 }
 
 // ---- TMA --------------------------------------------------------------------

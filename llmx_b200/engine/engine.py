@@ -117,6 +117,8 @@ class Engine:
         self.step_recordings = OrderedDict()
         self._shapes_seen: Dict[tuple, int] = {}
         self.last_h2d_bytes = 0
+        self._pinned_ring = [(None, None)] * 4
+        self._pinned_at = 0
 
     # -- construction ------------------------------------------------------------
     @classmethod
@@ -177,9 +179,10 @@ class Engine:
             n = len(e.tokens)
             if n == 0:
                 raise StepError(f"request {e.request_id!r}: an entry without tokens")
-            for t in e.tokens:
-                if not 0 <= int(t) < self.model.vocab_size:
-                    raise StepError(f"request {e.request_id!r}: token id {t} is outside the vocabulary of {self.model.vocab_size}")
+            ids = np.asarray(e.tokens)
+            if ids.dtype.kind not in "iu" or int(ids.min()) < 0 or int(ids.max()) >= self.model.vocab_size:
+                bad = next((t for t in e.tokens if not (isinstance(t, (int, np.integer)) and 0 <= int(t) < self.model.vocab_size)), None)
+                raise StepError(f"request {e.request_id!r}: token id {bad} is outside the vocabulary of {self.model.vocab_size}")
             if self.length(e.request_id) + n > self.max_positions:
                 raise StepError(f"request {e.request_id!r}: context length of {self.max_positions} exceeded")
             for w in e.want:
@@ -209,6 +212,24 @@ class Engine:
                               [rc.state_slot for rc in caches], max_context, plan, room,
                               [rc.state_slot_out for rc in caches])
 
+    def _pinned(self, ints: int) -> torch.Tensor:
+        """A pinned int32 buffer of `ints` values for a step's metadata, from a small ring: a buffer is used again only
+        once the copy that read it has finished."""
+        ring = self._pinned_ring
+        slot = self._pinned_at = (self._pinned_at + 1) % len(ring)
+        buf, event = ring[slot]
+        if event is not None:
+            event.synchronize()
+        if buf is None or buf.numel() < ints:
+            buf = torch.empty(max(ints, 4096), dtype=torch.int32, pin_memory=True)
+        ring[slot] = (buf, None)
+        return buf[:ints]
+
+    def _pinned_done(self, view: torch.Tensor) -> None:
+        ev = torch.cuda.Event()
+        ev.record()
+        self._pinned_ring[self._pinned_at] = (self._pinned_ring[self._pinned_at][0], ev)
+
     def _build_batch(self, entries: Sequence[StepEntry], caches) -> StepBatch:
         counts = [len(e.tokens) for e in entries]
         history = [rc.length for rc in caches]
@@ -218,11 +239,12 @@ class Engine:
         plan = self.model.plan_step(StepShape(counts, history, [tuple(e.want) for e in entries]))
         layout = StepLayout(counts, sum(len(e.want) for e in entries), max_pages, self.position_streams, plan.ints)
         # One int32 buffer for the whole step, one host-to-device copy.
-        host = torch.empty(layout.total, dtype=torch.int32, pin_memory=True)
+        host = self._pinned(layout.total)
         buf = host.numpy()
         self.fill_batch(buf, layout, entries, caches)
         plan.fill(history, layout.plan(buf))
         dev = host.to(self.device, non_blocking=True)
+        self._pinned_done(host)
         self.last_h2d_bytes = host.numel() * 4
         return self.batch_views(dev, layout, caches, history, max(h + c for h, c in zip(history, counts)), plan)
 
@@ -243,7 +265,7 @@ class Engine:
                 self._shapes_seen.clear()
             self._shapes_seen[key] = seen + 1
             return None
-        rec = recorded_step.Recording(self, counts, wants, key[2])
+        rec = recorded_step.Recording(self, counts, wants, key[2], typical_context=context)
         self.step_recordings[key] = rec
         self._shapes_seen.pop(key, None)
         while len(self.step_recordings) > recorded_step.MAX_STEP_RECORDINGS:

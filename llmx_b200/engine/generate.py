@@ -49,19 +49,25 @@ class LLM:
     reserve:          "full" or "prompt" (see llmx_b200.engine.scheduler)
     yarn, yarn_original_ctx:  the rope scaled by YaRN at this factor over this trained length (the reference's
                       --yarn and --yarn-original-ctx); the context becomes factor x length
+    kv_dtype:         the cache's element type when it is not the path's ("bfloat16" or "float32"; the reference's
+                      --cache-type-k / --cache-type-v)
+    invariant:        schedules chosen by sizes alone, so that a request's reply does not depend on what it was
+                      batched with, bit for bit (slower; see parts.base.Precision)
     """
 
     def __init__(self, model: Union[str, Engine], *, dtype: str = "bfloat16", kv_tokens: Optional[int] = None,
                  page_size: int = 16, ubatch: int = 512, max_seqs: int = 16, reserve: str = "full",
-                 device: str = "cuda:0", yarn: Optional[float] = None, yarn_original_ctx: Optional[int] = None):
+                 device: str = "cuda:0", yarn: Optional[float] = None, yarn_original_ctx: Optional[int] = None,
+                 kv_dtype: Optional[str] = None, invariant: bool = False):
         if isinstance(model, Engine):
             self.engine = model
         else:
             if kv_tokens is None:
-                kv_tokens = self._default_kv_tokens(model, dtype, page_size, device)
+                kv_tokens = self._default_kv_tokens(model, kv_dtype or dtype, page_size, device)
             self.engine = Engine.from_dir(model, EngineOptions(dtype=dtype, kv_tokens=kv_tokens, page_size=page_size,
                                                                max_requests=max_seqs, device=device, yarn=yarn,
-                                                               yarn_original_ctx=yarn_original_ctx))
+                                                               yarn_original_ctx=yarn_original_ctx, kv_dtype=kv_dtype,
+                                                               invariant=invariant))
         self.ubatch, self.max_seqs, self.reserve = int(ubatch), int(max_seqs), reserve
         self.stats = GenerationStats()
         self._next_id = 0

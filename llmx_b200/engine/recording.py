@@ -37,13 +37,14 @@ class _NoCache:
 
 
 class Recording:
-    def __init__(self, engine, counts: Sequence[int], wants: Sequence[Sequence[int]], room: int, ring: int = 3):
+    def __init__(self, engine, counts: Sequence[int], wants: Sequence[Sequence[int]], room: int, ring: int = 3,
+                 typical_context: int = 0):
         from .. import runtime
         eng = engine                         # not kept: the engine owns its recordings
         self.counts, self.room = [int(c) for c in counts], int(room)
         n = len(self.counts)
         max_pages = [max(1, -(-room // g.page_size)) for g in eng.cache.groups]
-        self.plan = eng.model.plan_step(StepShape(self.counts, None, [tuple(w) for w in wants], self.room))
+        self.plan = eng.model.plan_step(StepShape(self.counts, None, [tuple(w) for w in wants], self.room, typical_context))
         self.layout = StepLayout(self.counts, sum(len(w) for w in wants), max_pages, eng.position_streams, self.plan.ints)
         self.total = self.layout.total
         # The host may run several steps ahead of the device: a ring of pinned buffers, each reused only

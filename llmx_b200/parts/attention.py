@@ -33,7 +33,7 @@ class NativePlan(PartPlan):
 
     def __init__(self, model_handle, part_handles, shape: StepShape):
         self.plan = runtime.Plan(model_handle, list(part_handles), list(shape.counts),
-                                 None if shape.histories is None else list(shape.histories), shape.room)
+                                 None if shape.histories is None else list(shape.histories), shape.room, shape.typical_context)
         self.ints = self.plan.ints
 
     def fill(self, histories, out: np.ndarray) -> None:

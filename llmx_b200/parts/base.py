@@ -40,6 +40,7 @@ from typing import Any, Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
+from .. import runtime
 from ..weights.spec import TensorSpec
 
 
@@ -73,7 +74,6 @@ class Precision:
 
     @property
     def flags(self) -> int:
-        from .. import runtime
         return runtime.FLAG_INVARIANT if self.invariant else 0
 
 
@@ -82,11 +82,13 @@ class StepShape:
     """What a launch plan may depend on.  `counts[r]`: rows request r brings; `histories[r]`: tokens before them.
     `room` > 0: the step is recorded and replayed; every decision that shapes a launch (grids, scratch sizes, the
     plan's length) must then follow `counts` and `room` alone (`histories` is None), and `PartPlan.fill` writes what
-    follows the histories of the run at hand."""
+    follows the histories of the run at hand.  `typical_context` (with room): the context the step that caused the
+    recording had, a hint for decisions that are a matter of speed only."""
     counts: Sequence[int]
     histories: Optional[Sequence[int]]
     wants: Sequence[Sequence[int]] = ()
     room: int = 0
+    typical_context: int = 0
 
 
 class PartPlan:
@@ -166,17 +168,14 @@ class NativeHandle:
 
     def __init__(self, handle: int, keep=()):
         if not handle:
-            from .. import runtime
             raise runtime.KernelError(runtime.last_error())
         self.handle = handle
         self.keep = keep              # tensors and handles the native part points into
 
     def __del__(self):
         h, self.handle = getattr(self, "handle", None), None
-        if h:
-            from .. import runtime
-            if runtime._lib is not None:
-                runtime._lib.llmx_part_destroy(h)
+        if h and runtime is not None and runtime._lib is not None:
+            runtime._lib.llmx_part_destroy(h)
 
 
 @dataclass
@@ -243,7 +242,6 @@ class StepBatch:
 
     def struct_for(self, part, workspace_bytes: int = 0):
         """A copy of the step's `llmx_step` for one native part called from Python: its own plan and a workspace."""
-        from .. import runtime
         s = runtime.StepStruct.from_buffer_copy(self.struct)
         if self.plan is not None:
             handle, offset = self.plan.native_plan(part)

@@ -73,6 +73,7 @@ _SIGNATURES = {
     "llmx_rt_count_launches": (None, [_ll]),
     "llmx_rt_profile": (_i, [_i]),
     "llmx_rt_profile_read": (_i, [_i, ctypes.POINTER(ctypes.c_char_p), ctypes.POINTER(_f), ctypes.POINTER(_f)]),
+    "llmx_rt_fail_call": (None, [ctypes.c_char_p, _i]),
     "llmx_rt_missing": (_i, [_i, ctypes.POINTER(ctypes.c_char_p)]),
     "llmx_rt_reset_caches": (None, []),
     "llmx_gemm_plan": (None, [_i, _i, _i, _i, _i, ctypes.POINTER(_i), ctypes.POINTER(_i), ctypes.POINTER(_i)]),
@@ -84,7 +85,7 @@ _SIGNATURES = {
     "llmx_caches_destroy": (None, [_p]),
     "llmx_caches_set_kv": (_i, [_p, _i, _i, _p, _i, _ll, _i, _i, _i]),
     "llmx_caches_set_state": (_i, [_p, _i, _p, _ll, _ll]),
-    "llmx_plan_make": (_p, [_p, _p, _i, _p, _p, _i, _i]),
+    "llmx_plan_make": (_p, [_p, _p, _i, _p, _p, _i, _i, _i]),
     "llmx_plan_ints": (_i, [_p]),
     "llmx_plan_fill": (_i, [_p, _p, _p]),
     "llmx_plan_free": (None, [_p]),
@@ -185,6 +186,12 @@ def bind_missing() -> bool:
     if names:
         rt.llmx_rt_reset_caches()
     return bool(names)
+
+
+def fail_call(name: Optional[str], nth: int = 1) -> None:
+    """The nth call from now of kernel entry point `name` fails on the host, before anything is launched (for tests
+    of what a failed step leaves behind); `None` withdraws a pending failure."""
+    lib().llmx_rt_fail_call(name.encode() if name else None, int(nth))
 
 
 def launches() -> int:
@@ -289,12 +296,12 @@ class Plan:
     is recorded and replayed; `fill` then follows the histories of the run at hand."""
 
     def __init__(self, model_handle, part_handles: Sequence[int], counts: Sequence[int], histories: Optional[Sequence[int]],
-                 room: int = 0):
+                 room: int = 0, typical_context: int = 0):
         n = len(counts)
         c = (ctypes.c_int * n)(*counts)
         h = (ctypes.c_int * n)(*histories) if histories is not None else None
         parts = (ctypes.c_void_p * len(part_handles))(*part_handles) if part_handles else None
-        self.handle = lib().llmx_plan_make(model_handle, parts, len(part_handles), c, h, n, int(room))
+        self.handle = lib().llmx_plan_make(model_handle, parts, len(part_handles), c, h, n, int(room), int(typical_context))
         if not self.handle:
             raise KernelError(last_error())
         self.ints = lib().llmx_plan_ints(self.handle)

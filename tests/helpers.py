@@ -156,20 +156,23 @@ def _folder(model_dir: str):
 _ref_cache: Dict[tuple, np.ndarray] = {}
 
 
-def reference_logits(model_dir: str, ids: Sequence[int], bf16: bool) -> np.ndarray:
-    """Logits [len(ids), vocab] of the plain implementation; with `bf16`, rounding what that path rounds."""
-    key = (model_dir, tuple(ids), bf16)
+def reference_logits(model_dir: str, ids: Sequence[int], bf16: bool, cache: str = "same") -> np.ndarray:
+    """Logits [len(ids), vocab] of the plain implementation; with `bf16`, rounding what that path rounds.
+    `cache`: "same" (the cache has the path's type), "float32" or "bfloat16" (a cache type of its own)."""
+    key = (model_dir, tuple(ids), bf16, cache)
     if key not in _ref_cache:
         cfg, w = _folder(model_dir)
-        _ref_cache[key] = plain.forward(cfg, w, list(ids), act_round=plain.round_bf16 if bf16 else None)
+        cache_round = {"same": "same", "float32": None, "bfloat16": plain.round_bf16}[cache]
+        _ref_cache[key] = plain.forward(cfg, w, list(ids), act_round=plain.round_bf16 if bf16 else None, cache_round=cache_round)
     return _ref_cache[key]
 
 
-def compare(got: Dict[Tuple[str, int], np.ndarray], requests: Dict[str, List[int]], model_dir: str, bf16: bool):
+def compare(got: Dict[Tuple[str, int], np.ndarray], requests: Dict[str, List[int]], model_dir: str, bf16: bool,
+            cache: str = "same"):
     """(largest absolute difference, logit scale, where) over every wanted position."""
     worst, where, scale = 0.0, None, 0.0
     for rid, ids in requests.items():
-        ref = reference_logits(model_dir, ids, bf16)
+        ref = reference_logits(model_dir, ids, bf16, cache)
         scale = max(scale, float(np.abs(ref).max()))
         for p in range(len(ids)):
             if (rid, p) not in got:

@@ -140,7 +140,7 @@ def swiglu_ffn(h: np.ndarray, w_gate: np.ndarray, w_up: np.ndarray, w_down: np.n
 
 
 def attention_block(h: np.ndarray, w: Dict[str, np.ndarray], pre: str, cfg: dict, cos, sin, act_round=None,
-                    window: Optional[int] = None) -> np.ndarray:
+                    window: Optional[int] = None, cache_round="same") -> np.ndarray:
     """Projections, per-head q/k RMSNorm before the rotation, attention, output projection
     (src/model/arch/qwen3.hpp:272-295)."""
     H, G = cfg["num_attention_heads"], cfg["num_key_value_heads"]
@@ -152,8 +152,12 @@ def attention_block(h: np.ndarray, w: Dict[str, np.ndarray], pre: str, cfg: dict
     v = (h @ w[pre + "v_proj.weight"].T).astype(F).reshape(T, G, D)
     q = rope_rotate(rms_norm(q, w[pre + "q_norm.weight"], eps), cos, sin)
     k = rope_rotate(rms_norm(k, w[pre + "k_norm.weight"], eps), cos, sin)
-    if act_round is not None:   # what a reduced-precision path stores: queries, keys, values
-        q, k, v = act_round(q), act_round(k), act_round(v)
+    if cache_round == "same":   # the cache has the path's type unless it is given one of its own
+        cache_round = act_round
+    if act_round is not None:   # what a reduced-precision path stores: queries ...
+        q = act_round(q)
+    if cache_round is not None:  # ... and, in the cache, keys and values
+        k, v = cache_round(k), cache_round(v)
     o = attention(q, k, v, window=window).reshape(T, H * D)
     if act_round is not None:
         o = act_round(o)
@@ -172,12 +176,13 @@ def normalized_config(cfg: dict) -> dict:
     return c
 
 
-def forward(cfg: dict, w: Dict[str, np.ndarray], ids, act_round=None) -> np.ndarray:
+def forward(cfg: dict, w: Dict[str, np.ndarray], ids, act_round=None, cache_round="same") -> np.ndarray:
     """Logits [T, vocab] of one whole sequence: embed, L x (x += attn(norm x); x += ffn(norm x)),
     final norm, head (src/model/passes.hpp:771-830; head src/model/arch/blocks.hpp:267-272).
 
     `act_round` (optional) rounds what a reduced-precision path rounds: the inputs of every
-    matrix product and what the cache stores.  None is the float32 model.
+    matrix product and what the cache stores.  None is the float32 model.  `cache_round`: the rounding of keys and
+    values in the cache when the cache has a type of its own ("same": the path's; None: a 32-bit cache).
     """
     cfg = normalized_config(cfg)
     T = len(ids)
@@ -192,7 +197,7 @@ def forward(cfg: dict, w: Dict[str, np.ndarray], ids, act_round=None) -> np.ndar
     for l in range(cfg["num_hidden_layers"]):
         pre = f"model.layers.{l}."
         h = r(rms_norm(x, w[pre + "input_layernorm.weight"], eps))
-        x = (x + attention_block(h, w, pre + "self_attn.", cfg, cos, sin, act_round)).astype(F)
+        x = (x + attention_block(h, w, pre + "self_attn.", cfg, cos, sin, act_round, cache_round=cache_round)).astype(F)
         h = r(rms_norm(x, w[pre + "post_attention_layernorm.weight"], eps))
         x = (x + swiglu_ffn(h, w[pre + "mlp.gate_proj.weight"], w[pre + "mlp.up_proj.weight"],
                             w[pre + "mlp.down_proj.weight"], act_round)).astype(F)

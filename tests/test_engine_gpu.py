@@ -472,3 +472,185 @@ def test_hugging_face_golden_of_odd_sizes(tmp_path, dtype):
                 scale = float(np.abs(ref).max())
                 assert np.abs(whole - ref).max() <= TOL[dtype] * scale and np.abs(last - ref).max() <= TOL[dtype] * scale
         engine.cache.check()
+
+
+# ---------------------------------------------------------------------------------------------
+# What a failed step leaves behind, rolling back, cache types, invariance, memory.
+def _products(dtype):
+    return "llmx_gemm_plain" if dtype == "float32" else "llmx_gemm_tc"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_step_that_fails_inside_the_forward_pass_leaves_every_request_where_it_was(model_dirs, dtype):
+    """The reference's tests fail an operation of their backend in mid-pass, after keys were written, and check that
+    every length is back and the same prompt again is exact (tests/tiny_qwen.hpp:104-148).  Here the failure is made
+    on the host: the sixth matrix product of the step (the second layer's output projection: both layers' keys of
+    the portion are in their pages by then) returns an error instead of launching.  First in a step that holds a
+    portion of a live request beside a new request, then in a plain decode step, then in a replayed one."""
+    import torch
+    from llmx_b200 import ops_tc, runtime
+    from llmx_b200.engine import StepEntry
+    from llmx_b200.engine.decode_loop import DecodeSession
+    vocab = CONFIGS["D"][0]["vocab_size"]
+    a_ids, b_ids = helpers.random_ids(vocab, 60, seed=1), helpers.random_ids(vocab, 22, seed=2)
+    folder, engine = _engine(model_dirs, "D", dtype, 256)
+    _, clean = _engine(model_dirs, "D", dtype, 256)
+    tol = 0.0 if dtype == "float32" else 2e-3          # bfloat16 sums pieces with atomics: the last bits move from run to run
+
+    def same(x, y):
+        if tol == 0.0:
+            return torch.equal(x, y)
+        return float((x - y).abs().max()) <= tol * float(y.abs().max())
+
+    first = [StepEntry("a", a_ids[:30], [29])]
+    second = [StepEntry("a", a_ids[30:50], [0, 19]), StepEntry("b", b_ids[:10], [9])]
+    assert same(engine.step(first), clean.step(first))
+    used = engine.cache.used_pages()
+    runtime.fail_call(_products(dtype), 6)
+    with pytest.raises(runtime.KernelError, match="llmx_rt_fail_call"):
+        engine.step(second)
+    torch.cuda.synchronize()
+    assert engine.length("a") == 30 and "b" not in engine.cache.live and engine.cache.used_pages() == used
+    engine.cache.check()
+    assert same(engine.step(second), clean.step(second))          # the same step again is what it is on a clean engine
+    # a plain decode step fails: both requests stay where they are, and the next one is right
+    session, clean_session = DecodeSession(engine, ["a", "b"]), DecodeSession(clean, ["a", "b"])
+    runtime.fail_call(_products(dtype), 6)
+    with pytest.raises(runtime.KernelError):
+        session.step([a_ids[50], b_ids[10]])
+    assert (engine.length("a"), engine.length("b")) == (50, 10)
+    engine.cache.check()
+    got = {}
+    for t in range(8):
+        toks = [a_ids[50 + t], b_ids[10 + t]]
+        if t == 5:                                     # by now the session replays a recording: its launch fails
+            assert session.replays()
+            rec = session._rec
+            real, rec._graph.replay = rec._graph.replay, lambda: (_ for _ in ()).throw(RuntimeError("replay refused"))
+            with pytest.raises(RuntimeError, match="replay refused"):
+                session.step(toks)
+            rec._graph.replay = real
+            assert (engine.length("a"), engine.length("b")) == (55, 15)
+            engine.cache.check()
+        out, want = session.step(toks), clean_session.step(toks)
+        assert same(out, want), t
+        got[("a", 50 + t)], got[("b", 10 + t)] = out[0].float().cpu().numpy(), out[1].float().cpu().numpy()
+    runtime.fail_call(None)
+    ops_tc.check_errors()
+    worst, scale, where = helpers.compare(got, {"a": a_ids[:58], "b": b_ids[:18]}, folder, dtype == "bfloat16")
+    assert worst <= TOL[dtype] * scale, f"largest difference {worst:.3e} at {where}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_request_rolled_back_goes_on_as_if_the_tokens_had_never_come(model_dirs, dtype):
+    """`Engine.truncate`: the keys beyond the new length are forgotten and their pages given back; feeding the same
+    tokens again gives the same logits, feeding others gives theirs."""
+    import torch
+    from llmx_b200.engine import StepEntry, StepError
+    vocab = CONFIGS["B"][0]["vocab_size"]
+    ids = helpers.random_ids(vocab, 50, seed=8)
+    other = ids[:27] + helpers.random_ids(vocab, 20, seed=9)
+    folder, engine = _engine(model_dirs, "B", dtype, 128)
+    whole = engine.step([StepEntry("r", ids, list(range(50)))]).clone()
+    pages = engine.cache.used_pages()[0]
+    engine.truncate("r", 27)
+    assert engine.length("r") == 27 and engine.cache.used_pages()[0] == -(-27 // 8) < pages
+    engine.cache.check()
+    again = engine.step([StepEntry("r", ids[27:], list(range(23)))])
+    if dtype == "float32":
+        assert torch.equal(again, whole[27:])
+    engine.truncate("r", 27)
+    got_rows = engine.step([StepEntry("r", other[27:], list(range(20)))]).float().cpu().numpy()
+    got = {("r", 27 + i): got_rows[i] for i in range(20)}
+    worst, scale, where = helpers.compare(got, {"r": other}, folder, dtype == "bfloat16")
+    assert worst <= TOL[dtype] * scale, f"largest difference {worst:.3e} at {where}"
+    with pytest.raises(ValueError):
+        engine.truncate("r", 48)
+    with pytest.raises(StepError):
+        engine.truncate("nobody", 1)
+    engine.end("r")
+    assert engine.cache.used_pages() == [0]
+
+
+@pytest.mark.parametrize("name", ["B", "D", "E"])
+@pytest.mark.parametrize("dtype,kv_dtype", [("bfloat16", "float32"), ("float32", "bfloat16")])
+def test_a_cache_type_of_its_own(model_dirs, name, dtype, kv_dtype):
+    """The cache's element type is an option of its own (the reference's ModelOptions.kv_k / kv_v,
+    src/model/runtime.hpp:80-84): bfloat16 products over a float32 cache leave only the products' rounding, float32
+    products over a bfloat16 cache only the cache's.  Both run the general kernels; mixed cutting with pages used
+    again, against the plain implementation rounding exactly what each rounds."""
+    from llmx_b200.engine import Engine, EngineOptions
+    d16, d32, page = model_dirs[name]
+    folder = d32 if dtype == "float32" else d16
+    vocab = CONFIGS[name][0]["vocab_size"]
+    requests = {f"k{i}": helpers.random_ids(vocab, n, seed=60 + i) for i, n in enumerate([70, 9, 40, 33, 1])}
+    steps = helpers.trace_mixed(requests)
+    engine = Engine.from_dir(folder, EngineOptions(dtype=dtype, kv_dtype=kv_dtype, kv_tokens=helpers.tokens_needed(steps),
+                                                   page_size=page, max_requests=4))
+    import torch
+    assert engine.cache.groups[0].storage.dtype is getattr(torch, kv_dtype)
+    got = helpers.run_trace(engine, steps)
+    engine.cache.check()
+    worst, scale, where = helpers.compare(got, requests, folder, dtype == "bfloat16", cache=kv_dtype)
+    # float32 products over a bfloat16 cache: the plain twin rounds the same keys and values, so only the order of
+    # float32 sums differs -- but a key rounded on the other side of a bfloat16 step moves a logit by 1e-3 of the scale
+    tol = TOL["bfloat16"] if dtype == "bfloat16" else 2e-3
+    assert worst <= tol * scale, f"largest difference {worst:.3e} at {where} (logit scale {scale:.3f})"
+
+
+def test_an_engine_that_is_dropped_gives_its_memory_back(model_dirs):
+    """The kernels' descriptors of the cache belong to the cache (not to a module), so nothing outlives the engine:
+    after `del`, the device's free memory is back where it was."""
+    import gc
+    import torch
+    from llmx_b200.engine import Engine, EngineOptions, StepEntry
+    d16, _, page = model_dirs["D"]
+    warm = Engine.from_dir(d16, EngineOptions(dtype="bfloat16", kv_tokens=64, page_size=page, max_requests=2))
+    warm.step([StepEntry("w", [1] * 40, [39])])            # kernels loaded, per-device buffers made
+    del warm
+    gc.collect()
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    before = torch.cuda.mem_get_info()[0]
+    engine = Engine.from_dir(d16, EngineOptions(dtype="bfloat16", kv_tokens=512 * 1024, page_size=page, max_requests=2))
+    held = engine.cache.storage_bytes()
+    assert held >= 256 << 20
+    engine.step([StepEntry("x", [1] * 40, [39])])
+    engine.step([StepEntry("x", [2], [0])])
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] <= before - held
+    del engine
+    gc.collect()
+    torch.cuda.empty_cache()
+    assert torch.cuda.mem_get_info()[0] >= before - (32 << 20)
+
+
+@pytest.mark.parametrize("name", ["D", "wide"])
+def test_invariant_schedules_give_a_row_the_same_bits_in_any_batch(model_dirs, wide_model_dir, name):
+    """`EngineOptions.invariant` on the bfloat16 path: kernels and schedules follow sizes alone, so a position's logits
+    are the same bits however the tokens were cut and whatever else was in the step (the reference's rule,
+    src/backends/backend.hpp:141-150).  Without it the bits move with the batch; the difference is bounded."""
+    import torch
+    from llmx_b200.engine import Engine, EngineOptions
+    if name == "wide":
+        folder, page, vocab, lengths = wide_model_dir, 16, WIDE["vocab_size"], [150, 70, 33, 2]
+    else:
+        folder, page, vocab, lengths = model_dirs[name][0], model_dirs[name][2], CONFIGS[name][0]["vocab_size"], [70, 9, 40, 33, 133]
+    requests = {f"i{i}": helpers.random_ids(vocab, n, seed=80 + i) for i, n in enumerate(lengths)}
+    runs = {}
+    for invariant in (True, False):
+        for make in (helpers.trace_whole, helpers.trace_portions, helpers.trace_mixed):
+            steps = make(requests)
+            engine = Engine.from_dir(folder, EngineOptions(dtype="bfloat16", kv_tokens=helpers.tokens_needed(steps), page_size=page,
+                                                           max_requests=4, invariant=invariant))
+            runs[(invariant, make.__name__)] = helpers.run_trace(engine, steps)
+            del engine
+    base = runs[(True, "trace_whole")]
+    worst, scale, where = helpers.compare(base, requests, folder, True)
+    assert worst <= TOL["bfloat16"] * scale
+    for make in ("trace_portions", "trace_mixed"):
+        other = runs[(True, make)]
+        assert all(np.array_equal(base[k], other[k]) for k in base), make
+    # the serving schedules: not the same bits, but close
+    moved = max(float(np.abs(runs[(False, "trace_mixed")][k] - runs[(False, "trace_whole")][k]).max()) for k in base)
+    assert moved <= 1e-2 * scale

@@ -221,3 +221,69 @@ def test_command_line(model_dirs, tmp_path):
     for bad in (["bench", "--r", "2"], ["bench", "--model", d16, "--size", "64"]):
         r = subprocess.run(exe + bad, capture_output=True, text=True, timeout=120)
         assert r.returncode == 2 and "usage:" in r.stderr, bad
+
+
+@pytest.fixture(scope="module")
+def baseline_dirs(tmp_path_factory):
+    """The two tiny configurations exactly as the benchmark's baseline names them (context 128 and 256, no rope
+    scaling): {name: (bfloat16 folder, float32 folder)}."""
+    import torch
+    from configs import BASELINE_A, BASELINE_B
+    from llmx_b200.config import Qwen3Config
+    from llmx_b200.weights import write_random_model
+    out = {}
+    for name, raw, seed in (("A", BASELINE_A, 0), ("B", BASELINE_B, 1)):
+        c = Qwen3Config.from_dict(raw)
+        assert c.max_position_embeddings == (128 if name == "A" else 256) and c.rope_scaling is None
+        d16, d32 = str(tmp_path_factory.mktemp(f"base_{name}_bf16")), str(tmp_path_factory.mktemp(f"base_{name}_f32"))
+        write_random_model(d16, c, seed, dtype=torch.bfloat16)
+        write_random_model(d32, c, seed, dtype=torch.float32)
+        out[name] = (d16, d32)
+    return out
+
+
+def test_baseline_tiny_a_workload(baseline_dirs):
+    """Tiny A to the letter, float32: three requests of 5, 17 and 33 tokens, 16 greedy tokens each, against the
+    plain implementation token by token."""
+    from configs import BASELINE_A
+    from llmx_b200.engine.generate import LLM
+    from llmx_b200.sampling import SamplingParams
+    folder = baseline_dirs["A"][1]
+    prompts = [helpers.random_ids(BASELINE_A["vocab_size"], n, seed=n) for n in (5, 17, 33)]
+    llm = LLM(folder, dtype="float32", kv_tokens=192, page_size=16, ubatch=24, max_seqs=3)
+    assert llm.engine.max_positions == 128
+    outs = llm.generate(prompts, SamplingParams(max_tokens=16, temp=0.0, top_k=0, top_p=1.0, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert len(o.tokens) == 16
+        _check_greedy(folder, p, o.tokens, False)
+    assert llm.engine.cache.used_pages() == [0]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_baseline_tiny_b_workload_on_both_storages(baseline_dirs, dtype):
+    """Tiny B to the letter: four requests of 1, 9, 40 and 70 tokens as mixed portions and decoded tokens, pages of 8,
+    temperature 0.8 with fixed seeds -- on the float32 check path and on bfloat16 storage.  The same seeds give the
+    same replies, and a request's reply is the one it gets alone.  On bfloat16 that needs schedules that do not follow
+    the batch (`invariant`): with the serving schedules a row's last bits move with the batch and a draw near a
+    boundary may fall the other way."""
+    from configs import BASELINE_B
+    from llmx_b200.engine.generate import LLM
+    from llmx_b200.sampling import SamplingParams
+    folder = baseline_dirs["B"][1 if dtype == "float32" else 0]
+    prompts = [helpers.random_ids(BASELINE_B["vocab_size"], n, seed=n) for n in (1, 9, 40, 70)]
+    params = [SamplingParams(max_tokens=12, temp=0.8, top_k=40, top_p=0.95, seed=100 + i, ignore_eos=True) for i in range(4)]
+    llm = LLM(folder, dtype=dtype, kv_tokens=512, page_size=8, ubatch=32, max_seqs=4, invariant=dtype == "bfloat16")
+    assert llm.engine.max_positions == 256
+    first = [o.tokens for o in llm.generate(prompts, params)]
+    again = [o.tokens for o in llm.generate(prompts, params)]
+    assert first == again and all(len(t) == 12 for t in first)
+    alone = [llm.generate([p], [q])[0].tokens for p, q in zip(prompts, params)]
+    assert alone == first
+    # every drawn token has weight in the plain implementation's distribution (it is among its top 40)
+    cfg, w = plain.load_folder(folder)
+    for p, reply in zip(prompts, first):
+        ids = list(p)
+        for t in reply:
+            logits = plain.forward(cfg, w, ids, act_round=plain.round_bf16 if dtype == "bfloat16" else None)[-1]
+            assert logits[t] >= np.sort(logits)[-41]
+            ids.append(t)

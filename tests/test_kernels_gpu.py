@@ -592,3 +592,26 @@ def test_gemm_tensor_core_finishes_heads(tile, m, heads, kv_heads, k, rotate, no
         if sl >= 0:
             assert np.abs(cache_np[sl // page, 0, :, sl % page] - kk[r]).max() <= tol * np.abs(kk).max()
             assert np.abs(cache_np[sl // page, 1, :, sl % page] - v[r]).max() <= tol * np.abs(v).max()
+
+
+def test_a_wait_that_nothing_satisfies_gives_up_and_is_reported():
+    """Every wait in the kernels is bounded; a wait that runs out records a code in the device's error word and the
+    block goes on to its end.  The self-test kernel (csrc/selftest.cu) waits a millisecond on a barrier nobody
+    arrives at: the kernel returns, the word holds the code, and `check_errors` raises (and clears the word)."""
+    import ctypes
+    from llmx_b200 import ops_tc, runtime
+    from llmx_b200.csrc import build
+    fn = build.load("selftest").llmx_wait_selftest
+    fn.argtypes = [ctypes.c_ulonglong, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+    fn.restype = ctypes.c_int
+    torch.cuda.synchronize()
+    ops_tc.check_errors()
+    word = runtime.error_word(DEV)
+    out = torch.zeros(2, dtype=torch.int32, device=DEV)
+    assert fn(1_000_000, word.data_ptr(), out.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()                                    # returns: nothing hangs
+    assert out.tolist() == [2, 2]                               # the wait gave up; a later wait of the block returned at once
+    with pytest.raises(runtime.KernelError, match="nobody arrives"):
+        ops_tc.check_errors()
+    ops_tc.check_errors()                                       # the word was cleared
+    assert fn(10, word.data_ptr(), out.data_ptr(), None) == 10001          # limits outside 1 us .. 0.1 s are refused

@@ -479,3 +479,246 @@ def test_layer_order_is_checked():
         Model(order=[LayerStep(0, 0), LayerStep(2, 0, write_cache=False)], **kw).cache_entry_specs()
     with pytest.raises(ValueError, match="without gaps"):
         Model(order=[LayerStep(0, 1)], **kw)
+
+
+def test_a_failed_step_leaves_a_state_mixers_state_as_it_was(toy):
+    """State is part of the step's transaction: a step reads a request's state slot and writes its spare, and only a
+    commit swaps them.  A step fails on the host after the state mixer of the toy model has run (the step's second
+    attention launch comes after it); the same step again gives what a clean engine gives."""
+    from llmx_b200 import runtime
+    from llmx_b200.engine import Engine, EngineOptions, StepEntry
+    cfg, folder, w = toy
+    ids = helpers.random_ids(cfg.vocab_size, 40, seed=3)
+    ref = _plain_toy(cfg, w, ids)
+    scale = float(np.abs(ref).max())
+    engine = Engine.from_dir(folder, EngineOptions(dtype="float32", kv_tokens=256, page_size=4, max_requests=2))
+    engine.step([StepEntry("s", ids[:17], [])])
+    slots = (engine.cache.live["s"].state_slot, engine.cache.live["s"].state_slot_out)
+    before = engine.cache.state_storage[1].clone()
+    runtime.fail_call("llmx_attention_plain", 2)
+    with pytest.raises(runtime.KernelError):
+        engine.step([StepEntry("s", ids[17:30], [12])])
+    runtime.fail_call(None)
+    rc = engine.cache.live["s"]
+    assert rc.length == 17 and (rc.state_slot, rc.state_slot_out) == slots
+    assert torch.equal(engine.cache.state_storage[1][rc.state_slot], before[rc.state_slot])     # the state it will read
+    engine.cache.check()
+    got = engine.step([StepEntry("s", ids[17:30], [12])]).float().cpu().numpy()[0]
+    assert np.abs(got - ref[29]).max() <= 1e-4 * scale
+    got = engine.step([StepEntry("s", ids[30:], [9])]).float().cpu().numpy()[0]
+    assert np.abs(got - ref[39]).max() <= 1e-4 * scale
+    with pytest.raises(RuntimeError, match="fixed-size state"):
+        engine.truncate("s", 10)
+    engine.end("s")
+    assert engine.cache.state_slots.free_slots == 4
+
+
+# ---------------------------------------------------------------------------------------------
+# A mixer of this file that is recordable and plans on the host, and a position encoding with a stream of its own.
+def _planned_toy_classes():
+    from llmx_b200.parts import Part
+    from llmx_b200.parts.base import PartPlan
+    from llmx_b200.weights import TensorSpec
+
+    class MeanPlan(PartPlan):
+        """The host's share of `HistoryMeanMixer`: for every request 1 / (tokens it holds after the step), as
+        fixed-point ints, and the row count of the largest request (a launch decision: in a recorded step it follows
+        the recording's shape alone)."""
+
+        def __init__(self, shape):
+            self.counts = list(shape.counts)
+            self.ints = len(self.counts) + 1
+            self.recorded = shape.room > 0
+            self.fills = 0
+
+        def fill(self, histories, out):
+            self.fills += 1
+            out[:len(self.counts)] = [int(round(65536.0 / (h + c))) for h, c in zip(histories, self.counts)]
+            out[len(self.counts)] = max(self.counts)
+
+    class HistoryMeanMixer(Part):
+        """residual[rows of r] += scale[r] * (h W^T), scale[r] = 1 / (length of r after the step), read on the
+        device from the ints its plan put into the step's metadata: tensor ops only, so a step can be recorded."""
+        recordable = True
+        plans = []
+
+        def __init__(self, hidden):
+            self.hidden = hidden
+
+        def cache_spec(self):
+            return None
+
+        def tensor_specs(self):
+            return {"proj.weight": TensorSpec((self.hidden, self.hidden))}
+
+        def load(self, tensors, precision):
+            super().load(tensors, precision)
+            self.weight = tensors["proj.weight"].float()
+
+        def plan_step(self, shape):
+            plan = MeanPlan(shape)
+            HistoryMeanMixer.plans.append(plan)
+            return plan
+
+        def forward(self, h, step, cache_entry, residual, write_cache=True):
+            ints = step.plan_ints(self)
+            assert ints is not None and ints.numel() == step.requests + 1
+            scale = ints[:step.requests].float() / 65536.0
+            residual += (h.float() @ self.weight.T) * scale[step.row_request.long()][:, None]
+
+    class SecondStreamBias(Part):
+        """A feed-forward that adds bias * (the row's position in the step's second position stream)."""
+        position_streams = 2
+
+        def __init__(self, hidden):
+            self.hidden = hidden
+
+        def tensor_specs(self):
+            return {"bias": TensorSpec((self.hidden,), "vector", std=0.05)}
+
+        def load(self, tensors, precision):
+            super().load(tensors, precision)
+            self.bias = tensors["bias"].float()
+
+        def forward(self, h, step, residual):
+            residual += step.position_streams[1].float()[:, None] * self.bias[None, :] * 0.01
+
+    return HistoryMeanMixer, SecondStreamBias
+
+
+def test_a_recordable_mixer_with_a_plan_of_its_own_and_a_second_position_stream(tmp_path):
+    """An architecture of this file whose mixer plans on the host (`plan_step`) and reads its plan's ints on the
+    device, and whose feed-forward reads a second position stream the requests bring: registered, built, stepped
+    plainly and from recordings, with nothing changed under llmx_b200/engine/ (which knows no part's plan)."""
+    from llmx_b200.engine import Engine, EngineOptions, StepEntry
+    from llmx_b200.models import LayerStep, Model
+    from llmx_b200.parts import LogitsHead, PreNormBlock, RMSNorm, TokenEmbedding
+    from llmx_b200.registry import register_architecture, unregister_architecture
+    from llmx_b200.weights import RandomSource, write_safetensors
+    HistoryMeanMixer, SecondStreamBias = _planned_toy_classes()
+    E, V, eps = 48, 90, 1e-5
+
+    @dataclass(frozen=True)
+    class Cfg:
+        max_position_embeddings: int = 256
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls()
+
+        def to_dict(self):
+            return dict(architectures=["PlannedToy"], model_type="planned_toy")
+
+    def build(cfg):
+        blocks = [PreNormBlock(RMSNorm(E, eps), HistoryMeanMixer(E), RMSNorm(E, eps), SecondStreamBias(E)) for _ in range(2)]
+        emb = TokenEmbedding(V, E)
+        return Model(embedding=emb, blocks=blocks, head=LogitsHead(RMSNorm(E, eps), V, E, tied_to=emb),
+                     order=[LayerStep(0), LayerStep(1), LayerStep(0)], vocab_size=V, max_positions=256)
+
+    register_architecture(["PlannedToy", "planned_toy"], Cfg, build)
+    try:
+        (tmp_path / "config.json").write_text(json.dumps(Cfg().to_dict()))
+        src = RandomSource(build(Cfg()).tensor_specs(), 5, dtype=torch.float32, skip_optional=True)
+        tensors = {n: src.tensor(n) * (6.0 if n.endswith("proj.weight") else 1.0) for n in src.names()}
+        write_safetensors(str(tmp_path / "model.safetensors"), tensors)
+        w = {n: t.numpy() for n, t in tensors.items()}
+        engine = Engine.from_dir(str(tmp_path), EngineOptions(dtype="float32", kv_tokens=64, page_size=16, max_requests=3, record_after=1))
+        assert engine.model.recordable and engine.model.native is None and engine.position_streams == 2 and not engine.cache.groups
+
+        def plain_rows(ids, second, start, n):
+            """The model on rows start .. start + n of a request: no token mixes with another, only the lengths count."""
+            x = plain.embedding(w["model.embed_tokens.weight"], ids[start:start + n])
+            length_after = start + n
+            for b in (0, 1, 0):
+                pre = f"model.layers.{b}."
+                h = plain.rms_norm(x, w[pre + "input_layernorm.weight"], eps)
+                x = x + (h @ w[pre + "self_attn.proj.weight"].T) * np.float32(round(65536.0 / length_after) / 65536.0)
+                x = x + np.asarray(second[start:start + n], dtype=np.float32)[:, None] * w[pre + "mlp.bias"][None, :] * np.float32(0.01)
+            return plain.rms_norm(x, w["model.norm.weight"], eps) @ w["model.embed_tokens.weight"].T
+
+        reqs = {r: (helpers.random_ids(V, 60, seed=s), helpers.random_ids(97, 60, seed=50 + s)) for r, s in (("p", 1), ("q", 2))}
+        HistoryMeanMixer.plans.clear()
+        for run in range(3):                     # the same shapes three times: plain, then recorded, then replayed
+            at = {r: 0 for r in reqs}
+            for counts in ((7, 3), (2, 1), (2, 1), (13, 5), (2, 1)):
+                entries = []
+                for (r, (ids, second)), n in zip(reqs.items(), counts):
+                    entries.append(StepEntry(r, ids[at[r]:at[r] + n], list(range(n)), positions=[second[at[r]:at[r] + n]]))
+                logits = engine.step(entries, record=True).float().cpu().numpy()
+                k = 0
+                for (r, (ids, second)), n in zip(reqs.items(), counts):
+                    ref = plain_rows(ids, second, at[r], n)
+                    assert np.abs(logits[k:k + n] - ref).max() <= 1e-4 * np.abs(ref).max(), (run, counts, r)
+                    k += n
+                    at[r] += n
+            for r in reqs:
+                engine.end(r)
+        assert len(engine.step_recordings) == 3                                  # three shapes, each recorded once
+        recorded = [p for p in HistoryMeanMixer.plans if p.recorded]
+        assert len(recorded) == 3 and all(p.fills >= 2 for p in recorded)        # planned once, filled every run
+        with pytest.raises(Exception, match="positions must be 1 lists"):
+            engine.step([StepEntry("z", [1, 2], [1], positions=[[5]])])
+    finally:
+        unregister_architecture(["PlannedToy", "planned_toy"])
+
+
+@pytest.mark.parametrize("head_dim,heads,kv_heads", [(64, 6, 2), (128, 8, 2), (128, 10, 2)])
+def test_windowed_attention_in_bfloat16_with_pages_given_back_and_taken_again(head_dim, heads, kv_heads):
+    """The tiled bfloat16 kernels under a window, through the cache manager: two requests take turns with portions
+    that cross the window's edge and with decoded tokens, over a pool so small that the pages one gives back (its
+    window has passed them; its block table then holds -1 there) are the pages the other takes.  The tiled prefill
+    kernels start a stage below the window's first key, where those entries lie.  Every row against the plain
+    mixer with the same window."""
+    from llmx_b200 import ops_tc
+    from llmx_b200.cache import CacheManager, KVSpec
+    from llmx_b200.engine.batch import step_from_requests
+    from llmx_b200.parts import Attention, Precision, RotaryEmbedding
+    p = Precision.of("bfloat16")
+    E, window, page = 64, 40, 16
+    part = Attention(E, heads, kv_heads, head_dim, RotaryEmbedding(head_dim, 10000.0), qk_norm_eps=1e-6, window=window)
+    g = torch.Generator().manual_seed(4)
+    w = {n: (torch.randn(s.shape, generator=g) * (0.3 if s.kind == "matrix" else 0.1) + (0 if s.kind == "matrix" else 1)).to(p.act if s.kind == "matrix" else torch.float32)
+         for n, s in part.tensor_specs().items()}
+    part.load({n: t.to(DEV) for n, t in w.items()}, p)
+    part.prepare(512, DEV)
+    lengths = {"u": 230, "v": 190}
+    hs = {r: torch.randn(n, E, generator=g).to(p.act) for r, n in lengths.items()}
+    # a windowed request holds its window, the page it starts in and the portion being written: 2 x that, no more
+    cache = CacheManager([KVSpec(kv_heads, head_dim, window)], page, 2 * (window + 2 * page + 48 + page), 2, kv_dtype=p.act, device=DEV)
+    rcs = {r: cache.new_request(r) for r in lengths}
+    got = {r: torch.zeros(n, E, device=DEV) for r, n in lengths.items()}
+    at = {r: 0 for r in lengths}
+    seen_released, given_back, taken_again = False, set(), False
+    portions = {"u": [45, 1, 1, 37, 2, 48, 1, 3, 33, 1, 17, 41], "v": [1, 48, 2, 1, 29, 1, 40, 5, 1, 19, 43]}
+    k = 0
+    while any(at[r] < lengths[r] for r in lengths):
+        who = [r for r in lengths if at[r] < lengths[r] and (k % 3 != 2 or r == "u")]
+        counts = [min(portions[r][(k // 2) % len(portions[r])], lengths[r] - at[r]) for r in who]
+        for r, n in zip(who, counts):
+            rcs[r].prepare(n)
+        held = {pg for r in who for pg in rcs[r].tables[0].pages if pg >= 0}
+        taken_again = taken_again or bool(held & given_back)
+        seen_released = seen_released or any(-1 in rcs[r].tables[0].pages for r in who)
+        step = step_from_requests(cache, [rcs[r] for r in who], counts, DEV, parts=[part])
+        h = torch.cat([hs[r][at[r]:at[r] + n] for r, n in zip(who, counts)]).to(DEV)
+        res = torch.zeros(h.shape[0], E, device=DEV)
+        part.forward(h, step, 0, res)
+        a = 0
+        for r, n in zip(who, counts):
+            got[r][at[r]:at[r] + n] = res[a:a + n]
+            a += n
+            before = {pg for pg in rcs[r].tables[0].pages if pg >= 0}
+            rcs[r].commit()
+            given_back |= before - {pg for pg in rcs[r].tables[0].pages if pg >= 0}
+            at[r] += n
+        cache.check()
+        k += 1
+    torch.cuda.synchronize()
+    ops_tc.check_errors()
+    assert seen_released and taken_again, "the pool was not tight enough: no page was given back and taken again"
+    cfg = dict(num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim, rms_norm_eps=1e-6)
+    wf = {"p." + n: t.float().numpy() for n, t in w.items()}
+    for r, n in lengths.items():
+        cos, sin = plain.rope_tables(n, head_dim, 10000.0)
+        ref = plain.attention_block(hs[r].float().numpy(), wf, "p.", cfg, cos, sin, act_round=plain.round_bf16, window=window)
+        assert np.abs(got[r].cpu().numpy() - ref).max() <= 3e-2 * np.abs(ref).max(), r

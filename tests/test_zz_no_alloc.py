@@ -71,10 +71,11 @@ def test_static_entry_point_matches_the_ordinary_one_on_two_calls_in_a_row():
             # device's free memory exactly as it found it: were the entry point to allocate, even through a
             # pool, cudaMemGetInfo would show it.  Inputs and output exist already; only the call is repeated.
             out_again = torch.empty_like(q)
+            cmap = ops_attn.cache_map(cache)          # held until the call returns: the launch reads the descriptor from host memory
             torch.cuda.synchronize()
             free_before, _ = torch.cuda.mem_get_info()
             reserved_before = torch.cuda.memory_reserved()
-            status = fn(ctypes.c_void_p(ops_attn.cache_map(cache).address), q.data_ptr(), out_again.data_ptr(),
+            status = fn(ctypes.c_void_p(cmap.address), q.data_ptr(), out_again.data_ptr(),
                         _req_list.data_ptr(), step.requests, step.row_start.data_ptr(), step.row_count.data_ptr(),
                         step.history.data_ptr(), group.block_tables.data_ptr(), group.block_tables.shape[1], q.shape[0],
                         heads, kv_heads, head_dim, cache.shape[3], 0, 1.0 / math.sqrt(head_dim), splits, chunk,
