@@ -655,7 +655,7 @@ def test_a_recordable_mixer_with_a_plan_of_its_own_and_a_second_position_stream(
                 engine.end(r)
         assert len(engine.step_recordings) == 3                                  # three shapes, each recorded once
         recorded = [p for p in HistoryMeanMixer.plans if p.recorded]
-        assert len(recorded) == 3 and all(p.fills >= 2 for p in recorded)        # planned once, filled every run
+        assert len(recorded) == 6 and all(p.fills >= 2 for p in recorded)        # two mixers, three shapes: planned once each, filled every run
         with pytest.raises(Exception, match="positions must be 1 lists"):
             engine.step([StepEntry("z", [1, 2], [1], positions=[[5]])])
     finally:
@@ -692,7 +692,7 @@ def test_windowed_attention_in_bfloat16_with_pages_given_back_and_taken_again(he
     portions = {"u": [45, 1, 1, 37, 2, 48, 1, 3, 33, 1, 17, 41], "v": [1, 48, 2, 1, 29, 1, 40, 5, 1, 19, 43]}
     k = 0
     while any(at[r] < lengths[r] for r in lengths):
-        who = [r for r in lengths if at[r] < lengths[r] and (k % 3 != 2 or r == "u")]
+        who = [r for r in lengths if at[r] < lengths[r] and (k % 3 != 2 or r == "u")] or [r for r in lengths if at[r] < lengths[r]]
         counts = [min(portions[r][(k // 2) % len(portions[r])], lengths[r] - at[r]) for r in who]
         for r, n in zip(who, counts):
             rcs[r].prepare(n)
