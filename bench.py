@@ -15,7 +15,11 @@ tokens per request.  One JSON line is printed:
                measured bf16 peak its flops reach
   roofline     the bytes a decode step must read (every weight once, the cache of the live requests)
                divided by its time, against the measured copy bandwidth
-  points       decode tokens a second at batch 1 and batch 64
+  points       decode tokens a second at batch 1 and batch 64 (mean and sd over three timed regions, and the fraction
+               of the copy bandwidth), then the architecture's other published sizes: Qwen3-0.6B (decode at batch 64,
+               context 4,096; a 2,048-token prompt) and Qwen3-32B (decode at batch 1, 8, 32, context 4,096; a
+               2,048-token prompt), each with its roofline fraction
+  repeats      mean and sd of the headline over three timed regions of K steps (`value` is the first)
 
 For `value` and `points` the histories of the decoding requests are synthetic cache contents (pages taken and
 filled with random values): what a decode step costs depends on how much it reads, not on what it reads.
@@ -141,6 +145,8 @@ def main() -> int:
     if args.warmup < 3:
         args.warmup = 3
 
+    import gc
+    import statistics
     import torch
     from llmx_b200 import ops, ops_tc
     from llmx_b200.config import Qwen3Config
@@ -149,173 +155,220 @@ def main() -> int:
     from llmx_b200.sampling import RequestSampling, SamplingParams, sample
 
     pk = peaks()
-    raw = dict(QWEN3_8B)
-    raw.update(SIZES[args.size])
-    model_layers = raw["num_hidden_layers"]
-    if args.layers is None:
-        args.layers = model_layers
-    raw["num_hidden_layers"] = args.layers
-    cfg = Qwen3Config.from_dict(raw)
     page = 16
-    max_batch = max(args.batch, 1 if args.no_points else 64)
-    head_start = -(-args.context // 2048) * (args.batch - 1)          # see run_generate
-    per_request = -(-(args.context + args.steps + max(args.warmup, 8) + head_start + 64) // page) * page
     torch.cuda.set_device(0)
-    if args.only == "prefill":
-        max_batch = 1
-    # What fits: the weights and the cache of `max_batch` requests must leave room for the steps' buffers.  The
-    # batch 64 point is given up first (said in the line), then the run is refused.
-    kv_bytes_token = 2 * args.layers * cfg.num_key_value_heads * cfg.head_dim * 2
-    weights = 2 * (args.layers * (cfg.hidden_size * (cfg.q_width + 2 * cfg.kv_width) + cfg.q_width * cfg.hidden_size
-                                  + 3 * cfg.hidden_size * cfg.intermediate_size)
-                   + cfg.vocab_size * cfg.hidden_size * (1 if cfg.tie_word_embeddings else 2))
-    room = torch.cuda.get_device_properties(0).total_memory * 0.9 - weights - (8 << 30)
-    if max_batch > args.batch and max_batch * per_request * kv_bytes_token > room:
-        max_batch, args.no_points = args.batch, True
-        print(f"note: the batch 64 point does not fit beside {weights / 1e9:.0f} GB of weights and is left out", file=sys.stderr)
-    if max_batch * per_request * kv_bytes_token > room and args.only != "prefill":
-        print(f"bench: a cache of {max_batch} x {per_request} tokens ({max_batch * per_request * kv_bytes_token / 1e9:.0f} GB) does not "
-              f"fit beside the weights ({weights / 1e9:.0f} GB); give a smaller --batch, --context or --layers", file=sys.stderr)
-        return 1
-    kv_tokens = max(max_batch * per_request, args.prefill_tokens + page) if args.only != "prefill" else args.prefill_tokens + page
-    engine = Engine.from_config(cfg, seed=0, options=EngineOptions(dtype="bfloat16", kv_tokens=kv_tokens,
-                                                                   page_size=page, max_requests=max_batch,
-                                                                   record_after=2))
-    model = engine.model
-    gen = torch.Generator(device="cuda")
-    gen.manual_seed(1)
-    for g in engine.cache.groups:          # synthetic histories: random keys and values
-        for layer in range(g.storage.shape[0]):
-            g.storage[layer].normal_(0.0, 1.0, generator=gen)
     host_gen = torch.Generator()
     host_gen.manual_seed(2)
 
-    def ids(n):
-        return torch.randint(0, cfg.vocab_size, (n,), generator=host_gen).tolist()
+    class Bench:
+        """One model size on the device: its engine, and the timed runs over it."""
 
-    # ---- bytes a decode step must read ------------------------------------------------------------
-    E, F, Q, KV, V, L = cfg.hidden_size, cfg.intermediate_size, cfg.q_width, cfg.kv_width, cfg.vocab_size, args.layers
-    weight_bytes = 2 * (L * ((Q + 2 * KV) * E + E * Q + 2 * F * E + E * F) + V * E) + 4 * (L * (2 * E + 2 * cfg.head_dim) + E)
-    # (a tied head reads the embedding table as its weight: the same V * E bytes)
-    kv_bytes_per_token = L * 2 * KV * 2
+        def __init__(self, size, layers, batches, context, prefill_tokens, steps, warmup):
+            raw = dict(QWEN3_8B)
+            raw.update(SIZES[size])
+            self.size, self.model_layers = size, raw["num_hidden_layers"]
+            self.layers = layers if layers is not None else self.model_layers
+            raw["num_hidden_layers"] = self.layers
+            self.cfg = cfg = Qwen3Config.from_dict(raw)
+            self.context, self.prefill_tokens = context, prefill_tokens
+            E, F, Q, KV, V, L = cfg.hidden_size, cfg.intermediate_size, cfg.q_width, cfg.kv_width, cfg.vocab_size, self.layers
+            # bytes a decode step must read: every weight once (a tied head reads the embedding table as its weight: the
+            # same V * E bytes), the batch's embedding rows and the cache of the live requests
+            self.weight_bytes = 2 * (L * ((Q + 2 * KV) * E + E * Q + 2 * F * E + E * F) + V * E) + 4 * (L * (2 * E + 2 * cfg.head_dim) + E)
+            self.kv_bytes_per_token = L * 2 * KV * 2
+            resident = 2 * (L * (E * (Q + 2 * KV) + Q * E + 3 * E * F) + V * E * (1 if cfg.tie_word_embeddings else 2))
+            head_start = -(-context // 2048) * (max(batches) - 1)          # see run_generate
+            per_request = -(-(context + steps + max(warmup, 8) + head_start + 64) // page) * page
+            room = torch.cuda.get_device_properties(0).total_memory * 0.9 - resident - (8 << 30)
+            self.batches = [b for b in batches if b * per_request * self.kv_bytes_per_token <= room]
+            self.left_out = [b for b in batches if b not in self.batches]
+            if not self.batches and batches:
+                raise RuntimeError(f"a cache of {min(batches)} x {per_request} tokens does not fit beside the weights "
+                                   f"({resident / 1e9:.0f} GB); give a smaller --batch, --context or --layers")
+            max_batch = max(self.batches, default=1)
+            kv_tokens = max(max_batch * per_request if self.batches else 0, prefill_tokens + page)
+            self.engine = Engine.from_config(cfg, seed=0, options=EngineOptions(dtype="bfloat16", kv_tokens=kv_tokens, page_size=page,
+                                                                                max_requests=max_batch, record_after=2))
+            gen = torch.Generator(device="cuda")
+            gen.manual_seed(1)
+            for g in self.engine.cache.groups:          # synthetic histories: random keys and values
+                for layer in range(g.storage.shape[0]):
+                    g.storage[layer].normal_(0.0, 1.0, generator=gen)
 
-    def decode_bytes(batch, context):
-        return weight_bytes + batch * E * 2 + batch * context * kv_bytes_per_token
+        def close(self):
+            self.engine = None
+            gc.collect()
+            torch.cuda.synchronize()
+            torch.cuda.empty_cache()
 
-    def run_decode(batch, steps, warmup, e2e):
-        """Tokens a second and ms a step for `batch` requests at `context` tokens each."""
-        rids = [("bench", batch, i) for i in range(batch)]
-        for rid in rids:                                    # take pages for the history without running it
-            rc = engine.cache.new_request(rid)
-            rc.prepare(args.context)
-            rc.commit()
-        session = DecodeSession(engine, rids)
-        tokens = ids(batch)
-        states = [RequestSampling(SamplingParams(temp=0.0, top_k=0, top_p=1.0)) for _ in rids]
-        launches0 = ops.launch_count()
-        try:
-            if e2e:
-                for _ in range(warmup):
-                    tokens = sample(session.step(tokens), states)
-                torch.cuda.synchronize()
-                t0 = time.perf_counter()
-                for _ in range(steps):
-                    tokens = sample(session.step(tokens), states)     # host ids in, host ids out
-                torch.cuda.synchronize()
-                ms = (time.perf_counter() - t0) * 1e3 / steps
-            else:
+        def ids(self, n):
+            return torch.randint(0, self.cfg.vocab_size, (n,), generator=host_gen).tolist()
+
+        def decode_bytes(self, batch):
+            return self.weight_bytes + batch * self.cfg.hidden_size * 2 + batch * self.context * self.kv_bytes_per_token
+
+        def hbm_frac(self, batch, ms):
+            return self.decode_bytes(batch) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]
+
+        def run_decode(self, batch, steps, warmup, repeats=1):
+            """ms a step of `repeats` timed regions of `steps` decode steps each, for `batch` requests at `context`
+            tokens; the launches of the first region; the bytes a step copies to the device."""
+            engine = self.engine
+            rids = [("bench", batch, i) for i in range(batch)]
+            for rid in rids:                                    # take pages for the history without running it
+                rc = engine.cache.new_request(rid)
+                rc.prepare(self.context)
+                rc.commit()
+            session = DecodeSession(engine, rids)
+            tokens = self.ids(batch)
+            try:
                 for _ in range(warmup):
                     session.step(tokens)
                 torch.cuda.synchronize()
-                launches0 = ops.launch_count()
+                times, launches = [], None
+                for _ in range(repeats):
+                    launches0 = ops.launch_count()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    for _ in range(steps):
+                        session.step(tokens)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    times.append(e0.elapsed_time(e1) / steps)
+                    launches = launches if launches is not None else ops.launch_count() - launches0
+                h2d = session.h2d_bytes_per_step
+            finally:
+                session.close()
+                for rid in rids:
+                    engine.end(rid)
+            return times, launches, h2d
+
+        def run_generate(self, batch, steps, warmup):
+            """The same decode rate through the Python entry point, `LLM.generate`: host token ids in (prompts of
+            `context` tokens, which it prefills itself), sampled ids out.  Every step copies its metadata from pinned
+            host memory and reads the drawn ids back; the clock runs between the callbacks of two tokens of the
+            batch's last request, `steps` steps apart, after `warmup` decode steps."""
+            from llmx_b200.engine.generate import LLM
+            llm = LLM(self.engine, ubatch=2048, max_seqs=batch)
+            prompts = [self.ids(self.context) for _ in range(batch)]
+            seen, marks = [0], {}
+
+            def on_token(i, token):
+                if i == batch - 1:
+                    seen[0] += 1
+                    if seen[0] in (warmup + 1, warmup + 1 + steps):
+                        marks[seen[0]] = time.perf_counter()
+            # The requests' prompts end one after the other, so the first request decodes `head_start` steps before
+            # the last one starts; all must still be decoding when the last one's timed tokens are drawn.
+            head_start = -(-self.context // 2048) * (batch - 1)
+            llm.generate(prompts, SamplingParams(max_tokens=head_start + warmup + steps + 4, temp=0.0, top_k=0, top_p=1.0,
+                                                 ignore_eos=True), on_token)
+            ms = (marks[warmup + 1 + steps] - marks[warmup + 1]) * 1e3 / steps
+            h2d = max((rec.total * 4 for (b, _), rec in self.engine.decode_recordings.items() if b == batch), default=0)
+            return batch * 1e3 / ms, ms, h2d
+
+        def run_prefill(self, reps, warmup):
+            """(tokens a second, ms: mean and sd over `reps` prompts from an empty cache, fraction of the bf16 peak)."""
+            cfg, T, L = self.cfg, self.prefill_tokens, self.layers
+            E, F, Q, KV, V = cfg.hidden_size, cfg.intermediate_size, cfg.q_width, cfg.kv_width, cfg.vocab_size
+            prompt = self.ids(T)
+            times = []
+            for i in range(warmup + reps):
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
-                for _ in range(steps):
-                    session.step(tokens)
+                self.engine.step([StepEntry("prefill", prompt, [T - 1])], record=True)
                 e1.record()
                 torch.cuda.synchronize()
-                ms = e0.elapsed_time(e1) / steps
-            launches = ops.launch_count() - launches0
-            h2d = session.h2d_bytes_per_step
-        finally:
-            session.close()
-            for rid in rids:
-                engine.end(rid)
-        return batch * 1e3 / ms, ms, launches, h2d
+                self.engine.end("prefill")
+                if i >= warmup:
+                    times.append(e0.elapsed_time(e1))
+            ms = sum(times) / len(times)
+            sd = statistics.stdev(times) if len(times) > 1 else 0.0
+            flops = L * (2 * T * E * (Q + 2 * KV) + 2 * T * Q * E + 2 * T * E * 2 * F + 2 * T * F * E) \
+                + L * 2 * cfg.num_attention_heads * cfg.head_dim * T * T + 2 * V * E
+            return T * 1e3 / ms, ms, sd, flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops"]
 
-    def run_generate(batch, steps, warmup):
-        """The same decode rate through the Python entry point, `LLM.generate`: host token ids in (prompts of
-        `context` tokens, which it prefills itself), sampled ids out.  Every step copies its metadata from pinned
-        host memory and reads the drawn ids back; the clock runs between the callbacks of two tokens of the
-        batch's last request, `steps` steps apart, after `warmup` decode steps."""
-        from llmx_b200.engine.generate import LLM
-        llm = LLM(engine, ubatch=2048, max_seqs=batch)
-        prompts = [ids(args.context) for _ in range(batch)]
-        seen, marks = [0], {}
-
-        def on_token(i, token):
-            if i == batch - 1:
-                seen[0] += 1
-                if seen[0] in (warmup + 1, warmup + 1 + steps):
-                    marks[seen[0]] = time.perf_counter()
-        # The requests' prompts end one after the other, so the first request decodes `head_start` steps before
-        # the last one starts; all must still be decoding when the last one's timed tokens are drawn.
-        head_start = -(-args.context // 2048) * (batch - 1)
-        llm.generate(prompts, SamplingParams(max_tokens=head_start + warmup + steps + 4, temp=0.0, top_k=0, top_p=1.0,
-                                             ignore_eos=True), on_token)
-        ms = (marks[warmup + 1 + steps] - marks[warmup + 1]) * 1e3 / steps
-        h2d = max((rec.total * 4 for (b, _), rec in engine.decode_recordings.items() if b == batch), default=0)
-        return batch * 1e3 / ms, ms, h2d
-
-    def run_prefill(tokens_n, reps, warmup):
-        prompt = ids(tokens_n)
-        times = []
-        for i in range(warmup + reps):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            engine.step([StepEntry("prefill", prompt, [tokens_n - 1])], record=True)
-            e1.record()
-            torch.cuda.synchronize()
-            engine.end("prefill")
-            if i >= warmup:
-                times.append(e0.elapsed_time(e1))
-        ms = sum(times) / len(times)
-        T = tokens_n
-        flops = L * (2 * T * E * (Q + 2 * KV) + 2 * T * Q * E + 2 * T * E * 2 * F + 2 * T * F * E) \
-            + L * 2 * cfg.num_attention_heads * cfg.head_dim * T * T + 2 * V * E
-        return T * 1e3 / ms, ms, flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops"]
+    def rate(batch, ms_list):
+        """(mean tokens a second, its standard deviation over the repeats)."""
+        rates = [batch * 1e3 / ms for ms in ms_list]
+        return sum(rates) / len(rates), (statistics.stdev(rates) if len(rates) > 1 else 0.0)
 
     if args.only == "prefill":
-        pf_value, pf_ms, pf_frac = run_prefill(args.prefill_tokens, 3, 3)
+        b = Bench(args.size, args.layers, [], args.context, args.prefill_tokens, args.steps, args.warmup)
+        pf_value, pf_ms, pf_sd, pf_frac = b.run_prefill(3, 3)
         print(json.dumps({"only": "prefill", "value": round(pf_value, 1), "ms": round(pf_ms, 3), "frac": round(pf_frac, 4),
-                          "layers": args.layers}))
+                          "layers": b.layers}))
         return 0
     if args.only == "decode":
-        value, ms, launches, _ = run_decode(args.batch, args.steps, args.warmup, e2e=False)
-        print(json.dumps({"only": "decode", "value": round(value, 1), "ms_per_step": round(ms, 4), "batch": args.batch,
-                          "context": args.context, "layers": args.layers, "gpu_launches": launches}))
+        b = Bench(args.size, args.layers, [args.batch], args.context, args.prefill_tokens, args.steps, args.warmup)
+        times, launches, _ = b.run_decode(args.batch, args.steps, args.warmup)
+        print(json.dumps({"only": "decode", "value": round(args.batch * 1e3 / times[0], 1), "ms_per_step": round(times[0], 4),
+                          "batch": args.batch, "context": args.context, "layers": b.layers, "gpu_launches": launches}))
         return 0
     clocks = ClockSampler()          # clocks and throttle reasons over every timed region below
     clocks.start()
-    value, ms, launches, _ = run_decode(args.batch, args.steps, args.warmup, e2e=False)
-    e2e_value, e2e_ms, h2d = run_generate(args.batch, args.steps, max(args.warmup, 8))
-    pf_value, pf_ms, pf_frac = run_prefill(args.prefill_tokens, 3, 3)
+    REPEATS = 3                      # timed regions of K steps each; the headline is the first, mean and sd go beside it
+    main_batches = [args.batch] + ([] if args.no_points else [b for b in (1, 64) if b != args.batch])
+    try:
+        bench = Bench(args.size, args.layers, main_batches, args.context, args.prefill_tokens, args.steps, args.warmup)
+    except RuntimeError as e:
+        print(f"bench: {e}", file=sys.stderr)
+        return 1
+    if args.batch not in bench.batches:
+        print(f"bench: batch {args.batch} at context {args.context} does not fit; give a smaller --batch, --context or --layers", file=sys.stderr)
+        return 1
+    for left in bench.left_out:
+        print(f"note: the batch {left} point does not fit beside the weights and is left out", file=sys.stderr)
+    cfg = bench.cfg
+    times, launches, _ = bench.run_decode(args.batch, args.steps, args.warmup, REPEATS)
+    ms = times[0]
+    value = args.batch * 1e3 / ms
+    mean_rate, sd_rate = rate(args.batch, times)
+    e2e_value, e2e_ms, h2d = bench.run_generate(args.batch, args.steps, max(args.warmup, 8))
+    pf_value, pf_ms, pf_sd, pf_frac = bench.run_prefill(3, 3)
     points = {}
-    if not args.no_points:
-        for name, b, k in (("decode_b1", 1, args.steps), ("decode_b64", 64, max(args.steps // 2, 8))):
-            v, step_ms, _, _ = run_decode(b, k, args.warmup, e2e=False)
-            points[name] = round(v, 1)
-            # the same roofline as the headline's: bytes the step must read over its time, against the copy bandwidth
-            points[name + "_hbm_frac"] = round(decode_bytes(b, args.context) / (step_ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+    for b in bench.batches:
+        if b == args.batch:
+            continue
+        t, _, _ = bench.run_decode(b, args.steps if b < 64 else max(args.steps // 2, 8), args.warmup, REPEATS)
+        m, sd = rate(b, t)
+        points[f"decode_b{b}"] = round(m, 1)
+        points[f"decode_b{b}_sd"] = round(sd, 2)
+        # the same roofline as the headline's: bytes the step must read over its time, against the copy bandwidth
+        points[f"decode_b{b}_hbm_frac"] = round(bench.hbm_frac(b, b * 1e3 / m), 4)
+    achieved = bench.decode_bytes(args.batch) / (ms * 1e-3) / 1e9
+    model_layers, layers = bench.model_layers, bench.layers
+    E, F, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    bench.close()
+    # The other published sizes of the architecture (other widths, depths and head counts), each at its own context:
+    # the small one is bound by launches and the cache, the large one by 64 GB of weights.
+    if not args.no_points and args.size == "8b" and args.layers is None:
+        for tag, size, batches, ctx in (("q0_6b", "0.6b", [64], 4096), ("q32b", "32b", [1, 8, 32], 4096)):
+            try:
+                other = Bench(size, None, batches, ctx, 2048, args.steps, args.warmup)
+            except RuntimeError as e:
+                print(f"note: {size}: {e}", file=sys.stderr)
+                continue
+            for b in other.batches:
+                t, _, _ = other.run_decode(b, max(args.steps // 2, 8), args.warmup, REPEATS)
+                m, sd = rate(b, t)
+                points[f"{tag}_decode_b{b}_c{ctx}"] = round(m, 1)
+                points[f"{tag}_decode_b{b}_c{ctx}_sd"] = round(sd, 2)
+                points[f"{tag}_decode_b{b}_c{ctx}_hbm_frac"] = round(other.hbm_frac(b, b * 1e3 / m), 4)
+            v, p_ms, p_sd, frac = other.run_prefill(3, 3)
+            points[f"{tag}_prefill_2048"] = round(v, 1)
+            points[f"{tag}_prefill_2048_ms_sd"] = round(p_sd, 3)
+            points[f"{tag}_prefill_2048_frac"] = round(frac, 4)
+            other.close()
     clock_record = clocks.stop()
     ops_tc.check_errors()
-    achieved = decode_bytes(args.batch, args.context) / (ms * 1e-3) / 1e9
     line = {
         "metric": f"decode tok/s at batch {args.batch}, context {args.context} (Qwen3-{args.size.upper()} sizes, bf16, random weights)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic", "impl": "ours",
-        "config": {"model": f"Qwen3-{args.size.upper()} sizes, random weights", "layers": args.layers, "model_layers": model_layers,
+        "repeats": {"runs": REPEATS, "mean": round(mean_rate, 1), "sd": round(sd_rate, 2)},
+        "config": {"model": f"Qwen3-{args.size.upper()} sizes, random weights", "layers": layers, "model_layers": model_layers,
                    "hidden": E, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": F, "vocab": V, "global_batch": args.batch,
                    "seq_len": args.context, "page_size": page, "prefill_tokens": args.prefill_tokens,
@@ -324,7 +377,7 @@ def main() -> int:
         "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch},
         "gpu_launches": launches,
-        "prefill": {"value": round(pf_value, 1), "tokens": args.prefill_tokens, "ms": round(pf_ms, 3),
+        "prefill": {"value": round(pf_value, 1), "tokens": args.prefill_tokens, "ms": round(pf_ms, 3), "ms_sd": round(pf_sd, 3),
                     "frac": round(pf_frac, 4), "peak_tflops": pk["bf16_tflops"]},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},

@@ -615,3 +615,15 @@ def test_a_wait_that_nothing_satisfies_gives_up_and_is_reported():
         ops_tc.check_errors()
     ops_tc.check_errors()                                       # the word was cleared
     assert fn(10, word.data_ptr(), out.data_ptr(), None) == 10001          # limits outside 1 us .. 0.1 s are refused
+
+
+def test_random_weights_are_the_same_on_the_device_and_on_the_host():
+    """"Seed 0" names one model: the random-weights mode makes the same bits on the GPU (benchmarks, `Engine.from_config`)
+    as on the CPU (model folders, the tests' plain implementation)."""
+    from llmx_b200.weights.random_init import RandomSource
+    from llmx_b200.weights.spec import TensorSpec
+    specs = {"w.weight": TensorSpec((301, 257)), "n.weight": TensorSpec((129,), "vector", init="one_plus_normal", std=0.01)}
+    for dtype in (torch.float32, torch.bfloat16):
+        host, device = RandomSource(specs, 7, dtype=dtype, device="cpu"), RandomSource(specs, 7, dtype=dtype, device=DEV)
+        for name in specs:
+            assert torch.equal(host.tensor(name), device.tensor(name).cpu()), (name, dtype)

@@ -148,3 +148,23 @@ def test_random_weights_mode_writes_a_model_folder(tmp_path):
     assert not torch.equal(TensorDirectory(d3).tensor("lm_head.weight"), t.tensor("lm_head.weight"))
     only = RandomSource({"lm_head.weight": model.tensor_specs()["lm_head.weight"]}, 5)
     assert torch.equal(only.tensor("lm_head.weight"), t.tensor("lm_head.weight"))
+
+
+def test_random_values_are_a_function_of_seed_name_and_index():
+    """The generator is counter-based: a tensor's values depend on (seed, name, element index) alone -- not on how the
+    work is cut into chunks, on the other tensors, or on the order of making them -- and look like N(0, 1)."""
+    import torch
+    from llmx_b200.weights.random_init import RandomSource, standard_normal
+    from llmx_b200.weights.spec import TensorSpec
+    cpu = torch.device("cpu")
+    x = standard_normal(99, 200_000, cpu)
+    assert torch.equal(x[:5000], standard_normal(99, 5000, cpu, chunk=777))
+    assert abs(float(x.mean())) < 0.01 and abs(float(x.std()) - 1.0) < 0.01 and float(x.abs().max()) < 5.5
+    assert abs(float(((x[:-1] * x[1:]).mean()))) < 0.01                      # neighbours are not correlated
+    assert not torch.equal(x[:100], standard_normal(100, 100, cpu))
+    specs = {"a.weight": TensorSpec((6, 10)), "b.weight": TensorSpec((10,), "vector", init="one_plus_normal", std=0.01)}
+    one = RandomSource(specs, 3, dtype=torch.float32)
+    other = RandomSource({"b.weight": specs["b.weight"]}, 3, dtype=torch.float32)
+    assert torch.equal(one.tensor("b.weight"), other.tensor("b.weight"))
+    assert abs(float(one.tensor("b.weight").mean()) - 1.0) < 0.02
+    assert not torch.equal(one.tensor("a.weight"), RandomSource(specs, 4, dtype=torch.float32).tensor("a.weight"))
