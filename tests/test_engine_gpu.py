@@ -3,7 +3,8 @@
 Each test replays the same requests through `Engine.step` in a different way and compares every
 position's logits with `tests/plain_qwen3.py` (whole sequences, no cache).  float32 is held to
 1e-4 of the logit scale; bfloat16 is compared with the plain implementation rounding what the
-bfloat16 path rounds (inputs of products, cache) and held to BF16_TOL of the logit scale.
+bfloat16 path rounds (inputs of products, cache) and held to the configuration's frozen budget (tests/configs.py:
+twice the error measured for it), as a fraction of the logit scale.
 """
 import json
 import os
@@ -14,11 +15,16 @@ import numpy as np
 import pytest
 
 import helpers
-from configs import CONFIGS
+from configs import BF16_BUDGET, BF16_UNCALIBRATED, CONFIGS
 
 pytestmark = pytest.mark.gpu
 
-TOL = {"float32": 1e-4, "bfloat16": 2e-2}
+def tol(dtype, name=None):
+    """The most a logit may differ from the plain implementation, as a fraction of the logit scale: 1e-4 in float32;
+    in bfloat16 the configuration's frozen budget (tests/configs.py)."""
+    return 1e-4 if dtype == "float32" else BF16_BUDGET.get(name, BF16_UNCALIBRATED)
+
+
 LENGTHS = [70, 1, 9, 40, 133, 33, 5, 96]
 
 
@@ -35,7 +41,7 @@ def _engine(model_dirs, name, dtype, kv_tokens):
                                                          max_requests=8))
 
 
-def _check(engine, folder, steps, requests, dtype):
+def _check(engine, folder, steps, requests, dtype, name=None):
     from llmx_b200 import ops_tc
     got = helpers.run_trace(engine, steps)
     ops_tc.check_errors()
@@ -44,7 +50,7 @@ def _check(engine, folder, steps, requests, dtype):
     wanted = sum(len(e["want"]) for s in steps for e in s["entries"])
     assert len(got) == wanted == sum(len(v) for v in requests.values())
     worst, scale, where = helpers.compare(got, requests, folder, dtype == "bfloat16")
-    assert worst <= TOL[dtype] * scale, f"largest difference {worst:.3e} at {where} (logit scale {scale:.3f})"
+    assert worst <= tol(dtype, name) * scale, f"largest difference {worst:.3e} at {where} (logit scale {scale:.3f})"
     return worst, scale
 
 
@@ -55,20 +61,20 @@ class TestCuttings:
         requests = _requests(name)
         steps = helpers.trace_whole(requests)
         folder, engine = _engine(model_dirs, name, dtype, helpers.tokens_needed(steps))
-        _check(engine, folder, steps, requests, dtype)
+        _check(engine, folder, steps, requests, dtype, name)
 
     def test_last_32_one_by_one(self, model_dirs, name, dtype):
         requests = _requests(name)
         steps = helpers.trace_tail_decoded(requests, 32)
         folder, engine = _engine(model_dirs, name, dtype, helpers.tokens_needed(steps))
-        _check(engine, folder, steps, requests, dtype)
+        _check(engine, folder, steps, requests, dtype, name)
 
     def test_portions_of_changing_size(self, model_dirs, name, dtype):
         requests = _requests(name)
         steps = helpers.trace_portions(requests)
         assert min(len(e["tokens"]) for s in steps for e in s["entries"] if len(e["tokens"]) > 1) == 2
         folder, engine = _engine(model_dirs, name, dtype, helpers.tokens_needed(steps))
-        _check(engine, folder, steps, requests, dtype)
+        _check(engine, folder, steps, requests, dtype, name)
 
     def test_mixed_with_pages_used_again(self, model_dirs, name, dtype):
         requests = _requests(name)
@@ -103,7 +109,7 @@ class TestCuttings:
             engine.cache.check()
         assert reused, "no page was used again; the pool was not tight enough to test reuse"
         worst, scale, where = helpers.compare(got, requests, folder, dtype == "bfloat16")
-        assert worst <= TOL[dtype] * scale, f"largest difference {worst:.3e} at {where} (logit scale {scale:.3f})"
+        assert worst <= tol(dtype, name) * scale, f"largest difference {worst:.3e} at {where} (logit scale {scale:.3f})"
 
 
 @pytest.mark.parametrize("name", ["B", "D"])
@@ -114,7 +120,7 @@ def test_long_decoding(model_dirs, name, dtype):
     requests = {"long": helpers.random_ids(vocab, 320, seed=7)}
     steps = helpers.trace_tail_decoded(requests, tail=300)
     folder, engine = _engine(model_dirs, name, dtype, 320)
-    _check(engine, folder, steps, requests, dtype)
+    _check(engine, folder, steps, requests, dtype, name)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -125,7 +131,7 @@ def test_first_tokens_of_a_sequence(model_dirs, name, dtype):
     requests = {"s": helpers.random_ids(vocab, 3, seed=3), "t": helpers.random_ids(vocab, 1, seed=4)}
     steps = helpers.trace_tail_decoded(requests, tail=3)
     folder, engine = _engine(model_dirs, name, dtype, 128)
-    _check(engine, folder, steps, requests, dtype)
+    _check(engine, folder, steps, requests, dtype, name)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -148,7 +154,7 @@ def test_trace_run_program(model_dirs, tmp_path, dtype):
     assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
     got = helpers.read_trace_output(steps, str(out), vocab)
     worst, scale, where = helpers.compare(got, requests, folder, dtype == "bfloat16")
-    assert worst <= TOL[dtype] * scale, f"largest difference {worst:.3e} at {where} (logit scale {scale:.3f})"
+    assert worst <= tol(dtype, name) * scale, f"largest difference {worst:.3e} at {where} (logit scale {scale:.3f})"
 
 
 def test_step_refusals(model_dirs):
@@ -177,15 +183,11 @@ def test_step_refusals(model_dirs):
     assert engine.cache.used_pages() == [0]
 
 
-@pytest.fixture(scope="module")
-def sharp_model_dirs(model_dirs, tmp_path_factory):
-    """Models whose attention is sharp: the q/k norm weights are scaled by 4, so scores spread over +-16 and a
-    row's output hangs on a few keys anywhere in its history.  With the random weights' nearly uniform attention
-    a key that is dropped or read from the wrong page changes a row by ~1/length; here it changes it outright."""
+def _sharpened(model_dirs, tmp_path_factory, names, factor):
     import torch
     from llmx_b200.weights import TensorDirectory, write_safetensors
     out = {}
-    for name in ("B", "D"):
+    for name in names:
         made = []
         for src in model_dirs[name][:2]:
             d = str(tmp_path_factory.mktemp(f"sharp_{name}"))
@@ -194,7 +196,7 @@ def sharp_model_dirs(model_dirs, tmp_path_factory):
             for n in t.names():
                 x = t.tensor(n).clone()
                 if n.endswith("q_norm.weight") or n.endswith("k_norm.weight"):
-                    x = x * 4.0
+                    x = x * factor
                 tensors[n] = x
             write_safetensors(os.path.join(d, "model.safetensors"), tensors)
             with open(os.path.join(src, "config.json")) as f, open(os.path.join(d, "config.json"), "w") as g:
@@ -202,6 +204,37 @@ def sharp_model_dirs(model_dirs, tmp_path_factory):
             made.append(d)
         out[name] = (made[0], made[1], model_dirs[name][2])
     return out
+
+
+@pytest.fixture(scope="module")
+def sharp_model_dirs(model_dirs, tmp_path_factory):
+    """Models whose attention is sharp: the q/k norm weights are scaled by 4, so scores spread over +-16 and a
+    row's output hangs on a few keys anywhere in its history.  With the random weights' nearly uniform attention
+    a key that is dropped or read from the wrong page changes a row by ~1/length; here it changes it outright."""
+    return _sharpened(model_dirs, tmp_path_factory, ("B", "D"), 4.0)
+
+
+@pytest.fixture(scope="module")
+def half_sharp_model_dirs(model_dirs, tmp_path_factory):
+    """The same with the weights doubled (scores four times as wide as the random model's): sharp enough that a key
+    read from the wrong place moves a logit far beyond the budget, mild enough that one bfloat16 step in a query or
+    key does not."""
+    return _sharpened(model_dirs, tmp_path_factory, ("B", "D", "E"), 2.0)
+
+
+@pytest.mark.parametrize("name", ["B", "D", "E"])
+@pytest.mark.parametrize("cutting", ["whole", "tail", "portions", "mixed"])
+def test_sharpened_attention_in_bfloat16_under_cutting(half_sharp_model_dirs, name, cutting):
+    """The bfloat16 path's own choices inside the engine -- the product that finishes its heads, the decode kernel
+    that makes its own queries and keys, the tiled prefill kernels, recorded steps -- with attention that hangs on
+    single keys: every logit within the sharpened model's frozen budget of the plain implementation."""
+    vocab = CONFIGS[name][0]["vocab_size"]
+    requests = {f"s{i}": helpers.random_ids(vocab, n, seed=300 + i) for i, n in enumerate([200, 37, 150, 9, 64])}
+    make = {"whole": helpers.trace_whole, "tail": helpers.trace_tail_decoded, "portions": helpers.trace_portions,
+            "mixed": helpers.trace_mixed}[cutting]
+    steps = make(requests)
+    folder, engine = _engine(half_sharp_model_dirs, name, "bfloat16", helpers.tokens_needed(steps))
+    _check(engine, folder, steps, requests, "bfloat16", "sharp:" + name)
 
 
 @pytest.mark.parametrize("name", ["B", "D"])
@@ -301,7 +334,7 @@ def test_layers_of_8b_width_under_cutting(wide_model_dir, dtype):
         steps = make(requests)
         engine = Engine.from_dir(wide_model_dir, EngineOptions(dtype=dtype, kv_tokens=helpers.tokens_needed(steps),
                                                                page_size=16, max_requests=4))
-        _check(engine, wide_model_dir, steps, requests, dtype)
+        _check(engine, wide_model_dir, steps, requests, dtype, "wide")
         del engine
 
 
@@ -322,7 +355,7 @@ def test_long_prompts_at_8b_width(wide_model_dir):
     for steps in traces:
         engine = Engine.from_dir(wide_model_dir, EngineOptions(dtype="bfloat16", kv_tokens=helpers.tokens_needed(steps),
                                                                page_size=16, max_requests=4))
-        _check(engine, wide_model_dir, steps, requests, "bfloat16")
+        _check(engine, wide_model_dir, steps, requests, "bfloat16", "wide")
         del engine
 
 
@@ -345,7 +378,7 @@ def test_long_portions_recorded_at_8b_width(wide_model_dir):
         got = helpers.run_trace(engine, steps, record=True)
         ops_tc.check_errors()
         worst, scale, where = helpers.compare(got, requests, wide_model_dir, True)
-        assert worst <= TOL["bfloat16"] * scale, f"run {run}: largest difference {worst:.3e} at {where}"
+        assert worst <= tol("bfloat16", "wide") * scale, f"run {run}: largest difference {worst:.3e} at {where}"
     assert len(engine.step_recordings) == 2
     engine.end("pad")
     engine.cache.check()
@@ -376,7 +409,7 @@ def test_recorded_steps_of_any_shape(model_dirs, wide_model_dir, name, dtype):
         got = helpers.run_trace(engine, steps, record=True)
         ops_tc.check_errors()
         worst, scale, where = helpers.compare(got, requests, folder, dtype == "bfloat16")
-        assert worst <= TOL[dtype] * scale, f"run {run}: largest difference {worst:.3e} at {where} (logit scale {scale:.3f})"
+        assert worst <= tol(dtype, name) * scale, f"run {run}: largest difference {worst:.3e} at {where} (logit scale {scale:.3f})"
     assert len(engine.step_recordings) > 0
     replayed = sum(1 for s in steps if (tuple(len(e["tokens"]) for e in s["entries"])) in {k[0] for k in engine.step_recordings})
     assert replayed >= len(steps) // 2
@@ -436,7 +469,7 @@ def test_decode_sessions_replay_their_recordings(model_dirs, wide_model_dir, nam
     requests_seen = {rid: requests[rid][:at[rid]] for rid in requests}
     worst, scale, where = helpers.compare({k: v for k, v in got.items() if k[1] < len(requests_seen[k[0]])}, requests_seen,
                                           folder, dtype == "bfloat16")
-    assert worst <= TOL[dtype] * scale, f"largest difference {worst:.3e} at {where} (logit scale {scale:.3f})"
+    assert worst <= tol(dtype, name) * scale, f"largest difference {worst:.3e} at {where} (logit scale {scale:.3f})"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -470,7 +503,7 @@ def test_hugging_face_golden_of_odd_sizes(tmp_path, dtype):
             else:
                 ref = helpers.reference_logits(str(folder), ids, True)[-1]
                 scale = float(np.abs(ref).max())
-                assert np.abs(whole - ref).max() <= TOL[dtype] * scale and np.abs(last - ref).max() <= TOL[dtype] * scale
+                assert np.abs(whole - ref).max() <= tol(dtype) * scale and np.abs(last - ref).max() <= tol(dtype) * scale
         engine.cache.check()
 
 
@@ -538,7 +571,7 @@ def test_a_step_that_fails_inside_the_forward_pass_leaves_every_request_where_it
     runtime.fail_call(None)
     ops_tc.check_errors()
     worst, scale, where = helpers.compare(got, {"a": a_ids[:58], "b": b_ids[:18]}, folder, dtype == "bfloat16")
-    assert worst <= TOL[dtype] * scale, f"largest difference {worst:.3e} at {where}"
+    assert worst <= tol(dtype, "D") * scale, f"largest difference {worst:.3e} at {where}"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -563,7 +596,7 @@ def test_a_request_rolled_back_goes_on_as_if_the_tokens_had_never_come(model_dir
     got_rows = engine.step([StepEntry("r", other[27:], list(range(20)))]).float().cpu().numpy()
     got = {("r", 27 + i): got_rows[i] for i in range(20)}
     worst, scale, where = helpers.compare(got, {"r": other}, folder, dtype == "bfloat16")
-    assert worst <= TOL[dtype] * scale, f"largest difference {worst:.3e} at {where}"
+    assert worst <= tol(dtype, "B") * scale, f"largest difference {worst:.3e} at {where}"
     with pytest.raises(ValueError):
         engine.truncate("r", 48)
     with pytest.raises(StepError):
@@ -594,8 +627,8 @@ def test_a_cache_type_of_its_own(model_dirs, name, dtype, kv_dtype):
     worst, scale, where = helpers.compare(got, requests, folder, dtype == "bfloat16", cache=kv_dtype)
     # float32 products over a bfloat16 cache: the plain twin rounds the same keys and values, so only the order of
     # float32 sums differs -- but a key rounded on the other side of a bfloat16 step moves a logit by 1e-3 of the scale
-    tol = TOL["bfloat16"] if dtype == "bfloat16" else 2e-3
-    assert worst <= tol * scale, f"largest difference {worst:.3e} at {where} (logit scale {scale:.3f})"
+    bound = tol("bfloat16", name) if dtype == "bfloat16" else 2e-3
+    assert worst <= bound * scale, f"largest difference {worst:.3e} at {where} (logit scale {scale:.3f})"
 
 
 def test_an_engine_that_is_dropped_gives_its_memory_back(model_dirs):
@@ -647,7 +680,7 @@ def test_invariant_schedules_give_a_row_the_same_bits_in_any_batch(model_dirs, w
             del engine
     base = runs[(True, "trace_whole")]
     worst, scale, where = helpers.compare(base, requests, folder, True)
-    assert worst <= TOL["bfloat16"] * scale
+    assert worst <= tol("bfloat16", name) * scale
     for make in ("trace_portions", "trace_mixed"):
         other = runs[(True, make)]
         assert all(np.array_equal(base[k], other[k]) for k in base), make
