@@ -1,7 +1,8 @@
 // Tiled causal attention for prompt portions on the 5th-generation tensor cores (head width 128).
 //
-// A work item is one (request, kv head, 2 * 128 / ratio consecutive new rows): two row tiles, each 128 / ratio
-// new rows times the `ratio` query heads of the group = the 128 rows of both products,
+// A work item is one (request, kv head, 2 * (128 / ratio) consecutive new rows): two row tiles, each 128 / ratio
+// (rounded down) new rows times the `ratio` query heads of the group = the 128 rows of both products (with a ratio
+// that does not divide 128 the last rows of a tile are padding: 25 tokens x 5 heads = 125 rows and 3 idle ones),
 //     S[128 rows, 128 keys] = Q K^T        O[128 rows, 128 columns] += P V
 // issued as tcgen05.mma by one thread.  The two row tiles share every key stage and take turns on the tensor
 // core: while one tile's softmax runs, the other's products do.  A launch has one block of threads per SM at
@@ -25,7 +26,7 @@
 //                   At the end O / l is written.
 //
 // Every wait on an mbarrier is bounded (see tc_common.cuh).  Shapes this kernel does not take (head width
-// other than 128, a head ratio that does not divide 128, page size other than 16) run the warp-level
+// other than 128, more than 16 query heads a kv head, page size other than 16) run the warp-level
 // kernel in attention_prefill.cu.
 // Reference counterpart: llmx_attention_tile (src/backends/gpu/kernels/f32.gpu:1498-1636).
 #include "attn_common.cuh"
@@ -152,6 +153,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         const int stage = i / (OPERAND_BYTES / 16), off = i % (OPERAND_BYTES / 16);
         *reinterpret_cast<uint4*>(smem + SMEM_KV + stage * STAGE_BYTES + OPERAND_BYTES + off * 16) = make_uint4(0, 0, 0, 0);
     }
+    // Rows of the Q tiles that no copy writes (a head ratio that does not divide 128 leaves 128 % ratio of them)
+    // hold zeros: their scores and outputs are computed and never stored.  The 128-byte swizzle moves 16-byte pieces
+    // within a row's 128 bytes only, so a row is the same bytes swizzled or not.
+    for (int i = threadIdx.x; i < 4 * (ROWS - tokens_per_tile * ratio) * 8; i += THREADS) {
+        const int half_of_tile = i / ((ROWS - tokens_per_tile * ratio) * 8), rest = i % ((ROWS - tokens_per_tile * ratio) * 8);
+        *reinterpret_cast<uint4*>(smem + SMEM_Q + half_of_tile * HALF_BYTES + (tokens_per_tile * ratio + rest / 8) * 128 + (rest % 8) * 16) =
+            make_uint4(0, 0, 0, 0);
+    }
     tc::fence_proxy_async();
     tc::tc_fence_before();
     __syncthreads();
@@ -224,14 +233,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         for (int k = 0; ok && item_at(k, it); ++k) {
             if (it.n_iter == 0) continue;
             if (lane == 0) {
-                // Q: rows [token][head of the group], both 64-column halves, one box per row tile; the item
+                // Q: rows [token][head of the group], one box per row tile and 64-column half (a half's rows are
+                // tokens_per_tile * ratio <= 128, so the halves are copied apart, each to its own 16 KB); the item
                 // before must be done with the buffer (its last Q K^T has run).
                 ok = tc::mbar_wait(q_empty, (items_done & 1u) ^ 1u, abort_flag, error_word, ERR_TCA_PRODUCER);
                 if (ok) {
-                    tc::mbar_expect_tx(q_full, (uint32_t)((it.last_tile + 1) * OPERAND_BYTES));
-                    tc::tma_load_5d(smem + SMEM_Q, &q_map, 0, 0, it.q0 + it.tile_t0[0], 0, it.g, q_full);
-                    if (it.last_tile)
-                        tc::tma_load_5d(smem + SMEM_Q + OPERAND_BYTES, &q_map, 0, 0, it.q0 + it.tile_t0[1], 0, it.g, q_full);
+                    tc::mbar_expect_tx(q_full, (uint32_t)((it.last_tile + 1) * 2 * tokens_per_tile * ratio * 128));
+                    for (int t = 0; t <= it.last_tile; ++t)
+                        for (int h = 0; h < 2; ++h)
+                            tc::tma_load_5d(smem + SMEM_Q + t * OPERAND_BYTES + h * HALF_BYTES, &q_map, 0, 0, it.q0 + it.tile_t0[t], h,
+                                            it.g, q_full);
                 }
             }
             ++items_done;
@@ -531,14 +542,14 @@ attn_prefill_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __re
 }
 
 // q [rows, heads, 128] bfloat16 as (64 columns) x (head within the group) x (row) x (half of the head) x (kv head):
-// the box {64, ratio, 128 / ratio, 2, 1} is a tile's Q operand, [half][row][head][64 columns] in shared memory.
+// the box {64, ratio, 128 / ratio, 1, 1} is one half of a tile's Q operand, [row][head][64 columns] in shared memory.
 int make_q_map(CUtensorMap* map, const void* q, uint64_t rows, int heads, int kv_heads) {
     llmx_encode_tiled_fn enc = llmx_encode_tiled();
     if (!enc) return 10003;
     const uint64_t ratio = heads / kv_heads;
     const cuuint64_t dims[5] = {64, ratio, rows, 2, (cuuint64_t)kv_heads};
     const cuuint64_t strides[4] = {D * 2, (cuuint64_t)heads * D * 2, 128, ratio * D * 2};
-    const cuuint32_t box[5] = {64, (cuuint32_t)ratio, (cuuint32_t)(ROWS / ratio), 2, 1};
+    const cuuint32_t box[5] = {64, (cuuint32_t)ratio, (cuuint32_t)(ROWS / ratio), 1, 1};
     const cuuint32_t elem[5] = {1, 1, 1, 1, 1};
     const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(q), dims, strides, box, elem,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -581,7 +592,7 @@ LLMX_EXPORT int llmx_attn_prefill_tc(const void* cache_map, const void* q, void*
                                      int item_tiles, int key_splits, float* partial, int* error_word,
                                      cudaStream_t stream) {
     if (n_req <= 0 || max_rows <= 0) return 0;
-    if (head_dim != D || page_size != PAGE || heads % kv_heads || ROWS % (heads / kv_heads) || n_req > 65535 ||
+    if (head_dim != D || page_size != PAGE || heads % kv_heads || heads / kv_heads > 16 || n_req > 65535 ||
         kv_heads > 65535 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15))
         return LLMX_ERR_UNSUPPORTED;
     static bool configured = false;

@@ -335,7 +335,7 @@ bool tiled_attention_supported(int heads, int kv_heads, int head_dim, int page_s
     return (head_dim == 64 || head_dim == 128) && page_size == ATTN_PAGE && heads % kv_heads == 0 && heads / kv_heads <= 16;
 }
 bool tensor_core_prefill(int heads, int kv_heads, int head_dim, int page_size) {
-    return head_dim == 128 && page_size == ATTN_PAGE && heads % kv_heads == 0 && 128 % (heads / kv_heads) == 0;
+    return head_dim == 128 && page_size == ATTN_PAGE && heads % kv_heads == 0 && heads / kv_heads <= 16;
 }
 
 }  // namespace
@@ -573,8 +573,8 @@ struct Attention : Mixer {
     }
 
     // Which attention kernel runs for which rows: requests that bring one or a few rows run the split-KV decode
-    // kernel, requests that bring a portion of a prompt the tiled prefill kernel (tcgen05 where the head ratio
-    // divides 128, else warp-level); both read the same pages.  Anything the tiled kernels do not take runs the plain
+    // kernel, requests that bring a portion of a prompt the tiled prefill kernel (tcgen05 where the head width is
+    // 128, else warp-level); both read the same pages.  Anything the tiled kernels do not take runs the plain
     // kernel (one block per row and head).
     int attend(Ctx& c, const void* q, const CacheEntry& e, void* out, int rows, int group) {
         const llmx_step& s = *c.s;

@@ -2,7 +2,7 @@
 
 Requests of a step are split by how many rows they bring: those whose rows times the head ratio fit a 16-row
 tile run the split-KV decode kernel (csrc/attention_decode.cu), the others a tiled prefill kernel (tcgen05,
-csrc/attention_prefill_tc.cu, where the head width is 128 and the head ratio divides 128; else warp-level,
+csrc/attention_prefill_tc.cu, where the head width is 128; else warp-level,
 csrc/attention_prefill.cu).  All read the same pages; which kernel a request runs depends only on its own row
 count.  The dispatch and its launch plans are the native runtime's (`Attention::attend`, `llmx_plan_make` in
 csrc/runtime/runtime.cpp); the functions here call them for tests and for callers that have queries already.
@@ -33,7 +33,7 @@ def supported(heads: int, kv_heads: int, head_dim: int, page_size: int) -> bool:
 
 
 def tensor_core_prefill(heads: int, kv_heads: int, head_dim: int, page_size: int) -> bool:
-    """Whether prompt portions run the tcgen05 kernel (head width 128, a head ratio dividing 128)."""
+    """Whether prompt portions run the tcgen05 kernel (head width 128, up to 16 query heads a kv head)."""
     return runtime.tiled_attention(heads, kv_heads, head_dim, page_size) == 2
 
 

@@ -271,7 +271,7 @@ def test_attention_tiled_bf16(heads, kv_heads, head_dim, layout, window, spike):
 
 
 @pytest.mark.parametrize("item_tiles,key_splits", [(1, 1), (2, 1), (1, 2), (2, 2), (2, 3), (1, 5)])
-@pytest.mark.parametrize("heads,kv_heads", [(32, 8), (16, 8), (8, 8)])
+@pytest.mark.parametrize("heads,kv_heads", [(32, 8), (16, 8), (8, 8), (40, 8), (6, 2), (14, 2)])
 @pytest.mark.parametrize("window", [None, 300])
 def test_attention_prefill_items_of_any_shape(item_tiles, key_splits, heads, kv_heads, window):
     """The tcgen05 prefill kernel's work items hold one row tile or two, and all of a block's keys or one of
