@@ -49,6 +49,8 @@ SIZES = {
     "8b": {},
     "0.6b": dict(num_hidden_layers=28, hidden_size=1024, intermediate_size=3072, num_attention_heads=16,
                  num_key_value_heads=8, tie_word_embeddings=True),
+    "14b": dict(num_hidden_layers=40, hidden_size=5120, intermediate_size=17408, num_attention_heads=40,
+                num_key_value_heads=8),          # five query heads a kv head
     "32b": dict(num_hidden_layers=64, hidden_size=5120, intermediate_size=25600, num_attention_heads=64,
                 num_key_value_heads=8),
 }
@@ -128,7 +130,9 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--size", choices=sorted(SIZES), default="8b", help="layer sizes: Qwen3-8B (the default), 0.6B or 32B")
+    ap.add_argument("--size", choices=sorted(SIZES), default="8b", help="layer sizes: Qwen3-8B (the default), 0.6B, 14B or 32B")
+    ap.add_argument("--profile", action="store_true",
+                    help="with --only: also the device time by kernel of one plain (unrecorded) step, and the host's time for it")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (both numbers are reported)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
@@ -267,6 +271,44 @@ def main() -> int:
             h2d = max((rec.total * 4 for (b, _), rec in self.engine.decode_recordings.items() if b == batch), default=0)
             return batch * 1e3 / ms, ms, h2d
 
+        def profile_plain_step(self, entries, what):
+            """One plain (unrecorded) step of these entries: the host's time to enqueue it (the device idle, then
+            free to run ahead) and the device time by kernel entry point (`ops.kernel_times`; printed to stderr)."""
+            engine = self.engine
+            ids = [e.request_id for e in entries]
+
+            def undo():
+                for e in entries:
+                    rc = engine.cache.live[e.request_id]
+                    if rc.length == len(e.tokens):
+                        engine.end(e.request_id)
+                    else:
+                        engine.truncate(e.request_id, rc.length - len(e.tokens))
+            for _ in range(3):
+                engine.step(entries)
+                undo()
+            torch.cuda.synchronize()
+            host = []
+            for _ in range(5):
+                t0 = time.perf_counter()
+                engine.step(entries)
+                host.append((time.perf_counter() - t0) * 1e3)
+                torch.cuda.synchronize()
+                undo()
+            launches0 = ops.launch_count()
+            with ops.kernel_times() as times:
+                engine.step(entries)
+            kernels = ops.launch_count() - launches0
+            for rid in ids:
+                engine.end(rid)
+            for l in times.lines(what):
+                print(l, file=sys.stderr)
+            host.sort()
+            return {"host_ms_per_plain_step": round(host[len(host) // 2], 4), "kernels": kernels,
+                    "host_us_per_kernel": round(host[len(host) // 2] * 1e3 / max(kernels, 1), 2),
+                    "device_ms_by_kernel": {k: round(v[1], 4) for k, v in times.by_function.items()},
+                    "device_ms": round(times.total_ms, 4)}
+
         def run_prefill(self, reps, warmup):
             """(tokens a second, ms: mean and sd over `reps` prompts from an empty cache, fraction of the bf16 peak)."""
             cfg, T, L = self.cfg, self.prefill_tokens, self.layers
@@ -296,14 +338,24 @@ def main() -> int:
     if args.only == "prefill":
         b = Bench(args.size, args.layers, [], args.context, args.prefill_tokens, args.steps, args.warmup)
         pf_value, pf_ms, pf_sd, pf_frac = b.run_prefill(3, 3)
-        print(json.dumps({"only": "prefill", "value": round(pf_value, 1), "ms": round(pf_ms, 3), "frac": round(pf_frac, 4),
-                          "layers": b.layers}))
+        line = {"only": "prefill", "value": round(pf_value, 1), "ms": round(pf_ms, 3), "frac": round(pf_frac, 4), "layers": b.layers}
+        if args.profile:
+            line["profile"] = b.profile_plain_step([StepEntry("profile", b.ids(args.prefill_tokens), [args.prefill_tokens - 1])], f"pp{args.prefill_tokens}")
+        print(json.dumps(line))
         return 0
     if args.only == "decode":
         b = Bench(args.size, args.layers, [args.batch], args.context, args.prefill_tokens, args.steps, args.warmup)
         times, launches, _ = b.run_decode(args.batch, args.steps, args.warmup)
-        print(json.dumps({"only": "decode", "value": round(args.batch * 1e3 / times[0], 1), "ms_per_step": round(times[0], 4),
-                          "batch": args.batch, "context": args.context, "layers": b.layers, "gpu_launches": launches}))
+        line = {"only": "decode", "value": round(args.batch * 1e3 / times[0], 1), "ms_per_step": round(times[0], 4),
+                "batch": args.batch, "context": args.context, "layers": b.layers, "gpu_launches": launches}
+        if args.profile:
+            rids = [("profile", i) for i in range(args.batch)]
+            for rid in rids:
+                rc = b.engine.cache.new_request(rid)
+                rc.prepare(args.context)
+                rc.commit()
+            line["profile"] = b.profile_plain_step([StepEntry(rid, [1], [0]) for rid in rids], f"tg{args.batch}")
+        print(json.dumps(line))
         return 0
     clocks = ClockSampler()          # clocks and throttle reasons over every timed region below
     clocks.start()

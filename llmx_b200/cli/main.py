@@ -253,9 +253,9 @@ def _bench_synthetic(size: int, iters: int, p: int, g: int, device: str) -> int:
     per-head norm with rotation at width `size`, then a two-layer model with random weights end to end."""
     import torch
     from .. import ops, ops_tc
-    from ..config import Qwen3Config
     from ..engine import Engine, EngineOptions, StepEntry
     from ..engine.decode_loop import DecodeSession
+    from ..registry import architecture_of
     dev = torch.device(device)
     with torch.cuda.device(dev):
         x = torch.full((1, size), 0.5, device=dev)
@@ -286,9 +286,10 @@ def _bench_synthetic(size: int, iters: int, p: int, g: int, device: str) -> int:
         print("bench: rms_norm n=%d  %8.3f ms" % (size, rn_ms))
         print("bench: norm_rope n=%d  %8.3f ms" % (size, rp_ms))
         # End to end on a small model of random weights: 2 layers, width 256 (src/cli/main.cpp:1150-1165).
-        cfg = Qwen3Config.from_dict(dict(num_hidden_layers=2, hidden_size=256, intermediate_size=1024, num_attention_heads=8,
-                                         num_key_value_heads=2, head_dim=32, vocab_size=512,
-                                         max_position_embeddings=max(2048, p + g + 64)))
+        # (a config.json's worth of keys, read through the registry like any model's)
+        raw = dict(model_type="qwen3", num_hidden_layers=2, hidden_size=256, intermediate_size=1024, num_attention_heads=8,
+                   num_key_value_heads=2, head_dim=32, vocab_size=512, max_position_embeddings=max(2048, p + g + 64))
+        cfg = architecture_of(raw).config_cls.from_dict(raw)
         engine = Engine.from_config(cfg, 12345, EngineOptions(kv_tokens=-(-(p + g + 64) // 64) * 64, max_requests=1,
                                                               device=device))
         prompt, gen = _bench_ids(12345, p, 512), _bench_ids(777, g, 512)
