@@ -181,7 +181,7 @@ def main() -> int:
             self.weight_bytes = 2 * (L * ((Q + 2 * KV) * E + E * Q + 2 * F * E + E * F) + V * E) + 4 * (L * (2 * E + 2 * cfg.head_dim) + E)
             self.kv_bytes_per_token = L * 2 * KV * 2
             resident = 2 * (L * (E * (Q + 2 * KV) + Q * E + 3 * E * F) + V * E * (1 if cfg.tie_word_embeddings else 2))
-            head_start = -(-context // 2048) * (max(batches) - 1)          # see run_generate
+            head_start = -(-context // 2048) * (max(batches, default=1) - 1)          # see run_generate
             per_request = -(-(context + steps + max(warmup, 8) + head_start + 64) // page) * page
             room = torch.cuda.get_device_properties(0).total_memory * 0.9 - resident - (8 << 30)
             self.batches = [b for b in batches if b * per_request * self.kv_bytes_per_token <= room]
