@@ -201,6 +201,24 @@ class LLM:
         index = {r.request_id: i for i, r in enumerate(requests)}
         stats = self.stats
         stats.prompt_tokens += sum(len(r.prompt) for r in requests)
+        try:
+            self._loop(sched, index, on_token)
+        except BaseException:
+            # A step that fails leaves every request where it was (Engine.step); the call as a whole gives back what
+            # its requests hold, so that the engine serves the next call.
+            self._close_session()
+            for r in requests:
+                self.engine.end(r.request_id)
+            raise
+        self._close_session()
+        stats.preemptions += sched.preemptions
+        from .. import ops_tc
+        ops_tc.check_errors()
+        return [GenerationOutput(r.request_id, r.prompt, list(r.output), r.finish_reason or "unknown") for r in requests]
+
+    def _loop(self, sched: Scheduler, index, on_token) -> None:
+        """Plan, step, draw and book until every request of the call has finished."""
+        stats = self.stats
         while not sched.idle:
             entries = sched.plan()
             for rid in sched.take_releases():
@@ -234,8 +252,3 @@ class LLM:
             self._account(sched, entries, sampled, index, on_token)
             for rid in sched.take_releases():
                 self.engine.end(rid)
-        self._close_session()
-        stats.preemptions += sched.preemptions
-        from .. import ops_tc
-        ops_tc.check_errors()
-        return [GenerationOutput(r.request_id, r.prompt, list(r.output), r.finish_reason or "unknown") for r in requests]

@@ -288,3 +288,23 @@ def test_baseline_tiny_b_workload_on_both_storages(baseline_dirs, dtype):
             logits = plain.forward(cfg, w, ids, act_round=plain.round_bf16 if dtype == "bfloat16" else None)[-1]
             assert logits[t] >= np.sort(logits)[-41]
             ids.append(t)
+
+
+def test_a_call_that_fails_gives_back_what_its_requests_hold(model_dirs):
+    """A step fails on the host in the middle of `generate` (prompts half fed, some requests decoding): the error
+    reaches the caller, every page is back, and the same call again gives the replies of an engine that never failed."""
+    from llmx_b200 import runtime
+    from llmx_b200.engine.generate import LLM
+    from llmx_b200.sampling import SamplingParams
+    _, folder, page = model_dirs["A"]
+    prompts = [helpers.random_ids(256, n, seed=70 + n) for n in (40, 9, 33)]
+    params = SamplingParams(max_tokens=10, temp=0.0, ignore_eos=True)
+    llm = LLM(folder, dtype="float32", kv_tokens=512, page_size=page, ubatch=16, max_seqs=3)
+    want = [o.tokens for o in llm.generate(prompts, params)]
+    runtime.fail_call("llmx_attention_plain", 7)            # the fourth step's first layer
+    with pytest.raises(runtime.KernelError):
+        llm.generate(prompts, params)
+    runtime.fail_call(None)
+    llm.engine.cache.check()
+    assert llm.engine.cache.used_pages() == [0] and not llm.engine.cache.live
+    assert [o.tokens for o in llm.generate(prompts, params)] == want

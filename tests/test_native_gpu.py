@@ -89,3 +89,50 @@ def test_a_cpp_program_drives_a_model_through_the_runtimes_header(model_dirs, dr
     tol = BF16_BUDGET[name] if dtype == "bfloat16" else 1e-4
     worst = float(np.abs(got - ref).max())
     assert worst <= tol * float(np.abs(ref).max()), f"largest difference {worst:.3e}"
+
+
+def test_a_block_written_elsewhere_runs_inside_the_native_model(model_dirs):
+    """`llmx_callback_create`: a block that is a function of another language (here a ctypes callback) takes its
+    place in the native model's walk.  The callback stands in for the model's second layer and runs that layer's own
+    native block on a workspace of its own, so the logits must be exactly those of the model without the detour."""
+    import ctypes
+    from llmx_b200 import runtime
+    from llmx_b200.engine import Engine, EngineOptions, StepEntry
+    folder = model_dirs["D"][1]
+    engine = Engine.from_dir(folder, EngineOptions(dtype="float32", kv_tokens=128, page_size=16, max_requests=2))
+    model = engine.model
+    ids = helpers.random_ids(CONFIGS["D"][0]["vocab_size"], 40, seed=4)
+    want = engine.step([StepEntry("w", ids, list(range(40)))]).clone()
+    engine.end("w")
+    assert model.native
+    rt = runtime.lib()
+    calls, keep = [], []
+    CALLBACK = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.POINTER(runtime.StepStruct), ctypes.c_int, ctypes.c_void_p,
+                                ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int)
+
+    def second_layer(user, step, kind, h, x, rows, cache_entry, write_cache):
+        calls.append((kind, rows, cache_entry, write_cache))
+        mine = runtime.StepStruct.from_buffer_copy(step.contents)       # the same step, a workspace of its own
+        need = rt.llmx_part_workspace(model.blocks[1].native, ctypes.byref(mine), rows, cache_entry)
+        ws = torch.empty(int(need), dtype=torch.uint8, device="cuda")
+        keep.append(ws)
+        mine.workspace, mine.workspace_bytes = ws.data_ptr(), int(need)
+        return rt.llmx_block_forward(model.blocks[1].native, ctypes.byref(mine), x, rows, cache_entry, write_cache)
+
+    fn = CALLBACK(second_layer)
+    detour = rt.llmx_callback_create(0, ctypes.cast(fn, ctypes.c_void_p), None, model.embedding.hidden)
+    assert detour
+    blocks = (ctypes.c_void_p * 2)(model.blocks[0].native, detour)
+    order = (runtime.LayerStepStruct * 2)(runtime.LayerStepStruct(0, 0, 1), runtime.LayerStepStruct(1, 1, 1))
+    twin = rt.llmx_model_create(model.embedding.native, blocks, 2, order, 2, model.head.native, model.embedding.hidden, model.vocab_size)
+    assert twin
+    real, model._native.handle = model._native.handle, twin              # the engine's steps now walk the twin
+    try:
+        got = engine.step([StepEntry("c", ids[:25], list(range(25)))])
+        got = torch.cat([got, engine.step([StepEntry("c", ids[25:], list(range(15)))])])
+    finally:
+        model._native.handle = real
+        rt.llmx_model_destroy(twin)
+        rt.llmx_part_destroy(detour)
+    assert calls == [(0, 25, 1, 1), (0, 15, 1, 1)]
+    assert torch.equal(got, want)
