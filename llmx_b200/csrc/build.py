@@ -38,6 +38,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "gemm_plain": ["gemm_plain.cu"],
     "attention_plain": ["attention_plain.cu"],
     "gemm_tc": ["gemm_tc.cu"],
+    "gemm_tc_pair": ["gemm_tc_pair.cu"],
     "attention_decode": ["attention_decode.cu"],
     "attention_prefill": ["attention_prefill.cu"],
     "attention_prefill_tc": ["attention_prefill_tc.cu"],

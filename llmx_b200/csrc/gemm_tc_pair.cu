@@ -1,0 +1,345 @@
+// bfloat16 matrix product on pairs of SMs (tcgen05 `cta_group::2`):  C[M, N] (+)= A[M, K] * W[N, K]^T  for many tokens.
+//
+// Two thread blocks of a cluster work on one output tile of 256 weight rows x BN tokens.  Each block holds its own 128
+// weight rows (its half of the instruction's M = 256) and only HALF of the token tile (BN / 2 rows): the instruction
+// reads the token operand from both blocks' shared memory, so a block takes in 16 KB + 16 KB a k block where the
+// one-block kernel (gemm_tc.cu) takes 16 KB + 32 KB for the same multiply-adds.  One thread of the pair's first block
+// issues tcgen05.mma.cta_group::2 for both; each block's accumulator (its 128 weight rows x BN tokens) lies in its own
+// tensor memory and is written out by its own epilogue warps.
+//
+//   warp 0 (both blocks)   TMA producer: the block's weight rows and its half of the tokens, per k block, into the
+//                          block's own shared memory; the bytes are counted on the FIRST block's barrier (loads
+//                          without multicast: `cp.async.bulk.tensor...cta_group::2` only names whose barrier counts)
+//   warp 1 (first block)   waits for a stage of both blocks, issues the products, and frees the stage in both blocks
+//                          with one commit (`tcgen05.commit...multicast::cluster`, an arrival on each block's barrier)
+//   warps 2-5 (both)       epilogue: tensor memory -> float32 output (stored, or added with float atomics), then an
+//                          arrival on the first block's accumulator-empty barrier
+//
+// Work: the pair walks tiles pair, pair + pairs, ... (token tiles vary fastest), optionally with K cut into `splits`
+// ranges that are added with atomics.  Every wait is bounded (tc_common.cuh); the pair meets at a cluster barrier
+// after its barriers are initialised (before any block signals the other) and before either block exits (a block's
+// shared memory and barriers are read and signalled by its partner until then).
+//
+// The reference has no tensor-core path for this product (its kernels: f32.gpu:1034-1084).
+#include "tc_common.cuh"
+
+namespace {
+
+constexpr int BM = 128;      // weight rows per block (half of the pair's 256)
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int EPI_WARPS = 4;
+constexpr int THREADS = 64 + EPI_WARPS * 32;
+enum : int { MODE_STORE = 0, MODE_ACCUMULATE = 1 };
+enum : int { ERR_PAIR_PRODUCER = 111, ERR_PAIR_MMA_FULL = 112, ERR_PAIR_MMA_ACC = 113, ERR_PAIR_EPILOGUE = 114 };
+
+template <int BN>
+struct PairCfg {
+    static constexpr int A_BYTES = BM * BK * 2;                 // the block's weight rows
+    static constexpr int B_BYTES = (BN / 2) * BK * 2;           // the block's half of the token tile
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
+    static constexpr int ACC_COLS = BN;
+    static constexpr int TMEM_COLS = 2 * ACC_COLS;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+    static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "two accumulators in tensor memory");
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The address, in the cluster's shared window, of block `rank`'s copy of a shared-memory location of this block.
+__device__ __forceinline__ uint32_t peer_addr(const void* local, uint32_t rank) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(tc::smem_u32(local)), "r"(rank));
+    return a;
+}
+__device__ __forceinline__ void arrive_at(uint32_t cluster_bar_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr) : "memory");
+}
+// A tile load into this block's shared memory whose bytes are counted on a barrier given by its cluster address.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y, uint32_t cluster_bar_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(tc::smem_u32(smem_dst)), "l"(map), "r"(cluster_bar_addr), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc::smem_u32(smem_result)), "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+// D[tensor memory of both blocks] (+)= A[128 rows in each block] * B[BN / 2 rows in each block]^T, one thread of the pair.
+__device__ __forceinline__ void mma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// One arrival on the barrier at this offset in each block of `mask`, once the pair's earlier products have finished.
+__device__ __forceinline__ void mma_commit_pair(uint64_t* bar, uint16_t mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(tc::smem_u32(bar)), "h"(mask)
+                 : "memory");
+}
+
+struct Work {
+    int wt, mt, kb0, kb1;
+};
+
+// Tiles in the order (k range, group of token tiles, weight tile, token tile of the group): neighbouring pairs share
+// weight rows, and a group's token rows (`group` tiles of BN rows x K) stay in the L2 cache while every weight tile
+// passes over them -- with all token tiles in one group, 4,096 tokens x 12,288 columns are 100 MB that each wave of
+// pairs streams again (measured: 540 us against 300).
+struct PairScheduler {
+    int w_tiles, m_tiles, k_blocks, splits, group;
+    long long cur, end, step;
+    __device__ PairScheduler(int w_tiles_, int m_tiles_, int k_blocks_, int splits_, int group_)
+        : w_tiles(w_tiles_), m_tiles(m_tiles_), k_blocks(k_blocks_), splits(splits_), group(group_) {
+        cur = blockIdx.x >> 1;
+        step = gridDim.x >> 1;
+        end = (long long)w_tiles * m_tiles * splits;
+    }
+    __device__ bool next(Work& w) {
+        if (cur >= end) return false;
+        const long long per_split = (long long)w_tiles * m_tiles;
+        const int sp = (int)(cur / per_split);
+        long long rest = cur % per_split;
+        const long long per_group = (long long)w_tiles * group;
+        const int g = (int)(rest / per_group);                     // the last group may hold fewer token tiles
+        const int in_group = min(group, m_tiles - g * group);
+        rest -= (long long)g * per_group;
+        w.wt = (int)(rest / in_group);
+        w.mt = g * group + (int)(rest % in_group);
+        const int per = (k_blocks + splits - 1) / splits;
+        w.kb0 = sp * per;
+        w.kb1 = min(k_blocks, w.kb0 + per);
+        cur += step;
+        return true;
+    }
+};
+
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+                    float* __restrict__ C, int M, int N, int K, int mode, int splits, int group, int* error_word) {
+    using cfg = PairCfg<BN>;
+    pdl_trigger();
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* tiles = smem;
+    uint64_t* full_bar = (uint64_t*)(smem + cfg::STAGES * cfg::STAGE_BYTES);      // used in the first block
+    uint64_t* empty_bar = full_bar + cfg::STAGES;                                 // one in each block
+    uint64_t* acc_full = empty_bar + cfg::STAGES;                                 // [2], one in each block
+    uint64_t* acc_empty = acc_full + 2;                                           // [2], used in the first block
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const bool leader = rank == 0;
+    const int w_tiles = (N + 2 * BM - 1) / (2 * BM), m_tiles = (M + BN - 1) / BN, k_blocks = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < cfg::STAGES; ++s) {
+            tc::mbar_init(&full_bar[s], 1);
+            tc::mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            tc::mbar_init(&acc_full[b], 1);
+            tc::mbar_init(&acc_empty[b], 2 * EPI_WARPS);        // the epilogue warps of both blocks
+        }
+        *abort_flag = 0;
+        tc::fence_barrier_init();
+        tc::tma_prefetch_desc(&map_w);
+        tc::tma_prefetch_desc(&map_a);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, cfg::TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc::tc_fence_before();
+    __syncthreads();
+    cluster_sync();           // both blocks' barriers exist before either signals the other
+    tc::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();               // the activations and the output belong to the kernels before
+
+    if (warp == 0) {
+        if (tc::elect_one()) {
+            PairScheduler sched(w_tiles, m_tiles, k_blocks, splits, group);
+            Work w;
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            while (ok && sched.next(w)) {
+                const int weight_row = (w.wt * 2 + (int)rank) * BM;
+                const int token_row = w.mt * BN + (int)rank * (BN / 2);
+                for (int kb = w.kb0; kb < w.kb1; ++kb) {
+                    ok = tc::mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, error_word, ERR_PAIR_PRODUCER);
+                    if (!ok) break;
+                    // The first block's barrier counts both blocks' bytes for the stage.
+                    if (leader) tc::mbar_expect_tx(&full_bar[stage], 2 * cfg::STAGE_BYTES);
+                    const uint32_t bar = peer_addr(&full_bar[stage], 0);
+                    uint8_t* a_dst = tiles + stage * cfg::STAGE_BYTES;
+                    tma_load_2d_pair(a_dst, &map_w, kb * BK, weight_row, bar);
+                    tma_load_2d_pair(a_dst + cfg::A_BYTES, &map_a, kb * BK, token_row, bar);
+                    if (++stage == cfg::STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (leader && tc::elect_one()) {
+            constexpr uint32_t idesc = tc::instr_desc_bf16(2 * BM, BN);
+            PairScheduler sched(w_tiles, m_tiles, k_blocks, splits, group);
+            Work w;
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool ok = true;
+            while (ok && sched.next(w)) {
+                ok = tc::mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, error_word, ERR_PAIR_MMA_ACC);
+                if (!ok) break;
+                tc::tc_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * cfg::ACC_COLS;
+                for (int kb = w.kb0; kb < w.kb1; ++kb) {
+                    ok = tc::mbar_wait(&full_bar[stage], phase, abort_flag, error_word, ERR_PAIR_MMA_FULL);
+                    if (!ok) break;
+                    tc::tc_fence_after();
+                    const uint32_t a_addr = tc::smem_u32(tiles + stage * cfg::STAGE_BYTES);
+                    const uint64_t desc_a = tc::smem_desc_k_sw128(a_addr);
+                    const uint64_t desc_b = tc::smem_desc_k_sw128(a_addr + cfg::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        mma_bf16_pair(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
+                    mma_commit_pair(&empty_bar[stage], 3);      // the stage is free in both blocks
+                    if (++stage == cfg::STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                mma_commit_pair(&acc_full[acc], 3);             // both blocks' accumulators are complete
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        PairScheduler sched(w_tiles, m_tiles, k_blocks, splits, group);
+        Work w;
+        uint32_t acc = 0, acc_phase = 0;
+        bool ok = true;
+        const bool atomic = mode == MODE_ACCUMULATE || splits > 1;
+        while (ok && sched.next(w)) {
+            ok = tc::mbar_wait(&acc_full[acc], acc_phase, abort_flag, error_word, ERR_PAIR_EPILOGUE);
+            if (!ok) break;
+            tc::tc_fence_after();
+            const int n = (w.wt * 2 + (int)rank) * BM + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + acc * cfg::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+            if (w.kb1 > w.kb0) {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t r[32];
+                    tc::tmem_ld_32x32(taddr + c, r);
+                    tc::tmem_wait_ld();
+                    if (n < N) {
+                        float* out = C + (size_t)(w.mt * BN + c) * N + n;
+                        const int m_left = M - (w.mt * BN + c);
+                        if (atomic) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (j < m_left) atomicAdd(out + (size_t)j * N, __uint_as_float(r[j]));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (j < m_left) out[(size_t)j * N] = __uint_as_float(r[j]);
+                        }
+                    }
+                }
+            }
+            tc::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) arrive_at(peer_addr(&acc_empty[acc], 0));
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+    tc::tc_fence_before();
+    __syncthreads();
+    cluster_sync();           // the partner no longer reads this block's shared memory or signals its barriers
+    if (warp == 1) {
+        tc::tc_fence_after();
+        tmem_dealloc_pair(tmem_base, cfg::TMEM_COLS);
+    }
+}
+
+int g_sm_count = 0;
+
+template <int BN>
+int launch_pair(const CUtensorMap& map_w, const void* A, float* C, int M, int N, int K, int mode, int splits, int* error_word,
+                cudaStream_t stream) {
+    using cfg = PairCfg<BN>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_tc_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES) != cudaSuccess)
+            return (int)cudaGetLastError();
+        configured = true;
+    }
+    CUtensorMap map_a;
+    if (int e = llmx_make_map_bf16_2d(&map_a, A, (uint64_t)M, (uint64_t)K, BN / 2, BK)) return e;
+    const int w_tiles = (N + 2 * BM - 1) / (2 * BM), m_tiles = (M + BN - 1) / BN;
+    // Token tiles a group: what 24 MB hold of the tokens' rows of one k range (at least one, at most all).
+    const long long tile_bytes = (long long)BN * ((K + splits - 1) / splits) * 2;
+    int group = (int)((24ll << 20) / (tile_bytes > 0 ? tile_bytes : 1));
+    group = group < 1 ? 1 : group > m_tiles ? m_tiles : group;
+    long long pairs = (long long)w_tiles * m_tiles * splits;
+    if (pairs > g_sm_count / 2) pairs = g_sm_count / 2;
+    if (pairs < 1) pairs = 1;
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3((unsigned)(2 * pairs));
+    lc.blockDim = dim3(THREADS);
+    lc.dynamicSmemBytes = cfg::SMEM_BYTES;
+    lc.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr;
+    lc.numAttrs = llmx_pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&lc, gemm_tc_pair_kernel<BN>, map_w, map_a, C, M, N, K, mode, splits, group, error_word);
+    return launch_status();
+}
+
+}  // namespace
+
+// C (+)= A W^T on pairs of SMs.  `weight_map`: the weight's tensor map with boxes of 128 rows x 64 columns (the one
+// llmx_gemm_tc_weight_map makes); A [M, K] bfloat16; C float32 [M, N]; mode 0 stores, 1 adds (float atomics);
+// `splits` > 1 (mode 1 only) cuts K into ranges; `token_tile` 128 or 256.
+LLMX_EXPORT int llmx_gemm_tc_pair(const void* weight_map, const void* A, float* C, int M, int N, int K, int mode, int splits,
+                                  int token_tile, int* error_word, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || ((uintptr_t)A & 15) || ((uintptr_t)C & 3)) return LLMX_ERR_UNSUPPORTED;
+    if ((mode != MODE_STORE && mode != MODE_ACCUMULATE) || splits < 1 || (splits > 1 && mode != MODE_ACCUMULATE))
+        return LLMX_ERR_BAD_ARGUMENT;
+    if (!g_sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || g_sm_count <= 0) g_sm_count = 148;
+    }
+    const int k_blocks = (K + BK - 1) / BK;
+    if (splits > k_blocks) splits = k_blocks;
+    const CUtensorMap& map_w = *(const CUtensorMap*)weight_map;
+    switch (token_tile) {
+        case 128: return launch_pair<128>(map_w, A, C, M, N, K, mode, splits, error_word, stream);
+        case 256: return launch_pair<256>(map_w, A, C, M, N, K, mode, splits, error_word, stream);
+        default: return LLMX_ERR_BAD_ARGUMENT;
+    }
+}

@@ -50,6 +50,8 @@ long long llmx_rt_launches(void);                          // kernels launched t
 void llmx_rt_count_launches(long long n);                  // ... plus those a replayed recording launched
 // Entry point i (from 0) that the last dry runs (llmx_*_workspace) would have called and found unbound; 0 at the end.
 int llmx_rt_missing(int i, const char** name);
+// Whether products of many tokens may run on pairs of SMs (on at the start).  Returns the setting before.
+int llmx_rt_pair_products(int on);
 void llmx_rt_reset_caches(void);                           // forget what was learnt of the device and the kernel libraries
 // For tests of what a failed step leaves behind: the nth call (from now) of the entry point `name` fails on the host,
 // before anything is launched, with LLMX_RT_ERR_INJECTED.  nth <= 0 or a null name: no failure is pending.
@@ -60,7 +62,8 @@ int llmx_rt_profile(int on);
 int llmx_rt_profile_read(int i, const char** name, float* ms, float* idle_ms_before);
 
 // ---- launch decisions, exposed so that one implementation serves callers and tests -------------------------
-// (schedule, token tile, k ranges) of the tensor-core product out[m, n] (+)= a[m, k] w[n, k]^T.
+// (schedule, token tile, k ranges) of the tensor-core product out[m, n] (+)= a[m, k] w[n, k]^T.  Schedule 0: whole
+// tiles, a thread block each; 1: stream-K; 2: whole tiles of 256 weight rows, a pair of thread blocks each.
 void llmx_gemm_plan(int m, int n, int k, int accumulate, int sms, int* schedule, int* token_tile, int* splits);
 int llmx_heads_tile(int m, int heads, int kv_heads, int sms);
 // (key ranges, keys per range) of the split-KV decode kernel; clusters[s] = clusters of s blocks the device runs

@@ -47,6 +47,7 @@ typedef cudaStream_t S;
     X(llmx_gemm_tc_weight_map, (void*, const void*, int, int))                                                            \
     X(llmx_gemm_tc_weight_map_box, (void*, const void*, int, int, int))                                                   \
     X(llmx_gemm_tc, (const void*, const void*, float*, int, int, int, int, int, int, int, int*, S))                       \
+    X(llmx_gemm_tc_pair, (const void*, const void*, float*, int, int, int, int, int, int, int*, S))                       \
     X(llmx_gemm_tc_swiglu, (const void*, const void*, void*, int, int, int, int, int*, S))                                \
     X(llmx_gemm_tc_heads, (const void*, const void*, int, int, int, const float*, const float*, float, const float*,      \
                            const float*, const int*, const int*, void*, void*, int, int, int, int*, S))                   \
@@ -186,7 +187,8 @@ constexpr int HEADS_MIN_ROWS = 256;           // from this many tokens on the q/
 
 int gemm_schedule(int m, int n) { return m <= STREAM_K_MAX_ROWS && cdiv(n, 128) < STREAM_K_MAX_TILES ? 1 : 0; }
 
-struct GemmPlan { int schedule, token_tile, splits; };
+struct GemmPlan { int schedule, token_tile, splits; };   // schedule 0: whole tiles, 1: stream-K, 2: whole tiles on pairs of SMs
+bool g_pair_products = true;
 
 // Few tokens: stream-K.  Else whole tiles, and the token tile and the number of k ranges are chosen so that the
 // tiles fill the SMs: with a few hundred tokens a [4096, 4096] weight makes 32 to 128 tiles, which would leave most
@@ -194,40 +196,47 @@ struct GemmPlan { int schedule, token_tile, splits; };
 // timings of the layer's products at 96 to 2,048 tokens: a tile's time is its bytes over what one SM takes in
 // (110 GB/s) or its multiply-adds at the SM's share of the tensor rate; atomics run beside the main loop at 500 G a
 // second and show at the end of a block's last tile; a stored output that is added to in pieces must be cleared first.
-GemmPlan gemm_plan_compute(int m, int n, int k, bool accumulate, int n_sms) {
+// The same estimate serves the product on pairs of SMs (gemm_tc_pair.cu): a pair's tile is 256 weight rows, each block
+// of the pair takes in its 128 weight rows and half the token tile, and the multiply-adds ran a tenth faster there.
+GemmPlan gemm_plan_compute(int m, int n, int k, bool accumulate, int n_sms, bool pairs) {
     if (gemm_schedule(m, n) == 1) return {1, 0, 1};
     if (m <= STREAM_K_MAX_ROWS) return {0, 0, 1};   // few tokens, plenty of weight tiles (the logits head): the narrowest token tile
-    const int n_tiles = cdiv(n, 128), k_blocks = cdiv(k, 64);
+    const int k_blocks = cdiv(k, 64);
     double best_t = -1;
-    int best_bn = 128, best_splits = 1;
-    for (int bn : {128, 256}) {
-        if (bn == 256 && m <= 128) continue;
-        const int m_tiles = cdiv(m, bn);
-        for (int splits = 1; splits <= 4; ++splits) {
-            if (splits > k_blocks) break;
-            const long long tiles = (long long)n_tiles * m_tiles * splits;
-            const long long waves = (tiles + n_sms - 1) / n_sms;
-            const double kk = (double)cdiv(k_blocks, splits) * 64;
-            const double per_tile = std::max(kk * (128 + bn) * 2 / 110e3, 2.0 * 128 * bn * kk / 9.4e6);
-            double t = waves * per_tile;
-            if (splits > 1) {
-                t = std::max(t, (double)m * n * splits / 500e3) + std::min(bn, m) * 128 / 8e3;
-                if (!accumulate) t += (double)m * n * 4 / 5e6;
+    GemmPlan best = {0, 128, 1};
+    for (int pair = 0; pair <= (pairs && n_sms >= 2 ? 1 : 0); ++pair) {
+        const int units = pair ? n_sms / 2 : n_sms;                 // blocks, or pairs of blocks, that run at once
+        const int n_tiles = cdiv(n, pair ? 256 : 128);
+        for (int bn : {128, 256}) {
+            if (bn == 256 && m <= 128) continue;
+            const int m_tiles = cdiv(m, bn);
+            for (int splits = 1; splits <= 4; ++splits) {
+                if (splits > k_blocks) break;
+                const long long tiles = (long long)n_tiles * m_tiles * splits;
+                const long long waves = (tiles + units - 1) / units;
+                const double kk = (double)cdiv(k_blocks, splits) * 64;
+                const double per_tile = pair ? std::max(kk * (128 + bn / 2) * 2 / 110e3, 2.0 * 128 * bn * kk / 10.3e6)
+                                             : std::max(kk * (128 + bn) * 2 / 110e3, 2.0 * 128 * bn * kk / 9.4e6);
+                double t = waves * per_tile;
+                if (splits > 1) {
+                    t = std::max(t, (double)m * n * splits / 500e3) + std::min(bn, m) * 128 / 8e3;
+                    if (!accumulate) t += (double)m * n * 4 / 5e6;
+                }
+                t *= 1.0 + 0.03 * (splits - 1);
+                if (best_t < 0 || t < best_t) best_t = t, best = {pair ? 2 : 0, bn, splits};
             }
-            t *= 1.0 + 0.03 * (splits - 1);
-            if (best_t < 0 || t < best_t) best_t = t, best_bn = bn, best_splits = splits;
         }
     }
-    return {0, best_bn, best_splits};
+    return best;
 }
 
 GemmPlan gemm_plan(int m, int n, int k, bool accumulate) {
-    static std::map<std::tuple<int, int, int, bool>, GemmPlan> cache;
-    const auto key = std::make_tuple(m, n, k, accumulate);
+    static std::map<std::tuple<int, int, int, bool, bool>, GemmPlan> cache;
+    const auto key = std::make_tuple(m, n, k, accumulate, g_pair_products);
     auto it = cache.find(key);
     if (it != cache.end()) return it->second;
     if (cache.size() > 65536) cache.clear();
-    return cache[key] = gemm_plan_compute(m, n, k, accumulate, sms());
+    return cache[key] = gemm_plan_compute(m, n, k, accumulate, sms(), g_pair_products);
 }
 
 // Weight rows per tile (128: one head, 256: two) of the q/k/v product that finishes its heads in the epilogue, or 0
@@ -453,6 +462,9 @@ struct Linear : llmx_part {
                 return c.status = fail(LLMX_RT_ERR_BAD_ARGUMENT, "clearing a product's output failed");
             acc = true;
         }
+        if (p.schedule == 2)
+            return CALL(c, llmx_gemm_tc_pair, 1, (const void*)map128, a, out, rows, N, K, acc ? 1 : 0, p.splits, p.token_tile,
+                        c.s->error_word, c.stream);
         return CALL(c, llmx_gemm_tc, 1, (const void*)map128, a, out, rows, N, K, acc ? 1 : 0, p.splits, p.token_tile, p.schedule,
                     c.s->error_word, c.stream);
     }
@@ -854,6 +866,12 @@ LLMX_API void llmx_rt_reset_caches(void) {
     g_cluster_cache.clear();
 }
 
+LLMX_API int llmx_rt_pair_products(int on) {
+    const bool before = g_pair_products;
+    g_pair_products = on != 0;
+    return before ? 1 : 0;
+}
+
 LLMX_API int llmx_rt_profile(int on) {
     const bool before = g_profile;
     if (on && !g_profile) {
@@ -890,7 +908,7 @@ LLMX_API int llmx_rt_profile_read(int i, const char** name, float* ms, float* id
 }
 
 LLMX_API void llmx_gemm_plan(int m, int n, int k, int accumulate, int n_sms, int* schedule, int* token_tile, int* splits) {
-    const GemmPlan p = n_sms > 0 ? gemm_plan_compute(m, n, k, accumulate != 0, n_sms) : gemm_plan(m, n, k, accumulate != 0);
+    const GemmPlan p = n_sms > 0 ? gemm_plan_compute(m, n, k, accumulate != 0, n_sms, g_pair_products) : gemm_plan(m, n, k, accumulate != 0);
     *schedule = p.schedule, *token_tile = p.token_tile, *splits = p.splits;
 }
 LLMX_API int llmx_tiled_attention(int heads, int kv_heads, int head_dim, int page_size) {

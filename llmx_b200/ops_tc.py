@@ -13,6 +13,7 @@ from .ops import KernelError, _check, _cuda, _fn, _need, _ptr, _stream, register
 _i, _p = ctypes.c_int, ctypes.c_void_p
 register_signature("gemm_tc", "llmx_gemm_tc_weight_map", [_p, _p, _i, _i])
 register_signature("gemm_tc", "llmx_gemm_tc", [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p])
+register_signature("gemm_tc_pair", "llmx_gemm_tc_pair", [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _p])
 register_signature("gemm_tc", "llmx_gemm_tc_swiglu", [_p, _p, _p, _i, _i, _i, _i, _p, _p])
 register_signature("gemm_tc", "llmx_gemm_tc_weight_map_box", [_p, _p, _i, _i, _i])
 register_signature("gemm_tc", "llmx_gemm_tc_heads", [_p, _p, _i, _i, _i, _p, _p, ctypes.c_float, _p, _p, _p, _p, _p, _p,
@@ -92,9 +93,10 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
     """out (+)= a @ w.T; a [M, K] bfloat16, w [N, K] bfloat16, out float32 [M, N].
 
     schedule 0 walks whole tiles (`splits` > 1 cuts K and adds the pieces with atomics); schedule 1
-    (stream-K) shares out (tile, k block) units evenly and adds every piece with atomics.  Whenever pieces
+    (stream-K) shares out (tile, k block) units evenly and adds every piece with atomics; schedule 2 walks whole
+    tiles of 256 weight rows on pairs of SMs (`gemm_tc_pair`).  Whenever pieces
     are added, `out` is zeroed first unless accumulating.  By default `plan` chooses: stream-K for few
-    tokens, else the token tile and k ranges that fill the SMs.
+    tokens, else the kernel, token tile and k ranges that fill the SMs.
     """
     _cuda(a, w, out)
     m, k = a.shape
@@ -110,6 +112,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
         schedule = (1 if plan(m, n, k, accumulate)[0] == 1 else 0) if splits is None else 0
     if splits is None:
         splits = 1
+    if schedule == 2:
+        return gemm_tc_pair(a, w, out, accumulate, wmap, splits, token_tile or 128)
     if (schedule == 1 or splits > 1) and not accumulate:
         out.zero_()
         accumulate = True
@@ -177,3 +181,23 @@ def gemm_tc_heads(a: torch.Tensor, wmap: WeightMap, heads: int, kv_heads: int, q
         ctypes.c_void_p(wmap.address), _ptr(a), m, k, wmap.box_rows, _ptr(q_weight), _ptr(k_weight), float(eps),
         _ptr(cos), _ptr(sin), _ptr(positions), _ptr(slots), _ptr(q_out), _ptr(cache), heads, kv_heads,
         cache.shape[3], _ptr(error_word(a.device)), _stream()), "gemm_tc_heads")
+
+
+def gemm_tc_pair(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
+                 wmap: Optional[WeightMap] = None, splits: int = 1, token_tile: int = 256) -> torch.Tensor:
+    """out (+)= a @ w.T on pairs of SMs (csrc/gemm_tc_pair.cu: tcgen05 `cta_group::2`, a tile of 256 weight rows x
+    `token_tile` tokens per pair of thread blocks); a [M, K] bfloat16, w [N, K] bfloat16, out float32 [M, N]."""
+    _cuda(a, w, out)
+    m, k = a.shape
+    n = w.shape[0]
+    _need(a.dtype is torch.bfloat16 and w.dtype is torch.bfloat16 and out.dtype is torch.float32,
+          "gemm_tc_pair: bfloat16 inputs and a float32 output")
+    _need(w.shape[1] == k and tuple(out.shape) == (m, n) and k % 8 == 0, "gemm_tc_pair: shapes do not fit")
+    wmap = wmap or weight_map(w)
+    if splits > 1 and not accumulate:
+        out.zero_()
+        accumulate = True
+    _check(_fn("gemm_tc_pair", "llmx_gemm_tc_pair")(ctypes.c_void_p(wmap.address), _ptr(a), _ptr(out), m, n, k,
+                                                    1 if accumulate else 0, splits, token_tile, _ptr(error_word(a.device)),
+                                                    _stream()), "gemm_tc_pair")
+    return out

@@ -76,6 +76,7 @@ _SIGNATURES = {
     "llmx_rt_fail_call": (None, [ctypes.c_char_p, _i]),
     "llmx_rt_missing": (_i, [_i, ctypes.POINTER(ctypes.c_char_p)]),
     "llmx_rt_reset_caches": (None, []),
+    "llmx_rt_pair_products": (_i, [_i]),
     "llmx_gemm_plan": (None, [_i, _i, _i, _i, _i, ctypes.POINTER(_i), ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     "llmx_heads_tile": (_i, [_i, _i, _i, _i]),
     "llmx_decode_schedule": (None, [_i, _i, _i, _i, _p, ctypes.POINTER(_i), ctypes.POINTER(_i)]),
@@ -128,7 +129,7 @@ KERNEL_LIBS: Dict[str, str] = {
     "llmx_embed": "rowwise", "llmx_rmsnorm": "rowwise", "llmx_head_norm_rope_kv": "rowwise", "llmx_swiglu": "rowwise",
     "llmx_gemm_plain": "gemm_plain", "llmx_attention_plain": "attention_plain",
     "llmx_gemm_tc_weight_map": "gemm_tc", "llmx_gemm_tc_weight_map_box": "gemm_tc", "llmx_gemm_tc": "gemm_tc",
-    "llmx_gemm_tc_swiglu": "gemm_tc", "llmx_gemm_tc_heads": "gemm_tc",
+    "llmx_gemm_tc_swiglu": "gemm_tc", "llmx_gemm_tc_heads": "gemm_tc", "llmx_gemm_tc_pair": "gemm_tc_pair",
     "llmx_attn_cache_map": "attention_decode", "llmx_attn_decode_fused": "attention_decode",
     "llmx_attn_decode_qkv": "attention_decode", "llmx_attn_decode_max_clusters": "attention_decode",
     "llmx_attn_prefill_tc_cache_map": "attention_prefill_tc", "llmx_attn_prefill_tc": "attention_prefill_tc",
@@ -264,6 +265,11 @@ def gemm_plan(m: int, n: int, k: int, accumulate: bool, sms: int = 0):
     s, t, r = _i(), _i(), _i()
     lib().llmx_gemm_plan(m, n, k, 1 if accumulate else 0, sms, ctypes.byref(s), ctypes.byref(t), ctypes.byref(r))
     return s.value, t.value, r.value
+
+
+def pair_products(on: bool) -> bool:
+    """Products of many tokens may run on pairs of SMs (csrc/gemm_tc_pair.cu; on at the start).  Returns the setting before."""
+    return bool(lib().llmx_rt_pair_products(1 if on else 0))
 
 
 def heads_tile(m: int, heads: int, kv_heads: int, sms: int = 0) -> int:

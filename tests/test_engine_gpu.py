@@ -687,3 +687,28 @@ def test_invariant_schedules_give_a_row_the_same_bits_in_any_batch(model_dirs, w
     # the serving schedules: not the same bits, but close
     moved = max(float(np.abs(runs[(False, "trace_mixed")][k] - runs[(False, "trace_whole")][k]).max()) for k in base)
     assert moved <= 1e-2 * scale
+
+
+@pytest.mark.parametrize("name", ["A", "wide"])
+def test_products_on_pairs_of_sms_and_on_single_blocks_agree_with_the_plain_model(model_dirs, wide_model_dir, name):
+    """Prompt portions of more than 64 tokens run their output and down products on pairs of SMs
+    (csrc/gemm_tc_pair.cu); with that turned off, on single blocks.  Both stay within the bfloat16 budget."""
+    from llmx_b200 import runtime
+    from llmx_b200.engine import Engine, EngineOptions
+    if name == "wide":
+        folder, page, vocab = wide_model_dir, 16, WIDE["vocab_size"]
+    else:
+        folder, page, vocab = model_dirs[name][0], model_dirs[name][2], CONFIGS[name][0]["vocab_size"]
+    requests = {"p0": helpers.random_ids(vocab, 300, seed=91), "p1": helpers.random_ids(vocab, 131, seed=92)}
+    steps = helpers.trace_whole(requests)
+    for on in (True, False):
+        before = runtime.pair_products(on)
+        try:
+            engine = Engine.from_dir(folder, EngineOptions(dtype="bfloat16", kv_tokens=helpers.tokens_needed(steps), page_size=page,
+                                                           max_requests=2))
+            got = helpers.run_trace(engine, steps)
+            del engine
+        finally:
+            runtime.pair_products(before)
+        worst, scale, where = helpers.compare(got, requests, folder, True)
+        assert worst <= tol("bfloat16", name) * scale, (on, where)

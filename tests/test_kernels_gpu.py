@@ -170,6 +170,43 @@ def test_gemm_tensor_core_every_token_tile(tile):
     assert (out.cpu().double() - ref).abs().max() <= 2e-5 * ref.abs().max()
 
 
+@pytest.mark.parametrize("m", [65, 130, 257, 600])
+@pytest.mark.parametrize("n,k", [(100, 72), (384, 96), (1000, 160), (4096, 1024)])
+def test_gemm_tensor_core_on_pairs_of_sms(m, n, k):
+    """The two-block (tcgen05 `cta_group::2`) product at ragged sizes: a second block whose weight rows or token rows
+    lie wholly or partly beyond the matrix, K that is no multiple of 64, both token tiles, K in ranges."""
+    from llmx_b200 import ops_tc
+    g = torch.Generator().manual_seed(16)
+    a = _bf16(torch.randn(m, k, generator=g)).to(DEV)
+    w = _bf16(torch.randn(n, k, generator=g) * 0.1).to(DEV)
+    ref = a.float().cpu().double() @ w.float().cpu().double().T
+    base = torch.randn(m, n, generator=g).to(DEV)
+    for tile in (128, 256):
+        guard = torch.full((m + 2, n), 7.0, device=DEV)
+        out = guard[1:m + 1]
+        ops_tc.gemm_tc_pair(a, w, out, token_tile=tile)
+        torch.cuda.synchronize()
+        ops_tc.check_errors()
+        assert (out.cpu().double() - ref).abs().max() <= 2e-5 * max(1.0, ref.abs().max())
+        assert torch.all(guard[0] == 7.0) and torch.all(guard[m + 1] == 7.0)
+        for splits in (1, 2, 3):
+            acc = base.clone()
+            ops_tc.gemm_tc_pair(a, w, acc, accumulate=True, splits=splits, token_tile=tile)
+            assert (acc.cpu().double() - (ref + base.cpu().double())).abs().max() <= 3e-5 * max(1.0, ref.abs().max())
+    ops_tc.check_errors()
+
+
+def test_gemm_plan_may_choose_pairs_and_can_be_told_not_to():
+    from llmx_b200 import ops_tc, runtime
+    assert ops_tc.plan(2048, 4096, 4096, True)[0] == 2
+    before = runtime.pair_products(False)
+    try:
+        assert ops_tc.plan(2048, 4096, 4096, True)[0] == 0
+    finally:
+        runtime.pair_products(before)
+    assert ops_tc.plan(8, 4096, 4096, True)[0] == 1
+
+
 def test_gemm_tensor_core_refuses_unaligned_width():
     from llmx_b200 import ops_tc
     from llmx_b200.ops import KernelError
