@@ -20,8 +20,16 @@
 // after its barriers are initialised (before any block signals the other) and before either block exits (a block's
 // shared memory and barriers are read and signalled by its partner until then).
 //
+// Three forms share the kernel.  PLAIN: float32 output, stored or added.  DUAL: two products that share the token
+// tile -- weight rows n and n + N (gate and up of a gated feed-forward), two tiles of 128 rows a block and two
+// accumulators -- written as silu(gate) * up in bfloat16.  HEADS: the q/k/v product of heads of 128; the operands
+// change sides (the pair's 256 rows are tokens, 128 a block; the narrow side is 256 weight rows = two heads, of which
+// each block loads one), so a thread of the epilogue holds two whole heads of one token, norms and rotates them and
+// writes queries and cache rows as bfloat16 (gemm_heads_epilogue.cuh).
+//
 // The reference has no tensor-core path for this product (its kernels: f32.gpu:1034-1084).
 #include "tc_common.cuh"
+#include "gemm_heads_epilogue.cuh"
 
 namespace {
 
@@ -33,16 +41,22 @@ constexpr int THREADS = 64 + EPI_WARPS * 32;
 enum : int { MODE_STORE = 0, MODE_ACCUMULATE = 1 };
 enum : int { ERR_PAIR_PRODUCER = 111, ERR_PAIR_MMA_FULL = 112, ERR_PAIR_MMA_ACC = 113, ERR_PAIR_EPILOGUE = 114 };
 
-template <int BN>
+enum : int { PLAIN = 0, DUAL = 1, HEADS = 2 };
+
+// The instruction's 256-row side is the "wide" operand (128 rows a block; DUAL: two such tiles), its BN-row side the
+// "narrow" one (BN / 2 rows a block).
+template <int BN, int FORM>
 struct PairCfg {
-    static constexpr int A_BYTES = BM * BK * 2;                 // the block's weight rows
-    static constexpr int B_BYTES = (BN / 2) * BK * 2;           // the block's half of the token tile
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int A_TILES = FORM == DUAL ? 2 : 1;
+    static constexpr int A_BYTES = BM * BK * 2;                 // one tile of the block's wide rows
+    static constexpr int B_BYTES = (BN / 2) * BK * 2;           // the block's half of the narrow tile
+    static constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
     static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
-    static constexpr int ACC_COLS = BN;
+    static constexpr int ACC_COLS = A_TILES * BN;
     static constexpr int TMEM_COLS = 2 * ACC_COLS;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
-    static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "two accumulators in tensor memory");
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/ + 1024 /*norm weights*/;
+    static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "two accumulator sets in tensor memory");
+    static_assert(FORM != HEADS || BN == 256, "a block loads one whole head of the narrow side");
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -131,11 +145,15 @@ struct PairScheduler {
     }
 };
 
-template <int BN>
+// `map_wide` / `map_narrow`: the operands' maps (boxes of 128 and BN / 2 rows); `wide_rows` / `narrow_rows`: their
+// extents.  PLAIN: wide = weight [N, K], narrow = tokens [M, K], C float32 [M, N].  DUAL: the weight has 2 N rows,
+// C bfloat16 [M, N].  HEADS: wide = tokens, narrow = weight; the outputs are `hp`'s.
+template <int BN, int FORM>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
-                    float* __restrict__ C, int M, int N, int K, int mode, int splits, int group, int* error_word) {
-    using cfg = PairCfg<BN>;
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_wide, const __grid_constant__ CUtensorMap map_narrow,
+                    void* __restrict__ C_, int wide_rows, int narrow_rows, int K, int mode, int splits, int group,
+                    int* error_word, const HeadsEpilogue hp) {
+    using cfg = PairCfg<BN, FORM>;
     pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -146,11 +164,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     uint64_t* acc_empty = acc_full + 2;                                           // [2], used in the first block
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    float* norm_w = (float*)(smem + cfg::STAGES * cfg::STAGE_BYTES + 256);        // HEADS: q weights, then k weights
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();
     const bool leader = rank == 0;
-    const int w_tiles = (N + 2 * BM - 1) / (2 * BM), m_tiles = (M + BN - 1) / BN, k_blocks = (K + BK - 1) / BK;
+    const int N = wide_rows, M = narrow_rows;       // as PLAIN and DUAL name them
+    const int w_tiles = (wide_rows + 2 * BM - 1) / (2 * BM), m_tiles = (narrow_rows + BN - 1) / BN, k_blocks = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < cfg::STAGES; ++s) {
@@ -163,12 +183,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
         *abort_flag = 0;
         tc::fence_barrier_init();
-        tc::tma_prefetch_desc(&map_w);
-        tc::tma_prefetch_desc(&map_a);
+        tc::tma_prefetch_desc(&map_wide);
+        tc::tma_prefetch_desc(&map_narrow);
     }
     if (warp == 1) {
         tmem_alloc_pair(tmem_slot, cfg::TMEM_COLS);
         tmem_relinquish_pair();
+    }
+    if (FORM == HEADS && threadIdx.x >= 64) {
+        const int i = threadIdx.x - 64;             // norm weights are written by no kernel
+        norm_w[i] = hp.q_weight ? hp.q_weight[i] : 1.0f;
+        norm_w[128 + i] = hp.k_weight ? hp.k_weight[i] : 1.0f;
     }
     tc::tc_fence_before();
     __syncthreads();
@@ -184,8 +209,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             while (ok && sched.next(w)) {
-                const int weight_row = (w.wt * 2 + (int)rank) * BM;
-                const int token_row = w.mt * BN + (int)rank * (BN / 2);
+                const int wide_row = (w.wt * 2 + (int)rank) * BM;
+                const int narrow_row = w.mt * BN + (int)rank * (BN / 2);
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     ok = tc::mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, error_word, ERR_PAIR_PRODUCER);
                     if (!ok) break;
@@ -193,8 +218,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     if (leader) tc::mbar_expect_tx(&full_bar[stage], 2 * cfg::STAGE_BYTES);
                     const uint32_t bar = peer_addr(&full_bar[stage], 0);
                     uint8_t* a_dst = tiles + stage * cfg::STAGE_BYTES;
-                    tma_load_2d_pair(a_dst, &map_w, kb * BK, weight_row, bar);
-                    tma_load_2d_pair(a_dst + cfg::A_BYTES, &map_a, kb * BK, token_row, bar);
+                    tma_load_2d_pair(a_dst, &map_wide, kb * BK, wide_row, bar);
+                    if (FORM == DUAL) tma_load_2d_pair(a_dst + cfg::A_BYTES, &map_wide, kb * BK, N + wide_row, bar);
+                    tma_load_2d_pair(a_dst + cfg::A_TILES * cfg::A_BYTES, &map_narrow, kb * BK, narrow_row, bar);
                     if (++stage == cfg::STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -217,10 +243,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     tc::tc_fence_after();
                     const uint32_t a_addr = tc::smem_u32(tiles + stage * cfg::STAGE_BYTES);
                     const uint64_t desc_a = tc::smem_desc_k_sw128(a_addr);
-                    const uint64_t desc_b = tc::smem_desc_k_sw128(a_addr + cfg::A_BYTES);
+                    const uint64_t desc_b = tc::smem_desc_k_sw128(a_addr + cfg::A_TILES * cfg::A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k)
-                        mma_bf16_pair(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint32_t accumulate = (kb > w.kb0 || k > 0) ? 1u : 0u;
+                        mma_bf16_pair(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, accumulate);
+                        if (FORM == DUAL) {
+                            const uint64_t desc_a2 = tc::smem_desc_k_sw128(a_addr + cfg::A_BYTES);
+                            mma_bf16_pair(tmem_d + BN, desc_a2 + 2 * k, desc_b + 2 * k, idesc, accumulate);
+                        }
+                    }
                     mma_commit_pair(&empty_bar[stage], 3);      // the stage is free in both blocks
                     if (++stage == cfg::STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -242,14 +274,34 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             tc::tc_fence_after();
             const int n = (w.wt * 2 + (int)rank) * BM + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + acc * cfg::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
-            if (w.kb1 > w.kb0) {
+            if constexpr (FORM == HEADS) {
+                // n: this thread's token; the tile's two heads start at feature w.mt * BN
+                heads_epilogue<BN>(hp, norm_w, taddr, n, wide_rows, w.mt * BN, narrow_rows);
+            } else if (w.kb1 > w.kb0) {
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 32) {
                     uint32_t r[32];
                     tc::tmem_ld_32x32(taddr + c, r);
+                    if constexpr (FORM == DUAL) {
+                        uint32_t u[32];
+                        tc::tmem_ld_32x32(taddr + BN + c, u);
+                        tc::tmem_wait_ld();
+                        if (n < N) {
+                            // silu(g) * u in float32 with the fast exponential and reciprocal, as the one-block product
+                            __nv_bfloat16* out = (__nv_bfloat16*)C_ + (size_t)(w.mt * BN + c) * N + n;
+                            const int m_left = M - (w.mt * BN + c);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                const float g = __uint_as_float(r[j]), up = __uint_as_float(u[j]);
+                                const float act = __fdividef(g, 1.0f + __expf(-g)) * up;
+                                if (j < m_left) out[(size_t)j * N] = __float2bfloat16_rn(act);
+                            }
+                        }
+                        continue;
+                    }
                     tc::tmem_wait_ld();
                     if (n < N) {
-                        float* out = C + (size_t)(w.mt * BN + c) * N + n;
+                        float* out = (float*)C_ + (size_t)(w.mt * BN + c) * N + n;
                         const int m_left = M - (w.mt * BN + c);
                         if (atomic) {
 #pragma unroll
@@ -280,20 +332,27 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
 int g_sm_count = 0;
 
-template <int BN>
-int launch_pair(const CUtensorMap& map_w, const void* A, float* C, int M, int N, int K, int mode, int splits, int* error_word,
-                cudaStream_t stream) {
-    using cfg = PairCfg<BN>;
+void ensure_sm_count() {
+    if (!g_sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || g_sm_count <= 0) g_sm_count = 148;
+    }
+}
+
+// `wide` / `narrow`: the operands' maps with boxes of 128 and BN / 2 rows; their extents in rows.
+template <int BN, int FORM>
+int launch_pair(const CUtensorMap& wide, const CUtensorMap& narrow, void* C, int wide_rows, int narrow_rows, int K, int mode,
+                int splits, const HeadsEpilogue& hp, int* error_word, cudaStream_t stream) {
+    using cfg = PairCfg<BN, FORM>;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(gemm_tc_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES) != cudaSuccess)
+        if (cudaFuncSetAttribute(gemm_tc_pair_kernel<BN, FORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES) != cudaSuccess)
             return (int)cudaGetLastError();
         configured = true;
     }
-    CUtensorMap map_a;
-    if (int e = llmx_make_map_bf16_2d(&map_a, A, (uint64_t)M, (uint64_t)K, BN / 2, BK)) return e;
-    const int w_tiles = (N + 2 * BM - 1) / (2 * BM), m_tiles = (M + BN - 1) / BN;
-    // Token tiles a group: what 24 MB hold of the tokens' rows of one k range (at least one, at most all).
+    const int w_tiles = (wide_rows + 2 * BM - 1) / (2 * BM), m_tiles = (narrow_rows + BN - 1) / BN;
+    // Narrow tiles a group: what 24 MB hold of the narrow operand's rows of one k range (at least one, at most all).
     const long long tile_bytes = (long long)BN * ((K + splits - 1) / splits) * 2;
     int group = (int)((24ll << 20) / (tile_bytes > 0 ? tile_bytes : 1));
     group = group < 1 ? 1 : group > m_tiles ? m_tiles : group;
@@ -314,7 +373,8 @@ int launch_pair(const CUtensorMap& map_w, const void* A, float* C, int M, int N,
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr;
     lc.numAttrs = llmx_pdl_enabled() ? 2 : 1;
-    cudaLaunchKernelEx(&lc, gemm_tc_pair_kernel<BN>, map_w, map_a, C, M, N, K, mode, splits, group, error_word);
+    cudaLaunchKernelEx(&lc, gemm_tc_pair_kernel<BN, FORM>, wide, narrow, C, wide_rows, narrow_rows, K, mode, splits, group,
+                       error_word, hp);
     return launch_status();
 }
 
@@ -329,17 +389,53 @@ LLMX_EXPORT int llmx_gemm_tc_pair(const void* weight_map, const void* A, float* 
     if (K <= 0 || K % 8 || ((uintptr_t)A & 15) || ((uintptr_t)C & 3)) return LLMX_ERR_UNSUPPORTED;
     if ((mode != MODE_STORE && mode != MODE_ACCUMULATE) || splits < 1 || (splits > 1 && mode != MODE_ACCUMULATE))
         return LLMX_ERR_BAD_ARGUMENT;
-    if (!g_sm_count) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || g_sm_count <= 0) g_sm_count = 148;
-    }
+    if (token_tile != 128 && token_tile != 256) return LLMX_ERR_BAD_ARGUMENT;
+    ensure_sm_count();
     const int k_blocks = (K + BK - 1) / BK;
     if (splits > k_blocks) splits = k_blocks;
     const CUtensorMap& map_w = *(const CUtensorMap*)weight_map;
-    switch (token_tile) {
-        case 128: return launch_pair<128>(map_w, A, C, M, N, K, mode, splits, error_word, stream);
-        case 256: return launch_pair<256>(map_w, A, C, M, N, K, mode, splits, error_word, stream);
-        default: return LLMX_ERR_BAD_ARGUMENT;
-    }
+    CUtensorMap map_a;
+    if (int e = llmx_make_map_bf16_2d(&map_a, A, (uint64_t)M, (uint64_t)K, token_tile / 2, BK)) return e;
+    if (token_tile == 128) return launch_pair<128, PLAIN>(map_w, map_a, C, N, M, K, mode, splits, HeadsEpilogue{}, error_word, stream);
+    return launch_pair<256, PLAIN>(map_w, map_a, C, N, M, K, mode, splits, HeadsEpilogue{}, error_word, stream);
+}
+
+// out[m, n] = silu(A W[n]^T) * (A W[n + N]^T) as bfloat16 [M, N] on pairs of SMs; the weight has 2 N rows (gate rows,
+// then up rows) and `weight_map` boxes of 128 rows.  A pair's tile: 256 outputs x 128 tokens.
+LLMX_EXPORT int llmx_gemm_tc_pair_swiglu(const void* weight_map, const void* A, void* out, int M, int N, int K,
+                                         int* error_word, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || ((uintptr_t)A & 15) || ((uintptr_t)out & 1)) return LLMX_ERR_UNSUPPORTED;
+    ensure_sm_count();
+    const CUtensorMap& map_w = *(const CUtensorMap*)weight_map;
+    CUtensorMap map_a;
+    if (int e = llmx_make_map_bf16_2d(&map_a, A, (uint64_t)M, (uint64_t)K, 64, BK)) return e;
+    return launch_pair<128, DUAL>(map_w, map_a, out, N, M, K, MODE_STORE, 1, HeadsEpilogue{}, error_word, stream);
+}
+
+// The q/k/v product of a layer whose heads are 128 wide, finished in the epilogue, on pairs of SMs: the arguments of
+// llmx_gemm_tc_heads, with the weight's map of 128-row boxes (llmx_gemm_tc_weight_map).  A pair's tile: 256 tokens x
+// two heads.
+LLMX_EXPORT int llmx_gemm_tc_pair_heads(const void* weight_map, const void* A, int tokens, int K, const float* q_weight,
+                                        const float* k_weight, float eps, const float* cos_table, const float* sin_table,
+                                        const int* positions, const int* slots, void* q_out, void* cache, int heads,
+                                        int kv_heads, int page_size, int* error_word, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (K <= 0 || K % 8 || ((uintptr_t)A & 15) || ((uintptr_t)q_out & 15) || ((uintptr_t)cache & 15))
+        return LLMX_ERR_UNSUPPORTED;
+    if (heads <= 0 || kv_heads <= 0 || page_size <= 0 || !positions || !slots || !q_out || !cache ||
+        (cos_table == nullptr) != (sin_table == nullptr))
+        return LLMX_ERR_BAD_ARGUMENT;
+    if (((uintptr_t)cos_table & 15) || ((uintptr_t)sin_table & 15)) return LLMX_ERR_UNSUPPORTED;
+    ensure_sm_count();
+    HeadsEpilogue hp;
+    hp.q_weight = q_weight; hp.k_weight = k_weight; hp.cos_table = cos_table; hp.sin_table = sin_table;
+    hp.positions = positions; hp.slots = slots;
+    hp.q_out = (__nv_bfloat16*)q_out; hp.cache = (__nv_bfloat16*)cache;
+    hp.eps = eps; hp.heads = heads; hp.kv_heads = kv_heads; hp.page_size = page_size;
+    const int features = (heads + 2 * kv_heads) * 128;
+    CUtensorMap map_tokens;
+    if (int e = llmx_make_map_bf16_2d(&map_tokens, A, (uint64_t)tokens, (uint64_t)K, BM, BK)) return e;
+    return launch_pair<256, HEADS>(map_tokens, *(const CUtensorMap*)weight_map, nullptr, tokens, features, K, MODE_STORE, 1, hp,
+                                   error_word, stream);
 }

@@ -50,8 +50,9 @@ long long llmx_rt_launches(void);                          // kernels launched t
 void llmx_rt_count_launches(long long n);                  // ... plus those a replayed recording launched
 // Entry point i (from 0) that the last dry runs (llmx_*_workspace) would have called and found unbound; 0 at the end.
 int llmx_rt_missing(int i, const char** name);
-// Whether products of many tokens may run on pairs of SMs (on at the start).  Returns the setting before.
-int llmx_rt_pair_products(int on);
+// Which products of many tokens may run on pairs of SMs: a sum of 1 (plain products), 2 (the gated product) and 4 (the
+// q/k/v product that finishes its heads); all at the start.  Returns the setting before.
+int llmx_rt_pair_products(int which);
 void llmx_rt_reset_caches(void);                           // forget what was learnt of the device and the kernel libraries
 // For tests of what a failed step leaves behind: the nth call (from now) of the entry point `name` fails on the host,
 // before anything is launched, with LLMX_RT_ERR_INJECTED.  nth <= 0 or a null name: no failure is pending.

@@ -48,6 +48,9 @@ typedef cudaStream_t S;
     X(llmx_gemm_tc_weight_map_box, (void*, const void*, int, int, int))                                                   \
     X(llmx_gemm_tc, (const void*, const void*, float*, int, int, int, int, int, int, int, int*, S))                       \
     X(llmx_gemm_tc_pair, (const void*, const void*, float*, int, int, int, int, int, int, int*, S))                       \
+    X(llmx_gemm_tc_pair_swiglu, (const void*, const void*, void*, int, int, int, int*, S))                                \
+    X(llmx_gemm_tc_pair_heads, (const void*, const void*, int, int, const float*, const float*, float, const float*,      \
+                                const float*, const int*, const int*, void*, void*, int, int, int, int*, S))              \
     X(llmx_gemm_tc_swiglu, (const void*, const void*, void*, int, int, int, int, int*, S))                                \
     X(llmx_gemm_tc_heads, (const void*, const void*, int, int, int, const float*, const float*, float, const float*,      \
                            const float*, const int*, const int*, void*, void*, int, int, int, int*, S))                   \
@@ -188,7 +191,10 @@ constexpr int HEADS_MIN_ROWS = 256;           // from this many tokens on the q/
 int gemm_schedule(int m, int n) { return m <= STREAM_K_MAX_ROWS && cdiv(n, 128) < STREAM_K_MAX_TILES ? 1 : 0; }
 
 struct GemmPlan { int schedule, token_tile, splits; };   // schedule 0: whole tiles, 1: stream-K, 2: whole tiles on pairs of SMs
-bool g_pair_products = true;
+// Which products of many tokens may run on pairs of SMs: a sum of PAIR_PLAIN, PAIR_GATED and PAIR_HEADS.
+enum : int { PAIR_PLAIN = 1, PAIR_GATED = 2, PAIR_HEADS = 4, PAIR_ALL = 7 };
+int g_pair_products = PAIR_ALL;
+constexpr int PAIR_MIN_ROWS = 256;            // gated and q/k/v products: from this many tokens on
 
 // Few tokens: stream-K.  Else whole tiles, and the token tile and the number of k ranges are chosen so that the
 // tiles fill the SMs: with a few hundred tokens a [4096, 4096] weight makes 32 to 128 tiles, which would leave most
@@ -232,11 +238,12 @@ GemmPlan gemm_plan_compute(int m, int n, int k, bool accumulate, int n_sms, bool
 
 GemmPlan gemm_plan(int m, int n, int k, bool accumulate) {
     static std::map<std::tuple<int, int, int, bool, bool>, GemmPlan> cache;
-    const auto key = std::make_tuple(m, n, k, accumulate, g_pair_products);
+    const bool pairs = g_pair_products & PAIR_PLAIN;
+    const auto key = std::make_tuple(m, n, k, accumulate, pairs);
     auto it = cache.find(key);
     if (it != cache.end()) return it->second;
     if (cache.size() > 65536) cache.clear();
-    return cache[key] = gemm_plan_compute(m, n, k, accumulate, sms(), g_pair_products);
+    return cache[key] = gemm_plan_compute(m, n, k, accumulate, sms(), pairs);
 }
 
 // Weight rows per tile (128: one head, 256: two) of the q/k/v product that finishes its heads in the epilogue, or 0
@@ -474,6 +481,8 @@ struct Linear : llmx_part {
     bool fused_gate(int rows) const { return tensor_core && (invariant() || rows > STREAM_K_MAX_ROWS); }
     int gated(Ctx& c, const void* a, int rows, void* out) {
         if (ensure_map(c)) return c.status;
+        if (!invariant() && (g_pair_products & PAIR_GATED) && rows >= PAIR_MIN_ROWS)
+            return CALL(c, llmx_gemm_tc_pair_swiglu, 1, (const void*)map128, a, out, rows, N / 2, K, c.s->error_word, c.stream);
         return CALL(c, llmx_gemm_tc_swiglu, 1, (const void*)map128, a, out, rows, N / 2, K, invariant() ? 128 : 0, c.s->error_word, c.stream);
     }
     int ensure_head_map(Ctx& c, int tile) {
@@ -647,6 +656,13 @@ struct Attention : Mixer {
         if (tile && e.dtype == LLMX_DT_BF16 && e.page_size > 0 && !decoding_only) {
             // Many rows: the product norms, rotates and stores its heads in its own epilogue.
             void* q = c.alloc((size_t)rows * q_width * 2);
+            if ((g_pair_products & PAIR_HEADS) && rows >= PAIR_MIN_ROWS) {
+                if (qkv.ensure_map(c)) return c.status;
+                CALL(c, llmx_gemm_tc_pair_heads, 1, (const void*)qkv.map128, h, rows, qkv.K, d.q_norm, d.k_norm, d.qk_norm_eps, d.cos, d.sin,
+                     positions, slots, q, (void*)e.storage, d.heads, d.kv_heads, e.page_size, s.error_word, c.stream);
+                attend(c, q, e, o_buf, rows, g);
+                return o.forward(c, o_buf, rows, residual, true, false);
+            }
             if (qkv.ensure_head_map(c, tile)) return c.status;
             CALL(c, llmx_gemm_tc_heads, 1, (const void*)qkv.head_map[tile == 256], h, rows, qkv.K, tile, d.q_norm, d.k_norm, d.qk_norm_eps,
                  d.cos, d.sin, positions, slots, q, (void*)e.storage, d.heads, d.kv_heads, e.page_size, s.error_word, c.stream);
@@ -867,9 +883,9 @@ LLMX_API void llmx_rt_reset_caches(void) {
 }
 
 LLMX_API int llmx_rt_pair_products(int on) {
-    const bool before = g_pair_products;
-    g_pair_products = on != 0;
-    return before ? 1 : 0;
+    const int before = g_pair_products;
+    g_pair_products = on & PAIR_ALL;
+    return before;
 }
 
 LLMX_API int llmx_rt_profile(int on) {
@@ -908,7 +924,7 @@ LLMX_API int llmx_rt_profile_read(int i, const char** name, float* ms, float* id
 }
 
 LLMX_API void llmx_gemm_plan(int m, int n, int k, int accumulate, int n_sms, int* schedule, int* token_tile, int* splits) {
-    const GemmPlan p = n_sms > 0 ? gemm_plan_compute(m, n, k, accumulate != 0, n_sms, g_pair_products) : gemm_plan(m, n, k, accumulate != 0);
+    const GemmPlan p = n_sms > 0 ? gemm_plan_compute(m, n, k, accumulate != 0, n_sms, g_pair_products & PAIR_PLAIN) : gemm_plan(m, n, k, accumulate != 0);
     *schedule = p.schedule, *token_tile = p.token_tile, *splits = p.splits;
 }
 LLMX_API int llmx_tiled_attention(int heads, int kv_heads, int head_dim, int page_size) {

@@ -14,6 +14,9 @@ _i, _p = ctypes.c_int, ctypes.c_void_p
 register_signature("gemm_tc", "llmx_gemm_tc_weight_map", [_p, _p, _i, _i])
 register_signature("gemm_tc", "llmx_gemm_tc", [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p])
 register_signature("gemm_tc_pair", "llmx_gemm_tc_pair", [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _p])
+register_signature("gemm_tc_pair", "llmx_gemm_tc_pair_swiglu", [_p, _p, _p, _i, _i, _i, _p, _p])
+register_signature("gemm_tc_pair", "llmx_gemm_tc_pair_heads", [_p, _p, _i, _i, _p, _p, ctypes.c_float, _p, _p, _p, _p, _p, _p,
+                                                               _i, _i, _i, _p, _p])
 register_signature("gemm_tc", "llmx_gemm_tc_swiglu", [_p, _p, _p, _i, _i, _i, _i, _p, _p])
 register_signature("gemm_tc", "llmx_gemm_tc_weight_map_box", [_p, _p, _i, _i, _i])
 register_signature("gemm_tc", "llmx_gemm_tc_heads", [_p, _p, _i, _i, _i, _p, _p, ctypes.c_float, _p, _p, _p, _p, _p, _p,
@@ -124,8 +127,9 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
 
 
 def gemm_tc_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, wmap: Optional[WeightMap] = None,
-                   token_tile: int = 0) -> torch.Tensor:
-    """out = silu(a @ w[:F].T) * (a @ w[F:].T) as bfloat16 [M, F]; w [2F, K] holds the gate rows, then the up rows."""
+                   token_tile: int = 0, pair: bool = False) -> torch.Tensor:
+    """out = silu(a @ w[:F].T) * (a @ w[F:].T) as bfloat16 [M, F]; w [2F, K] holds the gate rows, then the up rows.
+    `pair`: on pairs of SMs (csrc/gemm_tc_pair.cu), 256 outputs x 128 tokens a pair."""
     _cuda(a, w, out)
     m, k = a.shape
     f = w.shape[0] // 2
@@ -134,6 +138,10 @@ def gemm_tc_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, wmap: Op
     _need(w.shape[0] == 2 * f and w.shape[1] == k and tuple(out.shape) == (m, f), "gemm_tc_swiglu: shapes do not fit")
     _need(k % 8 == 0, "gemm_tc_swiglu: the input width must be a multiple of 8")
     wmap = wmap or weight_map(w)
+    if pair:
+        _check(_fn("gemm_tc_pair", "llmx_gemm_tc_pair_swiglu")(ctypes.c_void_p(wmap.address), _ptr(a), _ptr(out), m, f, k,
+                                                               _ptr(error_word(a.device)), _stream()), "gemm_tc_pair_swiglu")
+        return out
     _check(_fn("gemm_tc", "llmx_gemm_tc_swiglu")(ctypes.c_void_p(wmap.address), _ptr(a), _ptr(out), m, f, k,
                                                  token_tile, _ptr(error_word(a.device)), _stream()), "gemm_tc_swiglu")
     return out
@@ -151,12 +159,13 @@ def heads_tile(m: int, heads: int, kv_heads: int) -> int:
 def gemm_tc_heads(a: torch.Tensor, wmap: WeightMap, heads: int, kv_heads: int, q_weight: Optional[torch.Tensor],
                   k_weight: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor],
                   sin: Optional[torch.Tensor], positions: torch.Tensor, slots: torch.Tensor, q_out: torch.Tensor,
-                  cache: torch.Tensor) -> None:
+                  cache: torch.Tensor, pair: bool = False) -> None:
     """The q/k/v product of a layer with heads of 128, finished in its epilogue: queries and keys normed per head
     and rotated, queries to `q_out` [M, heads * 128], keys and values to their cache slots.
 
     a [M, K] bfloat16; `wmap` a `WeightMap(w, 128 | 256, heads=True)` of the stacked weight
-    [(heads + 2 kv_heads) * 128, K]; cache [pages, 2, kv_heads, page_size, 128] bfloat16; cos/sin float32
+    [(heads + 2 kv_heads) * 128, K] (`pair`: on pairs of SMs, 256 tokens x two heads a pair, with a map of 128-row
+    boxes); cache [pages, 2, kv_heads, page_size, 128] bfloat16; cos/sin float32
     [positions, 64] or None; positions and slots int32 [M] (a negative slot: the row's key and value are not stored).
     """
     _cuda(a, wmap.weight, q_weight, k_weight, cos, sin, positions, slots, q_out, cache)
@@ -177,6 +186,13 @@ def gemm_tc_heads(a: torch.Tensor, wmap: WeightMap, heads: int, kv_heads: int, q
               "gemm_tc_heads: cos and sin tables [positions, 64]")
     for nw in (q_weight, k_weight):
         _need(nw is None or (nw.dtype == torch.float32 and nw.numel() == 128), "gemm_tc_heads: norm weight")
+    if pair:
+        _need(wmap.box_rows == 128, "gemm_tc_heads: on pairs of SMs each block loads one head (boxes of 128 rows)")
+        _check(_fn("gemm_tc_pair", "llmx_gemm_tc_pair_heads")(
+            ctypes.c_void_p(wmap.address), _ptr(a), m, k, _ptr(q_weight), _ptr(k_weight), float(eps),
+            _ptr(cos), _ptr(sin), _ptr(positions), _ptr(slots), _ptr(q_out), _ptr(cache), heads, kv_heads,
+            cache.shape[3], _ptr(error_word(a.device)), _stream()), "gemm_tc_pair_heads")
+        return
     _check(_fn("gemm_tc", "llmx_gemm_tc_heads")(
         ctypes.c_void_p(wmap.address), _ptr(a), m, k, wmap.box_rows, _ptr(q_weight), _ptr(k_weight), float(eps),
         _ptr(cos), _ptr(sin), _ptr(positions), _ptr(slots), _ptr(q_out), _ptr(cache), heads, kv_heads,

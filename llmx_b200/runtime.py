@@ -130,6 +130,7 @@ KERNEL_LIBS: Dict[str, str] = {
     "llmx_gemm_plain": "gemm_plain", "llmx_attention_plain": "attention_plain",
     "llmx_gemm_tc_weight_map": "gemm_tc", "llmx_gemm_tc_weight_map_box": "gemm_tc", "llmx_gemm_tc": "gemm_tc",
     "llmx_gemm_tc_swiglu": "gemm_tc", "llmx_gemm_tc_heads": "gemm_tc", "llmx_gemm_tc_pair": "gemm_tc_pair",
+    "llmx_gemm_tc_pair_swiglu": "gemm_tc_pair", "llmx_gemm_tc_pair_heads": "gemm_tc_pair",
     "llmx_attn_cache_map": "attention_decode", "llmx_attn_decode_fused": "attention_decode",
     "llmx_attn_decode_qkv": "attention_decode", "llmx_attn_decode_max_clusters": "attention_decode",
     "llmx_attn_prefill_tc_cache_map": "attention_prefill_tc", "llmx_attn_prefill_tc": "attention_prefill_tc",
@@ -267,9 +268,11 @@ def gemm_plan(m: int, n: int, k: int, accumulate: bool, sms: int = 0):
     return s.value, t.value, r.value
 
 
-def pair_products(on: bool) -> bool:
-    """Products of many tokens may run on pairs of SMs (csrc/gemm_tc_pair.cu; on at the start).  Returns the setting before."""
-    return bool(lib().llmx_rt_pair_products(1 if on else 0))
+def pair_products(which) -> int:
+    """Which products of many tokens may run on pairs of SMs (csrc/gemm_tc_pair.cu): a sum of 1 (plain products), 2 (the
+    gated product) and 4 (the q/k/v product that finishes its heads); True: all (as at the start), False: none.
+    Returns the setting before."""
+    return lib().llmx_rt_pair_products(7 if which is True else 0 if which is False else int(which))
 
 
 def heads_tile(m: int, heads: int, kv_heads: int, sms: int = 0) -> int:

@@ -564,23 +564,27 @@ def test_gemm_tensor_core_stream_k(m, n, k):
     assert (acc.cpu().double() - (ref + base.cpu().double())).abs().max() <= 3e-5 * max(1.0, ref.abs().max())
 
 
+@pytest.mark.parametrize("pair", [False, True])
 @pytest.mark.parametrize("m", [1, 16, 70, 128, 300])
 @pytest.mark.parametrize("f,k", [(128, 64), (172, 104), (200, 128), (1536, 512)])
-def test_gemm_tensor_core_gated(m, f, k):
-    """silu(gate) * up in the product's epilogue, for intermediate widths that are no multiple of a tile."""
+def test_gemm_tensor_core_gated(m, f, k, pair):
+    """silu(gate) * up in the product's epilogue, for intermediate widths that are no multiple of a tile; on single
+    blocks and on pairs of SMs."""
     from llmx_b200 import ops_tc
     g = torch.Generator().manual_seed(13)
     a = _bf16(torch.randn(m, k, generator=g)).to(DEV)
     w = _bf16(torch.randn(2 * f, k, generator=g) * 0.2).to(DEV)
-    out = torch.empty(m, f, dtype=torch.bfloat16, device=DEV)
-    ops_tc.gemm_tc_swiglu(a, w, out)
+    guard = torch.full((m + 2, f), 3.0, dtype=torch.bfloat16, device=DEV)
+    out = guard[1:m + 1]
+    ops_tc.gemm_tc_swiglu(a, w, out, pair=pair)
     ops_tc.check_errors()
+    assert torch.all(guard[0] == 3.0) and torch.all(guard[m + 1] == 3.0)
     gu = (a.float().cpu().double() @ w.float().cpu().double().T).numpy()
     ref = plain.silu(gu[:, :f].astype(np.float32)) * gu[:, f:].astype(np.float32)
     assert np.abs(out.float().cpu().numpy() - ref).max() <= 2 ** -7 * max(1.0, np.abs(ref).max())
 
 
-@pytest.mark.parametrize("tile", [128, 256])
+@pytest.mark.parametrize("tile", [128, 256, "pair"])
 @pytest.mark.parametrize("m,heads,kv_heads,k,rotate,norm", [(70, 4, 2, 64, True, True), (300, 3, 1, 200, True, True),
                                                             (129, 2, 2, 512, False, True), (1000, 5, 1, 136, True, False)])
 def test_gemm_tensor_core_finishes_heads(tile, m, heads, kv_heads, k, rotate, norm):
@@ -602,8 +606,9 @@ def test_gemm_tensor_core_finishes_heads(tile, m, heads, kv_heads, k, rotate, no
     slots[5] = -1
     cache = torch.zeros(pages, 2, kv_heads, page, D, dtype=torch.bfloat16, device=DEV)
     q_out = torch.zeros(m, heads * D, dtype=torch.bfloat16, device=DEV)
-    ops_tc.gemm_tc_heads(a, ops_tc.WeightMap(w, tile, heads=True), heads, kv_heads, qw, kw, 1e-6, cos, sin,
-                         positions.to(DEV), slots.to(DEV), q_out, cache)
+    pair = tile == "pair"       # on pairs of SMs: 256 tokens x two heads a pair, each block loads one head
+    ops_tc.gemm_tc_heads(a, ops_tc.WeightMap(w, 128 if pair else tile, heads=True), heads, kv_heads, qw, kw, 1e-6, cos, sin,
+                         positions.to(DEV), slots.to(DEV), q_out, cache, pair=pair)
     ops_tc.check_errors()
 
     qkv = torch.empty(m, w.shape[0], device=DEV)
