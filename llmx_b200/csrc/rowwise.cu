@@ -77,21 +77,24 @@ __device__ __forceinline__ void store4(__nv_bfloat16* dst, float a, float b, flo
 }
 
 // `zero` (optional): a float buffer of `zero_count` values (a multiple of 4, 16-byte aligned) that the launch
-// clears, shared out over its blocks: the output of the product that follows, when that product adds its
-// pieces with atomics.
+// clears with blocks of its own (those beyond `rows`): the output of the product that follows, when that product
+// adds its pieces with atomics.
 template <typename OutT>
 __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, OutT* __restrict__ y,
-                                   const int* __restrict__ row_index, int width, float eps, float* __restrict__ zero,
-                                   long long zero_count) {
+                                   const int* __restrict__ row_index, int rows, int width, float eps,
+                                   float* __restrict__ zero, long long zero_count) {
     pdl_trigger();
     pdl_wait();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
-    if (zero) {
+    if (r >= rows) {
+        // Blocks beyond the rows only clear: with a few rows, a few blocks would store for longer than the norm takes.
         float4* z = reinterpret_cast<float4*>(zero);
         const long long n4 = zero_count >> 2;
-        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x)
+        const long long blocks = gridDim.x - rows;
+        for (long long i = (long long)(r - rows) * blockDim.x + threadIdx.x; i < n4; i += blocks * blockDim.x)
             z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        return;
     }
     const float4* src = reinterpret_cast<const float4*>(x + (size_t)(row_index ? row_index[r] : r) * width);
     const float4* wv = reinterpret_cast<const float4*>(w);
@@ -133,10 +136,14 @@ LLMX_EXPORT int llmx_rmsnorm(const float* x, const float* w, void* y, int out_dt
         // The block width depends on the row width alone, so a row's sum has one order whatever the batch.
         int threads = ((n4 + 3) / 4 + 31) / 32 * 32;
         threads = threads < 32 ? 32 : threads > 256 ? 256 : threads;
+        // Clearing: blocks of their own, each about 16 KB (four 16-byte stores a thread), at most 1,024 of them.
+        long long zero_blocks = zero ? (zero_count / 4 + 4 * threads - 1) / (4 * threads) : 0;
+        zero_blocks = zero_blocks > 1024 ? 1024 : zero_blocks;
+        const dim3 grid((unsigned)(rows + zero_blocks));
         if (out_dtype == LLMX_BF16)
-            launch_kernel(rmsnorm_vec_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, x, w, (__nv_bfloat16*)y, row_index, width, eps, zero, zero_count);
+            launch_kernel(rmsnorm_vec_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, x, w, (__nv_bfloat16*)y, row_index, rows, width, eps, zero, zero_count);
         else
-            launch_kernel(rmsnorm_vec_kernel<float>, dim3(rows), dim3(threads), 0, stream, x, w, (float*)y, row_index, width, eps, zero, zero_count);
+            launch_kernel(rmsnorm_vec_kernel<float>, grid, dim3(threads), 0, stream, x, w, (float*)y, row_index, rows, width, eps, zero, zero_count);
         return launch_status();
     }
     if (zero && cudaMemsetAsync(zero, 0, (size_t)zero_count * sizeof(float), stream) != cudaSuccess) return launch_status();
