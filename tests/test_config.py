@@ -109,12 +109,23 @@ def test_matrix_product_plan_fills_the_sms():
     # few tokens: stream-K; the logits head has tiles enough and keeps whole tiles, unsplit
     assert ops_tc._plan(8, 4096, 4096, True, sms) == (1, 0, 1)
     assert ops_tc._plan(8, 151936, 4096, False, sms) == (0, 0, 1)
-    # a few hundred tokens on a [4096, 4096] weight: 32 to 64 tiles would idle most SMs, so K is cut
+    # a few hundred tokens on a [4096, 4096] weight: 32 to 64 tiles would idle most SMs, so K is cut; whole tiles run on
+    # single blocks (schedule 0: 128 weight rows a tile) or on pairs of SMs (schedule 2: 256 weight rows a pair)
     for m in (96, 128, 256, 512):
         schedule, tile, splits = ops_tc._plan(m, 4096, 4096, True, sms)
-        assert schedule == 0 and tile in (128, 256) and splits >= 2
-        tiles = -(-4096 // 128) * -(-m // tile) * splits
-        assert tiles >= 96
+        assert schedule in (0, 2) and tile in (128, 256)
+        units = -(-4096 // (256 if schedule == 2 else 128)) * -(-m // tile) * splits
+        assert units >= (48 if schedule == 2 else 96)          # of 74 pairs, of 148 blocks
+        assert splits >= 2 or units >= (64 if schedule == 2 else 128)
+    from llmx_b200 import runtime
+    before = runtime.pair_products(False)
+    try:
+        for m in (96, 128, 256, 512):
+            schedule, tile, splits = ops_tc._plan(m, 4096, 4096, True, sms)
+            assert schedule == 0 and tile in (128, 256) and splits >= 2
+            assert -(-4096 // 128) * -(-m // tile) * splits >= 96
+    finally:
+        runtime.pair_products(before)
     # many tokens: whole tiles fill the SMs by themselves
     assert ops_tc._plan(4096, 6144, 4096, False, sms)[2] == 1
     # k ranges never outnumber the k blocks
