@@ -44,7 +44,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "attention_prefill_tc": ["attention_prefill_tc.cu"],
     "sampling": ["sampling.cu"],
     "selftest": ["selftest.cu"],              # the bounded wait made to run out on purpose (tests)
-    "runtime": ["runtime/runtime.cpp"],       # host code: the parts' forward passes (no kernels of its own)
+    "runtime": ["runtime/runtime.cpp", "runtime/engine.cpp", "runtime/loader.cpp"],       # host code: the parts' forward passes (no kernels of its own)
 }
 
 _lock = threading.Lock()

@@ -67,7 +67,9 @@ typedef cudaStream_t S;
     X(llmx_attn_prefill_tc, (const void*, const void*, void*, int, const int*, int, const int*, const int*, const int*,   \
                              const int*, int, int, int, int, int, int, float, int, int, int, float*, int*, S))            \
     X(llmx_attn_prefill, (const void*, const void*, void*, const int*, int, const int*, const int*, const int*,           \
-                          const int*, int, int, int, int, int, int, float, int, int*, S))
+                          const int*, int, int, int, int, int, int, float, int, int*, S))                                 \
+    X(llmx_sample, (const float*, int, int, const void*, int*, int, S))                                                   \
+    X(llmx_penalize, (float*, int, const int*, const int*, const int*, const float*, const float*, const float*, int, S))
 
 struct Kernels {
 #define X(name, args) int(*name) args = nullptr;
@@ -843,6 +845,19 @@ LLMX_API int llmx_rt_bind(const char* name, void* function) {
     if (!name || !function) return fail(LLMX_RT_ERR_BAD_ARGUMENT, "llmx_rt_bind: a name and a function");
     if (!bind(name, function)) return fail(LLMX_RT_ERR_BAD_ARGUMENT, std::string("llmx_rt_bind: the runtime calls no kernel named ") + name);
     return 0;
+}
+
+// A bound entry point by name, for the engine's own calls (the sampler's kernels); null when it is not bound, and the
+// name is then noted as missing like a dry run's.
+LLMX_API void* llmx_rt_kernel(const char* name) {
+#define X(kname, args)                                                  \
+    if (!strcmp(name, #kname)) {                                        \
+        if (!kern.kname) note_missing(#kname);                          \
+        return reinterpret_cast<void*>(kern.kname);                     \
+    }
+    LLMX_KERNELS(X)
+#undef X
+    return nullptr;
 }
 
 LLMX_API int llmx_rt_load_kernels(const char* folder) {

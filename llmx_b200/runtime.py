@@ -135,6 +135,7 @@ KERNEL_LIBS: Dict[str, str] = {
     "llmx_attn_decode_qkv": "attention_decode", "llmx_attn_decode_max_clusters": "attention_decode",
     "llmx_attn_prefill_tc_cache_map": "attention_prefill_tc", "llmx_attn_prefill_tc": "attention_prefill_tc",
     "llmx_attn_prefill": "attention_prefill",
+    "llmx_sample": "sampling", "llmx_penalize": "sampling",
 }
 
 _lib = None

@@ -1,0 +1,221 @@
+"""The native engine (csrc/runtime/llmx_engine.h) through its thin Python face: the same traces and the same
+generation as the Python engine, with the cache's bookkeeping, the step's metadata, the scheduler and the sampler's
+state in C++."""
+import numpy as np
+import pytest
+
+import helpers
+from configs import CONFIGS, BF16_BUDGET, BF16_UNCALIBRATED
+
+pytestmark = pytest.mark.gpu
+
+
+def tol(dtype, name):
+    return 1e-4 if dtype == "float32" else BF16_BUDGET.get(name, BF16_UNCALIBRATED)
+
+
+class AsEngine:
+    """The native engine behind the two calls `helpers.run_trace` makes."""
+
+    def __init__(self, native):
+        self.native, self.ids, self.next = native, {}, 1000
+
+    def _id(self, name):
+        if name not in self.ids:
+            self.ids[name], self.next = self.next, self.next + 1
+        return self.ids[name]
+
+    def step(self, entries, record=False):
+        import torch
+        rows = self.native.forward([(self._id(e.request_id), list(e.tokens), list(e.want)) for e in entries])
+        return torch.from_numpy(rows) if rows.shape[0] else None
+
+    def end(self, name):
+        self.native.end(self._id(name))
+        self.ids.pop(name, None)
+
+
+LENGTHS = [70, 1, 9, 40, 133, 33]
+
+
+def _requests(name):
+    vocab = CONFIGS[name][0]["vocab_size"]
+    return {f"r{i}": helpers.random_ids(vocab, n, seed=100 * i + n) for i, n in enumerate(LENGTHS)}
+
+
+def _python_engine(folder, dtype, page, kv_tokens, max_requests=4):
+    from llmx_b200.engine import Engine, EngineOptions
+    return Engine.from_dir(folder, EngineOptions(dtype=dtype, kv_tokens=kv_tokens, page_size=page, max_requests=max_requests))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("cutting", ["whole", "tail", "portions", "mixed"])
+def test_native_engine_replays_the_traces(model_dirs, name, dtype, cutting):
+    """Whole prompts, the last tokens one by one, portions of changing size, and requests mixed over so few pages that
+    they are used again: the native engine's logits against the plain implementation, and its cache's books after
+    every trace (no page lost, held twice or freed twice)."""
+    from llmx_b200.native_engine import NativeEngine
+    folder, page = model_dirs[name][0 if dtype == "bfloat16" else 1], model_dirs[name][2]
+    requests = _requests(name)
+    make = {"whole": helpers.trace_whole, "tail": lambda r: helpers.trace_tail_decoded(r, 12), "portions": helpers.trace_portions,
+            "mixed": helpers.trace_mixed}[cutting]
+    steps = make(requests)
+    kv_tokens = helpers.tokens_needed(steps)
+    engine = _python_engine(folder, dtype, page, kv_tokens)
+    native = NativeEngine.over(engine)
+    got = helpers.run_trace(AsEngine(native), steps)
+    native.check()
+    total, free = native.pages()[0]
+    assert free == total                                  # every request of a trace ends
+    worst, scale, where = helpers.compare(got, requests, folder, dtype == "bfloat16")
+    assert worst <= tol(dtype, name) * scale, where
+    native.close()
+
+
+def test_native_engine_refuses_and_rolls_back(model_dirs):
+    """A batch it does not take, and pages that do not suffice: an error by name, and every request as it was."""
+    from llmx_b200.native_engine import NativeEngine, NativeEngineError, ERR_CACHE, ERR_REFUSED
+    folder, page = model_dirs["A"][1], model_dirs["A"][2]
+    vocab = CONFIGS["A"][0]["vocab_size"]
+    native = NativeEngine.over(_python_engine(folder, "float32", page, 4 * page), kv_tokens=4 * page)
+    ids = helpers.random_ids(vocab, 3 * page, seed=1)
+    first = native.forward([(1, ids, [len(ids) - 1])])
+    for bad, text in (([(1, [vocab], [0])], "outside the vocabulary"), ([(2, [], [])], "without tokens"),
+                      ([(2, [1, 2], [2])], "wanted place"), ([(2, [1], []), (2, [1], [])], "appears twice")):
+        with pytest.raises(NativeEngineError) as err:
+            native.forward(bad)
+        assert err.value.code == ERR_REFUSED and text in str(err.value)
+    with pytest.raises(NativeEngineError) as err:
+        native.forward([(1, [5], [0]), (2, helpers.random_ids(vocab, 2 * page, seed=2), [])])      # request 2 cannot fit
+    assert err.value.code == ERR_CACHE
+    native.check()
+    assert native.length(1) == len(ids) and native.length(2) == 0 and native.held_pages(1) == 3
+    # the same prompt again from the start, after a roll-back: the same logits
+    native.truncate(1, 0)
+    assert native.held_pages(1) == 0
+    again = native.forward([(1, ids, [len(ids) - 1])])
+    assert np.array_equal(first, again)
+    native.end(1)
+    native.check()
+    native.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_native_engine_generates_what_the_python_engine_generates(model_dirs, dtype):
+    """add_request / step: greedy and seeded draws, prompts longer than a step's token budget, more requests than run at
+    once.  The replies equal `LLM.generate`'s, which runs the same kernels under a scheduler of the same policy."""
+    from llmx_b200.engine.generate import LLM
+    from llmx_b200.native_engine import NativeEngine
+    from llmx_b200.sampling import SamplingParams
+    name = "B"
+    folder, page = model_dirs[name][0 if dtype == "bfloat16" else 1], model_dirs[name][2]
+    vocab = CONFIGS[name][0]["vocab_size"]
+    prompts = [helpers.random_ids(vocab, n, seed=40 + n) for n in (1, 9, 40, 70, 23)]
+    params = [SamplingParams(max_tokens=12, temp=0.0, top_k=0, top_p=1.0, ignore_eos=True),
+              SamplingParams(max_tokens=9, temp=0.8, top_k=20, top_p=0.9, seed=7, ignore_eos=True),
+              SamplingParams(max_tokens=14, temp=1.0, top_k=0, top_p=1.0, min_p=0.05, seed=11, ignore_eos=True),
+              SamplingParams(max_tokens=6, temp=0.7, penalty=1.3, presence_penalty=0.5, frequency_penalty=0.2, seed=3, ignore_eos=True),
+              SamplingParams(max_tokens=10, temp=0.0, top_k=0, top_p=1.0, ignore_eos=True)]
+    engine = _python_engine(folder, dtype, page, 1024, max_requests=3)
+    llm = LLM(engine, ubatch=32, max_seqs=3)
+    want = [(o.tokens, o.finish_reason) for o in llm.generate(prompts, params)]
+    native = NativeEngine.over(engine, ubatch=32, max_requests=3)
+    got = native.generate(prompts, params)
+    assert got == want
+    native.check()
+    assert all(free == total for total, free in native.pages())
+    native.close()
+
+
+def test_native_engine_pauses_the_latest_request_when_pages_run_out(model_dirs):
+    """Prompt-only reservation over a small pool: pages run out while decoding, the request admitted last gives its
+    pages back and recomputes later, and every reply is what the request gives alone."""
+    from llmx_b200.native_engine import NativeEngine
+    from llmx_b200.sampling import SamplingParams
+    folder, page = model_dirs["A"][1], model_dirs["A"][2]
+    vocab = CONFIGS["A"][0]["vocab_size"]
+    prompts = [helpers.random_ids(vocab, n, seed=60 + n) for n in (20, 25, 30)]
+    p = SamplingParams(max_tokens=40, temp=0.0, top_k=0, top_p=1.0, ignore_eos=True)
+    roomy = NativeEngine.over(_python_engine(folder, "float32", page, 1024), ubatch=64)
+    alone = [roomy.generate([q], p)[0] for q in prompts]
+    roomy.close()
+    pool = ((30 + 40 + page - 1) // page + 4) * page          # one request alone fits with a little to spare, three do not
+    tight = NativeEngine.over(_python_engine(folder, "float32", page, pool), kv_tokens=pool, ubatch=64, reserve="prompt")
+    got = tight.generate(prompts, p)
+    assert tight.preemptions > 0
+    assert got == alone
+    tight.check()
+    tight.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
+def test_native_loader_reads_a_model_folder(model_dirs, name, dtype):
+    """`NativeEngine.load`: config.json and the safetensors file read by the native loader (its own JSON reader, its
+    own rotation tables, weights stacked and converted on the host), a mixed trace against the plain implementation."""
+    from llmx_b200.native_engine import NativeEngine
+    folder, page = model_dirs[name][0 if dtype == "bfloat16" else 1], model_dirs[name][2]
+    requests = _requests(name)
+    steps = helpers.trace_mixed(requests)
+    native = NativeEngine.load(folder, dtype=dtype, kv_tokens=helpers.tokens_needed(steps), page_size=page, max_requests=4)
+    got = helpers.run_trace(AsEngine(native), steps)
+    native.check()
+    worst, scale, where = helpers.compare(got, requests, folder, dtype == "bfloat16")
+    assert worst <= tol(dtype, name) * scale, where
+    native.close()
+
+
+def test_native_loader_converts_between_stored_and_path_types(model_dirs):
+    """A bfloat16 folder run in float32 (widened exactly) and a float32 folder run in bfloat16 (rounded to nearest even):
+    the same logits as the Python engine gives for the same folder and path."""
+    from llmx_b200.native_engine import NativeEngine
+    from llmx_b200.engine import StepEntry
+    name = "A"
+    vocab, page = CONFIGS[name][0]["vocab_size"], model_dirs[name][2]
+    ids = helpers.random_ids(vocab, 40, seed=5)
+    for folder, dtype in ((model_dirs[name][0], "float32"), (model_dirs[name][1], "bfloat16")):
+        native = NativeEngine.load(folder, dtype=dtype, kv_tokens=256, page_size=page)
+        got = native.forward([(1, ids, list(range(len(ids))))])
+        native.close()
+        engine = _python_engine(folder, dtype, page, 256)
+        want = engine.step([StepEntry("a", ids, list(range(len(ids))))]).float().cpu().numpy()
+        scale = np.abs(want).max()
+        assert np.abs(got - want).max() <= (1e-5 if dtype == "float32" else tol(dtype, name)) * scale
+
+
+def test_a_cpp_program_generates_through_the_native_engine(model_dirs, tmp_path):
+    """tests/native/drive_engine.cpp: `llmx::Engine::load`, `add_request`, `step` with no Python in the process; its
+    replies equal the Python engine's."""
+    import os
+    import subprocess
+    from llmx_b200.csrc import build
+    from llmx_b200.engine.generate import LLM
+    from llmx_b200.sampling import SamplingParams
+    name = "B"
+    folder, page = model_dirs[name][1], model_dirs[name][2]
+    vocab = CONFIGS[name][0]["vocab_size"]
+    prompts = [helpers.random_ids(vocab, n, seed=70 + n) for n in (5, 33, 12)]
+    llm = LLM(_python_engine(folder, "float32", page, 512), ubatch=16, max_seqs=2)
+    greedy = SamplingParams(max_tokens=8, temp=0.0, top_k=0, top_p=1.0, ignore_eos=True)
+    seeded = SamplingParams(max_tokens=8, temp=0.9, top_k=10, top_p=0.9, seed=5, ignore_eos=True)
+    want = [o.tokens for o in llm.generate(prompts, [greedy, seeded, greedy])]
+    # every kernel library the run needs, built and in one folder
+    runtime_so = build.build("runtime")
+    for lib in ("rowwise", "gemm_plain", "attention_plain", "sampling"):
+        build.build(lib)
+    kernel_dir = os.path.dirname(runtime_so)
+    here = os.path.dirname(os.path.abspath(__file__))
+    exe = str(tmp_path / "drive_engine")
+    include = os.path.join(os.path.dirname(build.__file__), "runtime")
+    cmd = [build._nvcc(), "-O1", "-std=c++17", "-I", include, "-o", exe, os.path.join(here, "native", "drive_engine.cpp"),
+           runtime_so, "-Xlinker", "-rpath", "-Xlinker", kernel_dir]
+    done = subprocess.run(cmd, capture_output=True, text=True)
+    assert done.returncode == 0, done.stdout + done.stderr
+    lines = []
+    for ids, kind in zip(prompts, ("greedy", "seeded", "greedy")):
+        lines.append(kind + " " + " ".join(str(t) for t in ids))
+    out = subprocess.run([exe, folder, kernel_dir, str(page)], input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    got = [[int(t) for t in line.split()] for line in out.stdout.strip().splitlines()]
+    assert got == want
