@@ -15,8 +15,10 @@
 namespace llmx_engine_detail {
 
 thread_local std::string g_error;
+thread_local int g_code = 0;
 int fail(int code, const std::string& what) {
     g_error = what;
+    g_code = code;
     return code;
 }
 
@@ -130,7 +132,7 @@ void StateSlots::give_back(int s) {
 // slots, the one its state lies in and a spare that a step writes; commit swaps them, so a failed step leaves the
 // state as it was (the reference keeps checkpoints of its state slots to the same end, src/model/kv_cache.hpp:183-278).
 // ---------------------------------------------------------------------------------------------------------------
-Cache::Cache(const llmx_engine_desc& d) : page_size(d.page_size), max_requests(d.max_requests), kv_dtype(d.kv_dtype) {
+Cache::Cache(const llmx_engine_desc& d, bool books_only) : page_size(d.page_size), max_requests(d.max_requests), kv_dtype(d.kv_dtype) {
     if (page_size <= 0) throw Failure{LLMX_ENGINE_ERR_REFUSED, "page_size must be positive"};
     entries.assign(d.entries, d.entries + d.n_entries);
     const long long window_tokens = d.window_kv_tokens > 0 ? d.window_kv_tokens : d.kv_tokens;
@@ -155,6 +157,8 @@ Cache::Cache(const llmx_engine_desc& d) : page_size(d.page_size), max_requests(d
     if ((int)groups.size() > LLMX_MAX_GROUPS)
         throw Failure{LLMX_ENGINE_ERR_REFUSED, "a model may have " + std::to_string(LLMX_MAX_GROUPS) + " cache groups at most"};
     slots = StateSlots(has_state ? 2 * max_requests : 0);
+    state_storage.assign(entries.size(), nullptr);
+    if (books_only) return;
     // Storage, zero-filled: a kernel may load (and mask) slots of a page that were never written.
     views = llmx_caches_create((int)entries.size());
     const size_t elem = kv_dtype == LLMX_DT_BF16 ? 2 : 4;
@@ -169,7 +173,6 @@ Cache::Cache(const llmx_engine_desc& d) : page_size(d.page_size), max_requests(d
                                    gr.kv_heads, page_size, gr.head_dim))
                 throw Failure{LLMX_ENGINE_ERR_REFUSED, std::string("cache entry: ") + llmx_rt_last_error()};
     }
-    state_storage.assign(entries.size(), nullptr);
     for (size_t i = 0; i < entries.size(); ++i) {
         if (entries[i].kind != 2) continue;
         const size_t bytes = std::max<size_t>((size_t)slots.count() * (size_t)entries[i].state_bytes, 256);
@@ -496,14 +499,16 @@ using namespace llmx_engine_detail;
 
 llmx_engine::llmx_engine(llmx_model* m, const llmx_engine_desc& d, std::unique_ptr<LoadedModel> own)
     : owned(std::move(own)), model(m), vocab(d.vocab), max_positions(d.max_positions),
-      position_streams(std::max(d.position_streams, 1)), device(d.device) {
-    if (!model) throw Failure{LLMX_ENGINE_ERR_REFUSED, "an engine needs a model"};
+      position_streams(std::max(d.position_streams, 1)), device(d.device), books_only(m == nullptr && d.device < 0) {
+    if (!model && !books_only) throw Failure{LLMX_ENGINE_ERR_REFUSED, "an engine needs a model"};
     if (d.vocab <= 0 || d.max_positions <= 0 || d.max_requests <= 0 || d.n_entries < 0 || d.kv_tokens < 0)
         throw Failure{LLMX_ENGINE_ERR_REFUSED, "an engine needs a vocabulary, a context length and room for at least one request"};
     if (d.kv_dtype != LLMX_DT_BF16 && d.kv_dtype != LLMX_DT_F32) throw Failure{LLMX_ENGINE_ERR_REFUSED, "the cache holds bfloat16 or float32"};
-    cuda_check(cudaSetDevice(device), "choosing the device");
-    cuda_check(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), "creating the engine's stream");
-    cache.reset(new Cache(d));
+    if (!books_only) {
+        cuda_check(cudaSetDevice(device), "choosing the device");
+        cuda_check(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), "creating the engine's stream");
+    }
+    cache.reset(new Cache(d, books_only));
     sched.cache = cache.get();
     sched.max_positions = max_positions;
     sched.max_batch_tokens = d.max_batch_tokens > 0 ? d.max_batch_tokens : 512;
@@ -511,6 +516,7 @@ llmx_engine::llmx_engine(llmx_model* m, const llmx_engine_desc& d, std::unique_p
     sched.max_queue = d.max_queue;
     sched.reserve_prompt_only = d.reserve_prompt_only != 0;
     sched.eos_ids.assign(d.eos_ids, d.eos_ids + (d.eos_ids ? d.n_eos : 0));
+    if (books_only) return;
     cuda_check(cudaMalloc(&error_word, sizeof(int)), "allocating the error word");
     cuda_check(cudaMemset(error_word, 0, sizeof(int)), "clearing the error word");
     cuda_check(cudaMalloc(&counters, LLMX_COUNTERS * sizeof(int)), "allocating the counters");
@@ -518,6 +524,7 @@ llmx_engine::llmx_engine(llmx_model* m, const llmx_engine_desc& d, std::unique_p
     for (Pinned& p : ring) cuda_check(cudaEventCreateWithFlags(&p.done, cudaEventDisableTiming), "creating an event");
 }
 llmx_engine::~llmx_engine() {
+    if (books_only) return;
     if (stream) cudaStreamSynchronize(stream);
     for (Pinned& p : ring) {
         if (p.host) cudaFreeHost(p.host);
@@ -597,6 +604,11 @@ void llmx_engine::run(const std::vector<Batch>& batch) {
         for (size_t i = 0; i < batch.size(); ++i) {
             caches[i]->prepare((int)batch[i].tokens.size());
             prepared.push_back(caches[i]);
+        }
+        if (books_only) {          // the books alone: the pages are reserved, nothing runs
+            for (RequestCache* rc : caches) rc->commit();
+            ++steps;
+            return;
         }
 
         // ---- the metadata: one int32 buffer, sections padded to 16 bytes (the layout of llmx_step) ----
@@ -787,6 +799,7 @@ static int guarded(F&& f) {
 }
 
 LLMX_API const char* llmx_engine_last_error(void) { return g_error.c_str(); }
+LLMX_API int llmx_engine_last_code(void) { return g_code; }
 
 LLMX_API void llmx_sampling_defaults(llmx_sampling* p) {
     *p = llmx_sampling{64, 0.8f, 40, 0.95f, 0.0f, 1.0f, 0.0f, 0.0f, 0ull, 0, nullptr, 0};
@@ -809,7 +822,7 @@ LLMX_API void llmx_engine_destroy(llmx_engine* e) { delete e; }
 LLMX_API int llmx_engine_forward(llmx_engine* e, const llmx_entry* entries, int n, float* out, const float** device_logits) {
     return guarded([&] {
         if (!e || (n > 0 && !entries)) throw Failure{LLMX_ENGINE_ERR_REFUSED, "llmx_engine_forward: an engine and entries"};
-        cuda_check(cudaSetDevice(e->device), "choosing the device");
+        if (!e->books_only) cuda_check(cudaSetDevice(e->device), "choosing the device");
         std::vector<Batch> batch;
         for (int i = 0; i < n; ++i) {
             Batch b;
@@ -819,6 +832,7 @@ LLMX_API int llmx_engine_forward(llmx_engine* e, const llmx_entry* entries, int 
             batch.push_back(std::move(b));
         }
         e->run(batch);
+        if (e->books_only) return 0;
         if (out && e->last_wanted > 0)
             cuda_check(cudaMemcpyAsync(out, e->logits.ptr, (size_t)e->last_wanted * e->vocab * sizeof(float), cudaMemcpyDeviceToHost, e->stream),
                        "reading the logits");
@@ -869,47 +883,136 @@ LLMX_API long long llmx_engine_add_request(llmx_engine* e, const int* ids, int n
     return err ? -(long long)err : id;
 }
 
+// The first half of a step: give back what is to be given back, plan, and say which requests ended without running.
+// Leaves the planned entries in `planned`; returns false when there is nothing to run.
+bool llmx_engine::begin_step(std::vector<llmx_step_result>& early) {
+    auto release = [&] {
+        for (long long id : sched.to_release) cache->free_request(id);
+        sched.to_release.clear();
+    };
+    release();
+    std::vector<std::shared_ptr<Request>> ended;
+    planned = sched.plan(ended);
+    release();
+    for (const auto& r : ended) early.push_back(llmx_step_result{r->id, -1, r->finished});
+    if (planned.empty() && !sched.idle() && ended.empty())
+        throw Failure{LLMX_ENGINE_ERR_REFUSED, "the scheduler planned an empty step while requests are waiting"};
+    return !planned.empty();
+}
+// The planned entries through the model (or, for the books alone, through the cache's books); who wants a token.
+std::vector<Request*> llmx_engine::run_planned() {
+    std::vector<Batch> batch;
+    std::vector<Request*> wanting;
+    for (const Planned& p : planned) {
+        Batch b;
+        b.request = p.request->id;
+        b.tokens = p.tokens;
+        if (p.want_last) {
+            b.want.push_back((int)p.tokens.size() - 1);
+            wanting.push_back(p.request.get());
+        }
+        batch.push_back(std::move(b));
+    }
+    // The sampler's kernels must be there before the step changes anything.
+    if (!books_only && !wanting.empty() && (!llmx_rt_kernel("llmx_sample") || !llmx_rt_kernel("llmx_penalize")))
+        throw Failure{LLMX_ENGINE_ERR_UNBOUND, "kernel llmx_sample is not bound (its library was not loaded)"};
+    run(batch);
+    return wanting;
+}
+// The second half: book the tokens drawn for the entries that wanted one.
+std::vector<llmx_step_result> llmx_engine::finish_step(const std::vector<int>& drawn) {
+    std::vector<llmx_step_result> out = sched.complete(planned, drawn);
+    planned.clear();
+    for (long long id : sched.to_release) cache->free_request(id);
+    sched.to_release.clear();
+    return out;
+}
+
 LLMX_API int llmx_engine_step(llmx_engine* e, llmx_step_result* out, int capacity) {
     int written = 0;
     const int err = guarded([&] {
         if (!e || (capacity > 0 && !out)) throw Failure{LLMX_ENGINE_ERR_REFUSED, "llmx_engine_step: an engine and room for results"};
+        if (e->books_only) throw Failure{LLMX_ENGINE_ERR_REFUSED, "an engine of books alone runs nothing: llmx_engine_plan and llmx_engine_book"};
+        if (!e->planned.empty()) throw Failure{LLMX_ENGINE_ERR_REFUSED, "a planned step is waiting for llmx_engine_book"};
         cuda_check(cudaSetDevice(e->device), "choosing the device");
-        auto release = [&] {
-            for (long long id : e->sched.to_release) e->cache->free_request(id);
-            e->sched.to_release.clear();
-        };
-        auto give = [&](const llmx_step_result& r) {
-            if (written < capacity) out[written++] = r;
-        };
-        release();
-        std::vector<std::shared_ptr<Request>> ended;
-        const std::vector<Planned> entries = e->sched.plan(ended);
-        release();
-        for (const auto& r : ended) give(llmx_step_result{r->id, -1, r->finished});
-        if (entries.empty()) {
-            if (!e->sched.idle() && ended.empty()) throw Failure{LLMX_ENGINE_ERR_REFUSED, "the scheduler planned an empty step while requests are waiting"};
-            return 0;
-        }
-        std::vector<Batch> batch;
-        std::vector<Request*> wanting;
-        for (const Planned& p : entries) {
-            Batch b;
-            b.request = p.request->id;
-            b.tokens = p.tokens;
-            if (p.want_last) {
-                b.want.push_back((int)p.tokens.size() - 1);
-                wanting.push_back(p.request.get());
+        std::vector<llmx_step_result> results;
+        if (e->begin_step(results)) {
+            try {
+                const std::vector<Request*> wanting = e->run_planned();
+                const std::vector<int> drawn = e->draw(wanting);
+                if (wanting.empty()) e->sync_and_check();
+                for (const llmx_step_result& r : e->finish_step(drawn)) results.push_back(r);
+            } catch (...) {
+                e->planned.clear();
+                throw;
             }
-            batch.push_back(std::move(b));
         }
-        // The sampler's kernels must be there before the step changes anything.
-        if (!wanting.empty() && (!llmx_rt_kernel("llmx_sample") || !llmx_rt_kernel("llmx_penalize")))
-            throw Failure{LLMX_ENGINE_ERR_UNBOUND, "kernel llmx_sample is not bound (its library was not loaded)"};
-        e->run(batch);
-        const std::vector<int> drawn = e->draw(wanting);
-        if (wanting.empty()) e->sync_and_check();
-        for (const llmx_step_result& r : e->sched.complete(entries, drawn)) give(r);
-        release();
+        for (const llmx_step_result& r : results)
+            if (written < capacity) out[written++] = r;
+        return 0;
+    });
+    return err ? -err : written;
+}
+
+// The two halves of a step for a caller that draws the tokens itself.  llmx_engine_plan plans a step, reserves its
+// pages and (with a model) runs it; it writes the planned entries and returns their number (0: nothing to run; requests
+// that ended without running are then reported by llmx_engine_book).  llmx_engine_book takes one token for every entry
+// that wanted one, in order, and books them.  An engine created without a model and with device < 0 keeps the books
+// alone: the scheduler's decisions and the cache's pages can be followed without a GPU.
+LLMX_API int llmx_engine_plan(llmx_engine* e, llmx_planned_entry* out, int capacity) {
+    int written = 0;
+    const int err = guarded([&] {
+        if (!e || (capacity > 0 && !out)) throw Failure{LLMX_ENGINE_ERR_REFUSED, "llmx_engine_plan: an engine and room for entries"};
+        if (!e->planned.empty()) throw Failure{LLMX_ENGINE_ERR_REFUSED, "a planned step is waiting for llmx_engine_book"};
+        if (!e->books_only) cuda_check(cudaSetDevice(e->device), "choosing the device");
+        e->early.clear();
+        if (!e->begin_step(e->early)) return 0;
+        try {
+            e->run_planned();
+        } catch (...) {
+            e->planned.clear();
+            throw;
+        }
+        for (const Planned& p : e->planned)
+            if (written < capacity)
+                out[written++] = llmx_planned_entry{p.request->id, (int)p.tokens.size(), p.tokens.empty() ? -1 : p.tokens[0], p.want_last ? 1 : 0};
+        return 0;
+    });
+    return err ? -err : written;
+}
+// The logits of the step that ran last ([wanted, vocab] float32): copied to `out` (host, may be null); `device` (may be
+// null) receives the device buffer, valid until the next step.  Returns the number of wanted places.
+LLMX_API int llmx_engine_last_logits(llmx_engine* e, float* out, const float** device) {
+    int wanted = 0;
+    const int err = guarded([&] {
+        if (!e || e->books_only) throw Failure{LLMX_ENGINE_ERR_REFUSED, "llmx_engine_last_logits: an engine with a model"};
+        wanted = e->last_wanted;
+        if (out && wanted > 0)
+            cuda_check(cudaMemcpyAsync(out, e->logits.ptr, (size_t)wanted * e->vocab * sizeof(float), cudaMemcpyDeviceToHost, e->stream),
+                       "reading the logits");
+        e->sync_and_check();
+        if (device) *device = wanted > 0 ? (const float*)e->logits.ptr : nullptr;
+        return 0;
+    });
+    return err ? -err : wanted;
+}
+LLMX_API int llmx_engine_book(llmx_engine* e, const int* drawn, int n, llmx_step_result* out, int capacity) {
+    int written = 0;
+    const int err = guarded([&] {
+        if (!e || (n > 0 && !drawn) || (capacity > 0 && !out)) throw Failure{LLMX_ENGINE_ERR_REFUSED, "llmx_engine_book: an engine, tokens and room for results"};
+        std::vector<llmx_step_result> results = e->early;
+        e->early.clear();
+        if (!e->planned.empty()) {
+            int wanting = 0;
+            for (const Planned& p : e->planned) wanting += p.want_last ? 1 : 0;
+            if (wanting != n)
+                throw Failure{LLMX_ENGINE_ERR_REFUSED, "the planned step wants " + std::to_string(wanting) + " tokens, " + std::to_string(n) + " were given"};
+            for (const llmx_step_result& r : e->finish_step(std::vector<int>(drawn, drawn + n))) results.push_back(r);
+        } else if (n) {
+            throw Failure{LLMX_ENGINE_ERR_REFUSED, "no planned step is waiting for tokens"};
+        }
+        for (const llmx_step_result& r : results)
+            if (written < capacity) out[written++] = r;
         return 0;
     });
     return err ? -err : written;

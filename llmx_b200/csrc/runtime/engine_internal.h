@@ -102,7 +102,7 @@ struct Cache {
     std::map<long long, RequestCache> live;
     llmx_caches* views = nullptr;
 
-    explicit Cache(const llmx_engine_desc&);
+    Cache(const llmx_engine_desc&, bool books_only);      // books_only: no device storage
     ~Cache();
     Cache(const Cache&) = delete;
     RequestCache& new_request(long long id);
@@ -208,6 +208,7 @@ struct llmx_engine {
     std::unique_ptr<llmx_engine_detail::LoadedModel> owned;
     llmx_model* model;
     int vocab, max_positions, position_streams, device;
+    bool books_only;           // no model and no device: the cache's and the scheduler's books alone
     cudaStream_t stream = nullptr;
     std::unique_ptr<llmx_engine_detail::Cache> cache;
     llmx_engine_detail::Scheduler sched;
@@ -226,6 +227,11 @@ struct llmx_engine {
     ~llmx_engine();
     llmx_engine(const llmx_engine&) = delete;
     int* pinned(size_t ints);
+    std::vector<llmx_engine_detail::Planned> planned;      // a step that is planned and not yet booked
+    std::vector<llmx_step_result> early;                    // requests that ended while it was planned
+    bool begin_step(std::vector<llmx_step_result>& early_results);
+    std::vector<llmx_engine_detail::Request*> run_planned();
+    std::vector<llmx_step_result> finish_step(const std::vector<int>& drawn);
     void run(const std::vector<llmx_engine_detail::Batch>&);
     std::vector<int> draw(const std::vector<llmx_engine_detail::Request*>&);
     void sync_and_check();

@@ -95,6 +95,7 @@ llmx_engine* llmx_engine_create(llmx_model* model, const llmx_engine_desc*);    
 llmx_engine* llmx_engine_load(const char* model_dir, const llmx_engine_options*);
 void llmx_engine_destroy(llmx_engine*);
 const char* llmx_engine_last_error(void);
+int llmx_engine_last_code(void);            // the code of the calling thread's last failure (for calls that return a pointer)
 
 // ---- the low level: the caller says which requests bring which tokens ------------------------------------------
 typedef struct llmx_entry {
@@ -122,6 +123,21 @@ typedef struct llmx_step_result {
 // results were written (at most `capacity`; a step yields at most max_requests), 0 when nothing is left to do, or -code.
 int llmx_engine_step(llmx_engine*, llmx_step_result* out, int capacity);
 int llmx_engine_idle(llmx_engine*);
+// The two halves of llmx_engine_step, for a caller that draws the tokens itself.  llmx_engine_plan plans a step,
+// reserves its pages and runs it; it writes the planned entries and returns their number (0: nothing to run).
+// llmx_engine_book takes one token for every entry that wanted one, in the entries' order, books them, and writes the
+// results (with those of requests that ended while the step was planned).  An engine made by
+// llmx_engine_create(NULL, desc) with desc->device < 0 keeps the books alone (no model, no device memory): the
+// scheduler's decisions and the cache's pages can then be followed on any machine.
+typedef struct llmx_planned_entry {
+    long long request;
+    int n_tokens, first_token, want_last;
+} llmx_planned_entry;
+int llmx_engine_plan(llmx_engine*, llmx_planned_entry* out, int capacity);
+int llmx_engine_book(llmx_engine*, const int* drawn, int n, llmx_step_result* out, int capacity);
+// The logits of the step that ran last, [wanted, vocab] float32: copied to `out` (host, may be null); `device` (may be
+// null) receives the device buffer, valid until the next step.  Returns the number of wanted places or -code.
+int llmx_engine_last_logits(llmx_engine*, float* out, const float** device);
 // A request's reply so far (tokens written up to `capacity`; returns their number or -code); *finished as above.
 int llmx_engine_output(llmx_engine*, long long request, int* tokens, int capacity, int* finished);
 int llmx_engine_forget(llmx_engine*, long long request);              // a finished request's record

@@ -66,11 +66,16 @@ class StepResultC(ctypes.Structure):
     _fields_ = [("request", _ll), ("token", _i), ("finished", _i)]
 
 
+class PlannedEntryC(ctypes.Structure):
+    _fields_ = [("request", _ll), ("n_tokens", _i), ("first_token", _i), ("want_last", _i)]
+
+
 _SIGNATURES = {
     "llmx_engine_create": (_p, [_p, ctypes.POINTER(EngineDesc)]),
     "llmx_engine_load": (_p, [ctypes.c_char_p, ctypes.POINTER(EngineOptionsC)]),
     "llmx_engine_destroy": (None, [_p]),
     "llmx_engine_last_error": (ctypes.c_char_p, []),
+    "llmx_engine_last_code": (_i, []),
     "llmx_engine_forward": (_i, [_p, ctypes.POINTER(EntryC), _i, _p, _p]),
     "llmx_engine_end": (_i, [_p, _ll]),
     "llmx_engine_truncate": (_i, [_p, _ll, _i]),
@@ -78,6 +83,9 @@ _SIGNATURES = {
     "llmx_engine_add_request": (_ll, [_p, ctypes.POINTER(_i), _i, ctypes.POINTER(SamplingC)]),
     "llmx_engine_step": (_i, [_p, ctypes.POINTER(StepResultC), _i]),
     "llmx_engine_idle": (_i, [_p]),
+    "llmx_engine_plan": (_i, [_p, ctypes.POINTER(PlannedEntryC), _i]),
+    "llmx_engine_book": (_i, [_p, ctypes.POINTER(_i), _i, ctypes.POINTER(StepResultC), _i]),
+    "llmx_engine_last_logits": (_i, [_p, _p, _p]),
     "llmx_engine_output": (_i, [_p, _ll, ctypes.POINTER(_i), _i, ctypes.POINTER(_i)]),
     "llmx_engine_forget": (_i, [_p, _ll]),
     "llmx_engine_groups": (_i, [_p]),
@@ -133,7 +141,7 @@ def _sampling(params: SamplingParams):
 class NativeEngine:
     def __init__(self, handle: int, keep=()):
         if not handle:
-            raise _error(ERR_REFUSED)
+            raise _error(_lib().llmx_engine_last_code() or ERR_REFUSED)
         self._h = ctypes.c_void_p(handle)
         self._keep = keep                     # what the native engine points into and does not own
         self.vocab = _lib().llmx_engine_vocab(self._h)
@@ -173,6 +181,23 @@ class NativeEngine:
         if reserve not in ("full", "prompt"):
             raise ValueError("reserve must be 'full' or 'prompt'")
         return cls(_lib().llmx_engine_create(ctypes.c_void_p(handle), ctypes.byref(desc)), keep=(engine, entries, eos))
+
+    @classmethod
+    def books(cls, entries: Sequence[Tuple[int, int, int]], *, page_size: int = 16, kv_tokens: int = 8192,
+              window_kv_tokens: int = 0, max_requests: int = 16, ubatch: int = 512, reserve: str = "full", max_queue: int = 0,
+              vocab: int = 1 << 30, max_positions: int = 1 << 30, eos_ids: Sequence[int] = ()) -> "NativeEngine":
+        """The native engine's books alone (no model, no device): the scheduler's decisions and the cache's pages, for a
+        caller that supplies the tokens (`plan`, `book`).  `entries`: (kv_heads, head_dim, window) per cache entry."""
+        if reserve not in ("full", "prompt"):
+            raise ValueError("reserve must be 'full' or 'prompt'")
+        arr = (CacheEntryDesc * max(len(entries), 1))()
+        for i, (kvh, d, w) in enumerate(entries):
+            arr[i] = CacheEntryDesc(1, int(kvh), int(d), int(w or 0), 0)
+        eos = _ints(eos_ids)
+        desc = EngineDesc(int(vocab), int(max_positions), 1, int(page_size), int(kv_tokens), int(window_kv_tokens), int(max_requests),
+                          runtime.BF16, arr, len(entries), ctypes.cast(eos, ctypes.POINTER(_i)), len(eos_ids), int(ubatch),
+                          int(max_queue), 1 if reserve == "prompt" else 0, -1)
+        return cls(_lib().llmx_engine_create(None, ctypes.byref(desc)), keep=(arr, eos))
 
     @staticmethod
     def _options(dtype, kv_dtype, page_size, kv_tokens, window_kv_tokens, max_requests, ubatch, reserve, invariant, device):
@@ -255,6 +280,34 @@ class NativeEngine:
         if n < 0:
             raise _error(-n)
         return [(int(raw[k].request), int(raw[k].token), FINISHED[raw[k].finished]) for k in range(n)]
+
+    def plan(self) -> List[Tuple[int, int, int, bool]]:
+        """The first half of `step`: plan, reserve pages and (with a model) run.  [(request, tokens, first token, wants a
+        token)]; an empty list when nothing is to run."""
+        raw = (PlannedEntryC * 4096)()
+        n = self._call(_lib().llmx_engine_plan, self._h, raw, 4096)
+        if n < 0:
+            raise _error(-n)
+        return [(int(raw[k].request), int(raw[k].n_tokens), int(raw[k].first_token), bool(raw[k].want_last)) for k in range(n)]
+
+    def book(self, drawn: Sequence[int]) -> List[Tuple[int, int, Optional[str]]]:
+        """The second half: one token for every planned entry that wanted one, in order."""
+        raw = (StepResultC * 4096)()
+        arr = _ints(drawn)
+        n = _lib().llmx_engine_book(self._h, ctypes.cast(arr, ctypes.POINTER(_i)), len(drawn), raw, 4096)
+        if n < 0:
+            raise _error(-n)
+        return [(int(raw[k].request), int(raw[k].token), FINISHED[raw[k].finished]) for k in range(n)]
+
+    def last_logits(self) -> np.ndarray:
+        """The logits of the step that ran last, [wanted, vocab]."""
+        n = _lib().llmx_engine_last_logits(self._h, None, None)
+        if n < 0:
+            raise _error(-n)
+        out = np.empty((n, self.vocab), dtype=np.float32)
+        if n and _lib().llmx_engine_last_logits(self._h, out.ctypes.data_as(_p), None) < 0:
+            raise _error(ERR_DEVICE)
+        return out
 
     @property
     def idle(self) -> bool:
