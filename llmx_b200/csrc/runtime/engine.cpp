@@ -530,6 +530,7 @@ llmx_engine::~llmx_engine() {
         if (p.host) cudaFreeHost(p.host);
         if (p.done) cudaEventDestroy(p.done);
     }
+    recordings.clear();
     if (error_word) cudaFree(error_word);
     if (counters) cudaFree(counters);
     cache.reset();
@@ -559,6 +560,164 @@ void llmx_engine::sync_and_check() {
         cudaMemsetAsync(error_word, 0, sizeof(int), stream);
         throw Failure{LLMX_ENGINE_ERR_DEVICE, "a kernel gave up a bounded wait (code " + std::to_string(word) + ")"};
     }
+}
+
+// Where a step's metadata lies in its one int32 buffer (sections padded to 16 bytes): token ids [rows], positions
+// [streams, rows], the request of each row, first row / row count / history / state slots read of each request, the rows
+// whose logits are wanted, state slots written, then for every cache group its block tables [requests, max_pages] and the
+// rows' cache slots, then the ints of the launch plan.  Fills the offsets of `s`; returns the total.
+size_t llmx_engine::layout(llmx_step& s, const std::vector<int>& counts, int wanted, const std::vector<int>& max_pages, int plan_ints) const {
+    const int n_req = (int)counts.size(), n_groups = (int)cache->groups.size();
+    int rows = 0;
+    for (int c : counts) rows += c;
+    size_t at = 0;
+    auto section = [&](size_t n) {
+        const size_t off = at;
+        at += (std::max<size_t>(n, 1) + 3) & ~size_t(3);
+        return (int)off;
+    };
+    s.rows = rows, s.requests = n_req, s.wanted = wanted, s.groups = n_groups, s.position_streams = position_streams;
+    s.token_ids = section(rows);
+    s.positions = section((size_t)position_streams * rows);
+    s.row_request = section(rows);
+    s.row_start = section(n_req);
+    s.row_count = section(n_req);
+    s.history = section(n_req);
+    s.state_slots = section(n_req);
+    s.logit_rows = section(wanted);
+    s.state_slots_out = section(n_req);
+    for (int g = 0; g < n_groups; ++g) {
+        s.block_tables[g] = section((size_t)n_req * max_pages[g]);
+        s.table_stride[g] = max_pages[g];
+        s.slots[g] = section(rows);
+        s.page_size[g] = cache->page_size;
+    }
+    s.plan_offset = section(plan_ints);
+    s.caches = cache->views;
+    s.error_word = error_word;
+    s.counters = counters;
+    s.stream = stream;
+    return at;
+}
+
+void llmx_engine::fill_meta(int* buf, const llmx_step& s, size_t total, const std::vector<Batch>& batch,
+                            const std::vector<RequestCache*>& caches, const std::vector<int>& histories) const {
+    memset(buf, 0, total * sizeof(int));
+    const int n_groups = (int)cache->groups.size(), rows = s.rows, ps = cache->page_size;
+    int k = 0, a = 0;
+    for (int r = 0; r < s.requests; ++r) {
+        const int n = (int)batch[r].tokens.size();
+        for (int i = 0; i < n; ++i) {
+            buf[s.token_ids + a + i] = batch[r].tokens[i];
+            for (int st = 0; st < position_streams; ++st) buf[s.positions + (size_t)st * rows + a + i] = histories[r] + i;
+            buf[s.row_request + a + i] = r;
+        }
+        buf[s.row_start + r] = a;
+        buf[s.row_count + r] = n;
+        buf[s.history + r] = histories[r];
+        buf[s.state_slots + r] = caches[r]->state_slot;
+        buf[s.state_slots_out + r] = caches[r]->state_slot_out;
+        for (int w : batch[r].want) buf[s.logit_rows + k++] = a + w;
+        for (int g = 0; g < n_groups; ++g) {
+            const std::vector<int>& pg = caches[r]->tables[g].pages;
+            for (size_t p = 0; p < pg.size(); ++p) buf[s.block_tables[g] + (size_t)r * s.table_stride[g] + p] = pg[p];
+            // A released page (-1) is never addressed: the window keeps queries above it.
+            for (int i = 0; i < n; ++i) {
+                const int pos = histories[r] + i;
+                buf[s.slots[g] + a + i] = pg[pos / ps] * ps + pos % ps;
+            }
+        }
+        a += n;
+    }
+}
+
+// Recorded steps.  The kernels a step launches, their grids and the buffers they use depend on how many rows each
+// request brings, on which rows' logits are wanted and on how much context the block tables have room for -- not on the
+// requests' histories, tokens or pages, which the kernels read from the step's metadata on the device.  A recording
+// holds the CUDA graph of one such shape, made once the shape has come a few times (a scheduler that cuts prompts
+// into portions of its token budget, and every decode step of the same requests, bring the same shape again and again),
+// and the static metadata buffer, workspace and logits it uses; a step of that shape is then one copy and one launch.
+// What the model's parts decide on the host from a shape is decided once, for the recording's room; every run only
+// refills the plan's ints (llmx_plan_fill).
+Recording::~Recording() {
+    if (exec) cudaGraphExecDestroy(exec);
+    if (plan) llmx_plan_free(plan);
+}
+static int room_for(int context, int max_positions) {
+    return std::min((context / 2048 + 2) * 2048, std::max(max_positions, 1));       // at least 2,048 tokens ahead, so recordings change rarely
+}
+Recording* llmx_engine::recording_for(const std::vector<Batch>& batch, const std::vector<int>& counts, int context) {
+    if (!record_steps) return nullptr;
+    const int room = room_for(context, max_positions);
+    std::vector<int> key = {room, (int)batch.size()};
+    bool decode = true;
+    for (size_t r = 0; r < batch.size(); ++r) {
+        key.push_back(counts[r]);
+        key.push_back((int)batch[r].want.size());
+        key.insert(key.end(), batch[r].want.begin(), batch[r].want.end());
+        decode = decode && counts[r] == 1;
+    }
+    auto it = recordings.find(key);
+    if (it != recordings.end()) return it->second.get();
+    int& seen = shapes_seen[key];
+    if (seen < (decode ? 4 : 16)) {            // making a recording costs about as much as ten to twenty plain steps save
+        if (shapes_seen.size() > 4096) shapes_seen.clear();
+        else ++seen;
+        return nullptr;
+    }
+    shapes_seen.erase(key);
+    std::unique_ptr<Recording> rec(new Recording);
+    rec->room = room;
+    const int n_groups = (int)cache->groups.size();
+    std::vector<int> max_pages(n_groups);
+    for (int g = 0; g < n_groups; ++g) max_pages[g] = std::max(1, (room + cache->page_size - 1) / cache->page_size);
+    rec->plan = llmx_plan_make(model, nullptr, 0, counts.data(), nullptr, (int)counts.size(), room, context);
+    if (!rec->plan) throw Failure{LLMX_ENGINE_ERR_REFUSED, std::string("launch plan: ") + llmx_rt_last_error()};
+    int wanted = 0;
+    for (const Batch& b : batch) wanted += (int)b.want.size();
+    llmx_step& s = rec->step;
+    rec->total = layout(s, counts, wanted, max_pages, llmx_plan_ints(rec->plan));
+    s.room = room;
+    s.plan = rec->plan;
+    rec->meta.ensure(rec->total * sizeof(int), stream);
+    cuda_check(cudaMemsetAsync(rec->meta.ptr, 0, rec->total * sizeof(int), stream), "clearing a recording's metadata");
+    s.meta = (const int*)rec->meta.ptr;
+    const size_t need = llmx_model_workspace(model, &s);
+    const char* missing = nullptr;
+    if (llmx_rt_missing(0, &missing)) return nullptr;       // a plain step binds what is missing first
+    rec->workspace.ensure(need, stream);
+    s.workspace = rec->workspace.ptr, s.workspace_bytes = rec->workspace.bytes;
+    rec->logits.ensure((size_t)std::max(wanted, 1) * vocab * sizeof(float), stream);
+    // Keep the number of recordings bounded (the least recently used goes) before this one is made.
+    while (recordings.size() >= 24) {
+        auto oldest = recordings.begin();
+        for (auto j = recordings.begin(); j != recordings.end(); ++j)
+            if (j->second->last_use < oldest->second->last_use) oldest = j;
+        cuda_check(cudaStreamSynchronize(stream), "waiting before a recording goes");
+        recordings.erase(oldest);
+    }
+    const long long before = llmx_rt_launches();
+    cuda_check(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal), "beginning a recording");
+    const int err = llmx_model_forward(model, &s, (float*)rec->logits.ptr);
+    cudaGraph_t graph = nullptr;
+    const cudaError_t ended = cudaStreamEndCapture(stream, &graph);
+    if (err || ended != cudaSuccess || !graph) {
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+        record_steps = false;                               // this model's steps are not recorded; plain steps go on
+        return nullptr;
+    }
+    rec->launches = llmx_rt_launches() - before;
+    const cudaError_t made = cudaGraphInstantiate(&rec->exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (made != cudaSuccess) {
+        cudaGetLastError();
+        record_steps = false;
+        return nullptr;
+    }
+    Recording* out = rec.get();
+    recordings[key] = std::move(rec);
+    return out;
 }
 
 // One batch through the model: validate, reserve pages (all or none), lay out the metadata, copy it once, run the
@@ -613,99 +772,61 @@ void llmx_engine::run(const std::vector<Batch>& batch) {
 
         // ---- the metadata: one int32 buffer, sections padded to 16 bytes (the layout of llmx_step) ----
         const int n_req = (int)batch.size(), n_groups = (int)cache->groups.size();
-        std::vector<int> counts(n_req), histories(n_req), starts(n_req);
-        int rows = 0, wanted = 0;
+        std::vector<int> counts(n_req), histories(n_req);
+        int wanted = 0, context = 0;
         for (int r = 0; r < n_req; ++r) {
             counts[r] = (int)batch[r].tokens.size();
             histories[r] = caches[r]->length;
-            starts[r] = rows;
-            rows += counts[r];
             wanted += (int)batch[r].want.size();
+            context = std::max(context, histories[r] + counts[r]);
         }
-        plan = llmx_plan_make(model, nullptr, 0, counts.data(), histories.data(), n_req, 0, 0);
-        if (!plan) throw Failure{LLMX_ENGINE_ERR_REFUSED, std::string("launch plan: ") + llmx_rt_last_error()};
-        const int plan_ints = llmx_plan_ints(plan);
-        std::vector<int> max_pages(n_groups, 1);
-        for (int g = 0; g < n_groups; ++g)
-            for (RequestCache* rc : caches) max_pages[g] = std::max(max_pages[g], (int)rc->tables[g].pages.size());
-        auto pad4 = [](size_t n) { return (std::max<size_t>(n, 1) + 3) & ~size_t(3); };
-        size_t at = 0;
-        auto section = [&](size_t n) {
-            const size_t off = at;
-            at += pad4(n);
-            return (int)off;
-        };
-        llmx_step s = {};
-        s.rows = rows, s.requests = n_req, s.wanted = wanted, s.groups = n_groups, s.position_streams = position_streams, s.room = 0;
-        s.token_ids = section(rows);
-        s.positions = section((size_t)position_streams * rows);
-        s.row_request = section(rows);
-        s.row_start = section(n_req);
-        s.row_count = section(n_req);
-        s.history = section(n_req);
-        s.state_slots = section(n_req);
-        s.logit_rows = section(wanted);
-        s.state_slots_out = section(n_req);
-        for (int g = 0; g < n_groups; ++g) {
-            s.block_tables[g] = section((size_t)n_req * max_pages[g]);
-            s.table_stride[g] = max_pages[g];
-            s.slots[g] = section(rows);
-            s.page_size[g] = cache->page_size;
+        Recording* rec = recording_for(batch, counts, context);
+        if (rec) {
+            // A shape that keeps coming: its metadata into the recording's static buffer, one copy, one graph launch.
+            int* buf = pinned(rec->total);
+            fill_meta(buf, rec->step, rec->total, batch, caches, histories);
+            if (llmx_plan_ints(rec->plan) && llmx_plan_fill(rec->plan, histories.data(), buf + rec->step.plan_offset))
+                throw Failure{LLMX_ENGINE_ERR_REFUSED, std::string("launch plan: ") + llmx_rt_last_error()};
+            cuda_check(cudaMemcpyAsync(rec->meta.ptr, buf, rec->total * sizeof(int), cudaMemcpyHostToDevice, stream), "copying the step's metadata");
+            cuda_check(cudaEventRecord(ring[ring_at].done, stream), "recording the copy");
+            ring[ring_at].used = true;
+            last_h2d_bytes = (long long)(rec->total * sizeof(int));
+            cuda_check(cudaGraphLaunch(rec->exec, stream), "replaying a recorded step");
+            llmx_rt_count_launches(rec->launches);
+            rec->last_use = ++use_clock;
+            cur_logits = (float*)rec->logits.ptr;
+            ++replays;
+        } else {
+            plan = llmx_plan_make(model, nullptr, 0, counts.data(), histories.data(), n_req, 0, 0);
+            if (!plan) throw Failure{LLMX_ENGINE_ERR_REFUSED, std::string("launch plan: ") + llmx_rt_last_error()};
+            std::vector<int> max_pages(n_groups, 1);
+            for (int g = 0; g < n_groups; ++g)
+                for (RequestCache* rc : caches) max_pages[g] = std::max(max_pages[g], (int)rc->tables[g].pages.size());
+            llmx_step s = {};
+            const size_t total = layout(s, counts, wanted, max_pages, llmx_plan_ints(plan));
+            int* buf = pinned(total);
+            fill_meta(buf, s, total, batch, caches, histories);
+            if (llmx_plan_ints(plan) && llmx_plan_fill(plan, histories.data(), buf + s.plan_offset))
+                throw Failure{LLMX_ENGINE_ERR_REFUSED, std::string("launch plan: ") + llmx_rt_last_error()};
+            meta.ensure(total * sizeof(int), stream);
+            cuda_check(cudaMemcpyAsync(meta.ptr, buf, total * sizeof(int), cudaMemcpyHostToDevice, stream), "copying the step's metadata");
+            cuda_check(cudaEventRecord(ring[ring_at].done, stream), "recording the copy");
+            ring[ring_at].used = true;
+            last_h2d_bytes = (long long)(total * sizeof(int));
+            s.meta = (const int*)meta.ptr;
+            s.plan = plan;
+            const size_t need = llmx_model_workspace(model, &s);
+            const char* missing = nullptr;
+            if (llmx_rt_missing(0, &missing))
+                throw Failure{LLMX_ENGINE_ERR_UNBOUND, std::string("kernel ") + (missing ? missing : "?") + " is not bound (its library was not loaded)"};
+            workspace.ensure(need, stream);
+            s.workspace = workspace.ptr, s.workspace_bytes = workspace.bytes;
+            logits.ensure((size_t)std::max(wanted, 1) * vocab * sizeof(float), stream);
+            if (int err = llmx_model_forward(model, &s, (float*)logits.ptr))
+                throw Failure{err == LLMX_RT_ERR_UNBOUND ? (int)LLMX_ENGINE_ERR_UNBOUND : (int)LLMX_ENGINE_ERR_DEVICE,
+                              std::string("forward: ") + llmx_rt_last_error()};
+            cur_logits = (float*)logits.ptr;
         }
-        s.plan_offset = section(plan_ints);
-        const size_t total = at;
-        int* buf = pinned(total);
-        memset(buf, 0, total * sizeof(int));
-        int k = 0;
-        for (int r = 0; r < n_req; ++r) {
-            const int a = starts[r], n = counts[r];
-            for (int i = 0; i < n; ++i) {
-                buf[s.token_ids + a + i] = batch[r].tokens[i];
-                for (int st = 0; st < position_streams; ++st) buf[s.positions + (size_t)st * rows + a + i] = histories[r] + i;
-                buf[s.row_request + a + i] = r;
-            }
-            buf[s.row_start + r] = a;
-            buf[s.row_count + r] = n;
-            buf[s.history + r] = histories[r];
-            buf[s.state_slots + r] = caches[r]->state_slot;
-            buf[s.state_slots_out + r] = caches[r]->state_slot_out;
-            for (int w : batch[r].want) buf[s.logit_rows + k++] = a + w;
-            for (int g = 0; g < n_groups; ++g) {
-                const std::vector<int>& pg = caches[r]->tables[g].pages;
-                const int ps = cache->page_size;
-                for (size_t p = 0; p < pg.size(); ++p) buf[s.block_tables[g] + (size_t)r * max_pages[g] + p] = pg[p];
-                // A released page (-1) is never addressed: the window keeps queries above it.
-                for (int i = 0; i < n; ++i) {
-                    const int pos = histories[r] + i;
-                    buf[s.slots[g] + a + i] = pg[pos / ps] * ps + pos % ps;
-                }
-            }
-        }
-        if (plan_ints && llmx_plan_fill(plan, histories.data(), buf + s.plan_offset))
-            throw Failure{LLMX_ENGINE_ERR_REFUSED, std::string("launch plan: ") + llmx_rt_last_error()};
-        meta.ensure(total * sizeof(int), stream);
-        cuda_check(cudaMemcpyAsync(meta.ptr, buf, total * sizeof(int), cudaMemcpyHostToDevice, stream), "copying the step's metadata");
-        cuda_check(cudaEventRecord(ring[ring_at].done, stream), "recording the copy");
-        ring[ring_at].used = true;
-        last_h2d_bytes = (long long)(total * sizeof(int));
-
-        s.meta = (const int*)meta.ptr;
-        s.plan = plan;
-        s.caches = cache->views;
-        s.error_word = error_word;
-        s.counters = counters;
-        s.stream = stream;
-        s.workspace = nullptr, s.workspace_bytes = 0;
-        const size_t need = llmx_model_workspace(model, &s);
-        const char* missing = nullptr;
-        if (llmx_rt_missing(0, &missing))
-            throw Failure{LLMX_ENGINE_ERR_UNBOUND, std::string("kernel ") + (missing ? missing : "?") + " is not bound (its library was not loaded)"};
-        workspace.ensure(need, stream);
-        s.workspace = workspace.ptr, s.workspace_bytes = workspace.bytes;
-        logits.ensure((size_t)std::max(wanted, 1) * vocab * sizeof(float), stream);
-        if (int err = llmx_model_forward(model, &s, (float*)logits.ptr))
-            throw Failure{err == LLMX_RT_ERR_UNBOUND ? (int)LLMX_ENGINE_ERR_UNBOUND : (int)LLMX_ENGINE_ERR_DEVICE,
-                          std::string("forward: ") + llmx_rt_last_error()};
         last_wanted = wanted;
     } catch (...) {
         if (plan) llmx_plan_free(plan);
@@ -766,10 +887,10 @@ std::vector<int> llmx_engine::draw(const std::vector<Request*>& who) {
     Row* d_rows = (Row*)(d_pen + 3 * rows);
     int* d_out = (int*)(d_rows + rows);
     if (items)
-        if (int err = penalize((float*)logits.ptr, vocab, d_items, d_items + items, d_items + 2 * items, d_pen, d_pen + rows,
+        if (int err = penalize(cur_logits, vocab, d_items, d_items + items, d_items + 2 * items, d_pen, d_pen + rows,
                                d_pen + 2 * rows, (int)items, stream))
             throw Failure{LLMX_ENGINE_ERR_DEVICE, "penalize: error " + std::to_string(err)};
-    if (int err = sample((const float*)logits.ptr, rows, vocab, d_rows, d_out, all_greedy ? 1 : 0, stream))
+    if (int err = sample(cur_logits, rows, vocab, d_rows, d_out, all_greedy ? 1 : 0, stream))
         throw Failure{LLMX_ENGINE_ERR_DEVICE, "sample: error " + std::to_string(err)};
     if (host_ids_n < (size_t)rows) {
         if (host_ids) cudaFreeHost(host_ids);
@@ -834,10 +955,10 @@ LLMX_API int llmx_engine_forward(llmx_engine* e, const llmx_entry* entries, int 
         e->run(batch);
         if (e->books_only) return 0;
         if (out && e->last_wanted > 0)
-            cuda_check(cudaMemcpyAsync(out, e->logits.ptr, (size_t)e->last_wanted * e->vocab * sizeof(float), cudaMemcpyDeviceToHost, e->stream),
+            cuda_check(cudaMemcpyAsync(out, e->cur_logits, (size_t)e->last_wanted * e->vocab * sizeof(float), cudaMemcpyDeviceToHost, e->stream),
                        "reading the logits");
         e->sync_and_check();
-        if (device_logits) *device_logits = e->last_wanted > 0 ? (const float*)e->logits.ptr : nullptr;
+        if (device_logits) *device_logits = e->last_wanted > 0 ? (const float*)e->cur_logits : nullptr;
         return 0;
     });
 }
@@ -988,10 +1109,10 @@ LLMX_API int llmx_engine_last_logits(llmx_engine* e, float* out, const float** d
         if (!e || e->books_only) throw Failure{LLMX_ENGINE_ERR_REFUSED, "llmx_engine_last_logits: an engine with a model"};
         wanted = e->last_wanted;
         if (out && wanted > 0)
-            cuda_check(cudaMemcpyAsync(out, e->logits.ptr, (size_t)wanted * e->vocab * sizeof(float), cudaMemcpyDeviceToHost, e->stream),
+            cuda_check(cudaMemcpyAsync(out, e->cur_logits, (size_t)wanted * e->vocab * sizeof(float), cudaMemcpyDeviceToHost, e->stream),
                        "reading the logits");
         e->sync_and_check();
-        if (device) *device = wanted > 0 ? (const float*)e->logits.ptr : nullptr;
+        if (device) *device = wanted > 0 ? (const float*)e->cur_logits : nullptr;
         return 0;
     });
     return err ? -err : wanted;
@@ -1055,5 +1176,8 @@ LLMX_API int llmx_engine_check(llmx_engine* e) {
 }
 LLMX_API long long llmx_engine_preemptions(llmx_engine* e) { return e->sched.preemptions; }
 LLMX_API long long llmx_engine_steps(llmx_engine* e) { return e->steps; }
+LLMX_API long long llmx_engine_replays(llmx_engine* e) { return e->replays; }
+LLMX_API void llmx_engine_record_steps(llmx_engine* e, int on) { e->record_steps = on != 0; }
+LLMX_API long long llmx_engine_last_h2d_bytes(llmx_engine* e) { return e->last_h2d_bytes; }
 LLMX_API int llmx_engine_vocab(llmx_engine* e) { return e->vocab; }
 LLMX_API int llmx_engine_max_positions(llmx_engine* e) { return e->max_positions; }

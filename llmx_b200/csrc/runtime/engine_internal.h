@@ -202,6 +202,18 @@ struct Batch {
     std::vector<int> tokens, want;
 };
 
+// The CUDA graph of one step shape and what it reads and writes (see engine.cpp, "Recorded steps").
+struct Recording {
+    int room = 0;
+    llmx_step step{};
+    size_t total = 0;
+    llmx_plan* plan = nullptr;
+    DeviceBuffer meta, workspace, logits;
+    cudaGraphExec_t exec = nullptr;
+    long long launches = 0, last_use = 0;
+    ~Recording();
+};
+
 }  // namespace llmx_engine_detail
 
 struct llmx_engine {
@@ -215,6 +227,11 @@ struct llmx_engine {
     std::map<long long, std::shared_ptr<llmx_engine_detail::Request>> requests;
     long long next_id = 0, steps = 0, last_h2d_bytes = 0;
     int last_wanted = 0;
+    float* cur_logits = nullptr;       // the logits of the step that ran last (the engine's buffer or a recording's)
+    bool record_steps = true;
+    std::map<std::vector<int>, std::unique_ptr<llmx_engine_detail::Recording>> recordings;
+    std::map<std::vector<int>, int> shapes_seen;
+    long long use_clock = 0, replays = 0;
     int* error_word = nullptr;
     int* counters = nullptr;
     llmx_engine_detail::DeviceBuffer meta, workspace, logits, sample_buf;
@@ -233,6 +250,10 @@ struct llmx_engine {
     std::vector<llmx_engine_detail::Request*> run_planned();
     std::vector<llmx_step_result> finish_step(const std::vector<int>& drawn);
     void run(const std::vector<llmx_engine_detail::Batch>&);
+    size_t layout(llmx_step&, const std::vector<int>& counts, int wanted, const std::vector<int>& max_pages, int plan_ints) const;
+    void fill_meta(int* buf, const llmx_step&, size_t total, const std::vector<llmx_engine_detail::Batch>&,
+                   const std::vector<llmx_engine_detail::RequestCache*>&, const std::vector<int>& histories) const;
+    llmx_engine_detail::Recording* recording_for(const std::vector<llmx_engine_detail::Batch>&, const std::vector<int>& counts, int context);
     std::vector<int> draw(const std::vector<llmx_engine_detail::Request*>&);
     void sync_and_check();
 };

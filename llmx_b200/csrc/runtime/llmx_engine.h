@@ -149,6 +149,9 @@ int llmx_engine_held_pages(llmx_engine*, long long request, int group);
 int llmx_engine_check(llmx_engine*);        // no page lost, held twice or freed twice; 0 when so
 long long llmx_engine_preemptions(llmx_engine*);
 long long llmx_engine_steps(llmx_engine*);
+long long llmx_engine_replays(llmx_engine*);                 // steps that replayed a recorded (CUDA graph) step
+void llmx_engine_record_steps(llmx_engine*, int on);         // whether shapes that keep coming are recorded (on at the start)
+long long llmx_engine_last_h2d_bytes(llmx_engine*);          // metadata bytes the last step copied to the device
 int llmx_engine_vocab(llmx_engine*);
 int llmx_engine_max_positions(llmx_engine*);
 

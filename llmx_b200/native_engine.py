@@ -94,6 +94,9 @@ _SIGNATURES = {
     "llmx_engine_check": (_i, [_p]),
     "llmx_engine_preemptions": (_ll, [_p]),
     "llmx_engine_steps": (_ll, [_p]),
+    "llmx_engine_replays": (_ll, [_p]),
+    "llmx_engine_record_steps": (None, [_p, _i]),
+    "llmx_engine_last_h2d_bytes": (_ll, [_p]),
     "llmx_engine_vocab": (_i, [_p]),
     "llmx_engine_max_positions": (_i, [_p]),
 }
@@ -359,3 +362,16 @@ class NativeEngine:
     @property
     def steps(self) -> int:
         return int(_lib().llmx_engine_steps(self._h))
+
+    @property
+    def replays(self) -> int:
+        """Steps that replayed a recorded (CUDA graph) step."""
+        return int(_lib().llmx_engine_replays(self._h))
+
+    def record_steps(self, on: bool) -> None:
+        """Whether step shapes that keep coming are recorded as CUDA graphs (on at the start)."""
+        _lib().llmx_engine_record_steps(self._h, 1 if on else 0)
+
+    @property
+    def last_h2d_bytes(self) -> int:
+        return int(_lib().llmx_engine_last_h2d_bytes(self._h))

@@ -219,3 +219,41 @@ def test_a_cpp_program_generates_through_the_native_engine(model_dirs, tmp_path)
     assert out.returncode == 0, out.stderr
     got = [[int(t) for t in line.split()] for line in out.stdout.strip().splitlines()]
     assert got == want
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_native_engine_records_the_shapes_that_keep_coming(model_dirs, dtype):
+    """Decode steps of the same requests, and the equal portions a long prompt is cut into, are recorded as CUDA graphs
+    after a few plain steps and replayed: the same tokens as with recording off, and as each request gives alone."""
+    from llmx_b200.native_engine import NativeEngine
+    from llmx_b200.sampling import SamplingParams
+    name = "D"
+    folder, page = model_dirs[name][0 if dtype == "bfloat16" else 1], model_dirs[name][2]
+    vocab = CONFIGS[name][0]["vocab_size"]
+    prompts = [helpers.random_ids(vocab, n, seed=90 + n) for n in (400, 7, 21)]
+    params = [SamplingParams(max_tokens=40, temp=0.0, top_k=0, top_p=1.0, ignore_eos=True),
+              SamplingParams(max_tokens=60, temp=0.8, top_k=30, top_p=0.95, seed=9, ignore_eos=True),
+              SamplingParams(max_tokens=50, temp=0.0, top_k=0, top_p=1.0, ignore_eos=True)]
+    engine = _python_engine(folder, dtype, page, 2048, max_requests=4)
+    plain = NativeEngine.over(engine, ubatch=16)
+    plain.record_steps(False)
+    want = plain.generate(prompts, params)
+    assert plain.replays == 0
+    plain.close()
+    native = NativeEngine.over(engine, ubatch=16)
+    got = native.generate(prompts, params)
+    assert native.replays > 40                        # the decode steps, and the prompt's portions of sixteen tokens
+    assert native.last_h2d_bytes < 64 * 1024
+    if dtype == "float32":
+        assert got == want
+    else:                                             # bfloat16 sums move in their last bits from run to run; a greedy reply may part from a tie on
+        assert [len(t) for t, _ in got] == [len(t) for t, _ in want]
+        assert got[0][0][:8] == want[0][0][:8]
+    native.check()
+    # a second call finds its recordings ready
+    before = native.replays
+    again = native.generate(prompts[1:], params[1:])
+    assert native.replays > before
+    if dtype == "float32":
+        assert again == want[1:]
+    native.close()
