@@ -182,7 +182,7 @@ def main() -> int:
             self.kv_bytes_per_token = L * 2 * KV * 2
             resident = 2 * (L * (E * (Q + 2 * KV) + Q * E + 3 * E * F) + V * E * (1 if cfg.tie_word_embeddings else 2))
             head_start = -(-context // 2048) * (max(batches, default=1) - 1)          # see run_generate
-            per_request = -(-(context + steps + max(warmup, 8) + head_start + 64) // page) * page
+            per_request = -(-(context + 3 * steps + max(warmup, 8) + head_start + 64) // page) * page      # three timed regions (REPEATS)
             room = torch.cuda.get_device_properties(0).total_memory * 0.9 - resident - (8 << 30)
             self.batches = [b for b in batches if b * per_request * self.kv_bytes_per_token <= room]
             self.left_out = [b for b in batches if b not in self.batches]
@@ -270,6 +270,32 @@ def main() -> int:
             ms = (marks[warmup + 1 + steps] - marks[warmup + 1]) * 1e3 / steps
             h2d = max((rec.total * 4 for (b, _), rec in self.engine.decode_recordings.items() if b == batch), default=0)
             return batch * 1e3 / ms, ms, h2d
+
+        def run_native(self, batch, steps, warmup):
+            """The same decode rate through the native engine (csrc/runtime/llmx_engine.h: cache bookkeeping, scheduler,
+            step metadata and sampler state in C++) over the same weights: `add_request` with host token ids, `step`
+            until the last request has drawn its timed tokens.  Every step copies its metadata from pinned host memory,
+            draws on the device and reads the ids back before the next is planned."""
+            from llmx_b200.native_engine import NativeEngine
+            head_start = -(-self.context // 2048) * (batch - 1)
+            budget = head_start + warmup + steps + 4
+            tokens = batch * (self.context + budget + 64)
+            native = NativeEngine.over(self.engine, kv_tokens=min(tokens, self.engine.options.kv_tokens), ubatch=2048, max_requests=batch)
+            try:
+                params = SamplingParams(max_tokens=budget, temp=0.0, top_k=0, top_p=1.0, ignore_eos=True)
+                ids = [native.add_request(self.ids(self.context), params) for _ in range(batch)]
+                seen, marks, h2d = 0, {}, 0
+                while not native.idle:
+                    for rid, token, _ in native.step():
+                        if rid == ids[-1] and token >= 0:
+                            seen += 1
+                            if seen in (warmup + 1, warmup + 1 + steps):
+                                marks[seen] = time.perf_counter()
+                                h2d = native.last_h2d_bytes          # of a step of the whole batch
+                ms = (marks[warmup + 1 + steps] - marks[warmup + 1]) * 1e3 / steps
+                return batch * 1e3 / ms, ms, h2d, native.replays
+            finally:
+                native.close()
 
         def profile_plain_step(self, entries, what):
             """One plain (unrecorded) step of these entries: the host's time to enqueue it (the device idle, then
@@ -377,6 +403,11 @@ def main() -> int:
     value = args.batch * 1e3 / ms
     mean_rate, sd_rate = rate(args.batch, times)
     e2e_value, e2e_ms, h2d = bench.run_generate(args.batch, args.steps, max(args.warmup, 8))
+    try:
+        native_value, native_ms, native_h2d, native_replays = bench.run_native(args.batch, args.steps, max(args.warmup, 8))
+    except Exception as e:          # the point is left out, the line still stands
+        print(f"note: the native engine's point is left out: {e}", file=sys.stderr)
+        native_value = None
     pf_value, pf_ms, pf_sd, pf_frac = bench.run_prefill(3, 3)
     points = {}
     for b in bench.batches:
@@ -429,6 +460,10 @@ def main() -> int:
         "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch},
         "gpu_launches": launches,
+        "e2e_native": None if native_value is None else {
+            "value": round(native_value, 1), "unit": "tok/s", "ms_per_step": round(native_ms, 4), "h2d_bytes_per_step": native_h2d,
+            "d2h_bytes_per_step": 4 * args.batch, "replayed_steps": native_replays,
+            "what": "the same steps through the native (C++) engine: llmx_engine_add_request / llmx_engine_step"},
         "prefill": {"value": round(pf_value, 1), "tokens": args.prefill_tokens, "ms": round(pf_ms, 3), "ms_sd": round(pf_sd, 3),
                     "frac": round(pf_frac, 4), "peak_tflops": pk["bf16_tflops"]},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
