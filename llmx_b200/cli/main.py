@@ -17,7 +17,7 @@ USAGE = """usage:
   llmx generate MODEL (IDS | --file F) [-n N|--max-tokens N] [--temp T] [--topk K] [--topp P] [--min-p P]
                 [--penalty P] [--presence-penalty P] [--frequency-penalty P] [--seed S] [--ignore-eos]
                 [--dtype auto|bf16|f32] [--ubatch N] [--kv-tokens N] [--cache-type-k T] [--cache-type-v T]
-                [--yarn F] [--yarn-original-ctx N] [--device D] [--verbose]
+                [--yarn F] [--yarn-original-ctx N] [--device D] [--verbose] [--engine python|native]
       MODEL   a folder with config.json and model.safetensors
       IDS     the prompt as token ids, e.g. 1,2,3
       --yarn F   the rope scaled by YaRN at factor F over the trained length (--yarn-original-ctx N, default the
@@ -135,11 +135,13 @@ def cmd_generate(argv: List[str]) -> int:
     from ..sampling import SamplingParams
     valued = {k: k for k in ("--max-tokens", "--temp", "--topk", "--topp", "--min-p", "--penalty", "--presence-penalty",
                              "--frequency-penalty", "--seed", "--dtype", "--ubatch", "--kv-tokens", "--cache-type-k",
-                             "--cache-type-v", "--device", "--file", "--yarn", "--yarn-original-ctx")}
+                             "--cache-type-v", "--device", "--file", "--yarn", "--yarn-original-ctx", "--engine")}
     given, pos = _parse(argv, valued, ("--ignore-eos", "--verbose"))
     if not pos:
         raise UsageError("missing the model")
     model = pos[0]
+    if given.get("--engine", "python") not in ("python", "native"):
+        raise UsageError("--engine: python or native")
     if "--file" in given:
         if len(pos) > 1:
             raise UsageError(f"a second prompt, '{pos[1]}'")
@@ -172,6 +174,8 @@ def cmd_generate(argv: List[str]) -> int:
         kv_tokens = -(-(len(prompt) + params.max_tokens) // 64) * 64
     yarn, yarn_original = _yarn(given)
 
+    if given.get("--engine") == "native":
+        return _generate_native(model, prompt, params, dtype, kv_dtype, ubatch, kv_tokens, given, yarn)
     from ..engine.generate import LLM
     t0 = time.perf_counter()
     llm = LLM(model, dtype=dtype, kv_tokens=kv_tokens, ubatch=ubatch, max_seqs=1, device=given.get("--device", "cuda:0"),
@@ -188,6 +192,37 @@ def cmd_generate(argv: List[str]) -> int:
     if "--verbose" in given:
         c = llm.engine.cache
         print(f"kv: allocated {c.storage_bytes()} bytes, pages {c.total_pages()}, finish {out.finish_reason}")
+    return 0
+
+
+def _generate_native(model: str, prompt, params, dtype: str, kv_dtype, ubatch: int, kv_tokens: int, given, yarn) -> int:
+    """`llmx generate --engine native`: the files read, the request scheduled and the tokens drawn by the native engine
+    (csrc/runtime/llmx_engine.h); the same output lines."""
+    from ..native_engine import NativeEngine
+    if yarn is not None:
+        raise UsageError("--yarn: the native loader reads the rope scaling the files declare; use --engine python")
+    device = given.get("--device", "cuda:0")
+    t0 = time.perf_counter()
+    engine = NativeEngine.load(model, dtype=dtype, kv_dtype=kv_dtype, kv_tokens=kv_tokens, ubatch=ubatch, max_requests=1,
+                               device=int(device.split(":")[1]) if ":" in device else 0)
+    if "--verbose" in given:
+        print(f"load: {time.perf_counter() - t0:.2f} s", file=sys.stderr)
+        print(f"prompt tokens: {len(prompt)}")
+    rid = engine.add_request(prompt, params)
+    t0 = time.perf_counter()
+    first = None
+    while not engine.idle:
+        if engine.step() and first is None:
+            first = time.perf_counter()
+    end = time.perf_counter()
+    tokens, reason = engine.output(rid)
+    print("ids: " + ",".join(str(t) for t in tokens))
+    pp_ms, tg_ms = ((first or end) - t0) * 1e3, (end - (first or end)) * 1e3
+    print(f"pp: {len(prompt)} tok, {pp_ms:.0f} ms, {len(prompt) / max(pp_ms / 1e3, 1e-9):.2f} tok/s")
+    print(f"tg: {len(tokens)} tok, {tg_ms:.0f} ms, {len(tokens) / max(tg_ms / 1e3, 1e-9):.2f} tok/s")
+    if "--verbose" in given:
+        print(f"kv: pages {[t for t, _ in engine.pages()]}, steps {engine.steps} ({engine.replays} replayed), finish {reason}")
+    engine.close()
     return 0
 
 
