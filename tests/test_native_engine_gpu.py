@@ -257,3 +257,82 @@ def test_native_engine_records_the_shapes_that_keep_coming(model_dirs, dtype):
     if dtype == "float32":
         assert again == want[1:]
     native.close()
+
+
+def test_native_engine_runs_a_model_of_two_cache_groups_and_a_repeated_layer(tmp_path):
+    """A model put together in the test from the framework's own (native) parts: a layer with rotated full attention
+    that the order names twice (cache entries of its own each time), and a windowed layer without rotation or q/k norm
+    that runs a second time reading the keys it wrote the first time.  The native engine keeps a pool per group, gives
+    the window's pages back while the full group keeps its own, and its logits are the Python engine's bit for bit."""
+    import json
+    import os
+    import torch
+    from dataclasses import dataclass
+    from llmx_b200.engine import Engine, EngineOptions
+    from llmx_b200.models import LayerStep, Model
+    from llmx_b200.native_engine import NativeEngine
+    from llmx_b200.parts import (Attention, GatedMLP, LogitsHead, NoPositionEncoding, PreNormBlock, RMSNorm, RotaryEmbedding,
+                                 TokenEmbedding)
+    from llmx_b200.registry import register_architecture, unregister_architecture
+    from llmx_b200.weights import RandomSource, write_safetensors
+
+    @dataclass(frozen=True)
+    class Two:
+        hidden_size: int = 64
+        vocab_size: int = 120
+        window: int = 12
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(**{k: v for k, v in raw.items() if k not in ("architectures", "model_type")})
+
+        def to_dict(self):
+            return dict(self.__dict__, architectures=["TwoGroups"], model_type="two_groups")
+
+    def build(cfg):
+        E, H, G, D = cfg.hidden_size, 4, 2, 16
+        norm = lambda: RMSNorm(E, 1e-5)          # noqa: E731
+        mlp = lambda: GatedMLP(E, 96)            # noqa: E731
+        blocks = [PreNormBlock(norm(), Attention(E, H, G, D, RotaryEmbedding(D, 10000.0), qk_norm_eps=1e-5), norm(), mlp()),
+                  PreNormBlock(norm(), Attention(E, H, G, D, NoPositionEncoding(), qk_norm_eps=None, window=cfg.window), norm(), mlp())]
+        order = [LayerStep(0, 0), LayerStep(1, 1), LayerStep(0, 2), LayerStep(1, 1, write_cache=False)]
+        emb = TokenEmbedding(cfg.vocab_size, E)
+        return Model(embedding=emb, blocks=blocks, head=LogitsHead(norm(), cfg.vocab_size, E, tied_to=emb), order=order,
+                     vocab_size=cfg.vocab_size, max_positions=512)
+
+    register_architecture(["TwoGroups", "two_groups"], Two, build)
+    try:
+        cfg = Two()
+        folder = str(tmp_path)
+        with open(os.path.join(folder, "config.json"), "w") as f:
+            json.dump(cfg.to_dict(), f)
+        src = RandomSource(build(cfg).tensor_specs(), 5, dtype=torch.float32, skip_optional=True)
+        write_safetensors(os.path.join(folder, "model.safetensors"),
+                          {n: src.tensor(n) * (4.0 if n.endswith("proj.weight") else 1.0) for n in src.names()})
+        requests = {f"t{i}": helpers.random_ids(cfg.vocab_size, n, seed=i) for i, n in enumerate([50, 3, 77, 20, 1, 64])}
+        for make in (helpers.trace_portions, helpers.trace_mixed):
+            steps = make(requests)
+            tokens = helpers.tokens_needed(steps)
+            engine = Engine.from_dir(folder, EngineOptions(dtype="float32", kv_tokens=tokens, page_size=4, max_requests=4))
+            assert engine.model.native and len(engine.cache.groups) == 2
+            want = helpers.run_trace(engine, steps)
+            native = NativeEngine.over(engine)
+            got = helpers.run_trace(AsEngine(native), steps)
+            native.check()
+            assert all(free == total for total, free in native.pages()) and len(native.pages()) == 2
+            assert all(np.array_equal(got[k], want[k]) for k in want)
+            native.close()
+        # the window's pages go back while the request lives; the full group's stay
+        engine = Engine.from_dir(folder, EngineOptions(dtype="float32", kv_tokens=256, page_size=4, max_requests=2))
+        native = NativeEngine.over(engine)
+        ids = helpers.random_ids(cfg.vocab_size, 100, seed=5)
+        native.forward([(1, ids[:60], [])])
+        windowed = 1 if engine.cache.groups[1].spec.window else 0
+        assert native.held_pages(1, 1 - windowed) == 15 and native.held_pages(1, windowed) <= 4
+        for t in ids[60:]:
+            native.forward([(1, [t], [0])])
+            assert native.held_pages(1, windowed) <= 4
+        assert native.held_pages(1, 1 - windowed) == 25
+        native.close()
+    finally:
+        unregister_architecture(["TwoGroups", "two_groups"])
