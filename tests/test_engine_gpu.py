@@ -135,8 +135,10 @@ def test_first_tokens_of_a_sequence(model_dirs, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_trace_run_program(model_dirs, tmp_path, dtype):
-    """bin/trace_run as a user runs it: JSON steps on standard input, .f32 files out, `done` lines."""
+@pytest.mark.parametrize("which", ["python", "native"])
+def test_trace_run_program(model_dirs, tmp_path, dtype, which):
+    """bin/trace_run as a user runs it: JSON steps on standard input, .f32 files out, `done` lines; through the Python
+    engine (the default) and through the native one."""
     name = "B"
     d16, d32, page = model_dirs[name]
     folder = d32 if dtype == "float32" else d16
@@ -148,8 +150,8 @@ def test_trace_run_program(model_dirs, tmp_path, dtype):
     out = tmp_path / "out"
     text = "".join(json.dumps(s) + "\n" for s in steps)
     proc = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
-                           "--out", str(out), "--max-tokens", str(need)], input=text, capture_output=True, text=True,
-                          timeout=600)
+                           "--out", str(out), "--max-tokens", str(need)] + (["--engine", "native"] if which == "native" else []),
+                          input=text, capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stderr[-2000:]
     assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
     got = helpers.read_trace_output(steps, str(out), vocab)
