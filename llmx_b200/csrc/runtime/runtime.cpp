@@ -323,25 +323,47 @@ void decode_schedule(int n_requests, int kv_heads, int max_context, int head_dim
 // rows); a block of threads walks an item's key stages one after the other, so when items are fewer than the SMs the
 // longest item is the kernel's time.  Two row tiles an item share their key stages and keep the tensor core busier
 // (about 1.05 us a tile and stage of 128 keys against 1.9 us for a tile alone); cutting the keys into ranges makes
-// more, shorter items at the price of a second small kernel that adds the ranges up.  The cheapest combination wins.
+// more, shorter items at the price of the partial results' trip through memory and a second small kernel that adds
+// the ranges up.  The cheapest combination wins (the estimates below are within a tenth of what was measured at 512
+// rows after 4,096 keys, 256 after 8,192, and whole prompts of 1,024 to 8,192 tokens at 16, 32 and 64 heads over 8).
 void prefill_shape(int n_requests, int kv_heads, int ratio, int max_rows, int max_context, int window, int n_sms, int* tiles_out,
                    int* splits_out) {
     const int per_tile = std::max(1, 128 / ratio);
     const int reach = window ? std::min(max_context, window + max_rows) : max_context;
     const int stages = cdiv(reach, 128);
+    const int hist = std::max(max_context - max_rows, 0);
     double best_t = -1;
     int best_tiles = 2, best_splits = 1;
     const int tile_options[2] = {2, 1};
-    const double rates[2] = {2.1, 1.9};
+    const double rates[2] = {2.1, 1.9};           // us a key stage of an item of two tiles / of one
+    const double item_cost = 4.0;                 // us an item costs a block beside its stages
     static const int split_options[] = {1, 2, 3, 4, 6, 8};
     for (int o = 0; o < 2; ++o) {
-        const int tiles = tile_options[o];
-        const long long items = (long long)cdiv(max_rows, tiles * per_tile) * kv_heads * n_requests;
+        const int tiles = tile_options[o], rows_per_item = tiles * per_tile;
+        const int n_items = cdiv(max_rows, rows_per_item);
+        // The items of a request are not equally long: item i's rows see the history and the rows up to its own (or
+        // their window).  A block walks heavy and light items in turn, so many items share out evenly.
+        long long sum = 0;
+        int longest = 0;
+        for (int i = 1; i <= n_items; ++i) {
+            int keys = hist + std::min(i * rows_per_item, max_rows);
+            if (window) keys = std::min(keys, window + rows_per_item);
+            const int len = cdiv(keys, 128);
+            sum += len;
+            longest = std::max(longest, len);
+        }
+        const double total = (double)sum * kv_heads * n_requests;
         for (int splits : split_options) {
             if (splits > 1 && (stages < 8 * splits ||
                                (long long)max_rows * kv_heads * ratio * n_requests * splits * PREFILL_PART > PREFILL_MAX_PARTIAL))
                 break;
-            const double t = (double)((items * splits + n_sms - 1) / n_sms) * cdiv(stages, splits) * rates[o] + (splits > 1 ? 6.0 : 0.0);
+            const long long units = (long long)n_items * kv_heads * n_requests * splits;
+            const double unit_longest = cdiv(longest, splits);
+            const double walk = units <= n_sms ? unit_longest : std::max(unit_longest, total / n_sms + 0.5 * unit_longest);
+            // Ranges meet through memory: every (row, head, range) leaves 132 floats that the second kernel reads back
+            // (4,096 rows x 32 heads x 2 ranges are 138 MB each way: 244 us with two ranges against 161 with one).
+            const double meet = splits > 1 ? 4.0 + 2.0 * (double)max_rows * kv_heads * ratio * n_requests * splits * PREFILL_PART * 4 / 5e6 : 0.0;
+            const double t = walk * rates[o] + item_cost * (double)((units + n_sms - 1) / n_sms) + meet;
             if (best_t < 0 || t < best_t - 1e-9) best_t = t, best_tiles = tiles, best_splits = splits;
         }
     }
