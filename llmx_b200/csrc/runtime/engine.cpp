@@ -535,6 +535,7 @@ llmx_engine::~llmx_engine() {
     if (counters) cudaFree(counters);
     cache.reset();
     if (host_ids) cudaFreeHost(host_ids);
+    if (sample_host) cudaFreeHost(sample_host);
     if (stream) cudaStreamDestroy(stream);
 }
 
@@ -861,8 +862,15 @@ std::vector<int> llmx_engine::draw(const std::vector<Request*>& who) {
     const size_t items = row_of.size();
     const size_t bytes = items * 3 * sizeof(int) + (size_t)rows * 3 * sizeof(float) + (size_t)rows * sizeof(Row) + (size_t)rows * sizeof(int) + 64;
     sample_buf.ensure(bytes, stream);
-    std::vector<char> host(bytes);
-    char* h = host.data();
+    // Pinned staging, so that the settings' copy and the draw are enqueued behind the step without waiting for it
+    // (every call ends with a synchronisation, after which the buffer is free again).
+    if (sample_host_bytes < bytes) {
+        if (sample_host) cudaFreeHost(sample_host);
+        sample_host = nullptr;
+        cuda_check(cudaMallocHost((void**)&sample_host, std::max<size_t>(bytes + (bytes >> 1), 4096)), "allocating pinned memory");
+        sample_host_bytes = std::max<size_t>(bytes + (bytes >> 1), 4096);
+    }
+    char* h = sample_host;
     int* h_items = (int*)h;
     float* h_pen = (float*)(h_items + 3 * items);
     Row* h_rows = (Row*)(h_pen + 3 * rows);
@@ -881,7 +889,6 @@ std::vector<int> llmx_engine::draw(const std::vector<Request*>& who) {
     }
     char* d = (char*)sample_buf.ptr;
     cuda_check(cudaMemcpyAsync(d, h, (char*)(h_rows + rows) - h, cudaMemcpyHostToDevice, stream), "copying the sampling settings");
-    cuda_check(cudaStreamSynchronize(stream), "copying the sampling settings");        // `host` is pageable and about to go
     int* d_items = (int*)d;
     float* d_pen = (float*)(d_items + 3 * items);
     Row* d_rows = (Row*)(d_pen + 3 * rows);

@@ -239,6 +239,8 @@ struct llmx_engine {
     int ring_at = 0;
     int* host_ids = nullptr;
     size_t host_ids_n = 0;
+    char* sample_host = nullptr;       // pinned staging of a draw's settings
+    size_t sample_host_bytes = 0;
 
     llmx_engine(llmx_model*, const llmx_engine_desc&, std::unique_ptr<llmx_engine_detail::LoadedModel>);
     ~llmx_engine();
