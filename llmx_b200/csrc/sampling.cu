@@ -13,67 +13,23 @@
 //   the draw     target = r * weight of the walked set; the first token whose running sum exceeds it.
 //
 // `r` is the request's own uniform number, made on the host from its own generator, so a draw
-// does not depend on what else is in the batch.  One block works on one row.  The top-k threshold is found by
-// radix selection over the 32-bit order-preserving image of the score (counting tokens).  When the kept set
-// then fits shared memory (top-k of at most 1,024, the usual case) it is gathered there, ranked, and
-// the nucleus, min-p and the draw are one thread's walk over it with double sums, exactly the reference's
-// walk; the vocabulary is read seven times in all (16-byte loads), where every later threshold used to be
-// another radix selection over it (top-k 40, top-p 0.95 at 151,936 tokens: 670 us a draw before).  Without top-k
-// (or a larger one) nothing is gathered: thresholds by radix selection over the vocabulary, summing weights.
+// does not depend on what else is in the batch.  A row is the work of a thread-block cluster of up to eight blocks:
+// each scans its slice of the vocabulary, their counts and sums meet in the first block's shared memory, which
+// decides (one block alone issues instructions for 150,000 scores at about 25 us a pass, whatever its loads do).
+// The top-k threshold is found by radix selection over the 32-bit order-preserving image of the score (counting
+// tokens).  When the kept set then fits shared memory (top-k of at most 1,024, the usual case) it is gathered
+// there, ranked, and the nucleus, min-p and the draw are one thread's walk over it with double sums, exactly the
+// reference's walk.  Without top-k (or a larger one) nothing is gathered: thresholds by radix selection over the
+// vocabulary, summing weights.
 #include "common.cuh"
 #include <math.h>
 
 namespace {
 
 constexpr int THREADS = 1024;
-constexpr int KMAX = 1024;        // kept tokens a block gathers into shared memory
+constexpr int KMAX = 1024;        // kept tokens that are gathered into shared memory
 constexpr int TIES = 32;          // tokens with exactly the same score that are picked among without a second pass
-
-// Calls f(id, score, in_range) for every id of the row, four consecutive ids a thread and round with 16-byte loads
-// when the row allows.  Every thread of the block makes the same number of calls (ids past the end come with
-// in_range false), so f may use warp-wide operations.
-template <typename F>
-__device__ __forceinline__ void scan_row(const float* __restrict__ row, int n, F&& f) {
-    if ((((uintptr_t)row) & 15) == 0) {
-        const int n4 = n >> 2;
-        const float4* row4 = reinterpret_cast<const float4*>(row);
-        const int rounds = (n4 + THREADS - 1) / THREADS;
-        // Eight loads of a thread are in flight before the first is used: one block must cover the latency of the
-        // whole row by itself.
-        constexpr int AHEAD = 8;
-        for (int r0 = 0; r0 < rounds; r0 += AHEAD) {
-            float4 v[AHEAD];
-#pragma unroll
-            for (int u = 0; u < AHEAD; ++u) {
-                const int i = (r0 + u) * THREADS + threadIdx.x;
-                v[u] = i < n4 ? __ldg(row4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int u = 0; u < AHEAD; ++u) {
-                if (r0 + u >= rounds) break;          // the same for every thread
-                const int i = (r0 + u) * THREADS + threadIdx.x;
-                const bool ok = i < n4;
-                f(4 * i, v[u].x, ok);
-                f(4 * i + 1, v[u].y, ok);
-                f(4 * i + 2, v[u].z, ok);
-                f(4 * i + 3, v[u].w, ok);
-            }
-        }
-        if (n & 3) {
-            const int id = 4 * n4 + threadIdx.x;
-            const bool ok = id < n;
-            f(id, ok ? row[id] : 0.0f, ok);
-        }
-    } else {
-        const int rounds = (n + THREADS - 1) / THREADS;
-#pragma unroll 4
-        for (int r = 0; r < rounds; ++r) {
-            const int id = r * THREADS + threadIdx.x;
-            const bool ok = id < n;
-            f(id, ok ? row[id] : 0.0f, ok);
-        }
-    }
-}
+constexpr int MAX_CLUSTER = 8;    // blocks that share a row
 
 struct RowParams {
     float temperature, top_p, min_p, r;
@@ -86,16 +42,153 @@ __device__ __forceinline__ uint32_t order_bits(float s) {
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 
+// ---- the blocks of a row: a thread-block cluster.  Every block scans its slice of the vocabulary; what the blocks
+// find meets in the shared memory of the cluster's first block (the leader), which decides and from which all read
+// the decision back.  Nothing but the leader's shared memory is touched from outside its block, and the leader does
+// not leave before every block has read what it wants of it (a cluster barrier before each exit that follows a read).
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_blocks() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The address, in the cluster's shared window, of the leader's copy of a shared-memory location of this block.
+__device__ __forceinline__ uint32_t on_leader(const void* local) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(a) : "r"((uint32_t)__cvta_generic_to_shared(local)));
+    return a;
+}
+__device__ __forceinline__ void lead_add(const unsigned* p, unsigned v) {
+    asm volatile("red.relaxed.cluster.shared::cluster.add.u32 [%0], %1;" ::"r"(on_leader(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ void lead_add(const double* p, double v) {
+    asm volatile("red.relaxed.cluster.shared::cluster.add.f64 [%0], %1;" ::"r"(on_leader(p)), "d"(v) : "memory");
+}
+__device__ __forceinline__ int lead_take(const int* p) {       // the leader's counter before it is raised by one
+    int old;
+    asm volatile("atom.relaxed.cluster.shared::cluster.add.s32 %0, [%1], 1;" : "=r"(old) : "r"(on_leader(p)) : "memory");
+    return old;
+}
+__device__ __forceinline__ void lead_store(const int* p, int v) {
+    asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(on_leader(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ void lead_store(const uint32_t* p, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(on_leader(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ void lead_store(const float* p, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(on_leader(p)), "f"(v) : "memory");
+}
+__device__ __forceinline__ void lead_store(const double* p, double v) {
+    asm volatile("st.shared::cluster.f64 [%0], %1;" ::"r"(on_leader(p)), "d"(v) : "memory");
+}
+__device__ __forceinline__ int lead_load(const int* p) {
+    int v;
+    asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(on_leader(p)) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t lead_load(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(on_leader(p)) : "memory");
+    return v;
+}
+__device__ __forceinline__ double lead_load(const double* p) {
+    double v;
+    asm volatile("ld.shared::cluster.f64 %0, [%1];" : "=d"(v) : "r"(on_leader(p)) : "memory");
+    return v;
+}
+
 struct Shared {
+    // each block's own
     unsigned int count[256];
     double weight[256];
     double scan[THREADS];
     float best_score[32];
     int best_id[32];
+    // the leader's copy is where the blocks meet
+    unsigned int gcount[256];
+    double gweight[256];
+    double gsum;
+    float part_score[MAX_CLUSTER];
+    int part_id[MAX_CLUSTER];
+    double part_total[MAX_CLUSTER];
     uint32_t u32[4];
     double f64[4];
-    int i32[4];
+    int i32[8];
+    int n_hits, n_kept, walked;
+    int hit_list[TIES];
+    int c_id[KMAX], o_id[KMAX];
+    uint32_t c_bits[KMAX];
+    float c_w[KMAX], o_w[KMAX];
 };
+
+// One row as a block sees it: the row, the block's slice of ids [lo, hi) (lo a multiple of 4), its place in the cluster.
+struct Row {
+    const float* row;
+    int n, lo, hi;
+    uint32_t rank, blocks;
+    Shared* sh;
+};
+
+// The leader's turn: once every block's contributions have landed, the leader's threads run `body`; when they are
+// done every block may read what it left.  All threads of all blocks of the cluster call this.
+template <typename Body>
+__device__ __forceinline__ void leader_turn(const Row& c, Body&& body) {
+    cluster_sync();
+    if (c.rank == 0) body();
+    cluster_sync();
+}
+
+// Calls f(id, score, in_range) for every id of the block's slice, four consecutive ids a thread and round with 16-byte
+// loads when the row allows, eight loads of a thread in flight before the first is used.  Every thread of the block
+// makes the same number of calls (ids past the end come with in_range false), so f may use warp-wide operations.
+template <typename F>
+__device__ __forceinline__ void scan_slice(const Row& c, F&& f) {
+    const float* __restrict__ row = c.row;
+    if ((((uintptr_t)row) & 15) == 0) {
+        const int first4 = c.lo >> 2, n4 = c.hi >> 2;              // whole groups of four within the slice
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        const int rounds = (n4 - first4 + THREADS - 1) / THREADS;
+        constexpr int AHEAD = 8;
+        for (int r0 = 0; r0 < rounds; r0 += AHEAD) {
+            float4 v[AHEAD];
+#pragma unroll
+            for (int u = 0; u < AHEAD; ++u) {
+                const int i = first4 + (r0 + u) * THREADS + threadIdx.x;
+                v[u] = i < n4 ? __ldg(row4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < AHEAD; ++u) {
+                if (r0 + u >= rounds) break;          // the same for every thread
+                const int i = first4 + (r0 + u) * THREADS + threadIdx.x;
+                const bool ok = i < n4;
+                f(4 * i, v[u].x, ok);
+                f(4 * i + 1, v[u].y, ok);
+                f(4 * i + 2, v[u].z, ok);
+                f(4 * i + 3, v[u].w, ok);
+            }
+        }
+        if (c.hi & 3) {                               // the row's last one to three scores (the last slice only)
+            const int id = 4 * n4 + threadIdx.x;
+            const bool ok = id < c.hi;
+            f(id, ok ? row[id] : 0.0f, ok);
+        }
+    } else {
+        const int rounds = (c.hi - c.lo + THREADS - 1) / THREADS;
+#pragma unroll 4
+        for (int r = 0; r < rounds; ++r) {
+            const int id = c.lo + r * THREADS + threadIdx.x;
+            const bool ok = id < c.hi;
+            f(id, ok ? row[id] : 0.0f, ok);
+        }
+    }
+}
 
 // Which tokens take part: all but the masked one; then the top-k set; then the nucleus.
 struct Sets {
@@ -124,92 +217,93 @@ __device__ __forceinline__ bool in_nucleus(const Sets& s, int id, uint32_t bits,
     return true;
 }
 
-// The id of the (nth + 1)-th token, in id order, with these bits among the tokens of a set
-// (level 0: not masked, 1: kept, 2: nucleus).  Every thread returns the same id (-1 if there are fewer).
 template <int LEVEL>
-__device__ int nth_with_bits(const float* row, int n, uint32_t bits, int nth, const Sets& sets, float best_score,
-                             float temp, Shared& sh) {
-    __shared__ int found;
-    __shared__ int base;
-    __shared__ int n_hits;
-    __shared__ int hit_list[TIES];
-    if (threadIdx.x == 0) { found = -1; base = 0; n_hits = 0; }
-    __syncthreads();
-    // Scores are rarely equal bit for bit: one pass lists the few tokens that are, one thread picks among them.
-    scan_row(row, n, [&](int id, float s, bool ok) {
-        if (!ok) return;
-        const uint32_t b = order_bits(s);
-        if (b != bits) return;
-        bool hit;
-        if (LEVEL == 0) hit = id != sets.skip;
-        else if (LEVEL == 1) hit = in_kept(sets, id, b);
-        else hit = in_nucleus(sets, id, b, expf((s - best_score) / temp));
-        if (hit) {
-            const int slot = atomicAdd(&n_hits, 1);
-            if (slot < TIES) hit_list[slot] = id;
-        }
-    });
-    __syncthreads();
-    if (n_hits <= TIES) {
-        if (threadIdx.x == 0) {
-            for (int i = 1; i < n_hits; ++i) {          // by id, ascending
-                const int v = hit_list[i];
-                int j = i - 1;
-                for (; j >= 0 && hit_list[j] > v; --j) hit_list[j + 1] = hit_list[j];
-                hit_list[j + 1] = v;
-            }
-            found = nth < n_hits ? hit_list[nth] : -1;
-        }
-        __syncthreads();
-        const int id = found;
-        __syncthreads();
-        return id;
-    }
-    for (int start = 0; start < n; start += THREADS) {
-        const int id = start + threadIdx.x;
-        bool hit = false;
-        if (id < n) {
-            const float s = row[id];
-            const uint32_t b = order_bits(s);
-            if (b == bits) {
-                if (LEVEL == 0) hit = id != sets.skip;
-                else if (LEVEL == 1) hit = in_kept(sets, id, b);
-                else hit = in_nucleus(sets, id, b, expf((s - best_score) / temp));
-            }
-        }
-        // Rank of this hit among the block's hits in id order: ballot within the warp, warp totals through smem.
-        const unsigned ballot = __ballot_sync(0xffffffffu, hit);
-        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-        if (lane == 0) sh.count[warp] = __popc(ballot);
-        __syncthreads();
-        int before = base;
-        for (int w = 0; w < warp; ++w) before += sh.count[w];
-        before += __popc(ballot & ((1u << lane) - 1));
-        if (hit && before == nth) found = id;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            int total = 0;
-            for (int w = 0; w < THREADS / 32; ++w) total += sh.count[w];
-            base += total;
-        }
-        __syncthreads();
-        if (found >= 0 || base > nth) break;
-    }
-    __syncthreads();
-    return found;
+__device__ __forceinline__ bool in_level(const Sets& sets, int id, uint32_t b, float s, float best_score, float temp) {
+    if (LEVEL == 0) return id != sets.skip;
+    if (LEVEL == 1) return in_kept(sets, id, b);
+    return in_nucleus(sets, id, b, expf((s - best_score) / temp));
 }
 
-// Radix selection by count: the bits of the k-th best token (k >= 1) among the tokens of level 0
-// (not masked), and how many tokens with exactly those bits are among the k best.
-__device__ void select_by_count(const float* row, int n, int k, const Sets& sets, Shared& sh, uint32_t& out_bits,
-                                int& out_equal_taken) {
+// The id of the (nth + 1)-th token, in id order, with exactly these bits among the tokens of a set (level 0: not masked,
+// 1: kept, 2: nucleus); -1 if there are fewer.  Scores are rarely equal bit for bit: one pass lists the few tokens that
+// are and the leader picks among them; more ties than the list holds are walked by the leader alone, chunk by chunk.
+// Every thread of the cluster returns the same id.
+template <int LEVEL>
+__device__ int nth_with_bits(const Row& c, uint32_t bits, int nth, const Sets& sets, float best_score, float temp) {
+    Shared& sh = *c.sh;
+    scan_slice(c, [&](int id, float s, bool ok) {
+        if (!ok) return;
+        const uint32_t b = order_bits(s);
+        if (b != bits || !in_level<LEVEL>(sets, id, b, s, best_score, temp)) return;
+        const int slot = lead_take(&sh.n_hits);
+        if (slot < TIES) lead_store(&sh.hit_list[slot], id);
+    });
+    leader_turn(c, [&] {
+        if (threadIdx.x == 0) {
+            const int hits = sh.n_hits;
+            sh.n_hits = 0;
+            sh.i32[4] = hits;
+            if (hits <= TIES) {
+                for (int i = 1; i < hits; ++i) {          // by id, ascending
+                    const int v = sh.hit_list[i];
+                    int j = i - 1;
+                    for (; j >= 0 && sh.hit_list[j] > v; --j) sh.hit_list[j + 1] = sh.hit_list[j];
+                    sh.hit_list[j + 1] = v;
+                }
+                sh.i32[5] = nth < hits ? sh.hit_list[nth] : -1;
+            }
+        }
+    });
+    if (lead_load(&sh.i32[4]) <= TIES) return lead_load(&sh.i32[5]);
+    leader_turn(c, [&] {
+        // Rank of a hit among the row's hits in id order: ballot within the warp, warp totals through shared memory.
+        int& found = sh.i32[6];
+        int& base = sh.i32[7];
+        if (threadIdx.x == 0) { found = -1; base = 0; }
+        __syncthreads();
+        for (int start = 0; start < c.n; start += THREADS) {
+            const int id = start + threadIdx.x;
+            bool hit = false;
+            if (id < c.n) {
+                const float s = c.row[id];
+                const uint32_t b = order_bits(s);
+                hit = b == bits && in_level<LEVEL>(sets, id, b, s, best_score, temp);
+            }
+            const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+            const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+            if (lane == 0) sh.count[warp] = __popc(ballot);
+            __syncthreads();
+            int before = base;
+            for (int w = 0; w < warp; ++w) before += sh.count[w];
+            before += __popc(ballot & ((1u << lane) - 1));
+            if (hit && before == nth) found = id;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                int total = 0;
+                for (int w = 0; w < THREADS / 32; ++w) total += sh.count[w];
+                base += total;
+            }
+            __syncthreads();
+            if (found >= 0 || base > nth) break;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) sh.i32[5] = found;
+    });
+    return lead_load(&sh.i32[5]);
+}
+
+// Radix selection by count: the bits of the k-th best token (k >= 1) among the tokens that are not masked, and how many
+// tokens with exactly those bits are among the k best.  A round: every block counts its slice's tokens by the next
+// eight bits (the lanes of a warp that fall into one bin add to it once: most scores share their leading bits), adds
+// its bins to the leader's, and the leader finds the bin that holds the k-th.
+__device__ void select_by_count(const Row& c, int k, const Sets& sets, uint32_t& out_bits, int& out_equal_taken) {
+    Shared& sh = *c.sh;
     uint32_t prefix = 0, mask = 0;
     int remaining = k;
     for (int shift = 24; shift >= 0; shift -= 8) {
         for (int i = threadIdx.x; i < 256; i += THREADS) sh.count[i] = 0;
         __syncthreads();
-        // Most scores share their leading bits: the lanes of a warp that fall into one bin add to it once.
-        scan_row(row, n, [&](int id, float s, bool ok) {
+        scan_slice(c, [&](int id, float s, bool ok) {
             const uint32_t b = order_bits(s);
             const bool part = ok && id != sets.skip && (b & mask) == prefix;
             const unsigned who = __ballot_sync(0xffffffffu, part);
@@ -220,123 +314,124 @@ __device__ void select_by_count(const float* row, int n, int k, const Sets& sets
             }
         });
         __syncthreads();
-        if (threadIdx.x == 0) {
-            int acc = 0, bin = 255;
-            for (; bin > 0; --bin) {
-                if (acc + (int)sh.count[bin] >= remaining) break;
-                acc += (int)sh.count[bin];
+        if (threadIdx.x < 256 && sh.count[threadIdx.x]) lead_add(&sh.gcount[threadIdx.x], sh.count[threadIdx.x]);
+        leader_turn(c, [&] {
+            if (threadIdx.x == 0) {
+                int acc = 0, bin = 255;
+                for (; bin > 0; --bin) {
+                    if (acc + (int)sh.gcount[bin] >= remaining) break;
+                    acc += (int)sh.gcount[bin];
+                }
+                sh.u32[0] = (uint32_t)bin;
+                sh.i32[0] = remaining - acc;
             }
-            sh.u32[0] = (uint32_t)bin;
-            sh.i32[0] = remaining - acc;
-        }
-        __syncthreads();
-        prefix |= sh.u32[0] << shift;
+            __syncthreads();
+            if (threadIdx.x < 256) sh.gcount[threadIdx.x] = 0;        // for the next round
+        });
+        prefix |= lead_load(&sh.u32[0]) << shift;
         mask |= 255u << shift;
-        remaining = sh.i32[0];
-        __syncthreads();
+        remaining = lead_load(&sh.i32[0]);
     }
     out_bits = prefix;
     out_equal_taken = remaining;
 }
 
-// Radix selection by weight over the tokens of LEVEL, best first: the bits at which the running
-// weight first reaches `goal` (strict: first exceeds it), the weight of the tokens above those
-// bits, and how many tokens have exactly those bits.
+// Radix selection by weight over the tokens of LEVEL, best first: the bits at which the running weight first reaches
+// `goal` (strict: first exceeds it), the weight of the tokens above those bits, and how many tokens have exactly those
+// bits.
 template <int LEVEL>
-__device__ void select_by_weight(const float* row, int n, double goal, bool strict, const Sets& sets, float best_score,
-                                 float temp, Shared& sh, uint32_t& out_bits, double& out_above, int& out_equal_count) {
+__device__ void select_by_weight(const Row& c, double goal, bool strict, const Sets& sets, float best_score, float temp,
+                                 uint32_t& out_bits, double& out_above, int& out_equal_count) {
+    Shared& sh = *c.sh;
     uint32_t prefix = 0, mask = 0;
     double above = 0.0;
     for (int shift = 24; shift >= 0; shift -= 8) {
         for (int i = threadIdx.x; i < 256; i += THREADS) { sh.count[i] = 0; sh.weight[i] = 0.0; }
         __syncthreads();
-        for (int id = threadIdx.x; id < n; id += THREADS) {
-            const float s = row[id];
+        scan_slice(c, [&](int id, float s, bool ok) {
+            if (!ok) return;
             const uint32_t b = order_bits(s);
-            if ((b & mask) != prefix) continue;
+            if ((b & mask) != prefix) return;
             const float w = expf((s - best_score) / temp);
             const bool in = LEVEL == 1 ? in_kept(sets, id, b) : in_nucleus(sets, id, b, w);
-            if (!in) continue;
+            if (!in) return;
             const int bin = (b >> shift) & 255u;
             atomicAdd(&sh.count[bin], 1u);
             atomicAdd(&sh.weight[bin], (double)w);
-        }
+        });
         __syncthreads();
-        if (threadIdx.x == 0) {
-            double acc = above;
-            int bin = 255, last_nonempty = -1;
-            for (; bin >= 0; --bin) {
-                if (!sh.count[bin]) continue;
-                last_nonempty = bin;
-                const double next = acc + sh.weight[bin];
-                if (strict ? (goal < next) : (next >= goal)) break;
-                acc = next;
-            }
-            if (bin < 0) {               // rounding left the goal just out of reach: stop at the last tokens
-                bin = last_nonempty < 0 ? 0 : last_nonempty;
-                acc -= sh.weight[bin];
-            }
-            sh.u32[0] = (uint32_t)bin;
-            sh.f64[0] = acc;
-            sh.i32[0] = (int)sh.count[bin];
+        if (threadIdx.x < 256 && sh.count[threadIdx.x]) {
+            lead_add(&sh.gcount[threadIdx.x], sh.count[threadIdx.x]);
+            lead_add(&sh.gweight[threadIdx.x], sh.weight[threadIdx.x]);
         }
-        __syncthreads();
-        prefix |= sh.u32[0] << shift;
+        leader_turn(c, [&] {
+            if (threadIdx.x == 0) {
+                double acc = above;
+                int bin = 255, last_nonempty = -1;
+                for (; bin >= 0; --bin) {
+                    if (!sh.gcount[bin]) continue;
+                    last_nonempty = bin;
+                    const double next = acc + sh.gweight[bin];
+                    if (strict ? (goal < next) : (next >= goal)) break;
+                    acc = next;
+                }
+                if (bin < 0) {               // rounding left the goal just out of reach: stop at the last tokens
+                    bin = last_nonempty < 0 ? 0 : last_nonempty;
+                    acc -= sh.gweight[bin];
+                }
+                sh.u32[0] = (uint32_t)bin;
+                sh.f64[0] = acc;
+                sh.i32[0] = (int)sh.gcount[bin];
+            }
+            __syncthreads();
+            if (threadIdx.x < 256) { sh.gcount[threadIdx.x] = 0; sh.gweight[threadIdx.x] = 0.0; }
+        });
+        prefix |= lead_load(&sh.u32[0]) << shift;
         mask |= 255u << shift;
-        above = sh.f64[0];
-        out_equal_count = sh.i32[0];
-        __syncthreads();
+        above = lead_load(&sh.f64[0]);
+        out_equal_count = lead_load(&sh.i32[0]);
     }
     out_bits = prefix;
     out_above = above;
 }
 
-// Sum of the weights of LEVEL's tokens (min-p zeroing applied when asked), every thread gets the total.
+// Sum of the weights of LEVEL's tokens, every thread of the cluster gets the total.
 template <int LEVEL>
-__device__ double total_weight(const float* row, int n, const Sets& sets, float best_score, float temp, float zero_below,
-                               Shared& sh) {
+__device__ double total_weight(const Row& c, const Sets& sets, float best_score, float temp) {
+    Shared& sh = *c.sh;
     double mine = 0.0;
-    for (int id = threadIdx.x; id < n; id += THREADS) {
-        const float s = row[id];
+    scan_slice(c, [&](int id, float s, bool ok) {
+        if (!ok) return;
         const uint32_t b = order_bits(s);
-        float w = expf((s - best_score) / temp);
+        const float w = expf((s - best_score) / temp);
         const bool in = LEVEL == 1 ? in_kept(sets, id, b) : in_nucleus(sets, id, b, w);
-        if (!in) continue;
-        if (w < zero_below) w = 0.0f;
-        mine += (double)w;
-    }
+        if (in) mine += (double)w;
+    });
     sh.scan[threadIdx.x] = mine;
     __syncthreads();
     for (int o = THREADS / 2; o > 0; o >>= 1) {
         if (threadIdx.x < o) sh.scan[threadIdx.x] += sh.scan[threadIdx.x + o];
         __syncthreads();
     }
-    const double total = sh.scan[0];
-    __syncthreads();
-    return total;
+    if (threadIdx.x == 0) lead_add(&sh.gsum, sh.scan[0]);
+    leader_turn(c, [&] {
+        if (threadIdx.x == 0) {
+            sh.f64[1] = sh.gsum;
+            sh.gsum = 0.0;
+        }
+    });
+    return lead_load(&sh.f64[1]);
 }
 
-__global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict__ logits, int vocab,
-                                                         const RowParams* __restrict__ params, int* __restrict__ out) {
-    pdl_trigger();
-    pdl_wait();
-    __shared__ Shared sh;
-    const float* row = logits + (size_t)blockIdx.x * vocab;
-    const RowParams p = params[blockIdx.x];
-    const int n = vocab;
-    Sets sets;
-    sets.skip = (p.masked >= 0 && p.masked < n && n > 1) ? p.masked : -1;
-    sets.has_topk = sets.has_nucleus = sets.has_minp = false;
-    sets.topk_bits = sets.nuc_bits = 0;
-    sets.topk_last_id = sets.nuc_last_id = n;
-    sets.min_p = 0.0f;
-
-    // ---- the best token: largest score, ties to the lowest id; a NaN only as the first token taking part
-    const int first = sets.skip == 0 ? 1 : 0;
+// The best token: largest score, ties to the lowest id; a NaN only as the first token taking part
+// (src/inference/sampler.hpp:88-132).  Every thread of the cluster returns the same id.
+__device__ int best_token(const Row& c, int skip) {
+    Shared& sh = *c.sh;
+    const int first = skip == 0 ? 1 : 0;
     float bs = -INFINITY;
     int bi = first;
-    scan_row(row, n, [&](int id, float s, bool ok) {
-        if (ok && id != sets.skip && (s > bs || (s == bs && id < bi))) { bs = s; bi = id; }
+    scan_slice(c, [&](int id, float s, bool ok) {
+        if (ok && id != skip && (s > bs || (s == bs && id < bi))) { bs = s; bi = id; }
     });
     for (int o = 16; o > 0; o >>= 1) {
         const float os = __shfl_xor_sync(0xffffffffu, bs, o);
@@ -348,16 +443,63 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
     if (threadIdx.x == 0) {
         for (int w = 1; w < THREADS / 32; ++w)
             if (sh.best_score[w] > bs || (sh.best_score[w] == bs && sh.best_id[w] < bi)) { bs = sh.best_score[w]; bi = sh.best_id[w]; }
-        if (isnan(row[first])) bi = first;
-        sh.i32[1] = bi;
+        lead_store(&sh.part_score[c.rank], bs);
+        lead_store(&sh.part_id[c.rank], bi);
     }
+    leader_turn(c, [&] {
+        if (threadIdx.x == 0) {
+            float s = sh.part_score[0];
+            int i = sh.part_id[0];
+            for (uint32_t b = 1; b < c.blocks; ++b)
+                if (sh.part_score[b] > s || (sh.part_score[b] == s && sh.part_id[b] < i)) { s = sh.part_score[b]; i = sh.part_id[b]; }
+            if (isnan(c.row[first])) i = first;
+            sh.i32[1] = i;
+        }
+    });
+    return lead_load(&sh.i32[1]);
+}
+
+__device__ __forceinline__ Row row_of_block(const float* logits, int vocab, Shared* sh) {
+    Row c;
+    c.row = logits + (size_t)blockIdx.y * vocab;
+    c.n = vocab;
+    c.rank = cluster_rank();
+    c.blocks = cluster_blocks();
+    const int per = (((vocab + (int)c.blocks - 1) / (int)c.blocks) + 3) & ~3;      // slices begin at multiples of four
+    c.lo = min(vocab, (int)c.rank * per);
+    c.hi = min(vocab, c.lo + per);
+    c.sh = sh;
+    return c;
+}
+
+__global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict__ logits, int vocab,
+                                                         const RowParams* __restrict__ params, int* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ Shared sh;
+    const Row c = row_of_block(logits, vocab, &sh);
+    const float* row = c.row;
+    const RowParams p = params[blockIdx.y];
+    const int n = vocab;
+    // What the blocks meet in starts empty (only the leader's copy is ever used).
+    for (int i = threadIdx.x; i < 256; i += THREADS) { sh.gcount[i] = 0; sh.gweight[i] = 0.0; }
+    if (threadIdx.x == 0) { sh.gsum = 0.0; sh.n_hits = 0; sh.n_kept = 0; sh.walked = -1; }
     __syncthreads();
-    const int best = sh.i32[1];
+    cluster_sync();
+
+    Sets sets;
+    sets.skip = (p.masked >= 0 && p.masked < n && n > 1) ? p.masked : -1;
+    sets.has_topk = sets.has_nucleus = sets.has_minp = false;
+    sets.topk_bits = sets.nuc_bits = 0;
+    sets.topk_last_id = sets.nuc_last_id = n;
+    sets.min_p = 0.0f;
+
+    const int best = best_token(c, sets.skip);
     const float best_score = row[best];
     sets.best = best;
-    __syncthreads();
     if (!(p.temperature > 0.0f)) {
-        if (threadIdx.x == 0) out[blockIdx.x] = best;
+        if (c.rank == 0 && threadIdx.x == 0) out[blockIdx.y] = best;
+        cluster_sync();          // the other blocks have read the best token from the leader
         return;
     }
     const float temp = p.temperature;
@@ -368,49 +510,46 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
     if (keep < m) {
         uint32_t bits;
         int taken;
-        select_by_count(row, n, keep, sets, sh, bits, taken);
-        const int last = nth_with_bits<0>(row, n, bits, taken - 1, sets, best_score, temp, sh);
+        select_by_count(c, keep, sets, bits, taken);
+        const int last = nth_with_bits<0>(c, bits, taken - 1, sets, best_score, temp);
         sets.has_topk = true;
         sets.topk_bits = bits;
         sets.topk_last_id = last < 0 ? n : last;
     }
 
     if (sets.has_topk && keep <= KMAX) {
-        // ---- the kept tokens fit shared memory: gather them, put them in the order of the walk (ids ascending
-        // without top-p, best first with it), and let one thread walk them as the reference's sampler does.
-        __shared__ int c_id[KMAX], o_id[KMAX];
-        __shared__ uint32_t c_bits[KMAX];
-        __shared__ float c_w[KMAX], o_w[KMAX];
-        __shared__ int n_kept;
-        if (threadIdx.x == 0) n_kept = 0;
-        __syncthreads();
-        scan_row(row, n, [&](int id, float s, bool ok) {
+        // ---- the kept tokens fit shared memory: gather them in the leader's, put them in the order of the walk (ids
+        // ascending without top-p, best first with it), and let one thread walk them as the reference's sampler does.
+        scan_slice(c, [&](int id, float s, bool ok) {
             if (!ok) return;
             const uint32_t b = order_bits(s);
             if (!in_kept(sets, id, b)) return;
-            const int slot = atomicAdd(&n_kept, 1);
+            const int slot = lead_take(&sh.n_kept);
             if (slot < KMAX) {
-                c_id[slot] = id;
-                c_bits[slot] = b;
-                c_w[slot] = expf((s - best_score) / temp);
+                lead_store(&sh.c_id[slot], id);
+                lead_store(&sh.c_bits[slot], b);
+                lead_store(&sh.c_w[slot], expf((s - best_score) / temp));
             }
         });
-        __syncthreads();
-        const int K = min(n_kept, KMAX);
+        cluster_sync();
+        if (c.rank != 0) return;
+        const int K = min(sh.n_kept, KMAX);
         const bool ranked = p.top_p < 1.0f;
         for (int i = threadIdx.x; i < K; i += THREADS) {
-            const int id = c_id[i];
-            const uint32_t b = c_bits[i];
+            const int id = sh.c_id[i];
+            const uint32_t b = sh.c_bits[i];
             int before = 0;
             for (int j = 0; j < K; ++j) {
-                const bool first_j = ranked ? (c_bits[j] > b || (c_bits[j] == b && c_id[j] < id)) : c_id[j] < id;
+                const bool first_j = ranked ? (sh.c_bits[j] > b || (sh.c_bits[j] == b && sh.c_id[j] < id)) : sh.c_id[j] < id;
                 before += first_j ? 1 : 0;
             }
-            o_id[before] = id;
-            o_w[before] = c_w[i];
+            sh.o_id[before] = id;
+            sh.o_w[before] = sh.c_w[i];
         }
         __syncthreads();
         if (threadIdx.x == 0) {
+            const int* o_id = sh.o_id;
+            const float* o_w = sh.o_w;
             int pick = best;
             if (!ranked) {
                 // id order: min-p zeroes the weights below it; the first token whose running sum exceeds the target
@@ -450,17 +589,19 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
                 }
                 if (last >= 0) pick = last;
             }
-            out[blockIdx.x] = pick;
+            out[blockIdx.y] = pick;
         }
         return;
     }
 
     int chosen = best;
     if (p.top_p >= 1.0f) {
-        // ---- id order: each thread owns a run of consecutive ids; runs are scanned, one thread walks its run
+        // ---- id order over the whole vocabulary: every thread of the cluster owns a run of consecutive ids; the runs'
+        // weights are scanned (within the block, then over the blocks), one thread walks its run
         const float cut = p.min_p > 0.0f ? p.min_p : 0.0f;
-        const int seg = (n + THREADS - 1) / THREADS;
-        const int lo = threadIdx.x * seg, hi = min(n, lo + seg);
+        const int owners = (int)c.blocks * THREADS;
+        const int seg = (n + owners - 1) / owners;
+        const int lo = min(n, ((int)c.rank * THREADS + (int)threadIdx.x) * seg), hi = min(n, lo + seg);
         double mine = 0.0;
         for (int id = lo; id < hi; ++id) {
             const float s = row[id];
@@ -474,12 +615,17 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
         if (threadIdx.x == 0) {
             double acc = 0.0;
             for (int t = 0; t < THREADS; ++t) { const double v = sh.scan[t]; sh.scan[t] = acc; acc += v; }
-            sh.f64[1] = acc;
-            sh.i32[2] = -1;
+            lead_store(&sh.part_total[c.rank], acc);
         }
         __syncthreads();
-        const double target = (double)p.r * sh.f64[1];
-        const double before = sh.scan[threadIdx.x];
+        cluster_sync();
+        double before = sh.scan[threadIdx.x], total = 0.0;
+        for (uint32_t b = 0; b < c.blocks; ++b) {
+            const double t = lead_load(&sh.part_total[b]);
+            if (b < c.rank) before += t;
+            total += t;
+        }
+        const double target = (double)p.r * total;
         if (target >= before && target < before + mine) {
             double acc = before;
             for (int id = lo; id < hi; ++id) {
@@ -488,95 +634,63 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
                 float w = expf((s - best_score) / temp);
                 if (w < cut) w = 0.0f;
                 acc += (double)w;
-                if (target < acc) { sh.i32[2] = id; break; }
+                if (target < acc) { lead_store(&sh.walked, id); break; }
             }
         }
-        __syncthreads();
-        if (sh.i32[2] >= 0) chosen = sh.i32[2];
-    } else {
-        // ---- rank order: nucleus by weight, min-p on its tail, then the draw best first
-        const double kept_weight = total_weight<1>(row, n, sets, best_score, temp, 0.0f, sh);
-        const double goal = (double)p.top_p * kept_weight;
-        uint32_t bits;
-        double above;
-        int equal;
-        select_by_weight<1>(row, n, goal, false, sets, best_score, temp, sh, bits, above, equal);
-        {
-            // Tokens with the threshold's bits all weigh the same; take as many as reach the goal (at least one).
-            const float s_t = __uint_as_float((bits & 0x80000000u) ? (bits & 0x7fffffffu) : ~bits);
-            const double w_t = (double)expf((s_t - best_score) / temp);
-            long long j = 1;
-            if (w_t > 0.0 && above + w_t < goal) j = (long long)ceil((goal - above) / w_t);
-            if (j < 1) j = 1;
-            if (j > equal) j = equal;
-            const int last = nth_with_bits<1>(row, n, bits, (int)j - 1, sets, best_score, temp, sh);
-            sets.has_nucleus = true;
-            sets.nuc_bits = bits;
-            sets.nuc_last_id = last < 0 ? n : last;
-        }
-        if (p.min_p > 0.0f) { sets.has_minp = true; sets.min_p = p.min_p; }
-        const double nucleus_weight = total_weight<2>(row, n, sets, best_score, temp, 0.0f, sh);
-        const double target = (double)p.r * nucleus_weight;
-        select_by_weight<2>(row, n, target, true, sets, best_score, temp, sh, bits, above, equal);
-        {
-            const float s_t = __uint_as_float((bits & 0x80000000u) ? (bits & 0x7fffffffu) : ~bits);
-            const double w_t = (double)expf((s_t - best_score) / temp);
-            long long i = 0;
-            if (w_t > 0.0 && target > above) i = (long long)floor((target - above) / w_t);
-            if (i >= equal) i = equal - 1;
-            if (i < 0) i = 0;
-            const int id = nth_with_bits<2>(row, n, bits, (int)i, sets, best_score, temp, sh);
-            if (id >= 0) chosen = id;
-        }
+        cluster_sync();
+        if (c.rank == 0 && threadIdx.x == 0) out[blockIdx.y] = sh.walked >= 0 ? sh.walked : best;
+        return;
     }
-    if (threadIdx.x == 0) out[blockIdx.x] = chosen;
+    // ---- rank order over the whole vocabulary: nucleus by weight, min-p on its tail, then the draw best first
+    const double kept_weight = total_weight<1>(c, sets, best_score, temp);
+    const double goal = (double)p.top_p * kept_weight;
+    uint32_t bits;
+    double above;
+    int equal;
+    select_by_weight<1>(c, goal, false, sets, best_score, temp, bits, above, equal);
+    {
+        // Tokens with the threshold's bits all weigh the same; take as many as reach the goal (at least one).
+        const float s_t = __uint_as_float((bits & 0x80000000u) ? (bits & 0x7fffffffu) : ~bits);
+        const double w_t = (double)expf((s_t - best_score) / temp);
+        long long j = 1;
+        if (w_t > 0.0 && above + w_t < goal) j = (long long)ceil((goal - above) / w_t);
+        if (j < 1) j = 1;
+        if (j > equal) j = equal;
+        const int last = nth_with_bits<1>(c, bits, (int)j - 1, sets, best_score, temp);
+        sets.has_nucleus = true;
+        sets.nuc_bits = bits;
+        sets.nuc_last_id = last < 0 ? n : last;
+    }
+    if (p.min_p > 0.0f) { sets.has_minp = true; sets.min_p = p.min_p; }
+    const double nucleus_weight = total_weight<2>(c, sets, best_score, temp);
+    const double target = (double)p.r * nucleus_weight;
+    select_by_weight<2>(c, target, true, sets, best_score, temp, bits, above, equal);
+    {
+        const float s_t = __uint_as_float((bits & 0x80000000u) ? (bits & 0x7fffffffu) : ~bits);
+        const double w_t = (double)expf((s_t - best_score) / temp);
+        long long i = 0;
+        if (w_t > 0.0 && target > above) i = (long long)floor((target - above) / w_t);
+        if (i >= equal) i = equal - 1;
+        if (i < 0) i = 0;
+        const int id = nth_with_bits<2>(c, bits, (int)i, sets, best_score, temp);
+        if (id >= 0) chosen = id;
+    }
+    if (c.rank == 0 && threadIdx.x == 0) out[blockIdx.y] = chosen;
+    cluster_sync();              // the other blocks have read the last decision from the leader
 }
 
-// Greedy rows only: the largest score, ties to the lowest id, a NaN only as the first token taking part
-// (src/inference/sampler.hpp:88-132), with 16-byte loads.  Used when no row of the batch draws.
+// Greedy rows only: the best token of every row.  Used when no row of the batch draws.
 __global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict__ logits, int vocab,
                                                          const RowParams* __restrict__ params, int* __restrict__ out) {
     pdl_trigger();
     pdl_wait();
-    __shared__ float best_score[32];
-    __shared__ int best_id[32];
-    const float* row = logits + (size_t)blockIdx.x * vocab;
-    const int masked = params[blockIdx.x].masked;
+    __shared__ Shared sh;
+    const Row c = row_of_block(logits, vocab, &sh);
+    const int masked = params[blockIdx.y].masked;
     const int skip = (masked >= 0 && masked < vocab && vocab > 1) ? masked : -1;
-    const int first = skip == 0 ? 1 : 0;
-    float bs = -INFINITY;
-    int bi = first;
-    const bool vec = (vocab % 4 == 0) && (((uintptr_t)row & 15) == 0);
-    if (vec) {
-        const float4* row4 = reinterpret_cast<const float4*>(row);
-        for (int i = threadIdx.x; i < vocab / 4; i += THREADS) {
-            const float4 v = row4[i];
-            const float e[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const int id = 4 * i + k;
-                if (id != skip && (e[k] > bs || (e[k] == bs && id < bi))) { bs = e[k]; bi = id; }
-            }
-        }
-    } else {
-        for (int id = threadIdx.x; id < vocab; id += THREADS) {
-            const float s = row[id];
-            if (id != skip && (s > bs || (s == bs && id < bi))) { bs = s; bi = id; }
-        }
-    }
-    for (int o = 16; o > 0; o >>= 1) {
-        const float os = __shfl_xor_sync(0xffffffffu, bs, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (os > bs || (os == bs && oi < bi)) { bs = os; bi = oi; }
-    }
-    if ((threadIdx.x & 31) == 0) { best_score[threadIdx.x >> 5] = bs; best_id[threadIdx.x >> 5] = bi; }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        for (int w = 1; w < THREADS / 32; ++w)
-            if (best_score[w] > bs || (best_score[w] == bs && best_id[w] < bi)) { bs = best_score[w]; bi = best_id[w]; }
-        if (isnan(row[first])) bi = first;
-        out[blockIdx.x] = bi;
-    }
+    const int best = best_token(c, skip);
+    if (c.rank == 0 && threadIdx.x == 0) out[blockIdx.y] = best;
+    cluster_sync();              // the other blocks have read the best token from the leader
 }
 
 // One thread per (row, seen token): the repetition penalty, then the additive ones.
@@ -598,6 +712,29 @@ __global__ void penalty_kernel(float* __restrict__ logits, int vocab, const int*
     *v = s;
 }
 
+// A row's blocks: one for a small vocabulary, up to eight (a portable cluster) for a large one.
+int blocks_for(int vocab) { return vocab >= 65536 ? 8 : vocab >= 16384 ? 4 : vocab >= 8192 ? 2 : 1; }
+
+template <typename K>
+int launch_rows(K kernel, int rows, int vocab, const float* logits, const RowParams* params, int* out, cudaStream_t stream) {
+    const int blocks = blocks_for(vocab);
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3((unsigned)blocks, (unsigned)rows, 1);
+    lc.blockDim = dim3(THREADS);
+    lc.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)blocks;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr;
+    lc.numAttrs = llmx_pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&lc, kernel, logits, vocab, params, out);
+    return launch_status();
+}
+
 }  // namespace
 
 // params: rows x {temperature, top_p, min_p, r, top_k, masked} (24 bytes each) on the device.
@@ -605,13 +742,9 @@ __global__ void penalty_kernel(float* __restrict__ logits, int vocab, const int*
 LLMX_EXPORT int llmx_sample(const float* logits, int rows, int vocab, const void* params, int* out, int all_greedy,
                             cudaStream_t stream) {
     if (rows <= 0) return 0;
-    if (vocab <= 0) return LLMX_ERR_BAD_ARGUMENT;
-    if (all_greedy) {
-        launch_kernel(argmax_kernel, dim3(rows), dim3(THREADS), 0, stream, logits, vocab, (const RowParams*)params, out);
-        return launch_status();
-    }
-    launch_kernel(sample_kernel, dim3(rows), dim3(THREADS), 0, stream, logits, vocab, (const RowParams*)params, out);
-    return launch_status();
+    if (vocab <= 0 || rows > 65535) return LLMX_ERR_BAD_ARGUMENT;
+    if (all_greedy) return launch_rows(argmax_kernel, rows, vocab, logits, (const RowParams*)params, out, stream);
+    return launch_rows(sample_kernel, rows, vocab, logits, (const RowParams*)params, out, stream);
 }
 
 LLMX_EXPORT int llmx_penalize(float* logits, int vocab, const int* row_of, const int* token, const int* count,
