@@ -76,6 +76,11 @@ __device__ __forceinline__ int lead_take(const int* p) {       // the leader's c
     asm volatile("atom.relaxed.cluster.shared::cluster.add.s32 %0, [%1], 1;" : "=r"(old) : "r"(on_leader(p)) : "memory");
     return old;
 }
+__device__ __forceinline__ int lead_reserve(const int* p, int n) {       // the leader's counter before it is raised by n
+    int old;
+    asm volatile("atom.relaxed.cluster.shared::cluster.add.s32 %0, [%1], %2;" : "=r"(old) : "r"(on_leader(p)), "r"(n) : "memory");
+    return old;
+}
 __device__ __forceinline__ void lead_store(const int* p, int v) {
     asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(on_leader(p)), "r"(v) : "memory");
 }
@@ -124,7 +129,7 @@ struct Shared {
     int n_hits, n_kept, walked;
     int hit_list[TIES];
     int c_id[KMAX], o_id[KMAX];
-    uint32_t c_bits[KMAX];
+    uint32_t c_bits[KMAX], l_bits[KMAX];
     float c_w[KMAX], o_w[KMAX];
 };
 
@@ -224,6 +229,46 @@ __device__ __forceinline__ bool in_level(const Sets& sets, int id, uint32_t b, f
     return in_nucleus(sets, id, b, expf((s - best_score) / temp));
 }
 
+// The bin a radix round stops at, found by the leader's first warp: bins are walked from 255 down, `acc` (starting at
+// `above`) grows by each bin's amount, and the walk stops at the first bin where `reached(acc, acc + amount)` holds.
+// A lane sums eight consecutive bins, a shuffle scan gives what lies above each lane, the one lane whose bins hold the
+// stop walks them.  Returns the bin (or -1 when no bin stops the walk) and the amount above it; every lane of the
+// warp gets both.
+template <typename T, typename Amount, typename Reached>
+__device__ __forceinline__ int find_bin(Amount&& amount, T above, Reached&& reached, T& out_above) {
+    const int lane = threadIdx.x & 31;
+    T mine = 0;
+#pragma unroll
+    for (int b = 0; b < 8; ++b) mine += amount(lane * 8 + b);
+    // what the lanes above this one hold (lane 31 holds the highest bins)
+    T higher = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const T up = __shfl_down_sync(0xffffffffu, higher, o);
+        if (lane + o < 32) higher += up;
+    }
+    higher = higher - mine + above;
+    const bool here = reached(higher, higher + mine) ;
+    const unsigned stops = __ballot_sync(0xffffffffu, here);
+    if (!stops) {
+        out_above = above;
+        return -1;
+    }
+    const int owner = 31 - __clz(stops);              // the highest lane whose bins reach it
+    int bin = -1;
+    T acc = higher;
+    if (lane == owner) {
+        for (int b = 7; b >= 0; --b) {
+            const T a = amount(lane * 8 + b);
+            if (reached(acc, acc + a)) { bin = lane * 8 + b; break; }
+            acc += a;
+        }
+    }
+    bin = __shfl_sync(0xffffffffu, bin, owner);
+    out_above = __shfl_sync(0xffffffffu, acc, owner);
+    return bin;
+}
+
 // The id of the (nth + 1)-th token, in id order, with exactly these bits among the tokens of a set (level 0: not masked,
 // 1: kept, 2: nucleus); -1 if there are fewer.  Scores are rarely equal bit for bit: one pass lists the few tokens that
 // are and the leader picks among them; more ties than the list holds are walked by the leader alone, chunk by chunk.
@@ -294,8 +339,7 @@ __device__ int nth_with_bits(const Row& c, uint32_t bits, int nth, const Sets& s
 
 // Radix selection by count: the bits of the k-th best token (k >= 1) among the tokens that are not masked, and how many
 // tokens with exactly those bits are among the k best.  A round: every block counts its slice's tokens by the next
-// eight bits (the lanes of a warp that fall into one bin add to it once: most scores share their leading bits), adds
-// its bins to the leader's, and the leader finds the bin that holds the k-th.
+// eight bits, adds its bins to the leader's, and the leader finds the bin that holds the k-th.
 __device__ void select_by_count(const Row& c, int k, const Sets& sets, uint32_t& out_bits, int& out_equal_taken) {
     Shared& sh = *c.sh;
     uint32_t prefix = 0, mask = 0;
@@ -303,27 +347,34 @@ __device__ void select_by_count(const Row& c, int k, const Sets& sets, uint32_t&
     for (int shift = 24; shift >= 0; shift -= 8) {
         for (int i = threadIdx.x; i < 256; i += THREADS) sh.count[i] = 0;
         __syncthreads();
+        // Most scores share their leading bits: a thread keeps the count of the bin it met last and adds it to the
+        // block's bins only when the bin changes.
+        int run_bin = -1;
+        unsigned run = 0;
         scan_slice(c, [&](int id, float s, bool ok) {
             const uint32_t b = order_bits(s);
-            const bool part = ok && id != sets.skip && (b & mask) == prefix;
-            const unsigned who = __ballot_sync(0xffffffffu, part);
-            if (part) {
-                const unsigned bin = (b >> shift) & 255u;
-                const unsigned peers = __match_any_sync(who, bin);
-                if ((int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&sh.count[bin], (unsigned)__popc(peers));
+            if (!(ok && id != sets.skip && (b & mask) == prefix)) return;
+            const int bin = (b >> shift) & 255u;
+            if (bin != run_bin) {
+                if (run) atomicAdd(&sh.count[run_bin], run);
+                run_bin = bin;
+                run = 0;
             }
+            ++run;
         });
+        if (run) atomicAdd(&sh.count[run_bin], run);
         __syncthreads();
         if (threadIdx.x < 256 && sh.count[threadIdx.x]) lead_add(&sh.gcount[threadIdx.x], sh.count[threadIdx.x]);
         leader_turn(c, [&] {
-            if (threadIdx.x == 0) {
-                int acc = 0, bin = 255;
-                for (; bin > 0; --bin) {
-                    if (acc + (int)sh.gcount[bin] >= remaining) break;
-                    acc += (int)sh.gcount[bin];
+            if (threadIdx.x < 32) {
+                int above = 0;
+                int bin = find_bin<int>([&](int i) { return (int)sh.gcount[i]; }, 0,
+                                        [&](int before, int after) { return after >= remaining && after > before; }, above);
+                if (bin < 0) { bin = 0; above = 0; for (int i = 1; i < 256; ++i) above += (int)sh.gcount[i]; }
+                if (threadIdx.x == 0) {
+                    sh.u32[0] = (uint32_t)bin;
+                    sh.i32[0] = remaining - above;
                 }
-                sh.u32[0] = (uint32_t)bin;
-                sh.i32[0] = remaining - acc;
             }
             __syncthreads();
             if (threadIdx.x < 256) sh.gcount[threadIdx.x] = 0;        // for the next round
@@ -348,6 +399,13 @@ __device__ void select_by_weight(const Row& c, double goal, bool strict, const S
     for (int shift = 24; shift >= 0; shift -= 8) {
         for (int i = threadIdx.x; i < 256; i += THREADS) { sh.count[i] = 0; sh.weight[i] = 0.0; }
         __syncthreads();
+        // Additions of doubles to shared memory are slow when many threads meet in a bin, and the first rounds have a
+        // handful of bins for all tokens: a thread keeps four bins' counts and sums to itself and adds a bin's to the
+        // block's only when it needs the place for another.
+        int held_bin[4] = {-1, -1, -1, -1};
+        unsigned held_count[4] = {0, 0, 0, 0};
+        double held_weight[4] = {0.0, 0.0, 0.0, 0.0};
+        int next_out = 0;
         scan_slice(c, [&](int id, float s, bool ok) {
             if (!ok) return;
             const uint32_t b = order_bits(s);
@@ -356,9 +414,34 @@ __device__ void select_by_weight(const Row& c, double goal, bool strict, const S
             const bool in = LEVEL == 1 ? in_kept(sets, id, b) : in_nucleus(sets, id, b, w);
             if (!in) return;
             const int bin = (b >> shift) & 255u;
-            atomicAdd(&sh.count[bin], 1u);
-            atomicAdd(&sh.weight[bin], (double)w);
+            bool found = false;
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (held_bin[e] == bin) {
+                    ++held_count[e];
+                    held_weight[e] += (double)w;
+                    found = true;
+                }
+            if (found) return;
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (e == next_out) {
+                    if (held_count[e]) {
+                        atomicAdd(&sh.count[held_bin[e]], held_count[e]);
+                        atomicAdd(&sh.weight[held_bin[e]], held_weight[e]);
+                    }
+                    held_bin[e] = bin;
+                    held_count[e] = 1;
+                    held_weight[e] = (double)w;
+                }
+            next_out = (next_out + 1) & 3;
         });
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            if (held_count[e]) {
+                atomicAdd(&sh.count[held_bin[e]], held_count[e]);
+                atomicAdd(&sh.weight[held_bin[e]], held_weight[e]);
+            }
         __syncthreads();
         if (threadIdx.x < 256 && sh.count[threadIdx.x]) {
             lead_add(&sh.gcount[threadIdx.x], sh.count[threadIdx.x]);
@@ -520,17 +603,35 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
     if (sets.has_topk && keep <= KMAX) {
         // ---- the kept tokens fit shared memory: gather them in the leader's, put them in the order of the walk (ids
         // ascending without top-p, best first with it), and let one thread walk them as the reference's sampler does.
+        // (each block lists its own first, in the lists that the leader orders them into later, then takes room for
+        // all of them in the leader's lists at once: a thousand single additions to one counter of another block's
+        // shared memory would take longer than everything else)
+        __shared__ int n_mine, my_base;
+        if (threadIdx.x == 0) n_mine = 0;
+        __syncthreads();
         scan_slice(c, [&](int id, float s, bool ok) {
             if (!ok) return;
             const uint32_t b = order_bits(s);
             if (!in_kept(sets, id, b)) return;
-            const int slot = lead_take(&sh.n_kept);
+            const int slot = atomicAdd(&n_mine, 1);
             if (slot < KMAX) {
-                lead_store(&sh.c_id[slot], id);
-                lead_store(&sh.c_bits[slot], b);
-                lead_store(&sh.c_w[slot], expf((s - best_score) / temp));
+                sh.o_id[slot] = id;
+                sh.l_bits[slot] = b;
+                sh.o_w[slot] = expf((s - best_score) / temp);
             }
         });
+        __syncthreads();
+        const int mine = min(n_mine, KMAX);
+        if (threadIdx.x == 0) my_base = lead_reserve(&sh.n_kept, mine);
+        __syncthreads();
+        for (int i = threadIdx.x; i < mine; i += THREADS) {
+            const int slot = my_base + i;
+            if (slot < KMAX) {
+                lead_store(&sh.c_id[slot], sh.o_id[i]);
+                lead_store(&sh.c_bits[slot], sh.l_bits[i]);
+                lead_store(&sh.c_w[slot], sh.o_w[i]);
+            }
+        }
         cluster_sync();
         if (c.rank != 0) return;
         const int K = min(sh.n_kept, KMAX);

@@ -525,6 +525,31 @@ def test_sampling_against_the_plain_sampler(vocab):
     assert got == expected
 
 
+@pytest.mark.parametrize("vocab", [9001, 40000, 151936])
+@pytest.mark.parametrize("coarse", [False, True])
+def test_sampling_settings_at_random_against_the_plain_sampler(vocab, coarse):
+    """Vocabularies that two, four and eight blocks share; settings drawn at random (top-k beyond what is gathered into
+    shared memory too); with `coarse`, scores on a grid of quarters, so that hundreds of tokens tie exactly at every
+    threshold: ties go to the lowest ids, whichever block holds them."""
+    rng = np.random.default_rng(vocab + int(coarse))
+    settings = []
+    for i in range(24):
+        settings.append(dict(temp=float(rng.choice([0.3, 0.8, 1.0, 1.7])), top_k=int(rng.choice([0, 1, 7, 40, 300, 1024, 1025, 3000])),
+                             top_p=float(rng.choice([1.0, 0.95, 0.6, 0.1])), min_p=float(rng.choice([0.0, 0.0, 0.05, 0.3])),
+                             seed=int(rng.integers(1, 1 << 40))))
+        if i % 5 == 0:
+            settings[-1]["masked"] = int(rng.integers(0, vocab))
+    logits = (rng.standard_normal((len(settings), vocab)) * 2.5).astype(np.float32)
+    if coarse:
+        logits = (np.round(logits * 4) / 4).astype(np.float32)
+    expected = []
+    for row, s in zip(logits, settings):
+        r = plain.XorShift64(s["seed"]).unit()
+        expected.append(plain.sample(row, s["temp"], s["top_k"], s["top_p"], s["min_p"], r, masked=s.get("masked", -1)))
+    got, _ = _sample_rows(logits.copy(), settings)
+    assert got == expected
+
+
 def test_sampling_distribution_and_independence_of_the_batch():
     """Draws follow the softmax, and a request's draws do not depend on what shares its batch."""
     from llmx_b200.sampling import RequestSampling, SamplingParams, sample
