@@ -168,7 +168,7 @@ def cmd_generate(argv: List[str]) -> int:
         ignore_eos="--ignore-eos" in given)
     dtype = _dtype(given.get("--dtype", "auto"))
     kv_dtype = _cache_type(given)
-    ubatch = _int("--ubatch", given.get("--ubatch", "512"), 1)
+    ubatch = _int("--ubatch", given.get("--ubatch", "2048"), 1)
     kv_tokens = _int("--kv-tokens", given["--kv-tokens"], 1) if "--kv-tokens" in given else None
     if kv_tokens is None:
         kv_tokens = -(-(len(prompt) + params.max_tokens) // 64) * 64
@@ -245,7 +245,7 @@ def cmd_logits(argv: List[str]) -> int:
         ids = _ids(pos[1])
     top = _int("--top", given.get("--top", "5"), 1)
     last = min(_int("--last", given.get("--last", "1"), 1), len(ids))
-    ubatch = 1 if "--per-token" in given else _int("--ubatch", given.get("--ubatch", "512"), 1)
+    ubatch = 1 if "--per-token" in given else _int("--ubatch", given.get("--ubatch", "2048"), 1)
     engine = Engine.from_dir(pos[0], EngineOptions(dtype=_dtype(given.get("--dtype", "auto")),
                                                    kv_tokens=-(-len(ids) // 64) * 64, max_requests=1,
                                                    device=given.get("--device", "cuda:0"), kv_dtype=_cache_type(given)))
@@ -367,7 +367,7 @@ def cmd_bench(argv: List[str]) -> int:
     reps = _int("--r", given.get("--r", "3"), 1)
     seqs = _int("--seqs", given.get("--seqs", "1"), 1)
     depth = _int("--depth", given.get("--depth", "0"), 0)
-    ubatch = _int("--ubatch", given.get("--ubatch", "512"), 1)
+    ubatch = _int("--ubatch", given.get("--ubatch", "2048"), 1)
     dtype = _dtype(given.get("--dtype", "auto"))
     reach = max(p + g, depth + p) if seqs > 1 else depth + max(p, g)
     kv = (-(-(reach + 2) // 64) * 64 + 64) * seqs

@@ -511,7 +511,7 @@ llmx_engine::llmx_engine(llmx_model* m, const llmx_engine_desc& d, std::unique_p
     cache.reset(new Cache(d, books_only));
     sched.cache = cache.get();
     sched.max_positions = max_positions;
-    sched.max_batch_tokens = d.max_batch_tokens > 0 ? d.max_batch_tokens : 512;
+    sched.max_batch_tokens = d.max_batch_tokens > 0 ? d.max_batch_tokens : 2048;
     sched.max_requests = d.max_requests;
     sched.max_queue = d.max_queue;
     sched.reserve_prompt_only = d.reserve_prompt_only != 0;

@@ -156,7 +156,7 @@ struct Planned {
 };
 struct Scheduler {
     Cache* cache = nullptr;
-    long long max_positions = 0, max_batch_tokens = 512;
+    long long max_positions = 0, max_batch_tokens = 2048;
     int max_requests = 16, max_queue = 0;
     bool reserve_prompt_only = false;
     std::vector<int> eos_ids;

@@ -54,7 +54,7 @@ typedef struct llmx_engine_desc {
     const int* eos_ids;
     int n_eos;
     // the scheduler
-    int max_batch_tokens;           // the most tokens one step holds (0: 512)
+    int max_batch_tokens;           // the most tokens one step holds (0: 2,048)
     int max_queue;                  // waiting requests at most (0: no limit)
     int reserve_prompt_only;        // 0: a request reserves prompt + max_tokens; 1: its prompt and a page of growth
     int device;

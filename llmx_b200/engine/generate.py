@@ -44,7 +44,8 @@ class LLM:
     model:            a folder with config.json and safetensors files (or an `Engine`)
     dtype:            "bfloat16" (the serving path) or "float32" (everything in true 32-bit)
     kv_tokens:        tokens the cache pool is made for (default: the model's context, at most 1/3 of free memory)
-    ubatch:           the most tokens one step holds (the reference's --ubatch)
+    ubatch:           the most tokens one step holds (the reference's --ubatch; its default there is 512, here 2,048: a
+                      prompt of 8,192 tokens goes through in 119 ms in portions of 2,048 and in 156 ms in portions of 512)
     max_seqs:         the most requests that run at once
     reserve:          "full" or "prompt" (see llmx_b200.engine.scheduler)
     yarn, yarn_original_ctx:  the rope scaled by YaRN at this factor over this trained length (the reference's
@@ -56,7 +57,7 @@ class LLM:
     """
 
     def __init__(self, model: Union[str, Engine], *, dtype: str = "bfloat16", kv_tokens: Optional[int] = None,
-                 page_size: int = 16, ubatch: int = 512, max_seqs: int = 16, reserve: str = "full",
+                 page_size: int = 16, ubatch: int = 2048, max_seqs: int = 16, reserve: str = "full",
                  device: str = "cuda:0", yarn: Optional[float] = None, yarn_original_ctx: Optional[int] = None,
                  kv_dtype: Optional[str] = None, invariant: bool = False):
         if isinstance(model, Engine):

@@ -153,7 +153,7 @@ class NativeEngine:
     # -- construction -------------------------------------------------------------------------------------------
     @classmethod
     def over(cls, engine, *, kv_tokens: Optional[int] = None, page_size: Optional[int] = None, max_requests: Optional[int] = None,
-             ubatch: int = 512, reserve: str = "full", kv_dtype: Optional[str] = None) -> "NativeEngine":
+             ubatch: int = 2048, reserve: str = "full", kv_dtype: Optional[str] = None) -> "NativeEngine":
         """A native engine over the model a Python `Engine` has loaded (the weights are shared; the cache is its own)."""
         from .cache.manager import KVSpec, StateSpec
         model, opt = engine.model, engine.options
@@ -211,7 +211,7 @@ class NativeEngine:
 
     @classmethod
     def load(cls, model_dir: str, *, dtype: str = "bfloat16", kv_dtype: Optional[str] = None, page_size: int = 16,
-             kv_tokens: int = 8192, window_kv_tokens: Optional[int] = None, max_requests: int = 16, ubatch: int = 512,
+             kv_tokens: int = 8192, window_kv_tokens: Optional[int] = None, max_requests: int = 16, ubatch: int = 2048,
              reserve: str = "full", invariant: bool = False, device: int = 0) -> "NativeEngine":
         """config.json and the safetensors files of `model_dir`, read by the native loader."""
         opts = cls._options(dtype, kv_dtype, page_size, kv_tokens, window_kv_tokens, max_requests, ubatch, reserve, invariant, device)
