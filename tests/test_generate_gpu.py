@@ -196,7 +196,9 @@ def test_command_line(model_dirs, tmp_path):
     native = subprocess.run(exe + ["generate", d16, "5,17,3,99", "-n", "6", "--temp", "0", "--ignore-eos", "--engine", "native", "--verbose"],
                             capture_output=True, text=True, timeout=600)
     assert native.returncode == 0, native.stderr[-2000:]
-    assert ids in native.stdout and "pp: 4 tok" in native.stdout and "tg: 6 tok" in native.stdout and "finish length" in native.stdout
+    assert "pp: 4 tok" in native.stdout and "tg: 6 tok" in native.stdout and "finish length" in native.stdout
+    native_ids = next(l for l in native.stdout.splitlines() if l.startswith("ids: "))
+    _check_greedy(d16, [5, 17, 3, 99], [int(t) for t in native_ids[5:].split(",")], True)
     for bad in (["generate", d16, "1,2", "--temp", "-1"], ["generate", d16, "1,2", "--engine", "rust"], ["generate", d16, "1,2", "-n", "3", "-n", "4"],
                 ["generate", d16], ["generate", d16, "1,2", "--bogus"], ["generate", d16, "1,2", "--topp", "1.5"],
                 ["frobnicate"]):

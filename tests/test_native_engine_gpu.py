@@ -43,9 +43,10 @@ def _requests(name):
     return {f"r{i}": helpers.random_ids(vocab, n, seed=100 * i + n) for i, n in enumerate(LENGTHS)}
 
 
-def _python_engine(folder, dtype, page, kv_tokens, max_requests=4):
+def _python_engine(folder, dtype, page, kv_tokens, max_requests=4, invariant=False):
     from llmx_b200.engine import Engine, EngineOptions
-    return Engine.from_dir(folder, EngineOptions(dtype=dtype, kv_tokens=kv_tokens, page_size=page, max_requests=max_requests))
+    return Engine.from_dir(folder, EngineOptions(dtype=dtype, kv_tokens=kv_tokens, page_size=page, max_requests=max_requests,
+                                                 invariant=invariant))
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -117,7 +118,9 @@ def test_native_engine_generates_what_the_python_engine_generates(model_dirs, dt
               SamplingParams(max_tokens=14, temp=1.0, top_k=0, top_p=1.0, min_p=0.05, seed=11, ignore_eos=True),
               SamplingParams(max_tokens=6, temp=0.7, penalty=1.3, presence_penalty=0.5, frequency_penalty=0.2, seed=3, ignore_eos=True),
               SamplingParams(max_tokens=10, temp=0.0, top_k=0, top_p=1.0, ignore_eos=True)]
-    engine = _python_engine(folder, dtype, page, 1024, max_requests=3)
+    # (bfloat16 with the schedules that follow sizes alone: sums added in pieces move in their last bits from run to run,
+    # and a reply may part from a near tie on; those schedules give a row the same bits every time)
+    engine = _python_engine(folder, dtype, page, 1024, max_requests=3, invariant=dtype == "bfloat16")
     llm = LLM(engine, ubatch=32, max_seqs=3)
     want = [(o.tokens, o.finish_reason) for o in llm.generate(prompts, params)]
     native = NativeEngine.over(engine, ubatch=32, max_requests=3)
