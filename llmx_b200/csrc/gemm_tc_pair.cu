@@ -16,7 +16,8 @@
 //                          arrival on the first block's accumulator-empty barrier
 //
 // Work: the pair walks tiles pair, pair + pairs, ... (token tiles vary fastest), optionally with K cut into `splits`
-// ranges that are added with atomics.  Every wait is bounded (tc_common.cuh); the pair meets at a cluster barrier
+// ranges that are added with atomics, or (`splits` 0) with only the last, partial round's tiles cut.  Every wait
+// is bounded (tc_common.cuh); the pair meets at a cluster barrier
 // after its barriers are initialised (before any block signals the other) and before either block exits (a block's
 // shared memory and barriers are read and signalled by its partner until then).
 //
@@ -118,26 +119,44 @@ struct Work {
 // passes over them -- with all token tiles in one group, 4,096 tokens x 12,288 columns are 100 MB that each wave of
 // pairs streams again (measured: 540 us against 300).
 struct PairScheduler {
-    int w_tiles, m_tiles, k_blocks, splits, group;
-    long long cur, end, step;
-    __device__ PairScheduler(int w_tiles_, int m_tiles_, int k_blocks_, int splits_, int group_)
-        : w_tiles(w_tiles_), m_tiles(m_tiles_), k_blocks(k_blocks_), splits(splits_), group(group_) {
+    int w_tiles, m_tiles, k_blocks, splits, group, tail;
+    long long cur, end, step, whole;
+    // `tail` > 0 (with `splits` 1): whole tiles for as many full rounds of the pairs as there are, then the remaining
+    // tiles with K cut into `tail` ranges, range by range -- the pieces that run at one time are equally long and
+    // neighbours read the same k blocks, so what they share still meets in the L2 cache (runs of arbitrary k blocks
+    // a pair were tried: they lose that and were slower than the half-empty last round they avoid).
+    __device__ PairScheduler(int w_tiles_, int m_tiles_, int k_blocks_, int splits_, int group_, int tail_)
+        : w_tiles(w_tiles_), m_tiles(m_tiles_), k_blocks(k_blocks_), splits(splits_), group(group_), tail(tail_) {
         cur = blockIdx.x >> 1;
         step = gridDim.x >> 1;
-        end = (long long)w_tiles * m_tiles * splits;
+        const long long tiles = (long long)w_tiles * m_tiles;
+        whole = tail > 0 ? tiles / step * step : tiles * splits;
+        end = tail > 0 ? whole + (tiles - whole) * tail : whole;
     }
-    __device__ bool next(Work& w) {
-        if (cur >= end) return false;
-        const long long per_split = (long long)w_tiles * m_tiles;
-        const int sp = (int)(cur / per_split);
-        long long rest = cur % per_split;
+    __device__ void tile_at(long long rest, Work& w) const {
         const long long per_group = (long long)w_tiles * group;
         const int g = (int)(rest / per_group);                     // the last group may hold fewer token tiles
         const int in_group = min(group, m_tiles - g * group);
         rest -= (long long)g * per_group;
         w.wt = (int)(rest / in_group);
         w.mt = g * group + (int)(rest % in_group);
-        const int per = (k_blocks + splits - 1) / splits;
+    }
+    __device__ bool next(Work& w) {
+        if (cur >= end) return false;
+        const long long per_split = (long long)w_tiles * m_tiles;
+        int sp, ranges;
+        if (tail > 0 && cur < whole) {
+            sp = 0, ranges = 1;
+            tile_at(cur, w);
+        } else if (tail > 0) {
+            const long long left = per_split - whole, at = cur - whole;
+            sp = (int)(at / left), ranges = tail;
+            tile_at(whole + at % left, w);
+        } else {
+            sp = (int)(cur / per_split), ranges = splits;
+            tile_at(cur % per_split, w);
+        }
+        const int per = (k_blocks + ranges - 1) / ranges;
         w.kb0 = sp * per;
         w.kb1 = min(k_blocks, w.kb0 + per);
         cur += step;
@@ -152,7 +171,7 @@ template <int BN, int FORM>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_wide, const __grid_constant__ CUtensorMap map_narrow,
                     void* __restrict__ C_, int wide_rows, int narrow_rows, int K, int mode, int splits, int group,
-                    int* error_word, const HeadsEpilogue hp) {
+                    int tail, int* error_word, const HeadsEpilogue hp) {
     using cfg = PairCfg<BN, FORM>;
     pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
@@ -204,7 +223,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_wide, const __grid_c
 
     if (warp == 0) {
         if (tc::elect_one()) {
-            PairScheduler sched(w_tiles, m_tiles, k_blocks, splits, group);
+            PairScheduler sched(w_tiles, m_tiles, k_blocks, splits, group, tail);
             Work w;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
@@ -228,7 +247,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_wide, const __grid_c
     } else if (warp == 1) {
         if (leader && tc::elect_one()) {
             constexpr uint32_t idesc = tc::instr_desc_bf16(2 * BM, BN);
-            PairScheduler sched(w_tiles, m_tiles, k_blocks, splits, group);
+            PairScheduler sched(w_tiles, m_tiles, k_blocks, splits, group, tail);
             Work w;
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
@@ -263,7 +282,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_wide, const __grid_c
         }
     } else {
         const int quarter = warp & 3;
-        PairScheduler sched(w_tiles, m_tiles, k_blocks, splits, group);
+        PairScheduler sched(w_tiles, m_tiles, k_blocks, splits, group, tail);
         Work w;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
@@ -353,12 +372,30 @@ int launch_pair(const CUtensorMap& wide, const CUtensorMap& narrow, void* C, int
     }
     const int w_tiles = (wide_rows + 2 * BM - 1) / (2 * BM), m_tiles = (narrow_rows + BN - 1) / BN;
     // Narrow tiles a group: what 24 MB hold of the narrow operand's rows of one k range (at least one, at most all).
-    const long long tile_bytes = (long long)BN * ((K + splits - 1) / splits) * 2;
+    const long long tile_bytes = (long long)BN * ((K + (splits ? splits : 1) - 1) / (splits ? splits : 1)) * 2;
     int group = (int)((24ll << 20) / (tile_bytes > 0 ? tile_bytes : 1));
     group = group < 1 ? 1 : group > m_tiles ? m_tiles : group;
-    long long pairs = (long long)w_tiles * m_tiles * splits;
+    const long long tiles = (long long)w_tiles * m_tiles;
+    long long pairs = tiles * (splits ? splits : 8);
     if (pairs > g_sm_count / 2) pairs = g_sm_count / 2;
     if (pairs < 1) pairs = 1;
+    // `splits` 0: whole tiles while they fill every pair, the rest in k ranges -- as many as make the rest's rounds
+    // shortest.  A piece's write-out runs beside the next piece's products and takes as long as 26 k blocks (the L2
+    // cache adds about 500 G floats a second for all pairs together), so shorter pieces gain nothing.
+    int tail = 0;
+    if (splits == 0) {
+        const long long left = tiles % pairs;
+        const int k_blocks = (K + BK - 1) / BK;
+        long long best = -1;
+        tail = 1;
+        for (int r = 1; left > 0 && r <= 8 && r <= k_blocks; ++r) {
+            const int per = (k_blocks + r - 1) / r;
+            if ((long long)(r - 1) * per >= k_blocks) continue;                 // an empty last range
+            const long long cost = (left * r + pairs - 1) / pairs * (r > 1 && per < 26 ? 26 : per);
+            if (best < 0 || cost < best) best = cost, tail = r;
+        }
+        splits = 1;
+    }
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3((unsigned)(2 * pairs));
     lc.blockDim = dim3(THREADS);
@@ -374,7 +411,7 @@ int launch_pair(const CUtensorMap& wide, const CUtensorMap& narrow, void* C, int
     lc.attrs = attr;
     lc.numAttrs = llmx_pdl_enabled() ? 2 : 1;
     cudaLaunchKernelEx(&lc, gemm_tc_pair_kernel<BN, FORM>, wide, narrow, C, wide_rows, narrow_rows, K, mode, splits, group,
-                       error_word, hp);
+                       tail, error_word, hp);
     return launch_status();
 }
 
@@ -382,12 +419,13 @@ int launch_pair(const CUtensorMap& wide, const CUtensorMap& narrow, void* C, int
 
 // C (+)= A W^T on pairs of SMs.  `weight_map`: the weight's tensor map with boxes of 128 rows x 64 columns (the one
 // llmx_gemm_tc_weight_map makes); A [M, K] bfloat16; C float32 [M, N]; mode 0 stores, 1 adds (float atomics);
-// `splits` > 1 (mode 1 only) cuts K into ranges; `token_tile` 128 or 256.
+// `splits` > 1 (mode 1 only) cuts K into ranges; `splits` 0 (mode 1 only) runs whole tiles while they fill every pair
+// and cuts only the remaining tiles' K, so that the last round is not half empty; `token_tile` 128 or 256.
 LLMX_EXPORT int llmx_gemm_tc_pair(const void* weight_map, const void* A, float* C, int M, int N, int K, int mode, int splits,
                                   int token_tile, int* error_word, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || ((uintptr_t)A & 15) || ((uintptr_t)C & 3)) return LLMX_ERR_UNSUPPORTED;
-    if ((mode != MODE_STORE && mode != MODE_ACCUMULATE) || splits < 1 || (splits > 1 && mode != MODE_ACCUMULATE))
+    if ((mode != MODE_STORE && mode != MODE_ACCUMULATE) || splits < 0 || (splits != 1 && mode != MODE_ACCUMULATE))
         return LLMX_ERR_BAD_ARGUMENT;
     if (token_tile != 128 && token_tile != 256) return LLMX_ERR_BAD_ARGUMENT;
     ensure_sm_count();

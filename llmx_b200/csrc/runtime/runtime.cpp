@@ -192,7 +192,7 @@ constexpr int HEADS_MIN_ROWS = 256;           // from this many tokens on the q/
 
 int gemm_schedule(int m, int n) { return m <= STREAM_K_MAX_ROWS && cdiv(n, 128) < STREAM_K_MAX_TILES ? 1 : 0; }
 
-struct GemmPlan { int schedule, token_tile, splits; };   // schedule 0: whole tiles, 1: stream-K, 2: whole tiles on pairs of SMs
+struct GemmPlan { int schedule, token_tile, splits; };   // schedule 0: whole tiles, 1: stream-K, 2: on pairs of SMs (splits 0: only the last, partial round's tiles are cut)
 // Which products of many tokens may run on pairs of SMs: a sum of PAIR_PLAIN, PAIR_GATED and PAIR_HEADS.
 enum : int { PAIR_PLAIN = 1, PAIR_GATED = 2, PAIR_HEADS = 4, PAIR_ALL = 7 };
 int g_pair_products = PAIR_ALL;
@@ -232,6 +232,31 @@ GemmPlan gemm_plan_compute(int m, int n, int k, bool accumulate, int n_sms, bool
                 }
                 t *= 1.0 + 0.03 * (splits - 1);
                 if (best_t < 0 || t < best_t) best_t = t, best = {pair ? 2 : 0, bn, splits};
+            }
+            if (pair) {
+                // `splits` 0: whole tiles while they fill every pair, then the remaining tiles' K in `r` ranges (the
+                // kernel's launcher chooses r the same way), so that the last round is not half empty.
+                const long long tiles = (long long)n_tiles * m_tiles;
+                const long long at_once = std::min<long long>(units, tiles * 8), left = tiles % at_once;
+                long long best_cost = -1;
+                int r_best = 1;
+                for (int r = 1; left > 0 && r <= 8 && r <= k_blocks; ++r) {
+                    const int per = cdiv(k_blocks, r);
+                    if ((long long)(r - 1) * per >= k_blocks) continue;
+                    const long long cost = (left * r + at_once - 1) / at_once * (r > 1 && per < 26 ? 26 : per);
+                    if (best_cost < 0 || cost < best_cost) best_cost = cost, r_best = r;
+                }
+                if (r_best > 1) {
+                    auto tile_time = [&](double kk) {
+                        return std::max(kk * (128 + bn / 2) * 2 / 110e3, 2.0 * 128 * bn * kk / 10.3e6);
+                    };
+                    const long long rounds = (left * r_best + at_once - 1) / at_once;
+                    double t = (double)(tiles / at_once) * tile_time(k_blocks * 64.0) + rounds * tile_time(std::max(cdiv(k_blocks, r_best), 26) * 64.0);
+                    t += std::min(bn, m) * 128 / 8e3;
+                    if (!accumulate) t += (double)m * n * 4 / 5e6;
+                    t *= 1.03;
+                    if (t < best_t) best_t = t, best = {2, bn, 0};
+                }
             }
         }
     }
@@ -460,7 +485,7 @@ struct Linear : llmx_part {
     bool adds_pieces(int rows) const {
         if (!tensor_core || invariant()) return false;
         const GemmPlan p = gemm_plan(rows, N, K, false);
-        return p.schedule == 1 || p.splits > 1;
+        return p.schedule == 1 || p.splits != 1;
     }
     long long output_to_clear(int rows) const {
         if (!adds_pieces(rows) || ((long long)rows * N) % 4) return 0;
@@ -488,7 +513,7 @@ struct Linear : llmx_part {
             return CALL(c, llmx_gemm_tc, 1, (const void*)map128, a, out, rows, N, K, accumulate ? 1 : 0, 1, 128, 0, c.s->error_word, c.stream);
         bool acc = accumulate || (cleared && adds_pieces(rows));
         const GemmPlan p = gemm_plan(rows, N, K, acc);
-        if ((p.schedule == 1 || p.splits > 1) && !acc) {
+        if ((p.schedule == 1 || p.splits != 1) && !acc) {
             if (!c.dry && !c.status && cudaMemsetAsync(out, 0, (size_t)rows * N * sizeof(float), c.stream) != cudaSuccess)
                 return c.status = fail(LLMX_RT_ERR_BAD_ARGUMENT, "clearing a product's output failed");
             acc = true;

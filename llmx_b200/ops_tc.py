@@ -87,7 +87,7 @@ def plan(m: int, n: int, k: int, accumulate: bool) -> Tuple[int, int, int]:
 def adds_pieces(m: int, n: int, k: int) -> bool:
     """Whether a stored product of this shape adds its pieces into the output, which then must start as zeros."""
     schedule, _, splits = plan(m, n, k, False)
-    return schedule == 1 or splits > 1
+    return schedule == 1 or splits != 1
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
@@ -97,7 +97,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
 
     schedule 0 walks whole tiles (`splits` > 1 cuts K and adds the pieces with atomics); schedule 1
     (stream-K) shares out (tile, k block) units evenly and adds every piece with atomics; schedule 2 walks whole
-    tiles of 256 weight rows on pairs of SMs (`gemm_tc_pair`).  Whenever pieces
+    tiles of 256 weight rows on pairs of SMs (`gemm_tc_pair`; `splits` 0: the tiles of the last, partial round are cut there).  Whenever pieces
     are added, `out` is zeroed first unless accumulating.  By default `plan` chooses: stream-K for few
     tokens, else the kernel, token tile and k ranges that fill the SMs.
     """
@@ -210,7 +210,7 @@ def gemm_tc_pair(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate
           "gemm_tc_pair: bfloat16 inputs and a float32 output")
     _need(w.shape[1] == k and tuple(out.shape) == (m, n) and k % 8 == 0, "gemm_tc_pair: shapes do not fit")
     wmap = wmap or weight_map(w)
-    if splits > 1 and not accumulate:
+    if splits != 1 and not accumulate:      # pieces of a tile meet by addition (splits 0: the last round's tiles are cut)
         out.zero_()
         accumulate = True
     _check(_fn("gemm_tc_pair", "llmx_gemm_tc_pair")(ctypes.c_void_p(wmap.address), _ptr(a), _ptr(out), m, n, k,

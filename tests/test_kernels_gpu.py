@@ -189,10 +189,34 @@ def test_gemm_tensor_core_on_pairs_of_sms(m, n, k):
         ops_tc.check_errors()
         assert (out.cpu().double() - ref).abs().max() <= 2e-5 * max(1.0, ref.abs().max())
         assert torch.all(guard[0] == 7.0) and torch.all(guard[m + 1] == 7.0)
-        for splits in (1, 2, 3):
+        for splits in (1, 2, 3, 0):
             acc = base.clone()
             ops_tc.gemm_tc_pair(a, w, acc, accumulate=True, splits=splits, token_tile=tile)
             assert (acc.cpu().double() - (ref + base.cpu().double())).abs().max() <= 3e-5 * max(1.0, ref.abs().max())
+    ops_tc.check_errors()
+
+
+@pytest.mark.parametrize("m,n,k", [(2300, 2100, 1104), (1100, 4100, 3000), (520, 1000, 64), (4100, 2300, 8200)])
+def test_gemm_on_pairs_cuts_only_the_last_round(m, n, k):
+    """`splits` 0: whole tiles for the full rounds of the 74 pairs, the remaining tiles' K in ranges.  Sizes with one
+    or two full rounds and a ragged rest, fewer tiles than pairs, a single k block, and a K long enough that the
+    rest is cut into many ranges; added to what the output holds, and stored."""
+    from llmx_b200 import ops_tc
+    g = torch.Generator().manual_seed(18)
+    a = _bf16(torch.randn(m, k, generator=g)).to(DEV)
+    w = _bf16(torch.randn(n, k, generator=g) * 0.1).to(DEV)
+    ref = a.float().double() @ w.float().double().T
+    base = torch.randn(m, n, generator=g).to(DEV)
+    bound = 3e-5 * max(1.0, ref.abs().max().item())
+    for tile in (128, 256):
+        acc = base.clone()
+        ops_tc.gemm_tc_pair(a, w, acc, accumulate=True, splits=0, token_tile=tile)
+        assert (acc.double() - (ref + base.double())).abs().max() <= bound
+        guard = torch.full((m + 2, n), 7.0, device=DEV)
+        out = guard[1:m + 1]
+        ops_tc.gemm_tc_pair(a, w, out, splits=0, token_tile=tile)
+        assert (out.double() - ref).abs().max() <= bound
+        assert torch.all(guard[0] == 7.0) and torch.all(guard[m + 1] == 7.0)
     ops_tc.check_errors()
 
 
