@@ -138,7 +138,7 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true")
-    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "sample"], default=None,
                     help="run one part only (for profiling); the line then holds only that part")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -361,6 +361,36 @@ def main() -> int:
         rates = [batch * 1e3 / ms for ms in ms_list]
         return sum(rates) / len(rates), (statistics.stdev(rates) if len(rates) > 1 else 0.0)
 
+    if args.only == "sample":
+        # The sampling kernel alone over --batch rows of the size's vocabulary, settings in turn: device time of a draw
+        # (settings uploaded, kernel, ids left on the device), draws back to back.
+        from llmx_b200.sampling.sampler import sample_async
+        raw = dict(QWEN3_8B)
+        raw.update(SIZES[args.size])
+        vocab = raw["vocab_size"]
+        dev_gen = torch.Generator(device="cuda")
+        dev_gen.manual_seed(3)
+        logits = torch.randn(args.batch, vocab, device="cuda", generator=dev_gen) * 3.0
+        settings = {"greedy": SamplingParams(temp=0.0, top_k=0, top_p=1.0),
+                    "top_k40_top_p0.95": SamplingParams(temp=0.8, top_k=40, top_p=0.95),
+                    "top_k1000": SamplingParams(temp=1.0, top_k=1000, top_p=1.0),
+                    "top_p0.95": SamplingParams(temp=1.0, top_k=0, top_p=0.95),
+                    "temperature": SamplingParams(temp=1.0, top_k=0, top_p=1.0)}
+        line = {"only": "sample", "rows": args.batch, "vocab": vocab, "unit": "us a draw"}
+        for name, params in settings.items():
+            states = [RequestSampling(params) for _ in range(args.batch)]
+            for _ in range(args.warmup):
+                sample_async(logits, states).result()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                sample_async(logits, states)
+            e1.record()
+            torch.cuda.synchronize()
+            line[name] = round(e0.elapsed_time(e1) * 1e3 / args.steps, 1)
+        print(json.dumps(line))
+        return 0
     if args.only == "prefill":
         b = Bench(args.size, args.layers, [], args.context, args.prefill_tokens, args.steps, args.warmup)
         pf_value, pf_ms, pf_sd, pf_frac = b.run_prefill(3, 3)

@@ -30,6 +30,7 @@ constexpr int THREADS = 1024;
 constexpr int KMAX = 1024;        // kept tokens that are gathered into shared memory
 constexpr int TIES = 32;          // tokens with exactly the same score that are picked among without a second pass
 constexpr int MAX_CLUSTER = 8;    // blocks that share a row
+constexpr int NO_ID = 0x7fffffff;
 
 struct RowParams {
     float temperature, top_p, min_p, r;
@@ -70,6 +71,9 @@ __device__ __forceinline__ void lead_add(const unsigned* p, unsigned v) {
 }
 __device__ __forceinline__ void lead_add(const double* p, double v) {
     asm volatile("red.relaxed.cluster.shared::cluster.add.f64 [%0], %1;" ::"r"(on_leader(p)), "d"(v) : "memory");
+}
+__device__ __forceinline__ void lead_min(const int* p, int v) {
+    asm volatile("red.relaxed.cluster.shared::cluster.min.s32 [%0], %1;" ::"r"(on_leader(p)), "r"(v) : "memory");
 }
 __device__ __forceinline__ int lead_take(const int* p) {       // the leader's counter before it is raised by one
     int old;
@@ -113,13 +117,14 @@ struct Shared {
     // each block's own
     unsigned int count[256];
     double weight[256];
+    int min_id[256];              // a selection's last round: the lowest id of each bin
     double scan[THREADS];
     float best_score[32];
     int best_id[32];
     // the leader's copy is where the blocks meet
     unsigned int gcount[256];
     double gweight[256];
-    double gsum;
+    int gmin_id[256];
     float part_score[MAX_CLUSTER];
     int part_id[MAX_CLUSTER];
     double part_total[MAX_CLUSTER];
@@ -151,16 +156,15 @@ __device__ __forceinline__ void leader_turn(const Row& c, Body&& body) {
 }
 
 // Calls f(id, score, in_range) for every id of the block's slice, four consecutive ids a thread and round with 16-byte
-// loads when the row allows, eight loads of a thread in flight before the first is used.  Every thread of the block
+// loads when the row allows, AHEAD loads of a thread in flight before the first is used.  Every thread of the block
 // makes the same number of calls (ids past the end come with in_range false), so f may use warp-wide operations.
-template <typename F>
+template <int AHEAD = 8, typename F>
 __device__ __forceinline__ void scan_slice(const Row& c, F&& f) {
     const float* __restrict__ row = c.row;
     if ((((uintptr_t)row) & 15) == 0) {
         const int first4 = c.lo >> 2, n4 = c.hi >> 2;              // whole groups of four within the slice
         const float4* row4 = reinterpret_cast<const float4*>(row);
         const int rounds = (n4 - first4 + THREADS - 1) / THREADS;
-        constexpr int AHEAD = 8;
         for (int r0 = 0; r0 < rounds; r0 += AHEAD) {
             float4 v[AHEAD];
 #pragma unroll
@@ -337,15 +341,18 @@ __device__ int nth_with_bits(const Row& c, uint32_t bits, int nth, const Sets& s
     return lead_load(&sh.i32[5]);
 }
 
-// Radix selection by count: the bits of the k-th best token (k >= 1) among the tokens that are not masked, and how many
-// tokens with exactly those bits are among the k best.  A round: every block counts its slice's tokens by the next
-// eight bits, adds its bins to the leader's, and the leader finds the bin that holds the k-th.
-__device__ void select_by_count(const Row& c, int k, const Sets& sets, uint32_t& out_bits, int& out_equal_taken) {
+// Radix selection by count: the bits of the k-th best token (k >= 1) among the tokens that are not masked, how many
+// tokens with exactly those bits are among the k best, and the lowest id with those bits (the last round notes each
+// bin's, so that the usual case -- one token of the tie is taken -- needs no pass of its own).  A round: every block
+// counts its slice's tokens by the next eight bits, adds its bins to the leader's, and the leader finds the bin that
+// holds the k-th.
+__device__ void select_by_count(const Row& c, int k, const Sets& sets, uint32_t& out_bits, int& out_equal_taken,
+                                int& out_first_id) {
     Shared& sh = *c.sh;
     uint32_t prefix = 0, mask = 0;
     int remaining = k;
     for (int shift = 24; shift >= 0; shift -= 8) {
-        for (int i = threadIdx.x; i < 256; i += THREADS) sh.count[i] = 0;
+        for (int i = threadIdx.x; i < 256; i += THREADS) { sh.count[i] = 0; sh.min_id[i] = NO_ID; }
         __syncthreads();
         // Most scores share their leading bits: a thread keeps the count of the bin it met last and adds it to the
         // block's bins only when the bin changes.
@@ -355,6 +362,7 @@ __device__ void select_by_count(const Row& c, int k, const Sets& sets, uint32_t&
             const uint32_t b = order_bits(s);
             if (!(ok && id != sets.skip && (b & mask) == prefix)) return;
             const int bin = (b >> shift) & 255u;
+            if (shift == 0) atomicMin(&sh.min_id[bin], id);
             if (bin != run_bin) {
                 if (run) atomicAdd(&sh.count[run_bin], run);
                 run_bin = bin;
@@ -364,7 +372,10 @@ __device__ void select_by_count(const Row& c, int k, const Sets& sets, uint32_t&
         });
         if (run) atomicAdd(&sh.count[run_bin], run);
         __syncthreads();
-        if (threadIdx.x < 256 && sh.count[threadIdx.x]) lead_add(&sh.gcount[threadIdx.x], sh.count[threadIdx.x]);
+        if (threadIdx.x < 256 && sh.count[threadIdx.x]) {
+            lead_add(&sh.gcount[threadIdx.x], sh.count[threadIdx.x]);
+            if (shift == 0) lead_min(&sh.gmin_id[threadIdx.x], sh.min_id[threadIdx.x]);
+        }
         leader_turn(c, [&] {
             if (threadIdx.x < 32) {
                 int above = 0;
@@ -374,10 +385,11 @@ __device__ void select_by_count(const Row& c, int k, const Sets& sets, uint32_t&
                 if (threadIdx.x == 0) {
                     sh.u32[0] = (uint32_t)bin;
                     sh.i32[0] = remaining - above;
+                    sh.i32[2] = sh.gmin_id[bin];
                 }
             }
             __syncthreads();
-            if (threadIdx.x < 256) sh.gcount[threadIdx.x] = 0;        // for the next round
+            if (threadIdx.x < 256) { sh.gcount[threadIdx.x] = 0; sh.gmin_id[threadIdx.x] = NO_ID; }      // for the next round
         });
         prefix |= lead_load(&sh.u32[0]) << shift;
         mask |= 255u << shift;
@@ -385,19 +397,23 @@ __device__ void select_by_count(const Row& c, int k, const Sets& sets, uint32_t&
     }
     out_bits = prefix;
     out_equal_taken = remaining;
+    const int first = lead_load(&sh.i32[2]);
+    out_first_id = first == NO_ID ? -1 : first;
 }
 
-// Radix selection by weight over the tokens of LEVEL, best first: the bits at which the running weight first reaches
-// `goal` (strict: first exceeds it), the weight of the tokens above those bits, and how many tokens have exactly those
-// bits.
+// Radix selection by weight over the tokens of LEVEL, best first.  The goal is `fraction` of the set's whole weight,
+// which the first round's bins give; found are the bits at which the running weight first reaches the goal (strict:
+// first exceeds it), the weight of the tokens above those bits, how many tokens have exactly those bits, and the
+// lowest id among them (each bin's is noted in the last round).
 template <int LEVEL>
-__device__ void select_by_weight(const Row& c, double goal, bool strict, const Sets& sets, float best_score, float temp,
-                                 uint32_t& out_bits, double& out_above, int& out_equal_count) {
+__device__ void select_by_weight(const Row& c, double fraction, bool strict, const Sets& sets, float best_score, float temp,
+                                 uint32_t& out_bits, double& out_goal, double& out_above, int& out_equal_count,
+                                 int& out_first_id) {
     Shared& sh = *c.sh;
     uint32_t prefix = 0, mask = 0;
-    double above = 0.0;
+    double above = 0.0, goal = 0.0;
     for (int shift = 24; shift >= 0; shift -= 8) {
-        for (int i = threadIdx.x; i < 256; i += THREADS) { sh.count[i] = 0; sh.weight[i] = 0.0; }
+        for (int i = threadIdx.x; i < 256; i += THREADS) { sh.count[i] = 0; sh.weight[i] = 0.0; sh.min_id[i] = NO_ID; }
         __syncthreads();
         // Additions of doubles to shared memory are slow when many threads meet in a bin, and the first rounds have a
         // handful of bins for all tokens: a thread keeps four bins' counts and sums to itself and adds a bin's to the
@@ -406,7 +422,7 @@ __device__ void select_by_weight(const Row& c, double goal, bool strict, const S
         unsigned held_count[4] = {0, 0, 0, 0};
         double held_weight[4] = {0.0, 0.0, 0.0, 0.0};
         int next_out = 0;
-        scan_slice(c, [&](int id, float s, bool ok) {
+        scan_slice<4>(c, [&](int id, float s, bool ok) {
             if (!ok) return;
             const uint32_t b = order_bits(s);
             if ((b & mask) != prefix) return;
@@ -414,6 +430,7 @@ __device__ void select_by_weight(const Row& c, double goal, bool strict, const S
             const bool in = LEVEL == 1 ? in_kept(sets, id, b) : in_nucleus(sets, id, b, w);
             if (!in) return;
             const int bin = (b >> shift) & 255u;
+            if (shift == 0) atomicMin(&sh.min_id[bin], id);
             bool found = false;
 #pragma unroll
             for (int e = 0; e < 4; ++e)
@@ -446,64 +463,64 @@ __device__ void select_by_weight(const Row& c, double goal, bool strict, const S
         if (threadIdx.x < 256 && sh.count[threadIdx.x]) {
             lead_add(&sh.gcount[threadIdx.x], sh.count[threadIdx.x]);
             lead_add(&sh.gweight[threadIdx.x], sh.weight[threadIdx.x]);
+            if (shift == 0) lead_min(&sh.gmin_id[threadIdx.x], sh.min_id[threadIdx.x]);
         }
         leader_turn(c, [&] {
-            if (threadIdx.x == 0) {
+            if (threadIdx.x < 32) {
+                const int lane = threadIdx.x;
+                auto amount = [&](int i) { return sh.gcount[i] ? sh.gweight[i] : 0.0; };
+                double all = 0.0;                    // this round's bins together
+#pragma unroll
+                for (int b = 0; b < 8; ++b) all += amount(lane * 8 + b);
+                for (int o = 16; o > 0; o >>= 1) all += __shfl_xor_sync(0xffffffffu, all, o);
+                double goal_now = goal;
+                if (shift == 24) {
+                    goal_now = fraction * all;
+                    if (lane == 0) sh.f64[2] = goal_now;
+                }
                 double acc = above;
-                int bin = 255, last_nonempty = -1;
-                for (; bin >= 0; --bin) {
-                    if (!sh.gcount[bin]) continue;
-                    last_nonempty = bin;
-                    const double next = acc + sh.gweight[bin];
-                    if (strict ? (goal < next) : (next >= goal)) break;
-                    acc = next;
+                int bin = find_bin<double>(amount, above,
+                                           [&](double before, double after) {
+                                               return after > before && (strict ? (goal_now < after) : (after >= goal_now));
+                                           }, acc);
+                if (bin < 0) {
+                    // Rounding left the goal just out of reach (or nothing weighs anything): stop at the last tokens,
+                    // the lowest bin that holds any.
+                    unsigned holds = 0;
+#pragma unroll
+                    for (int b = 0; b < 8; ++b)
+                        if (sh.gcount[lane * 8 + b]) holds |= 1u << b;
+                    const unsigned lanes = __ballot_sync(0xffffffffu, holds != 0);
+                    if (!lanes) {
+                        bin = 0;
+                        acc = above;
+                    } else {
+                        const int owner = __ffs(lanes) - 1;
+                        bin = owner * 8 + __ffs(__shfl_sync(0xffffffffu, holds, owner)) - 1;
+                        acc = above + all - amount(bin);
+                    }
                 }
-                if (bin < 0) {               // rounding left the goal just out of reach: stop at the last tokens
-                    bin = last_nonempty < 0 ? 0 : last_nonempty;
-                    acc -= sh.gweight[bin];
+                if (lane == 0) {
+                    sh.u32[0] = (uint32_t)bin;
+                    sh.f64[0] = acc;
+                    sh.i32[0] = (int)sh.gcount[bin];
+                    sh.i32[2] = sh.gmin_id[bin];
                 }
-                sh.u32[0] = (uint32_t)bin;
-                sh.f64[0] = acc;
-                sh.i32[0] = (int)sh.gcount[bin];
             }
             __syncthreads();
-            if (threadIdx.x < 256) { sh.gcount[threadIdx.x] = 0; sh.gweight[threadIdx.x] = 0.0; }
+            if (threadIdx.x < 256) { sh.gcount[threadIdx.x] = 0; sh.gweight[threadIdx.x] = 0.0; sh.gmin_id[threadIdx.x] = NO_ID; }
         });
         prefix |= lead_load(&sh.u32[0]) << shift;
         mask |= 255u << shift;
         above = lead_load(&sh.f64[0]);
+        if (shift == 24) goal = lead_load(&sh.f64[2]);
         out_equal_count = lead_load(&sh.i32[0]);
     }
     out_bits = prefix;
+    out_goal = goal;
     out_above = above;
-}
-
-// Sum of the weights of LEVEL's tokens, every thread of the cluster gets the total.
-template <int LEVEL>
-__device__ double total_weight(const Row& c, const Sets& sets, float best_score, float temp) {
-    Shared& sh = *c.sh;
-    double mine = 0.0;
-    scan_slice(c, [&](int id, float s, bool ok) {
-        if (!ok) return;
-        const uint32_t b = order_bits(s);
-        const float w = expf((s - best_score) / temp);
-        const bool in = LEVEL == 1 ? in_kept(sets, id, b) : in_nucleus(sets, id, b, w);
-        if (in) mine += (double)w;
-    });
-    sh.scan[threadIdx.x] = mine;
-    __syncthreads();
-    for (int o = THREADS / 2; o > 0; o >>= 1) {
-        if (threadIdx.x < o) sh.scan[threadIdx.x] += sh.scan[threadIdx.x + o];
-        __syncthreads();
-    }
-    if (threadIdx.x == 0) lead_add(&sh.gsum, sh.scan[0]);
-    leader_turn(c, [&] {
-        if (threadIdx.x == 0) {
-            sh.f64[1] = sh.gsum;
-            sh.gsum = 0.0;
-        }
-    });
-    return lead_load(&sh.f64[1]);
+    const int first = lead_load(&sh.i32[2]);
+    out_first_id = first == NO_ID ? -1 : first;
 }
 
 // The best token: largest score, ties to the lowest id; a NaN only as the first token taking part
@@ -565,8 +582,8 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
     const RowParams p = params[blockIdx.y];
     const int n = vocab;
     // What the blocks meet in starts empty (only the leader's copy is ever used).
-    for (int i = threadIdx.x; i < 256; i += THREADS) { sh.gcount[i] = 0; sh.gweight[i] = 0.0; }
-    if (threadIdx.x == 0) { sh.gsum = 0.0; sh.n_hits = 0; sh.n_kept = 0; sh.walked = -1; }
+    for (int i = threadIdx.x; i < 256; i += THREADS) { sh.gcount[i] = 0; sh.gweight[i] = 0.0; sh.gmin_id[i] = NO_ID; }
+    if (threadIdx.x == 0) { sh.n_hits = 0; sh.n_kept = 0; sh.walked = -1; }
     __syncthreads();
     cluster_sync();
 
@@ -592,9 +609,9 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
     // ---- top-k: the bits of the k-th best and the last id taken among its ties
     if (keep < m) {
         uint32_t bits;
-        int taken;
-        select_by_count(c, keep, sets, bits, taken);
-        const int last = nth_with_bits<0>(c, bits, taken - 1, sets, best_score, temp);
+        int taken, first;
+        select_by_count(c, keep, sets, bits, taken, first);
+        const int last = taken == 1 ? first : nth_with_bits<0>(c, bits, taken - 1, sets, best_score, temp);
         sets.has_topk = true;
         sets.topk_bits = bits;
         sets.topk_last_id = last < 0 ? n : last;
@@ -743,12 +760,10 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
         return;
     }
     // ---- rank order over the whole vocabulary: nucleus by weight, min-p on its tail, then the draw best first
-    const double kept_weight = total_weight<1>(c, sets, best_score, temp);
-    const double goal = (double)p.top_p * kept_weight;
     uint32_t bits;
-    double above;
-    int equal;
-    select_by_weight<1>(c, goal, false, sets, best_score, temp, bits, above, equal);
+    double goal, above;
+    int equal, first;
+    select_by_weight<1>(c, (double)p.top_p, false, sets, best_score, temp, bits, goal, above, equal, first);
     {
         // Tokens with the threshold's bits all weigh the same; take as many as reach the goal (at least one).
         const float s_t = __uint_as_float((bits & 0x80000000u) ? (bits & 0x7fffffffu) : ~bits);
@@ -757,15 +772,14 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
         if (w_t > 0.0 && above + w_t < goal) j = (long long)ceil((goal - above) / w_t);
         if (j < 1) j = 1;
         if (j > equal) j = equal;
-        const int last = nth_with_bits<1>(c, bits, (int)j - 1, sets, best_score, temp);
+        const int last = j == 1 ? first : nth_with_bits<1>(c, bits, (int)j - 1, sets, best_score, temp);
         sets.has_nucleus = true;
         sets.nuc_bits = bits;
         sets.nuc_last_id = last < 0 ? n : last;
     }
     if (p.min_p > 0.0f) { sets.has_minp = true; sets.min_p = p.min_p; }
-    const double nucleus_weight = total_weight<2>(c, sets, best_score, temp);
-    const double target = (double)p.r * nucleus_weight;
-    select_by_weight<2>(c, target, true, sets, best_score, temp, bits, above, equal);
+    double target;
+    select_by_weight<2>(c, (double)p.r, true, sets, best_score, temp, bits, target, above, equal, first);
     {
         const float s_t = __uint_as_float((bits & 0x80000000u) ? (bits & 0x7fffffffu) : ~bits);
         const double w_t = (double)expf((s_t - best_score) / temp);
@@ -773,7 +787,7 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
         if (w_t > 0.0 && target > above) i = (long long)floor((target - above) / w_t);
         if (i >= equal) i = equal - 1;
         if (i < 0) i = 0;
-        const int id = nth_with_bits<2>(c, bits, (int)i, sets, best_score, temp);
+        const int id = i == 0 ? first : nth_with_bits<2>(c, bits, (int)i, sets, best_score, temp);
         if (id >= 0) chosen = id;
     }
     if (c.rank == 0 && threadIdx.x == 0) out[blockIdx.y] = chosen;
