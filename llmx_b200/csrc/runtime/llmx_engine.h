@@ -18,6 +18,10 @@
 // Every function returns 0 (or a count, or an id) on success and a negative or LLMX_ENGINE_ERR_* code on failure;
 // `llmx_engine_last_error` gives the text for the calling thread.  A step that fails leaves every request as it was.
 // The engine runs on its own CUDA stream and synchronises where a result goes to the host.
+//
+// Threads: an engine is one caller's at a time -- its functions take no lock, so calls on the same engine from several
+// threads must be serialised by the caller (a server puts its step loop on one thread and hands requests to it).
+// Different engines may be used from different threads; the error text is kept per thread.
 #pragma once
 #include "llmx_runtime.h"
 
