@@ -10,7 +10,6 @@
 // src/model/arch/hf_config.hpp:317-336, src/model/weights.hpp:77-92).
 #include "engine_internal.h"
 
-#include <dirent.h>
 #include <fcntl.h>
 #include <math.h>
 #include <stdio.h>
@@ -491,19 +490,52 @@ struct TensorFiles {
         files.push_back(std::move(m));
     }
 
-    // Every *.safetensors file of a folder (one model.safetensors, or the shards an index names).
+    // The files of a model folder: those its model.safetensors.index.json names, each holding exactly the tensors the
+    // index maps to it, or its single model.safetensors (src/format/safetensors.hpp:133-171).
     void add_folder(const std::string& dir) {
-        DIR* d = opendir(dir.c_str());
-        if (!d) throw Failure{LLMX_ENGINE_ERR_FILE, dir + ": not a folder that can be read"};
-        std::vector<std::string> names;
-        while (dirent* ent = readdir(d)) {
-            const std::string n = ent->d_name;
-            if (n.size() > 12 && !n.compare(n.size() - 12, 12, ".safetensors")) names.push_back(n);
+        const std::string index = dir + "/model.safetensors.index.json";
+        struct stat st;
+        if (stat(index.c_str(), &st) != 0) {
+            const std::string single = dir + "/model.safetensors";
+            if (stat(single.c_str(), &st) != 0)
+                throw Failure{LLMX_ENGINE_ERR_FILE, dir + ": neither model.safetensors nor model.safetensors.index.json"};
+            add_file(single);
+            return;
         }
-        closedir(d);
-        std::sort(names.begin(), names.end());
-        if (names.empty()) throw Failure{LLMX_ENGINE_ERR_FILE, dir + ": no safetensors file"};
-        for (const std::string& n : names) add_file(dir + "/" + n);
+        auto bad = [&](const std::string& what) -> void { throw Failure{LLMX_ENGINE_ERR_FILE, index + ": " + what}; };
+        const std::string text = read_text(index, index + ": cannot be read");
+        Json root;
+        try {
+            root = JsonReader(text.data(), text.size()).parse();
+        } catch (const Failure& f) {
+            bad(f.what);
+        }
+        const Json* map = root.kind == Json::OBJ ? root.get("weight_map") : nullptr;
+        if (!map || map->kind != Json::OBJ) bad("weight_map must map tensor names to file names");
+        std::map<std::string, std::set<std::string>> named;       // file -> the tensors the index gives it
+        for (const auto& kv : map->obj) {
+            if (kv.second.kind != Json::STR) bad("weight_map must map tensor names to file names");
+            const std::string& file = kv.second.str;
+            if (file.empty() || file == "." || file == ".." || file.find_first_of("/\\:") != std::string::npos)
+                bad("'" + file + "' names a path outside the model folder");
+            named[file].insert(kv.first);
+        }
+        for (const auto& item : named) {
+            std::set<std::string> had;
+            for (const auto& t : tensors) had.insert(t.first);
+            add_file(dir + "/" + item.first);
+            std::vector<std::string> differ;
+            for (const auto& t : tensors)
+                if (!had.count(t.first) && !item.second.count(t.first)) differ.push_back(t.first);
+            for (const std::string& name : item.second)
+                if (!tensors.count(name) || had.count(name)) differ.push_back(name);
+            if (!differ.empty()) {
+                std::sort(differ.begin(), differ.end());
+                std::string list;
+                for (size_t i = 0; i < differ.size() && i < 8; ++i) list += (i ? ", " : "") + differ[i];
+                bad("weight_map and " + item.first + " disagree on " + list);
+            }
+        }
     }
 };
 

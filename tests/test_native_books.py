@@ -198,7 +198,7 @@ def test_native_loader_names_what_is_wrong_with_the_files(tmp_path):
     missing = dict(TINY_A)
     del missing["vocab_size"], missing["hidden_size"]
     assert "missing config.json key(s): hidden_size, vocab_size" in str(_load_error(_folder(tmp_path / "e", missing)))
-    assert "no safetensors file" in str(_load_error(_folder(tmp_path / "f", TINY_A)))
+    assert "neither model.safetensors nor model.safetensors.index.json" in str(_load_error(_folder(tmp_path / "f", TINY_A)))
 
     def raw(header, data=b""):
         text = json.dumps(header).encode() if not isinstance(header, bytes) else header
@@ -218,6 +218,37 @@ def test_native_loader_names_what_is_wrong_with_the_files(tmp_path):
             (raw({"a": {"dtype": "F32", "shape": [1], "data_offsets": [0, 4]}}, b"\0" * 9), "does not end at the end of the file")]):
         err = _load_error(_folder(tmp_path / f"s{k}", TINY_A, raw_file=blob))
         assert err.code == ERR_FILE and text in str(err), (text, str(err))
+
+
+def test_native_loader_follows_the_index_of_a_sharded_folder(tmp_path):
+    """model.safetensors.index.json: only the files it names are read, each must hold exactly the tensors the index
+    gives it, and none may lie outside the folder (src/format/safetensors.hpp:133-171).  The errors, without a GPU."""
+    import torch
+    from llmx_b200.weights import write_safetensors
+
+    def folder(k, weight_map, text=None):
+        d = tmp_path / f"i{k}"
+        os.makedirs(d)
+        (d / "config.json").write_text(json.dumps(TINY_A))
+        write_safetensors(str(d / "one.safetensors"), {"a": torch.ones(2)})
+        write_safetensors(str(d / "two.safetensors"), {"b": torch.zeros(3)})
+        (d / "model.safetensors.index.json").write_text(text if text is not None else json.dumps({"weight_map": weight_map}))
+        return str(d)
+
+    for k, (weight_map, text, message) in enumerate([
+            (None, "{not json", "not JSON"),
+            (None, json.dumps({"metadata": {}}), "weight_map must map tensor names to file names"),
+            ({"a": 3}, None, "weight_map must map tensor names to file names"),
+            ({"a": "../one.safetensors"}, None, "outside the model folder"),
+            ({"a": "sub/one.safetensors"}, None, "outside the model folder"),
+            ({"a": "one.safetensors", "b": "one.safetensors"}, None, "weight_map and one.safetensors disagree on b"),
+            ({"a": "one.safetensors", "b": "two.safetensors", "c": "two.safetensors"}, None, "weight_map and two.safetensors disagree on c"),
+            ({"a": "one.safetensors", "b": "three.safetensors"}, None, "three.safetensors: cannot be opened")]):
+        err = _load_error(folder(k, weight_map, text))
+        assert err.code == ERR_FILE and message in str(err), (message, str(err))
+    # A well-formed index: the files are read, and the model's comparison then names what the architecture misses.
+    err = _load_error(folder("ok", {"a": "one.safetensors", "b": "two.safetensors"}))
+    assert err.code == ERR_WEIGHTS and "unexpected (2)" in str(err)
 
 
 def test_native_loader_lists_missing_unexpected_and_wrong_tensors_in_one_error(tmp_path):

@@ -169,6 +169,40 @@ def test_native_loader_reads_a_model_folder(model_dirs, name, dtype):
     native.close()
 
 
+def test_native_loader_reads_a_sharded_folder(model_dirs, tmp_path):
+    """The same tensors in three files named by model.safetensors.index.json (and a stray file the index does not name,
+    which is not read): the same logits, bit for bit, as from the single file."""
+    import json
+    import os
+    import shutil
+    from llmx_b200.native_engine import NativeEngine
+    from llmx_b200.weights import TensorDirectory, write_safetensors
+    name = "B"
+    folder, page = model_dirs[name][1], model_dirs[name][2]
+    ids = helpers.random_ids(CONFIGS[name][0]["vocab_size"], 24, seed=6)
+    whole = NativeEngine.load(folder, dtype="float32", kv_tokens=128, page_size=page)
+    want = whole.forward([(1, ids, list(range(len(ids))))])
+    whole.close()
+    d = TensorDirectory(folder)
+    names = sorted(d.names())
+    shards = tmp_path / "shards"
+    os.makedirs(shards)
+    shutil.copy(os.path.join(folder, "config.json"), shards / "config.json")
+    weight_map = {}
+    for k in range(3):
+        part = {n: d.tensor(n).clone() for n in names[k::3]}
+        fname = f"model-0000{k + 1}-of-00003.safetensors"
+        write_safetensors(str(shards / fname), part)
+        weight_map.update({n: fname for n in part})
+    write_safetensors(str(shards / "consolidated.safetensors"), {n: d.tensor(n).clone() for n in names[:2]})
+    d.close()
+    (shards / "model.safetensors.index.json").write_text(json.dumps({"metadata": {"total_size": 0}, "weight_map": weight_map}))
+    sharded = NativeEngine.load(str(shards), dtype="float32", kv_tokens=128, page_size=page)
+    got = sharded.forward([(1, ids, list(range(len(ids))))])
+    sharded.close()
+    assert np.array_equal(got, want)
+
+
 def test_native_loader_converts_between_stored_and_path_types(model_dirs):
     """A bfloat16 folder run in float32 (widened exactly) and a float32 folder run in bfloat16 (rounded to nearest even):
     the same logits as the Python engine gives for the same folder and path."""
