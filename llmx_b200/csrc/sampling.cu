@@ -816,13 +816,27 @@ __global__ void penalty_kernel(float* __restrict__ logits, int vocab, const int*
     *v = s;
 }
 
-// A row's blocks: one for a small vocabulary, up to eight (a portable cluster) for a large one.
-int blocks_for(int vocab) { return vocab >= 65536 ? 8 : vocab >= 16384 ? 4 : vocab >= 8192 ? 2 : 1; }
+// A row's blocks: one for a small vocabulary, up to eight (a portable cluster) for a large one -- but no more than let
+// all rows run at the same time (one block of 1,024 threads an SM; 15 clusters of eight, 35 of four, 74 of two on 148
+// SMs): a second round of clusters costs more than the wider scan saves.  Measured at 151,936 scores, top-k 40 with
+// top-p / top-p alone, us a draw: 16 rows 79 / 171 with eight blocks, 72 / 124 with four; 64 rows 166 / 408 with
+// eight, 116 / 204 with two; 128 rows 280 / 726 with eight, 177 / 342 with one.
+int blocks_for(int vocab, int rows) {
+    int blocks = vocab >= 65536 ? 8 : vocab >= 16384 ? 4 : vocab >= 8192 ? 2 : 1;
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    while (blocks > 1 && (long long)rows * blocks > (blocks == 8 ? sms * 13 / 16 : blocks == 4 ? sms * 15 / 16 : sms)) blocks >>= 1;
+    return blocks;
+}
 
 template <typename K>
 int launch_rows(K kernel, int dynamic_bytes, int rows, int vocab, const float* logits, const RowParams* params, int* out,
                 cudaStream_t stream) {
-    const int blocks = blocks_for(vocab);
+    const int blocks = blocks_for(vocab, rows);
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3((unsigned)blocks, (unsigned)rows, 1);
     lc.blockDim = dim3(THREADS);

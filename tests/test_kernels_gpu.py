@@ -552,7 +552,7 @@ def test_sampling_against_the_plain_sampler(vocab):
 @pytest.mark.parametrize("vocab", [9001, 40000, 151936])
 @pytest.mark.parametrize("coarse", [False, True])
 def test_sampling_settings_at_random_against_the_plain_sampler(vocab, coarse):
-    """Vocabularies that two, four and eight blocks share; settings drawn at random (top-k beyond what is gathered into
+    """Vocabularies that two, four and eight blocks share (see the end); settings drawn at random (top-k beyond what is gathered into
     shared memory too); with `coarse`, scores on a grid of quarters, so that hundreds of tokens tie exactly at every
     threshold: ties go to the lowest ids, whichever block holds them."""
     rng = np.random.default_rng(vocab + int(coarse))
@@ -572,6 +572,10 @@ def test_sampling_settings_at_random_against_the_plain_sampler(vocab, coarse):
         expected.append(plain.sample(row, s["temp"], s["top_k"], s["top_p"], s["min_p"], r, masked=s.get("masked", -1)))
     got, _ = _sample_rows(logits.copy(), settings)
     assert got == expected
+    # The kernel gives a row fewer blocks when the rows are many (all rows run at one time): twelve rows a call still
+    # get the most blocks their vocabulary allows, twenty-four at the largest vocabulary get half as many.
+    halves = _sample_rows(logits[:12].copy(), settings[:12])[0] + _sample_rows(logits[12:].copy(), settings[12:])[0]
+    assert halves == expected
 
 
 def test_sampling_distribution_and_independence_of_the_batch():
