@@ -880,6 +880,9 @@ std::vector<int> llmx_engine::draw(const std::vector<Request*>& who) {
         memcpy(h_items + 2 * items, count.data(), items * sizeof(int));
     }
     bool all_greedy = true;
+    std::vector<unsigned long long> generators(rows);      // a draw that fails leaves the requests' generators as they were
+    for (int r = 0; r < rows; ++r) generators[r] = who[r]->sampling.rng.state;
+    try {
     for (int r = 0; r < rows; ++r) {
         const llmx_sampling& p = who[r]->params;
         h_pen[r] = p.penalty, h_pen[rows + r] = p.presence_penalty, h_pen[2 * rows + r] = p.frequency_penalty;
@@ -907,6 +910,10 @@ std::vector<int> llmx_engine::draw(const std::vector<Request*>& who) {
     }
     cuda_check(cudaMemcpyAsync(host_ids, d_out, (size_t)rows * sizeof(int), cudaMemcpyDeviceToHost, stream), "reading the drawn ids");
     sync_and_check();
+    } catch (...) {
+        for (int r = 0; r < rows; ++r) who[r]->sampling.rng.state = generators[r];
+        throw;
+    }
     return std::vector<int>(host_ids, host_ids + rows);
 }
 
@@ -1065,12 +1072,33 @@ LLMX_API int llmx_engine_step(llmx_engine* e, llmx_step_result* out, int capacit
         cuda_check(cudaSetDevice(e->device), "choosing the device");
         std::vector<llmx_step_result> results;
         if (e->begin_step(results)) {
+            // What the cache held before the step: a failure that shows only after the step's rows were committed (a
+            // kernel that gave up a wait, a draw that could not run) takes the rows back, so that every request is
+            // as it was and the same step can be planned again.
+            std::vector<std::pair<long long, int>> before;       // request, committed tokens (-1: not in the cache yet)
+            for (const Planned& p : e->planned) {
+                const auto it = e->cache->live.find(p.request->id);
+                before.emplace_back(p.request->id, it == e->cache->live.end() ? -1 : it->second.length);
+            }
+            bool ran = false;
             try {
                 const std::vector<Request*> wanting = e->run_planned();
+                ran = true;
                 const std::vector<int> drawn = e->draw(wanting);
                 if (wanting.empty()) e->sync_and_check();
                 for (const llmx_step_result& r : e->finish_step(drawn)) results.push_back(r);
             } catch (...) {
+                if (ran)
+                    for (const auto& b : before) {
+                        const auto it = e->cache->live.find(b.first);
+                        if (it == e->cache->live.end()) continue;
+                        try {
+                            if (b.second < 0) e->cache->free_request(b.first);
+                            else it->second.truncate(b.second);
+                        } catch (const Failure&) {
+                            // fixed-size state or a window that has moved on cannot be taken back: the step's failure is what is reported
+                        }
+                    }
                 e->planned.clear();
                 throw;
             }

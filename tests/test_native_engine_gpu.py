@@ -169,6 +169,92 @@ def test_native_loader_reads_a_model_folder(model_dirs, name, dtype):
     native.close()
 
 
+def test_a_failure_that_shows_after_the_step_ran_takes_the_step_back(model_dirs):
+    """A kernel that gives up a bounded wait is known only when the step's results are read, after the step's rows were
+    committed to the cache.  Here the failure is made on the host: a block written in the test (a callback in the native
+    model's walk) runs the model's own second layer and, when armed, writes an error code into the step's error word as
+    such a kernel would.  The failing step must leave pages, lengths and the requests' generators as they were: the
+    replies, drawn with temperature, equal those of an engine that never failed."""
+    import ctypes
+    import torch
+    from cuda.bindings import runtime as cudart
+    from llmx_b200 import runtime
+    from llmx_b200.engine import Engine, EngineOptions
+    from llmx_b200.native_engine import NativeEngine, NativeEngineError
+    from llmx_b200.sampling import SamplingParams
+    folder = model_dirs["D"][1]
+    vocab = CONFIGS["D"][0]["vocab_size"]
+    engine = Engine.from_dir(folder, EngineOptions(dtype="float32", kv_tokens=256, page_size=16, max_requests=4))
+    model = engine.model
+    assert model.native                                # the native model is made on first use
+    rt = runtime.lib()
+    armed, keep = [False], []
+    CALLBACK = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.POINTER(runtime.StepStruct), ctypes.c_int, ctypes.c_void_p,
+                                ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int)
+    code = np.array([77], dtype=np.int32)
+
+    def second_layer(user, step, kind, h, x, rows, cache_entry, write_cache):
+        mine = runtime.StepStruct.from_buffer_copy(step.contents)
+        need = rt.llmx_part_workspace(model.blocks[1].native, ctypes.byref(mine), rows, cache_entry)
+        ws = torch.empty(int(need), dtype=torch.uint8, device="cuda")
+        keep.append(ws)
+        mine.workspace, mine.workspace_bytes = ws.data_ptr(), int(need)
+        if armed[0]:
+            err, = cudart.cudaMemcpy(int(step.contents.error_word), code.ctypes.data, 4, cudart.cudaMemcpyKind.cudaMemcpyHostToDevice)
+            assert int(err) == 0
+        return rt.llmx_block_forward(model.blocks[1].native, ctypes.byref(mine), x, rows, cache_entry, write_cache)
+
+    fn = CALLBACK(second_layer)
+    detour = rt.llmx_callback_create(0, ctypes.cast(fn, ctypes.c_void_p), None, model.embedding.hidden)
+    n_blocks = len(model.blocks)
+    blocks = (ctypes.c_void_p * n_blocks)(*[detour if i == 1 else b.native for i, b in enumerate(model.blocks)])
+    order = (runtime.LayerStepStruct * n_blocks)(*[runtime.LayerStepStruct(i, i, 1) for i in range(n_blocks)])
+    twin = rt.llmx_model_create(model.embedding.native, blocks, n_blocks, order, n_blocks, model.head.native, model.embedding.hidden,
+                                model.vocab_size)
+    assert detour and twin
+    real, model._native.handle = model._native.handle, twin
+    prompts = [helpers.random_ids(vocab, 20, seed=31), helpers.random_ids(vocab, 9, seed=32)]
+    params = [SamplingParams(max_tokens=7, temp=0.9, top_k=20, top_p=0.9, seed=5, ignore_eos=True),
+              SamplingParams(max_tokens=5, temp=1.1, top_k=0, top_p=0.8, seed=6, ignore_eos=True)]
+
+    def run(fail_at):
+        native = NativeEngine.over(engine, kv_tokens=256, page_size=16, max_requests=4)
+        native.record_steps(False)                     # the callback copies from the host, which no recording may hold
+        ids = [native.add_request(p, sp) for p, sp in zip(prompts, params)]
+        failures, step = 0, 0
+        while not native.idle:
+            if step in fail_at:
+                held = [native.held_pages(i) for i in ids]
+                armed[0] = True
+                try:
+                    with pytest.raises(NativeEngineError) as e:
+                        native.step()
+                finally:
+                    armed[0] = False
+                assert e.value.code == 20005 and "code 77" in str(e.value)
+                native.check()
+                assert [native.held_pages(i) for i in ids] == held
+                fail_at = fail_at - {step}
+                failures += 1
+                continue
+            native.step()
+            step += 1
+        out = [native.output(i) for i in ids]
+        native.check()
+        native.close()
+        return out, failures
+
+    try:
+        want, none = run(set())
+        got, failures = run({0, 1, 3})                 # the prompts' step, the first decoding step, a later one
+    finally:
+        model._native.handle = real
+        rt.llmx_model_destroy(twin)
+        rt.llmx_part_destroy(detour)
+    assert none == 0 and failures == 3
+    assert got == want and [len(o[0]) for o in want] == [7, 5]
+
+
 def test_native_loader_reads_a_sharded_folder(model_dirs, tmp_path):
     """The same tensors in three files named by model.safetensors.index.json (and a stray file the index does not name,
     which is not read): the same logits, bit for bit, as from the single file."""
