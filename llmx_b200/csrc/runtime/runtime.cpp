@@ -207,7 +207,17 @@ constexpr int PAIR_MIN_ROWS = 256;            // gated and q/k/v products: from 
 // The same estimate serves the product on pairs of SMs (gemm_tc_pair.cu): a pair's tile is 256 weight rows, each block
 // of the pair takes in its 128 weight rows and half the token tile, and the multiply-adds ran a tenth faster there.
 GemmPlan gemm_plan_compute(int m, int n, int k, bool accumulate, int n_sms, bool pairs) {
-    if (gemm_schedule(m, n) == 1) return {1, 0, 1};
+    if (gemm_schedule(m, n) == 1) {
+        // 33 to 64 tokens: a piece's write-out is 128 x 64 atomics, and stream-K cuts the tiles into about tiles +
+        // blocks pieces.  Whole tiles with K in equal ranges make fewer pieces when they still fill the blocks that
+        // run at once (two an SM).
+        if (m > 32) {
+            const int tiles = cdiv(n, 128), slots = 2 * n_sms;
+            int splits = std::min(std::min(slots / std::max(tiles, 1), 8), cdiv(k, 64));
+            if (splits >= 2 && tiles * splits * 4 >= slots * 3) return {0, 64, splits};
+        }
+        return {1, 0, 1};
+    }
     if (m <= STREAM_K_MAX_ROWS) return {0, 0, 1};   // few tokens, plenty of weight tiles (the logits head): the narrowest token tile
     const int k_blocks = cdiv(k, 64);
     double best_t = -1;
