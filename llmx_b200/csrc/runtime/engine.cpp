@@ -883,33 +883,33 @@ std::vector<int> llmx_engine::draw(const std::vector<Request*>& who) {
     std::vector<unsigned long long> generators(rows);      // a draw that fails leaves the requests' generators as they were
     for (int r = 0; r < rows; ++r) generators[r] = who[r]->sampling.rng.state;
     try {
-    for (int r = 0; r < rows; ++r) {
-        const llmx_sampling& p = who[r]->params;
-        h_pen[r] = p.penalty, h_pen[rows + r] = p.presence_penalty, h_pen[2 * rows + r] = p.frequency_penalty;
-        const bool greedy = p.temp <= 0.0f;
-        all_greedy = all_greedy && greedy;
-        h_rows[r] = Row{p.temp, p.top_p, p.min_p, greedy ? 0.0f : who[r]->sampling.rng.unit(), p.top_k, who[r]->sampling.masked};
-    }
-    char* d = (char*)sample_buf.ptr;
-    cuda_check(cudaMemcpyAsync(d, h, (char*)(h_rows + rows) - h, cudaMemcpyHostToDevice, stream), "copying the sampling settings");
-    int* d_items = (int*)d;
-    float* d_pen = (float*)(d_items + 3 * items);
-    Row* d_rows = (Row*)(d_pen + 3 * rows);
-    int* d_out = (int*)(d_rows + rows);
-    if (items)
-        if (int err = penalize(cur_logits, vocab, d_items, d_items + items, d_items + 2 * items, d_pen, d_pen + rows,
-                               d_pen + 2 * rows, (int)items, stream))
-            throw Failure{LLMX_ENGINE_ERR_DEVICE, "penalize: error " + std::to_string(err)};
-    if (int err = sample(cur_logits, rows, vocab, d_rows, d_out, all_greedy ? 1 : 0, stream))
-        throw Failure{LLMX_ENGINE_ERR_DEVICE, "sample: error " + std::to_string(err)};
-    if (host_ids_n < (size_t)rows) {
-        if (host_ids) cudaFreeHost(host_ids);
-        host_ids = nullptr;
-        cuda_check(cudaMallocHost((void**)&host_ids, (size_t)std::max(rows, 64) * sizeof(int)), "allocating pinned memory");
-        host_ids_n = (size_t)std::max(rows, 64);
-    }
-    cuda_check(cudaMemcpyAsync(host_ids, d_out, (size_t)rows * sizeof(int), cudaMemcpyDeviceToHost, stream), "reading the drawn ids");
-    sync_and_check();
+        for (int r = 0; r < rows; ++r) {
+            const llmx_sampling& p = who[r]->params;
+            h_pen[r] = p.penalty, h_pen[rows + r] = p.presence_penalty, h_pen[2 * rows + r] = p.frequency_penalty;
+            const bool greedy = p.temp <= 0.0f;
+            all_greedy = all_greedy && greedy;
+            h_rows[r] = Row{p.temp, p.top_p, p.min_p, greedy ? 0.0f : who[r]->sampling.rng.unit(), p.top_k, who[r]->sampling.masked};
+        }
+        char* d = (char*)sample_buf.ptr;
+        cuda_check(cudaMemcpyAsync(d, h, (char*)(h_rows + rows) - h, cudaMemcpyHostToDevice, stream), "copying the sampling settings");
+        int* d_items = (int*)d;
+        float* d_pen = (float*)(d_items + 3 * items);
+        Row* d_rows = (Row*)(d_pen + 3 * rows);
+        int* d_out = (int*)(d_rows + rows);
+        if (items)
+            if (int err = penalize(cur_logits, vocab, d_items, d_items + items, d_items + 2 * items, d_pen, d_pen + rows,
+                                   d_pen + 2 * rows, (int)items, stream))
+                throw Failure{LLMX_ENGINE_ERR_DEVICE, "penalize: error " + std::to_string(err)};
+        if (int err = sample(cur_logits, rows, vocab, d_rows, d_out, all_greedy ? 1 : 0, stream))
+            throw Failure{LLMX_ENGINE_ERR_DEVICE, "sample: error " + std::to_string(err)};
+        if (host_ids_n < (size_t)rows) {
+            if (host_ids) cudaFreeHost(host_ids);
+            host_ids = nullptr;
+            cuda_check(cudaMallocHost((void**)&host_ids, (size_t)std::max(rows, 64) * sizeof(int)), "allocating pinned memory");
+            host_ids_n = (size_t)std::max(rows, 64);
+        }
+        cuda_check(cudaMemcpyAsync(host_ids, d_out, (size_t)rows * sizeof(int), cudaMemcpyDeviceToHost, stream), "reading the drawn ids");
+        sync_and_check();
     } catch (...) {
         for (int r = 0; r < rows; ++r) who[r]->sampling.rng.state = generators[r];
         throw;
