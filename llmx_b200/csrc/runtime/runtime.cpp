@@ -192,7 +192,8 @@ constexpr int HEADS_MIN_ROWS = 256;           // from this many tokens on the q/
 
 int gemm_schedule(int m, int n) { return m <= STREAM_K_MAX_ROWS && cdiv(n, 128) < STREAM_K_MAX_TILES ? 1 : 0; }
 
-struct GemmPlan { int schedule, token_tile, splits; };   // schedule 0: whole tiles, 1: stream-K, 2: on pairs of SMs (splits 0: only the last, partial round's tiles are cut)
+// schedule 0: whole tiles, 1: stream-K, 2: on pairs of SMs (there splits 0: only the last, partial round's tiles are cut)
+struct GemmPlan { int schedule, token_tile, splits; };
 // Which products of many tokens may run on pairs of SMs: a sum of PAIR_PLAIN, PAIR_GATED and PAIR_HEADS.
 enum : int { PAIR_PLAIN = 1, PAIR_GATED = 2, PAIR_HEADS = 4, PAIR_ALL = 7 };
 int g_pair_products = PAIR_ALL;
