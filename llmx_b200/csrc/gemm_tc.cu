@@ -16,7 +16,9 @@
 // of two ways:
 //   tiles     a block walks whole output tiles (blockIdx.x, + gridDim.x, ...), optionally with K
 //             cut into `splits` ranges that are added with float atomics; used for many tokens.
-//   stream-K  all (tile, k block) units are cut into gridDim.x equal runs; a block's run may end
+//   stream-K  all (tile, k block) units are cut into gridDim.x runs (the second half of the blocks a
+//             little shorter ones, so that they leave early and the next kernel's blocks come in two
+//             halves); a block's run may end
 //             one tile and begin the next, and every piece is added to C with float atomics
 //             (C is zeroed first when the product is to be stored).  A few tokens make few
 //             tiles; this keeps every SM streaming weights whatever N is.
@@ -76,13 +78,27 @@ struct Scheduler {
     int n_tiles, m_tiles, k_blocks, splits;
     bool wide_first;            // tiles schedule: the 128-row side's tiles vary fastest instead of the narrow side's
     long long cur, end;
-    __device__ Scheduler(int n_tiles_, int m_tiles_, int k_blocks_, int splits_, bool wide_first_ = false)
+    // `skew` (stream-K, percent): the first half of the blocks take that much more than an even share and the second
+    // half what is left, so the second half leaves early (see llmx_gemm_tc).
+    __device__ Scheduler(int n_tiles_, int m_tiles_, int k_blocks_, int splits_, bool wide_first_ = false, int skew = 0)
         : n_tiles(n_tiles_), m_tiles(m_tiles_), k_blocks(k_blocks_), splits(splits_), wide_first(wide_first_) {
         if (STREAMK) {
             const long long units = (long long)n_tiles * m_tiles * k_blocks;
-            const long long per = (units + gridDim.x - 1) / gridDim.x;
-            cur = per * blockIdx.x;
-            end = cur + per < units ? cur + per : units;
+            const long long blocks = gridDim.x, half = blocks / 2;
+            if (skew > 0 && blocks >= 8) {
+                const long long more = (units * (100 + skew) + 100 * blocks - 1) / (100 * blocks);
+                const long long rest = units > more * half ? units - more * half : 0;
+                const long long less = (rest + (blocks - half) - 1) / (blocks - half);
+                const long long b = blockIdx.x;
+                cur = b < half ? more * b : more * half + less * (b - half);
+                end = cur + (b < half ? more : less);
+                if (cur > units) cur = units;
+                if (end > units) end = units;
+            } else {
+                const long long per = (units + blocks - 1) / blocks;
+                cur = per * blockIdx.x;
+                end = cur + per < units ? cur + per : units;
+            }
         } else {
             cur = blockIdx.x;
             end = (long long)n_tiles * m_tiles * splits;
@@ -126,7 +142,7 @@ struct Scheduler {
 template <int BN, bool STREAMK, bool DUAL, bool HEADS>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
-               void* __restrict__ C_, int M, int N, int K, int mode, int splits, int* error_word,
+               void* __restrict__ C_, int M, int N, int K, int mode, int splits, int skew, int* error_word,
                const HeadsEpilogue hp) {
     // HEADS: `map_w` is the tokens' map and N their number, `map_a` the weight's and M its rows.
     using cfg = Cfg<BN, DUAL>;
@@ -180,7 +196,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // the output) is touched only after pdl_wait(), when the kernel before has finished.
     if (warp == 0) {
         if (tc::elect_one()) {
-            Scheduler<STREAMK> sched(n_tiles, m_tiles, k_blocks, splits, HEADS && n_tiles <= HEADS_TOKEN_FIRST_TILES);
+            Scheduler<STREAMK> sched(n_tiles, m_tiles, k_blocks, splits, HEADS && n_tiles <= HEADS_TOKEN_FIRST_TILES, skew);
             Work w;
             uint32_t stage = 0, phase = 0;
             bool ok = true, waited = false;
@@ -234,7 +250,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     } else if (warp == 1) {
         if (tc::elect_one()) {
             constexpr uint32_t idesc = tc::instr_desc_bf16(BM, BN);
-            Scheduler<STREAMK> sched(n_tiles, m_tiles, k_blocks, splits, HEADS && n_tiles <= HEADS_TOKEN_FIRST_TILES);
+            Scheduler<STREAMK> sched(n_tiles, m_tiles, k_blocks, splits, HEADS && n_tiles <= HEADS_TOKEN_FIRST_TILES, skew);
             Work w;
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
@@ -271,7 +287,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     } else {
         // Epilogue: warp w may read the tensor-memory lanes 32 * (w % 4) .. + 31.
         const int quarter = warp & 3;
-        Scheduler<STREAMK> sched(n_tiles, m_tiles, k_blocks, splits, HEADS && n_tiles <= HEADS_TOKEN_FIRST_TILES);
+        Scheduler<STREAMK> sched(n_tiles, m_tiles, k_blocks, splits, HEADS && n_tiles <= HEADS_TOKEN_FIRST_TILES, skew);
         Work w;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
@@ -372,8 +388,22 @@ int launch(const CUtensorMap& map_w, const void* A, void* C, int M, int N, int K
     }
     if (grid > (long long)g_sm_count * cfg::CTAS_PER_SM) grid = (long long)g_sm_count * cfg::CTAS_PER_SM;
     if (grid < 1) grid = 1;
+    // Stream-K: uneven shares.  With even shares all blocks of a product leave at one moment, the next kernel's blocks
+    // all arrive, set up and ask for their first weights at one moment, and for those microseconds nothing streams.
+    // With the second half of the blocks (the second block of every SM) given less, that half leaves early: the next
+    // product's first blocks take its place, set up and fill their stages while the first half still streams, and
+    // stream themselves while the rest arrives.  The shares differ by what the weights take to stream in STAGGER_NS
+    // (measured at Qwen3-8B sizes, decode at batch 8: 4.457 ms a step even, 4.423 with 3 us, 4.383 with 4 to 5 us,
+    // 4.463 with 7 us; batch 1: 3.309 -> 3.252).  Not for products that stream for less than that themselves (Qwen3-0.6B
+    // sizes, batch 8: 1.368 ms a step even, 1.418 with uneven shares).
+    int skew = 0;
+    if (STREAMK && grid >= 8) {
+        constexpr double STAGGER_NS = 4500.0, BYTES_PER_NS = 6500.0;
+        const double stream_ns = (double)N * K * 2 / BYTES_PER_NS;
+        if (stream_ns >= STAGGER_NS) skew = (int)(100.0 * STAGGER_NS / (2 * stream_ns) + 0.5);
+    }
     launch_kernel(gemm_tc_kernel<BN, STREAMK, DUAL, false>, dim3((unsigned)grid), dim3(THREADS), cfg::SMEM_BYTES, stream, 
-        map_w, map_a, C, M, N, K, mode, splits, error_word, HeadsEpilogue{});
+        map_w, map_a, C, M, N, K, mode, splits, skew, error_word, HeadsEpilogue{});
     return launch_status();
 }
 
@@ -394,7 +424,7 @@ int launch_heads(const CUtensorMap& map_weight, const void* A, int tokens, int f
     long long grid = (long long)((tokens + BM - 1) / BM) * ((features + BN - 1) / BN);
     if (grid > g_sm_count) grid = g_sm_count;
     launch_kernel(gemm_tc_kernel<BN, false, false, true>, dim3((unsigned)grid), dim3(THREADS), cfg::SMEM_BYTES, stream,
-        map_tokens, map_weight, (void*)nullptr, features, tokens, K, (int)MODE_STORE, 1, error_word, hp);
+        map_tokens, map_weight, (void*)nullptr, features, tokens, K, (int)MODE_STORE, 1, 0, error_word, hp);
     return launch_status();
 }
 

@@ -599,9 +599,10 @@ def test_sampling_distribution_and_independence_of_the_batch():
 
 
 @pytest.mark.parametrize("m", [1, 8, 33, 64])
-@pytest.mark.parametrize("n,k", [(128, 64), (100, 72), (1000, 160), (6144, 1024), (4096, 4096)])
+@pytest.mark.parametrize("n,k", [(128, 64), (100, 72), (1000, 160), (6144, 1024), (4096, 4096), (5000, 4104)])
 def test_gemm_tensor_core_stream_k(m, n, k):
-    """Few tokens: (tile, k block) units shared out evenly, pieces added with atomics."""
+    """Few tokens: (tile, k block) units shared out over the blocks, pieces added with atomics.  The two largest
+    weights stream long enough to get uneven shares (the second half of the blocks a shorter run each)."""
     from llmx_b200 import ops_tc
     g = torch.Generator().manual_seed(12)
     a = _bf16(torch.randn(m, k, generator=g)).to(DEV)
