@@ -126,6 +126,16 @@ def test_matrix_product_plan_fills_the_sms():
             assert -(-4096 // 128) * -(-m // tile) * splits >= 96
     finally:
         runtime.pair_products(before)
+    # 33 to 64 tokens: whole tiles of 64 tokens with K in equal ranges where those still fill three quarters of the 296
+    # blocks that run at once (fewer pieces to add up than stream-K makes); else stream-K, as up to 32 tokens
+    assert ops_tc._plan(64, 4096, 4096, True, sms) == (0, 64, 8)
+    assert ops_tc._plan(40, 6144, 4096, False, sms) == (0, 64, 6)
+    assert ops_tc._plan(64, 24576, 4096, False, sms) == (1, 0, 1)          # 192 tiles: one range each would leave a third of the blocks idle
+    assert ops_tc._plan(32, 4096, 4096, True, sms) == (1, 0, 1)
+    # many tokens on pairs of SMs: where the tiles leave a partial last round (128 pair tiles on 74 pairs), only that
+    # round's tiles are cut (splits 0), and only for a product that adds to its output or is cleared first
+    assert ops_tc._plan(2048, 4096, 12288, True, sms) == (2, 256, 0)
+    assert ops_tc._plan(8192, 4096, 12288, True, sms) == (2, 256, 1)        # 512 tiles: 6.9 rounds, nothing to cut
     # many tokens: whole tiles fill the SMs by themselves
     assert ops_tc._plan(4096, 6144, 4096, False, sms)[2] == 1
     # k ranges never outnumber the k blocks
