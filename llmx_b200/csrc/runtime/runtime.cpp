@@ -186,7 +186,7 @@ inline size_t elem(int dtype) { return dtype == LLMX_DT_BF16 ? 2 : 4; }
 // ---------------------------------------------------------------------------------------------------------------
 // Launch decisions of the tensor-core product.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int STREAM_K_MAX_ROWS = 64;         // at most this many tokens: few tiles, so (tile, k block) units are shared out evenly
+constexpr int STREAM_K_MAX_ROWS = 64;         // at most this many tokens: few tiles, so (tile, k block) units are shared out over all blocks
 constexpr int STREAM_K_MAX_TILES = 4 * 148;   // ... unless the weight alone makes plenty of tiles (the logits head)
 constexpr int HEADS_MIN_ROWS = 256;           // from this many tokens on the q/k/v product finishes its heads itself
 

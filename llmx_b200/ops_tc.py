@@ -60,7 +60,7 @@ def weight_map(weight: torch.Tensor) -> WeightMap:
     return m
 
 
-STREAM_K_MAX_ROWS = 64          # at most this many tokens: few tiles, so (tile, k block) units are shared out evenly
+STREAM_K_MAX_ROWS = 64          # at most this many tokens: few tiles, so (tile, k block) units are shared out over all blocks
 
 _sm_count = 0
 
@@ -96,7 +96,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
     """out (+)= a @ w.T; a [M, K] bfloat16, w [N, K] bfloat16, out float32 [M, N].
 
     schedule 0 walks whole tiles (`splits` > 1 cuts K and adds the pieces with atomics); schedule 1
-    (stream-K) shares out (tile, k block) units evenly and adds every piece with atomics; schedule 2 walks whole
+    (stream-K) shares out (tile, k block) units over all blocks (in two sizes of run, csrc/gemm_tc.cu) and adds every piece with atomics; schedule 2 walks whole
     tiles of 256 weight rows on pairs of SMs (`gemm_tc_pair`; `splits` 0: the tiles of the last, partial round are cut there).  Whenever pieces
     are added, `out` is zeroed first unless accumulating.  By default `plan` chooses: stream-K for few
     tokens, else the kernel, token tile and k ranges that fill the SMs.
