@@ -130,7 +130,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
                    int kv_heads, int window, float scale_log2, int splits, const int* __restrict__ chunk_ptr,
                    int chunk_keys, int* __restrict__ counters, int* error_word, const QkvInput made, int cluster_merge) {
     pdl_trigger();
-    pdl_wait();
+    // What the kernel before this one writes (the queries or the product's output, this step's keys and values) is
+    // touched only after pdl_wait(), which every warp reaches on its own path below.  The step's metadata and the
+    // pages that lie wholly below the request's history were written before the step began: the producer asks for
+    // those pages at once, while the kernel before still runs.
     using cfg = Cfg<D>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ int is_last;
@@ -170,6 +173,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
     __syncthreads();          // the barriers are ready
     // The producer warp starts the key stages at once; the other warps meanwhile make the block's queries and new
     // keys (if it is given the product's output) and meet at a barrier of their own before they use them.
+    if (warp != CONSUMERS) pdl_wait();
     if constexpr (D == 128) {
         if (made.qkv && warp < CONSUMERS) {
             for (int i = warp; i < M; i += CONSUMERS) {
@@ -217,6 +221,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
         // One lane per page of a stage: each reads its page's id from the block table (one stage ahead, so the
         // table's latency is off the copies' path) and issues its copy; a single thread issuing all of a
         // stage's copies was what bounded a block's rate.
+        bool waited = false;
         if (n_pages > 0 && lane < PAGES_PER_STAGE) {
             if (lane == 0) tc::tma_prefetch_desc(&cache_map);
             const int* table = block_tables + (size_t)r * table_stride + kv_begin / PAGE;
@@ -224,6 +229,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
             for (int it = 0; it < iters; ++it) {
                 const int stage = it % STAGES;
                 const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
+                // A stage whose pages end at or below the history holds earlier steps' keys only: no need to wait.
+                if (!waited && kv_begin + (it + 1) * PAGES_PER_STAGE * PAGE > hist) {
+                    pdl_wait();
+                    waited = true;
+                }
                 const int id = id_next;
                 const int nxt = (it + 1) * PAGES_PER_STAGE + lane;
                 id_next = nxt < n_pages ? max(table[nxt], 0) : 0;
@@ -240,6 +250,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap cache_map, const __nv_bfl
                                     id * 2, &full_bar[stage]);
             }
         }
+        if (!waited) pdl_wait();      // every thread has waited before the block's results are written
     } else {
         // ---- query fragments: row i of the tile is (new row i / ratio, head g * ratio + i % ratio)
         uint32_t qa[D / 16][4];
