@@ -15,6 +15,7 @@ from __future__ import annotations
 import ctypes
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -156,10 +157,11 @@ def build(name: str, verbose: bool = True) -> str:
             pass
         raise BuildError(f"nvcc failed for {name}:\n{' '.join(cmd)}\n{log}")
     os.replace(tmp, out)
-    # Older builds of the same library are of no further use.
-    prefix = f"llmx_{name}_"
+    # Older builds of the same library are of no further use (the digest is 16 hex digits: `gemm_tc_pair` is no older
+    # build of `gemm_tc`).
+    older = re.compile(rf"llmx_{re.escape(name)}_[0-9a-f]{{16}}\.so")
     for f in os.listdir(os.path.dirname(out)):
-        if f.startswith(prefix) and f.endswith(".so") and os.path.join(os.path.dirname(out), f) != out:
+        if older.fullmatch(f) and os.path.join(os.path.dirname(out), f) != out:
             try:
                 os.remove(os.path.join(os.path.dirname(out), f))
             except OSError:

@@ -59,7 +59,7 @@ def driver(tmp_path_factory):
     """The C++ program, compiled against the header and linked with the built runtime library."""
     from llmx_b200.csrc import build
     runtime_so = build.build("runtime")
-    for name in ("rowwise", "gemm_plain", "attention_plain", "gemm_tc", "attention_decode", "attention_prefill", "attention_prefill_tc"):
+    for name in build.LIBRARIES:           # the program cannot compile what it finds missing: everything is built first
         build.build(name)
     exe = str(tmp_path_factory.mktemp("native") / "drive_model")
     include = os.path.join(os.path.dirname(build.__file__), "runtime")
