@@ -6,7 +6,9 @@
 //
 //   producer warp    walks the request's block table and fetches its pages with TMA
 //                    (boxes of [16 slots, 64 columns], 128-byte swizzle), four pages a stage, one
-//                    lane issuing each page's copy, three stages in flight
+//                    lane issuing each page's copy, three stages in flight; stages whose pages lie wholly
+//                    below the request's history (earlier steps' keys) are asked for before the kernel
+//                    waits for the kernel before it
 //   4 consumer warps warps 0-1 take the even stages, warps 2-3 the odd ones; of a stage's four pages a warp
 //                    takes two as one tile of 32 keys: S = Q K^T (mma.sync m16n8k16, bfloat16 in,
 //                    float32 out), masks (causal, window, end of the key range), online softmax
