@@ -127,6 +127,19 @@ def library_path(name: str) -> str:
     return os.path.join(_build_dir(), f"llmx_{name}_{_digest(name)}.so")
 
 
+def _remove_older_builds(name: str, keep: str) -> None:
+    """Older builds of library `name` beside `keep` are of no further use.  A build's file is the library's name and 16
+    hex digits of digest: `llmx_gemm_tc_pair_<digest>.so` is no older build of `gemm_tc`."""
+    older = re.compile(rf"llmx_{re.escape(name)}_[0-9a-f]{{16}}\.so")
+    folder = os.path.dirname(keep)
+    for f in os.listdir(folder):
+        if older.fullmatch(f) and os.path.join(folder, f) != keep:
+            try:
+                os.remove(os.path.join(folder, f))
+            except OSError:
+                pass
+
+
 def build(name: str, verbose: bool = True) -> str:
     """Compile library `name` if its up-to-date build is missing; return the path."""
     if name not in LIBRARIES:
@@ -157,15 +170,7 @@ def build(name: str, verbose: bool = True) -> str:
             pass
         raise BuildError(f"nvcc failed for {name}:\n{' '.join(cmd)}\n{log}")
     os.replace(tmp, out)
-    # Older builds of the same library are of no further use (the digest is 16 hex digits: `gemm_tc_pair` is no older
-    # build of `gemm_tc`).
-    older = re.compile(rf"llmx_{re.escape(name)}_[0-9a-f]{{16}}\.so")
-    for f in os.listdir(os.path.dirname(out)):
-        if older.fullmatch(f) and os.path.join(os.path.dirname(out), f) != out:
-            try:
-                os.remove(os.path.join(os.path.dirname(out), f))
-            except OSError:
-                pass
+    _remove_older_builds(name, out)
     if verbose:
         print(f"[llmx_b200] compiled {name} in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
     return out

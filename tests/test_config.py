@@ -201,3 +201,17 @@ def test_yarn_forced_over_the_files_rope():
     for given in ({"--yarn": "1"}, {"--yarn": "0.5"}, {"--yarn-original-ctx": "128"}, {"--yarn": "2", "--yarn-original-ctx": "0"}):
         with pytest.raises(UsageError):
             _yarn(given)
+
+
+def test_a_rebuilt_library_removes_its_own_older_builds_only(tmp_path):
+    """Build files are `llmx_<library>_<16 hex digits>.so`; `gemm_tc_pair` and `attention_prefill_tc` are libraries of
+    their own, not older builds of `gemm_tc` and `attention_prefill`."""
+    from llmx_b200.csrc import build
+    names = ["llmx_gemm_tc_0123456789abcdef.so", "llmx_gemm_tc_fedcba9876543210.so", "llmx_gemm_tc_pair_0123456789abcdef.so",
+             "llmx_attention_prefill_tc_0123456789abcdef.so", "llmx_gemm_tc_0123456789abcdef.so.123.tmp", "notes.txt"]
+    for n in names:
+        (tmp_path / n).write_bytes(b"")
+    build._remove_older_builds("gemm_tc", str(tmp_path / "llmx_gemm_tc_fedcba9876543210.so"))
+    assert sorted(p.name for p in tmp_path.iterdir()) == sorted(n for n in names if n != "llmx_gemm_tc_0123456789abcdef.so")
+    build._remove_older_builds("attention_prefill", str(tmp_path / "llmx_attention_prefill_0000000000000000.so"))
+    assert (tmp_path / "llmx_attention_prefill_tc_0123456789abcdef.so").exists()
