@@ -215,3 +215,14 @@ def test_a_rebuilt_library_removes_its_own_older_builds_only(tmp_path):
     assert sorted(p.name for p in tmp_path.iterdir()) == sorted(n for n in names if n != "llmx_gemm_tc_0123456789abcdef.so")
     build._remove_older_builds("attention_prefill", str(tmp_path / "llmx_attention_prefill_0000000000000000.so"))
     assert (tmp_path / "llmx_attention_prefill_tc_0123456789abcdef.so").exists()
+
+
+def test_bench_refuses_more_than_one_gpu_in_one_line():
+    """`bench.py --gpus N` for N > 1: one line that says so, exit code 2, before anything of CUDA is touched."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    done = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--gpus", "2"], capture_output=True, text=True, timeout=120)
+    assert done.returncode == 2
+    assert len(done.stdout.strip().splitlines()) == 1 and "one GPU" in done.stdout
